@@ -1,0 +1,426 @@
+"""Engine configuration.
+
+Plain dataclasses, validated on construction, grouped the way the reference
+groups them (``aphrodite/config/*.py``: model, cache, parallel, scheduler,
+speculative, observability) and gathered in one ``EngineConfig`` (the
+reference's ``AphroditeConfig``, ``config/aphrodite.py``).  ``EngineArgs``
+is the flat user-facing form (``aphrodite/engine/arg_utils.py``): every field
+is a keyword of ``LLM(...)`` and a ``--flag`` of the CLI.
+"""
+from __future__ import annotations
+
+import argparse
+import dataclasses
+import json
+import os
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+
+_DTYPES = {
+    "auto": None, "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+    "float16": torch.float16, "half": torch.float16, "fp16": torch.float16,
+    "float32": torch.float32, "float": torch.float32, "fp32": torch.float32,
+}
+
+# Architectures that can be instantiated by name with random weights (there is
+# no network for checkpoints on a benchmark box).  Values are HF-style config
+# dictionaries.
+ARCH_PRESETS: dict[str, dict[str, Any]] = {
+    "qwen3-0.6b": dict(
+        architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=28, hidden_size=1024,
+        num_attention_heads=16, num_key_value_heads=8, head_dim=128, intermediate_size=3072,
+        vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=True,
+        max_position_embeddings=40960),
+    "llama-3-8b": dict(
+        architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=32, hidden_size=4096,
+        num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336,
+        vocab_size=128256, rope_theta=5e5, rms_norm_eps=1e-5, tie_word_embeddings=False,
+        max_position_embeddings=8192),
+    "llama-3-70b": dict(
+        architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=80, hidden_size=8192,
+        num_attention_heads=64, num_key_value_heads=8, head_dim=128, intermediate_size=28672,
+        vocab_size=128256, rope_theta=5e5, rms_norm_eps=1e-5, tie_word_embeddings=False,
+        max_position_embeddings=8192),
+    "qwen3-30b-a3b": dict(
+        architectures=["Qwen3MoeForCausalLM"], model_type="qwen3_moe", num_hidden_layers=48, hidden_size=2048,
+        num_attention_heads=32, num_key_value_heads=4, head_dim=128, intermediate_size=6144,
+        moe_intermediate_size=768, num_experts=128, num_experts_per_tok=8, norm_topk_prob=True,
+        vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False,
+        max_position_embeddings=40960),
+    "deepseek-v3.2": dict(
+        architectures=["DeepseekV32ForCausalLM"], model_type="deepseek_v32", num_hidden_layers=61,
+        hidden_size=7168, num_attention_heads=128, num_key_value_heads=128, q_lora_rank=1536,
+        kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128,
+        index_n_heads=64, index_head_dim=128, index_topk=2048, n_routed_experts=256, n_shared_experts=1,
+        num_experts_per_tok=8, n_group=8, topk_group=4, moe_intermediate_size=2048,
+        first_k_dense_replace=3, intermediate_size=18432, routed_scaling_factor=2.5,
+        scoring_func="sigmoid", norm_topk_prob=True, vocab_size=129280, rope_theta=1e4,
+        rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=163840),
+    # tiny shapes for tests and smoke runs (same code paths, seconds on CPU)
+    "tiny-llama": dict(
+        architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=2, hidden_size=256,
+        num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=512,
+        vocab_size=1024, rope_theta=1e4, rms_norm_eps=1e-5, tie_word_embeddings=False,
+        max_position_embeddings=2048),
+    "tiny-llama-128": dict(
+        architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=2, hidden_size=512,
+        num_attention_heads=4, num_key_value_heads=2, head_dim=128, intermediate_size=1024,
+        vocab_size=2048, rope_theta=5e5, rms_norm_eps=1e-5, tie_word_embeddings=False,
+        max_position_embeddings=4096),
+    "tiny-qwen3": dict(
+        architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=256,
+        num_attention_heads=4, num_key_value_heads=2, head_dim=128, intermediate_size=512,
+        vocab_size=1024, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=True,
+        max_position_embeddings=2048),
+    "tiny-qwen3-moe": dict(
+        architectures=["Qwen3MoeForCausalLM"], model_type="qwen3_moe", num_hidden_layers=2, hidden_size=256,
+        num_attention_heads=4, num_key_value_heads=2, head_dim=128, intermediate_size=512,
+        moe_intermediate_size=128, num_experts=8, num_experts_per_tok=2, norm_topk_prob=True,
+        vocab_size=1024, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False,
+        max_position_embeddings=2048),
+    "tiny-deepseek": dict(
+        architectures=["DeepseekV32ForCausalLM"], model_type="deepseek_v32", num_hidden_layers=3,
+        hidden_size=256, num_attention_heads=4, num_key_value_heads=4, q_lora_rank=96,
+        kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32,
+        index_n_heads=4, index_head_dim=32, index_topk=16, n_routed_experts=8, n_shared_experts=1,
+        num_experts_per_tok=2, n_group=4, topk_group=2, moe_intermediate_size=64,
+        first_k_dense_replace=1, intermediate_size=512, routed_scaling_factor=2.5,
+        scoring_func="sigmoid", norm_topk_prob=True, vocab_size=1024, rope_theta=1e4,
+        rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=2048),
+}
+
+
+def _resolve_hf_config(model: str) -> tuple[dict[str, Any], str | None]:
+    """Return (hf config dict, checkpoint dir or None)."""
+    key = model.lower()
+    if key in ARCH_PRESETS:
+        return dict(ARCH_PRESETS[key]), None
+    cfg_path = os.path.join(model, "config.json")
+    if os.path.isdir(model) and os.path.isfile(cfg_path):
+        with open(cfg_path) as f:
+            return json.load(f), model
+    raise ValueError(
+        f"model {model!r} is neither a built-in architecture preset ({', '.join(sorted(ARCH_PRESETS))}) "
+        "nor a local directory with config.json (no hub access in this build)")
+
+
+@dataclass
+class ModelConfig:
+    model: str
+    hf_config: dict[str, Any] = field(default_factory=dict)
+    checkpoint_dir: str | None = None
+    tokenizer: str | None = None
+    dtype: torch.dtype = torch.bfloat16
+    seed: int = 0
+    max_model_len: int = 0
+    quantization: str | None = None          # None | "fp8" (128x128 block scales)
+    load_format: str = "auto"                # auto | safetensors | dummy
+    skip_tokenizer_init: bool = False
+    served_model_name: str | None = None
+    generation_config: dict[str, Any] = field(default_factory=dict)
+
+    def __post_init__(self) -> None:
+        if not self.hf_config:
+            self.hf_config, ckpt = _resolve_hf_config(self.model)
+            self.checkpoint_dir = self.checkpoint_dir or ckpt
+        if self.load_format == "auto":
+            self.load_format = "safetensors" if self.checkpoint_dir else "dummy"
+        if self.tokenizer is None and self.checkpoint_dir is not None:
+            self.tokenizer = self.checkpoint_dir
+        qc = self.hf_config.get("quantization_config")
+        if self.quantization is None and isinstance(qc, dict) and qc.get("quant_method") == "fp8":
+            self.quantization = "fp8"
+        if self.quantization not in (None, "fp8"):
+            raise ValueError(f"unsupported quantization {self.quantization!r}; supported: fp8")
+        derived = int(self.hf_config.get("max_position_embeddings", 8192))
+        if not self.max_model_len:
+            self.max_model_len = derived
+        if self.checkpoint_dir:
+            gc = os.path.join(self.checkpoint_dir, "generation_config.json")
+            if os.path.isfile(gc) and not self.generation_config:
+                with open(gc) as f:
+                    self.generation_config = json.load(f)
+        self.served_model_name = self.served_model_name or self.model
+
+    # convenience accessors ------------------------------------------------
+    def get(self, key: str, default: Any = None) -> Any:
+        return self.hf_config.get(key, default)
+
+    @property
+    def architecture(self) -> str:
+        return self.hf_config["architectures"][0]
+
+    @property
+    def vocab_size(self) -> int:
+        return int(self.hf_config["vocab_size"])
+
+    @property
+    def hidden_size(self) -> int:
+        return int(self.hf_config["hidden_size"])
+
+    @property
+    def num_layers(self) -> int:
+        return int(self.hf_config["num_hidden_layers"])
+
+    @property
+    def num_attention_heads(self) -> int:
+        return int(self.hf_config["num_attention_heads"])
+
+    @property
+    def num_kv_heads(self) -> int:
+        return int(self.hf_config.get("num_key_value_heads", self.num_attention_heads))
+
+    @property
+    def head_dim(self) -> int:
+        hd = self.hf_config.get("head_dim")
+        return int(hd) if hd else self.hidden_size // self.num_attention_heads
+
+    @property
+    def is_mla(self) -> bool:
+        return self.hf_config.get("kv_lora_rank") is not None
+
+    @property
+    def eos_token_id(self) -> int | list[int] | None:
+        return self.generation_config.get("eos_token_id", self.hf_config.get("eos_token_id"))
+
+
+@dataclass
+class CacheConfig:
+    block_size: int = 16
+    gpu_memory_utilization: float = 0.90
+    num_gpu_blocks_override: int | None = None
+    enable_prefix_caching: bool = True
+    prefix_caching_hash_algo: str = "sha256"   # sha256 | builtin
+    cache_dtype: str = "auto"                  # auto | fp8
+    swap_space_gb: float = 0.0
+    kv_offload_cpu_gb: float = 0.0
+    sliding_window: int | None = None
+
+    def __post_init__(self) -> None:
+        if self.block_size not in (8, 16, 32, 64, 128):
+            raise ValueError(f"block_size must be one of 8/16/32/64/128, got {self.block_size}")
+        if not 0.0 < self.gpu_memory_utilization <= 1.0:
+            raise ValueError("gpu_memory_utilization must be in (0, 1]")
+        if self.cache_dtype not in ("auto", "fp8", "fp8_e4m3", "bfloat16", "float16"):
+            raise ValueError(f"unsupported kv cache dtype {self.cache_dtype}")
+        if self.cache_dtype == "fp8_e4m3":
+            self.cache_dtype = "fp8"
+
+
+@dataclass
+class ParallelConfig:
+    tensor_parallel_size: int = 1
+    pipeline_parallel_size: int = 1
+    data_parallel_size: int = 1
+    enable_expert_parallel: bool = False
+    decode_context_parallel_size: int = 1
+    prefill_context_parallel_size: int = 1
+    expert_placement: str = "linear"            # linear | round_robin
+    all2all_backend: str = "fused_nvlink"       # fused_nvlink | allgather_reducescatter
+    enable_eplb: bool = False
+    eplb_window: int = 1000
+    eplb_interval: int = 3000
+    num_redundant_experts: int = 0
+    distributed_executor_backend: str | None = None   # None | uni | mp | external_launcher
+    data_parallel_rank: int = 0
+    enable_sequence_parallel: bool = True        # fused RS/AG GEMM path inside the TP group
+    disable_custom_all_reduce: bool = False
+
+    def __post_init__(self) -> None:
+        for name in ("tensor_parallel_size", "pipeline_parallel_size", "data_parallel_size",
+                     "decode_context_parallel_size", "prefill_context_parallel_size"):
+            if getattr(self, name) < 1:
+                raise ValueError(f"{name} must be >= 1")
+        if self.tensor_parallel_size % self.decode_context_parallel_size:
+            raise ValueError("decode_context_parallel_size must divide tensor_parallel_size")
+        if self.expert_placement not in ("linear", "round_robin"):
+            raise ValueError("expert_placement must be linear or round_robin")
+
+    @property
+    def world_size(self) -> int:
+        """Ranks inside one engine replica (DP replicas are separate engines
+        unless expert parallelism spans them)."""
+        return self.tensor_parallel_size * self.pipeline_parallel_size * self.prefill_context_parallel_size
+
+    @property
+    def world_size_across_dp(self) -> int:
+        return self.world_size * self.data_parallel_size
+
+
+@dataclass
+class SchedulerConfig:
+    max_num_batched_tokens: int = 8192
+    max_num_seqs: int = 256
+    max_model_len: int = 8192
+    enable_chunked_prefill: bool = True
+    long_prefill_token_threshold: int = 0
+    max_num_partial_prefills: int = 1
+    policy: str = "fcfs"                         # fcfs | priority
+    async_scheduling: bool = False
+    watermark: float = 0.01
+
+    def __post_init__(self) -> None:
+        if self.policy not in ("fcfs", "priority"):
+            raise ValueError("scheduling policy must be fcfs or priority")
+        if self.max_num_seqs < 1 or self.max_num_batched_tokens < 1:
+            raise ValueError("max_num_seqs and max_num_batched_tokens must be positive")
+        if not self.enable_chunked_prefill and self.max_num_batched_tokens < self.max_model_len:
+            raise ValueError("without chunked prefill the token budget must cover max_model_len")
+
+
+@dataclass
+class SpeculativeConfig:
+    method: str | None = None          # None | ngram
+    num_speculative_tokens: int = 0
+    prompt_lookup_max: int = 4
+    prompt_lookup_min: int = 2
+
+
+@dataclass
+class ObservabilityConfig:
+    log_stats: bool = False
+    trace_file: str | None = None
+    collect_kv_events: bool = False
+
+
+@dataclass
+class EngineConfig:
+    model: ModelConfig
+    cache: CacheConfig
+    parallel: ParallelConfig
+    scheduler: SchedulerConfig
+    speculative: SpeculativeConfig = field(default_factory=SpeculativeConfig)
+    observability: ObservabilityConfig = field(default_factory=ObservabilityConfig)
+    enforce_eager: bool = False
+    device: str = "auto"               # auto | cuda | cpu
+
+    def __post_init__(self) -> None:
+        self.scheduler.max_model_len = self.model.max_model_len
+        if self.device == "auto":
+            self.device = "cuda" if torch.cuda.is_available() else "cpu"
+        if self.device == "cpu" and self.model.dtype == torch.bfloat16 and self.model.load_format == "dummy" \
+                and os.environ.get("SONAR_CPU_KEEP_DTYPE") is None:
+            pass  # dtype is honoured as given; CPU tests pass float32 explicitly
+        tp = self.parallel.tensor_parallel_size
+        if self.model.num_attention_heads % tp:
+            raise ValueError(f"tensor_parallel_size {tp} must divide {self.model.num_attention_heads} heads")
+
+
+@dataclass
+class EngineArgs:
+    """Flat user-facing argument set → ``EngineConfig``."""
+    model: str = "tiny-llama"
+    tokenizer: str | None = None
+    skip_tokenizer_init: bool = False
+    dtype: str = "auto"
+    seed: int = 0
+    max_model_len: int | None = None
+    quantization: str | None = None
+    load_format: str = "auto"
+    served_model_name: str | None = None
+    hf_overrides: dict[str, Any] | None = None
+    # cache
+    block_size: int = 16
+    gpu_memory_utilization: float = 0.90
+    num_gpu_blocks_override: int | None = None
+    enable_prefix_caching: bool = True
+    prefix_caching_hash_algo: str = "sha256"
+    kv_cache_dtype: str = "auto"
+    # parallel
+    tensor_parallel_size: int = 1
+    pipeline_parallel_size: int = 1
+    data_parallel_size: int = 1
+    enable_expert_parallel: bool = False
+    decode_context_parallel_size: int = 1
+    prefill_context_parallel_size: int = 1
+    expert_placement: str = "linear"
+    all2all_backend: str = "fused_nvlink"
+    enable_eplb: bool = False
+    distributed_executor_backend: str | None = None
+    disable_custom_all_reduce: bool = False
+    # scheduler
+    max_num_batched_tokens: int | None = None
+    max_num_seqs: int = 256
+    enable_chunked_prefill: bool = True
+    long_prefill_token_threshold: int = 0
+    scheduling_policy: str = "fcfs"
+    async_scheduling: bool = False
+    # speculative
+    speculative_method: str | None = None
+    num_speculative_tokens: int = 0
+    # misc
+    enforce_eager: bool = False
+    device: str = "auto"
+    disable_log_stats: bool = True
+    trace_file: str | None = None
+
+    def create_engine_config(self) -> EngineConfig:
+        dtype = _DTYPES.get(self.dtype, "bad")
+        if dtype == "bad":
+            raise ValueError(f"unknown dtype {self.dtype!r}")
+        device = self.device
+        if device == "auto":
+            device = "cuda" if torch.cuda.is_available() else "cpu"
+        if dtype is None:
+            dtype = torch.bfloat16 if device == "cuda" else torch.float32
+        model = ModelConfig(
+            model=self.model, tokenizer=self.tokenizer, dtype=dtype, seed=self.seed,
+            max_model_len=self.max_model_len or 0, quantization=self.quantization,
+            load_format=self.load_format, skip_tokenizer_init=self.skip_tokenizer_init,
+            served_model_name=self.served_model_name)
+        if self.hf_overrides:
+            model.hf_config.update(self.hf_overrides)
+        cache = CacheConfig(
+            block_size=self.block_size, gpu_memory_utilization=self.gpu_memory_utilization,
+            num_gpu_blocks_override=self.num_gpu_blocks_override,
+            enable_prefix_caching=self.enable_prefix_caching,
+            prefix_caching_hash_algo=self.prefix_caching_hash_algo, cache_dtype=self.kv_cache_dtype)
+        parallel = ParallelConfig(
+            tensor_parallel_size=self.tensor_parallel_size,
+            pipeline_parallel_size=self.pipeline_parallel_size,
+            data_parallel_size=self.data_parallel_size,
+            enable_expert_parallel=self.enable_expert_parallel,
+            decode_context_parallel_size=self.decode_context_parallel_size,
+            prefill_context_parallel_size=self.prefill_context_parallel_size,
+            expert_placement=self.expert_placement, all2all_backend=self.all2all_backend,
+            enable_eplb=self.enable_eplb,
+            distributed_executor_backend=self.distributed_executor_backend,
+            disable_custom_all_reduce=self.disable_custom_all_reduce)
+        budget = self.max_num_batched_tokens
+        if budget is None:
+            budget = 8192 if self.enable_chunked_prefill else max(model.max_model_len, 8192)
+        sched = SchedulerConfig(
+            max_num_batched_tokens=budget, max_num_seqs=self.max_num_seqs,
+            max_model_len=model.max_model_len, enable_chunked_prefill=self.enable_chunked_prefill,
+            long_prefill_token_threshold=self.long_prefill_token_threshold,
+            policy=self.scheduling_policy, async_scheduling=self.async_scheduling)
+        spec = SpeculativeConfig(method=self.speculative_method,
+                                 num_speculative_tokens=self.num_speculative_tokens)
+        obs = ObservabilityConfig(log_stats=not self.disable_log_stats, trace_file=self.trace_file)
+        return EngineConfig(model=model, cache=cache, parallel=parallel, scheduler=sched,
+                            speculative=spec, observability=obs,
+                            enforce_eager=self.enforce_eager, device=device)
+
+    # CLI ------------------------------------------------------------------
+    @staticmethod
+    def add_cli_args(parser: argparse.ArgumentParser) -> argparse.ArgumentParser:
+        for f in dataclasses.fields(EngineArgs):
+            flag = "--" + f.name.replace("_", "-")
+            if f.name == "model":
+                continue  # positional / --model handled by the caller
+            if f.type in ("bool", bool):
+                parser.add_argument(flag, action=argparse.BooleanOptionalAction, default=f.default)
+            elif f.name == "hf_overrides":
+                parser.add_argument(flag, type=json.loads, default=None)
+            else:
+                base = str(f.type).replace(" | None", "")
+                conv = {"int": int, "float": float, "str": str}.get(base, str)
+                parser.add_argument(flag, type=conv, default=f.default)
+        return parser
+
+    @classmethod
+    def from_cli_args(cls, ns: argparse.Namespace) -> "EngineArgs":
+        names = {f.name for f in dataclasses.fields(cls)}
+        return cls(**{k: v for k, v in vars(ns).items() if k in names})

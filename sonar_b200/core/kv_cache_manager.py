@@ -1,0 +1,202 @@
+"""Per-request block tables on top of ``BlockPool``.
+
+One manager per KV-cache *group* (layers that share a block table).  The
+default model has a single full-attention group; sliding-window layers use
+``SlidingWindowPolicy`` to return blocks that slid out of the window, and MLA
+models differ only in bytes per block (``KVCacheSpec``).
+
+Parity: ``aphrodite/v1/core/kv_cache_manager.py:108-560``
+(``get_computed_blocks``, ``allocate_slots``, ``free``),
+``single_type_kv_cache_manager.py`` (full / sliding-window managers) and the
+spec classes of ``v1/kv_cache_interface.py:100-860``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+from sonar_b200.core.block_pool import NULL_BLOCK, BlockPool
+from sonar_b200.request import Request
+
+
+@dataclass(frozen=True)
+class KVCacheSpec:
+    """Shape of one layer's cache page."""
+    block_size: int
+    num_kv_heads: int
+    head_size: int
+    dtype_bytes: int
+    kind: str = "full"            # full | sliding_window | mla
+    sliding_window: int | None = None
+    # MLA stores one latent row (kv_lora_rank + rope dim) per token, no K/V split
+    mla_row: int = 0
+
+    @property
+    def page_bytes(self) -> int:
+        if self.kind == "mla":
+            return self.block_size * self.mla_row * self.dtype_bytes
+        return 2 * self.block_size * self.num_kv_heads * self.head_size * self.dtype_bytes
+
+
+@dataclass
+class KVCacheConfig:
+    num_blocks: int
+    num_layers: int
+    spec: KVCacheSpec
+
+    @property
+    def bytes_total(self) -> int:
+        return self.num_blocks * self.num_layers * self.spec.page_bytes
+
+
+def get_kv_cache_config(spec: KVCacheSpec, num_layers: int, available_bytes: int,
+                        max_model_len: int, override: int | None = None) -> KVCacheConfig:
+    """Turn a byte budget into a block count; refuse a budget that cannot hold
+    even one sequence of ``max_model_len`` tokens."""
+    per_block = spec.page_bytes * num_layers
+    num_blocks = override if override is not None else available_bytes // per_block
+    need = -(-max_model_len // spec.block_size) + 1
+    if num_blocks < need:
+        raise ValueError(
+            f"KV cache of {num_blocks} blocks cannot hold one sequence of max_model_len={max_model_len} "
+            f"({need} blocks of {spec.block_size} tokens needed); lower max_model_len or raise "
+            "gpu_memory_utilization")
+    return KVCacheConfig(num_blocks=int(num_blocks), num_layers=num_layers, spec=spec)
+
+
+class KVCacheManager:
+    def __init__(self, num_blocks: int, block_size: int, enable_caching: bool = True,
+                 sliding_window: int | None = None, collect_events: bool = False,
+                 watermark: float = 0.0) -> None:
+        self.block_size = block_size
+        self.enable_caching = enable_caching
+        self.sliding_window = sliding_window
+        self.pool = BlockPool(num_blocks, enable_caching, collect_events)
+        self.req_blocks: dict[str, list[int]] = {}
+        self.num_cached_blocks: dict[str, int] = {}
+        self.watermark_blocks = int(watermark * num_blocks)
+        self.prefix_queries = 0
+        self.prefix_hits = 0
+
+    # ------------------------------------------------------------------
+    @property
+    def usage(self) -> float:
+        return self.pool.get_usage()
+
+    def get_block_ids(self, request_id: str) -> list[int]:
+        return self.req_blocks.get(request_id, [])
+
+    def get_computed_blocks(self, request: Request) -> tuple[list[int], int]:
+        """Longest cached prefix of the request.  At least one token is always
+        left to compute so the step yields logits."""
+        if not self.enable_caching:
+            return [], 0
+        if request.sampling_params is not None and request.sampling_params.prompt_logprobs is not None:
+            return [], 0
+        max_blocks = (request.num_tokens - 1) // self.block_size
+        hit: list[int] = []
+        for h in request.block_hashes[:max_blocks]:
+            b = self.pool.get_cached_block(h)
+            if b is None:
+                break
+            hit.append(b)
+        if self.sliding_window is not None and hit:
+            # only the blocks overlapping the window of the first new token matter
+            first_needed = max(0, (len(hit) * self.block_size - self.sliding_window + 1)) // self.block_size
+            hit = [NULL_BLOCK] * first_needed + hit[first_needed:]
+        n_tok = len(hit) * self.block_size
+        self.prefix_queries += request.num_tokens
+        self.prefix_hits += n_tok
+        return hit, n_tok
+
+    def allocate_slots(self, request: Request, num_new_tokens: int,
+                       new_computed_blocks: list[int] | None = None,
+                       num_new_computed_tokens: int = 0, num_lookahead_tokens: int = 0,
+                       ) -> list[int] | None:
+        """Make room for ``num_new_tokens`` more tokens of ``request``.
+
+        Returns the newly appended block ids (possibly empty), or ``None`` when
+        the pool cannot serve the request now (the caller preempts or waits).
+        """
+        assert num_new_tokens > 0
+        rid = request.request_id
+        new_computed_blocks = new_computed_blocks or []
+        blocks = self.req_blocks.get(rid)
+        if blocks is None:
+            blocks = []
+        if self.sliding_window is not None and blocks:
+            self._drop_out_of_window(request, blocks)
+        computed = request.num_computed_tokens + num_new_computed_tokens
+        need_tokens = computed + num_new_tokens + num_lookahead_tokens
+        need_blocks = -(-need_tokens // self.block_size)
+        num_new_blocks = need_blocks - len(blocks) - len(new_computed_blocks)
+        # cached blocks in the free list stop being evictable once touched
+        evictable_hits = sum(1 for b in new_computed_blocks
+                             if b != NULL_BLOCK and self.pool.ref_cnt[b] == 0)
+        if num_new_blocks > self.pool.get_num_free_blocks() - evictable_hits - \
+                (self.watermark_blocks if rid not in self.req_blocks else 0):
+            return None
+        if new_computed_blocks:
+            assert not blocks, "prefix hits only apply to a request without blocks"
+            self.pool.touch(b for b in new_computed_blocks if b != NULL_BLOCK)
+            blocks.extend(new_computed_blocks)
+            self.num_cached_blocks[rid] = len(new_computed_blocks)
+        self.req_blocks[rid] = blocks
+        fresh: list[int] = []
+        if num_new_blocks > 0:
+            fresh = self.pool.get_new_blocks(num_new_blocks)
+            blocks.extend(fresh)
+        if self.enable_caching:
+            # tokens that will be complete after this step, excluding drafts
+            full = min(computed + num_new_tokens, request.num_tokens) // self.block_size
+            self._cache(request, blocks, full)
+        return fresh
+
+    def _cache(self, request: Request, blocks: list[int], num_full: int) -> None:
+        rid = request.request_id
+        done = self.num_cached_blocks.get(rid, 0)
+        num_full = min(num_full, len(request.block_hashes))
+        if num_full > done:
+            self.pool.cache_full_blocks(blocks, request.block_hashes, done, num_full,
+                                        request.all_token_ids, self.block_size)
+            self.num_cached_blocks[rid] = num_full
+
+    def cache_blocks(self, request: Request, num_computed_tokens: int) -> None:
+        if self.enable_caching and request.request_id in self.req_blocks:
+            self._cache(request, self.req_blocks[request.request_id],
+                        min(num_computed_tokens, request.num_tokens) // self.block_size)
+
+    def _drop_out_of_window(self, request: Request, blocks: list[int]) -> None:
+        first_needed = max(0, request.num_computed_tokens - self.sliding_window + 1) // self.block_size
+        freed = []
+        for i in range(first_needed - 1, -1, -1):
+            if blocks[i] == NULL_BLOCK:
+                break
+            freed.append(blocks[i])
+            blocks[i] = NULL_BLOCK
+        self.pool.free_blocks(freed)
+
+    def free(self, request: Request) -> None:
+        blocks = self.req_blocks.pop(request.request_id, None)
+        self.num_cached_blocks.pop(request.request_id, None)
+        if blocks:
+            # tail first: deeper prefix blocks become eviction candidates first
+            self.pool.free_blocks(reversed(blocks))
+
+    def reset_prefix_cache(self) -> bool:
+        ok = self.pool.reset_prefix_cache()
+        if ok:
+            self.prefix_queries = self.prefix_hits = 0
+        return ok
+
+    def get_num_common_prefix_blocks(self, request_id: str, num_running: int) -> int:
+        """Blocks shared by every running request (cascade attention input)."""
+        n = 0
+        for b in self.req_blocks.get(request_id, []):
+            if self.pool.ref_cnt[b] == num_running:
+                n += 1
+            else:
+                break
+        return n
+
+    def take_events(self):
+        return self.pool.take_events()

@@ -1,0 +1,428 @@
+"""Continuous-batching scheduler.
+
+There is no prefill phase and no decode phase: every step hands out a token
+budget, first to the requests already running (one token each for decoders,
+more for a partially prefilled prompt or for draft tokens), then to waiting
+requests, whose prompts may be split over several steps (chunked prefill).
+When the KV pool runs dry the lowest-ranked running request is preempted:
+its blocks are released and it re-enters the waiting queue at the front, to be
+recomputed (its prefix usually still sits in the prefix cache).
+
+Parity: ``aphrodite/v1/core/sched/scheduler.py:69`` — ``schedule`` (:393),
+``update_from_output`` (:1499), ``finish_requests`` (:2017),
+``_preempt_request`` (:1140); stop test ``sched/utils.py:95``;
+``SchedulerOutput`` ``sched/output.py:183``; queues ``request_queue.py``.
+"""
+from __future__ import annotations
+
+import heapq
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Iterable
+
+from sonar_b200.config import CacheConfig, SchedulerConfig, SpeculativeConfig
+from sonar_b200.core.block_pool import make_block_hasher
+from sonar_b200.core.kv_cache_manager import KVCacheManager
+from sonar_b200.request import (EngineCoreOutput, EngineCoreOutputs, EngineCoreRequest, Request,
+                                RequestStatus, SchedulerStats)
+from sonar_b200.sampling_params import SamplingParams
+
+
+@dataclass
+class NewRequestData:
+    req_id: str
+    prompt_token_ids: list[int]
+    output_token_ids: list[int]
+    sampling_params: SamplingParams | None
+    block_ids: list[int]
+    num_computed_tokens: int
+    pooling: bool = False
+    lora_name: str | None = None
+
+
+@dataclass
+class CachedRequestData:
+    """Requests the runner already knows: only deltas travel."""
+    req_ids: list[str] = field(default_factory=list)
+    new_block_ids: list[list[int]] = field(default_factory=list)
+    num_computed_tokens: list[int] = field(default_factory=list)
+    # tokens sampled on another pipeline stage that this runner has not seen
+    new_token_ids: list[list[int]] = field(default_factory=list)
+
+
+@dataclass
+class SchedulerOutput:
+    scheduled_new_reqs: list[NewRequestData] = field(default_factory=list)
+    scheduled_cached_reqs: CachedRequestData = field(default_factory=CachedRequestData)
+    num_scheduled_tokens: dict[str, int] = field(default_factory=dict)
+    total_num_scheduled_tokens: int = 0
+    scheduled_spec_decode_tokens: dict[str, list[int]] = field(default_factory=dict)
+    finished_req_ids: set[str] = field(default_factory=set)
+    preempted_req_ids: set[str] = field(default_factory=set)
+    num_common_prefix_blocks: int = 0
+    step_id: int = 0
+
+
+@dataclass
+class ModelRunnerOutput:
+    req_ids: list[str] = field(default_factory=list)
+    sampled_token_ids: list[list[int]] = field(default_factory=list)
+    logprobs: list[list[dict[int, float]] | None] | None = None
+    prompt_logprobs: dict[str, list[dict[int, float] | None]] = field(default_factory=dict)
+    spec_token_ids: list[list[int]] | None = None
+    pooled: dict[str, object] = field(default_factory=dict)
+
+
+EMPTY_RUNNER_OUTPUT = ModelRunnerOutput()
+
+
+class _WaitingQueue:
+    """FCFS deque or (priority, arrival) heap behind one interface."""
+
+    def __init__(self, policy: str) -> None:
+        self.policy = policy
+        self._dq: deque[Request] = deque()
+        self._heap: list[Request] = []
+
+    def __len__(self) -> int:
+        return len(self._dq) if self.policy == "fcfs" else len(self._heap)
+
+    def __bool__(self) -> bool:
+        return len(self) > 0
+
+    def __iter__(self):
+        return iter(self._dq if self.policy == "fcfs" else self._heap)
+
+    def add(self, r: Request) -> None:
+        if self.policy == "fcfs":
+            self._dq.append(r)
+        else:
+            heapq.heappush(self._heap, r)
+
+    def add_front(self, r: Request) -> None:
+        if self.policy == "fcfs":
+            self._dq.appendleft(r)
+        else:
+            heapq.heappush(self._heap, r)
+
+    def peek(self) -> Request:
+        return self._dq[0] if self.policy == "fcfs" else self._heap[0]
+
+    def pop(self) -> Request:
+        return self._dq.popleft() if self.policy == "fcfs" else heapq.heappop(self._heap)
+
+    def remove_many(self, reqs: Iterable[Request]) -> None:
+        ids = {r.request_id for r in reqs}
+        if not ids:
+            return
+        if self.policy == "fcfs":
+            self._dq = deque(r for r in self._dq if r.request_id not in ids)
+        else:
+            self._heap = [r for r in self._heap if r.request_id not in ids]
+            heapq.heapify(self._heap)
+
+
+def check_stop(request: Request, max_model_len: int) -> bool:
+    """Decide whether the last appended token ends the request."""
+    sp = request.sampling_params
+    if sp is None:
+        request.status = RequestStatus.FINISHED_STOPPED
+        return True
+    n_out = request.num_output_tokens
+    if n_out >= sp.min_tokens and n_out > 0:
+        last = request.output_token_ids[-1]
+        if not sp.ignore_eos and last == request.eos_token_id:
+            request.status = RequestStatus.FINISHED_STOPPED
+            return True
+        if last in sp.stop_token_ids or (not sp.ignore_eos and last in sp.all_stop_token_ids):
+            request.status = RequestStatus.FINISHED_STOPPED
+            request.stop_reason = last
+            return True
+    if request.num_tokens >= max_model_len or n_out >= request.max_tokens:
+        request.status = RequestStatus.FINISHED_LENGTH_CAPPED
+        return True
+    return False
+
+
+class Scheduler:
+    def __init__(self, sched_cfg: SchedulerConfig, cache_cfg: CacheConfig, num_blocks: int,
+                 spec_cfg: SpeculativeConfig | None = None, sliding_window: int | None = None,
+                 log_stats: bool = False, collect_kv_events: bool = False) -> None:
+        self.cfg = sched_cfg
+        self.cache_cfg = cache_cfg
+        self.block_size = cache_cfg.block_size
+        self.max_model_len = sched_cfg.max_model_len
+        self.num_spec_tokens = spec_cfg.num_speculative_tokens if spec_cfg and spec_cfg.method else 0
+        self.kv = KVCacheManager(num_blocks, cache_cfg.block_size, cache_cfg.enable_prefix_caching,
+                                 sliding_window=sliding_window, collect_events=collect_kv_events,
+                                 watermark=sched_cfg.watermark)
+        self.block_hasher = (make_block_hasher(cache_cfg.block_size, cache_cfg.prefix_caching_hash_algo)
+                             if cache_cfg.enable_prefix_caching else None)
+        self.requests: dict[str, Request] = {}
+        self.waiting = _WaitingQueue(sched_cfg.policy)
+        self.running: list[Request] = []
+        self.finished_req_ids: set[str] = set()
+        self._preempted_since_last: set[str] = set()
+        self._known_to_runner: set[str] = set()
+        self.log_stats = log_stats
+        self.step_id = 0
+        self.num_preempted_total = 0
+        self._spec_drafts = self._spec_accepted = 0
+
+    # ------------------------------------------------------------------ API
+    def add_request(self, core_req: EngineCoreRequest | Request) -> None:
+        req = core_req if isinstance(core_req, Request) else Request(core_req, self.block_hasher)
+        if req.request_id in self.requests:
+            raise ValueError(f"duplicate request id {req.request_id}")
+        if req.num_prompt_tokens >= self.max_model_len:
+            raise ValueError(
+                f"prompt of {req.num_prompt_tokens} tokens leaves no room under max_model_len="
+                f"{self.max_model_len}")
+        self.requests[req.request_id] = req
+        self.waiting.add(req)
+        req.record_event("queued")
+
+    def has_unfinished_requests(self) -> bool:
+        return bool(self.running) or bool(self.waiting)
+
+    def has_finished_requests(self) -> bool:
+        return bool(self.finished_req_ids)
+
+    def has_requests(self) -> bool:
+        return self.has_unfinished_requests() or self.has_finished_requests()
+
+    def get_num_unfinished_requests(self) -> int:
+        return len(self.running) + len(self.waiting)
+
+    def get_request_counts(self) -> tuple[int, int]:
+        return len(self.running), len(self.waiting)
+
+    def reset_prefix_cache(self) -> bool:
+        return self.kv.reset_prefix_cache()
+
+    # ------------------------------------------------------------- schedule
+    def schedule(self) -> SchedulerOutput:
+        cfg = self.cfg
+        out = SchedulerOutput(step_id=self.step_id)
+        self.step_id += 1
+        budget = cfg.max_num_batched_tokens
+        num_sched = out.num_scheduled_tokens
+        cached = out.scheduled_cached_reqs
+        preempted: list[Request] = []
+        new_blocks_of: dict[str, list[int]] = {}
+        threshold = cfg.long_prefill_token_threshold
+
+        # ---- 1. running requests ---------------------------------------
+        idx = 0
+        while idx < len(self.running) and budget > 0:
+            req = self.running[idx]
+            num_new = req.num_tokens_with_spec + req.num_output_placeholders - req.num_computed_tokens
+            if 0 < threshold < num_new:
+                num_new = threshold
+            num_new = min(num_new, budget, self.max_model_len - 1 - req.num_computed_tokens)
+            if num_new <= 0:
+                idx += 1
+                continue
+            new_blocks = None
+            shifted = False
+            while True:
+                new_blocks = self.kv.allocate_slots(req, num_new, num_lookahead_tokens=self.num_spec_tokens)
+                if new_blocks is not None:
+                    break
+                victim = self._pick_victim()
+                self.running.remove(victim)
+                shifted = True
+                self._preempt(victim)
+                preempted.append(victim)
+                given = num_sched.pop(victim.request_id, None)
+                if given is not None:  # ranked below req yet already served this step
+                    budget += given
+                    out.scheduled_spec_decode_tokens.pop(victim.request_id, None)
+                    new_blocks_of.pop(victim.request_id, None)
+                if victim is req:
+                    break
+            if new_blocks is None:
+                break  # req itself was preempted: nothing below it can run either
+            idx = self.running.index(req) + 1 if shifted else idx + 1
+            num_sched[req.request_id] = num_new
+            budget -= num_new
+            new_blocks_of[req.request_id] = new_blocks
+            if req.spec_token_ids:
+                n_spec = num_new + req.num_computed_tokens - req.num_tokens
+                if n_spec > 0:
+                    out.scheduled_spec_decode_tokens[req.request_id] = req.spec_token_ids[:n_spec]
+        for rid, blocks in new_blocks_of.items():
+            cached.req_ids.append(rid)
+            cached.new_block_ids.append(blocks)
+            cached.num_computed_tokens.append(self.requests[rid].num_computed_tokens)
+
+        # ---- 2. waiting requests ---------------------------------------
+        if not preempted:
+            while self.waiting and budget > 0 and len(self.running) < cfg.max_num_seqs:
+                req = self.waiting.peek()
+                if req.num_computed_tokens == 0:
+                    hit_blocks, hit_tokens = self.kv.get_computed_blocks(req)
+                else:
+                    hit_blocks, hit_tokens = [], 0
+                num_new = req.num_tokens - req.num_computed_tokens - hit_tokens
+                if 0 < threshold < num_new:
+                    num_new = threshold
+                if not cfg.enable_chunked_prefill and num_new > budget:
+                    break
+                num_new = min(num_new, budget)
+                assert num_new > 0
+                new_blocks = self.kv.allocate_slots(req, num_new, hit_blocks, hit_tokens,
+                                                    num_lookahead_tokens=self.num_spec_tokens)
+                if new_blocks is None:
+                    break
+                self.waiting.pop()
+                self.running.append(req)
+                was_preempted = req.status == RequestStatus.PREEMPTED
+                req.status = RequestStatus.RUNNING
+                req.num_computed_tokens += hit_tokens
+                if req.num_cached_tokens < 0:
+                    req.num_cached_tokens = hit_tokens
+                req.record_event("scheduled")
+                num_sched[req.request_id] = num_new
+                budget -= num_new
+                out.scheduled_new_reqs.append(NewRequestData(
+                    req_id=req.request_id, prompt_token_ids=req.prompt_token_ids,
+                    output_token_ids=list(req.output_token_ids) if was_preempted else [],
+                    sampling_params=req.sampling_params,
+                    block_ids=list(self.kv.get_block_ids(req.request_id)),
+                    num_computed_tokens=req.num_computed_tokens,
+                    pooling=req.pooling_params is not None, lora_name=req.lora_name))
+                self._known_to_runner.add(req.request_id)
+
+        total = cfg.max_num_batched_tokens - budget
+        out.total_num_scheduled_tokens = total
+        assert len(self.running) <= cfg.max_num_seqs
+        if self.running and total:
+            out.num_common_prefix_blocks = self.kv.get_num_common_prefix_blocks(
+                self.running[0].request_id, len(self.running))
+        out.finished_req_ids = self.finished_req_ids
+        self.finished_req_ids = set()
+        out.preempted_req_ids = self._preempted_since_last
+        self._preempted_since_last = set()
+        # advance now, so the next schedule() can be built before this step's
+        # tokens are known (async scheduling)
+        for rid, n in num_sched.items():
+            self.requests[rid].num_computed_tokens += n
+        return out
+
+    def _pick_victim(self) -> Request:
+        if self.cfg.policy == "priority":
+            return max(self.running, key=lambda r: (r.priority, r.arrival_time))
+        return self.running[-1]
+
+    def _preempt(self, req: Request) -> None:
+        self.kv.free(req)
+        req.status = RequestStatus.PREEMPTED
+        req.num_computed_tokens = 0
+        req.spec_token_ids = []
+        req.num_preemptions += 1
+        req.record_event("preempted")
+        self.num_preempted_total += 1
+        self.waiting.add_front(req)
+        self._preempted_since_last.add(req.request_id)
+        self._known_to_runner.discard(req.request_id)
+
+    # ------------------------------------------------------ update / finish
+    def update_from_output(self, sched_out: SchedulerOutput, run_out: ModelRunnerOutput) -> EngineCoreOutputs:
+        outputs: list[EngineCoreOutput] = []
+        index = {rid: i for i, rid in enumerate(run_out.req_ids)}
+        stopped: list[Request] = []
+        n_prompt = n_gen = 0
+        for rid, n_tok in sched_out.num_scheduled_tokens.items():
+            req = self.requests.get(rid)
+            if req is None or req.is_finished or req.status != RequestStatus.RUNNING:
+                continue  # aborted or preempted while the step was in flight
+            i = index.get(rid)
+            new_ids = run_out.sampled_token_ids[i] if i is not None else []
+            drafts = sched_out.scheduled_spec_decode_tokens.get(rid)
+            if drafts:
+                # every draft position was computed; rejected ones are rolled back
+                n_rejected = len(drafts) + 1 - len(new_ids)
+                req.num_computed_tokens -= n_rejected
+                self._spec_drafts += len(drafts)
+                self._spec_accepted += len(new_ids) - 1
+            if req.num_output_placeholders:
+                req.num_output_placeholders = max(0, req.num_output_placeholders - len(new_ids))
+            if req.num_output_tokens == 0:
+                n_prompt += n_tok - len(new_ids) + (1 if new_ids else 0)
+            n_gen += len(new_ids)
+            finished = False
+            emitted = new_ids
+            for k, tok in enumerate(new_ids):
+                req.append_output_token_ids(tok)
+                if check_stop(req, self.max_model_len):
+                    finished = True
+                    emitted = new_ids[:k + 1]
+                    break
+            if run_out.spec_token_ids is not None and i is not None and not finished:
+                req.spec_token_ids = run_out.spec_token_ids[i]
+            else:
+                req.spec_token_ids = []
+            pooled = run_out.pooled.get(rid)
+            if pooled is not None:
+                req.status = RequestStatus.FINISHED_STOPPED
+                finished = True
+            plp = run_out.prompt_logprobs.get(rid)
+            if emitted or finished or plp is not None:
+                lp = None
+                if run_out.logprobs is not None and i is not None and run_out.logprobs[i] is not None:
+                    lp = run_out.logprobs[i][:len(emitted)]
+                outputs.append(EngineCoreOutput(
+                    request_id=rid, new_token_ids=list(emitted), new_logprobs=lp, prompt_logprobs=plp,
+                    finish_reason=req.get_finished_reason(), stop_reason=req.stop_reason,
+                    num_cached_tokens=max(req.num_cached_tokens, 0), pooled=pooled))
+            if finished:
+                stopped.append(req)
+        if stopped:
+            ids = {r.request_id for r in stopped}
+            self.running = [r for r in self.running if r.request_id not in ids]
+            for r in stopped:
+                self._free(r)
+        res = EngineCoreOutputs(outputs=outputs, timestamp=time.monotonic())
+        if self.log_stats:
+            res.scheduler_stats = self.make_stats(n_prompt, n_gen)
+        return res
+
+    def finish_requests(self, request_ids: str | Iterable[str], status: RequestStatus) -> None:
+        """Abort / externally finish requests, wherever they are queued."""
+        assert RequestStatus.is_finished(status)
+        if isinstance(request_ids, str):
+            request_ids = (request_ids,)
+        waiting, running = [], set()
+        for rid in request_ids:
+            req = self.requests.get(rid)
+            if req is None or req.is_finished:
+                continue
+            if req.status == RequestStatus.RUNNING:
+                running.add(rid)
+            else:
+                waiting.append(req)
+            req.status = status
+        if running:
+            self.running = [r for r in self.running if r.request_id not in running]
+        self.waiting.remove_many(waiting)
+        for rid in list(running) + [r.request_id for r in waiting]:
+            self._free(self.requests[rid])
+
+    def _free(self, req: Request) -> None:
+        assert req.is_finished
+        self.kv.free(req)
+        if req.request_id in self._known_to_runner:
+            self.finished_req_ids.add(req.request_id)
+            self._known_to_runner.discard(req.request_id)
+        del self.requests[req.request_id]
+        req.record_event("finished")
+
+    def make_stats(self, n_prompt: int = 0, n_gen: int = 0) -> SchedulerStats:
+        return SchedulerStats(
+            num_running=len(self.running), num_waiting=len(self.waiting), kv_cache_usage=self.kv.usage,
+            prefix_cache_queries=self.kv.prefix_queries, prefix_cache_hits=self.kv.prefix_hits,
+            num_preempted=self.num_preempted_total, step_prompt_tokens=n_prompt,
+            step_generation_tokens=n_gen, spec_num_drafts=self._spec_drafts,
+            spec_num_accepted=self._spec_accepted)

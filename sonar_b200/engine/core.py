@@ -1,0 +1,82 @@
+"""Engine core: scheduler + executor + the step loop.
+
+``step()`` = schedule → execute on the workers → fold the sampled tokens back
+into the scheduler → per-request outputs.  ``EngineCoreProc`` (``core_proc.py``)
+wraps the same object in a busy loop behind ZMQ sockets for the server.
+
+Parity: ``aphrodite/v1/engine/core.py:102`` (``_initialize_kv_caches`` :232,
+``step`` :508).
+"""
+from __future__ import annotations
+
+import time
+from typing import Any
+
+from sonar_b200.config import EngineConfig
+from sonar_b200.core.scheduler import Scheduler
+from sonar_b200.executor.base import Executor
+from sonar_b200.logger import init_logger
+from sonar_b200.request import EngineCoreOutputs, EngineCoreRequest, RequestStatus
+from sonar_b200.utils.tracing import get_tracer
+
+logger = init_logger(__name__)
+
+
+class EngineCore:
+    def __init__(self, cfg: EngineConfig, executor_class: type[Executor] | None = None) -> None:
+        self.cfg = cfg
+        t0 = time.time()
+        self.executor = (executor_class or Executor.get_class(cfg))(cfg)
+        self.kv_cfg = self.executor.initialize_kv_cache()
+        sliding = self.kv_cfg.spec.sliding_window
+        self.scheduler = Scheduler(cfg.scheduler, cfg.cache, self.kv_cfg.num_blocks, cfg.speculative,
+                                   sliding_window=sliding, log_stats=cfg.observability.log_stats,
+                                   collect_kv_events=cfg.observability.collect_kv_events)
+        self.tracer = get_tracer(cfg.observability.trace_file)
+        self.paused = False
+        self.steps = 0
+        logger.info("engine core ready in %.1fs (%d KV blocks of %d tokens)", time.time() - t0,
+                    self.kv_cfg.num_blocks, cfg.cache.block_size)
+
+    # ------------------------------------------------------------------
+    def add_request(self, req: EngineCoreRequest) -> None:
+        self.scheduler.add_request(req)
+
+    def abort_requests(self, request_ids: list[str]) -> None:
+        self.scheduler.finish_requests(request_ids, RequestStatus.FINISHED_ABORTED)
+
+    def has_unfinished_requests(self) -> bool:
+        return self.scheduler.has_unfinished_requests()
+
+    def step(self) -> EngineCoreOutputs:
+        if self.paused or not self.scheduler.has_requests():
+            return EngineCoreOutputs()
+        with self.tracer.span("schedule"):
+            so = self.scheduler.schedule()
+        with self.tracer.span("execute_model", tokens=so.total_num_scheduled_tokens):
+            ro = self.executor.execute_model(so)
+        with self.tracer.span("update"):
+            outs = self.scheduler.update_from_output(so, ro)
+        self.steps += 1
+        return outs
+
+    # utility RPCs ---------------------------------------------------------
+    def reset_prefix_cache(self) -> bool:
+        return self.scheduler.reset_prefix_cache()
+
+    def pause(self) -> None:
+        self.paused = True
+
+    def resume(self) -> None:
+        self.paused = False
+
+    def collective_rpc(self, method: str, *args, **kwargs) -> list[Any]:
+        return self.executor.collective_rpc(method, *args, **kwargs)
+
+    def get_stats(self) -> dict:
+        s = self.scheduler.make_stats()
+        return {"scheduler": s, "workers": self.executor.collective_rpc("get_stats")}
+
+    def shutdown(self) -> None:
+        self.executor.shutdown()
+        self.tracer.close()

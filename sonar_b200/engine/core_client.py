@@ -1,0 +1,242 @@
+"""Clients through which a frontend drives an engine core.
+
+``InprocClient`` calls the core directly (offline ``LLM``; ``get_output`` runs
+one step).  ``MPClient`` / ``AsyncMPClient`` talk to an ``EngineCoreProc``
+running in a child process over two ZMQ sockets (requests out, outputs in)
+with msgpack frames, monitor the child and surface its death as
+``EngineDeadError``.
+
+Parity: ``aphrodite/v1/engine/core_client.py:90`` (``make_client``), ``:295``
+(in-proc), ``:484,:756,:920`` (multiprocess clients, monitor ``:668``).
+"""
+from __future__ import annotations
+
+import asyncio
+import multiprocessing as mp
+import os
+import threading
+import uuid
+import weakref
+from typing import Any
+
+from sonar_b200.config import EngineConfig
+from sonar_b200.logger import init_logger
+from sonar_b200.request import EngineCoreOutputs, EngineCoreRequest
+
+logger = init_logger(__name__)
+
+
+class EngineDeadError(RuntimeError):
+    """The engine-core process is gone; every call from now on fails with this."""
+
+
+class EngineCoreClient:
+    @staticmethod
+    def make_client(cfg: EngineConfig, multiprocess: bool, asyncio_mode: bool, executor_class=None):
+        if asyncio_mode:
+            return AsyncMPClient(cfg, executor_class)
+        if multiprocess:
+            return SyncMPClient(cfg, executor_class)
+        return InprocClient(cfg, executor_class)
+
+
+class InprocClient(EngineCoreClient):
+    def __init__(self, cfg: EngineConfig, executor_class=None) -> None:
+        from sonar_b200.engine.core import EngineCore
+        self.engine_core = EngineCore(cfg, executor_class)
+
+    def add_request(self, req: EngineCoreRequest) -> None:
+        self.engine_core.add_request(req)
+
+    def abort_requests(self, ids: list[str]) -> None:
+        self.engine_core.abort_requests(ids)
+
+    def get_output(self) -> EngineCoreOutputs:
+        return self.engine_core.step()
+
+    def call_utility(self, method: str, *args, **kwargs) -> Any:
+        return getattr(self.engine_core, method)(*args, **kwargs)
+
+    def shutdown(self) -> None:
+        self.engine_core.shutdown()
+
+
+# ---------------------------------------------------------------------------
+# multiprocess clients
+# ---------------------------------------------------------------------------
+def _ipc_path(tag: str) -> str:
+    return f"ipc:///tmp/sonar-{os.getpid()}-{tag}-{uuid.uuid4().hex[:8]}"
+
+
+class _MPBase(EngineCoreClient):
+    def __init__(self, cfg: EngineConfig, executor_class=None) -> None:
+        import zmq
+        from sonar_b200.engine.core_proc import run_engine_core
+        self.cfg = cfg
+        self.input_addr, self.output_addr = _ipc_path("in"), _ipc_path("out")
+        self.ctx = zmq.Context(io_threads=2)
+        self.input_sock = self.ctx.socket(zmq.PUSH)
+        self.input_sock.bind(self.input_addr)
+        self.output_sock = self.ctx.socket(zmq.PULL)
+        self.output_sock.bind(self.output_addr)
+        spawn = mp.get_context("spawn")
+        self.ready = spawn.Event()
+        self.proc = spawn.Process(target=run_engine_core, name="sonar-engine-core",
+                                  args=(cfg, self.input_addr, self.output_addr, self.ready, executor_class),
+                                  daemon=True)
+        self.proc.start()
+        self.dead = False
+        while not self.ready.wait(timeout=1.0):
+            if not self.proc.is_alive():
+                raise EngineDeadError(f"engine core exited during start-up (code {self.proc.exitcode})")
+        self._utility_results: dict[int, Any] = {}
+        self._utility_id = 0
+        self._monitor = threading.Thread(target=self._watch, args=(weakref.ref(self),), daemon=True)
+        self._monitor.start()
+
+    @staticmethod
+    def _watch(ref) -> None:
+        self = ref()
+        if self is None:
+            return
+        proc = self.proc
+        del self
+        proc.join()
+        self = ref()
+        if self is not None and not getattr(self, "_closing", False):
+            self.dead = True
+            logger.error("engine core process died (exit code %s)", proc.exitcode)
+            self._on_death()
+
+    def _on_death(self) -> None:
+        pass
+
+    def _check(self) -> None:
+        if self.dead:
+            raise EngineDeadError("engine core process is dead")
+
+    def _send(self, kind: bytes, payload: Any) -> None:
+        from sonar_b200.engine.serial import encode
+        self._check()
+        self.input_sock.send_multipart([kind, encode(payload)])
+
+    def shutdown(self) -> None:
+        self._closing = True
+        try:
+            if self.proc.is_alive():
+                self.input_sock.send_multipart([b"X", b""])
+                self.proc.join(timeout=5)
+            if self.proc.is_alive():
+                self.proc.terminate()
+        finally:
+            self.input_sock.close(linger=0)
+            self.output_sock.close(linger=0)
+            self.ctx.term()
+
+
+class SyncMPClient(_MPBase):
+    def add_request(self, req: EngineCoreRequest) -> None:
+        self._send(b"A", req)
+
+    def abort_requests(self, ids: list[str]) -> None:
+        self._send(b"B", ids)
+
+    def get_output(self) -> EngineCoreOutputs:
+        from sonar_b200.engine.serial import decode
+        import zmq
+        while True:
+            self._check()
+            if self.output_sock.poll(timeout=200, flags=zmq.POLLIN):
+                outs: EngineCoreOutputs = decode(self.output_sock.recv())
+                if outs.utility_output is not None:
+                    uid, val = outs.utility_output
+                    self._utility_results[uid] = val
+                    continue
+                return outs
+
+    def call_utility(self, method: str, *args, **kwargs) -> Any:
+        from sonar_b200.engine.serial import decode
+        self._utility_id += 1
+        uid = self._utility_id
+        self._send(b"U", (uid, method, args, kwargs))
+        while uid not in self._utility_results:
+            self._check()
+            if self.output_sock.poll(timeout=200):
+                outs = decode(self.output_sock.recv())
+                if outs.utility_output is not None:
+                    self._utility_results[outs.utility_output[0]] = outs.utility_output[1]
+        val = self._utility_results.pop(uid)
+        if isinstance(val, Exception):
+            raise val
+        return val
+
+
+class AsyncMPClient(_MPBase):
+    """asyncio flavour: a reader thread moves frames into an asyncio queue."""
+
+    def __init__(self, cfg: EngineConfig, executor_class=None) -> None:
+        super().__init__(cfg, executor_class)
+        self.loop: asyncio.AbstractEventLoop | None = None
+        self.outputs: asyncio.Queue | None = None
+        self._futures: dict[int, asyncio.Future] = {}
+        self._reader: threading.Thread | None = None
+
+    def _ensure_loop(self) -> None:
+        if self.loop is None:
+            self.loop = asyncio.get_running_loop()
+            self.outputs = asyncio.Queue()
+            self._reader = threading.Thread(target=self._read_loop, daemon=True)
+            self._reader.start()
+
+    def _read_loop(self) -> None:
+        from sonar_b200.engine.serial import decode
+        import zmq
+        while not self.dead and not getattr(self, "_closing", False):
+            try:
+                if not self.output_sock.poll(timeout=200, flags=zmq.POLLIN):
+                    continue
+                outs = decode(self.output_sock.recv())
+            except Exception:  # socket closed during shutdown
+                return
+            self.loop.call_soon_threadsafe(self._dispatch, outs)
+
+    def _dispatch(self, outs: EngineCoreOutputs) -> None:
+        if outs.utility_output is not None:
+            uid, val = outs.utility_output
+            fut = self._futures.pop(uid, None)
+            if fut is not None and not fut.done():
+                if isinstance(val, Exception):
+                    fut.set_exception(val)
+                else:
+                    fut.set_result(val)
+            return
+        self.outputs.put_nowait(outs)
+
+    def _on_death(self) -> None:
+        if self.loop is not None:
+            self.loop.call_soon_threadsafe(self.outputs.put_nowait, EngineDeadError("engine core died"))
+
+    async def add_request_async(self, req: EngineCoreRequest) -> None:
+        self._ensure_loop()
+        self._send(b"A", req)
+
+    async def abort_requests_async(self, ids: list[str]) -> None:
+        if ids:
+            self._send(b"B", ids)
+
+    async def get_output_async(self) -> EngineCoreOutputs:
+        self._ensure_loop()
+        item = await self.outputs.get()
+        if isinstance(item, Exception):
+            self.outputs.put_nowait(item)
+            raise item
+        return item
+
+    async def call_utility_async(self, method: str, *args, **kwargs) -> Any:
+        self._ensure_loop()
+        self._utility_id += 1
+        uid = self._utility_id
+        fut = self.loop.create_future()
+        self._futures[uid] = fut
+        self._send(b"U", (uid, method, args, kwargs))
+        return await fut

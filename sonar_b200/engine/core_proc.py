@@ -1,0 +1,112 @@
+"""Engine core as a process: busy loop between a request socket and an output socket.
+
+An input thread drains the PULL socket into a queue, the main thread runs
+``EngineCore.step()`` while there is work (blocking on the queue when idle),
+an output thread pushes encoded ``EngineCoreOutputs`` frames.  Frame kinds:
+``A`` add request, ``B`` abort, ``U`` utility call ``(id, method, args,
+kwargs)``, ``X`` shut down.
+
+Parity: ``aphrodite/v1/engine/core.py:902`` (``run_busy_loop`` :1253,
+``process_input_sockets`` :1495, ``process_output_sockets`` :1585).
+"""
+from __future__ import annotations
+
+import queue
+import signal
+import threading
+import traceback
+
+from sonar_b200.config import EngineConfig
+from sonar_b200.logger import init_logger
+from sonar_b200.request import EngineCoreOutputs
+
+logger = init_logger(__name__)
+
+
+class EngineCoreProc:
+    def __init__(self, cfg: EngineConfig, input_addr: str, output_addr: str, executor_class=None) -> None:
+        import zmq
+        from sonar_b200.engine.core import EngineCore
+        self.core = EngineCore(cfg, executor_class)
+        self.ctx = zmq.Context()
+        self.input_addr, self.output_addr = input_addr, output_addr
+        self.inq: queue.Queue = queue.Queue()
+        self.outq: queue.Queue = queue.Queue()
+        self._stop = False
+        threading.Thread(target=self._input_loop, daemon=True).start()
+        threading.Thread(target=self._output_loop, daemon=True).start()
+
+    def _input_loop(self) -> None:
+        import zmq
+        from sonar_b200.engine.serial import decode
+        sock = self.ctx.socket(zmq.PULL)
+        sock.connect(self.input_addr)
+        while True:
+            kind, payload = sock.recv_multipart()
+            if kind == b"X":
+                self.inq.put((kind, None))
+                return
+            self.inq.put((kind, decode(payload)))
+
+    def _output_loop(self) -> None:
+        import zmq
+        from sonar_b200.engine.serial import encode
+        sock = self.ctx.socket(zmq.PUSH)
+        sock.connect(self.output_addr)
+        while True:
+            item = self.outq.get()
+            if item is None:
+                return
+            sock.send(encode(item))
+
+    def _handle(self, kind: bytes, payload) -> None:
+        if kind == b"A":
+            try:
+                self.core.add_request(payload)
+            except Exception as e:  # report as an errored request, keep serving
+                from sonar_b200.request import EngineCoreOutput, FinishReason
+                logger.warning("rejected request %s: %s", payload.request_id, e)
+                self.outq.put(EngineCoreOutputs(outputs=[EngineCoreOutput(
+                    payload.request_id, [], finish_reason=FinishReason.ERROR, stop_reason=str(e))]))
+        elif kind == b"B":
+            self.core.abort_requests(payload)
+        elif kind == b"U":
+            uid, method, args, kwargs = payload
+            try:
+                val = getattr(self.core, method)(*args, **kwargs)
+            except Exception as e:
+                val = e
+            self.outq.put(EngineCoreOutputs(utility_output=(uid, val)))
+        elif kind == b"X":
+            self._stop = True
+
+    def run_busy_loop(self) -> None:
+        while not self._stop:
+            busy = self.core.scheduler.has_requests() and not self.core.paused
+            try:
+                # block when idle, only peek while generating
+                item = self.inq.get(block=not busy, timeout=None if not busy else 0)
+                self._handle(*item)
+                while not self.inq.empty():
+                    self._handle(*self.inq.get_nowait())
+            except queue.Empty:
+                pass
+            if self._stop:
+                break
+            if self.core.scheduler.has_requests() and not self.core.paused:
+                outs = self.core.step()
+                if outs.outputs or outs.scheduler_stats is not None:
+                    self.outq.put(outs)
+        self.outq.put(None)
+        self.core.shutdown()
+
+
+def run_engine_core(cfg: EngineConfig, input_addr: str, output_addr: str, ready, executor_class=None) -> None:
+    signal.signal(signal.SIGINT, signal.SIG_IGN)
+    try:
+        proc = EngineCoreProc(cfg, input_addr, output_addr, executor_class)
+        ready.set()
+        proc.run_busy_loop()
+    except Exception:
+        logger.error("engine core crashed:\n%s", traceback.format_exc())
+        raise

@@ -1,0 +1,158 @@
+"""Synchronous engine frontend: prompts in, ``RequestOutput`` out.
+
+Tokenises / validates requests (``InputProcessor``), fans out ``n > 1``,
+forwards ``EngineCoreRequest`` to the core through an ``EngineCoreClient``
+(in-process by default, a ZMQ-connected process when multiprocessing is on)
+and post-processes core outputs (``OutputProcessor``).
+
+Parity: ``aphrodite/v1/engine/llm_engine.py:48`` (``add_request`` :207, ``step`` :283),
+``input_processor.py`` (456).
+"""
+from __future__ import annotations
+
+import time
+from typing import Any
+
+from sonar_b200.config import EngineArgs, EngineConfig
+from sonar_b200.engine.core_client import EngineCoreClient
+from sonar_b200.engine.output_processor import OutputProcessor, ParentRequest
+from sonar_b200.logger import init_logger
+from sonar_b200.outputs import RequestOutput
+from sonar_b200.request import EngineCoreRequest
+from sonar_b200.sampling_params import PoolingParams, SamplingParams
+from sonar_b200.utils.tokenizer import get_tokenizer
+
+logger = init_logger(__name__)
+
+PromptType = "str | list[int] | dict"
+
+
+class InputProcessor:
+    def __init__(self, cfg: EngineConfig, tokenizer) -> None:
+        self.cfg = cfg
+        self.tokenizer = tokenizer
+        self.max_model_len = cfg.model.max_model_len
+        self.vocab_size = cfg.model.vocab_size
+        self.eos = cfg.model.eos_token_id
+        if self.eos is None and tokenizer is not None:
+            self.eos = getattr(tokenizer, "eos_token_id", None)
+
+    def process(self, request_id: str, prompt, params: SamplingParams | PoolingParams,
+                arrival_time: float | None = None, priority: int = 0, lora_name: str | None = None,
+                cache_salt: str | None = None) -> tuple[str | None, EngineCoreRequest]:
+        text: str | None = None
+        if isinstance(prompt, str):
+            text = prompt
+        elif isinstance(prompt, dict):
+            text = prompt.get("prompt")
+            ids = prompt.get("prompt_token_ids")
+            cache_salt = prompt.get("cache_salt", cache_salt)
+            if ids is not None:
+                prompt = list(ids)
+            elif text is None:
+                raise ValueError("prompt dict needs 'prompt' or 'prompt_token_ids'")
+            else:
+                prompt = text
+        if isinstance(prompt, str):
+            if self.tokenizer is None:
+                raise ValueError("text prompts need a tokenizer (skip_tokenizer_init is set)")
+            ids = self.tokenizer.encode(prompt)
+        else:
+            ids = list(prompt)
+        if not ids:
+            raise ValueError("the prompt is empty")
+        bad = [t for t in ids if not 0 <= t < self.vocab_size]
+        if bad:
+            raise ValueError(f"token id {bad[0]} is outside the vocabulary [0, {self.vocab_size})")
+        if len(ids) >= self.max_model_len:
+            raise ValueError(f"the prompt has {len(ids)} tokens but max_model_len is {self.max_model_len}")
+        eos_id = None
+        if isinstance(params, SamplingParams):
+            params = params.clone()
+            if params.max_tokens is None:
+                params.max_tokens = self.max_model_len - len(ids)
+            params.max_tokens = min(params.max_tokens, self.max_model_len - len(ids))
+            params.update_from_generation_config(self.eos)
+            eos_id = params._eos_token_id
+            if params.bad_words and self.tokenizer is not None:
+                params._bad_words_token_ids = [
+                    self.tokenizer.encode(w, add_special_tokens=False) for w in params.bad_words]
+            if params.structured_outputs is not None:
+                raise ValueError("structured outputs need a grammar backend, which this build does not bundle")
+            if params.stop and self.tokenizer is None:
+                raise ValueError("stop strings need a tokenizer")
+            if self.tokenizer is None:
+                params.detokenize = False
+            sp, pp = params, None
+        else:
+            sp, pp = None, params
+        req = EngineCoreRequest(request_id=request_id, prompt_token_ids=ids, sampling_params=sp,
+                                pooling_params=pp, eos_token_id=eos_id,
+                                arrival_time=arrival_time or time.time(), priority=priority,
+                                cache_salt=cache_salt, lora_name=lora_name)
+        return text, req
+
+
+class LLMEngine:
+    def __init__(self, cfg: EngineConfig, multiprocess: bool = False, executor_class=None) -> None:
+        self.cfg = cfg
+        tok = None
+        if not cfg.model.skip_tokenizer_init:
+            tok = get_tokenizer(cfg.model.tokenizer, cfg.model.vocab_size)
+        self.tokenizer = tok
+        self.input_processor = InputProcessor(cfg, tok)
+        self.output_processor = OutputProcessor(tok, cfg.observability.log_stats)
+        self.core = EngineCoreClient.make_client(cfg, multiprocess=multiprocess, asyncio_mode=False,
+                                                 executor_class=executor_class)
+
+    @classmethod
+    def from_engine_args(cls, args: EngineArgs, **kw: Any) -> "LLMEngine":
+        return cls(args.create_engine_config(), **kw)
+
+    # ------------------------------------------------------------------
+    def add_request(self, request_id: str, prompt, params: SamplingParams | PoolingParams,
+                    arrival_time: float | None = None, priority: int = 0, lora_name: str | None = None) -> None:
+        text, req = self.input_processor.process(request_id, prompt, params, arrival_time, priority, lora_name)
+        n = params.n if isinstance(params, SamplingParams) else 1
+        if n == 1:
+            self.output_processor.add_request(req, text)
+            self.core.add_request(req)
+            return
+        parent = ParentRequest(request_id, req.sampling_params)
+        for i in range(n):
+            child = EngineCoreRequest(
+                request_id=parent.child_id(i), prompt_token_ids=req.prompt_token_ids,
+                sampling_params=parent.child_params(i), eos_token_id=req.eos_token_id,
+                arrival_time=req.arrival_time, priority=priority, cache_salt=req.cache_salt, lora_name=lora_name)
+            self.output_processor.add_request(child, text, parent, i)
+            self.core.add_request(child)
+
+    def abort_request(self, request_ids: list[str]) -> None:
+        ids = self.output_processor.abort_requests(request_ids)
+        if ids:
+            self.core.abort_requests(ids)
+
+    def has_unfinished_requests(self) -> bool:
+        return self.output_processor.has_unfinished_requests()
+
+    def get_num_unfinished_requests(self) -> int:
+        return self.output_processor.get_num_unfinished_requests()
+
+    def step(self) -> list[RequestOutput]:
+        outs = self.core.get_output()
+        results, to_abort = self.output_processor.process_outputs(outs.outputs)
+        if to_abort:
+            self.core.abort_requests(to_abort)
+        return results
+
+    def reset_prefix_cache(self) -> bool:
+        return self.core.call_utility("reset_prefix_cache")
+
+    def collective_rpc(self, method: str, *args, **kwargs):
+        return self.core.call_utility("collective_rpc", method, *args, **kwargs)
+
+    def get_stats(self) -> dict:
+        return self.core.call_utility("get_stats")
+
+    def shutdown(self) -> None:
+        self.core.shutdown()

@@ -1,0 +1,199 @@
+"""Turns engine-core outputs into ``RequestOutput`` objects.
+
+Holds one ``RequestState`` per live request: detokeniser, accumulated token
+ids, logprobs, output kind (cumulative / delta / final-only) and, for ``n > 1``,
+the parent that merges the children into one result.
+
+Parity: ``aphrodite/v1/engine/output_processor.py`` (793),
+``parallel_sampling.py`` (146), ``logprobs.py`` (334).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+from sonar_b200.engine.detokenizer import IncrementalDetokenizer
+from sonar_b200.outputs import (CompletionOutput, Logprob, PoolingOutput, PoolingRequestOutput, RequestMetrics,
+                                RequestOutput)
+from sonar_b200.request import EngineCoreOutput, EngineCoreRequest, FinishReason
+from sonar_b200.sampling_params import RequestOutputKind, SamplingParams
+
+
+class ParentRequest:
+    """Fan-out bookkeeping for ``n > 1``: children ``{i}_{parent_id}``."""
+
+    def __init__(self, request_id: str, params: SamplingParams) -> None:
+        self.request_id = request_id
+        self.params = params
+        self.n = params.n
+        self.completions: dict[int, CompletionOutput] = {}
+        self.finished_children = 0
+
+    def child_id(self, index: int) -> str:
+        return f"{index}_{self.request_id}"
+
+    def child_params(self, index: int) -> SamplingParams:
+        p = self.params.clone()
+        p.n = 1
+        if p.seed is not None:
+            p.seed += index
+        return p
+
+
+@dataclass
+class RequestState:
+    request_id: str
+    prompt: str | None
+    prompt_token_ids: list[int]
+    params: SamplingParams | None
+    detok: IncrementalDetokenizer | None
+    parent: ParentRequest | None = None
+    index: int = 0
+    token_ids: list[int] = field(default_factory=list)
+    logprobs: list[dict[int, Logprob]] | None = None
+    prompt_logprobs: list[dict[int, Logprob] | None] | None = None
+    cumulative_logprob: float = 0.0
+    sent_tokens: int = 0
+    metrics: RequestMetrics = field(default_factory=RequestMetrics)
+    queue: object = None          # asyncio queue of the streaming consumer, if any
+    is_pooling: bool = False
+
+
+class OutputProcessor:
+    def __init__(self, tokenizer, log_stats: bool = False) -> None:
+        self.tokenizer = tokenizer
+        self.states: dict[str, RequestState] = {}
+        self.parents: dict[str, ParentRequest] = {}
+        self.log_stats = log_stats
+
+    def get_num_unfinished_requests(self) -> int:
+        return len(self.states)
+
+    def has_unfinished_requests(self) -> bool:
+        return bool(self.states)
+
+    def add_request(self, req: EngineCoreRequest, prompt: str | None, parent: ParentRequest | None = None,
+                    index: int = 0, queue=None) -> None:
+        if req.request_id in self.states:
+            raise ValueError(f"request id {req.request_id} already running")
+        p = req.sampling_params
+        detok = IncrementalDetokenizer(self.tokenizer, req.prompt_token_ids, p) if p is not None else None
+        st = RequestState(req.request_id, prompt, req.prompt_token_ids, p, detok, parent, index, queue=queue,
+                          is_pooling=req.pooling_params is not None)
+        st.metrics.arrival_time = req.arrival_time
+        if p is not None and p.logprobs is not None:
+            st.logprobs = []
+        self.states[req.request_id] = st
+        if parent is not None:
+            self.parents[parent.request_id] = parent
+
+    def abort_requests(self, request_ids: list[str]) -> list[str]:
+        """Drop states; returns the engine-core request ids to abort (children for parents)."""
+        out = []
+        for rid in request_ids:
+            if rid in self.states:
+                del self.states[rid]
+                out.append(rid)
+            parent = self.parents.pop(rid, None)
+            if parent is not None:
+                for i in range(parent.n):
+                    cid = parent.child_id(i)
+                    if self.states.pop(cid, None) is not None:
+                        out.append(cid)
+        return out
+
+    # ------------------------------------------------------------------
+    def process_outputs(self, outputs: list[EngineCoreOutput]) -> tuple[list, list[str]]:
+        """Returns (request outputs for non-streaming callers, ids to abort in the core
+        because a stop string ended them)."""
+        results: list = []
+        to_abort: list[str] = []
+        now = time.time()
+        for eo in outputs:
+            st = self.states.get(eo.request_id)
+            if st is None:
+                continue  # aborted meanwhile
+            if st.is_pooling:
+                if eo.pooled is not None or eo.finished:
+                    del self.states[eo.request_id]
+                    ro = PoolingRequestOutput(st.request_id, PoolingOutput(eo.pooled), st.prompt_token_ids)
+                    self._deliver(st, ro, results)
+                continue
+            finish, stop_reason = eo.finish_reason, eo.stop_reason
+            if eo.new_token_ids and st.metrics.first_token_time is None:
+                st.metrics.first_token_time = now
+            st.token_ids.extend(eo.new_token_ids)
+            st.metrics.num_cached_tokens = eo.num_cached_tokens
+            if eo.prompt_logprobs is not None:
+                conv = [None if d is None else self._convert(d) for d in eo.prompt_logprobs]
+                st.prompt_logprobs = (st.prompt_logprobs or []) + conv
+            if eo.new_logprobs is not None and st.logprobs is not None:
+                for tok, d in zip(eo.new_token_ids, eo.new_logprobs):
+                    st.logprobs.append(self._convert(d))
+                    st.cumulative_logprob += d.get(tok, 0.0)
+            if st.detok is not None:
+                hit = st.detok.update(eo.new_token_ids, finish is not None)
+                if hit is not None and finish is None:
+                    finish, stop_reason = FinishReason.STOP, hit
+                    to_abort.append(eo.request_id)
+            finished = finish is not None
+            if finished:
+                st.metrics.finished_time = now
+                st.metrics.num_generation_tokens = len(st.token_ids)
+                del self.states[eo.request_id]
+            ro = self._make_output(st, finish, stop_reason)
+            if ro is not None:
+                self._deliver(st, ro, results)
+        return results, to_abort
+
+    def _deliver(self, st: RequestState, ro, results: list) -> None:
+        if st.queue is not None:
+            st.queue.put_nowait(ro)
+        else:
+            results.append(ro)
+
+    def _convert(self, d: dict[int, float]) -> dict[int, Logprob]:
+        ranked = sorted(d.items(), key=lambda kv: -kv[1])
+        out = {}
+        for rank, (tok, lp) in enumerate(ranked, 1):
+            text = None
+            if self.tokenizer is not None:
+                text = self.tokenizer.decode([tok], skip_special_tokens=False)
+            out[tok] = Logprob(lp, rank, text)
+        return out
+
+    def _make_output(self, st: RequestState, finish: FinishReason | None, stop_reason) -> RequestOutput | None:
+        p = st.params
+        finished = finish is not None
+        kind = p.output_kind
+        if kind == RequestOutputKind.FINAL_ONLY and not finished:
+            return None
+        delta = kind == RequestOutputKind.DELTA
+        text = st.detok.get_next_text(finished, delta) if st.detok is not None and st.detok.enabled else ""
+        if delta:
+            toks = st.token_ids[st.sent_tokens:]
+            lps = st.logprobs[st.sent_tokens:] if st.logprobs is not None else None
+            st.sent_tokens = len(st.token_ids)
+        else:
+            toks, lps = list(st.token_ids), st.logprobs
+        comp = CompletionOutput(st.index, text, toks, st.cumulative_logprob if st.logprobs is not None else None,
+                                lps, str(finish) if finished else None, stop_reason)
+        parent = st.parent
+        if parent is None:
+            return RequestOutput(st.request_id, st.prompt, st.prompt_token_ids, [comp], finished,
+                                 st.prompt_logprobs, st.metrics, st.metrics.num_cached_tokens)
+        # n > 1: merge children
+        if finished:
+            parent.finished_children += 1
+        all_done = parent.finished_children == parent.n
+        if kind == RequestOutputKind.FINAL_ONLY:
+            parent.completions[st.index] = comp
+            if not all_done:
+                return None
+            comps = [parent.completions[i] for i in sorted(parent.completions)]
+        else:
+            comps = [comp]
+        if all_done:
+            self.parents.pop(parent.request_id, None)
+        return RequestOutput(parent.request_id, st.prompt, st.prompt_token_ids, comps, all_done,
+                             st.prompt_logprobs, st.metrics, st.metrics.num_cached_tokens)

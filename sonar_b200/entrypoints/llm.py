@@ -1,0 +1,134 @@
+"""Offline inference API.
+
+``LLM(model=..., tensor_parallel_size=..., ...)`` builds an engine;
+``generate`` / ``chat`` / ``embed`` / ``beam_search`` run requests to
+completion and return results in submission order.
+
+Parity: ``aphrodite/entrypoints/llm.py:67`` (``generate`` :397, ``chat`` :591,
+``collective_rpc`` :546) and the run loop ``entrypoints/offline_utils.py:535-556``.
+"""
+from __future__ import annotations
+
+import itertools
+from typing import Any, Sequence
+
+from sonar_b200.config import EngineArgs
+from sonar_b200.engine.llm_engine import LLMEngine
+from sonar_b200.outputs import BeamSearchOutput, BeamSearchSequence, PoolingRequestOutput, RequestOutput
+from sonar_b200.sampling_params import (BeamSearchParams, PoolingParams, RequestOutputKind, SamplingParams)
+from sonar_b200.utils.tokenizer import apply_chat_template
+
+
+class LLM:
+    def __init__(self, model: str, **kwargs: Any) -> None:
+        multiprocess = kwargs.pop("engine_multiprocessing", False)
+        executor_class = kwargs.pop("executor_class", None)
+        self.engine_args = EngineArgs(model=model, **kwargs)
+        self.llm_engine = LLMEngine.from_engine_args(self.engine_args, multiprocess=multiprocess,
+                                                     executor_class=executor_class)
+        self._counter = itertools.count()
+
+    def get_tokenizer(self):
+        return self.llm_engine.tokenizer
+
+    # ------------------------------------------------------------------
+    def _enqueue(self, prompts, params, priority: Sequence[int] | None = None) -> list[str]:
+        if isinstance(prompts, (str, dict)) or (isinstance(prompts, list) and prompts and isinstance(prompts[0], int)):
+            prompts = [prompts]
+        if not isinstance(params, (list, tuple)):
+            params = [params] * len(prompts)
+        if len(params) != len(prompts):
+            raise ValueError("the number of sampling params must match the number of prompts")
+        ids = []
+        for i, (prompt, p) in enumerate(zip(prompts, params)):
+            rid = str(next(self._counter))
+            if isinstance(p, SamplingParams):
+                p = p.clone()
+                p.output_kind = RequestOutputKind.FINAL_ONLY
+            self.llm_engine.add_request(rid, prompt, p, priority=priority[i] if priority else 0)
+            ids.append(rid)
+        return ids
+
+    def _run_engine(self, ids: list[str]) -> list:
+        done: dict[str, Any] = {}
+        while self.llm_engine.has_unfinished_requests():
+            for out in self.llm_engine.step():
+                if out.finished:
+                    done[out.request_id] = out
+        return [done[i] for i in ids if i in done]
+
+    def generate(self, prompts, sampling_params: SamplingParams | Sequence[SamplingParams] | None = None,
+                 priority: Sequence[int] | None = None, use_tqdm: bool = False) -> list[RequestOutput]:
+        if sampling_params is None:
+            sampling_params = SamplingParams()
+        return self._run_engine(self._enqueue(prompts, sampling_params, priority))
+
+    def chat(self, messages, sampling_params: SamplingParams | None = None, chat_template: str | None = None,
+             add_generation_prompt: bool = True, tools: list[dict] | None = None) -> list[RequestOutput]:
+        convs = messages if messages and isinstance(messages[0], list) else [messages]
+        tok = self.get_tokenizer()
+        prompts = [apply_chat_template(tok, c, add_generation_prompt, chat_template, tools) for c in convs]
+        return self.generate(prompts, sampling_params)
+
+    def embed(self, prompts, pooling_params: PoolingParams | None = None) -> list[PoolingRequestOutput]:
+        return self._run_engine(self._enqueue(prompts, pooling_params or PoolingParams()))
+
+    encode = embed
+
+    def beam_search(self, prompts, params: BeamSearchParams) -> list[BeamSearchOutput]:
+        """Width-``beam_width`` search driven through ``generate`` one token at a
+        time with ``logprobs = 2·width`` (prefix caching makes each round a
+        one-token step)."""
+        if isinstance(prompts, (str, dict)) or (prompts and isinstance(prompts[0], int)):
+            prompts = [prompts]
+        tok = self.get_tokenizer()
+        width = params.beam_width
+        eos = self.llm_engine.input_processor.eos
+        eos_ids = {eos} if isinstance(eos, int) else set(eos or [])
+        results = []
+        for prompt in prompts:
+            if isinstance(prompt, str):
+                base = tok.encode(prompt)
+            elif isinstance(prompt, dict):
+                base = prompt.get("prompt_token_ids") or tok.encode(prompt["prompt"])
+            else:
+                base = list(prompt)
+            beams = [BeamSearchSequence(tokens=list(base))]
+            finished: list[BeamSearchSequence] = []
+            sp = SamplingParams(max_tokens=1, temperature=0.0, logprobs=2 * width, detokenize=False)
+            for _ in range(params.max_tokens):
+                if not beams:
+                    break
+                outs = self.generate([{"prompt_token_ids": b.tokens} for b in beams], sp)
+                cand: list[BeamSearchSequence] = []
+                for beam, out in zip(beams, outs):
+                    for tid, lp in out.outputs[0].logprobs[0].items():
+                        seq = BeamSearchSequence(beam.tokens + [tid], beam.cum_logprob + lp.logprob)
+                        if tid in eos_ids and not params.ignore_eos:
+                            seq.finish_reason = "stop"
+                            finished.append(seq)
+                        else:
+                            cand.append(seq)
+                cand.sort(key=lambda s: s.cum_logprob, reverse=True)
+                beams = cand[:width]
+            finished.extend(beams)
+
+            def score(s: BeamSearchSequence) -> float:
+                n = len(s.tokens) - len(base)
+                return s.cum_logprob / (max(n, 1) ** params.length_penalty)
+            best = sorted(finished, key=score, reverse=True)[:width]
+            if tok is not None:
+                for s in best:
+                    s.text = tok.decode(s.tokens[len(base):])
+            results.append(BeamSearchOutput(best))
+        return results
+
+    # ------------------------------------------------------------------
+    def collective_rpc(self, method: str, *args, **kwargs):
+        return self.llm_engine.collective_rpc(method, *args, **kwargs)
+
+    def reset_prefix_cache(self) -> bool:
+        return self.llm_engine.reset_prefix_cache()
+
+    def shutdown(self) -> None:
+        self.llm_engine.shutdown()

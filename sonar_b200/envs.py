@@ -1,0 +1,65 @@
+"""Environment-variable registry with lazy, typed getters.
+
+Every variable the engine reads is declared here once, with its default and
+parser; ``envs.NAME`` evaluates the getter on access so tests can monkeypatch
+``os.environ``.  Parity: ``aphrodite/envs.py`` (lazy getters, one table).
+"""
+from __future__ import annotations
+
+import os
+from typing import Any, Callable
+
+
+def _bool(name: str, default: bool) -> Callable[[], bool]:
+    return lambda: os.environ.get(name, "1" if default else "0").lower() in ("1", "true", "yes", "on")
+
+
+def _int(name: str, default: int) -> Callable[[], int]:
+    return lambda: int(os.environ.get(name, default))
+
+
+def _str(name: str, default: str | None) -> Callable[[], str | None]:
+    return lambda: os.environ.get(name, default)
+
+
+def _float(name: str, default: float) -> Callable[[], float]:
+    return lambda: float(os.environ.get(name, default))
+
+
+environment_variables: dict[str, Callable[[], Any]] = {
+    # logging / debugging
+    "SONAR_LOG_LEVEL": _str("SONAR_LOG_LEVEL", "INFO"),
+    "SONAR_LOG_STATS_INTERVAL": _float("SONAR_LOG_STATS_INTERVAL", 10.0),
+    # op dispatch: "auto" uses the CUDA extension on a GPU and the PyTorch
+    # restatement on CPU; "torch" forces the restatement (tests, debugging).
+    "SONAR_OPS": _str("SONAR_OPS", "auto"),
+    # GEMM: "tcgen05" = hand-written kernel, "cublas" = torch.matmul baseline.
+    "SONAR_GEMM": _str("SONAR_GEMM", "tcgen05"),
+    # collectives: "fused" = GEMM+collective kernels, "custom" = P2P all-reduce,
+    # "nccl" = torch.distributed only (the baseline arm).
+    "SONAR_TP_COMM": _str("SONAR_TP_COMM", "fused"),
+    "SONAR_CUDA_GRAPHS": _bool("SONAR_CUDA_GRAPHS", True),
+    "SONAR_SYMM_HEAP_MB": _int("SONAR_SYMM_HEAP_MB", 512),
+    # server
+    "SONAR_HOST": _str("SONAR_HOST", "0.0.0.0"),
+    "SONAR_PORT": _int("SONAR_PORT", 2242),
+    "SONAR_API_KEY": _str("SONAR_API_KEY", None),
+    # engine process plumbing
+    "SONAR_RPC_TIMEOUT_S": _float("SONAR_RPC_TIMEOUT_S", 600.0),
+    "SONAR_WORKER_HEARTBEAT_S": _float("SONAR_WORKER_HEARTBEAT_S", 2.0),
+    "SONAR_ENGINE_MULTIPROCESSING": _bool("SONAR_ENGINE_MULTIPROCESSING", False),
+    "SONAR_MAX_N_SEQUENCES": _int("SONAR_MAX_N_SEQUENCES", 16384),
+    # pipeline-parallel layer partition override, e.g. "10,11,11"
+    "SONAR_PP_LAYER_PARTITION": _str("SONAR_PP_LAYER_PARTITION", None),
+    "SONAR_TRACE_FILE": _str("SONAR_TRACE_FILE", None),
+}
+
+
+def __getattr__(name: str) -> Any:
+    if name in environment_variables:
+        return environment_variables[name]()
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+
+
+def __dir__() -> list[str]:
+    return list(environment_variables)

@@ -1,0 +1,125 @@
+"""Executor interface: the engine core talks to workers only through this.
+
+``collective_rpc(method, *args)`` runs a worker method on every worker and
+returns the replies (all, or only the output rank's).  Implementations:
+``UniProcExecutor`` (worker in this process), ``ExternalLauncherExecutor``
+(this process *is* one rank of a torchrun job; every rank runs the same engine
+loop in lock step), ``MultiprocExecutor`` (spawns one process per GPU and
+broadcasts calls over a shared-memory ring).
+
+Parity: ``aphrodite/v1/executor/abstract.py:37-237``, ``uniproc_executor.py:45,150``.
+"""
+from __future__ import annotations
+
+import os
+from typing import Any
+
+from sonar_b200.config import EngineConfig
+from sonar_b200.core.kv_cache_manager import KVCacheConfig
+from sonar_b200.core.scheduler import ModelRunnerOutput, SchedulerOutput
+from sonar_b200.worker.worker import Worker, size_kv_cache
+
+
+class Executor:
+    def __init__(self, cfg: EngineConfig) -> None:
+        self.cfg = cfg
+        self.is_failed = False
+        self._failure_cb = None
+        self._init_executor()
+
+    @staticmethod
+    def get_class(cfg: EngineConfig) -> type["Executor"]:
+        backend = cfg.parallel.distributed_executor_backend
+        world = cfg.parallel.world_size
+        if backend is None:
+            if os.environ.get("WORLD_SIZE") and int(os.environ["WORLD_SIZE"]) > 1:
+                backend = "external_launcher"
+            else:
+                backend = "mp" if world > 1 else "uni"
+        if backend == "uni":
+            return UniProcExecutor
+        if backend == "external_launcher":
+            return ExternalLauncherExecutor
+        if backend == "mp":
+            from sonar_b200.executor.multiproc import MultiprocExecutor
+            return MultiprocExecutor
+        raise ValueError(f"unknown distributed_executor_backend {backend!r}")
+
+    # subclasses ---------------------------------------------------------
+    def _init_executor(self) -> None:
+        raise NotImplementedError
+
+    def collective_rpc(self, method: str, *args, output_rank_only: bool = False, **kwargs) -> list[Any]:
+        raise NotImplementedError
+
+    def shutdown(self) -> None:
+        pass
+
+    def register_failure_callback(self, cb) -> None:
+        self._failure_cb = cb
+
+    # common -------------------------------------------------------------
+    def initialize_kv_cache(self) -> KVCacheConfig:
+        specs = self.collective_rpc("get_kv_cache_spec")
+        avail = self.collective_rpc("determine_available_memory")
+        kv_cfg = size_kv_cache(self.cfg, specs, avail)
+        self.collective_rpc("initialize_from_config", kv_cfg)
+        self.collective_rpc("compile_or_warm_up_model")
+        return kv_cfg
+
+    def execute_model(self, so: SchedulerOutput) -> ModelRunnerOutput:
+        out = self.collective_rpc("execute_model", so, output_rank_only=True)
+        return out[0]
+
+    def check_health(self) -> None:
+        self.collective_rpc("check_health")
+
+
+class UniProcExecutor(Executor):
+    def _init_executor(self) -> None:
+        self.worker = Worker(self.cfg, rank=0, local_rank=0, world_size=1)
+        self.worker.init_device()
+        self.worker.load_model()
+
+    def collective_rpc(self, method: str, *args, output_rank_only: bool = False, **kwargs) -> list[Any]:
+        return [getattr(self.worker, method)(*args, **kwargs)]
+
+    def shutdown(self) -> None:
+        if getattr(self, "worker", None) is not None:
+            self.worker.shutdown()
+            self.worker = None
+
+
+class ExternalLauncherExecutor(UniProcExecutor):
+    """One rank of an externally launched SPMD job (torchrun).  Every rank owns
+    a full engine and scheduler; they stay identical because scheduling is a
+    deterministic function of the requests and of the sampled tokens, which the
+    output rank broadcasts when they are not already identical everywhere."""
+
+    def _init_executor(self) -> None:
+        rank = int(os.environ.get("RANK", 0))
+        local = int(os.environ.get("LOCAL_RANK", rank))
+        world = int(os.environ.get("WORLD_SIZE", 1))
+        self.worker = Worker(self.cfg, rank=rank, local_rank=local, world_size=world)
+        self.worker.init_device()
+        self.worker.load_model()
+
+    def initialize_kv_cache(self) -> KVCacheConfig:
+        from sonar_b200.parallel import state
+        spec = self.worker.get_kv_cache_spec()
+        avail = self.worker.determine_available_memory()
+        world = state.get_world_group()
+        all_avail = world.all_gather_object(avail)
+        kv_cfg = size_kv_cache(self.cfg, [spec], [min(all_avail)])
+        self.worker.initialize_from_config(kv_cfg)
+        self.worker.compile_or_warm_up_model()
+        return kv_cfg
+
+    def execute_model(self, so: SchedulerOutput) -> ModelRunnerOutput:
+        from sonar_b200.parallel import state
+        out = self.worker.execute_model(so)
+        pp = state.get_pp_group()
+        if pp.world_size > 1:
+            out = pp.broadcast_object(out, src=pp.world_size - 1)
+            self.worker.runner.apply_remote_output(so, out)
+        return out

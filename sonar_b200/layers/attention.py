@@ -1,0 +1,83 @@
+"""Attention layer glue: metadata, rotary tables, cache binding.
+
+``AttentionMetadata`` is built once per step by the model runner and shared by
+all layers.  ``Attention.forward`` takes the packed qkv activations, applies
+(optional q/k norm +) RoPE, writes K/V into this layer's paged cache and runs
+the unified varlen paged-attention kernel, all through ``sonar_b200.ops``.
+
+Parity: ``aphrodite/model_executor/layers/attention/attention.py:204,457`` and the
+metadata builders of ``v1/attention/backends/flash_attn.py``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+from torch import nn
+
+from sonar_b200 import ops
+from sonar_b200.ops import torch_ref
+
+
+@dataclass
+class AttentionMetadata:
+    num_tokens: int                 # real tokens this step (before padding)
+    num_seqs: int
+    positions: torch.Tensor         # int64/int32 [T]
+    slot_mapping: torch.Tensor      # int32 [T]; -1 = do not write
+    block_tables: torch.Tensor      # int32 [max_seqs, max_blocks]
+    seq_lens: torch.Tensor          # int32 [max_seqs] context length incl. this step's tokens
+    query_start_loc: torch.Tensor   # int32 [max_seqs + 1]
+    max_query_len: int = 1
+    max_seq_len: int = 1
+    # host copies (metadata builders for the kernels avoid device round trips)
+    query_lens_cpu: list[int] = field(default_factory=list)
+    seq_lens_cpu: list[int] = field(default_factory=list)
+    # kernel work list built by the runner for the CUDA path
+    work: Any = None
+    # decode-context-parallel: this rank holds tokens with index % dcp == dcp_rank
+    dcp_size: int = 1
+    dcp_rank: int = 0
+    # DeepSeek sparse attention: per-token selected key positions [T, K]
+    topk_indices: torch.Tensor | None = None
+
+
+_ROPE_CACHE: dict[tuple, torch.Tensor] = {}
+
+
+def get_cos_sin_cache(rot_dim: int, max_pos: int, theta: float, scaling: dict | None, device) -> torch.Tensor:
+    key = (rot_dim, max_pos, theta, str(scaling), str(device))
+    if key not in _ROPE_CACHE:
+        _ROPE_CACHE[key] = torch_ref.build_cos_sin_cache(rot_dim, max_pos, theta, scaling, device)
+    return _ROPE_CACHE[key]
+
+
+class Attention(nn.Module):
+    def __init__(self, num_heads: int, num_kv_heads: int, head_dim: int, scale: float, layer_idx: int,
+                 rope_theta: float, max_position: int, rope_scaling: dict | None = None,
+                 sliding_window: int | None = None, device=None, qk_norm_eps: float | None = None,
+                 dtype=torch.bfloat16) -> None:
+        super().__init__()
+        self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
+        self.scale, self.layer_idx, self.sliding_window = scale, layer_idx, sliding_window
+        self.cos_sin = get_cos_sin_cache(head_dim, max_position, rope_theta, rope_scaling, device)
+        self.kv_cache: torch.Tensor | None = None
+        self.k_scale = self.v_scale = 1.0
+        self.qk_norm_eps = qk_norm_eps
+        if qk_norm_eps is not None:
+            self.q_norm_weight = nn.Parameter(torch.ones(head_dim, dtype=dtype, device=device), requires_grad=False)
+            self.k_norm_weight = nn.Parameter(torch.ones(head_dim, dtype=dtype, device=device), requires_grad=False)
+        else:
+            self.q_norm_weight = self.k_norm_weight = None
+
+    def bind_kv_cache(self, cache: torch.Tensor) -> None:
+        self.kv_cache = cache
+
+    def forward(self, qkv: torch.Tensor, meta: AttentionMetadata) -> torch.Tensor:
+        q = ops.rope_and_cache(qkv, meta.positions, self.cos_sin, self.kv_cache, meta.slot_mapping,
+                               self.num_heads, self.num_kv_heads, self.head_dim,
+                               self.q_norm_weight, self.k_norm_weight, self.qk_norm_eps or 1e-6,
+                               self.k_scale, self.v_scale)
+        return ops.paged_attention(q, self.kv_cache, meta, self.scale, self.sliding_window,
+                                   self.k_scale, self.v_scale)

@@ -1,0 +1,223 @@
+"""Linear layers with tensor-parallel sharding and pluggable weight formats.
+
+``ColumnParallelLinear`` shards the output dim, ``RowParallelLinear`` the input
+dim; merged variants (``QKVParallelLinear``, ``MergedColumnParallelLinear``)
+stack several checkpoint tensors into one GEMM.  Layers only hold weights and
+apply the local GEMM — *communication lives in* ``sonar_b200.parallel.tp_ops``.
+A ``LinearMethod`` owns the weight format: bf16/fp16/fp32 (``UnquantizedMethod``)
+or fp8 e4m3 with 128×128 block scales and per-token-group activation scales
+(``Fp8BlockMethod``; checkpoint tensors ``weight`` + ``weight_scale_inv``).
+
+Parity: ``aphrodite/model_executor/layers/linear.py:143-1643`` and
+``layers/quantization/fp8.py:95-465``.
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from sonar_b200 import ops
+from sonar_b200.ops import torch_ref
+from sonar_b200.parallel import state
+
+FP8_BLOCK = 128
+
+
+class UnquantizedMethod:
+    name = "none"
+
+    def create(self, layer: "LinearBase", n: int, k: int, dtype: torch.dtype, device) -> None:
+        layer.weight = nn.Parameter(torch.empty(n, k, dtype=dtype, device=device), requires_grad=False)
+
+    def apply(self, layer: "LinearBase", x: torch.Tensor) -> torch.Tensor:
+        return ops.gemm(x, layer.weight, layer.bias)
+
+    def process_after_load(self, layer: "LinearBase") -> None:
+        pass
+
+
+class Fp8BlockMethod:
+    """fp8 e4m3 weights with one fp32 scale per 128×128 block; activations are
+    quantised on the fly with one scale per token per 128 input channels."""
+    name = "fp8"
+
+    def create(self, layer: "LinearBase", n: int, k: int, dtype: torch.dtype, device) -> None:
+        if k % FP8_BLOCK:
+            raise ValueError(f"fp8 block quantisation needs the input dim ({k}) to be a multiple of {FP8_BLOCK}")
+        layer.weight = nn.Parameter(torch.empty(n, k, dtype=torch.float8_e4m3fn, device=device),
+                                    requires_grad=False)
+        layer.weight_scale_inv = nn.Parameter(
+            torch.ones(-(-n // FP8_BLOCK), k // FP8_BLOCK, dtype=torch.float32, device=device),
+            requires_grad=False)
+        layer.out_dtype = dtype
+
+    def apply(self, layer: "LinearBase", x: torch.Tensor) -> torch.Tensor:
+        xq, xs = ops.per_token_group_quant_fp8(x, FP8_BLOCK)
+        y = ops.gemm_fp8_block(xq, xs, layer.weight, layer.weight_scale_inv, layer.out_dtype)
+        return y if layer.bias is None else y + layer.bias
+
+    def process_after_load(self, layer: "LinearBase") -> None:
+        pass
+
+    @staticmethod
+    def quantize_into(layer: "LinearBase", w: torch.Tensor) -> None:
+        q, s = torch_ref.block_quant_fp8_weight(w, FP8_BLOCK)
+        layer.weight.data.copy_(q)
+        layer.weight_scale_inv.data.copy_(s)
+
+
+def make_linear_method(quantization: str | None):
+    return Fp8BlockMethod() if quantization == "fp8" else UnquantizedMethod()
+
+
+class LinearBase(nn.Module):
+    def __init__(self, in_features: int, out_features: int, bias: bool, dtype: torch.dtype, device,
+                 quantization: str | None, prefix: str) -> None:
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.prefix = prefix
+        self.method = make_linear_method(quantization)
+        self.bias = None
+        self._want_bias = bias
+        self.dtype, self.device_ = dtype, device
+
+    def _alloc(self, n_local: int, k_local: int) -> None:
+        self.method.create(self, n_local, k_local, self.dtype, self.device_)
+        if self._want_bias:
+            self.bias = nn.Parameter(torch.zeros(n_local, dtype=self.dtype, device=self.device_),
+                                     requires_grad=False)
+
+    def apply(self, x: torch.Tensor) -> torch.Tensor:
+        return self.method.apply(self, x)
+
+    forward = apply
+
+    # weight loading helpers -------------------------------------------------
+    def _copy_rows(self, param: torch.Tensor, row_off: int, src: torch.Tensor) -> None:
+        param.data[row_off:row_off + src.shape[0]].copy_(src)
+
+
+class ReplicatedLinear(LinearBase):
+    def __init__(self, in_features, out_features, bias=False, dtype=torch.bfloat16, device=None,
+                 quantization=None, prefix="") -> None:
+        super().__init__(in_features, out_features, bias, dtype, device, quantization, prefix)
+        self._alloc(out_features, in_features)
+
+    def load_weight(self, name: str, tensor: torch.Tensor, shard_id=None) -> None:
+        getattr(self, name).data.copy_(tensor)
+
+
+class ColumnParallelLinear(LinearBase):
+    """Output dim split over the TP group.  ``output_sizes`` lists the logical
+    sub-matrices stacked along N (each is split separately, so every rank holds
+    its slice of every one)."""
+
+    def __init__(self, in_features, output_sizes: list[int], bias=False, dtype=torch.bfloat16, device=None,
+                 quantization=None, prefix="", tp_size: int | None = None, tp_rank: int | None = None) -> None:
+        super().__init__(in_features, sum(output_sizes), bias, dtype, device, quantization, prefix)
+        self.tp_size = tp_size if tp_size is not None else state.tp_world_size()
+        self.tp_rank = tp_rank if tp_rank is not None else state.tp_rank()
+        for n in output_sizes:
+            if n % self.tp_size:
+                raise ValueError(f"{prefix}: output size {n} not divisible by tp={self.tp_size}")
+        self.output_sizes = output_sizes
+        self.local_sizes = [n // self.tp_size for n in output_sizes]
+        self._alloc(sum(self.local_sizes), in_features)
+
+    def _local_offset(self, idx: int) -> int:
+        return sum(self.local_sizes[:idx])
+
+    def load_weight(self, name: str, tensor: torch.Tensor, shard_id: int | None = None) -> None:
+        """``tensor`` is the full (unsharded) checkpoint tensor of sub-matrix
+        ``shard_id`` (or of the whole layer when there is only one)."""
+        param = getattr(self, name)
+        ids = range(len(self.output_sizes)) if shard_id is None and len(self.output_sizes) > 1 else [shard_id or 0]
+        src_off = 0
+        for i in ids:
+            full, local = self.output_sizes[i], self.local_sizes[i]
+            if name == "weight_scale_inv":
+                # scale rows follow weight rows in units of 128
+                assert local % FP8_BLOCK == 0 or self.tp_size == 1, \
+                    f"{self.prefix}: fp8 block scales need shard rows ({local}) divisible by {FP8_BLOCK}"
+                fb, lb = -(-full // FP8_BLOCK), -(-local // FP8_BLOCK)
+                src = tensor[src_off // FP8_BLOCK + self.tp_rank * lb: src_off // FP8_BLOCK + (self.tp_rank + 1) * lb]
+                dst_off = self._local_offset(i) // FP8_BLOCK
+                param.data[dst_off:dst_off + lb].copy_(src)
+                if shard_id is None:
+                    src_off += fb * FP8_BLOCK
+            else:
+                src = tensor[src_off + self.tp_rank * local: src_off + (self.tp_rank + 1) * local]
+                self._copy_rows(param, self._local_offset(i), src)
+                if shard_id is None:
+                    src_off += full
+
+
+class MergedColumnParallelLinear(ColumnParallelLinear):
+    """gate_proj and up_proj in one GEMM."""
+
+
+class QKVParallelLinear(ColumnParallelLinear):
+    """q, k and v projections in one GEMM.  When there are fewer KV heads than
+    TP ranks the KV heads are replicated (each rank holds one)."""
+
+    def __init__(self, hidden_size, head_dim, num_heads, num_kv_heads, bias=False, dtype=torch.bfloat16,
+                 device=None, quantization=None, prefix="", tp_size=None, tp_rank=None) -> None:
+        tp = tp_size if tp_size is not None else state.tp_world_size()
+        rank = tp_rank if tp_rank is not None else state.tp_rank()
+        self.head_dim = head_dim
+        self.total_heads, self.total_kv_heads = num_heads, num_kv_heads
+        self.num_heads = num_heads // tp
+        if num_kv_heads >= tp:
+            self.num_kv_heads, self.kv_replicas = num_kv_heads // tp, 1
+        else:
+            self.num_kv_heads, self.kv_replicas = 1, tp // num_kv_heads
+        LinearBase.__init__(self, hidden_size, (num_heads + 2 * num_kv_heads) * head_dim, bias, dtype, device,
+                            quantization, prefix)
+        self.tp_size, self.tp_rank = tp, rank
+        self.output_sizes = [num_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * head_dim]
+        self.local_sizes = [self.num_heads * head_dim, self.num_kv_heads * head_dim, self.num_kv_heads * head_dim]
+        self._alloc(sum(self.local_sizes), hidden_size)
+
+    def load_weight(self, name: str, tensor: torch.Tensor, shard_id: int | str | None = None) -> None:
+        idx = {"q": 0, "k": 1, "v": 2}.get(shard_id, shard_id)
+        param = getattr(self, name)
+        unit = FP8_BLOCK if name == "weight_scale_inv" else 1
+        if idx is None:  # fused qkv tensor in the checkpoint
+            off = 0
+            for i, full in enumerate(self.output_sizes):
+                self.load_weight(name, tensor[off // unit:(off + full) // unit], i)
+                off += full
+            return
+        local = self.local_sizes[idx]
+        shard = self.tp_rank if idx == 0 else self.tp_rank // self.kv_replicas
+        src = tensor[shard * local // unit:(shard + 1) * local // unit]
+        dst = self._local_offset(idx) // unit
+        param.data[dst:dst + src.shape[0]].copy_(src)
+
+
+class RowParallelLinear(LinearBase):
+    """Input dim split over the TP group; the caller reduces the partial outputs."""
+
+    def __init__(self, in_features, out_features, bias=False, dtype=torch.bfloat16, device=None,
+                 quantization=None, prefix="", tp_size=None, tp_rank=None) -> None:
+        super().__init__(in_features, out_features, bias, dtype, device, quantization, prefix)
+        self.tp_size = tp_size if tp_size is not None else state.tp_world_size()
+        self.tp_rank = tp_rank if tp_rank is not None else state.tp_rank()
+        if in_features % self.tp_size:
+            raise ValueError(f"{prefix}: input size {in_features} not divisible by tp={self.tp_size}")
+        self.k_local = in_features // self.tp_size
+        self._alloc(out_features, self.k_local)
+        if self.bias is not None and self.tp_rank != 0:
+            self.bias = None  # added once, by rank 0's partial
+
+    def load_weight(self, name: str, tensor: torch.Tensor, shard_id=None) -> None:
+        param = getattr(self, name)
+        if name == "bias":
+            param.data.copy_(tensor)
+            return
+        unit = FP8_BLOCK if name == "weight_scale_inv" else 1
+        k = self.k_local // unit if unit > 1 else self.k_local
+        if unit > 1:
+            assert self.k_local % FP8_BLOCK == 0 or self.tp_size == 1
+            k = -(-self.k_local // FP8_BLOCK)
+        param.data.copy_(tensor[:, self.tp_rank * k:(self.tp_rank + 1) * k])

@@ -1,0 +1,181 @@
+"""Model construction and weight loading.
+
+``load_model`` builds the architecture on the target device and fills it
+either from HF-format safetensors shards (bf16/fp16/fp32, or fp8 e4m3 with
+``weight_scale_inv`` 128×128 block scales) or, for ``load_format="dummy"``,
+with seeded random weights of the right shapes and formats.  The safetensors
+reader is in-tree (the format is an 8-byte header length, a JSON header and raw
+little-endian tensors), memory-maps the shard and copies each tensor straight
+into its (possibly TP-sliced) destination.
+
+Parity: ``aphrodite/model_executor/model_loader/`` (default and dummy loaders)
+and ``models/utils.py`` ``AutoWeightsLoader``.
+"""
+from __future__ import annotations
+
+import glob
+import json
+import mmap
+import os
+import struct
+from typing import Iterator
+
+import torch
+from torch import nn
+
+from sonar_b200.config import EngineConfig, ModelConfig
+from sonar_b200.layers.linear import Fp8BlockMethod, LinearBase
+from sonar_b200.logger import init_logger
+from sonar_b200.models.registry import resolve_model_cls
+
+logger = init_logger(__name__)
+
+_ST_DTYPES = {
+    "F32": torch.float32, "F16": torch.float16, "BF16": torch.bfloat16, "F8_E4M3": torch.float8_e4m3fn,
+    "I64": torch.int64, "I32": torch.int32, "U8": torch.uint8, "I8": torch.int8, "BOOL": torch.bool,
+    "F64": torch.float64, "I16": torch.int16,
+}
+_ST_NAMES = {v: k for k, v in _ST_DTYPES.items()}
+
+
+def read_safetensors(path: str) -> Iterator[tuple[str, torch.Tensor]]:
+    """Yield ``(name, tensor)`` views over a memory-mapped safetensors file."""
+    with open(path, "rb") as f:
+        (hlen,) = struct.unpack("<Q", f.read(8))
+        header = json.loads(f.read(hlen))
+        mm = mmap.mmap(f.fileno(), 0, access=mmap.ACCESS_READ)
+    base = 8 + hlen
+    buf = memoryview(mm)
+    for name, info in header.items():
+        if name == "__metadata__":
+            continue
+        dtype = _ST_DTYPES[info["dtype"]]
+        lo, hi = info["data_offsets"]
+        if hi == lo:
+            yield name, torch.empty(info["shape"], dtype=dtype)
+            continue
+        flat = torch.frombuffer(buf[base + lo: base + hi], dtype=torch.uint8)
+        yield name, flat.view(dtype).reshape(info["shape"])
+
+
+def write_safetensors(path: str, tensors: dict[str, torch.Tensor]) -> None:
+    header, off, blobs = {}, 0, []
+    for name, t in tensors.items():
+        raw = t.detach().cpu().contiguous().view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        header[name] = {"dtype": _ST_NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
+        off += len(raw)
+        blobs.append(raw)
+    hjson = json.dumps(header, separators=(",", ":")).encode()
+    hjson += b" " * ((8 - len(hjson) % 8) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(hjson)))
+        f.write(hjson)
+        for b in blobs:
+            f.write(b)
+
+
+def save_checkpoint(directory: str, hf_config: dict, tensors: dict[str, torch.Tensor]) -> None:
+    """Write an HF-layout checkpoint directory (used by tests and tools)."""
+    os.makedirs(directory, exist_ok=True)
+    with open(os.path.join(directory, "config.json"), "w") as f:
+        json.dump(hf_config, f)
+    write_safetensors(os.path.join(directory, "model.safetensors"), tensors)
+
+
+def _iter_checkpoint(directory: str) -> Iterator[tuple[str, torch.Tensor]]:
+    files = sorted(glob.glob(os.path.join(directory, "*.safetensors")))
+    if not files:
+        raise FileNotFoundError(f"no *.safetensors files in {directory}")
+    for path in files:
+        yield from read_safetensors(path)
+
+
+def _assign(model: nn.Module, name: str, tensor: torch.Tensor, shard) -> bool:
+    mod_path, _, pname = name.rpartition(".")
+    try:
+        mod = model.get_submodule(mod_path)
+    except AttributeError:
+        return False
+    if not hasattr(mod, pname):
+        return False
+    if hasattr(mod, "load_weight"):
+        mod.load_weight(pname, tensor, shard)
+    else:
+        getattr(mod, pname).data.copy_(tensor)
+    return True
+
+
+def load_weights_from(model: nn.Module, weights: Iterator[tuple[str, torch.Tensor]]) -> set[str]:
+    loaded: set[str] = set()
+    custom = getattr(model, "load_special_weight", None)
+    for name, tensor in weights:
+        if custom is not None and custom(name, tensor):
+            loaded.add(name)
+            continue
+        mapped = model.map_checkpoint_name(name)
+        if mapped is None:
+            continue
+        target, shard = mapped
+        if _assign(model, target, tensor, shard):
+            loaded.add(name)
+    return loaded
+
+
+@torch.no_grad()
+def initialize_dummy_weights(model: nn.Module, seed: int, std: float = 0.02) -> None:
+    """Seeded random weights: normal(0, std) for matrices, ones for norm
+    gains, zeros for biases; fp8 layers get random bf16 weights quantised with
+    real 128×128 block scales."""
+    done: set[int] = set()
+    for mod_name, mod in model.named_modules():
+        if isinstance(mod, LinearBase) and isinstance(mod.method, Fp8BlockMethod):
+            gen = torch.Generator(device=mod.weight.device).manual_seed(_name_seed(mod_name, seed))
+            w = torch.empty(mod.weight.shape, dtype=torch.bfloat16, device=mod.weight.device)
+            w.normal_(0.0, std, generator=gen)
+            Fp8BlockMethod.quantize_into(mod, w)
+            done.add(id(mod.weight))
+            done.add(id(mod.weight_scale_inv))
+        init = getattr(mod, "init_dummy", None)
+        if init is not None:
+            done.update(init(seed, std))
+    for name, p in model.named_parameters():
+        if id(p) in done:
+            continue
+        done.add(id(p))
+        if "norm" in name and p.dim() == 1:
+            p.data.fill_(1.0)
+        elif name.endswith("bias") or p.dim() == 1:
+            p.data.zero_()
+        elif p.dtype in (torch.float32, torch.float16, torch.bfloat16):
+            gen = torch.Generator(device=p.device).manual_seed(_name_seed(name, seed))
+            p.data.normal_(0.0, std, generator=gen)
+        else:
+            raise TypeError(f"no dummy initialiser for {name} of dtype {p.dtype}")
+
+
+def _name_seed(name: str, seed: int) -> int:
+    h = 1469598103934665603
+    for ch in name.encode():
+        h = ((h ^ ch) * 1099511628211) & 0xFFFFFFFFFFFFFFFF
+    return (h ^ seed) & 0x7FFFFFFFFFFFFFFF
+
+
+def load_model(cfg: EngineConfig | ModelConfig, device: torch.device | str) -> nn.Module:
+    mcfg = cfg.model if isinstance(cfg, EngineConfig) else cfg
+    cls = resolve_model_cls(mcfg.architecture)
+    model = cls(mcfg, torch.device(device))
+    model.eval()
+    if mcfg.load_format == "dummy":
+        initialize_dummy_weights(model, mcfg.seed)
+    else:
+        loaded = load_weights_from(model, _iter_checkpoint(mcfg.checkpoint_dir))
+        logger.info("loaded %d tensors from %s", len(loaded), mcfg.checkpoint_dir)
+        if not loaded:
+            raise RuntimeError(f"no tensor of {mcfg.checkpoint_dir} matched the model")
+    for mod in model.modules():
+        if isinstance(mod, LinearBase):
+            mod.method.process_after_load(mod)
+        post = getattr(mod, "process_after_load", None)
+        if post is not None and not isinstance(mod, LinearBase):
+            post()
+    return model

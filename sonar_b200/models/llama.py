@@ -1,0 +1,191 @@
+"""Llama-family dense decoders: Llama 2/3, Mistral, Qwen2 (qkv bias), Qwen3
+(per-head q/k RMSNorm, optional tied LM head).
+
+The decoder layer is written against ``TPContext`` (``parallel/tp_ops.py``):
+``add_norm → col_linear → attention → row_linear → add_norm → col_linear →
+SwiGLU → row_linear``; whether activations between blocks are replicated or
+token-scattered, and where the collectives run, is the context's business.
+
+Parity: ``aphrodite/model_executor/models/llama.py:80-510``,
+``models/qwen3.py:71-331`` (q/k norm ``:152-168``, tied head ``:289-292``).
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from sonar_b200 import ops
+from sonar_b200.config import ModelConfig
+from sonar_b200.layers.attention import Attention, AttentionMetadata
+from sonar_b200.layers.embedding import ParallelLMHead, VocabParallelEmbedding
+from sonar_b200.layers.linear import MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear
+from sonar_b200.layers.norm import RMSNorm
+from sonar_b200.parallel import state
+from sonar_b200.parallel.tp_ops import get_tp_context
+
+
+def pp_layer_range(num_layers: int) -> tuple[int, int]:
+    """Layers ``[start, end)`` held by this pipeline stage (even split, the
+    remainder going to the later stages; ``SONAR_PP_LAYER_PARTITION`` overrides)."""
+    from sonar_b200 import envs
+    if not state.model_parallel_is_initialized():
+        return 0, num_layers
+    pp = state.get_pp_group()
+    n, r = pp.world_size, pp.rank_in_group
+    override = envs.SONAR_PP_LAYER_PARTITION
+    if override:
+        parts = [int(x) for x in override.split(",")]
+        if len(parts) != n or sum(parts) != num_layers:
+            raise ValueError(f"SONAR_PP_LAYER_PARTITION={override!r} does not fit {num_layers} layers on {n} stages")
+    else:
+        base, rem = divmod(num_layers, n)
+        parts = [base + (1 if i >= n - rem else 0) for i in range(n)]
+    start = sum(parts[:r])
+    return start, start + parts[r]
+
+
+class LlamaMLP(nn.Module):
+    def __init__(self, hidden: int, inter: int, dtype, device, quant, prefix: str) -> None:
+        super().__init__()
+        self.gate_up_proj = MergedColumnParallelLinear(hidden, [inter, inter], False, dtype, device, quant,
+                                                       f"{prefix}.gate_up_proj")
+        self.down_proj = RowParallelLinear(inter, hidden, False, dtype, device, quant, f"{prefix}.down_proj")
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        tp = get_tp_context()
+        gu = tp.col_linear(x, self.gate_up_proj)
+        return tp.row_linear(ops.silu_and_mul(gu), self.down_proj)
+
+
+class LlamaAttention(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> None:
+        super().__init__()
+        hidden, hd = cfg.hidden_size, cfg.head_dim
+        quant = cfg.quantization
+        bias = bool(cfg.get("attention_bias", False)) or cfg.get("model_type") == "qwen2"
+        self.qkv_proj = QKVParallelLinear(hidden, hd, cfg.num_attention_heads, cfg.num_kv_heads, bias,
+                                          cfg.dtype, device, quant, f"{prefix}.qkv_proj")
+        self.o_proj = RowParallelLinear(cfg.num_attention_heads * hd, hidden, False, cfg.dtype, device, quant,
+                                        f"{prefix}.o_proj")
+        qk_eps = cfg.get("rms_norm_eps", 1e-6) if cfg.get("model_type") in ("qwen3", "qwen3_moe") else None
+        sw = cfg.get("sliding_window") if cfg.get("use_sliding_window", cfg.get("model_type") == "mistral") else None
+        self.attn = Attention(self.qkv_proj.num_heads, self.qkv_proj.num_kv_heads, hd, hd ** -0.5, layer_idx,
+                              float(cfg.get("rope_theta", 1e4)), cfg.max_model_len, cfg.get("rope_scaling"),
+                              sw, device, qk_eps, cfg.dtype)
+
+    def forward(self, x: torch.Tensor, meta: AttentionMetadata) -> torch.Tensor:
+        tp = get_tp_context()
+        qkv = tp.col_linear(x, self.qkv_proj)
+        o = self.attn(qkv, meta)
+        return tp.row_linear(o, self.o_proj)
+
+
+class LlamaDecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> None:
+        super().__init__()
+        eps = cfg.get("rms_norm_eps", 1e-6)
+        self.self_attn = LlamaAttention(cfg, layer_idx, device, f"{prefix}.self_attn")
+        self.mlp = self._make_mlp(cfg, layer_idx, device, f"{prefix}.mlp")
+        self.input_layernorm = RMSNorm(cfg.hidden_size, eps, cfg.dtype, device)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, eps, cfg.dtype, device)
+
+    def _make_mlp(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> nn.Module:
+        return LlamaMLP(cfg.hidden_size, int(cfg.get("intermediate_size")), cfg.dtype, device,
+                        cfg.quantization, prefix)
+
+    def forward(self, h: torch.Tensor, residual: torch.Tensor | None, meta: AttentionMetadata):
+        tp = get_tp_context()
+        x, residual = tp.add_norm(h, residual, self.input_layernorm.weight, self.input_layernorm.eps)
+        h = self.self_attn(x, meta)
+        x, residual = tp.add_norm(h, residual, self.post_attention_layernorm.weight,
+                                  self.post_attention_layernorm.eps)
+        h = self.mlp(x)
+        return h, residual
+
+
+class LlamaModel(nn.Module):
+    layer_cls = LlamaDecoderLayer
+
+    def __init__(self, cfg: ModelConfig, device) -> None:
+        super().__init__()
+        self.cfg = cfg
+        self.start_layer, self.end_layer = pp_layer_range(cfg.num_layers)
+        pp = state.get_pp_group() if state.model_parallel_is_initialized() else None
+        self.is_first = pp is None or pp.rank_in_group == 0
+        self.is_last = pp is None or pp.rank_in_group == pp.world_size - 1
+        tied = bool(cfg.get("tie_word_embeddings", False))
+        if self.is_first or (tied and self.is_last):
+            self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device,
+                                                       "model.embed_tokens")
+        self.layers = nn.ModuleDict({
+            str(i): self.layer_cls(cfg, i, device, f"model.layers.{i}")
+            for i in range(self.start_layer, self.end_layer)})
+        if self.is_last:
+            self.norm = RMSNorm(cfg.hidden_size, cfg.get("rms_norm_eps", 1e-6), cfg.dtype, device)
+
+    def forward(self, input_ids: torch.Tensor | None, meta: AttentionMetadata,
+                intermediate: tuple[torch.Tensor, torch.Tensor | None] | None = None):
+        tp = get_tp_context()
+        if self.is_first:
+            h = tp.embed_reduce(self.embed_tokens(input_ids))
+            residual = None
+        else:
+            h, residual = intermediate
+        for layer in self.layers.values():
+            h, residual = layer(h, residual, meta)
+        if not self.is_last:
+            return h, residual
+        x, _ = tp.add_norm(h, residual, self.norm.weight, self.norm.eps)
+        return x
+
+
+class LlamaForCausalLM(nn.Module):
+    model_cls = LlamaModel
+    # checkpoint name fragments → (merged parameter, shard id)
+    stacked_params = [
+        (".q_proj.", ".qkv_proj.", "q"), (".k_proj.", ".qkv_proj.", "k"), (".v_proj.", ".qkv_proj.", "v"),
+        (".gate_proj.", ".gate_up_proj.", 0), (".up_proj.", ".gate_up_proj.", 1)]
+
+    def __init__(self, cfg: ModelConfig, device=None) -> None:
+        super().__init__()
+        self.cfg = cfg
+        self.model = self.model_cls(cfg, device)
+        self.tied = bool(cfg.get("tie_word_embeddings", False))
+        if self.model.is_last:
+            if self.tied:
+                self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device, "lm_head")
+                self.lm_head.weight = self.model.embed_tokens.weight
+            else:
+                self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device, "lm_head")
+
+    def forward(self, input_ids, meta, intermediate=None):
+        return self.model(input_ids, meta, intermediate)
+
+    def compute_logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        return self.lm_head.logits(hidden)
+
+    def attention_layers(self) -> list[Attention]:
+        return [layer.self_attn.attn for layer in self.model.layers.values()]
+
+    def map_checkpoint_name(self, name: str) -> tuple[str, int | str | None] | None:
+        """Checkpoint tensor name → (parameter path in this module, shard id);
+        ``None`` for tensors this rank/stage does not hold."""
+        if "rotary_emb.inv_freq" in name:
+            return None
+        if name.startswith("lm_head.") and self.tied:
+            return None
+        if ".self_attn.q_norm." in name:
+            name = name.replace(".self_attn.q_norm.weight", ".self_attn.attn.q_norm_weight")
+        if ".self_attn.k_norm." in name:
+            name = name.replace(".self_attn.k_norm.weight", ".self_attn.attn.k_norm_weight")
+        shard = None
+        for frag, merged, sid in self.stacked_params:
+            if frag in name:
+                name, shard = name.replace(frag, merged), sid
+                break
+        return name, shard
+
+
+Qwen3ForCausalLM = LlamaForCausalLM
+Qwen2ForCausalLM = LlamaForCausalLM
+MistralForCausalLM = LlamaForCausalLM

@@ -1,0 +1,33 @@
+"""Architecture name → model class (lazy imports).
+Parity: ``aphrodite/model_executor/models/registry.py``."""
+from __future__ import annotations
+
+import importlib
+
+_MODELS: dict[str, tuple[str, str]] = {
+    "LlamaForCausalLM": ("sonar_b200.models.llama", "LlamaForCausalLM"),
+    "MistralForCausalLM": ("sonar_b200.models.llama", "LlamaForCausalLM"),
+    "Qwen2ForCausalLM": ("sonar_b200.models.llama", "LlamaForCausalLM"),
+    "Qwen3ForCausalLM": ("sonar_b200.models.llama", "LlamaForCausalLM"),
+    "Qwen3MoeForCausalLM": ("sonar_b200.models.qwen3_moe", "Qwen3MoeForCausalLM"),
+    "MixtralForCausalLM": ("sonar_b200.models.qwen3_moe", "MixtralForCausalLM"),
+    "DeepseekV2ForCausalLM": ("sonar_b200.models.deepseek", "DeepseekForCausalLM"),
+    "DeepseekV3ForCausalLM": ("sonar_b200.models.deepseek", "DeepseekForCausalLM"),
+    "DeepseekV32ForCausalLM": ("sonar_b200.models.deepseek", "DeepseekForCausalLM"),
+}
+
+
+def register_model(arch: str, module: str, cls: str) -> None:
+    """Plugin hook: make an out-of-tree architecture loadable."""
+    _MODELS[arch] = (module, cls)
+
+
+def supported_architectures() -> list[str]:
+    return sorted(_MODELS)
+
+
+def resolve_model_cls(arch: str):
+    if arch not in _MODELS:
+        raise ValueError(f"architecture {arch!r} is not supported; known: {supported_architectures()}")
+    module, cls = _MODELS[arch]
+    return getattr(importlib.import_module(module), cls)

@@ -1,0 +1,182 @@
+"""Device-op front door.
+
+Every op has two implementations: hand-written sm_100a kernels
+(``sonar_b200.ops.cuda``, loaded from the in-tree ``_C.so``) and the PyTorch
+restatement (``sonar_b200.ops.torch_ref``) that defines the numerics and runs on
+CPU.  CUDA tensors always go to the kernels; if the library is missing on a GPU
+machine the import fails loudly instead of silently degrading.  Setting
+``SONAR_OPS=torch`` forces the restatement (debugging only).
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from sonar_b200.ops import torch_ref as ref
+
+_FORCE_TORCH = os.environ.get("SONAR_OPS", "auto") == "torch"
+_cuda = None
+
+
+def cuda_ops():
+    """The ctypes binding of the kernel library (imported on first use)."""
+    global _cuda
+    if _cuda is None:
+        from sonar_b200.ops import cuda as _c
+        _cuda = _c
+    return _cuda
+
+
+def _use_cuda(x: torch.Tensor) -> bool:
+    return x.is_cuda and not _FORCE_TORCH
+
+
+# ---- norms -----------------------------------------------------------------
+def rms_norm(x, weight, eps, out=None):
+    if _use_cuda(x):
+        return cuda_ops().rms_norm(x, weight, eps, out)
+    y = ref.rms_norm(x, weight, eps)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def fused_add_rms_norm(x, residual, weight, eps):
+    """In place: residual <- x + residual; x <- norm(residual).  Returns (x, residual)."""
+    if _use_cuda(x):
+        return cuda_ops().fused_add_rms_norm(x, residual, weight, eps)
+    y, r = ref.fused_add_rms_norm(x, residual, weight, eps)
+    x.copy_(y)
+    residual.copy_(r)
+    return x, residual
+
+
+# ---- rope + cache ------------------------------------------------------------
+def rope_and_cache(qkv, positions, cos_sin, kv_cache, slot_mapping, num_q_heads, num_kv_heads, head_dim,
+                   q_norm_w=None, k_norm_w=None, eps=1e-6, k_scale=1.0, v_scale=1.0):
+    """One pass over packed ``qkv [T, (Hq+2Hk)*D]``: optional per-head q/k RMSNorm,
+    NeoX RoPE on q and k (q rotated in place), K and V scattered into the paged
+    cache.  Returns the q view ``[T, Hq, D]``."""
+    t = qkv.shape[0]
+    qd, kd = num_q_heads * head_dim, num_kv_heads * head_dim
+    if _use_cuda(qkv):
+        cuda_ops().rope_and_cache(qkv, positions, cos_sin, kv_cache, slot_mapping, num_q_heads,
+                                  num_kv_heads, head_dim, q_norm_w, k_norm_w, eps, k_scale, v_scale)
+        return qkv.as_strided((t, num_q_heads, head_dim), (qkv.stride(0), head_dim, 1))
+    q, k, v = qkv.split([qd, kd, kd], dim=-1)
+    if q_norm_w is not None:
+        q, k = ref.qk_norm_rope(q, k, q_norm_w, k_norm_w, eps, positions, cos_sin, head_dim)
+    else:
+        q, k = ref.rope(q, k, positions, cos_sin, head_dim, True)
+    if kv_cache is not None:
+        ref.reshape_and_cache(k.reshape(t, num_kv_heads, head_dim), v.reshape(t, num_kv_heads, head_dim),
+                              kv_cache, slot_mapping, k_scale, v_scale)
+    return q.reshape(t, num_q_heads, head_dim)
+
+
+def paged_attention(q, kv_cache, meta, scale, sliding_window=None, k_scale=1.0, v_scale=1.0, out=None):
+    """q: [T, Hq, D] (may be a strided view of packed qkv) → [T, Hq*D]."""
+    if _use_cuda(q):
+        return cuda_ops().paged_attention(q, kv_cache, meta, scale, sliding_window, k_scale, v_scale, out)
+    o = ref.paged_attention(q, kv_cache, meta.block_tables, meta.seq_lens, meta.query_start_loc, scale,
+                            meta.num_seqs, sliding_window, k_scale, v_scale)
+    o = o.reshape(q.shape[0], -1)
+    if out is not None:
+        out.copy_(o)
+        return out
+    return o
+
+
+def merge_attn_states(o1, lse1, o2, lse2):
+    if _use_cuda(o1):
+        return cuda_ops().merge_attn_states(o1, lse1, o2, lse2)
+    return ref.merge_attn_states(o1, lse1, o2, lse2)
+
+
+# ---- activations ---------------------------------------------------------------
+def silu_and_mul(x, out=None):
+    if _use_cuda(x):
+        return cuda_ops().silu_and_mul(x, out)
+    y = ref.silu_and_mul(x)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+# ---- GEMM ----------------------------------------------------------------------
+def gemm(x, w, bias=None, out=None):
+    """y[T, N] = x[T, K] @ w[N, K]^T."""
+    if _use_cuda(x):
+        return cuda_ops().gemm(x, w, bias, out)
+    y = ref.gemm(x, w, bias)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def per_token_group_quant_fp8(x, group=128):
+    if _use_cuda(x):
+        return cuda_ops().per_token_group_quant_fp8(x, group)
+    return ref.per_token_group_quant_fp8(x, group)
+
+
+def gemm_fp8_block(xq, xs, wq, ws, out_dtype=torch.bfloat16, out=None):
+    if _use_cuda(xq):
+        return cuda_ops().gemm_fp8_block(xq, xs, wq, ws, out_dtype, out)
+    y = ref.gemm_fp8_block(xq, xs, wq, ws, out_dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+# ---- MoE -----------------------------------------------------------------------
+def topk_softmax(logits, k, renormalize):
+    if _use_cuda(logits):
+        return cuda_ops().topk_softmax(logits, k, renormalize)
+    return ref.topk_softmax(logits, k, renormalize)
+
+
+def grouped_topk(logits, bias, k, n_group, topk_group, renormalize, scale, scoring="sigmoid"):
+    if _use_cuda(logits):
+        return cuda_ops().grouped_topk(logits, bias, k, n_group, topk_group, renormalize, scale, scoring)
+    return ref.grouped_topk(logits, bias, k, n_group, topk_group, renormalize, scale, scoring)
+
+
+def fused_experts(x, w13, w2, topk_w, topk_ids, expert_map=None):
+    if _use_cuda(x):
+        return cuda_ops().fused_experts(x, w13, w2, topk_w, topk_ids, expert_map)
+    return ref.fused_experts(x, w13, w2, topk_w, topk_ids, expert_map)
+
+
+# ---- MLA -----------------------------------------------------------------------
+def mla_cache_write(kv_c, k_pe, cache, slot_mapping):
+    if _use_cuda(kv_c):
+        return cuda_ops().mla_cache_write(kv_c, k_pe, cache, slot_mapping)
+    return ref.mla_cache_write(kv_c, k_pe, cache, slot_mapping)
+
+
+def mla_paged_attention(q_nope, q_pe, cache, meta, scale, kv_lora_rank, topk_indices=None):
+    if _use_cuda(q_nope):
+        return cuda_ops().mla_paged_attention(q_nope, q_pe, cache, meta, scale, kv_lora_rank, topk_indices)
+    return ref.mla_paged_attention(q_nope, q_pe, cache, meta.block_tables, meta.seq_lens,
+                                   meta.query_start_loc, scale, kv_lora_rank, topk_indices)
+
+
+# ---- sampling --------------------------------------------------------------------
+def sample(logits, temperature, top_k, top_p, min_p, noise=None, seeds=None, generators=None):
+    """Token ids ``[B]`` from ``logits [B, V]``: arg-max for temperature 0 rows,
+    top-k/top-p/min-p truncated sampling for the rest."""
+    if _use_cuda(logits):
+        return cuda_ops().sample(logits, temperature, top_k, top_p, min_p, noise, seeds)
+    return ref.sample_from_logits(logits, temperature, top_k, top_p, min_p, noise, generators)
+
+
+def argmax(logits):
+    if _use_cuda(logits):
+        return cuda_ops().argmax(logits)
+    return logits.argmax(dim=-1)

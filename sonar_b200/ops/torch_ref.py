@@ -1,0 +1,402 @@
+"""Plain-PyTorch restatement of every device op.
+
+These functions define the numerics: the CUDA kernels are tested against them
+(in fp32), and they are what runs on a CPU-only machine.  They are not a
+fallback on a GPU box: ``sonar_b200.ops`` refuses to use them on CUDA tensors
+unless ``SONAR_OPS=torch`` is set explicitly.
+
+KV-cache layout (one tensor per layer):
+``[num_blocks, 2, num_kv_heads, block_size, head_dim]`` — K and V planes of a
+block, each head's ``block_size × head_dim`` tile contiguous.
+MLA cache layout: ``[num_blocks, block_size, kv_lora_rank + rope_dim]``.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+FP8_MAX = 448.0
+
+
+# ---------------------------------------------------------------- norms
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    var = xf.pow(2).mean(dim=-1, keepdim=True)
+    return (xf * torch.rsqrt(var + eps) * weight.float()).to(x.dtype)
+
+
+def fused_add_rms_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float
+                       ) -> tuple[torch.Tensor, torch.Tensor]:
+    """residual <- x + residual (stored in the activation dtype), out = norm(residual)."""
+    r = (x.float() + residual.float()).to(x.dtype)
+    return rms_norm(r, weight, eps), r
+
+
+# ---------------------------------------------------------------- rope
+def build_cos_sin_cache(rot_dim: int, max_pos: int, theta: float, scaling: dict | None = None,
+                        device=None) -> torch.Tensor:
+    """``[max_pos, rot_dim]`` fp32: cos in the first half, sin in the second."""
+    inv = 1.0 / (theta ** (torch.arange(0, rot_dim, 2, dtype=torch.float32) / rot_dim))
+    mscale = 1.0
+    if scaling:
+        kind = scaling.get("rope_type", scaling.get("type"))
+        if kind == "llama3":
+            factor = scaling["factor"]
+            lo, hi = scaling.get("low_freq_factor", 1.0), scaling.get("high_freq_factor", 4.0)
+            old = scaling["original_max_position_embeddings"]
+            wavelen = 2 * math.pi / inv
+            smooth = ((old / wavelen) - lo) / (hi - lo)
+            scaled = torch.where(wavelen > old / lo, inv / factor,
+                                 torch.where(wavelen < old / hi, inv,
+                                             (1 - smooth) * inv / factor + smooth * inv))
+            inv = scaled
+        elif kind == "linear":
+            inv = inv / scaling["factor"]
+        elif kind in ("yarn", "deepseek_yarn"):
+            factor = scaling["factor"]
+            old = scaling["original_max_position_embeddings"]
+            beta_fast, beta_slow = scaling.get("beta_fast", 32), scaling.get("beta_slow", 1)
+
+            def corr(n_rot: float) -> float:
+                return rot_dim * math.log(old / (n_rot * 2 * math.pi)) / (2 * math.log(theta))
+            low = max(math.floor(corr(beta_fast)), 0)
+            high = min(math.ceil(corr(beta_slow)), rot_dim // 2 - 1)
+            ramp = ((torch.arange(rot_dim // 2, dtype=torch.float32) - low) / max(high - low, 1e-3)).clamp(0, 1)
+            mask = 1.0 - ramp
+            inv = inv / factor * (1 - mask) + inv * mask
+            ms = scaling.get("mscale", 1.0)
+            ms_all = scaling.get("mscale_all_dim", 0.0)
+
+            def get_mscale(scale: float, m: float) -> float:
+                return 1.0 if scale <= 1 else 0.1 * m * math.log(scale) + 1.0
+            if kind == "deepseek_yarn":
+                mscale = get_mscale(factor, ms) / get_mscale(factor, ms_all) * scaling.get("attn_factor", 1.0)
+            else:
+                mscale = get_mscale(factor, 1.0) * scaling.get("attn_factor", 1.0)
+    t = torch.arange(max_pos, dtype=torch.float32)
+    freqs = torch.outer(t, inv)
+    cache = torch.cat([freqs.cos() * mscale, freqs.sin() * mscale], dim=-1)
+    return cache.to(device) if device is not None else cache
+
+
+def _rotate(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, neox: bool) -> torch.Tensor:
+    # x: [T, H, rot]; cos/sin: [T, 1, rot/2]
+    if neox:
+        x1, x2 = x[..., : x.shape[-1] // 2], x[..., x.shape[-1] // 2:]
+        return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
+    x1, x2 = x[..., 0::2], x[..., 1::2]
+    return torch.stack([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).flatten(-2)
+
+
+def rope(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor,
+         head_dim: int, neox: bool = True) -> tuple[torch.Tensor, torch.Tensor]:
+    """q: [T, Hq*D], k: [T, Hk*D]; rotates the first ``rot_dim`` lanes of each head."""
+    rot = cos_sin.shape[-1]
+    cs = cos_sin[positions.long()]
+    cos, sin = cs[:, None, : rot // 2], cs[:, None, rot // 2:]
+
+    def one(x: torch.Tensor) -> torch.Tensor:
+        t = x.shape[0]
+        xv = x.reshape(t, -1, head_dim).float()
+        xr = _rotate(xv[..., :rot], cos, sin, neox)
+        return torch.cat([xr, xv[..., rot:]], dim=-1).reshape(t, -1).to(x.dtype)
+    return one(q), one(k)
+
+
+def qk_norm_rope(q: torch.Tensor, k: torch.Tensor, q_w: torch.Tensor, k_w: torch.Tensor, eps: float,
+                 positions: torch.Tensor, cos_sin: torch.Tensor, head_dim: int
+                 ) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per-head RMSNorm of q and k followed by NeoX RoPE (Qwen3)."""
+    t = q.shape[0]
+    qn = rms_norm(q.reshape(t, -1, head_dim), q_w, eps).reshape(t, -1)
+    kn = rms_norm(k.reshape(t, -1, head_dim), k_w, eps).reshape(t, -1)
+    return rope(qn, kn, positions, cos_sin, head_dim, True)
+
+
+# ---------------------------------------------------------------- activations
+def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
+    d = x.shape[-1] // 2
+    return (F.silu(x[..., :d].float()) * x[..., d:].float()).to(x.dtype)
+
+
+def gelu_and_mul(x: torch.Tensor, approximate: str = "none") -> torch.Tensor:
+    d = x.shape[-1] // 2
+    return (F.gelu(x[..., :d].float(), approximate=approximate) * x[..., d:].float()).to(x.dtype)
+
+
+# ---------------------------------------------------------------- KV cache
+def reshape_and_cache(k: torch.Tensor, v: torch.Tensor, kv_cache: torch.Tensor,
+                      slot_mapping: torch.Tensor, k_scale: float = 1.0, v_scale: float = 1.0) -> None:
+    """Scatter ``k, v: [T, Hk, D]`` into the paged cache; negative slots are skipped."""
+    bs = kv_cache.shape[3]
+    valid = slot_mapping >= 0
+    slots = slot_mapping[valid].long()
+    blk, off = slots // bs, slots % bs
+    kk, vv = k[valid], v[valid]
+    if kv_cache.dtype == torch.float8_e4m3fn:
+        kk = (kk.float() / k_scale).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+        vv = (vv.float() / v_scale).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+        kv_cache.view(torch.uint8)[blk, 0, :, off] = kk.view(torch.uint8)
+        kv_cache.view(torch.uint8)[blk, 1, :, off] = vv.view(torch.uint8)
+    else:
+        kv_cache[blk, 0, :, off] = kk.to(kv_cache.dtype)
+        kv_cache[blk, 1, :, off] = vv.to(kv_cache.dtype)
+
+
+def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_tables: torch.Tensor,
+                    seq_lens: torch.Tensor, query_start_loc: torch.Tensor, scale: float,
+                    num_seqs: int | None = None, sliding_window: int | None = None,
+                    k_scale: float = 1.0, v_scale: float = 1.0, return_lse: bool = False):
+    """Causal varlen attention over the paged cache.
+
+    q: ``[T, Hq, D]`` with sequence ``i`` owning rows
+    ``query_start_loc[i]:query_start_loc[i+1]``, which are the *last* tokens of
+    a context of ``seq_lens[i]`` tokens already present in the cache.
+    """
+    t, hq, d = q.shape
+    hk, bs = kv_cache.shape[2], kv_cache.shape[3]
+    group = hq // hk
+    out = torch.zeros_like(q)
+    lse = torch.full((t, hq), float("-inf"), dtype=torch.float32, device=q.device)
+    n = num_seqs if num_seqs is not None else seq_lens.shape[0]
+    qsl = query_start_loc.tolist()
+    sl = seq_lens.tolist()
+    for i in range(n):
+        s, e, ctx = qsl[i], qsl[i + 1], sl[i]
+        ql = e - s
+        if ql <= 0:
+            continue
+        nb = -(-ctx // bs)
+        blocks = block_tables[i, :nb].long()
+        kv = kv_cache[blocks]                                   # [nb, 2, hk, bs, d]
+        if kv.dtype == torch.float8_e4m3fn:
+            kf = kv[:, 0].float() * k_scale
+            vf = kv[:, 1].float() * v_scale
+        else:
+            kf, vf = kv[:, 0].float(), kv[:, 1].float()
+        kf = kf.permute(1, 0, 2, 3).reshape(hk, nb * bs, d)[:, :ctx]
+        vf = vf.permute(1, 0, 2, 3).reshape(hk, nb * bs, d)[:, :ctx]
+        qi = q[s:e].float().permute(1, 0, 2).reshape(hk, group, ql, d)
+        scores = torch.einsum("hgqd,hkd->hgqk", qi, kf) * scale
+        qpos = torch.arange(ctx - ql, ctx, device=q.device)[:, None]
+        kpos = torch.arange(ctx, device=q.device)[None, :]
+        mask = kpos <= qpos
+        if sliding_window:
+            mask &= kpos > qpos - sliding_window
+        scores = scores.masked_fill(~mask, float("-inf"))
+        l = torch.logsumexp(scores, dim=-1)
+        p = torch.exp(scores - l[..., None])
+        o = torch.einsum("hgqk,hkd->hgqd", p, vf)
+        out[s:e] = o.reshape(hq, ql, d).permute(1, 0, 2).to(q.dtype)
+        lse[s:e] = l.reshape(hq, ql).permute(1, 0)
+    return (out, lse) if return_lse else out
+
+
+def merge_attn_states(o1: torch.Tensor, lse1: torch.Tensor, o2: torch.Tensor, lse2: torch.Tensor
+                      ) -> tuple[torch.Tensor, torch.Tensor]:
+    """Combine two partial attention results over disjoint key sets."""
+    m = torch.maximum(lse1, lse2)
+    m = torch.where(torch.isinf(m), torch.zeros_like(m), m)
+    w1, w2 = torch.exp(lse1 - m), torch.exp(lse2 - m)
+    den = (w1 + w2).clamp_min(1e-30)
+    o = (o1.float() * (w1 / den)[..., None] + o2.float() * (w2 / den)[..., None]).to(o1.dtype)
+    return o, m + torch.log(den)
+
+
+# ---------------------------------------------------------------- MLA
+def mla_cache_write(kv_c: torch.Tensor, k_pe: torch.Tensor, cache: torch.Tensor,
+                    slot_mapping: torch.Tensor) -> None:
+    """cache: [blocks, block_size, R + P]; kv_c: [T, R]; k_pe: [T, P]."""
+    bs = cache.shape[1]
+    valid = slot_mapping >= 0
+    slots = slot_mapping[valid].long()
+    row = torch.cat([kv_c[valid], k_pe[valid]], dim=-1).to(cache.dtype)
+    cache[slots // bs, slots % bs] = row
+
+
+def mla_paged_attention(q_nope: torch.Tensor, q_pe: torch.Tensor, cache: torch.Tensor,
+                        block_tables: torch.Tensor, seq_lens: torch.Tensor,
+                        query_start_loc: torch.Tensor, scale: float, kv_lora_rank: int,
+                        topk_indices: torch.Tensor | None = None) -> torch.Tensor:
+    """Absorbed-form MLA attention (MQA over the latent cache).
+
+    q_nope: ``[T, H, R]`` (already multiplied by W_UK), q_pe: ``[T, H, P]``;
+    returns ``[T, H, R]`` (to be multiplied by W_UV).  ``topk_indices``
+    (``[T, K]``, -1 padded, positions inside the sequence) restricts each query
+    to the listed keys — DeepSeek sparse attention.
+    """
+    t, h, r = q_nope.shape
+    bs = cache.shape[1]
+    out = torch.zeros(t, h, r, dtype=q_nope.dtype, device=q_nope.device)
+    qsl, sl = query_start_loc.tolist(), seq_lens.tolist()
+    for i in range(seq_lens.shape[0]):
+        s, e, ctx = qsl[i], qsl[i + 1], sl[i]
+        ql = e - s
+        if ql <= 0:
+            continue
+        nb = -(-ctx // bs)
+        rows = cache[block_tables[i, :nb].long()].reshape(nb * bs, -1)[:ctx].float()
+        kc, kp = rows[:, :kv_lora_rank], rows[:, kv_lora_rank:]
+        scores = (torch.einsum("qhr,kr->hqk", q_nope[s:e].float(), kc)
+                  + torch.einsum("qhp,kp->hqk", q_pe[s:e].float(), kp)) * scale
+        qpos = torch.arange(ctx - ql, ctx, device=cache.device)[:, None]
+        kpos = torch.arange(ctx, device=cache.device)[None, :]
+        mask = kpos <= qpos
+        if topk_indices is not None:
+            sel = torch.zeros(ql, ctx + 1, dtype=torch.bool, device=cache.device)
+            idx = topk_indices[s:e].long()
+            idx = torch.where(idx < 0, torch.full_like(idx, ctx), idx).clamp_max(ctx)
+            sel.scatter_(1, idx, True)
+            mask &= sel[:, :ctx]
+        scores = scores.masked_fill(~mask[None], float("-inf"))
+        p = torch.softmax(scores, dim=-1)
+        out[s:e] = torch.einsum("hqk,kr->qhr", p, kc).to(out.dtype)
+    return out
+
+
+# ---------------------------------------------------------------- GEMM / quant
+def gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """y = x @ w.T (+ bias); ``w`` is ``[N, K]`` as stored in checkpoints."""
+    return F.linear(x, w, bias)
+
+
+def per_token_group_quant_fp8(x: torch.Tensor, group: int = 128, ue8m0: bool = False
+                              ) -> tuple[torch.Tensor, torch.Tensor]:
+    """x: [T, K] → (fp8 [T, K], scales fp32 [T, K/group])."""
+    t, k = x.shape
+    xg = x.float().reshape(t, k // group, group)
+    amax = xg.abs().amax(dim=-1).clamp_min(1e-10)
+    scale = amax / FP8_MAX
+    if ue8m0:
+        scale = torch.exp2(torch.ceil(torch.log2(scale)))
+    q = (xg / scale[..., None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return q.reshape(t, k), scale
+
+
+def block_quant_fp8_weight(w: torch.Tensor, block: int = 128) -> tuple[torch.Tensor, torch.Tensor]:
+    """w: [N, K] → (fp8 [N, K], scales fp32 [ceil(N/b), ceil(K/b)])."""
+    n, k = w.shape
+    nb, kb = -(-n // block), -(-k // block)
+    wp = torch.zeros(nb * block, kb * block, dtype=torch.float32, device=w.device)
+    wp[:n, :k] = w.float()
+    wv = wp.reshape(nb, block, kb, block)
+    amax = wv.abs().amax(dim=(1, 3)).clamp_min(1e-10)
+    scale = amax / FP8_MAX
+    q = (wv / scale[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).reshape(nb * block, kb * block)[:n, :k]
+    return q.to(torch.float8_e4m3fn).contiguous(), scale
+
+
+def gemm_fp8_block(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor,
+                   out_dtype: torch.dtype = torch.bfloat16, block: int = 128) -> torch.Tensor:
+    """Block-scaled fp8 GEMM: per-token 1×128 activation scales, 128×128 weight scales."""
+    t, k = xq.shape
+    n = wq.shape[0]
+    x = xq.float().reshape(t, k // block, block) * xs[..., None]
+    wsx = ws.repeat_interleave(block, 0)[:n].repeat_interleave(block, 1)[:, :k]
+    w = wq.float() * wsx
+    return (x.reshape(t, k) @ w.t()).to(out_dtype)
+
+
+def scaled_fp8_quant(x: torch.Tensor, scale: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per-tensor fp8 quantisation; dynamic when ``scale`` is None."""
+    if scale is None:
+        scale = (x.float().abs().max().clamp_min(1e-10) / FP8_MAX).reshape(1)
+    q = (x.float() / scale).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return q, scale
+
+
+# ---------------------------------------------------------------- MoE
+def topk_softmax(logits: torch.Tensor, k: int, renormalize: bool) -> tuple[torch.Tensor, torch.Tensor]:
+    probs = torch.softmax(logits.float(), dim=-1)
+    w, ids = probs.topk(k, dim=-1)
+    if renormalize:
+        w = w / w.sum(dim=-1, keepdim=True)
+    return w, ids.int()
+
+
+def grouped_topk(logits: torch.Tensor, bias: torch.Tensor | None, k: int, n_group: int, topk_group: int,
+                 renormalize: bool, scale: float, scoring: str = "sigmoid"
+                 ) -> tuple[torch.Tensor, torch.Tensor]:
+    """DeepSeek routing: score → (+bias for selection) → best groups by top-2 sum →
+    top-k experts inside them; weights come from the unbiased scores."""
+    s = torch.sigmoid(logits.float()) if scoring == "sigmoid" else torch.softmax(logits.float(), -1)
+    sel = s + bias.float() if bias is not None else s
+    t, e = s.shape
+    g = sel.reshape(t, n_group, e // n_group)
+    gscore = g.topk(2, dim=-1).values.sum(-1) if bias is not None else g.max(-1).values
+    gidx = gscore.topk(topk_group, dim=-1).indices
+    gmask = torch.zeros(t, n_group, dtype=torch.bool, device=s.device).scatter_(1, gidx, True)
+    masked = sel.masked_fill(~gmask[:, :, None].expand_as(g).reshape(t, e), float("-inf"))
+    ids = masked.topk(k, dim=-1).indices
+    w = s.gather(1, ids)
+    if renormalize:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return w * scale, ids.int()
+
+
+def fused_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: torch.Tensor,
+                  topk_ids: torch.Tensor, expert_map: torch.Tensor | None = None) -> torch.Tensor:
+    """Reference MoE FFN.  w13: [E, 2I, H] (gate rows then up rows), w2: [E, H, I].
+    ``expert_map[global id] = local id or -1`` restricts to locally held experts."""
+    t, h = x.shape
+    out = torch.zeros(t, h, dtype=torch.float32, device=x.device)
+    ids = topk_ids.long()
+    if expert_map is not None:
+        ids = expert_map[ids].long()
+    for e in range(w13.shape[0]):
+        tok, slot = (ids == e).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        a = silu_and_mul(F.linear(x[tok], w13[e]))
+        y = F.linear(a, w2[e]).float()
+        out.index_add_(0, tok, y * topk_w[tok, slot, None].float())
+    return out.to(x.dtype)
+
+
+# ---------------------------------------------------------------- sampling
+def apply_penalties(logits: torch.Tensor, prompt_mask: torch.Tensor, output_counts: torch.Tensor,
+                    presence: torch.Tensor, frequency: torch.Tensor, repetition: torch.Tensor) -> torch.Tensor:
+    """logits [B, V] fp32; prompt_mask [B, V] bool; output_counts [B, V] int."""
+    seen = prompt_mask | (output_counts > 0)
+    rep = repetition[:, None]
+    logits = torch.where(seen, torch.where(logits > 0, logits / rep, logits * rep), logits)
+    logits = logits - frequency[:, None] * output_counts.float()
+    logits = logits - presence[:, None] * (output_counts > 0).float()
+    return logits
+
+
+def top_k_top_p_min_p(logits: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+                      min_p: torch.Tensor) -> torch.Tensor:
+    """Mask logits outside the nucleus.  top_k: int [B] (0 = off), top_p/min_p: float [B]."""
+    b, v = logits.shape
+    srt, idx = logits.sort(dim=-1, descending=True)
+    k = torch.where(top_k <= 0, torch.full_like(top_k, v), top_k).clamp_max(v).long()
+    rank = torch.arange(v, device=logits.device)[None, :]
+    srt = srt.masked_fill(rank >= k[:, None], float("-inf"))
+    probs = torch.softmax(srt, dim=-1)
+    cum = probs.cumsum(dim=-1)
+    # keep a token while the mass before it is below top_p (the first always stays)
+    srt = srt.masked_fill((cum - probs) >= top_p[:, None], float("-inf"))
+    srt = srt.masked_fill(probs < min_p[:, None] * probs[:, :1], float("-inf"))
+    return torch.full_like(logits, float("-inf")).scatter_(1, idx, srt)
+
+
+def sample_from_logits(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
+                       top_p: torch.Tensor, min_p: torch.Tensor, noise: torch.Tensor | None = None,
+                       generators: dict[int, torch.Generator] | None = None) -> torch.Tensor:
+    """Greedy rows (temperature 0) take the arg-max; the others sample with the
+    exponential-race trick: argmax(p / e), e ~ Exp(1) (``noise`` supplies e)."""
+    greedy = temperature < 1e-5
+    temp = torch.where(greedy, torch.ones_like(temperature), temperature)
+    scaled = logits.float() / temp[:, None]
+    masked = top_k_top_p_min_p(scaled, top_k, top_p, min_p)
+    probs = torch.softmax(masked, dim=-1)
+    if noise is None:
+        noise = torch.empty_like(probs).exponential_()
+        if generators:
+            for row, gen in generators.items():
+                noise[row].exponential_(generator=gen)
+    sampled = (probs / noise).argmax(dim=-1)
+    return torch.where(greedy, logits.argmax(dim=-1), sampled)

@@ -1,0 +1,276 @@
+"""Process-group layout: one process per GPU, ranks laid out DP × PP × PCP × TP.
+
+``initialize_model_parallel`` reshapes ``arange(world)`` to
+``[dp, pp, pcp, tp]`` and builds, per axis, one ``GroupCoordinator`` holding a
+device group (NCCL on GPUs, gloo on CPU) and a gloo CPU group for host-side
+objects.  The expert-parallel group spans DP × PCP × TP of one pipeline stage;
+decode-context-parallel groups are contiguous sub-groups of a TP group.
+
+Parity: ``aphrodite/distributed/parallel_state.py:1475`` (init),
+``:1619-1818`` (layout and groups), ``:367`` (``GroupCoordinator``),
+``:1288-1344`` (accessors).
+"""
+from __future__ import annotations
+
+import datetime
+import os
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from sonar_b200.logger import init_logger
+
+logger = init_logger(__name__)
+
+
+class GroupCoordinator:
+    """Ranks along one parallel axis plus the collectives the engine needs."""
+
+    def __init__(self, group_ranks: list[list[int]], backend: str, name: str, timeout_s: float = 600.0) -> None:
+        self.name = name
+        self.rank = dist.get_rank()
+        self.ranks: list[int] = []
+        self.device_group = None
+        self.cpu_group = None
+        timeout = datetime.timedelta(seconds=timeout_s)
+        for ranks in group_ranks:
+            dg = dist.new_group(ranks, backend=backend, timeout=timeout)
+            cg = dg if backend == "gloo" else dist.new_group(ranks, backend="gloo", timeout=timeout)
+            if self.rank in ranks:
+                self.ranks, self.device_group, self.cpu_group = list(ranks), dg, cg
+        assert self.device_group is not None, f"rank {self.rank} is in no {name} group"
+        self.world_size = len(self.ranks)
+        self.rank_in_group = self.ranks.index(self.rank)
+
+    # identity -----------------------------------------------------------
+    @property
+    def first_rank(self) -> int:
+        return self.ranks[0]
+
+    @property
+    def last_rank(self) -> int:
+        return self.ranks[-1]
+
+    @property
+    def is_first_rank(self) -> bool:
+        return self.rank == self.first_rank
+
+    @property
+    def is_last_rank(self) -> bool:
+        return self.rank == self.last_rank
+
+    @property
+    def next_rank(self) -> int:
+        return self.ranks[(self.rank_in_group + 1) % self.world_size]
+
+    @property
+    def prev_rank(self) -> int:
+        return self.ranks[(self.rank_in_group - 1) % self.world_size]
+
+    # device collectives (the NCCL baseline; fused kernels bypass these) ----
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self.world_size > 1:
+            dist.all_reduce(x, group=self.device_group)
+        return x
+
+    def all_gather(self, x: torch.Tensor, dim: int = 0) -> torch.Tensor:
+        if self.world_size == 1:
+            return x
+        x = x.contiguous()
+        out = torch.empty((self.world_size,) + tuple(x.shape), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x, group=self.device_group)
+        if dim == 0:
+            return out.reshape((-1,) + tuple(x.shape[1:]))
+        dim = dim % x.dim()
+        return out.movedim(0, dim).reshape(x.shape[:dim] + (self.world_size * x.shape[dim],) + x.shape[dim + 1:])
+
+    def reduce_scatter(self, x: torch.Tensor) -> torch.Tensor:
+        """Sum over ranks, rank r keeps rows ``[r*n/ws, (r+1)*n/ws)`` of dim 0."""
+        if self.world_size == 1:
+            return x
+        x = x.contiguous()
+        assert x.shape[0] % self.world_size == 0
+        out = torch.empty((x.shape[0] // self.world_size,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        if self.device_group is self.cpu_group:  # gloo has no reduce_scatter_tensor
+            dist.all_reduce(x, group=self.device_group)
+            n = out.shape[0]
+            out.copy_(x[self.rank_in_group * n:(self.rank_in_group + 1) * n])
+        else:
+            dist.reduce_scatter_tensor(out, x, group=self.device_group)
+        return out
+
+    def all_gatherv(self, x: torch.Tensor, sizes: list[int]) -> torch.Tensor:
+        """Variable-row all-gather along dim 0 (``sizes[r]`` rows from rank r)."""
+        if self.world_size == 1:
+            return x
+        outs = [torch.empty((n,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device) for n in sizes]
+        dist.all_gather(outs, x.contiguous(), group=self.device_group)
+        return torch.cat(outs, dim=0)
+
+    def reduce_scatterv(self, x: torch.Tensor, sizes: list[int]) -> torch.Tensor:
+        if self.world_size == 1:
+            return x
+        dist.all_reduce(x, group=self.device_group)
+        start = sum(sizes[:self.rank_in_group])
+        return x[start:start + sizes[self.rank_in_group]].contiguous()
+
+    def broadcast(self, x: torch.Tensor, src: int = 0) -> torch.Tensor:
+        if self.world_size > 1:
+            dist.broadcast(x, src=self.ranks[src], group=self.device_group)
+        return x
+
+    def send(self, x: torch.Tensor, dst: int | None = None):
+        return dist.isend(x, self.next_rank if dst is None else self.ranks[dst], group=self.device_group)
+
+    def recv(self, shape, dtype, device, src: int | None = None) -> torch.Tensor:
+        out = torch.empty(shape, dtype=dtype, device=device)
+        dist.recv(out, self.prev_rank if src is None else self.ranks[src], group=self.device_group)
+        return out
+
+    # host-side objects -----------------------------------------------------
+    def broadcast_object(self, obj: Any = None, src: int = 0) -> Any:
+        if self.world_size == 1:
+            return obj
+        box = [obj]
+        dist.broadcast_object_list(box, src=self.ranks[src], group=self.cpu_group)
+        return box[0]
+
+    def all_gather_object(self, obj: Any) -> list[Any]:
+        if self.world_size == 1:
+            return [obj]
+        out: list[Any] = [None] * self.world_size
+        dist.all_gather_object(out, obj, group=self.cpu_group)
+        return out
+
+    def barrier(self) -> None:
+        if self.world_size > 1:
+            dist.barrier(group=self.cpu_group)
+
+
+class _State:
+    world: GroupCoordinator | None = None
+    tp: GroupCoordinator | None = None
+    pp: GroupCoordinator | None = None
+    dp: GroupCoordinator | None = None
+    ep: GroupCoordinator | None = None
+    dcp: GroupCoordinator | None = None
+    pcp: GroupCoordinator | None = None
+    backend: str = "gloo"
+
+
+_S = _State()
+
+
+def init_distributed_environment(world_size: int = -1, rank: int = -1, local_rank: int = -1,
+                                 init_method: str | None = None, backend: str | None = None,
+                                 timeout_s: float = 600.0) -> None:
+    """Join the job.  With no arguments the torchrun environment is used."""
+    if dist.is_initialized():
+        return
+    if rank < 0:
+        rank = int(os.environ.get("RANK", 0))
+    if world_size < 0:
+        world_size = int(os.environ.get("WORLD_SIZE", 1))
+    if local_rank < 0:
+        local_rank = int(os.environ.get("LOCAL_RANK", rank))
+    cuda = torch.cuda.is_available()
+    if backend is None:
+        backend = "nccl" if cuda else "gloo"
+    if cuda:
+        torch.cuda.set_device(local_rank)
+    if init_method is None:
+        addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
+        port = os.environ.get("MASTER_PORT", "29511")
+        init_method = f"tcp://{addr}:{port}"
+    kwargs: dict[str, Any] = {}
+    if backend == "nccl":
+        kwargs["device_id"] = torch.device("cuda", local_rank)
+    dist.init_process_group(backend=backend, init_method=init_method, world_size=world_size, rank=rank,
+                            timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
+    _S.backend = backend
+
+
+def initialize_model_parallel(tp: int = 1, pp: int = 1, dp: int = 1, pcp: int = 1, dcp: int = 1,
+                              timeout_s: float = 600.0) -> None:
+    if not dist.is_initialized():
+        init_distributed_environment(1, 0, 0)
+    world = dist.get_world_size()
+    if world != tp * pp * dp * pcp:
+        raise ValueError(f"world size {world} != dp {dp} × pp {pp} × pcp {pcp} × tp {tp}")
+    backend = dist.get_backend()
+    _S.backend = backend
+    layout = torch.arange(world).reshape(dp, pp, pcp, tp)
+
+    def groups_along(axes_last: int) -> list[list[int]]:
+        moved = layout.movedim(axes_last, -1)
+        return moved.reshape(-1, moved.shape[-1]).tolist()
+
+    _S.world = GroupCoordinator([list(range(world))], backend, "world", timeout_s)
+    _S.tp = GroupCoordinator(groups_along(3), backend, "tp", timeout_s)
+    _S.pcp = GroupCoordinator(groups_along(2), backend, "pcp", timeout_s)
+    _S.pp = GroupCoordinator(groups_along(1), backend, "pp", timeout_s)
+    _S.dp = GroupCoordinator(groups_along(0), backend, "dp", timeout_s)
+    ep_groups = layout.permute(1, 0, 2, 3).reshape(pp, dp * pcp * tp).tolist()
+    _S.ep = GroupCoordinator(ep_groups, backend, "ep", timeout_s)
+    tp_groups = groups_along(3)
+    dcp_groups = [g[i:i + dcp] for g in tp_groups for i in range(0, tp, dcp)]
+    _S.dcp = GroupCoordinator(dcp_groups, backend, "dcp", timeout_s)
+    logger.debug("rank %d: tp=%s pp=%s dp=%s ep=%s", dist.get_rank(), _S.tp.ranks, _S.pp.ranks,
+                 _S.dp.ranks, _S.ep.ranks)
+
+
+def model_parallel_is_initialized() -> bool:
+    return _S.tp is not None
+
+
+def _need(g: GroupCoordinator | None, name: str) -> GroupCoordinator:
+    assert g is not None, f"{name} group is not initialised"
+    return g
+
+
+def get_world_group() -> GroupCoordinator:
+    return _need(_S.world, "world")
+
+
+def get_tp_group() -> GroupCoordinator:
+    return _need(_S.tp, "tensor-parallel")
+
+
+def get_pp_group() -> GroupCoordinator:
+    return _need(_S.pp, "pipeline-parallel")
+
+
+def get_dp_group() -> GroupCoordinator:
+    return _need(_S.dp, "data-parallel")
+
+
+def get_ep_group() -> GroupCoordinator:
+    return _need(_S.ep, "expert-parallel")
+
+
+def get_dcp_group() -> GroupCoordinator:
+    return _need(_S.dcp, "decode-context-parallel")
+
+
+def get_pcp_group() -> GroupCoordinator:
+    return _need(_S.pcp, "prefill-context-parallel")
+
+
+def tp_world_size() -> int:
+    return _S.tp.world_size if _S.tp is not None else 1
+
+
+def tp_rank() -> int:
+    return _S.tp.rank_in_group if _S.tp is not None else 0
+
+
+def destroy_model_parallel() -> None:
+    for name in ("world", "tp", "pp", "dp", "ep", "dcp", "pcp"):
+        setattr(_S, name, None)
+
+
+def destroy_distributed_environment() -> None:
+    destroy_model_parallel()
+    if dist.is_initialized():
+        dist.destroy_process_group()

@@ -1,0 +1,83 @@
+"""Tensor-parallel linear pipeline.
+
+A decoder half-block is ``norm → column-parallel GEMM → … → row-parallel
+GEMM``.  The three calls below are the only places a model touches the TP
+group, so the communication strategy is chosen once:
+
+``single``     tp = 1: plain kernels.
+``allreduce``  the classic layout (activations replicated, row-parallel output
+               all-reduced) — NCCL baseline, also what the CPU/gloo tests run.
+``fused``      sequence-parallel layout with the collectives inside the
+               kernels (``sonar_b200.parallel.fused_tp``): the row-parallel
+               GEMM's epilogue pushes each partial tile to the rank that owns
+               those token rows (reduce-scatter), the owner's add+norm kernel
+               sums the partials and pushes the normalised rows to every peer
+               (all-gather), and the next column-parallel GEMM waits per row
+               block on arrival flags.  Activations between blocks stay
+               scattered ``[T/tp, H]``.
+
+Parity: the op pairs are the ones the reference's sequence-parallel and
+async-TP passes rewrite (``compilation/passes/fusion/sequence_parallelism.py:153-250``,
+``collective_fusion.py:327-388``); its default is the all-reduce layout
+(``layers/linear.py:1642-1643``).
+"""
+from __future__ import annotations
+
+import torch
+
+from sonar_b200 import ops
+from sonar_b200.parallel import state
+
+
+class TPContext:
+    """``single`` / ``allreduce`` strategies; ``FusedTPContext`` subclasses this."""
+
+    scattered = False  # True when activations between blocks are [T/tp, H]
+
+    def __init__(self) -> None:
+        self.group = state.get_tp_group() if state.model_parallel_is_initialized() else None
+        self.world_size = self.group.world_size if self.group else 1
+        self.rank = self.group.rank_in_group if self.group else 0
+
+    # token rows this rank holds between blocks
+    def local_tokens(self, num_tokens: int) -> int:
+        return num_tokens
+
+    def begin_step(self, num_tokens: int) -> None:
+        pass
+
+    def embed_reduce(self, partial: torch.Tensor) -> torch.Tensor:
+        """Vocab-parallel embedding partials → block input layout."""
+        return self.group.all_reduce(partial) if self.world_size > 1 else partial
+
+    def add_norm(self, h: torch.Tensor, residual: torch.Tensor | None, weight: torch.Tensor, eps: float
+                 ) -> tuple[torch.Tensor, torch.Tensor]:
+        if residual is None:
+            return ops.rms_norm(h, weight, eps), h
+        return ops.fused_add_rms_norm(h, residual, weight, eps)
+
+    def col_linear(self, x: torch.Tensor, layer) -> torch.Tensor:
+        return layer.apply(x)
+
+    def row_linear(self, x: torch.Tensor, layer) -> torch.Tensor:
+        y = layer.apply(x)
+        return self.group.all_reduce(y) if self.world_size > 1 else y
+
+    def gather_tokens(self, h: torch.Tensor, num_tokens: int) -> torch.Tensor:
+        """Block layout → replicated ``[T, H]`` (before the LM head)."""
+        return h
+
+
+_ctx: TPContext | None = None
+
+
+def get_tp_context() -> TPContext:
+    global _ctx
+    if _ctx is None:
+        _ctx = TPContext()
+    return _ctx
+
+
+def set_tp_context(ctx: TPContext | None) -> None:
+    global _ctx
+    _ctx = ctx

@@ -1,0 +1,188 @@
+"""Engine-side request record and the wire structs between frontend and core.
+
+``EngineCoreRequest`` / ``EngineCoreOutput(s)`` are what crosses the
+frontend ⇄ core boundary (in-process or over ZMQ+msgpack); ``Request`` is the
+scheduler's mutable view.  Parity: ``aphrodite/v1/engine/__init__.py:97-257``
+and ``aphrodite/v1/request.py``.
+"""
+from __future__ import annotations
+
+import enum
+import time
+from dataclasses import dataclass, field
+from typing import Any
+
+from sonar_b200.sampling_params import PoolingParams, SamplingParams
+
+
+class FinishReason(enum.IntEnum):
+    STOP = 0
+    LENGTH = 1
+    ABORT = 2
+    ERROR = 3
+
+    def __str__(self) -> str:
+        return ("stop", "length", "abort", "error")[self.value]
+
+
+class RequestStatus(enum.IntEnum):
+    WAITING = 0
+    WAITING_FOR_REMOTE_KVS = 1
+    RUNNING = 2
+    PREEMPTED = 3
+    # anything after PREEMPTED is finished
+    FINISHED_STOPPED = 4
+    FINISHED_LENGTH_CAPPED = 5
+    FINISHED_ABORTED = 6
+    FINISHED_ERROR = 7
+
+    @staticmethod
+    def is_finished(status: "RequestStatus") -> bool:
+        return status > RequestStatus.PREEMPTED
+
+    @staticmethod
+    def finish_reason(status: "RequestStatus") -> FinishReason | None:
+        return _FINISH_MAP.get(status)
+
+
+_FINISH_MAP = {
+    RequestStatus.FINISHED_STOPPED: FinishReason.STOP,
+    RequestStatus.FINISHED_LENGTH_CAPPED: FinishReason.LENGTH,
+    RequestStatus.FINISHED_ABORTED: FinishReason.ABORT,
+    RequestStatus.FINISHED_ERROR: FinishReason.ERROR,
+}
+
+
+@dataclass
+class EngineCoreRequest:
+    request_id: str
+    prompt_token_ids: list[int]
+    sampling_params: SamplingParams | None
+    pooling_params: PoolingParams | None = None
+    eos_token_id: int | None = None
+    arrival_time: float = 0.0
+    priority: int = 0
+    cache_salt: str | None = None
+    lora_name: str | None = None
+    data_parallel_rank: int | None = None
+    client_index: int = 0
+
+
+@dataclass
+class EngineCoreOutput:
+    request_id: str
+    new_token_ids: list[int]
+    new_logprobs: list[dict[int, float]] | None = None
+    prompt_logprobs: list[dict[int, float] | None] | None = None
+    finish_reason: FinishReason | None = None
+    stop_reason: int | str | None = None
+    num_cached_tokens: int = 0
+    pooled: Any = None
+
+    @property
+    def finished(self) -> bool:
+        return self.finish_reason is not None
+
+
+@dataclass
+class SchedulerStats:
+    num_running: int = 0
+    num_waiting: int = 0
+    kv_cache_usage: float = 0.0
+    prefix_cache_queries: int = 0
+    prefix_cache_hits: int = 0
+    num_preempted: int = 0
+    step_prompt_tokens: int = 0
+    step_generation_tokens: int = 0
+    spec_num_drafts: int = 0
+    spec_num_accepted: int = 0
+
+
+@dataclass
+class EngineCoreOutputs:
+    outputs: list[EngineCoreOutput] = field(default_factory=list)
+    scheduler_stats: SchedulerStats | None = None
+    timestamp: float = 0.0
+    engine_index: int = 0
+    finished_requests: set[str] | None = None
+    utility_output: Any = None
+
+
+class Request:
+    """Scheduler-owned mutable state of one sequence."""
+
+    __slots__ = (
+        "request_id", "prompt_token_ids", "sampling_params", "pooling_params", "eos_token_id",
+        "arrival_time", "priority", "cache_salt", "lora_name", "client_index", "status", "stop_reason",
+        "output_token_ids", "all_token_ids", "num_prompt_tokens", "num_computed_tokens",
+        "num_cached_tokens", "spec_token_ids", "max_tokens", "block_hashes", "num_preemptions",
+        "events", "num_output_placeholders", "_hasher")
+
+    def __init__(self, core_req: EngineCoreRequest, block_hasher=None) -> None:
+        self.request_id = core_req.request_id
+        self.prompt_token_ids = list(core_req.prompt_token_ids)
+        self.sampling_params = core_req.sampling_params
+        self.pooling_params = core_req.pooling_params
+        self.eos_token_id = core_req.eos_token_id
+        self.arrival_time = core_req.arrival_time or time.time()
+        self.priority = core_req.priority
+        self.cache_salt = core_req.cache_salt
+        self.lora_name = core_req.lora_name
+        self.client_index = core_req.client_index
+        self.status = RequestStatus.WAITING
+        self.stop_reason: int | str | None = None
+        self.output_token_ids: list[int] = []
+        self.all_token_ids: list[int] = list(self.prompt_token_ids)
+        self.num_prompt_tokens = len(self.prompt_token_ids)
+        self.num_computed_tokens = 0
+        self.num_cached_tokens = -1
+        self.spec_token_ids: list[int] = []
+        if self.sampling_params is not None:
+            assert self.sampling_params.max_tokens is not None
+            self.max_tokens = self.sampling_params.max_tokens
+        else:
+            self.max_tokens = 1
+        self.block_hashes: list[bytes] = []
+        self.num_preemptions = 0
+        self.events: list[tuple[str, float]] = []
+        self.num_output_placeholders = 0
+        self._hasher = block_hasher
+        if block_hasher is not None:
+            self.block_hashes.extend(block_hasher(self))
+
+    # ------------------------------------------------------------------
+    @property
+    def num_tokens(self) -> int:
+        return len(self.all_token_ids)
+
+    @property
+    def num_tokens_with_spec(self) -> int:
+        return len(self.all_token_ids) + len(self.spec_token_ids)
+
+    @property
+    def num_output_tokens(self) -> int:
+        return len(self.output_token_ids)
+
+    @property
+    def is_finished(self) -> bool:
+        return RequestStatus.is_finished(self.status)
+
+    def append_output_token_ids(self, token_ids: int | list[int]) -> None:
+        if isinstance(token_ids, int):
+            self.output_token_ids.append(token_ids)
+            self.all_token_ids.append(token_ids)
+        else:
+            self.output_token_ids.extend(token_ids)
+            self.all_token_ids.extend(token_ids)
+        if self._hasher is not None:
+            self.block_hashes.extend(self._hasher(self))
+
+    def get_finished_reason(self) -> FinishReason | None:
+        return RequestStatus.finish_reason(self.status)
+
+    def record_event(self, name: str) -> None:
+        self.events.append((name, time.monotonic()))
+
+    def __lt__(self, other: "Request") -> bool:
+        return (self.priority, self.arrival_time, self.request_id) < \
+               (other.priority, other.arrival_time, other.request_id)

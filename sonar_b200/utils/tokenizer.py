@@ -1,0 +1,83 @@
+"""Tokenizer access.
+
+Checkpoints with tokenizer files load through ``transformers``; architecture
+presets (random weights, no files) get ``ByteTokenizer`` — UTF-8 bytes shifted
+past a few special ids — so that text-in/text-out paths, the server and the
+tests work without any download.  Parity: ``aphrodite/tokenizers/``.
+"""
+from __future__ import annotations
+
+from typing import Any
+
+
+class ByteTokenizer:
+    """ids 0..3 = pad/bos/eos/unk, 4..259 = bytes; larger ids decode to nothing."""
+    pad_token_id, bos_token_id, eos_token_id, unk_token_id = 0, 1, 2, 3
+    _OFFSET = 4
+    is_fast = False
+
+    def __init__(self, vocab_size: int = 260) -> None:
+        self.vocab_size = max(vocab_size, 260)
+        self.all_special_ids = [0, 1, 2, 3]
+        self.chat_template = None
+
+    def __len__(self) -> int:
+        return self.vocab_size
+
+    def encode(self, text: str, add_special_tokens: bool = True, **_: Any) -> list[int]:
+        ids = [b + self._OFFSET for b in text.encode("utf-8")]
+        return ([self.bos_token_id] + ids) if add_special_tokens else ids
+
+    def __call__(self, text: str, add_special_tokens: bool = True, **_: Any) -> dict:
+        return {"input_ids": self.encode(text, add_special_tokens)}
+
+    def decode(self, ids, skip_special_tokens: bool = True, **_: Any) -> str:
+        if isinstance(ids, int):
+            ids = [ids]
+        out = bytearray()
+        for i in ids:
+            if self._OFFSET <= i < self._OFFSET + 256:
+                out.append(i - self._OFFSET)
+            elif i < self._OFFSET and not skip_special_tokens:
+                out.extend(("<pad>", "<s>", "</s>", "<unk>")[i].encode())
+        return out.decode("utf-8", errors="replace")
+
+    def convert_ids_to_tokens(self, ids, skip_special_tokens: bool = False):
+        if isinstance(ids, int):
+            return self.decode([ids], skip_special_tokens)
+        return [self.decode([i], skip_special_tokens) for i in ids]
+
+    def apply_chat_template(self, messages, tokenize: bool = False, add_generation_prompt: bool = True,
+                            **_: Any):
+        text = "".join(f"<|{m['role']}|>\n{_content_text(m.get('content'))}\n" for m in messages)
+        if add_generation_prompt:
+            text += "<|assistant|>\n"
+        return self.encode(text) if tokenize else text
+
+
+def _content_text(content) -> str:
+    if content is None:
+        return ""
+    if isinstance(content, str):
+        return content
+    return "".join(p.get("text", "") for p in content if isinstance(p, dict))
+
+
+def get_tokenizer(path: str | None, vocab_size: int = 260):
+    if path is None:
+        return ByteTokenizer(vocab_size)
+    from transformers import AutoTokenizer
+    return AutoTokenizer.from_pretrained(path, local_files_only=True)
+
+
+def apply_chat_template(tokenizer, messages: list[dict], add_generation_prompt: bool = True,
+                        chat_template: str | None = None, tools: list[dict] | None = None) -> str:
+    if isinstance(tokenizer, ByteTokenizer) or (getattr(tokenizer, "chat_template", None) is None
+                                                and chat_template is None):
+        return ByteTokenizer.apply_chat_template(tokenizer, messages, False, add_generation_prompt)
+    kwargs = {"tokenize": False, "add_generation_prompt": add_generation_prompt}
+    if chat_template is not None:
+        kwargs["chat_template"] = chat_template
+    if tools:
+        kwargs["tools"] = tools
+    return tokenizer.apply_chat_template(messages, **kwargs)

@@ -1,0 +1,68 @@
+"""Span tracer writing Chrome trace-event JSON (open in Perfetto / chrome://tracing).
+
+Disabled (zero-cost no-op spans) unless a file is configured with
+``--trace-file`` or ``SONAR_TRACE_FILE``.  Parity: the reference's
+OpenTelemetry hooks in ``aphrodite/tracing/`` and the torch-profiler routes;
+here spans are written locally because the box has no collector.
+"""
+from __future__ import annotations
+
+import contextlib
+import json
+import os
+import threading
+import time
+
+
+class _NullTracer:
+    enabled = False
+
+    @contextlib.contextmanager
+    def span(self, name: str, **args):
+        yield
+
+    def instant(self, name: str, **args) -> None:
+        pass
+
+    def close(self) -> None:
+        pass
+
+
+class Tracer(_NullTracer):
+    enabled = True
+
+    def __init__(self, path: str) -> None:
+        self.path = path
+        self._events: list[dict] = []
+        self._lock = threading.Lock()
+        self._pid = os.getpid()
+
+    @contextlib.contextmanager
+    def span(self, name: str, **args):
+        t0 = time.perf_counter_ns()
+        try:
+            yield
+        finally:
+            t1 = time.perf_counter_ns()
+            ev = {"name": name, "ph": "X", "ts": t0 / 1e3, "dur": (t1 - t0) / 1e3, "pid": self._pid,
+                  "tid": threading.get_ident() % 100000, "args": args}
+            with self._lock:
+                self._events.append(ev)
+
+    def instant(self, name: str, **args) -> None:
+        with self._lock:
+            self._events.append({"name": name, "ph": "i", "ts": time.perf_counter_ns() / 1e3, "s": "p",
+                                 "pid": self._pid, "tid": threading.get_ident() % 100000, "args": args})
+
+    def close(self) -> None:
+        with self._lock:
+            with open(self.path, "w") as f:
+                json.dump({"traceEvents": self._events}, f)
+
+
+_NULL = _NullTracer()
+
+
+def get_tracer(path: str | None = None):
+    path = path or os.environ.get("SONAR_TRACE_FILE")
+    return Tracer(path) if path else _NULL

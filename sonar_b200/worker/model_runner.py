@@ -1,0 +1,443 @@
+"""Model runner: persistent batch state, per-step input build, forward, sample.
+
+The runner mirrors the scheduler's running set in flat host arrays (token ids,
+block tables, positions, sampling controls) so a step only applies deltas.
+Per step it builds, vectorised in numpy on pinned memory, the flattened token
+ids / positions / slot mapping / per-sequence lengths, ships them with one
+asynchronous H2D copy each, runs the model (eagerly or by replaying a CUDA
+graph captured for that padded token count), samples on the device and reads
+the sampled ids back with one D2H copy.
+
+Parity: ``aphrodite/v1/worker/gpu_model_runner.py:432`` (``_update_states`` :1089,
+``_prepare_inputs`` :1822, ``execute_model`` :3863, ``sample_tokens`` :4215,
+``capture_model`` :6249), ``gpu_input_batch.py`` and ``block_table.py``.
+"""
+from __future__ import annotations
+
+import time
+from typing import Any
+
+import numpy as np
+import torch
+
+from sonar_b200.config import EngineConfig
+from sonar_b200.core.kv_cache_manager import KVCacheConfig, KVCacheSpec
+from sonar_b200.core.scheduler import ModelRunnerOutput, SchedulerOutput
+from sonar_b200.layers.attention import AttentionMetadata
+from sonar_b200.loader import load_model
+from sonar_b200.logger import init_logger
+from sonar_b200.parallel import state
+from sonar_b200.parallel.tp_ops import get_tp_context
+from sonar_b200.sample.sampler import Sampler, make_sampling_metadata
+from sonar_b200.sampling_params import SamplingParams
+
+logger = init_logger(__name__)
+
+
+class InputBatch:
+    """Flat host-side mirror of the running requests (row = request)."""
+
+    def __init__(self, max_seqs: int, max_model_len: int, block_size: int, pin: bool) -> None:
+        self.max_seqs = max_seqs
+        self.max_blocks = -(-max_model_len // block_size) + 1
+        self.token_ids = np.zeros((max_seqs, max_model_len + 8), dtype=np.int32)
+        self.num_tokens = np.zeros(max_seqs, dtype=np.int32)         # known tokens (prompt + sampled)
+        self.num_prompt = np.zeros(max_seqs, dtype=np.int32)
+        self.num_computed = np.zeros(max_seqs, dtype=np.int32)
+        self.block_table = torch.zeros((max_seqs, self.max_blocks), dtype=torch.int32, pin_memory=pin)
+        self.block_table_np = self.block_table.numpy()
+        self.num_blocks = np.zeros(max_seqs, dtype=np.int32)
+        self.req_ids: list[str | None] = [None] * max_seqs
+        self.index: dict[str, int] = {}
+        self.params: list[SamplingParams | None] = [None] * max_seqs
+        self.pooling: list[bool] = [False] * max_seqs
+        self.generators: dict[str, torch.Generator] = {}
+        self.mirostat_mu: dict[str, float] = {}
+        self.num_reqs = 0
+
+    def add(self, req_id: str, prompt: list[int], outputs: list[int], params: SamplingParams | None,
+            block_ids: list[int], num_computed: int, pooling: bool, device) -> int:
+        row = self.num_reqs
+        assert row < self.max_seqs
+        self.num_reqs += 1
+        self.req_ids[row] = req_id
+        self.index[req_id] = row
+        n_p, n_o = len(prompt), len(outputs)
+        self.token_ids[row, :n_p] = prompt
+        if n_o:
+            self.token_ids[row, n_p:n_p + n_o] = outputs
+        self.num_tokens[row] = n_p + n_o
+        self.num_prompt[row] = n_p
+        self.num_computed[row] = num_computed
+        nb = len(block_ids)
+        self.block_table_np[row, :nb] = block_ids
+        self.num_blocks[row] = nb
+        self.params[row] = params
+        self.pooling[row] = pooling
+        if params is not None and params.seed is not None:
+            gdev = device if torch.device(device).type == "cuda" else "cpu"
+            self.generators[req_id] = torch.Generator(device=gdev).manual_seed(params.seed)
+        return row
+
+    def remove(self, req_id: str) -> None:
+        row = self.index.pop(req_id, None)
+        if row is None:
+            return
+        self.generators.pop(req_id, None)
+        self.mirostat_mu.pop(req_id, None)
+        last = self.num_reqs - 1
+        if row != last:  # move the last row into the hole
+            n = int(self.num_tokens[last])
+            self.token_ids[row, :n] = self.token_ids[last, :n]
+            for arr in (self.num_tokens, self.num_prompt, self.num_computed, self.num_blocks):
+                arr[row] = arr[last]
+            nb = int(self.num_blocks[last])
+            self.block_table_np[row, :nb] = self.block_table_np[last, :nb]
+            rid = self.req_ids[last]
+            self.req_ids[row] = rid
+            self.index[rid] = row
+            self.params[row] = self.params[last]
+            self.pooling[row] = self.pooling[last]
+        self.req_ids[last] = None
+        self.params[last] = None
+        self.num_reqs = last
+
+    def append_blocks(self, row: int, block_ids: list[int]) -> None:
+        if block_ids:
+            nb = int(self.num_blocks[row])
+            self.block_table_np[row, nb:nb + len(block_ids)] = block_ids
+            self.num_blocks[row] = nb + len(block_ids)
+
+
+class ModelRunner:
+    def __init__(self, cfg: EngineConfig, device: torch.device) -> None:
+        self.cfg = cfg
+        self.device = device
+        self.is_cuda = device.type == "cuda"
+        self.model_cfg = cfg.model
+        self.block_size = cfg.cache.block_size
+        self.max_seqs = cfg.scheduler.max_num_seqs
+        self.max_tokens = cfg.scheduler.max_num_batched_tokens
+        self.max_model_len = cfg.model.max_model_len
+        self.batch = InputBatch(self.max_seqs, self.max_model_len, self.block_size, self.is_cuda)
+        self.sampler = Sampler()
+        self.model: torch.nn.Module | None = None
+        self.kv_caches: list[torch.Tensor] = []
+        self.kv_cfg: KVCacheConfig | None = None
+        pin = self.is_cuda
+        T, S = self.max_tokens, self.max_seqs
+
+        def host(n, dtype):
+            return torch.zeros(n, dtype=dtype, pin_memory=pin)
+        # pinned staging + persistent device inputs (stable addresses for graphs)
+        self.h_input_ids, self.h_positions, self.h_slots = host(T, torch.int32), host(T, torch.int64), host(T, torch.int32)
+        self.h_seq_lens, self.h_qsl, self.h_logit_idx = host(S, torch.int32), host(S + 1, torch.int32), host(S * 8, torch.int64)
+        self.d_input_ids = torch.zeros(T, dtype=torch.int32, device=device)
+        self.d_positions = torch.zeros(T, dtype=torch.int64, device=device)
+        self.d_slots = torch.full((T,), -1, dtype=torch.int32, device=device)
+        self.d_seq_lens = torch.zeros(S, dtype=torch.int32, device=device)
+        self.d_qsl = torch.zeros(S + 1, dtype=torch.int32, device=device)
+        self.d_logit_idx = torch.zeros(S * 8, dtype=torch.int64, device=device)
+        self.d_block_table = torch.zeros((S, self.batch.max_blocks), dtype=torch.int32, device=device)
+        self.h_sampled = host(S * 8, torch.int64)
+        self.h_bt = torch.zeros((S, self.batch.max_blocks), dtype=torch.int32, pin_memory=pin)
+        self.h_bt_np = self.h_bt.numpy()
+        self._pending: dict[str, Any] | None = None
+        self.graphs: dict[int, Any] = {}
+        self.stats = {"steps": 0, "prep_s": 0.0, "h2d_bytes": 0, "d2h_bytes": 0}
+        pp = state.get_pp_group() if state.model_parallel_is_initialized() else None
+        self.pp = pp if pp is not None and pp.world_size > 1 else None
+        self.spec_cfg = cfg.speculative
+        self._ngram = None
+        if self.spec_cfg.method == "ngram":
+            from sonar_b200.sample.spec_decode import NgramProposer
+            self._ngram = NgramProposer(self.spec_cfg)
+
+    # --------------------------------------------------------------- set-up
+    def load_model(self) -> None:
+        t0 = time.time()
+        with torch.inference_mode():
+            self.model = load_model(self.cfg, self.device)
+        logger.info("model %s built in %.1fs", self.model_cfg.model, time.time() - t0)
+
+    def kv_cache_spec(self) -> KVCacheSpec:
+        m = self.model_cfg
+        cache_dtype = self.cfg.cache.cache_dtype
+        nbytes = 1 if cache_dtype == "fp8" else torch.empty((), dtype=m.dtype).element_size()
+        spec_fn = getattr(self.model, "kv_cache_spec", None)
+        if spec_fn is not None:
+            return spec_fn(self.block_size, nbytes)
+        attn = self.model.attention_layers()[0]
+        return KVCacheSpec(self.block_size, attn.num_kv_heads, attn.head_dim, nbytes, "full",
+                           attn.sliding_window)
+
+    def num_local_layers(self) -> int:
+        return len(self.model.attention_layers())
+
+    def initialize_kv_cache(self, kv_cfg: KVCacheConfig) -> None:
+        self.kv_cfg = kv_cfg
+        spec = kv_cfg.spec
+        m = self.model_cfg
+        if self.cfg.cache.cache_dtype == "fp8":
+            dtype = torch.float8_e4m3fn
+        else:
+            dtype = m.dtype
+        self.kv_caches = []
+        for layer in self.model.attention_layers():
+            if spec.kind == "mla":
+                shape = (kv_cfg.num_blocks, spec.block_size, spec.mla_row)
+            else:
+                shape = (kv_cfg.num_blocks, 2, spec.num_kv_heads, spec.block_size, spec.head_size)
+            cache = torch.zeros(shape, dtype=dtype, device=self.device)
+            layer.bind_kv_cache(cache)
+            self.kv_caches.append(cache)
+        logger.info("KV cache: %d blocks × %d layers, %.2f GiB", kv_cfg.num_blocks, len(self.kv_caches),
+                    kv_cfg.num_blocks * len(self.kv_caches) * spec.page_bytes / 2**30)
+
+    # --------------------------------------------------------------- states
+    def _update_states(self, so: SchedulerOutput) -> None:
+        b = self.batch
+        for rid in so.finished_req_ids:
+            b.remove(rid)
+        for rid in so.preempted_req_ids:
+            b.remove(rid)
+        for nr in so.scheduled_new_reqs:
+            if nr.req_id in b.index:
+                b.remove(nr.req_id)
+            b.add(nr.req_id, nr.prompt_token_ids, nr.output_token_ids, nr.sampling_params, nr.block_ids,
+                  nr.num_computed_tokens, nr.pooling, self.device)
+        c = so.scheduled_cached_reqs
+        for i, rid in enumerate(c.req_ids):
+            row = b.index[rid]
+            b.append_blocks(row, c.new_block_ids[i])
+            b.num_computed[row] = c.num_computed_tokens[i]
+            if c.new_token_ids:  # non-last pipeline stages learn sampled tokens here
+                toks = c.new_token_ids[i]
+                n = int(b.num_tokens[row])
+                b.token_ids[row, n:n + len(toks)] = toks
+                b.num_tokens[row] = n + len(toks)
+
+    # --------------------------------------------------------------- inputs
+    def _prepare_inputs(self, so: SchedulerOutput) -> tuple[AttentionMetadata, np.ndarray, np.ndarray]:
+        b = self.batch
+        n = b.num_reqs
+        sched = np.fromiter((so.num_scheduled_tokens.get(b.req_ids[i], 0) for i in range(n)),
+                            dtype=np.int32, count=n)
+        rows = np.nonzero(sched)[0]
+        # scheduled rows first keeps the kernel work list dense; rows with no
+        # tokens this step (budget ran out) simply do not appear
+        q_lens = sched[rows]
+        total = int(q_lens.sum())
+        starts = np.zeros(len(rows) + 1, dtype=np.int32)
+        np.cumsum(q_lens, out=starts[1:])
+        req_of_tok = np.repeat(np.arange(len(rows), dtype=np.int32), q_lens)
+        computed = b.num_computed[rows]
+        offs = np.arange(total, dtype=np.int32) - starts[:-1][req_of_tok]
+        pos = computed[req_of_tok] + offs
+        row_of_tok = rows[req_of_tok]
+        # draft tokens are written after the known tokens so they are read like any other
+        for rid, drafts in so.scheduled_spec_decode_tokens.items():
+            r = b.index[rid]
+            nt = int(b.num_tokens[r])
+            b.token_ids[r, nt:nt + len(drafts)] = drafts
+        ids = b.token_ids[row_of_tok, pos]
+        blk = b.block_table_np[row_of_tok, pos // self.block_size]
+        slots = blk * self.block_size + pos % self.block_size
+        seq_lens = computed + q_lens
+        ns = len(rows)
+        self.h_input_ids.numpy()[:total] = ids
+        self.h_positions.numpy()[:total] = pos
+        self.h_slots.numpy()[:total] = slots
+        self.h_seq_lens.numpy()[:ns] = seq_lens
+        self.h_qsl.numpy()[:ns + 1] = starts
+        self.h_qsl.numpy()[ns + 1:] = total
+        self.h_seq_lens.numpy()[ns:] = 0
+        nb_used = int(b.num_blocks[rows].max()) if ns else 1
+        nbt = self.d_block_table.shape[1]
+        nb_used = min(nbt, max(nb_used, 1))
+        if ns:  # block-table rows in step order
+            self.h_bt_np[:ns, :nb_used] = b.block_table_np[rows, :nb_used]
+        nbl = self.is_cuda
+        self.d_input_ids[:total].copy_(self.h_input_ids[:total], non_blocking=nbl)
+        self.d_positions[:total].copy_(self.h_positions[:total], non_blocking=nbl)
+        self.d_slots[:total].copy_(self.h_slots[:total], non_blocking=nbl)
+        self.d_seq_lens.copy_(self.h_seq_lens, non_blocking=nbl)
+        self.d_qsl.copy_(self.h_qsl, non_blocking=nbl)
+        if ns:
+            self.d_block_table[:ns, :nb_used].copy_(self.h_bt[:ns, :nb_used], non_blocking=nbl)
+        self.stats["h2d_bytes"] += total * 16 + (2 * self.max_seqs + 1) * 4 + ns * nb_used * 4
+        meta = AttentionMetadata(
+            num_tokens=total, num_seqs=ns, positions=self.d_positions[:total], slot_mapping=self.d_slots[:total],
+            block_tables=self.d_block_table, seq_lens=self.d_seq_lens, query_start_loc=self.d_qsl,
+            max_query_len=int(q_lens.max()) if ns else 0, max_seq_len=int(seq_lens.max()) if ns else 0,
+            query_lens_cpu=q_lens, seq_lens_cpu=seq_lens)
+        return meta, rows, q_lens
+
+    # --------------------------------------------------------------- execute
+    @torch.inference_mode()
+    def execute_model(self, so: SchedulerOutput, intermediate=None) -> ModelRunnerOutput | tuple | None:
+        t0 = time.perf_counter()
+        self._update_states(so)
+        if so.total_num_scheduled_tokens == 0:
+            return ModelRunnerOutput()
+        meta, rows, q_lens = self._prepare_inputs(so)
+        self.stats["prep_s"] += time.perf_counter() - t0
+        self.stats["steps"] += 1
+        total = meta.num_tokens
+        tp = get_tp_context()
+        tp.begin_step(total)
+        if self.is_cuda:
+            from sonar_b200.ops import cuda as cuda_ops
+            cuda_ops.build_attention_work(meta, self)
+        ids = self.d_input_ids[:total]
+        if self.pp is not None and not self.pp.is_first_rank:
+            intermediate = self._recv_intermediate(tp.local_tokens(total))
+        out = self.model(ids, meta, intermediate)
+        if self.pp is not None and not self.pp.is_last_rank:
+            self._send_intermediate(out)
+            return None
+        hidden = tp.gather_tokens(out, total)
+        return self._sample(so, hidden, meta, rows, q_lens)
+
+    def _send_intermediate(self, out) -> None:
+        h, r = out
+        self.pp.send(h.contiguous()).wait()
+        self.pp.send(r.contiguous()).wait()
+
+    def _recv_intermediate(self, n: int):
+        hdim = self.model_cfg.hidden_size
+        h = self.pp.recv((n, hdim), self.model_cfg.dtype, self.device)
+        r = self.pp.recv((n, hdim), self.model_cfg.dtype, self.device)
+        return h, r
+
+    def _sample(self, so: SchedulerOutput, hidden: torch.Tensor, meta: AttentionMetadata, rows: np.ndarray,
+                q_lens: np.ndarray) -> ModelRunnerOutput:
+        b = self.batch
+        ns = len(rows)
+        starts = np.zeros(ns + 1, dtype=np.int64)
+        np.cumsum(q_lens, out=starts[1:])
+        computed_after = b.num_computed[rows] + q_lens
+        known = b.num_tokens[rows]
+        req_ids = [b.req_ids[r] for r in rows]
+        n_draft = np.array([len(so.scheduled_spec_decode_tokens.get(rid, ())) for rid in req_ids], dtype=np.int64)
+        # a row yields tokens once every known token has been computed
+        samples = computed_after >= known
+        out = ModelRunnerOutput(req_ids=req_ids, sampled_token_ids=[[] for _ in range(ns)])
+        # pooling requests: hand back the last hidden state when the prompt is complete
+        pool_rows = [i for i in range(ns) if b.pooling[rows[i]]]
+        for i in pool_rows:
+            if samples[i]:
+                vec = hidden[starts[i + 1] - 1].float()
+                out.pooled[req_ids[i]] = torch.nn.functional.normalize(vec, dim=0).cpu()
+            samples[i] = False
+        self._prompt_logprobs(so, hidden, rows, q_lens, starts, req_ids, out)
+        idx = np.nonzero(samples)[0]
+        if len(idx) == 0:
+            return out
+        # logits rows: the last position, plus one per draft token before it
+        gather: list[int] = []
+        row_span: list[tuple[int, int]] = []
+        for i in idx:
+            k = int(n_draft[i])
+            end = int(starts[i + 1])
+            row_span.append((len(gather), k + 1))
+            gather.extend(range(end - 1 - k, end))
+        g = len(gather)
+        self.h_logit_idx.numpy()[:g] = gather
+        self.d_logit_idx[:g].copy_(self.h_logit_idx[:g], non_blocking=self.is_cuda)
+        sel = hidden.index_select(0, self.d_logit_idx[:g])
+        logits = self.model.compute_logits(sel)
+        params, prompts, outs_hist, gens, sample_rids = [], [], [], {}, []
+        for j, i in enumerate(idx):
+            r = rows[i]
+            p = b.params[r]
+            lo, cnt = row_span[j]
+            npmt, ntok = int(b.num_prompt[r]), int(b.num_tokens[r])
+            need_hist = p.needs_penalties or p.needs_extended or p.min_tokens > 0 or bool(p._bad_words_token_ids)
+            for c in range(cnt):
+                params.append(p)
+                sample_rids.append(req_ids[i])
+                if need_hist:
+                    prompts.append(b.token_ids[r, :npmt].tolist())
+                    outs_hist.append(b.token_ids[r, npmt:ntok + c].tolist())
+                else:
+                    prompts.append([])
+                    outs_hist.append([])
+                gen = b.generators.get(req_ids[i])
+                if gen is not None:
+                    gens[lo + c] = gen
+        mu = {k: b.mirostat_mu[rid] for k, rid in enumerate(sample_rids) if rid in b.mirostat_mu}
+        md = make_sampling_metadata(params, prompts, outs_hist, logits.device, gens, mu, sample_rids)
+        res = self.sampler(logits, md)
+        for k, v in md.mirostat_mu.items():
+            b.mirostat_mu[sample_rids[k]] = v
+        self.h_sampled[:g].copy_(res.token_ids, non_blocking=False)
+        self.stats["d2h_bytes"] += g * 8
+        sampled = self.h_sampled[:g].tolist()
+        want_lp = res.logprobs is not None
+        if want_lp:
+            out.logprobs = [None] * ns
+        spec_out: list[list[int]] | None = [[] for _ in range(ns)] if self._ngram is not None else None
+        for j, i in enumerate(idx):
+            lo, cnt = row_span[j]
+            r = rows[i]
+            toks = sampled[lo:lo + cnt]
+            if cnt > 1:
+                # greedy verification: keep sampled tokens while they agree with the drafts
+                drafts = so.scheduled_spec_decode_tokens[req_ids[i]]
+                acc = 0
+                while acc < len(drafts) and toks[acc] == drafts[acc]:
+                    acc += 1
+                toks = toks[:acc + 1]
+            nt = int(b.num_tokens[r])
+            b.token_ids[r, nt:nt + len(toks)] = toks
+            b.num_tokens[r] = nt + len(toks)
+            out.sampled_token_ids[i] = toks
+            if want_lp:
+                out.logprobs[i] = res.logprobs[lo:lo + len(toks)]
+            if spec_out is not None:
+                spec_out[i] = self._ngram.propose(b.token_ids[r, :nt + len(toks)])
+        out.spec_token_ids = spec_out
+        return out
+
+    def _prompt_logprobs(self, so, hidden, rows, q_lens, starts, req_ids, out: ModelRunnerOutput) -> None:
+        b = self.batch
+        for i, r in enumerate(rows):
+            p = b.params[r]
+            if p is None or p.prompt_logprobs is None:
+                continue
+            comp, npmt = int(b.num_computed[r]), int(b.num_prompt[r])
+            if comp >= npmt:
+                continue
+            n = min(int(q_lens[i]), npmt - comp)
+            logits = self.model.compute_logits(hidden[starts[i]:starts[i] + n])
+            lp = torch.log_softmax(logits, dim=-1)
+            k = lp.shape[-1] if p.prompt_logprobs == -1 else max(p.prompt_logprobs, 0)
+            entries: list[dict[int, float] | None] = []
+            if comp == 0:
+                entries.append(None)  # the first prompt token has no predecessor
+            tv, ti = (lp.topk(k, dim=-1) if k else (None, None))
+            for j in range(n):
+                tgt_pos = comp + j + 1
+                if tgt_pos >= npmt:
+                    break
+                tgt = int(b.token_ids[r, tgt_pos])
+                d = {tgt: float(lp[j, tgt])}
+                if k:
+                    for a, c in zip(ti[j].tolist(), tv[j].tolist()):
+                        d.setdefault(a, c)
+                entries.append(d)
+            out.prompt_logprobs[req_ids[i]] = entries
+
+    # --------------------------------------------------------------- misc
+    def profile_activation_bytes(self) -> int:
+        """Upper bound of transient device memory of one full-budget step."""
+        m = self.model_cfg
+        tp = state.tp_world_size()
+        t = self.max_tokens
+        el = torch.empty((), dtype=m.dtype).element_size()
+        inter = int(m.get("intermediate_size", 4 * m.hidden_size))
+        widest = max((m.num_attention_heads + 2 * m.num_kv_heads) * m.head_dim, 2 * inter) // tp
+        act = t * (4 * m.hidden_size + 2 * widest) * el
+        logits = self.max_seqs * (m.vocab_size * 6)
+        return int(1.2 * (act + logits)) + (256 << 20)

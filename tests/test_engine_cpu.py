@@ -1,0 +1,82 @@
+"""End-to-end engine behaviour on CPU with the PyTorch op restatements."""
+import random
+
+import pytest
+
+from sonar_b200 import LLM, SamplingParams
+
+
+@pytest.fixture(scope="module")
+def llm():
+    eng = LLM("tiny-llama", dtype="float32", max_model_len=512, num_gpu_blocks_override=256,
+              max_num_seqs=8, max_num_batched_tokens=64)
+    yield eng
+    eng.shutdown()
+
+
+def _prompts(n, seed=0, lo=5, hi=90):
+    rng = random.Random(seed)
+    return [[rng.randrange(4, 1000) for _ in range(rng.randrange(lo, hi))] for _ in range(n)]
+
+
+def test_batched_equals_single(llm):
+    sp = SamplingParams(temperature=0, max_tokens=12, ignore_eos=True)
+    prompts = _prompts(12)
+    batched = llm.generate([{"prompt_token_ids": p} for p in prompts], sp)
+    assert [o.request_id for o in batched] == sorted((o.request_id for o in batched), key=int)
+    for p, o in zip(prompts[:4], batched[:4]):
+        single = llm.generate({"prompt_token_ids": p}, sp)[0]
+        assert single.outputs[0].token_ids == o.outputs[0].token_ids
+        assert o.outputs[0].finish_reason == "length"
+        assert len(o.outputs[0].token_ids) == 12
+
+
+def test_prefix_cache_hit_same_output(llm):
+    sp = SamplingParams(temperature=0, max_tokens=8, ignore_eos=True)
+    p = _prompts(1, seed=3, lo=70, hi=80)[0]
+    first = llm.generate({"prompt_token_ids": p}, sp)[0]
+    second = llm.generate({"prompt_token_ids": p}, sp)[0]
+    assert second.num_cached_tokens >= 64
+    assert first.outputs[0].token_ids == second.outputs[0].token_ids
+
+
+def test_seeded_sampling_reproducible(llm):
+    sp = SamplingParams(temperature=0.9, top_p=0.9, top_k=50, seed=1234, max_tokens=10, ignore_eos=True)
+    p = _prompts(1, seed=5)[0]
+    a = llm.generate({"prompt_token_ids": p}, sp)[0].outputs[0].token_ids
+    b = llm.generate({"prompt_token_ids": p}, sp)[0].outputs[0].token_ids
+    assert a == b
+
+
+def test_n_greater_than_one(llm):
+    sp = SamplingParams(temperature=1.0, n=3, seed=7, max_tokens=5, ignore_eos=True)
+    out = llm.generate({"prompt_token_ids": _prompts(1, seed=6)[0]}, sp)[0]
+    assert len(out.outputs) == 3
+    assert sorted(c.index for c in out.outputs) == [0, 1, 2]
+
+
+def test_logprobs(llm):
+    sp = SamplingParams(temperature=0, max_tokens=4, logprobs=3, prompt_logprobs=2, ignore_eos=True)
+    p = _prompts(1, seed=8, lo=10, hi=12)[0]
+    out = llm.generate({"prompt_token_ids": p}, sp)[0]
+    comp = out.outputs[0]
+    assert len(comp.logprobs) == 4
+    for tok, d in zip(comp.token_ids, comp.logprobs):
+        assert tok in d and d[tok].rank == 1  # greedy token is the most likely
+        assert len(d) >= 3
+    assert out.prompt_logprobs[0] is None and len(out.prompt_logprobs) == len(p)
+
+
+def test_stop_token_and_text(llm):
+    sp = SamplingParams(temperature=0, max_tokens=12, ignore_eos=True)
+    p = _prompts(1, seed=9)[0]
+    ref = llm.generate({"prompt_token_ids": p}, sp)[0].outputs[0].token_ids
+    sp2 = SamplingParams(temperature=0, max_tokens=12, stop_token_ids=[ref[3]])
+    out = llm.generate({"prompt_token_ids": p}, sp2)[0].outputs[0]
+    cut = ref.index(ref[3])
+    assert out.token_ids == ref[:cut + 1] and out.finish_reason == "stop" and out.stop_reason == ref[3]
+
+
+def test_text_prompt_roundtrip(llm):
+    out = llm.generate("hello world", SamplingParams(temperature=0, max_tokens=4, ignore_eos=True))[0]
+    assert out.prompt == "hello world" and len(out.outputs[0].token_ids) == 4

@@ -1,0 +1,256 @@
+"""Headline benchmark: offline generation throughput (output tokens / s).
+
+Workload (the reference's offline-throughput configuration for a Llama-3-8B
+architecture decoder): 2000 requests, each 1024 uniform-random prompt token ids
+and 256 generated tokens (``ignore_eos``), ``max_num_seqs`` 256, KV block size
+16, bf16, random-init weights, tensor parallel over the N GPUs of one node.
+
+    python bench.py                      # N=1, whole workload
+    python bench.py --steps 200 --warmup 8          # a steady-state window
+    torchrun ... bench.py --gpus 8 ...   # one rank per GPU
+
+A *step* is one engine step (schedule → forward → sample).  With ``--steps 0``
+(default) every step of the workload is timed, start to finish.  With
+``--steps K`` the engine is first driven (untimed) until the batch is in steady
+state — every sequence slot filled and the first completions happening — then W
+warm-up steps and exactly K timed steps follow.
+
+``value`` is timed on the device (CUDA events around the K steps, max over
+ranks).  ``e2e`` repeats the whole workload through the public API
+(``LLM.generate``) on the host clock; every engine step copies its inputs from
+pinned host memory and reads the sampled ids back, and those bytes are
+counted by the model runner.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "output_tokens_per_second"
+BASELINE_PUBLISHED = None  # BASELINE.json "published" is empty: no published number to divide by
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=0, help="0 = time the whole workload")
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="sonar", choices=["sonar", "reference"])
+    ap.add_argument("--model", default="llama-3-8b")
+    ap.add_argument("--num-requests", type=int, default=2000)
+    ap.add_argument("--input-len", type=int, default=1024)
+    ap.add_argument("--output-len", type=int, default=256)
+    ap.add_argument("--max-num-seqs", type=int, default=256)
+    ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end repeat (debugging)")
+    ap.add_argument("--temperature", type=float, default=1.0)
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of this rank's GPU while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.gpu = gpu_index
+        self.rows: list[list[str]] = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self) -> None:
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.gpu)], capture_output=True, text=True, timeout=5).stdout
+                for line in out.strip().splitlines():
+                    self.rows.append([c.strip() for c in line.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def start(self) -> None:
+        self._thread.start()
+
+    def stop(self) -> dict:
+        self._stop.set()
+        self._thread.join(timeout=6)
+        sm = [float(r[1]) for r in self.rows if len(r) > 8 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) > 8 and r[2].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) > 8 for n, v in zip(names, r[5:9]) if v.lower() == "active"})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def reference_arm(args) -> None:
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    why = None
+    if not os.path.isdir(os.path.join(ref_dir, "aphrodite")):
+        why = ("reference not installed: `pip install --no-index --no-build-isolation --find-links /opt/wheelhouse "
+               "--target baseline/_ref /root/reference` fails in metadata generation (setup.py imports "
+               "setuptools_scm, absent from the image and the wheelhouse); its CUDA build also fetches CUTLASS "
+               "and FlashAttention sources from the network")
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why or "reference import failed"}))
+
+
+def make_prompts(n: int, length: int, vocab: int, seed: int = 0) -> list[list[int]]:
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    return rng.integers(0, vocab, size=(n, length), dtype=np.int64).tolist()
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+    import torch
+    import torch.distributed as dist
+
+    from sonar_b200 import LLM, SamplingParams
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit(f"--gpus {args.gpus} needs one rank per GPU: launch with "
+                             f"`python -m torch.distributed.run --nproc-per-node {args.gpus} bench.py ...`")
+        args.gpus = world
+    os.environ.setdefault("SONAR_LOG_LEVEL", "WARNING" if rank else "INFO")
+    max_len = args.input_len + args.output_len + 16
+    llm = LLM(args.model, dtype="bfloat16", max_model_len=max_len, max_num_seqs=args.max_num_seqs,
+              max_num_batched_tokens=args.max_num_batched_tokens, block_size=16, enable_prefix_caching=True,
+              skip_tokenizer_init=True, tensor_parallel_size=args.gpus, seed=0,
+              distributed_executor_backend="external_launcher" if world > 1 else "uni")
+    engine = llm.llm_engine
+    vocab = engine.cfg.model.vocab_size
+    from sonar_b200.ops import cuda as cuda_ops
+
+    def barrier() -> None:
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sp = SamplingParams(temperature=args.temperature, max_tokens=args.output_len, ignore_eos=True, detokenize=False)
+    from sonar_b200.sampling_params import RequestOutputKind
+    sp.output_kind = RequestOutputKind.FINAL_ONLY
+
+    # ---- warm-up: a small workload of the same shape, run to completion (untimed)
+    warm = make_prompts(min(32, args.num_requests), args.input_len, vocab, seed=12345)
+    wsp = SamplingParams(temperature=args.temperature, max_tokens=max(args.warmup, 3), ignore_eos=True, detokenize=False)
+    llm.generate([{"prompt_token_ids": p} for p in warm], wsp)
+    llm.reset_prefix_cache()
+    barrier()
+
+    prompts = make_prompts(args.num_requests, args.input_len, vocab, seed=0)
+    runner = engine.core.engine_core.executor.worker.runner
+
+    # ---- device-timed run -------------------------------------------------------------------
+    for i, p in enumerate(prompts):
+        engine.add_request(f"b{i}", {"prompt_token_ids": p}, sp)
+    primed_steps = 0
+    if args.steps > 0:
+        # untimed: drive until steady state (all slots busy and the first requests completing)
+        finished = 0
+        while engine.has_unfinished_requests() and finished == 0:
+            finished += sum(1 for o in engine.step() if o.finished)
+            primed_steps += 1
+        for _ in range(args.warmup):
+            engine.step()
+            primed_steps += 1
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = cuda_ops.launch_count
+    h2d0, d2h0 = runner.stats["h2d_bytes"], runner.stats["d2h_bytes"]
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    t_host0 = time.perf_counter()
+    steps = 0
+    out_tokens = 0
+    core = engine.core.engine_core
+    while engine.has_unfinished_requests() and (args.steps == 0 or steps < args.steps):
+        outs = core.step()
+        steps += 1
+        out_tokens += sum(len(o.new_token_ids) for o in outs.outputs)
+        engine.output_processor.process_outputs(outs.outputs)
+    end.record()
+    barrier()
+    host_s = time.perf_counter() - t_host0
+    clocks = sampler.stop()
+    dev_ms = start.elapsed_time(end)
+    launches = cuda_ops.launch_count - launches0
+    h2d, d2h = runner.stats["h2d_bytes"] - h2d0, runner.stats["d2h_bytes"] - d2h0
+    if world > 1:
+        t = torch.tensor([dev_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms = float(t.item())
+    # drain whatever is left of a windowed run, untimed
+    while engine.has_unfinished_requests():
+        engine.step()
+    cuda_ops.check_device_errors()
+    value = out_tokens / (dev_ms / 1e3)
+
+    # ---- end-to-end through the public API -----------------------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        llm.reset_prefix_cache()
+        barrier()
+        h2d0, d2h0, s0 = runner.stats["h2d_bytes"], runner.stats["d2h_bytes"], runner.stats["steps"]
+        t0 = time.perf_counter()
+        results = llm.generate([{"prompt_token_ids": p} for p in prompts], sp)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([dt], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        n_out = sum(len(r.outputs[0].token_ids) for r in results)
+        n_steps = max(runner.stats["steps"] - s0, 1)
+        e2e = {"value": n_out / dt, "unit": "tokens/s", "seconds": dt, "engine_steps": n_steps,
+               "h2d_bytes_per_step": (runner.stats["h2d_bytes"] - h2d0) // n_steps,
+               "d2h_bytes_per_step": (runner.stats["d2h_bytes"] - d2h0) // n_steps}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps,
+            "warmup": args.warmup, "ms_per_step": dev_ms / max(steps, 1), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": (value / BASELINE_PUBLISHED) if BASELINE_PUBLISHED else None,
+            "dtype": "bf16", "data": "synthetic (uniform-random token ids, random-init weights)",
+            "impl": "sonar_b200",
+            "config": {
+                "model": args.model, "num_requests": args.num_requests, "input_len": args.input_len,
+                "output_len": args.output_len, "max_num_seqs": args.max_num_seqs,
+                "max_num_batched_tokens": args.max_num_batched_tokens, "block_size": 16,
+                "global_batch": args.max_num_seqs, "seq_len": args.input_len + args.output_len,
+                "parallelism": f"tp{args.gpus}", "temperature": args.temperature,
+                "window": "whole_workload" if args.steps == 0 else f"steady_state (after {primed_steps} untimed steps)",
+                "l2": "no flush needed: every step streams the full weight set and KV pages (tens of GB, L2 is 126 MB)",
+            },
+            "output_tokens": out_tokens, "device_seconds": dev_ms / 1e3, "host_seconds": host_s,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "h2d_bytes_per_step": h2d // max(steps, 1), "d2h_bytes_per_step": d2h // max(steps, 1),
+        }
+        print(json.dumps(line))
+    llm.shutdown()
+    if world > 1 and dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,497 @@
+// Paged GQA attention over the block-table KV cache: decode and prefill kernels.
+//
+// Cache layout (one tensor per layer): [blocks, 2, kv_heads, 16, HD]; a (block, K|V, head) tile is a
+// contiguous 16×HD run, streamed to shared memory with 16-byte cp.async into an XOR-swizzled tile
+// (chunk ^= key & 7) that ldmatrix reads without bank conflicts.  Scores and outputs use
+// mma.sync.m16n8k16 (bf16/f16 in, fp32 accumulate) with an online softmax in the exp2 domain.
+//
+//  * decode kernel:  one CTA per (sequence, kv head, kv split); the q_len × group ≤ 16 query rows of
+//    that kv head form one MMA row tile; the 4 warps take every 4th page with private 3-stage
+//    pipelines (≈96 KB in flight per CTA, 2 CTAs/SM) and merge their partial softmax states through
+//    shared memory.  Long contexts at small batch are split over gridDim.z, merged by attn_merge_kernel.
+//  * prefill kernel: one CTA per (sequence, kv head, 64-row query tile); rows are (query position, head
+//    in group) pairs, 16 per warp; the CTA streams 64-key tiles (4 pages) through a 2-stage pipeline
+//    shared by the 4 warps, causal limit per tile.
+//
+// Attention FLOPs are a few percent of a decoder step at serving sequence lengths and decode is bound
+// by the KV bytes, so this kernel family targets HBM bandwidth; the tcgen05 pipeline is spent on the GEMMs.
+// Behavioural parity: the reference's paged attention backends (v1/attention/backends/flash_attn.py:715,
+// v1/attention/ops/triton_unified_attention.py).
+#include "common.cuh"
+
+namespace sonar {
+
+constexpr int PAGE = 16;
+
+__device__ __forceinline__ void cp_async16(uint32_t smem, const void* gptr) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem), "l"(gptr));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+template <typename T> __device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1);
+template <> __device__ __forceinline__ void mma16816<__nv_bfloat16>(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void mma16816<__half>(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Per-warp softmax state for a 16-row tile: each thread owns rows lane/4 and lane/4+8.
+template <int HD>
+struct RowState {
+  float m[2], l[2];
+  float o[HD / 8][4];
+  __device__ __forceinline__ void init() {
+    m[0] = m[1] = -INFINITY;
+    l[0] = l[1] = 0.f;
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  }
+};
+
+// Issue the cp.async copies of one 16-key page (K and V tiles of one kv head) by one warp.
+template <typename T, int HD>
+__device__ __forceinline__ void load_page_warp(uint32_t k_smem, uint32_t v_smem, const T* k_g, const T* v_g, int lane) {
+  constexpr int CPR = HD / 8;             // 16-byte chunks per key row
+  constexpr int CHUNKS = PAGE * CPR;
+#pragma unroll
+  for (int c = lane; c < CHUNKS; c += 32) {
+    int key = c / CPR, ch = c % CPR;
+    uint32_t off = key * (HD * 2) + ((ch ^ (key & 7)) << 4);
+    cp_async16(k_smem + off, k_g + c * 8);
+    cp_async16(v_smem + off, v_g + c * 8);
+  }
+}
+
+// Scores, online softmax and P·V for one 16-key page held in shared memory.
+// key0: absolute index of the page's first key.  limit[r]: keys <= limit[r] are visible to row r
+// (already includes the context length); lower[r]: keys >= lower[r] (sliding window).
+template <typename T, int HD>
+__device__ __forceinline__ void process_page(RowState<HD>& st, const uint32_t (*qf)[4], uint32_t k_smem,
+                                             uint32_t v_smem, int key0, const int* limit, const int* lower,
+                                             float scale_log2, int lane) {
+  float s[2][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+  const int j = lane >> 3, r = lane & 7;
+  {
+    const int key = ((j >> 1) << 3) + r;
+    const uint32_t row = k_smem + key * (HD * 2);
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      int ch = ks * 2 + (j & 1);
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4(row + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
+      mma16816<T>(s[0], qf[ks], b0, b1);
+      mma16816<T>(s[1], qf[ks], b2, b3);
+    }
+  }
+  const int c0 = key0 + ((lane & 3) << 1);
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      int key = c0 + nt * 8 + (e & 1);
+      int rr = e >> 1;
+      bool ok = key <= limit[rr] && key >= lower[rr];
+      float v = ok ? s[nt][e] * scale_log2 : -INFINITY;
+      s[nt][e] = v;
+      mx[rr] = fmaxf(mx[rr], v);
+    }
+  float alpha[2];
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
+    mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
+    float m_new = fmaxf(st.m[rr], mx[rr]);
+    float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+    alpha[rr] = exp2f(st.m[rr] - m_use);      // -inf - x -> 0
+    st.m[rr] = m_new;
+    st.l[rr] *= alpha[rr];
+    mx[rr] = m_use;
+  }
+  uint32_t pf[4];
+  {
+    float p[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        p[nt][e] = exp2f(s[nt][e] - mx[e >> 1]);
+        st.l[e >> 1] += p[nt][e];
+      }
+    pf[0] = pack2<T>(p[0][0], p[0][1]);
+    pf[1] = pack2<T>(p[0][2], p[0][3]);
+    pf[2] = pack2<T>(p[1][0], p[1][1]);
+    pf[3] = pack2<T>(p[1][2], p[1][3]);
+  }
+  {
+    const int key = ((j & 1) << 3) + r;
+    const uint32_t row = v_smem + key * (HD * 2);
+#pragma unroll
+    for (int np = 0; np < HD / 16; ++np) {
+      int ch = np * 2 + (j >> 1);
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4_t(row + ((ch ^ (key & 7)) << 4), b0, b1, b2, b3);
+      float* o0 = st.o[np * 2];
+      float* o1 = st.o[np * 2 + 1];
+      o0[0] *= alpha[0]; o0[1] *= alpha[0]; o0[2] *= alpha[1]; o0[3] *= alpha[1];
+      o1[0] *= alpha[0]; o1[1] *= alpha[0]; o1[2] *= alpha[1]; o1[3] *= alpha[1];
+      mma16816<T>(o0, pf, b0, b1);
+      mma16816<T>(o1, pf, b2, b3);
+    }
+  }
+}
+
+// Load the Q fragments of a 16-row tile straight from global memory.
+// row r ↔ (query position qp0 + r / group, head kvh*group + r % group).
+template <typename T, int HD>
+__device__ __forceinline__ void load_q_frags(uint32_t (*qf)[4], const T* q, long q_tok_stride, int tok0, int qp0,
+                                             int q_len, int kvh, int group, int row_base, int lane) {
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    int rrow = row_base + (lane >> 2) + half * 8;
+    int qp = qp0 + rrow / group;
+    int head = kvh * group + rrow % group;
+    bool ok = qp < q_len;
+    const T* src = q + (long)(tok0 + qp) * q_tok_stride + (long)head * HD + ((lane & 3) << 1);
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      qf[ks][half] = ok ? *reinterpret_cast<const uint32_t*>(src + ks * 16) : 0u;
+      qf[ks][half + 2] = ok ? *reinterpret_cast<const uint32_t*>(src + ks * 16 + 8) : 0u;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ decode
+template <typename T, int HD, int NSTAGE>
+__global__ void __launch_bounds__(128) attn_decode_kernel(
+    const T* __restrict__ q, long q_tok_stride, const T* __restrict__ cache, const int* __restrict__ block_tables,
+    int bt_stride, const int* __restrict__ seq_lens, const int* __restrict__ qsl, const int* __restrict__ items,
+    const int* __restrict__ n_items, T* __restrict__ out, long out_tok_stride, float* __restrict__ part_o,
+    float* __restrict__ part_lse, int hq, int hk, float scale_log2, int window, int num_splits, int total_rows) {
+  if ((int)blockIdx.x >= *n_items) return;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  constexpr int TILE = PAGE * HD * 2;            // bytes of one K (or V) page tile
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seq = items[blockIdx.x], kvh = blockIdx.y, split = blockIdx.z;
+  const int ctx = seq_lens[seq], tok0 = qsl[seq], q_len = qsl[seq + 1] - tok0;
+  const int group = hq / hk;
+  const int n_pages = (ctx + PAGE - 1) / PAGE;
+  int first_key = 0;
+  if (window > 0) first_key = max(0, ctx - q_len - window + 1);
+  const int pages_per_split = (n_pages + num_splits - 1) / num_splits;
+  const int p_begin = max(split * pages_per_split, first_key / PAGE);
+  const int p_end = min(n_pages, (split + 1) * pages_per_split);
+
+  uint32_t qf[HD / 16][4];
+  load_q_frags<T, HD>(qf, q, q_tok_stride, tok0, 0, q_len, kvh, group, 0, lane);
+  int limit[2], lower[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    int qp = ((lane >> 2) + h * 8) / group;
+    limit[h] = qp < q_len ? ctx - q_len + qp : -1;
+    lower[h] = window > 0 ? limit[h] - window + 1 : 0;
+  }
+  RowState<HD> st;
+  st.init();
+
+  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem_raw) + warp * (NSTAGE * 2 * TILE);
+  const int* bt = block_tables + (long)seq * bt_stride;
+  const long head_off = (long)kvh * PAGE * HD;
+  const long blk_stride = 2L * hk * PAGE * HD;
+  const long v_off = (long)hk * PAGE * HD;
+  const int my_first = p_begin + warp;
+  const int n_mine = my_first < p_end ? (p_end - my_first + 3) / 4 : 0;
+  // block-table entries of this warp's pages, 32 at a time in lane registers
+  int bt_reg = 0;
+  auto refill = [&](int base_iter) {
+    int it = base_iter + lane;
+    bt_reg = it < n_mine ? bt[my_first + it * 4] : 0;
+  };
+  refill(0);
+  auto issue = [&](int it) {
+    if (it < n_mine) {
+      int blk = __shfl_sync(0xffffffffu, bt_reg, it & 31);
+      const T* kg = cache + (long)blk * blk_stride + head_off;
+      uint32_t sb = sbase + (it % NSTAGE) * 2 * TILE;
+      load_page_warp<T, HD>(sb, sb + TILE, kg, kg + v_off, lane);
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int i = 0; i < NSTAGE - 1; ++i) issue(i);
+  for (int it = 0; it < n_mine; ++it) {
+    cp_async_wait<NSTAGE - 2>();
+    __syncwarp();
+    uint32_t sb = sbase + (it % NSTAGE) * 2 * TILE;
+    process_page<T, HD>(st, qf, sb, sb + TILE, (my_first + it * 4) * PAGE, limit, lower, scale_log2, lane);
+    __syncwarp();
+    int nxt = it + NSTAGE - 1;
+    if ((nxt & 31) == 0) refill(nxt);
+    issue(nxt);
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- merge the four warps through shared memory (the pipeline buffers are free now)
+  float* sm_o = reinterpret_cast<float*>(smem_raw);                 // [4][16][HD]
+  float* sm_m = sm_o + 4 * 16 * HD;                                  // [4][16]
+  float* sm_l = sm_m + 64;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float l = st.l[h];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    int row = (lane >> 2) + h * 8;
+    if ((lane & 3) == 0) { sm_m[warp * 16 + row] = st.m[h]; sm_l[warp * 16 + row] = l; }
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt) {
+      float* dst = sm_o + ((warp * 16 + row) * HD) + nt * 8 + ((lane & 3) << 1);
+      dst[0] = st.o[nt][h * 2];
+      dst[1] = st.o[nt][h * 2 + 1];
+    }
+  }
+  __syncthreads();
+  const int rows_valid = min(16, q_len * group);
+  for (int idx = threadIdx.x; idx < rows_valid * HD; idx += 128) {
+    int row = idx / HD, d = idx % HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w * 16 + row]);
+    float L = 0.f, acc = 0.f;
+    if (M != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        float sc = exp2f(sm_m[w * 16 + row] - M);
+        L += sm_l[w * 16 + row] * sc;
+        acc += sm_o[(w * 16 + row) * HD + d] * sc;
+      }
+    }
+    float val = L > 0.f ? acc / L : 0.f;
+    int qp = row / group, head = kvh * group + row % group;
+    long tok = tok0 + qp;
+    if (num_splits == 1) {
+      out[tok * out_tok_stride + (long)head * HD + d] = from_f<T>(val);
+    } else {
+      long prow = (((long)split * gridDim.x + blockIdx.x) * hk + kvh) * 16 + row;
+      part_o[prow * HD + d] = val;
+      if (d == 0) part_lse[prow] = L > 0.f ? M + log2f(L) : -INFINITY;
+    }
+  }
+}
+
+// Merge split-KV partial results: out = Σ_s 2^(lse_s - M) o_s / Σ_s 2^(lse_s - M).
+// Partials are indexed ((split * n_ctas + item) * kv_heads + kvh) * 16 + row; grid = (items, kv heads).
+template <typename T, int HD>
+__global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict__ part_o,
+                                                         const float* __restrict__ part_lse,
+                                                         const int* __restrict__ items, const int* __restrict__ n_items,
+                                                         const int* __restrict__ qsl, T* __restrict__ out,
+                                                         long out_tok_stride, int hq, int hk, int num_splits) {
+  if ((int)blockIdx.x >= *n_items) return;
+  const int seq = items[blockIdx.x], kvh = blockIdx.y;
+  const int tok0 = qsl[seq], q_len = qsl[seq + 1] - tok0;
+  const int group = hq / hk;
+  const int rows_valid = min(16, q_len * group);
+  for (int idx = threadIdx.x; idx < rows_valid * HD; idx += 128) {
+    int row = idx / HD, d = idx % HD;
+    float M = -INFINITY;
+    for (int s = 0; s < num_splits; ++s)
+      M = fmaxf(M, part_lse[(((long)s * gridDim.x + blockIdx.x) * hk + kvh) * 16 + row]);
+    float W = 0.f, acc = 0.f;
+    if (M != -INFINITY) {
+      for (int s = 0; s < num_splits; ++s) {
+        long prow = (((long)s * gridDim.x + blockIdx.x) * hk + kvh) * 16 + row;
+        float w = exp2f(part_lse[prow] - M);
+        W += w;
+        acc += w * part_o[prow * HD + d];
+      }
+    }
+    int qp = row / group, head = kvh * group + row % group;
+    out[(long)(tok0 + qp) * out_tok_stride + (long)head * HD + d] = from_f<T>(W > 0.f ? acc / W : 0.f);
+  }
+}
+
+// ------------------------------------------------------------------ prefill
+// work[2*i] = sequence, work[2*i+1] = query tile.  64 rows per CTA = 64/group query positions.
+template <typename T, int HD>
+__global__ void __launch_bounds__(128) attn_prefill_kernel(
+    const T* __restrict__ q, long q_tok_stride, const T* __restrict__ cache, const int* __restrict__ block_tables,
+    int bt_stride, const int* __restrict__ seq_lens, const int* __restrict__ qsl, const int* __restrict__ work,
+    const int* __restrict__ n_work, T* __restrict__ out, long out_tok_stride, int hq, int hk, float scale_log2,
+    int window) {
+  if ((int)blockIdx.x >= *n_work) return;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  constexpr int TILE = PAGE * HD * 2;
+  constexpr int KT = 4;                           // pages per kv tile
+  constexpr int STAGE = KT * 2 * TILE;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seq = work[2 * blockIdx.x], qt = work[2 * blockIdx.x + 1], kvh = blockIdx.y;
+  const int ctx = seq_lens[seq], tok0 = qsl[seq], q_len = qsl[seq + 1] - tok0;
+  const int group = hq / hk;
+  const int qpt = 64 / group;                     // query positions per CTA
+  const int qp0 = qt * qpt;
+  uint32_t qf[HD / 16][4];
+  load_q_frags<T, HD>(qf, q, q_tok_stride, tok0, qp0, q_len, kvh, group, warp * 16, lane);
+  int limit[2], lower[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    int qp = qp0 + (warp * 16 + (lane >> 2) + h * 8) / group;
+    limit[h] = qp < q_len ? ctx - q_len + qp : -1;
+    lower[h] = window > 0 ? limit[h] - window + 1 : 0;
+  }
+  const int last_qp = min(q_len, qp0 + qpt) - 1;
+  const int kv_end = ctx - q_len + last_qp + 1;           // keys [kv_begin, kv_end) matter to this CTA
+  int kv_begin = 0;
+  if (window > 0) kv_begin = max(0, ctx - q_len + qp0 - window + 1);
+  const int p_begin = kv_begin / PAGE, p_end = (kv_end + PAGE - 1) / PAGE;
+  const int n_tiles = (p_end - p_begin + KT - 1) / KT;
+  // warp-level causal bound: pages entirely after this warp's last visible key are skipped
+  int warp_last = max(limit[0], limit[1]);
+  warp_last = max(warp_last, __shfl_xor_sync(0xffffffffu, warp_last, 4));
+  warp_last = max(warp_last, __shfl_xor_sync(0xffffffffu, warp_last, 8));
+  warp_last = max(warp_last, __shfl_xor_sync(0xffffffffu, warp_last, 16));
+
+  RowState<HD> st;
+  st.init();
+  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem_raw);
+  const int* bt = block_tables + (long)seq * bt_stride;
+  const long head_off = (long)kvh * PAGE * HD;
+  const long blk_stride = 2L * hk * PAGE * HD;
+  const long v_off = (long)hk * PAGE * HD;
+  auto issue = [&](int t) {
+    if (t < n_tiles) {
+      int p = p_begin + t * KT + warp;              // warp w loads page w of the tile
+      if (p < p_end) {
+        int blk = bt[p];
+        const T* kg = cache + (long)blk * blk_stride + head_off;
+        uint32_t sb = sbase + (t & 1) * STAGE + warp * 2 * TILE;
+        load_page_warp<T, HD>(sb, sb + TILE, kg, kg + v_off, lane);
+      }
+    }
+    cp_async_commit();
+  };
+  issue(0);
+  for (int t = 0; t < n_tiles; ++t) {
+    issue(t + 1);
+    cp_async_wait<1>();
+    __syncthreads();
+#pragma unroll
+    for (int pg = 0; pg < KT; ++pg) {
+      int p = p_begin + t * KT + pg;
+      if (p < p_end && p * PAGE <= warp_last) {
+        uint32_t sb = sbase + (t & 1) * STAGE + pg * 2 * TILE;
+        process_page<T, HD>(st, qf, sb, sb + TILE, p * PAGE, limit, lower, scale_log2, lane);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float l = st.l[h];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    int rrow = warp * 16 + (lane >> 2) + h * 8;
+    int qp = qp0 + rrow / group;
+    if (qp >= q_len) continue;
+    int head = kvh * group + rrow % group;
+    float inv = l > 0.f ? 1.f / l : 0.f;
+    T* dst = out + (long)(tok0 + qp) * out_tok_stride + (long)head * HD + ((lane & 3) << 1);
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt)
+      *reinterpret_cast<uint32_t*>(dst + nt * 8) = pack2<T>(st.o[nt][h * 2] * inv, st.o[nt][h * 2 + 1] * inv);
+  }
+}
+
+template <typename T, int HD>
+int launch_attention(const T* q, long q_tok_stride, const T* cache, const int* bt, int bt_stride, const int* seq_lens,
+                     const int* qsl, const int* dec_items, const int* n_dec, int max_dec, const int* pre_work,
+                     const int* n_pre, int max_pre, T* out, long out_tok_stride, float* part_o, float* part_lse,
+                     int hq, int hk, float scale, int window, int num_splits, int total_rows, cudaStream_t s) {
+  constexpr int NSTAGE = 3;
+  constexpr int TILE = PAGE * HD * 2;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  if (max_dec > 0) {
+    int smem = 4 * NSTAGE * 2 * TILE;
+    int need_merge = 4 * 16 * HD * 4 + 512;
+    if (smem < need_merge) smem = need_merge;
+    auto kern = attn_decode_kernel<T, HD, NSTAGE>;
+    static bool attr_done = false;
+    if (!attr_done) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      attr_done = true;
+    }
+    dim3 grid(max_dec, hk, num_splits);
+    kern<<<grid, 128, smem, s>>>(q, q_tok_stride, cache, bt, bt_stride, seq_lens, qsl, dec_items, n_dec, out,
+                                 out_tok_stride, part_o, part_lse, hq, hk, scale_log2, window, num_splits, total_rows);
+    if (num_splits > 1)
+      attn_merge_kernel<T, HD><<<dim3(max_dec, hk), 128, 0, s>>>(part_o, part_lse, dec_items, n_dec, qsl, out,
+                                                                 out_tok_stride, hq, hk, num_splits);
+  }
+  if (max_pre > 0) {
+    int smem = 2 * 4 * 2 * TILE;
+    auto kern = attn_prefill_kernel<T, HD>;
+    static bool attr_done = false;
+    if (!attr_done) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      attr_done = true;
+    }
+    dim3 grid(max_pre, hk);
+    kern<<<grid, 128, smem, s>>>(q, q_tok_stride, cache, bt, bt_stride, seq_lens, qsl, pre_work, n_pre, out,
+                                 out_tok_stride, hq, hk, scale_log2, window);
+  }
+  return check_launch();
+}
+
+}  // namespace sonar
+
+using namespace sonar;
+
+// counts[0] = number of decode items, counts[1] = number of prefill work entries (device memory, so a
+// captured graph can be replayed with different batch compositions); max_* bound the grids.
+SONAR_API int sonar_paged_attention(const void* q, long q_tok_stride, const void* cache, const int* block_tables,
+                                    int bt_stride, const int* seq_lens, const int* qsl, const int* dec_items,
+                                    int max_dec, const int* pre_work, int max_pre, const int* counts, void* out,
+                                    long out_tok_stride, float* part_o, float* part_lse, int hq, int hk, int head_dim,
+                                    int block_size, float scale, int window, int num_splits, int total_rows, int dtype,
+                                    cudaStream_t s) {
+  if (block_size != PAGE || hq % hk || (64 % (hq / hk)) || hq / hk > 16) return SONAR_BAD_ARG;
+  if (num_splits < 1 || (num_splits > 1 && (!part_o || !part_lse))) return SONAR_BAD_ARG;
+  if (q_tok_stride % 2 || out_tok_stride % 2) return SONAR_BAD_ARG;
+  SONAR_DISPATCH_HALF(dtype, T, {
+    if (head_dim == 128)
+      return launch_attention<T, 128>((const T*)q, q_tok_stride, (const T*)cache, block_tables, bt_stride, seq_lens, qsl,
+                                      dec_items, counts, max_dec, pre_work, counts + 1, max_pre, (T*)out, out_tok_stride,
+                                      part_o, part_lse, hq, hk, scale, window, num_splits, total_rows, s);
+    if (head_dim == 64)
+      return launch_attention<T, 64>((const T*)q, q_tok_stride, (const T*)cache, block_tables, bt_stride, seq_lens, qsl,
+                                     dec_items, counts, max_dec, pre_work, counts + 1, max_pre, (T*)out, out_tok_stride,
+                                     part_o, part_lse, hq, hk, scale, window, num_splits, total_rows, s);
+    return SONAR_BAD_ARG;
+  });
+}

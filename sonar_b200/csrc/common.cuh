@@ -1,0 +1,99 @@
+// Shared device/host helpers for the sonar_b200 kernel library (sm_100a only).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define SONAR_API extern "C" __attribute__((visibility("default")))
+
+// Error codes returned by every entry point (0 = launched).
+enum SonarStatus : int {
+  SONAR_OK = 0,
+  SONAR_BAD_ARG = 1,        // unsupported shape / alignment / dtype
+  SONAR_CUDA_ERROR = 2,     // a CUDA runtime/driver call failed (see sonar_last_cuda_error)
+  SONAR_TOO_LARGE = 3,      // exceeds a compiled-in maximum
+};
+
+// dtype tags shared with the Python binding
+enum SonarDtype : int { SONAR_BF16 = 0, SONAR_F16 = 1, SONAR_F32 = 2, SONAR_FP8E4M3 = 3 };
+
+namespace sonar {
+
+extern int g_last_cuda_error;
+
+inline int check_launch() {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return SONAR_CUDA_ERROR; }
+  return SONAR_OK;
+}
+
+template <typename T> struct Vec8 { uint4 raw; };  // 8 × 16-bit
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum for blocks of up to 1024 threads; `red` is 32 floats of smem.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  int nw = (blockDim.x + 31) >> 5;
+  float t = (threadIdx.x < nw) ? red[threadIdx.x] : 0.f;
+  if (w == 0) { t = warp_sum(t); if (lane == 0) red[0] = t; }
+  __syncthreads();
+  float r = red[0];
+  __syncthreads();
+  return r;
+}
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+
+// 16-byte vector of 8 half-precision values <-> 8 floats
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& raw, float* f) {
+  const T* p = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = to_f<T>(p[i]);
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 raw;
+  T* p = reinterpret_cast<T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) p[i] = from_f<T>(f[i]);
+  return raw;
+}
+
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+}  // namespace sonar
+
+// dispatch on a 16-bit activation dtype tag
+#define SONAR_DISPATCH_HALF(dtype, T, ...)                                   \
+  do {                                                                       \
+    if ((dtype) == SONAR_BF16) { using T = __nv_bfloat16; __VA_ARGS__; }     \
+    else if ((dtype) == SONAR_F16) { using T = __half; __VA_ARGS__; }        \
+    else return SONAR_BAD_ARG;                                               \
+  } while (0)

@@ -1,0 +1,229 @@
+// RMSNorm (+residual), SiLU-and-mul, fused (q/k-norm +) RoPE + paged KV-cache write.
+// All kernels are memory-bound: 16-byte vector accesses, one pass over the data,
+// fp32 math, a row per block (or per warp for per-head work).
+//
+// Behavioural parity with the reference's CUDA ops (not code): rms_norm /
+// fused_add_rms_norm (csrc/libtorch_stable/layernorm_kernels.cu:15,108), act_and_mul
+// (activation_kernels.cu:102), rotary_embedding (pos_encoding_kernels.cu:77),
+// fusedQKNormRope (fused_qknorm_rope_kernel.cu:104), reshape_and_cache_flash
+// (cache_kernels.cu:315) — here RoPE and the cache write are one kernel.
+#include "common.cuh"
+
+namespace sonar {
+int g_last_cuda_error = 0;
+
+// ------------------------------------------------------------------ RMSNorm
+// One block per row.  ADD: residual <- x + residual (rounded to T), normalise that.
+// The row is cached in registers (up to 8 vectors of 8 per thread).
+template <typename T, bool ADD, int VPT>
+__global__ void __launch_bounds__(1024) rms_norm_kernel(const T* __restrict__ x, T* __restrict__ residual,
+                                                        const T* __restrict__ w, T* __restrict__ out,
+                                                        int hidden, long x_stride, long out_stride, float eps) {
+  __shared__ float red[32];
+  const long row = blockIdx.x;
+  const uint4* xv = reinterpret_cast<const uint4*>(x + row * x_stride);
+  uint4* rv = ADD ? reinterpret_cast<uint4*>(residual + row * (long)hidden) : nullptr;
+  const uint4* wv = reinterpret_cast<const uint4*>(w);
+  uint4* ov = reinterpret_cast<uint4*>(out + row * out_stride);
+  const int nvec = hidden >> 3;
+  float vals[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      unpack8<T>(xv[v], vals[i]);
+      if (ADD) {
+        float r[8];
+        unpack8<T>(rv[v], r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vals[i][j] = to_f<T>(from_f<T>(vals[i][j] + r[j]));
+        rv[v] = pack8<T>(vals[i]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      float g[8];
+      unpack8<T>(wv[v], g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) vals[i][j] = vals[i][j] * inv * g[j];
+      ov[v] = pack8<T>(vals[i]);
+    }
+  }
+}
+
+template <typename T, bool ADD>
+int launch_rms_norm(const T* x, T* residual, const T* w, T* out, int rows, int hidden, long x_stride,
+                    long out_stride, float eps, cudaStream_t s) {
+  if (hidden % 8 || rows < 0) return SONAR_BAD_ARG;
+  if (rows == 0) return SONAR_OK;
+  int nvec = hidden / 8;
+  int threads = nvec >= 1024 ? 1024 : ((nvec + 31) / 32) * 32;
+  if (nvec > 256 && nvec <= 512 * 2) threads = ((nvec / 2 + 31) / 32) * 32;  // 2 vectors per thread
+  int vpt = (nvec + threads - 1) / threads;
+  if (vpt <= 1) rms_norm_kernel<T, ADD, 1><<<rows, threads, 0, s>>>(x, residual, w, out, hidden, x_stride, out_stride, eps);
+  else if (vpt <= 2) rms_norm_kernel<T, ADD, 2><<<rows, threads, 0, s>>>(x, residual, w, out, hidden, x_stride, out_stride, eps);
+  else if (vpt <= 4) rms_norm_kernel<T, ADD, 4><<<rows, threads, 0, s>>>(x, residual, w, out, hidden, x_stride, out_stride, eps);
+  else return SONAR_TOO_LARGE;  // hidden > 32768
+  return check_launch();
+}
+
+// ------------------------------------------------------------------ SiLU and mul
+template <typename T>
+__global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int d,
+                                                       long x_stride, long total_vec) {
+  // grid-stride over (row, vec) pairs; x row = [gate(d) | up(d)]
+  const int vec_per_row = d >> 3;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total_vec; i += (long)gridDim.x * blockDim.x) {
+    long row = i / vec_per_row;
+    int v = (int)(i - row * vec_per_row);
+    const uint4* g = reinterpret_cast<const uint4*>(x + row * x_stride) + v;
+    const uint4* u = reinterpret_cast<const uint4*>(x + row * x_stride + d) + v;
+    float a[8], b[8];
+    unpack8<T>(*g, a);
+    unpack8<T>(*u, b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = (a[j] / (1.f + __expf(-a[j]))) * b[j];
+    reinterpret_cast<uint4*>(out + row * (long)d)[v] = pack8<T>(a);
+  }
+}
+
+// ------------------------------------------------------------------ RoPE + cache write
+// One warp per (token, head) over packed qkv rows [q heads | k heads | v heads], head_dim 128
+// or 64 (HD/8 lanes active... we use all 32 lanes with HD/32 elements each, NeoX pairing:
+// element i pairs with i + HD/2).  q heads: optional RMSNorm, rotate, write back in place.
+// k heads: optional RMSNorm, rotate, write to cache (and back in place).  v heads: copy to cache.
+// Cache layout [blocks, 2, kv_heads, block_size, HD]; CT is the cache element type.
+template <typename T, typename CT, int HD>
+__global__ void __launch_bounds__(256) rope_cache_kernel(
+    T* __restrict__ qkv, long row_stride, const long* __restrict__ positions,
+    const float* __restrict__ cos_sin, int rot_dim, CT* __restrict__ cache, const int* __restrict__ slots,
+    int n_tokens, int hq, int hk, int block_size, const T* __restrict__ qw, const T* __restrict__ kw, float eps,
+    float inv_k_scale, float inv_v_scale) {
+  constexpr int EPL = HD / 32;          // elements per lane in each half... lanes hold pairs
+  constexpr int HALF = HD / 2;
+  constexpr int PPL = HALF / 32;        // rotation pairs per lane (HD=128 → 2, HD=64 → 1)
+  (void)EPL;
+  const int heads = hq + 2 * hk;
+  const long warp = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= (long)n_tokens * heads) return;
+  const int tok = (int)(warp / heads), head = (int)(warp % heads);
+  T* p = qkv + (long)tok * row_stride + (long)head * HD;
+  const bool is_q = head < hq, is_k = !is_q && head < hq + hk;
+  float lo[PPL], hi[PPL];
+#pragma unroll
+  for (int i = 0; i < PPL; ++i) {
+    lo[i] = to_f<T>(p[lane * PPL + i]);
+    hi[i] = to_f<T>(p[HALF + lane * PPL + i]);
+  }
+  if (is_q || is_k) {
+    const T* nw = is_q ? qw : kw;
+    if (nw != nullptr) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < PPL; ++i) ss += lo[i] * lo[i] + hi[i] * hi[i];
+      ss = warp_sum(ss);
+      float inv = rsqrtf(ss / (float)HD + eps);
+#pragma unroll
+      for (int i = 0; i < PPL; ++i) {
+        lo[i] = to_f<T>(from_f<T>(lo[i] * inv * to_f<T>(nw[lane * PPL + i])));
+        hi[i] = to_f<T>(from_f<T>(hi[i] * inv * to_f<T>(nw[HALF + lane * PPL + i])));
+      }
+    }
+    const float* cs = cos_sin + positions[tok] * (long)rot_dim;
+    const int rh = rot_dim >> 1;
+#pragma unroll
+    for (int i = 0; i < PPL; ++i) {
+      int j = lane * PPL + i;          // pair index inside the head
+      if (rot_dim == HD) {
+        float c = cs[j], s = cs[rh + j];
+        float a = lo[i], b = hi[i];
+        lo[i] = a * c - b * s;
+        hi[i] = b * c + a * s;
+      }
+    }
+    if (is_q) {
+#pragma unroll
+      for (int i = 0; i < PPL; ++i) {
+        p[lane * PPL + i] = from_f<T>(lo[i]);
+        p[HALF + lane * PPL + i] = from_f<T>(hi[i]);
+      }
+      return;
+    }
+  }
+  if (cache == nullptr) return;
+  const int slot = slots[tok];
+  if (slot < 0) return;
+  const int kvh = is_k ? head - hq : head - hq - hk;
+  const long blk = slot / block_size, off = slot % block_size;
+  CT* dst = cache + (((blk * 2 + (is_k ? 0 : 1)) * hk + kvh) * block_size + off) * HD;
+  const float sc = is_k ? inv_k_scale : inv_v_scale;
+#pragma unroll
+  for (int i = 0; i < PPL; ++i) {
+    if constexpr (sizeof(CT) == 1) {
+      dst[lane * PPL + i] = CT(lo[i] * sc);
+      dst[HALF + lane * PPL + i] = CT(hi[i] * sc);
+    } else {
+      dst[lane * PPL + i] = from_f<CT>(lo[i]);
+      dst[HALF + lane * PPL + i] = from_f<CT>(hi[i]);
+    }
+  }
+}
+
+}  // namespace sonar
+
+using namespace sonar;
+
+SONAR_API int sonar_last_cuda_error() { return g_last_cuda_error; }
+
+SONAR_API int sonar_rms_norm(const void* x, void* residual, const void* w, void* out, int rows, int hidden,
+                             long x_stride, long out_stride, float eps, int dtype, cudaStream_t s) {
+  SONAR_DISPATCH_HALF(dtype, T, {
+    if (residual) return launch_rms_norm<T, true>((const T*)x, (T*)residual, (const T*)w, (T*)out, rows, hidden, x_stride, out_stride, eps, s);
+    return launch_rms_norm<T, false>((const T*)x, nullptr, (const T*)w, (T*)out, rows, hidden, x_stride, out_stride, eps, s);
+  });
+}
+
+SONAR_API int sonar_silu_and_mul(const void* x, void* out, int rows, int d, long x_stride, int dtype, cudaStream_t s) {
+  if (d % 8) return SONAR_BAD_ARG;
+  if (rows == 0) return SONAR_OK;
+  long total = (long)rows * (d / 8);
+  int blocks = (int)((total + 255) / 256 < 148L * 16 ? (total + 255) / 256 : 148L * 16);
+  SONAR_DISPATCH_HALF(dtype, T, {
+    silu_mul_kernel<T><<<blocks, 256, 0, s>>>((const T*)x, (T*)out, d, x_stride, total);
+    return check_launch();
+  });
+}
+
+SONAR_API int sonar_rope_and_cache(void* qkv, long row_stride, const long* positions, const float* cos_sin,
+                                   int rot_dim, void* cache, const int* slots, int n_tokens, int hq, int hk,
+                                   int head_dim, int block_size, const void* qw, const void* kw, float eps,
+                                   float k_scale, float v_scale, int dtype, int cache_dtype, cudaStream_t s) {
+  if (n_tokens == 0) return SONAR_OK;
+  if (rot_dim != head_dim) return SONAR_BAD_ARG;  // partial rotary is not built yet
+  long warps = (long)n_tokens * (hq + 2 * hk);
+  int blocks = (int)((warps + 7) / 8);
+#define LAUNCH(T, CT, HD)                                                                               \
+  rope_cache_kernel<T, CT, HD><<<blocks, 256, 0, s>>>((T*)qkv, row_stride, positions, cos_sin, rot_dim,  \
+      (CT*)cache, slots, n_tokens, hq, hk, block_size, (const T*)qw, (const T*)kw, eps, 1.f / k_scale,   \
+      1.f / v_scale)
+  SONAR_DISPATCH_HALF(dtype, T, {
+    if (cache_dtype == SONAR_FP8E4M3) {
+      if (head_dim == 128) LAUNCH(T, __nv_fp8_e4m3, 128); else if (head_dim == 64) LAUNCH(T, __nv_fp8_e4m3, 64);
+      else return SONAR_BAD_ARG;
+    } else if (cache_dtype == dtype) {
+      if (head_dim == 128) LAUNCH(T, T, 128); else if (head_dim == 64) LAUNCH(T, T, 64);
+      else return SONAR_BAD_ARG;
+    } else return SONAR_BAD_ARG;
+    return check_launch();
+  });
+#undef LAUNCH
+}

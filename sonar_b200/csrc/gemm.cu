@@ -1,0 +1,428 @@
+// Persistent warp-specialised tcgen05 GEMM:  C[M,N] = A[M,K] · B[N,K]^T (+ bias), 16-bit inputs, fp32
+// accumulation in TMEM, 16-bit or fp32 output.
+//
+// One CTA per SM loops over 128×BN output tiles (BN ∈ {64,128,256}).  Warp 0 is the TMA producer (one
+// elected lane issues 128-byte-swizzled tile loads of A and B into a multi-stage shared-memory ring),
+// warp 1 allocates TMEM and issues tcgen05.mma (UMMA 128×BN×16, four per 64-wide K block), committing
+// each stage's completion to the ring's "empty" barrier and each tile's to a "tmem full" barrier;
+// warps 2-5 are the epilogue: tcgen05.ld the accumulator (two TMEM buffers, so the next tile's
+// mainloop overlaps this tile's epilogue), convert and store.
+//
+// Two optional collective hooks make this the tensor-parallel kernel as well:
+//  * row_ready: before loading A rows of a 128-row block the producer waits (bounded) until the
+//    block's arrival counter, which peers bump after pushing those rows into this GPU's gather
+//    buffer, reaches `ready_target` — the all-gather overlaps the GEMM block by block.  Loads are
+//    plain TMA from local memory.
+//  * scatter epilogue: output rows are split in `n_dst` contiguous shards of `rows_per_dst` rows;
+//    shard d is stored through dst_ptrs[d] (a peer mapping of rank d's partial buffer, slot = this
+//    rank), so every rank receives the partial products of its own token rows as they are produced —
+//    the push half of a reduce-scatter; a counter per destination is bumped when a tile lands.
+//
+// Baselines this replaces: cuBLAS via F.linear (reference layers/utils.py:86) and the async-TP
+// decomposition into library GEMMs + copies (reference compilation/passes/fusion/collective_fusion.py:327-388).
+#include <mutex>
+#include <unordered_map>
+
+#include "tcgen05.cuh"
+
+namespace sonar {
+
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+int make_tmap_2d(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                 uint32_t box_cols, int elem_bytes) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return SONAR_CUDA_ERROR;
+  if (((uintptr_t)ptr & 15) || ((ld * elem_bytes) & 15) || box_cols * elem_bytes != 128 || box_rows > 256)
+    return SONAR_BAD_ARG;
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstride[1] = {ld * (uint64_t)elem_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { g_last_cuda_error = (int)r; return SONAR_CUDA_ERROR; }
+  return SONAR_OK;
+}
+
+namespace {
+
+constexpr int BM = 128, BK = 64;
+constexpr int NUM_THREADS = 192;
+
+struct GemmParams {
+  int M, N, K;
+  void* C;            // plain epilogue destination
+  long ldc;
+  const void* bias;   // [N] or null (same dtype as C when C is 16-bit, fp32 when C is fp32)
+  int* err;           // device error word
+  // all-gather hook
+  const int* row_ready;   // [ceil(M/128)] arrival counters, or null
+  int ready_target;
+  // scatter hook
+  void* const* dst_ptrs;  // [n_dst] device array of destination bases, or null
+  int rows_per_dst;
+  int* const* done_ctr;   // [n_dst] counters at the destinations (bumped once per tile per dst), or null
+};
+
+template <int BN> struct Cfg {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <typename OutT>
+__device__ __forceinline__ void store32(OutT* dst, const uint32_t* v, const OutT* bias, int ncols_ok);
+
+template <>
+__device__ __forceinline__ void store32<float>(float* dst, const uint32_t* v, const float* bias, int ncols_ok) {
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    if (g * 4 + 4 <= ncols_ok) {
+      float4 o;
+      o.x = __uint_as_float(v[g * 4 + 0]); o.y = __uint_as_float(v[g * 4 + 1]);
+      o.z = __uint_as_float(v[g * 4 + 2]); o.w = __uint_as_float(v[g * 4 + 3]);
+      if (bias) { o.x += bias[g * 4]; o.y += bias[g * 4 + 1]; o.z += bias[g * 4 + 2]; o.w += bias[g * 4 + 3]; }
+      *reinterpret_cast<float4*>(dst + g * 4) = o;
+    }
+  }
+}
+template <typename OutT>
+__device__ __forceinline__ void store32(OutT* dst, const uint32_t* v, const OutT* bias, int ncols_ok) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    if (g * 8 + 8 <= ncols_ok) {
+      float f[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        f[i] = __uint_as_float(v[g * 8 + i]);
+        if (bias) f[i] += to_f<OutT>(bias[g * 8 + i]);
+      }
+      *reinterpret_cast<uint4*>(dst + g * 8) = pack8<OutT>(f);
+    }
+  }
+}
+
+template <int BN, typename OutT, int AB_FMT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                    const GemmParams p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_dyn[];
+  const uint32_t smem0 = (tc::smem_u32(smem_dyn) + 1023u) & ~1023u;
+  uint8_t* smem_al = smem_dyn + (smem0 - tc::smem_u32(smem_dyn));
+  // barrier block after the ring
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + C::STAGES * C::STAGE_BYTES);
+  const uint32_t bar0 = smem0 + C::STAGES * C::STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (C::STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * C::STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * C::STAGES + 2 + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) { tc::mbar_init(full_bar(s), 1); tc::mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { tc::mbar_init(tfull_bar(b), 1); tc::mbar_init(tempty_bar(b), 128); }
+    *abort_flag = 0;
+    tc::mbar_fence_init();
+  }
+  if (warp == 1) tc::tmem_alloc(tc::smem_u32(tmem_slot), C::TMEM_COLS);
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tc::tma_prefetch_desc(&tma_a);
+      tc::tma_prefetch_desc(&tma_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m_idx = tile % num_m, n_idx = tile / num_m;
+        if (p.row_ready != nullptr) {
+          // bounded wait for the peers' rows of this block (plain loads of a local counter)
+          const int* ctr = p.row_ready + m_idx;
+          auto peek = [&]() {
+            int v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
+            return v;
+          };
+          if (peek() < p.ready_target) {
+            const uint64_t t0 = globaltimer_ns();
+            uint32_t spins = 0;
+            while (peek() < p.ready_target) {
+              if ((++spins & 63u) == 0) {
+                if (*abort_flag) { ok = false; break; }
+                if (globaltimer_ns() - t0 > tc::WAIT_LIMIT_NS) {
+                  *abort_flag = 1;
+                  if (p.err) atomicCAS(p.err, 0, tc::SITE_FLAG | (blockIdx.x << 8));
+                  ok = false;
+                  break;
+                }
+              }
+            }
+            if (!ok) break;
+          }
+          // the acquire above orders the peers' row stores before the TMA (async proxy) reads below
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1;
+          if (!tc::mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.err, tc::SITE_EMPTY)) { ok = false; break; }
+          tc::mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+          const uint32_t a_dst = smem0 + s * C::STAGE_BYTES;
+          tc::tma_load_2d(a_dst, &tma_a, full_bar(s), kb * BK, m_idx * BM);
+          tc::tma_load_2d(a_dst + C::A_BYTES, &tma_b, full_bar(s), kb * BK, n_idx * BN);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc::make_idesc_f16(BM, BN, AB_FMT);
+      uint32_t it = 0, t_local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t_local) {
+        const int buf = t_local & 1;
+        const uint32_t bph = (t_local >> 1) & 1;
+        if (!tc::mbar_wait(tempty_bar(buf), bph ^ 1, abort_flag, p.err, tc::SITE_TMEM_EMPTY)) break;
+        tc::fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1;
+          if (!tc::mbar_wait(full_bar(s), ph, abort_flag, p.err, tc::SITE_FULL)) { ok = false; break; }
+          tc::fence_after_sync();
+          const uint32_t a_addr = smem0 + s * C::STAGE_BYTES;
+          const uint64_t adesc = tc::make_smem_desc_sw128(a_addr);
+          const uint64_t bdesc = tc::make_smem_desc_sw128(a_addr + C::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // +32 bytes per 16-element K step inside the 128-byte swizzled row
+            tc::mma_f16(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+          }
+          tc::mma_commit(empty_bar(s));
+        }
+        if (ok) tc::mma_commit(tfull_bar(buf));
+      }
+    }
+  } else {
+    // ------------------------------------------------ epilogue (warps 2..5 ↔ TMEM lane groups 2,3,0,1)
+    const int lane_grp = warp & 3;
+    uint32_t t_local = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t_local) {
+      const int m_idx = tile % num_m, n_idx = tile / num_m;
+      const int buf = t_local & 1;
+      const uint32_t bph = (t_local >> 1) & 1;
+      if (!tc::mbar_wait(tfull_bar(buf), bph, abort_flag, p.err, tc::SITE_TMEM_FULL)) break;
+      tc::fence_after_sync();
+      const int row = m_idx * BM + lane_grp * 32 + lane;
+      const int n0 = n_idx * BN;
+      OutT* crow = nullptr;
+      if (row < p.M) {
+        if (p.dst_ptrs != nullptr) {
+          const int d = row / p.rows_per_dst;
+          crow = reinterpret_cast<OutT*>(p.dst_ptrs[d]) + (long)(row - d * p.rows_per_dst) * p.ldc;
+        } else {
+          crow = reinterpret_cast<OutT*>(p.C) + (long)row * p.ldc;
+        }
+      }
+      const uint32_t t_row = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tc::tmem_ld32(t_row + c * 32, v);
+        tc::tmem_ld_wait();
+        const int col = n0 + c * 32;
+        if (crow != nullptr && col < p.N) {
+          const OutT* b = p.bias ? reinterpret_cast<const OutT*>(p.bias) + col : nullptr;
+          store32<OutT>(crow + col, v, b, min(32, p.N - col));
+        }
+      }
+      tc::fence_before_sync();
+      tc::mbar_arrive(tempty_bar(buf));
+      if (p.done_ctr != nullptr) {
+        // publish: every lane fences its stores, then one release-increment per warp per destination
+        // the tile touches (a destination expects 4 × its overlapping tiles)
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const int r_lo = m_idx * BM, r_hi = min(p.M, r_lo + BM) - 1;
+          for (int d = r_lo / p.rows_per_dst; d <= r_hi / p.rows_per_dst; ++d)
+            asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(p.done_ctr[d]) : "memory");
+        }
+      }
+    }
+  }
+  // ---- teardown: everyone meets here, also after an abort
+  tc::fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies already in flight time to land before shared memory is released
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+struct MapKey {
+  const void* ptr; uint64_t rows, cols, ld; uint32_t box_rows; int eb;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows && eb == o.eb;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = (size_t)k.ptr;
+    h = h * 1000003u ^ k.rows; h = h * 1000003u ^ k.cols; h = h * 1000003u ^ k.ld;
+    h = h * 1000003u ^ k.box_rows; h = h * 1000003u ^ (size_t)k.eb;
+    return h;
+  }
+};
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+std::mutex g_maps_mu;
+
+int cached_tmap(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows, int eb) {
+  MapKey k{ptr, rows, cols, ld, box_rows, eb};
+  std::lock_guard<std::mutex> g(g_maps_mu);
+  auto it = g_maps.find(k);
+  if (it != g_maps.end()) { *out = it->second; return SONAR_OK; }
+  CUtensorMap m;
+  int rc = make_tmap_2d(&m, ptr, rows, cols, ld, box_rows, 128 / eb, eb);
+  if (rc != SONAR_OK) return rc;
+  if (g_maps.size() > 65536) g_maps.clear();
+  g_maps.emplace(k, m);
+  *out = m;
+  return SONAR_OK;
+}
+
+int g_num_sms = 0;
+int num_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+// Tile width by a small cost model: waves × per-tile time, where a 128×BN×64 block costs
+// max(tensor time ∝ BN, shared-memory operand traffic ∝ 128+BN).
+int pick_bn(int M, int N) {
+  const int sms = num_sms();
+  const int num_m = (M + BM - 1) / BM;
+  int best = 64;
+  double best_cost = 1e30;
+  for (int bn : {256, 128, 64}) {
+    int tiles = num_m * ((N + bn - 1) / bn);
+    int waves = (tiles + sms - 1) / sms;
+    double per_tile = bn > (128 + bn) * 0.5 ? (double)bn : (128 + bn) * 0.5;
+    double cost = waves * per_tile;
+    if (cost < best_cost - 1e-9) { best_cost = cost; best = bn; }
+  }
+  return best;
+}
+
+template <int BN, typename OutT, int AB_FMT>
+int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t s) {
+  using C = Cfg<BN>;
+  auto kern = gemm_tcgen05_kernel<BN, OutT, AB_FMT>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
+      return check_launch();
+    attr_done = true;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < num_sms() ? tiles : num_sms();
+  kern<<<grid, NUM_THREADS, C::SMEM, s>>>(ta, tb, p);
+  return check_launch();
+}
+
+template <typename OutT, int AB_FMT>
+int launch_bn(int bn, const void* A, const void* B, const GemmParams& p, long lda, long ldb, cudaStream_t s) {
+  CUtensorMap ta, tb;
+  int rc = cached_tmap(&ta, A, p.M, p.K, lda, BM, 2);
+  if (rc != SONAR_OK) return rc;
+  rc = cached_tmap(&tb, B, p.N, p.K, ldb, bn, 2);
+  if (rc != SONAR_OK) return rc;
+  if (bn == 256) return launch_cfg<256, OutT, AB_FMT>(ta, tb, p, s);
+  if (bn == 128) return launch_cfg<128, OutT, AB_FMT>(ta, tb, p, s);
+  return launch_cfg<64, OutT, AB_FMT>(ta, tb, p, s);
+}
+
+}  // namespace
+}  // namespace sonar
+
+using namespace sonar;
+
+// C = A · B^T (+ bias).  in_dtype: bf16/f16 for A and B; out_dtype: same 16-bit type or fp32.
+// Requirements: K % 8 == 0 (16-byte row pitch), N % 8 == 0 (N % 4 for fp32 out), 16-byte aligned bases.
+// err: optional device int that receives a wait-site code if a pipeline wait timed out.
+SONAR_API int sonar_gemm(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long lda,
+                         long ldb, long ldc, int in_dtype, int out_dtype, int force_bn, int* err, cudaStream_t s) {
+  if (M <= 0 || N <= 0 || K <= 0) return M == 0 ? SONAR_OK : SONAR_BAD_ARG;
+  if (K % 8 || lda % 8 || ldb % 8) return SONAR_BAD_ARG;
+  if ((out_dtype == SONAR_F32 ? (N % 4 || ldc % 4) : (N % 8 || ldc % 8)) || ((uintptr_t)C & 15)) return SONAR_BAD_ARG;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.bias = bias; p.err = err;
+  const int bn = force_bn ? force_bn : pick_bn(M, N);
+  if (bn != 64 && bn != 128 && bn != 256) return SONAR_BAD_ARG;
+  if (in_dtype == SONAR_BF16) {
+    if (out_dtype == SONAR_BF16) return launch_bn<__nv_bfloat16, 1>(bn, A, B, p, lda, ldb, s);
+    if (out_dtype == SONAR_F32) return launch_bn<float, 1>(bn, A, B, p, lda, ldb, s);
+  } else if (in_dtype == SONAR_F16) {
+    if (out_dtype == SONAR_F16) return launch_bn<__half, 0>(bn, A, B, p, lda, ldb, s);
+    if (out_dtype == SONAR_F32) return launch_bn<float, 0>(bn, A, B, p, lda, ldb, s);
+  }
+  return SONAR_BAD_ARG;
+}
+
+// Tensor-parallel variant (bf16 only).  row_ready/ready_target: all-gather hook; dst_ptrs/rows_per_dst/
+// done_ctr: scatter epilogue (see the file header).  Either hook may be null.
+SONAR_API int sonar_gemm_tp(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc,
+                            const int* row_ready, int ready_target, void* const* dst_ptrs, int rows_per_dst,
+                            int* const* done_ctr, int force_bn, int* err, cudaStream_t s) {
+  if (M <= 0 || N <= 0 || K <= 0) return M == 0 ? SONAR_OK : SONAR_BAD_ARG;
+  if (K % 8 || lda % 8 || ldb % 8 || N % 8 || ldc % 8) return SONAR_BAD_ARG;
+  if (dst_ptrs != nullptr && rows_per_dst <= 0) return SONAR_BAD_ARG;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.err = err;
+  p.row_ready = row_ready; p.ready_target = ready_target;
+  p.dst_ptrs = dst_ptrs; p.rows_per_dst = rows_per_dst; p.done_ctr = done_ctr;
+  const int bn = force_bn ? force_bn : pick_bn(M, N);
+  return launch_bn<__nv_bfloat16, 1>(bn, A, B, p, lda, ldb, s);
+}
+
+SONAR_API int sonar_gemm_pick_bn(int M, int N) { return pick_bn(M, N); }

@@ -1,0 +1,106 @@
+"""Builds the kernel library ``sonar_b200/_C.so`` from ``sonar_b200/csrc/*.cu``.
+
+Plain ``nvcc`` (no torch headers, so each file compiles in seconds), sm_100a
+only, objects cached under ``build/`` by source hash.  The library exports C
+symbols (``sonar_*``) that ``sonar_b200.ops.cuda`` binds with ctypes.
+
+    python -m sonar_b200.ops.build [--force] [--verbose]
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+
+PKG_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+SRC_DIR = os.path.join(PKG_DIR, "csrc")
+ROOT = os.path.dirname(PKG_DIR)
+BUILD_DIR = os.path.join(ROOT, "build", "sonar_b200_C")
+LIB_PATH = os.path.join(PKG_DIR, "_C.so")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+]
+
+
+def find_nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found (set NVCC or add it to PATH)")
+
+
+def sources() -> list[str]:
+    return sorted(os.path.join(SRC_DIR, f) for f in os.listdir(SRC_DIR) if f.endswith(".cu"))
+
+
+def _digest(path: str, headers_digest: str) -> str:
+    h = hashlib.sha256()
+    h.update(headers_digest.encode())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    with open(path, "rb") as f:
+        h.update(f.read())
+    return h.hexdigest()[:16]
+
+
+def _headers_digest() -> str:
+    h = hashlib.sha256()
+    for f in sorted(os.listdir(SRC_DIR)):
+        if f.endswith((".cuh", ".h")):
+            with open(os.path.join(SRC_DIR, f), "rb") as fh:
+                h.update(fh.read())
+    return h.hexdigest()
+
+
+def build_extension(force: bool = False, verbose: bool = False) -> str:
+    nvcc = find_nvcc()
+    os.makedirs(BUILD_DIR, exist_ok=True)
+    hd = _headers_digest()
+    jobs = []
+    objs = []
+    for src in sources():
+        obj = os.path.join(BUILD_DIR, f"{os.path.basename(src)[:-3]}.{_digest(src, hd)}.o")
+        objs.append(obj)
+        if force or not os.path.exists(obj):
+            jobs.append((src, obj))
+    stamp = os.path.join(BUILD_DIR, "link.stamp")
+    want = "\n".join(objs)
+    if not jobs and os.path.exists(LIB_PATH) and os.path.exists(stamp) and open(stamp).read() == want:
+        return LIB_PATH
+
+    def compile_one(job):
+        src, obj = job
+        cmd = [nvcc, *NVCC_FLAGS, "-I", SRC_DIR, "-c", src, "-o", obj]
+        if verbose:
+            cmd.insert(1, "-Xptxas=-v")
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"nvcc failed for {src}:\n{res.stderr}")
+        if verbose:
+            sys.stderr.write(res.stderr)
+        return obj
+
+    with cf.ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as ex:
+        list(ex.map(compile_one, jobs))
+    res = subprocess.run([nvcc, "-shared", "-o", LIB_PATH, *objs, "-gencode", "arch=compute_100a,code=sm_100a"],
+                         capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"link failed:\n{res.stderr}")
+    with open(stamp, "w") as f:
+        f.write(want)
+    # drop objects of older source versions
+    keep = set(objs)
+    for f in os.listdir(BUILD_DIR):
+        p = os.path.join(BUILD_DIR, f)
+        if f.endswith(".o") and p not in keep:
+            os.remove(p)
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    path = build_extension(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    print(path)

@@ -1,0 +1,315 @@
+"""ctypes binding of the sm_100a kernel library (``sonar_b200/_C.so``).
+
+Importing this module loads the library and fails loudly if it is missing —
+there is no silent PyTorch fallback on a GPU machine.  Every wrapper launches
+on the current torch CUDA stream, takes/returns torch tensors and raises on a
+non-zero status from the C entry point.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_long, c_uint, c_void_p
+
+import numpy as np
+import torch
+
+from sonar_b200.ops import torch_ref as ref
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_C.so")
+if not os.path.exists(_LIB_PATH):
+    raise ImportError(
+        f"kernel library {_LIB_PATH} is missing: build it with `python -m sonar_b200.ops.build` "
+        "(CUDA tensors are never routed to a PyTorch fallback)")
+lib = ctypes.CDLL(_LIB_PATH)
+
+BF16, F16, F32, FP8 = 0, 1, 2, 3
+_DT = {torch.bfloat16: BF16, torch.float16: F16, torch.float32: F32, torch.float8_e4m3fn: FP8}
+_STATUS = {1: "bad argument (shape/alignment/dtype unsupported)", 2: "CUDA error", 3: "size exceeds kernel limit"}
+
+launch_count = 0   # kernels launched through this binding (bench.py reports it)
+
+
+def _sig(name, *argtypes):
+    fn = getattr(lib, name)
+    fn.argtypes = list(argtypes)
+    fn.restype = c_int
+    return fn
+
+
+_rms_norm = _sig("sonar_rms_norm", c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_long, c_long, c_float,
+                 c_int, c_void_p)
+_silu = _sig("sonar_silu_and_mul", c_void_p, c_void_p, c_int, c_int, c_long, c_int, c_void_p)
+_rope = _sig("sonar_rope_and_cache", c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+             c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_float, c_int, c_int, c_void_p)
+_attn = _sig("sonar_paged_attention", c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+             c_int, c_void_p, c_int, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+             c_float, c_int, c_int, c_int, c_int, c_void_p)
+_gemm = _sig("sonar_gemm", c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_long,
+             c_int, c_int, c_int, c_void_p, c_void_p)
+_gemm_tp = _sig("sonar_gemm_tp", c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_long,
+                c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p)
+_argmax = _sig("sonar_argmax", c_void_p, c_long, c_int, c_int, c_void_p, c_void_p)
+_sample = _sig("sonar_sample", c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+               c_long, c_void_p, c_uint, c_void_p, c_void_p)
+lib.sonar_last_cuda_error.restype = c_int
+lib.sonar_gemm_pick_bn.argtypes = [c_int, c_int]
+lib.sonar_gemm_pick_bn.restype = c_int
+
+
+def _check(rc: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
+    if rc != 0:
+        extra = f" (cudaError {lib.sonar_last_cuda_error()})" if rc == 2 else ""
+        raise RuntimeError(f"{what}: {_STATUS.get(rc, rc)}{extra}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+# ---------------------------------------------------------------- device error word
+_err_words: dict[int, torch.Tensor] = {}
+
+
+def error_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 that pipeline kernels write when a bounded wait gives up."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _err_words:
+        _err_words[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _err_words[idx]
+
+
+def check_device_errors(device: torch.device | None = None) -> None:
+    """Synchronising check: raise if any kernel recorded a wait timeout."""
+    for idx, w in _err_words.items():
+        v = int(w.item())
+        if v:
+            w.zero_()
+            sites = {1: "smem ring (empty)", 2: "smem ring (full)", 3: "tmem full", 4: "tmem empty", 5: "peer flag"}
+            raise RuntimeError(f"cuda:{idx}: kernel wait timed out at {sites.get(v & 255, v & 255)} "
+                               f"(block {v >> 8})")
+
+
+# ---------------------------------------------------------------- norms / activations
+def rms_norm(x, weight, eps, out=None):
+    assert x.dim() == 2 and x.stride(1) == 1
+    if out is None:
+        out = torch.empty((x.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
+    _check(_rms_norm(x.data_ptr(), None, weight.data_ptr(), out.data_ptr(), x.shape[0], x.shape[1], x.stride(0),
+                     out.stride(0), eps, _DT[x.dtype], _stream()), "rms_norm")
+    return out
+
+
+def fused_add_rms_norm(x, residual, weight, eps):
+    assert x.dim() == 2 and x.is_contiguous() and residual.is_contiguous()
+    _check(_rms_norm(x.data_ptr(), residual.data_ptr(), weight.data_ptr(), x.data_ptr(), x.shape[0], x.shape[1],
+                     x.stride(0), x.stride(0), eps, _DT[x.dtype], _stream()), "fused_add_rms_norm")
+    return x, residual
+
+
+def silu_and_mul(x, out=None):
+    assert x.dim() == 2 and x.stride(1) == 1
+    d = x.shape[1] // 2
+    if out is None:
+        out = torch.empty((x.shape[0], d), dtype=x.dtype, device=x.device)
+    _check(_silu(x.data_ptr(), out.data_ptr(), x.shape[0], d, x.stride(0), _DT[x.dtype], _stream()), "silu_and_mul")
+    return out
+
+
+def rope_and_cache(qkv, positions, cos_sin, kv_cache, slot_mapping, hq, hk, head_dim, q_w, k_w, eps, k_scale, v_scale):
+    assert qkv.stride(1) == 1 and positions.dtype == torch.int64 and slot_mapping.dtype == torch.int32
+    bs = kv_cache.shape[3] if kv_cache is not None else 16
+    cdt = _DT[kv_cache.dtype] if kv_cache is not None else _DT[qkv.dtype]
+    _check(_rope(qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), cos_sin.data_ptr(), cos_sin.shape[1],
+                 _ptr(kv_cache), slot_mapping.data_ptr(), qkv.shape[0], hq, hk, head_dim, bs, _ptr(q_w), _ptr(k_w),
+                 eps, k_scale, v_scale, _DT[qkv.dtype], cdt, _stream()), "rope_and_cache")
+
+
+# ---------------------------------------------------------------- attention
+class AttentionWork:
+    """Device-side work lists of one step, shared by all layers."""
+    __slots__ = ("dec_items", "pre_work", "counts", "n_dec", "n_pre", "num_splits", "part_o", "part_lse")
+
+
+class _AttnBuffers:
+    def __init__(self, device, max_seqs: int, max_tokens: int) -> None:
+        self.max_dec = max_seqs
+        self.max_pre = max_tokens + max_seqs
+        pin = True
+        self.h_dec = torch.zeros(self.max_dec, dtype=torch.int32, pin_memory=pin)
+        self.h_pre = torch.zeros(self.max_pre * 2, dtype=torch.int32, pin_memory=pin)
+        self.h_counts = torch.zeros(2, dtype=torch.int32, pin_memory=pin)
+        self.d_dec = torch.zeros(self.max_dec, dtype=torch.int32, device=device)
+        self.d_pre = torch.zeros(self.max_pre * 2, dtype=torch.int32, device=device)
+        self.d_counts = torch.zeros(2, dtype=torch.int32, device=device)
+        self.part_o = None
+        self.part_lse = None
+
+
+_attn_buffers: dict[int, _AttnBuffers] = {}
+MAX_SPLIT_CTAS = 1024
+
+
+def build_attention_work(meta, runner=None, group: int | None = None, num_kv_heads: int | None = None) -> None:
+    """Classify this step's sequences into decode items (q_len·group ≤ 16 rows) and
+    prefill tiles (64 rows each) and upload the lists; picks the KV split count."""
+    dev = meta.seq_lens.device
+    if group is None:
+        attn = runner.model.attention_layers()[0]
+        group, num_kv_heads = attn.num_heads // attn.num_kv_heads, attn.num_kv_heads
+    key = dev.index or 0
+    buf = _attn_buffers.get(key)
+    need_seqs, need_toks = meta.seq_lens.shape[0], max(int(meta.num_tokens), 1)
+    if buf is None or buf.max_dec < need_seqs or buf.max_pre < need_toks + need_seqs:
+        ms = runner.max_seqs if runner is not None else need_seqs
+        mt = runner.max_tokens if runner is not None else need_toks
+        buf = _attn_buffers[key] = _AttnBuffers(dev, max(ms, need_seqs), max(mt, need_toks))
+    q_lens = np.asarray(meta.query_lens_cpu, dtype=np.int64)
+    ns = len(q_lens)
+    is_dec = q_lens * group <= 16
+    dec = np.nonzero(is_dec & (q_lens > 0))[0].astype(np.int32)
+    pre_seqs = np.nonzero(~is_dec)[0]
+    qpt = 64 // group
+    n_tiles = (q_lens[pre_seqs] + qpt - 1) // qpt
+    n_pre = int(n_tiles.sum())
+    n_dec = len(dec)
+    w = AttentionWork()
+    if n_dec:
+        buf.h_dec.numpy()[:n_dec] = dec
+        buf.d_dec[:n_dec].copy_(buf.h_dec[:n_dec], non_blocking=True)
+    if n_pre:
+        seq_of = np.repeat(pre_seqs, n_tiles)
+        first = np.cumsum(n_tiles) - n_tiles
+        tile_of = np.arange(n_pre) - np.repeat(first, n_tiles)
+        hp = buf.h_pre.numpy()
+        hp[0:2 * n_pre:2] = seq_of
+        hp[1:2 * n_pre:2] = tile_of
+        buf.d_pre[:2 * n_pre].copy_(buf.h_pre[:2 * n_pre], non_blocking=True)
+    buf.h_counts[0], buf.h_counts[1] = n_dec, n_pre
+    buf.d_counts.copy_(buf.h_counts, non_blocking=True)
+    # split long contexts when the decode grid alone cannot fill the GPU
+    splits = 1
+    if n_dec and n_dec * num_kv_heads < 2 * 148:
+        seq_lens = np.asarray(meta.seq_lens_cpu)
+        max_pages = int(-(-seq_lens[dec].max() // 16))
+        splits = int(min(-(-2 * 148 // (n_dec * num_kv_heads)), max(1, max_pages // 8), 32,
+                         MAX_SPLIT_CTAS // (n_dec * num_kv_heads)))
+        splits = max(splits, 1)
+    if splits > 1 and buf.part_o is None:
+        buf.part_o = torch.empty(MAX_SPLIT_CTAS * 16 * 128, dtype=torch.float32, device=dev)
+        buf.part_lse = torch.empty(MAX_SPLIT_CTAS * 16, dtype=torch.float32, device=dev)
+    w.dec_items, w.pre_work, w.counts = buf.d_dec, buf.d_pre, buf.d_counts
+    w.n_dec, w.n_pre, w.num_splits = n_dec, n_pre, splits
+    w.part_o, w.part_lse = buf.part_o, buf.part_lse
+    meta.work = w
+
+
+def paged_attention(q, kv_cache, meta, scale, sliding_window=None, k_scale=1.0, v_scale=1.0, out=None):
+    """q: [T, Hq, D] view with unit inner stride and head stride D (e.g. a slice of packed qkv)."""
+    t, hq, d = q.shape
+    assert q.stride(2) == 1 and q.stride(1) == d
+    if kv_cache.dtype != q.dtype:
+        raise NotImplementedError("fp8 KV cache attention kernel is not built yet")
+    hk = kv_cache.shape[2]
+    if meta.work is None:
+        build_attention_work(meta, None, hq // hk, hk)
+    w = meta.work
+    if out is None:
+        out = torch.empty((t, hq * d), dtype=q.dtype, device=q.device)
+    _check(_attn(q.data_ptr(), q.stride(0), kv_cache.data_ptr(), meta.block_tables.data_ptr(),
+                 meta.block_tables.stride(0), meta.seq_lens.data_ptr(), meta.query_start_loc.data_ptr(),
+                 w.dec_items.data_ptr(), w.n_dec, w.pre_work.data_ptr(), w.n_pre, w.counts.data_ptr(),
+                 out.data_ptr(), out.stride(0), _ptr(w.part_o), _ptr(w.part_lse), hq, hk, d, kv_cache.shape[3],
+                 scale, sliding_window or 0, w.num_splits, 0, _DT[q.dtype], _stream()), "paged_attention")
+    return out
+
+
+def merge_attn_states(o1, lse1, o2, lse2):
+    return ref.merge_attn_states(o1, lse1, o2, lse2)
+
+
+# ---------------------------------------------------------------- GEMM
+def gemm(x, w, bias=None, out=None, out_dtype=None, force_bn: int = 0):
+    """y = x @ w.T (+ bias) on the tcgen05 kernel; x [M, K], w [N, K], 16-bit, unit inner strides."""
+    if os.environ.get("SONAR_GEMM", "tcgen05") == "cublas":
+        y = torch.nn.functional.linear(x, w, bias)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    assert x.dim() == 2 and w.dim() == 2 and x.stride(1) == 1 and w.stride(1) == 1 and x.shape[1] == w.shape[1]
+    m, k = x.shape
+    n = w.shape[0]
+    odt = out_dtype or (out.dtype if out is not None else x.dtype)
+    if out is None:
+        out = torch.empty((m, n), dtype=odt, device=x.device)
+    kbias = bias if (bias is not None and bias.dtype == odt) else None
+    _check(_gemm(x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(kbias), m, n, k, x.stride(0), w.stride(0),
+                 out.stride(0), _DT[x.dtype], _DT[odt], force_bn, error_word(x.device).data_ptr(), _stream()), "gemm")
+    if bias is not None and kbias is None:
+        out += bias.to(odt)
+    return out
+
+
+def per_token_group_quant_fp8(x, group=128):
+    return ref.per_token_group_quant_fp8(x, group)
+
+
+def gemm_fp8_block(xq, xs, wq, ws, out_dtype=torch.bfloat16, out=None):
+    y = ref.gemm_fp8_block(xq, xs, wq, ws, out_dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+# ---------------------------------------------------------------- MoE / MLA (composed until their kernels land)
+def topk_softmax(logits, k, renormalize):
+    return ref.topk_softmax(logits, k, renormalize)
+
+
+def grouped_topk(logits, bias, k, n_group, topk_group, renormalize, scale, scoring="sigmoid"):
+    return ref.grouped_topk(logits, bias, k, n_group, topk_group, renormalize, scale, scoring)
+
+
+def fused_experts(x, w13, w2, topk_w, topk_ids, expert_map=None):
+    return ref.fused_experts(x, w13, w2, topk_w, topk_ids, expert_map)
+
+
+def mla_cache_write(kv_c, k_pe, cache, slot_mapping):
+    return ref.mla_cache_write(kv_c, k_pe, cache, slot_mapping)
+
+
+def mla_paged_attention(q_nope, q_pe, cache, meta, scale, kv_lora_rank, topk_indices=None):
+    return ref.mla_paged_attention(q_nope, q_pe, cache, meta.block_tables, meta.seq_lens, meta.query_start_loc,
+                                   scale, kv_lora_rank, topk_indices)
+
+
+# ---------------------------------------------------------------- sampling
+_sample_step = 0
+
+
+def argmax(logits):
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    out = torch.empty(logits.shape[0], dtype=torch.int64, device=logits.device)
+    _check(_argmax(logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], out.data_ptr(), _stream()),
+           "argmax")
+    return out
+
+
+def sample(logits, temperature, top_k, top_p, min_p, noise=None, seeds=None):
+    global _sample_step
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    b, v = logits.shape
+    out = torch.empty(b, dtype=torch.int64, device=logits.device)
+    _sample_step += 1
+    _check(_sample(logits.data_ptr(), logits.stride(0), b, v, temperature.data_ptr(), _ptr(top_k), _ptr(top_p),
+                   _ptr(min_p), _ptr(noise), noise.stride(0) if noise is not None else 0, _ptr(seeds),
+                   _sample_step & 0xFFFFFFFF, out.data_ptr(), _stream()), "sample")
+    return out

@@ -1,0 +1,225 @@
+"""Numerics of every CUDA kernel against the plain PyTorch fp32 restatement."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from sonar_b200.layers.attention import AttentionMetadata  # noqa: E402
+from sonar_b200.ops import torch_ref as ref  # noqa: E402
+
+
+@pytest.fixture(scope="module")
+def cu():
+    from sonar_b200.ops import cuda
+    return cuda
+
+
+DEV = "cuda"
+
+
+def _close(a, b, atol, rtol):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    bad = err > tol
+    assert not bad.any(), f"max err {err.max().item():.4g} (tol {atol}+{rtol}·|ref|), {int(bad.sum())} / {bad.numel()} off"
+
+
+@pytest.mark.parametrize("hidden", [256, 1024, 4096, 8192])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_rms_norm(cu, hidden, dtype):
+    torch.manual_seed(0)
+    x = torch.randn(37, hidden, device=DEV, dtype=dtype)
+    w = (torch.rand(hidden, device=DEV) + 0.5).to(dtype)
+    want = ref.rms_norm(x.float(), w.float(), 1e-5)
+    got = cu.rms_norm(x, w, 1e-5)
+    _close(got, want, 2e-2, 1e-2)
+
+
+@pytest.mark.parametrize("hidden", [1024, 4096])
+def test_fused_add_rms_norm(cu, hidden):
+    torch.manual_seed(1)
+    x = torch.randn(65, hidden, device=DEV, dtype=torch.bfloat16)
+    r = torch.randn(65, hidden, device=DEV, dtype=torch.bfloat16)
+    w = (torch.rand(hidden, device=DEV) + 0.5).to(torch.bfloat16)
+    want_y, want_r = ref.fused_add_rms_norm(x, r, w, 1e-6)
+    xy, rr = x.clone(), r.clone()
+    cu.fused_add_rms_norm(xy, rr, w, 1e-6)
+    _close(rr, want_r, 1e-6, 0)          # residual add is exact in bf16
+    _close(xy, want_y, 3e-2, 1e-2)
+
+
+def test_silu_and_mul(cu):
+    torch.manual_seed(2)
+    x = torch.randn(50, 2 * 1536, device=DEV, dtype=torch.bfloat16)
+    want = ref.silu_and_mul(x.float())
+    got = cu.silu_and_mul(x)
+    _close(got, want, 2e-2, 1e-2)
+
+
+@pytest.mark.parametrize("qk_norm", [False, True])
+@pytest.mark.parametrize("head_dim", [128, 64])
+def test_rope_and_cache(cu, qk_norm, head_dim):
+    torch.manual_seed(3)
+    t, hq, hk, bs, nblocks = 45, 8, 2, 16, 12
+    qkv = torch.randn(t, (hq + 2 * hk) * head_dim, device=DEV, dtype=torch.bfloat16)
+    pos = torch.randint(0, 500, (t,), device=DEV, dtype=torch.int64)
+    cs = ref.build_cos_sin_cache(head_dim, 512, 1e4, None, DEV)
+    slots = torch.randperm(nblocks * bs, device=DEV)[:t].int()
+    slots[5] = -1
+    qw = (torch.rand(head_dim, device=DEV) + 0.5).to(torch.bfloat16) if qk_norm else None
+    kw = (torch.rand(head_dim, device=DEV) + 0.5).to(torch.bfloat16) if qk_norm else None
+    cache_ref = torch.zeros(nblocks, 2, hk, bs, head_dim, device=DEV, dtype=torch.bfloat16)
+    cache = cache_ref.clone()
+    q, k, v = qkv.float().split([hq * head_dim, hk * head_dim, hk * head_dim], dim=-1)
+    if qk_norm:
+        q_ref, k_ref = ref.qk_norm_rope(q, k, qw.float(), kw.float(), 1e-6, pos, cs, head_dim)
+    else:
+        q_ref, k_ref = ref.rope(q, k, pos, cs, head_dim)
+    ref.reshape_and_cache(k_ref.reshape(t, hk, head_dim), v.reshape(t, hk, head_dim), cache_ref, slots)
+    work = qkv.clone()
+    cu.rope_and_cache(work, pos, cs, cache, slots, hq, hk, head_dim, qw, kw, 1e-6, 1.0, 1.0)
+    _close(work[:, : hq * head_dim], q_ref, 4e-2, 2e-2)
+    _close(cache, cache_ref, 4e-2, 2e-2)
+
+
+def _make_attn_case(q_lens, ctx_lens, hq, hk, d, seed=0, nblocks=None):
+    torch.manual_seed(seed)
+    bs = 16
+    ns = len(q_lens)
+    need = sum(-(-c // bs) for c in ctx_lens)
+    nblocks = nblocks or need + 4
+    cache = torch.randn(nblocks, 2, hk, bs, d, device=DEV, dtype=torch.bfloat16) * 0.5
+    perm = torch.randperm(nblocks - 1)[:need] + 1
+    max_b = max(-(-c // bs) for c in ctx_lens)
+    bt = torch.zeros(ns, max_b, dtype=torch.int32)
+    off = 0
+    for i, c in enumerate(ctx_lens):
+        nb = -(-c // bs)
+        bt[i, :nb] = perm[off:off + nb].int()
+        off += nb
+    t = sum(q_lens)
+    q = torch.randn(t, hq, d, device=DEV, dtype=torch.bfloat16)
+    qsl = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    meta = AttentionMetadata(
+        num_tokens=t, num_seqs=ns, positions=None, slot_mapping=None, block_tables=bt.to(DEV),
+        seq_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), query_start_loc=qsl,
+        max_query_len=max(q_lens), max_seq_len=max(ctx_lens), query_lens_cpu=q_lens, seq_lens_cpu=ctx_lens)
+    return q, cache, meta
+
+
+ATTN_CASES = [
+    ([1, 1, 1], [17, 300, 1025], 8, 2, 128),               # decode, GQA 4
+    ([1] * 5, [5, 16, 31, 64, 700], 32, 8, 128),           # decode, llama-8b head layout
+    ([1, 1], [40, 90], 8, 1, 128),                         # decode, GQA 8 (70B TP8 shard)
+    ([33, 7, 128], [33, 50, 400], 8, 2, 128),              # prefill, chunked (ctx > q)
+    ([1, 200, 1, 64], [130, 200, 9, 1000], 8, 2, 128),     # mixed
+    ([2, 3], [60, 70], 4, 2, 64),                          # head_dim 64, short multi-token (spec decode shape)
+    ([1], [5000], 8, 2, 128),                              # long context, single sequence → split-KV
+]
+
+
+@pytest.mark.parametrize("q_lens,ctx_lens,hq,hk,d", ATTN_CASES)
+def test_paged_attention(cu, q_lens, ctx_lens, hq, hk, d):
+    q, cache, meta = _make_attn_case(q_lens, ctx_lens, hq, hk, d)
+    scale = d ** -0.5
+    want = ref.paged_attention(q.float(), cache.float(), meta.block_tables, meta.seq_lens, meta.query_start_loc, scale)
+    got = cu.paged_attention(q, cache, meta, scale)
+    _close(got.view(-1, hq, d), want, 2e-2, 2e-2)
+
+
+def test_paged_attention_sliding_window(cu):
+    q, cache, meta = _make_attn_case([1, 70], [300, 200], 8, 2, 128, seed=4)
+    scale = 128 ** -0.5
+    want = ref.paged_attention(q.float(), cache.float(), meta.block_tables, meta.seq_lens, meta.query_start_loc, scale,
+                               sliding_window=64)
+    got = cu.paged_attention(q, cache, meta, scale, sliding_window=64)
+    _close(got.view(-1, 8, 128), want, 2e-2, 2e-2)
+
+
+def test_paged_attention_strided_q(cu):
+    """q as a view into packed qkv rows (the layout the model uses)."""
+    q, cache, meta = _make_attn_case([1, 40], [100, 40], 8, 2, 128, seed=5)
+    t = q.shape[0]
+    packed = torch.randn(t, (8 + 4) * 128, device=DEV, dtype=torch.bfloat16)
+    packed[:, : 8 * 128] = q.reshape(t, -1)
+    qv = packed.as_strided((t, 8, 128), (packed.stride(0), 128, 1))
+    scale = 128 ** -0.5
+    want = ref.paged_attention(q.float(), cache.float(), meta.block_tables, meta.seq_lens, meta.query_start_loc, scale)
+    got = cu.paged_attention(qv, cache, meta, scale)
+    _close(got.view(-1, 8, 128), want, 2e-2, 2e-2)
+
+
+GEMM_SHAPES = [
+    (128, 256, 64), (128, 256, 256), (1, 64, 64), (7, 4096, 4096), (300, 6144, 4096), (1280, 4096, 1024),
+    (129, 1024, 8), (256, 128256 // 8, 512), (2048, 2048, 14336 // 8), (33, 72, 136),
+]
+
+
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
+@pytest.mark.parametrize("bn", [0, 64, 128, 256])
+def test_gemm_bf16(cu, m, n, k, bn):
+    torch.manual_seed(m * 7 + n + k)
+    x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(n, k, device=DEV, dtype=torch.bfloat16) * (1.0 / math.sqrt(k))
+    want = x.float() @ w.float().t()
+    got = cu.gemm(x, w, force_bn=bn)
+    torch.cuda.synchronize()
+    cu.check_device_errors()
+    _close(got, want, 3e-2, 2e-2)
+
+
+def test_gemm_fp32_out_bias_fp16(cu):
+    torch.manual_seed(9)
+    x = torch.randn(100, 512, device=DEV, dtype=torch.float16)
+    w = torch.randn(264, 512, device=DEV, dtype=torch.float16) * 0.05
+    b = torch.randn(264, device=DEV, dtype=torch.float16)
+    _close(cu.gemm(x, w, b), x.float() @ w.float().t() + b.float(), 3e-2, 2e-2)
+    _close(cu.gemm(x, w, out_dtype=torch.float32), x.float() @ w.float().t(), 2e-3, 2e-3)
+    cu.check_device_errors()
+
+
+def test_gemm_strided_rows(cu):
+    torch.manual_seed(10)
+    big = torch.randn(64, 1024, device=DEV, dtype=torch.bfloat16)
+    x = big[:, 256:768]                     # row pitch 1024, 512 columns, 16-byte aligned start
+    w = torch.randn(128, 512, device=DEV, dtype=torch.bfloat16) * 0.05
+    _close(cu.gemm(x, w), x.float() @ w.float().t(), 3e-2, 2e-2)
+    cu.check_device_errors()
+
+
+def test_argmax(cu):
+    torch.manual_seed(11)
+    logits = torch.randn(33, 128256, device=DEV)
+    assert torch.equal(cu.argmax(logits), logits.argmax(-1))
+
+
+def test_sample_matches_reference_with_shared_noise(cu):
+    torch.manual_seed(12)
+    b, v = 24, 5000
+    logits = torch.randn(b, v, device=DEV) * 3
+    noise = torch.empty(b, v, device=DEV).exponential_()
+    temp = torch.tensor([0.0, 1.0, 0.7, 1.3] * 6, device=DEV)
+    top_k = torch.tensor([0, 0, 50, 0, 7, 1] * 4, device=DEV, dtype=torch.int32)
+    top_p = torch.tensor([1.0, 1.0, 1.0, 0.9, 0.5, 1.0, 0.8, 0.95] * 3, device=DEV)
+    min_p = torch.tensor([0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.05, 0.0, 0.2, 0.0] * 2, device=DEV)
+    want = ref.sample_from_logits(logits, temp, top_k, top_p, min_p, noise)
+    got = cu.sample(logits, temp, top_k, top_p, min_p, noise=noise)
+    assert torch.equal(got, want), f"rows differ: {(got != want).nonzero().flatten().tolist()}"
+
+
+def test_sample_rng_statistics(cu):
+    """Without supplied noise the built-in RNG must reproduce the categorical distribution."""
+    torch.manual_seed(13)
+    v, n = 16, 4096
+    row = torch.randn(v, device=DEV) * 1.5
+    logits = row[None].repeat(n, 1).contiguous()
+    temp = torch.ones(n, device=DEV)
+    ids = cu.sample(logits, temp, None, None, None)
+    freq = torch.bincount(ids, minlength=v).float() / n
+    p = torch.softmax(row, -1)
+    assert (freq - p).abs().max() < 0.03
+    ids2 = cu.sample(logits, temp, None, None, None)
+    assert not torch.equal(ids, ids2)       # successive calls draw fresh noise

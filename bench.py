@@ -176,8 +176,12 @@ def main() -> None:
     sampler = ClockSampler(local_rank)
     sampler.start()
     launches0 = cuda_ops.launch_count
+    core0 = dict(engine.core.engine_core.host_time)
+    run0 = {k: runner.stats[k] for k in ("prep_s", "launch_s", "sample_s")}
     h2d0, d2h0 = runner.stats["h2d_bytes"], runner.stats["d2h_bytes"]
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if os.environ.get("SONAR_PROFILE_REGION"):
+        torch.cuda.profiler.start()
     start.record()
     t_host0 = time.perf_counter()
     steps = 0
@@ -190,7 +194,10 @@ def main() -> None:
         engine.output_processor.process_outputs(outs.outputs)
     end.record()
     barrier()
+    if os.environ.get("SONAR_PROFILE_REGION"):
+        torch.cuda.profiler.stop()
     host_s = time.perf_counter() - t_host0
+    runner_stats_end = dict(runner.stats)
     clocks = sampler.stop()
     dev_ms = start.elapsed_time(end)
     launches = cuda_ops.launch_count - launches0
@@ -243,6 +250,8 @@ def main() -> None:
             },
             "output_tokens": out_tokens, "device_seconds": dev_ms / 1e3, "host_seconds": host_s,
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "host_ms_per_step": {**{k: round((core.host_time[k] - core0[k]) * 1e3 / max(steps, 1), 3) for k in core0},
+                                 **{k: round((runner_stats_end[k] - run0[k]) * 1e3 / max(steps, 1), 3) for k in run0}},
             "h2d_bytes_per_step": h2d // max(steps, 1), "d2h_bytes_per_step": d2h // max(steps, 1),
         }
         print(json.dumps(line))

@@ -8,15 +8,18 @@
 // warps 2-5 are the epilogue: tcgen05.ld the accumulator (two TMEM buffers, so the next tile's
 // mainloop overlaps this tile's epilogue), convert and store.
 //
-// Two optional collective hooks make this the tensor-parallel kernel as well:
-//  * row_ready: before loading A rows of a 128-row block the producer waits (bounded) until the
-//    block's arrival counter, which peers bump after pushing those rows into this GPU's gather
-//    buffer, reaches `ready_target` — the all-gather overlaps the GEMM block by block.  Loads are
-//    plain TMA from local memory.
-//  * scatter epilogue: output rows are split in `n_dst` contiguous shards of `rows_per_dst` rows;
-//    shard d is stored through dst_ptrs[d] (a peer mapping of rank d's partial buffer, slot = this
-//    rank), so every rank receives the partial products of its own token rows as they are produced —
-//    the push half of a reduce-scatter; a counter per destination is bumped when a tile lands.
+// Two optional collective hooks make this the tensor-parallel kernel as well (sequence-parallel layout,
+// token rows split in `tp` contiguous shards of `shard_rows`):
+//  * gather wait (column-parallel GEMM, A = all-gathered activations in this GPU's gather buffer): before
+//    loading the A rows of a 128-row block the producer waits (bounded) until every source rank
+//    overlapping the block has stored `seq` into gather_flags[block * tp + rank]; peers set the flag after
+//    pushing those rows.  Blocks holding this rank's own rows are scheduled first.  Loads are plain
+//    TMA from local memory — the all-gather overlaps the GEMM block by block.
+//  * scatter epilogue (row-parallel GEMM): output rows of shard d are stored through dst_ptrs[d] (a peer
+//    mapping of rank d's partial-sum buffer, slot = this rank), so every rank receives the partial
+//    products of its own token rows while the GEMM is still running — the push half of a
+//    reduce-scatter.  Epilogue warps count finished tiles per destination in a local counter; the one
+//    completing destination d's share stores `seq` (release, system scope) to flag_ptrs[d].
 //
 // Baselines this replaces: cuBLAS via F.linear (reference layers/utils.py:86) and the async-TP
 // decomposition into library GEMMs + copies (reference compilation/passes/fusion/collective_fusion.py:327-388).
@@ -68,13 +71,13 @@ struct GemmParams {
   long ldc;
   const void* bias;   // [N] or null (same dtype as C when C is 16-bit, fp32 when C is fp32)
   int* err;           // device error word
-  // all-gather hook
-  const int* row_ready;   // [ceil(M/128)] arrival counters, or null
-  int ready_target;
-  // scatter hook
-  void* const* dst_ptrs;  // [n_dst] device array of destination bases, or null
-  int rows_per_dst;
-  int* const* done_ctr;   // [n_dst] counters at the destinations (bumped once per tile per dst), or null
+  // gather wait
+  const int* gather_flags;  // [num_m_blocks * tp] local flags, or null
+  int tp, shard_rows, seq, m_rot;
+  // scatter epilogue
+  void* const* dst_ptrs;    // [tp] destination bases (peer mappings), or null
+  int* local_done;          // [tp] local arrival counters (zero between launches)
+  int* const* flag_ptrs;    // [tp] remote flag words to publish `seq` to
 };
 
 template <int BN> struct Cfg {
@@ -161,19 +164,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m_idx = tile % num_m, n_idx = tile / num_m;
-        if (p.row_ready != nullptr) {
-          // bounded wait for the peers' rows of this block (plain loads of a local counter)
-          const int* ctr = p.row_ready + m_idx;
-          auto peek = [&]() {
-            int v;
-            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
-            return v;
-          };
-          if (peek() < p.ready_target) {
+        const int m_idx = (tile % num_m + p.m_rot) % num_m, n_idx = tile / num_m;
+        if (p.gather_flags != nullptr) {
+          // bounded wait until every source rank of this row block has published this launch's sequence number
+          const int r_lo = m_idx * BM, r_hi = min(p.M, r_lo + BM) - 1;
+          for (int src = r_lo / p.shard_rows; src <= r_hi / p.shard_rows && ok; ++src) {
+            const int* flag = p.gather_flags + m_idx * p.tp + src;
+            auto arrived = [&]() {
+              int v;
+              asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+              return (v - p.seq) >= 0;
+            };
+            if (arrived()) continue;
             const uint64_t t0 = globaltimer_ns();
             uint32_t spins = 0;
-            while (peek() < p.ready_target) {
+            while (!arrived()) {
               if ((++spins & 63u) == 0) {
                 if (*abort_flag) { ok = false; break; }
                 if (globaltimer_ns() - t0 > tc::WAIT_LIMIT_NS) {
@@ -184,9 +189,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
                 }
               }
             }
-            if (!ok) break;
           }
-          // the acquire above orders the peers' row stores before the TMA (async proxy) reads below
+          if (!ok) break;
+          // the acquire loads order the peers' row stores before the TMA (async proxy) reads below
           asm volatile("fence.proxy.async;" ::: "memory");
         }
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
@@ -235,7 +240,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     const int lane_grp = warp & 3;
     uint32_t t_local = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t_local) {
-      const int m_idx = tile % num_m, n_idx = tile / num_m;
+      const int m_idx = (tile % num_m + p.m_rot) % num_m, n_idx = tile / num_m;
       const int buf = t_local & 1;
       const uint32_t bph = (t_local >> 1) & 1;
       if (!tc::mbar_wait(tfull_bar(buf), bph, abort_flag, p.err, tc::SITE_TMEM_FULL)) break;
@@ -245,8 +250,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       OutT* crow = nullptr;
       if (row < p.M) {
         if (p.dst_ptrs != nullptr) {
-          const int d = row / p.rows_per_dst;
-          crow = reinterpret_cast<OutT*>(p.dst_ptrs[d]) + (long)(row - d * p.rows_per_dst) * p.ldc;
+          const int d = row / p.shard_rows;
+          crow = reinterpret_cast<OutT*>(p.dst_ptrs[d]) + (long)(row - d * p.shard_rows) * p.ldc;
         } else {
           crow = reinterpret_cast<OutT*>(p.C) + (long)row * p.ldc;
         }
@@ -265,15 +270,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       }
       tc::fence_before_sync();
       tc::mbar_arrive(tempty_bar(buf));
-      if (p.done_ctr != nullptr) {
-        // publish: every lane fences its stores, then one release-increment per warp per destination
-        // the tile touches (a destination expects 4 × its overlapping tiles)
+      if (p.dst_ptrs != nullptr) {
+        // publish: every lane fences its stores; one arrival per warp per destination the tile touches;
+        // the arrival completing a destination's share (4 warps × its tiles) sends the flag
         __threadfence_system();
         __syncwarp();
         if (lane == 0) {
           const int r_lo = m_idx * BM, r_hi = min(p.M, r_lo + BM) - 1;
-          for (int d = r_lo / p.rows_per_dst; d <= r_hi / p.rows_per_dst; ++d)
-            asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(p.done_ctr[d]) : "memory");
+          for (int d = r_lo / p.shard_rows; d <= r_hi / p.shard_rows; ++d) {
+            const int d_lo = d * p.shard_rows, d_hi = min(p.M, d_lo + p.shard_rows) - 1;
+            const int expected = 4 * num_n * (d_hi / BM - d_lo / BM + 1);
+            int prev;
+            asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(prev) : "l"(p.local_done + d) : "memory");
+            if (prev + 1 == expected) {
+              p.local_done[d] = 0;
+              __threadfence_system();
+              asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.flag_ptrs[d]), "r"(p.seq) : "memory");
+            }
+          }
         }
       }
     }
@@ -337,19 +351,21 @@ int num_sms() {
   return g_num_sms;
 }
 
-// Tile width by a small cost model: waves × per-tile time, where a 128×BN×64 block costs
-// max(tensor time ∝ BN, shared-memory operand traffic ∝ 128+BN).
+// Tile width by a small cost model: waves × measured relative cost of one 128×BN tile pass
+// (a 128×256 tile runs the tensor pipe near its peak; narrower tiles re-read A from shared memory
+// per fewer columns and reach ≈70 % / ≈40 % of that rate, so they only win when they save waves).
 int pick_bn(int M, int N) {
   const int sms = num_sms();
   const int num_m = (M + BM - 1) / BM;
-  int best = 64;
+  int best = 256;
   double best_cost = 1e30;
-  for (int bn : {256, 128, 64}) {
-    int tiles = num_m * ((N + bn - 1) / bn);
+  const int bns[3] = {256, 128, 64};
+  const double per_tile[3] = {1.0, 0.725, 0.66};
+  for (int i = 0; i < 3; ++i) {
+    int tiles = num_m * ((N + bns[i] - 1) / bns[i]);
     int waves = (tiles + sms - 1) / sms;
-    double per_tile = bn > (128 + bn) * 0.5 ? (double)bn : (128 + bn) * 0.5;
-    double cost = waves * per_tile;
-    if (cost < best_cost - 1e-9) { best_cost = cost; best = bn; }
+    double cost = waves * per_tile[i];
+    if (cost < best_cost - 1e-9) { best_cost = cost; best = bns[i]; }
   }
   return best;
 }
@@ -397,6 +413,7 @@ SONAR_API int sonar_gemm(const void* A, const void* B, void* C, const void* bias
   if ((out_dtype == SONAR_F32 ? (N % 4 || ldc % 4) : (N % 8 || ldc % 8)) || ((uintptr_t)C & 15)) return SONAR_BAD_ARG;
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.bias = bias; p.err = err;
+  p.tp = 1; p.shard_rows = M;
   const int bn = force_bn ? force_bn : pick_bn(M, N);
   if (bn != 64 && bn != 128 && bn != 256) return SONAR_BAD_ARG;
   if (in_dtype == SONAR_BF16) {
@@ -409,18 +426,22 @@ SONAR_API int sonar_gemm(const void* A, const void* B, void* C, const void* bias
   return SONAR_BAD_ARG;
 }
 
-// Tensor-parallel variant (bf16 only).  row_ready/ready_target: all-gather hook; dst_ptrs/rows_per_dst/
-// done_ctr: scatter epilogue (see the file header).  Either hook may be null.
+// Tensor-parallel variant (bf16).  gather_flags != null: wait per row block for the all-gathered A rows
+// (flags hold the sequence number of the launch that filled them).  dst_ptrs != null: scatter epilogue
+// into the peers' partial buffers with completion flags (see the file header).
 SONAR_API int sonar_gemm_tp(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc,
-                            const int* row_ready, int ready_target, void* const* dst_ptrs, int rows_per_dst,
-                            int* const* done_ctr, int force_bn, int* err, cudaStream_t s) {
-  if (M <= 0 || N <= 0 || K <= 0) return M == 0 ? SONAR_OK : SONAR_BAD_ARG;
+                            const int* gather_flags, int tp, int shard_rows, int seq, int rank,
+                            void* const* dst_ptrs, int* local_done, int* const* flag_ptrs, int force_bn, int* err,
+                            cudaStream_t s) {
+  if (M <= 0 || N <= 0 || K <= 0) return SONAR_BAD_ARG;
   if (K % 8 || lda % 8 || ldb % 8 || N % 8 || ldc % 8) return SONAR_BAD_ARG;
-  if (dst_ptrs != nullptr && rows_per_dst <= 0) return SONAR_BAD_ARG;
+  if (tp < 1 || shard_rows <= 0 || (long)tp * shard_rows < M) return SONAR_BAD_ARG;
+  if (dst_ptrs != nullptr && (!local_done || !flag_ptrs)) return SONAR_BAD_ARG;
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.err = err;
-  p.row_ready = row_ready; p.ready_target = ready_target;
-  p.dst_ptrs = dst_ptrs; p.rows_per_dst = rows_per_dst; p.done_ctr = done_ctr;
+  p.gather_flags = gather_flags; p.tp = tp; p.shard_rows = shard_rows; p.seq = seq;
+  p.m_rot = gather_flags ? (int)(((long)rank * shard_rows) / BM) : 0;
+  p.dst_ptrs = dst_ptrs; p.local_done = local_done; p.flag_ptrs = flag_ptrs;
   const int bn = force_bn ? force_bn : pick_bn(M, N);
   return launch_bn<__nv_bfloat16, 1>(bn, A, B, p, lda, ldb, s);
 }

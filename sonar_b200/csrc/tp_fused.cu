@@ -1,0 +1,284 @@
+// Tensor-parallel glue kernels that run between the fused GEMMs (sequence-parallel layout).
+//
+//  tp_add_norm:  the owner of a token row sums the tp partial products that the row-parallel GEMMs
+//                pushed into its partial buffer (reduce half of the reduce-scatter), adds the residual,
+//                applies RMSNorm and stores the normalised row into every rank's gather buffer
+//                (all-gather by push over NVLink peer mappings), then publishes per-128-row-block flags
+//                that the next column-parallel GEMM's TMA producer waits on.
+//  tp_wait:      bounded wait for gather flags (before a non-fused consumer, e.g. the LM head).
+//  all_reduce:   one-shot P2P all-reduce for small replicated tensors (each rank pushes its input to
+//                every peer's slot, then sums the slots in rank order → bitwise identical results).
+//
+// Every wait is bounded (2 s) and reports through the device error word instead of hanging.
+// Behavioural parity: the reduce-scatter → norm → all-gather rewrite of the reference's sequence-parallel
+// pass (compilation/passes/fusion/sequence_parallelism.py:153-250) and its custom all-reduce
+// (csrc/custom_all_reduce.cuh:9) — here as single kernels over peer memory.
+#include <string.h>
+
+#include "common.cuh"
+
+namespace sonar {
+namespace {
+
+constexpr uint64_t WAIT_NS = 2000000000ull;
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Wait until *flag - seq >= 0 (wrap-safe).  Returns false after the time limit.
+__device__ __forceinline__ bool wait_flag(const int* flag, int seq, int* err, int code) {
+  if ((ld_acquire_sys(flag) - seq) >= 0) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while ((ld_acquire_sys(flag) - seq) < 0) {
+    if ((++spins & 127u) == 0 && globaltimer_ns() - t0 > WAIT_NS) {
+      if (err) atomicCAS(err, 0, code);
+      return false;
+    }
+  }
+  return true;
+}
+
+struct AddNormParams {
+  const void* src;          // partial buffer base (slot 0) or the local input rows
+  long slot_stride;         // elements between slots
+  int n_src;
+  const int* src_flags;     // [n_src] flags to wait for (null: no wait)
+  int wait_seq;
+  void* residual;           // [rows, H] in/out (always written)
+  int residual_in;          // 1: add the incoming residual
+  const void* weight;
+  float eps;
+  int H, rows;              // local rows (this rank's shard)
+  void* const* gather_ptrs; // [tp] bases of every rank's gather buffer (peer mappings; own included)
+  int tp, rank, shard_rows;
+  int* blk_done;            // local per-block counters
+  int* const* gather_flag_ptrs;  // [tp] bases of every rank's gather flag array
+  int send_seq;
+  int* err;
+};
+
+template <typename T, int VPT>
+__global__ void __launch_bounds__(1024) tp_add_norm_kernel(const AddNormParams p) {
+  __shared__ float red[32];
+  __shared__ int ok_s;
+  const int i = blockIdx.x;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (p.src_flags != nullptr && threadIdx.x < p.n_src) {
+    if (!wait_flag(p.src_flags + threadIdx.x, p.wait_seq, p.err, 5 | (blockIdx.x << 8))) ok_s = 0;
+  }
+  __syncthreads();
+  if (!ok_s) return;
+  const int nvec = p.H >> 3;
+  const T* src = reinterpret_cast<const T*>(p.src) + (long)i * p.H;
+  uint4* res = reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.residual) + (long)i * p.H);
+  float vals[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int v = threadIdx.x + k * blockDim.x;
+    if (v < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) vals[k][j] = 0.f;
+      for (int s = 0; s < p.n_src; ++s) {
+        float f[8];
+        unpack8<T>(reinterpret_cast<const uint4*>(src + s * p.slot_stride)[v], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vals[k][j] += f[j];
+      }
+      if (p.residual_in) {
+        float f[8];
+        unpack8<T>(res[v], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vals[k][j] += f[j];
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) vals[k][j] = to_f<T>(from_f<T>(vals[k][j]));
+      res[v] = pack8<T>(vals[k]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += vals[k][j] * vals[k][j];
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)p.H + p.eps);
+  const long grow = (long)p.rank * p.shard_rows + i;
+  const uint4* wv = reinterpret_cast<const uint4*>(p.weight);
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int v = threadIdx.x + k * blockDim.x;
+    if (v < nvec) {
+      float g[8];
+      unpack8<T>(wv[v], g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) vals[k][j] = vals[k][j] * inv * g[j];
+      const uint4 packed = pack8<T>(vals[k]);
+      for (int q = 0; q < p.tp; ++q) {
+        const int dst = (p.rank + q) % p.tp;   // start with the local copy, spread peers
+        reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.gather_ptrs[dst]) + grow * p.H)[v] = packed;
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int b = (int)(grow >> 7);
+    const long lo = max((long)p.rank * p.shard_rows, (long)b << 7);
+    const long hi = min((long)p.rank * p.shard_rows + p.rows, ((long)b + 1) << 7);
+    const int expected = (int)(hi - lo);
+    int prev;
+    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(prev) : "l"(p.blk_done + b) : "memory");
+    if (prev + 1 == expected) {
+      p.blk_done[b] = 0;
+      __threadfence_system();
+      for (int q = 0; q < p.tp; ++q) st_release_sys(p.gather_flag_ptrs[q] + b * p.tp + p.rank, p.send_seq);
+    }
+  }
+}
+
+__global__ void tp_wait_kernel(const int* flags, int n_blocks, int tp, int shard_rows, int M, int seq, int* err) {
+  for (int idx = threadIdx.x; idx < n_blocks * tp; idx += blockDim.x) {
+    const int b = idx / tp, src = idx % tp;
+    const long r_lo = (long)b << 7, r_hi = min((long)M, r_lo + 128) - 1;
+    if (src < r_lo / shard_rows || src > r_hi / shard_rows) continue;
+    wait_flag(flags + idx, seq, err, 5 | (255 << 8));
+  }
+}
+
+// One-shot all-reduce: slot layout [tp][n] in every rank's buffer.  Phase 1 pushes the local input into
+// slot `rank` of every peer and raises flag[rank] there; phase 2 sums the slots in rank order.
+struct AllReduceParams {
+  const void* in;
+  void* out;
+  long n;                   // elements (multiple of 8)
+  void* const* slot_ptrs;   // [tp] peer buffer bases
+  int* const* flag_ptrs;    // [tp] peer flag arrays ([tp] ints each)
+  const void* local_slots;  // this rank's buffer
+  const int* local_flags;
+  int* arrive;              // local counter (zero between launches)
+  int tp, rank, seq;
+  int* err;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(512) all_reduce_kernel(const AllReduceParams p) {
+  __shared__ int ok_s;
+  const long nvec = p.n >> 3;
+  const uint4* in = reinterpret_cast<const uint4*>(p.in);
+  for (long v = blockIdx.x * (long)blockDim.x + threadIdx.x; v < nvec; v += (long)gridDim.x * blockDim.x) {
+    const uint4 x = in[v];
+    for (int q = 0; q < p.tp; ++q) {
+      const int dst = (p.rank + q) % p.tp;
+      reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.slot_ptrs[dst]) + (long)p.rank * p.n)[v] = x;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ok_s = 1;
+    int prev;
+    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(prev) : "l"(p.arrive) : "memory");
+    if (prev + 1 == (int)gridDim.x) {
+      *p.arrive = 0;
+      __threadfence_system();
+      for (int q = 0; q < p.tp; ++q) st_release_sys(p.flag_ptrs[q] + p.rank, p.seq);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < p.tp) {
+    if (!wait_flag(p.local_flags + threadIdx.x, p.seq, p.err, 5 | (254 << 8))) ok_s = 0;
+  }
+  __syncthreads();
+  if (!ok_s) return;
+  const T* slots = reinterpret_cast<const T*>(p.local_slots);
+  uint4* out = reinterpret_cast<uint4*>(p.out);
+  for (long v = blockIdx.x * (long)blockDim.x + threadIdx.x; v < nvec; v += (long)gridDim.x * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int s = 0; s < p.tp; ++s) {
+      float f[8];
+      unpack8<T>(reinterpret_cast<const uint4*>(slots + (long)s * p.n)[v], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+    out[v] = pack8<T>(acc);
+  }
+}
+
+}  // namespace
+}  // namespace sonar
+
+using namespace sonar;
+
+SONAR_API int sonar_tp_add_norm(const void* src, long slot_stride, int n_src, const int* src_flags, int wait_seq,
+                                void* residual, int residual_in, const void* weight, float eps, int H, int rows,
+                                void* const* gather_ptrs, int tp, int rank, int shard_rows, int* blk_done,
+                                int* const* gather_flag_ptrs, int send_seq, int* err, int dtype, cudaStream_t s) {
+  if (H % 8 || rows <= 0 || rows > shard_rows || n_src < 1 || n_src > 32) return SONAR_BAD_ARG;
+  AddNormParams p{src, slot_stride, n_src, src_flags, wait_seq, residual, residual_in, weight, eps, H, rows,
+                  gather_ptrs, tp, rank, shard_rows, blk_done, gather_flag_ptrs, send_seq, err};
+  const int nvec = H / 8;
+  int threads = nvec >= 1024 ? 1024 : ((nvec + 31) / 32) * 32;
+  if (nvec > 256 && nvec <= 1024) threads = ((nvec / 2 + 31) / 32) * 32;
+  if (threads < 32) threads = 32;
+  const int vpt = (nvec + threads - 1) / threads;
+  SONAR_DISPATCH_HALF(dtype, T, {
+    if (vpt <= 1) tp_add_norm_kernel<T, 1><<<rows, threads, 0, s>>>(p);
+    else if (vpt <= 2) tp_add_norm_kernel<T, 2><<<rows, threads, 0, s>>>(p);
+    else if (vpt <= 4) tp_add_norm_kernel<T, 4><<<rows, threads, 0, s>>>(p);
+    else return SONAR_TOO_LARGE;
+    return check_launch();
+  });
+}
+
+SONAR_API int sonar_tp_wait(const int* flags, int tp, int shard_rows, int M, int seq, int* err, cudaStream_t s) {
+  const int n_blocks = (M + 127) / 128;
+  tp_wait_kernel<<<1, 256, 0, s>>>(flags, n_blocks, tp, shard_rows, M, seq, err);
+  return check_launch();
+}
+
+SONAR_API int sonar_all_reduce(const void* in, void* out, long n, void* const* slot_ptrs, int* const* flag_ptrs,
+                               const void* local_slots, const int* local_flags, int* arrive, int tp, int rank, int seq,
+                               int* err, int dtype, cudaStream_t s) {
+  if (n % 8 || n <= 0 || tp > 32) return SONAR_BAD_ARG;
+  AllReduceParams p{in, out, n, slot_ptrs, flag_ptrs, local_slots, local_flags, arrive, tp, rank, seq, err};
+  long nvec = n / 8;
+  int blocks = (int)((nvec + 511) / 512);
+  if (blocks > 64) blocks = 64;   // all blocks must be co-resident: each waits for the peers' flags
+  SONAR_DISPATCH_HALF(dtype, T, {
+    all_reduce_kernel<T><<<blocks, 512, 0, s>>>(p);
+    return check_launch();
+  });
+}
+
+// ---- peer-memory plumbing fallback (cudaMalloc + CUDA IPC handles) used when the framework's symmetric
+// memory allocator is unavailable: allocate, export a 64-byte handle, open a peer's handle.
+SONAR_API int sonar_peer_malloc(size_t bytes, void** out) {
+  cudaError_t e = cudaMalloc(out, bytes);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return SONAR_CUDA_ERROR; }
+  e = cudaMemset(*out, 0, bytes);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return SONAR_CUDA_ERROR; }
+  return SONAR_OK;
+}
+SONAR_API int sonar_peer_free(void* p) { cudaFree(p); return SONAR_OK; }
+SONAR_API int sonar_ipc_get_handle(void* ptr, void* out64) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, ptr);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return SONAR_CUDA_ERROR; }
+  memcpy(out64, &h, sizeof(h));
+  return SONAR_OK;
+}
+SONAR_API int sonar_ipc_open_handle(const void* in64, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, in64, sizeof(h));
+  cudaError_t e = cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return SONAR_CUDA_ERROR; }
+  return SONAR_OK;
+}
+SONAR_API int sonar_ipc_close_handle(void* p) { cudaIpcCloseMemHandle(p); return SONAR_OK; }

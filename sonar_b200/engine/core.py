@@ -35,6 +35,7 @@ class EngineCore:
         self.tracer = get_tracer(cfg.observability.trace_file)
         self.paused = False
         self.steps = 0
+        self.host_time = {"schedule": 0.0, "execute": 0.0, "update": 0.0}
         logger.info("engine core ready in %.1fs (%d KV blocks of %d tokens)", time.time() - t0,
                     self.kv_cfg.num_blocks, cfg.cache.block_size)
 
@@ -51,12 +52,19 @@ class EngineCore:
     def step(self) -> EngineCoreOutputs:
         if self.paused or not self.scheduler.has_requests():
             return EngineCoreOutputs()
+        t0 = time.perf_counter()
         with self.tracer.span("schedule"):
             so = self.scheduler.schedule()
+        t1 = time.perf_counter()
         with self.tracer.span("execute_model", tokens=so.total_num_scheduled_tokens):
             ro = self.executor.execute_model(so)
+        t2 = time.perf_counter()
         with self.tracer.span("update"):
             outs = self.scheduler.update_from_output(so, ro)
+        t3 = time.perf_counter()
+        self.host_time["schedule"] += t1 - t0
+        self.host_time["execute"] += t2 - t1
+        self.host_time["update"] += t3 - t2
         self.steps += 1
         return outs
 

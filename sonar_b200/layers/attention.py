@@ -75,9 +75,18 @@ class Attention(nn.Module):
         self.kv_cache = cache
 
     def forward(self, qkv: torch.Tensor, meta: AttentionMetadata) -> torch.Tensor:
-        q = ops.rope_and_cache(qkv, meta.positions, self.cos_sin, self.kv_cache, meta.slot_mapping,
+        """qkv may carry padding rows beyond ``meta.num_tokens`` (token-scattered TP pads the
+        step to a multiple of tp); they are passed through untouched and unspecified."""
+        t = meta.positions.shape[0]
+        rows = qkv.shape[0]
+        q = ops.rope_and_cache(qkv[:t], meta.positions, self.cos_sin, self.kv_cache, meta.slot_mapping,
                                self.num_heads, self.num_kv_heads, self.head_dim,
                                self.q_norm_weight, self.k_norm_weight, self.qk_norm_eps or 1e-6,
                                self.k_scale, self.v_scale)
-        return ops.paged_attention(q, self.kv_cache, meta, self.scale, self.sliding_window,
-                                   self.k_scale, self.v_scale)
+        if rows == t:
+            return ops.paged_attention(q, self.kv_cache, meta, self.scale, self.sliding_window,
+                                       self.k_scale, self.v_scale)
+        out = torch.zeros((rows, self.num_heads * self.head_dim), dtype=qkv.dtype, device=qkv.device)
+        ops.paged_attention(q, self.kv_cache, meta, self.scale, self.sliding_window, self.k_scale, self.v_scale,
+                            out=out[:t])
+        return out

@@ -25,9 +25,10 @@ def pad_vocab(vocab: int, tp: int) -> int:
 
 
 class VocabParallelEmbedding(nn.Module):
-    def __init__(self, vocab_size: int, hidden_size: int, dtype=torch.bfloat16, device=None, prefix="") -> None:
+    def __init__(self, vocab_size: int, hidden_size: int, dtype=torch.bfloat16, device=None, prefix="",
+                 replicated: bool = False) -> None:
         super().__init__()
-        self.tp_size, self.tp_rank = state.tp_world_size(), state.tp_rank()
+        self.tp_size, self.tp_rank = (1, 0) if replicated else (state.tp_world_size(), state.tp_rank())
         self.vocab_size = vocab_size
         self.padded = pad_vocab(vocab_size, self.tp_size)
         self.local = self.padded // self.tp_size

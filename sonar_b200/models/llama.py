@@ -114,9 +114,11 @@ class LlamaModel(nn.Module):
         self.is_first = pp is None or pp.rank_in_group == 0
         self.is_last = pp is None or pp.rank_in_group == pp.world_size - 1
         tied = bool(cfg.get("tie_word_embeddings", False))
+        # token-scattered TP layout: every rank embeds only its own rows, from a full table
+        self.replicated_embed = get_tp_context().scattered
         if self.is_first or (tied and self.is_last):
             self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device,
-                                                       "model.embed_tokens")
+                                                       "model.embed_tokens", replicated=self.replicated_embed)
         self.layers = nn.ModuleDict({
             str(i): self.layer_cls(cfg, i, device, f"model.layers.{i}")
             for i in range(self.start_layer, self.end_layer)})
@@ -127,7 +129,10 @@ class LlamaModel(nn.Module):
                 intermediate: tuple[torch.Tensor, torch.Tensor | None] | None = None):
         tp = get_tp_context()
         if self.is_first:
-            h = tp.embed_reduce(self.embed_tokens(input_ids))
+            if tp.scattered:
+                h = self.embed_tokens(tp.shard_token_ids(input_ids))
+            else:
+                h = tp.embed_reduce(self.embed_tokens(input_ids))
             residual = None
         else:
             h, residual = intermediate
@@ -153,7 +158,8 @@ class LlamaForCausalLM(nn.Module):
         self.tied = bool(cfg.get("tie_word_embeddings", False))
         if self.model.is_last:
             if self.tied:
-                self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device, "lm_head")
+                self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device, "lm_head",
+                                              replicated=self.model.replicated_embed)
                 self.lm_head.weight = self.model.embed_tokens.weight
             else:
                 self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device, "lm_head")

@@ -48,7 +48,12 @@ _attn = _sig("sonar_paged_attention", c_void_p, c_long, c_void_p, c_void_p, c_in
 _gemm = _sig("sonar_gemm", c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_long,
              c_int, c_int, c_int, c_void_p, c_void_p)
 _gemm_tp = _sig("sonar_gemm_tp", c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_long,
-                c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p)
+                c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p)
+_tp_add_norm = _sig("sonar_tp_add_norm", c_void_p, c_long, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float,
+                    c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p)
+_tp_wait = _sig("sonar_tp_wait", c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p)
+_all_reduce = _sig("sonar_all_reduce", c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                   c_int, c_int, c_int, c_void_p, c_int, c_void_p)
 _argmax = _sig("sonar_argmax", c_void_p, c_long, c_int, c_int, c_void_p, c_void_p)
 _sample = _sig("sonar_sample", c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                c_long, c_void_p, c_uint, c_void_p, c_void_p)
@@ -254,6 +259,40 @@ def gemm(x, w, bias=None, out=None, out_dtype=None, force_bn: int = 0):
                  out.stride(0), _DT[x.dtype], _DT[odt], force_bn, error_word(x.device).data_ptr(), _stream()), "gemm")
     if bias is not None and kbias is None:
         out += bias.to(odt)
+    return out
+
+
+def gemm_tp(a, w, out, *, tp, shard_rows, seq, rank, gather_flags=None, dst_ptrs=None, local_done=None,
+            flag_ptrs=None, n_out=None, ldc=None, err=None, force_bn: int = 0):
+    """Tensor-parallel GEMM: ``gather_flags`` → wait for all-gathered A rows per 128-row block;
+    ``dst_ptrs`` → scatter the output rows to their owners' partial buffers (``out`` is then None)."""
+    m, k = a.shape
+    n = w.shape[0] if n_out is None else n_out
+    assert a.stride(1) == 1 and w.stride(1) == 1 and a.dtype == torch.bfloat16
+    c_ptr = out.data_ptr() if out is not None else None
+    c_ld = out.stride(0) if out is not None else ldc
+    _check(_gemm_tp(a.data_ptr(), w.data_ptr(), c_ptr, m, n, k, a.stride(0), w.stride(0), c_ld,
+                    _ptr(gather_flags), tp, shard_rows, seq, rank, _ptr(dst_ptrs), _ptr(local_done), _ptr(flag_ptrs),
+                    force_bn, _ptr(err), _stream()), "gemm_tp")
+    return out
+
+
+def tp_add_norm(src_ptr, slot_stride, n_src, src_flags_ptr, wait_seq, residual, residual_in, weight, eps, hidden, rows,
+                gather_ptrs, tp, rank, shard_rows, blk_done, gather_flag_ptrs, send_seq, err, dtype):
+    _check(_tp_add_norm(src_ptr, slot_stride, n_src, src_flags_ptr, wait_seq, residual.data_ptr(), residual_in,
+                        weight.data_ptr(), eps, hidden, rows, gather_ptrs.data_ptr(), tp, rank, shard_rows,
+                        blk_done.data_ptr(), gather_flag_ptrs.data_ptr(), send_seq, err.data_ptr(), _DT[dtype],
+                        _stream()), "tp_add_norm")
+
+
+def tp_wait(flags, tp, shard_rows, m, seq, err):
+    _check(_tp_wait(flags.data_ptr(), tp, shard_rows, m, seq, err.data_ptr(), _stream()), "tp_wait")
+
+
+def all_reduce(x, out, slot_ptrs, flag_ptrs, local_slots_ptr, local_flags_ptr, arrive, tp, rank, seq, err):
+    _check(_all_reduce(x.data_ptr(), out.data_ptr(), x.numel(), slot_ptrs.data_ptr(), flag_ptrs.data_ptr(),
+                       local_slots_ptr, local_flags_ptr, arrive.data_ptr(), tp, rank, seq, err.data_ptr(),
+                       _DT[x.dtype], _stream()), "all_reduce")
     return out
 
 

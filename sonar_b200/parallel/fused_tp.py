@@ -1,0 +1,224 @@
+"""Tensor parallelism with the collectives inside the kernels.
+
+Layout: between decoder blocks every rank holds only its own contiguous shard
+of the token rows (``[T/tp, H]`` hidden + residual).  One half-block is
+
+    row-parallel GEMM ──(epilogue stores partial tiles into the row owners' partial
+                         buffers over NVLink; per-destination completion flag)──▶
+    add+norm on the owner (sums the tp partials + residual, RMSNorm, stores the
+                         normalised rows into every rank's gather buffer; per-128-row
+                         block flags)──▶
+    column-parallel GEMM (TMA producer waits per row block on those flags, own
+                         rows first; operands are read from local memory only)
+
+so a reduce-scatter and an all-gather happen with no collective call and no
+extra pass over the activations.  Flags carry a launch sequence number that is
+identical on all ranks (every rank issues the same kernel sequence), so buffers
+are reused without resets; waits are bounded and surface through the device
+error word.
+
+``mode="custom"`` keeps the replicated layout and only swaps NCCL's all-reduce
+for the one-shot P2P kernel on small tensors (the reference's custom
+all-reduce strategy).
+
+Parity targets: ``compilation/passes/fusion/sequence_parallelism.py:153-250``,
+``collective_fusion.py:327-388`` (async-TP decomposition — the baseline this
+replaces) and ``device_communicators/custom_all_reduce.py``.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from sonar_b200 import ops
+from sonar_b200.layers.linear import UnquantizedMethod
+from sonar_b200.logger import init_logger
+from sonar_b200.parallel import state
+from sonar_b200.parallel.symm import SymmetricBuffer
+from sonar_b200.parallel.tp_ops import TPContext
+
+logger = init_logger(__name__)
+
+
+@dataclass
+class Partial:
+    """Row-parallel output in flight: partial tiles are landing in the owners' buffers."""
+    seq: int
+
+
+@dataclass
+class Gathered:
+    """Normalised activations landing in every rank's gather buffer."""
+    seq: int
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+class FusedTPContext(TPContext):
+    scattered = True
+
+    def __init__(self, hidden: int, max_tokens: int, dtype: torch.dtype, device: torch.device) -> None:
+        super().__init__()
+        from sonar_b200.ops import cuda as cu
+        self.cu = cu
+        self.device, self.dtype, self.H = device, dtype, hidden
+        tp, rank = self.world_size, self.rank
+        el = torch.empty((), dtype=dtype).element_size()
+        self.T_max = (max_tokens + tp - 1) // tp * tp
+        self.Tl_max = self.T_max // tp
+        self.n_blk = (self.T_max + 127) // 128 + 1
+        self.slot_elems = self.Tl_max * hidden
+        off = 0
+        self.off_partial = off
+        off += _align(tp * self.slot_elems * el)
+        self.off_gather = off
+        off += _align(self.T_max * hidden * el)
+        self.off_pflags = off
+        off += _align(tp * 4)
+        self.off_gflags = off
+        off += _align(self.n_blk * tp * 4)
+        self.off_ar = off                      # small all-reduce area: 2 sets × tp slots
+        self.ar_max = 1 << 20
+        off += _align(2 * tp * self.ar_max)
+        self.off_arflags = off
+        off += _align(2 * tp * 4)
+        self.buf = SymmetricBuffer(off, device, self.group.device_group, self.group.ranks)
+        b = self.buf
+        self.partial = b.view(self.off_partial, (tp, self.Tl_max, hidden), dtype)
+        self.gather = b.view(self.off_gather, (self.T_max, hidden), dtype)
+        self.pflags = b.view(self.off_pflags, (tp,), torch.int32)
+        self.gflags = b.view(self.off_gflags, (self.n_blk * tp,), torch.int32)
+        self.dst_ptrs = b.ptr_table(self.off_partial + rank * self.slot_elems * el)
+        self.pflag_ptrs = b.ptr_table(self.off_pflags + rank * 4)
+        self.gather_ptrs = b.ptr_table(self.off_gather)
+        self.gflag_ptrs = b.ptr_table(self.off_gflags)
+        self.ar_slot_ptrs = [b.ptr_table(self.off_ar + s * tp * self.ar_max) for s in range(2)]
+        self.ar_flag_ptrs = [b.ptr_table(self.off_arflags + s * tp * 4) for s in range(2)]
+        self.local_done = torch.zeros(tp, dtype=torch.int32, device=device)
+        self.blk_done = torch.zeros(self.n_blk, dtype=torch.int32, device=device)
+        self.ar_arrive = torch.zeros(1, dtype=torch.int32, device=device)
+        self.seq = 0
+        self.ar_seq = 0
+        self.T = self.T_pad = self.Tl = 0
+        self.err = cu.error_word(device)
+        logger.info("fused TP: tp=%d, %s peer memory, %.0f MiB symmetric heap%s", tp, b.backend, off / 2**20,
+                    ", NVSwitch multicast address available" if b.multicast_ptr else "")
+
+    # ------------------------------------------------------------------ step geometry
+    def begin_step(self, num_tokens: int) -> None:
+        tp = self.world_size
+        self.T = num_tokens
+        self.T_pad = (num_tokens + tp - 1) // tp * tp
+        self.Tl = self.T_pad // tp
+        if self.T_pad > self.T_max:
+            raise ValueError(f"{num_tokens} tokens exceed the fused-TP buffers sized for {self.T_max}")
+
+    def local_tokens(self, num_tokens: int) -> int:
+        return (num_tokens + self.world_size - 1) // self.world_size
+
+    def shard_token_ids(self, input_ids: torch.Tensor) -> torch.Tensor:
+        """This rank's contiguous shard of the (padded) token ids."""
+        lo = self.rank * self.Tl
+        hi = min(lo + self.Tl, self.T)
+        out = torch.zeros(self.Tl, dtype=input_ids.dtype, device=input_ids.device)
+        if hi > lo:
+            out[: hi - lo] = input_ids[lo:hi]
+        return out
+
+    def embed_reduce(self, partial: torch.Tensor) -> torch.Tensor:
+        return partial  # the embedding is replicated in this layout: local rows need no reduction
+
+    # ------------------------------------------------------------------ the three fused ops
+    def add_norm(self, h, residual, weight, eps):
+        cu, tp = self.cu, self.world_size
+        if isinstance(h, Partial):
+            src, stride, n_src, flags, wait_seq = self.partial.data_ptr(), self.slot_elems, tp, self.pflags.data_ptr(), h.seq
+        else:
+            assert h.shape[0] == self.Tl and h.is_contiguous()
+            src, stride, n_src, flags, wait_seq = h.data_ptr(), 0, 1, None, 0
+        res_in = 1
+        if residual is None:
+            residual = torch.empty((self.Tl, self.H), dtype=self.dtype, device=self.device)
+            res_in = 0
+        self.seq += 1
+        cu.tp_add_norm(src, stride, n_src, flags, wait_seq, residual, res_in, weight, eps, self.H, self.Tl,
+                       self.gather_ptrs, tp, self.rank, self.Tl, self.blk_done, self.gflag_ptrs, self.seq, self.err,
+                       self.dtype)
+        return Gathered(self.seq), residual
+
+    def col_linear(self, x, layer):
+        if not isinstance(x, Gathered):
+            return layer.apply(x)
+        if not isinstance(layer.method, UnquantizedMethod):
+            return layer.apply(self._materialize(x))
+        out = torch.empty((self.T_pad, layer.weight.shape[0]), dtype=self.dtype, device=self.device)
+        self.cu.gemm_tp(self.gather[: self.T_pad], layer.weight, out, gather_flags=self.gflags, tp=self.world_size,
+                        shard_rows=self.Tl, seq=x.seq, rank=self.rank, err=self.err)
+        if layer.bias is not None:
+            out += layer.bias
+        return out
+
+    def row_linear(self, x, layer):
+        assert x.shape[0] == self.T_pad, (x.shape, self.T_pad)
+        if not isinstance(layer.method, UnquantizedMethod) or layer.bias is not None:
+            y = layer.apply(x)
+            return self._push_partial(y)
+        self.seq += 1
+        self.cu.gemm_tp(x, layer.weight, None, n_out=layer.weight.shape[0], tp=self.world_size, shard_rows=self.Tl,
+                        seq=self.seq, rank=self.rank, dst_ptrs=self.dst_ptrs, local_done=self.local_done,
+                        flag_ptrs=self.pflag_ptrs, ldc=self.H, err=self.err)
+        return Partial(self.seq)
+
+    def _push_partial(self, y: torch.Tensor) -> torch.Tensor:
+        """Unfused fallback (quantised layers): NCCL reduce-scatter to the local shard."""
+        return self.group.reduce_scatter(y)
+
+    def _materialize(self, x: Gathered) -> torch.Tensor:
+        self.cu.tp_wait(self.gflags, self.world_size, self.Tl, self.T_pad, x.seq, self.err)
+        return self.gather[: self.T_pad]
+
+    def gather_tokens(self, h, num_tokens: int) -> torch.Tensor:
+        if isinstance(h, Gathered):
+            return self._materialize(h)[:num_tokens]
+        return self.group.all_gather(h, dim=0)[:num_tokens]
+
+    # ------------------------------------------------------------------ small all-reduce
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        nbytes = x.numel() * x.element_size()
+        if (nbytes > self.ar_max or x.dtype not in (torch.bfloat16, torch.float16) or x.numel() % 8
+                or not x.is_contiguous()):
+            return self.group.all_reduce(x)
+        self.ar_seq += 1
+        s = self.ar_seq & 1
+        slots = self.buf.local_ptr + self.off_ar + s * self.world_size * self.ar_max
+        flags = self.buf.local_ptr + self.off_arflags + s * self.world_size * 4
+        self.cu.all_reduce(x, x, self.ar_slot_ptrs[s], self.ar_flag_ptrs[s], slots, flags, self.ar_arrive,
+                           self.world_size, self.rank, self.ar_seq, self.err)
+        return x
+
+
+class CustomARContext(TPContext):
+    """Replicated layout; all-reduce by the one-shot P2P kernel when the tensor is small."""
+
+    def __init__(self, fused: FusedTPContext) -> None:
+        super().__init__()
+        self.f = fused
+
+    def embed_reduce(self, partial):
+        return self.f.all_reduce(partial) if self.world_size > 1 else partial
+
+    def row_linear(self, x, layer):
+        y = layer.apply(x)
+        return self.f.all_reduce(y) if self.world_size > 1 else y
+
+
+def make_context(cfg, device: torch.device, mode: str):
+    if state.get_pp_group().world_size > 1 and mode == "fused":
+        logger.info("pipeline parallelism keeps the replicated TP layout; using the P2P all-reduce")
+        mode = "custom"
+    fused = FusedTPContext(cfg.model.hidden_size, cfg.scheduler.max_num_batched_tokens, cfg.model.dtype, device)
+    return fused if mode == "fused" else CustomARContext(fused)

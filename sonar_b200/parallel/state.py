@@ -78,10 +78,11 @@ class GroupCoordinator:
         if self.world_size == 1:
             return x
         x = x.contiguous()
-        out = torch.empty((self.world_size,) + tuple(x.shape), dtype=x.dtype, device=x.device)
-        dist.all_gather_into_tensor(out, x, group=self.device_group)
+        flat = torch.empty((self.world_size * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(flat, x, group=self.device_group)
         if dim == 0:
-            return out.reshape((-1,) + tuple(x.shape[1:]))
+            return flat
+        out = flat.view((self.world_size,) + tuple(x.shape))
         dim = dim % x.dim()
         return out.movedim(0, dim).reshape(x.shape[:dim] + (self.world_size * x.shape[dim],) + x.shape[dim + 1:])
 

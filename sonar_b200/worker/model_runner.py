@@ -144,7 +144,7 @@ class ModelRunner:
         self.h_bt_np = self.h_bt.numpy()
         self._pending: dict[str, Any] | None = None
         self.graphs: dict[int, Any] = {}
-        self.stats = {"steps": 0, "prep_s": 0.0, "h2d_bytes": 0, "d2h_bytes": 0}
+        self.stats = {"steps": 0, "prep_s": 0.0, "launch_s": 0.0, "sample_s": 0.0, "h2d_bytes": 0, "d2h_bytes": 0}
         pp = state.get_pp_group() if state.model_parallel_is_initialized() else None
         self.pp = pp if pp is not None and pp.world_size > 1 else None
         self.spec_cfg = cfg.speculative
@@ -292,12 +292,17 @@ class ModelRunner:
         ids = self.d_input_ids[:total]
         if self.pp is not None and not self.pp.is_first_rank:
             intermediate = self._recv_intermediate(tp.local_tokens(total))
+        t1 = time.perf_counter()
         out = self.model(ids, meta, intermediate)
+        self.stats["launch_s"] += time.perf_counter() - t1
         if self.pp is not None and not self.pp.is_last_rank:
             self._send_intermediate(out)
             return None
         hidden = tp.gather_tokens(out, total)
-        return self._sample(so, hidden, meta, rows, q_lens)
+        t2 = time.perf_counter()
+        res = self._sample(so, hidden, meta, rows, q_lens)
+        self.stats["sample_s"] += time.perf_counter() - t2
+        return res
 
     def _send_intermediate(self, out) -> None:
         h, r = out

@@ -1,0 +1,14 @@
+"""Tensor-parallel sharding and the replicated-layout collectives on CPU ranks (gloo, world size 2)."""
+import torch
+
+from tp_common import launch, make_checkpoint
+
+
+def test_tp2_matches_tp1_on_cpu(tmp_path):
+    ckpt = make_checkpoint(str(tmp_path / "ckpt"), "tiny-llama", dtype=torch.float32)
+    one = launch(1, ckpt, str(tmp_path / "tp1.json"), "cpu")
+    two = launch(2, ckpt, str(tmp_path / "tp2.json"), "cpu", port=29613)
+    for a, b in zip(one, two):
+        assert a["tokens"] == b["tokens"]
+        d = (torch.tensor(a["prompt_logprobs"]) - torch.tensor(b["prompt_logprobs"])).abs().max()
+        assert d < 1e-3, d

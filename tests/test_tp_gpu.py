@@ -1,0 +1,31 @@
+"""Tensor parallelism on 2 GPUs: the fused GEMM+collective path, the P2P all-reduce path and the NCCL
+baseline must all reproduce the single-GPU numbers.  Ranks are child processes; NVLS is off."""
+import pytest
+import torch
+
+from tp_common import launch, make_checkpoint
+
+pytestmark = pytest.mark.gpu
+
+needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+
+
+@pytest.fixture(scope="module")
+def baseline(tmp_path_factory):
+    d = tmp_path_factory.mktemp("tp")
+    ckpt = make_checkpoint(str(d / "ckpt"), "tiny-llama-128")
+    one = launch(1, ckpt, str(d / "tp1.json"), "cuda")
+    return d, ckpt, one
+
+
+@needs2
+@pytest.mark.parametrize("mode", ["fused", "custom", "nccl"])
+def test_tp2_matches_tp1(baseline, mode):
+    d, ckpt, one = baseline
+    two = launch(2, ckpt, str(d / f"tp2_{mode}.json"), "cuda",
+                 env_extra={"SONAR_TP_COMM": mode, "NCCL_NVLS_ENABLE": "0"}, port=29621 + len(mode))
+    worst = 0.0
+    for a, b in zip(one, two):
+        diff = (torch.tensor(a["prompt_logprobs"]) - torch.tensor(b["prompt_logprobs"])).abs().max().item()
+        worst = max(worst, diff)
+    assert worst < 0.1, worst

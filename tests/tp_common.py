@@ -1,0 +1,54 @@
+"""Helpers shared by the tensor-parallel tests: a tiny HF-layout checkpoint and a rank launcher."""
+import json
+import os
+import subprocess
+import sys
+
+import torch
+
+from sonar_b200.config import ARCH_PRESETS
+from sonar_b200.loader.weights import save_checkpoint
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def make_checkpoint(directory: str, preset: str = "tiny-llama-128", dtype=torch.bfloat16, seed: int = 0) -> str:
+    cfg = dict(ARCH_PRESETS[preset])
+    g = torch.Generator().manual_seed(seed)
+    h, inter, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    hd, hq, hk = cfg["head_dim"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
+
+    def w(*shape, std=0.05):
+        return (torch.randn(*shape, generator=g) * std).to(dtype)
+    t = {"model.embed_tokens.weight": w(v, h, std=0.5), "model.norm.weight": (1 + 0.1 * torch.randn(h, generator=g)).to(dtype),
+         "lm_head.weight": w(v, h)}
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        t[p + "self_attn.q_proj.weight"] = w(hq * hd, h)
+        t[p + "self_attn.k_proj.weight"] = w(hk * hd, h)
+        t[p + "self_attn.v_proj.weight"] = w(hk * hd, h)
+        t[p + "self_attn.o_proj.weight"] = w(h, hq * hd)
+        t[p + "mlp.gate_proj.weight"] = w(inter, h)
+        t[p + "mlp.up_proj.weight"] = w(inter, h)
+        t[p + "mlp.down_proj.weight"] = w(h, inter)
+        t[p + "input_layernorm.weight"] = (1 + 0.1 * torch.randn(h, generator=g)).to(dtype)
+        t[p + "post_attention_layernorm.weight"] = (1 + 0.1 * torch.randn(h, generator=g)).to(dtype)
+    save_checkpoint(directory, cfg, t)
+    return directory
+
+
+def launch(world: int, ckpt: str, out: str, device: str, env_extra=None, port: int = 29611, timeout: int = 600):
+    env = dict(os.environ)
+    env.update(env_extra or {})
+    env.setdefault("SONAR_LOG_LEVEL", "WARNING")
+    worker = os.path.join(HERE, "tp_worker.py")
+    if world == 1:
+        cmd = [sys.executable, worker, ckpt, out, device]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+               "--master-addr", "127.0.0.1", "--master-port", str(port), worker, ckpt, out, device]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    if res.returncode != 0:
+        raise RuntimeError(f"rank program failed ({res.returncode}):\n{res.stdout[-3000:]}\n{res.stderr[-6000:]}")
+    with open(out) as f:
+        return json.load(f)

@@ -1,0 +1,55 @@
+"""Rank program for the multi-process tensor-parallel tests (launched by torch.distributed.run).
+
+usage: tp_worker.py <checkpoint dir> <output json> [device]
+Every rank builds the engine with tensor_parallel_size = WORLD_SIZE, runs a fixed greedy workload with
+prompt logprobs, and rank 0 writes the results.
+"""
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch  # noqa: E402
+
+from sonar_b200 import LLM, SamplingParams  # noqa: E402
+
+
+def prompts():
+    g = torch.Generator().manual_seed(7)
+    return [torch.randint(4, 1000, (int(torch.randint(20, 200, (1,), generator=g)),), generator=g).tolist()
+            for _ in range(6)]
+
+
+def run(ckpt: str, device: str, world: int):
+    dtype = "bfloat16" if device == "cuda" else "float32"
+    llm = LLM(ckpt, dtype=dtype, max_model_len=512, max_num_seqs=8, max_num_batched_tokens=160,
+              gpu_memory_utilization=0.05, skip_tokenizer_init=True, tensor_parallel_size=world, device=device,
+              num_gpu_blocks_override=512 if device == "cpu" else None,
+              distributed_executor_backend="external_launcher" if world > 1 else "uni")
+    sp = SamplingParams(temperature=0, max_tokens=4, prompt_logprobs=0, ignore_eos=True, detokenize=False)
+    outs = llm.generate([{"prompt_token_ids": p} for p in prompts()], sp)
+    res = []
+    for o, p in zip(outs, prompts()):
+        lps = [o.prompt_logprobs[i][p[i]].logprob for i in range(1, len(p))]
+        res.append({"tokens": o.outputs[0].token_ids, "prompt_logprobs": lps})
+    if device == "cuda":
+        from sonar_b200.ops import cuda as cu
+        torch.cuda.synchronize()
+        cu.check_device_errors()
+    llm.shutdown()
+    return res
+
+
+if __name__ == "__main__":
+    ckpt, out = sys.argv[1], sys.argv[2]
+    device = sys.argv[3] if len(sys.argv) > 3 else ("cuda" if torch.cuda.is_available() else "cpu")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    res = run(ckpt, device, world)
+    if int(os.environ.get("RANK", "0")) == 0:
+        with open(out, "w") as f:
+            json.dump(res, f)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()

@@ -186,9 +186,12 @@ def main() -> None:
     t_host0 = time.perf_counter()
     steps = 0
     out_tokens = 0
+    step_log: list[tuple[float, int]] = []
     core = engine.core.engine_core
     while engine.has_unfinished_requests() and (args.steps == 0 or steps < args.steps):
+        t_s = time.perf_counter()
         outs = core.step()
+        step_log.append((time.perf_counter() - t_s, len(outs.outputs)))
         steps += 1
         out_tokens += sum(len(o.new_token_ids) for o in outs.outputs)
         engine.output_processor.process_outputs(outs.outputs)
@@ -232,6 +235,9 @@ def main() -> None:
                "h2d_bytes_per_step": (runner.stats["h2d_bytes"] - h2d0) // n_steps,
                "d2h_bytes_per_step": (runner.stats["d2h_bytes"] - d2h0) // n_steps}
 
+    if rank == 0 and os.environ.get("SONAR_BENCH_STEPLOG"):
+        with open(os.environ["SONAR_BENCH_STEPLOG"], "w") as f:
+            json.dump([[round(t * 1e3, 3), n] for t, n in step_log], f)
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps,

@@ -71,9 +71,15 @@ struct GemmParams {
   long ldc;
   const void* bias;   // [N] or null (same dtype as C when C is 16-bit, fp32 when C is fp32)
   int* err;           // device error word
+  float* ws;          // stream-K workspace: gridDim.x partial tiles of 128×BN fp32 (null: whole-tile ranges)
+  int* ws_flags;      // [gridDim.x] partial-ready flags, zero between launches
+  int ws_ctas;        // workspace capacity in CTAs
+  int sk_tiles, sk_split; // split-K tail: the last sk_tiles tiles are each split over sk_split CTAs (0: none)
+  int* ws_count;          // [sk_tiles] arrival counters of the split tiles, zero between launches
   // gather wait
   const int* gather_flags;  // [num_m_blocks * tp] local flags, or null
   int tp, shard_rows, seq, m_rot;
+  const int* seq_base;      // device word added to `seq` (lets a captured graph advance sequence numbers)
   // scatter epilogue
   void* const* dst_ptrs;    // [tp] destination bases (peer mappings), or null
   int* local_done;          // [tp] local arrival counters (zero between launches)
@@ -138,16 +144,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * C::STAGES + 2 + b); };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* epi_ctr = reinterpret_cast<int*>(tmem_slot + 2);   // two warp-arrival counters of the epilogue
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (p.K + BK - 1) / BK;
+  const int seq_now = p.seq + (p.seq_base ? *p.seq_base : 0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { tc::mbar_init(full_bar(s), 1); tc::mbar_init(empty_bar(s), 1); }
     for (int b = 0; b < 2; ++b) { tc::mbar_init(tfull_bar(b), 1); tc::mbar_init(tempty_bar(b), 128); }
     *abort_flag = 0;
+    epi_ctr[0] = epi_ctr[1] = 0;
     tc::mbar_fence_init();
   }
   if (warp == 1) tc::tmem_alloc(tc::smem_u32(tmem_slot), C::TMEM_COLS);
@@ -156,6 +165,41 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   tc::fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  // ---- work split: whole waves of tiles are handed out round-robin (tile = cta + i·grid, so CTAs
+  // that run together work on neighbouring tiles and share operand tiles in L2).  The last, partial
+  // wave (sk_tiles tiles) is split along K: tile j of it goes to the sk_split consecutive CTAs
+  // j·S … j·S+S-1, part s taking k-blocks [s·kbs, (s+1)·kbs).  Every part parks its fp32 partial
+  // accumulator in the workspace, the parts meet on a per-tile counter, and each then reduces and
+  // stores its own share of the tile's 32-column chunks (chunk ch belongs to part ch mod S), so the
+  // fix-up is spread over all S CTAs instead of serialised on one.
+  const int S = p.sk_split;
+  const int dp_waves = p.sk_tiles > 0 ? (num_tiles - p.sk_tiles) / (int)gridDim.x : (num_tiles + gridDim.x - 1) / gridDim.x;
+  const int sk_tile0 = num_tiles - p.sk_tiles;
+  const bool in_sk = p.sk_tiles > 0 && (int)blockIdx.x < p.sk_tiles * S;
+  const int sk_j = in_sk ? (int)blockIdx.x / S : 0, sk_s = in_sk ? (int)blockIdx.x % S : 0;
+  const int kbs = S > 0 ? (num_kb + S - 1) / S : num_kb;
+  // segment iterator shared by the three roles: whole tiles first, then this CTA's split-K part
+  struct Seg { int tile, kb0, kb1; bool split; };
+  auto next_seg = [&](int& wave, long& g, Seg& sg) -> bool {
+    while (wave < dp_waves) {
+      const int t = (int)blockIdx.x + wave * (int)gridDim.x;
+      ++wave;
+      if (t >= (p.sk_tiles > 0 ? sk_tile0 : num_tiles)) continue;
+      sg.tile = t; sg.kb0 = 0; sg.kb1 = num_kb; sg.split = false;
+      return true;
+    }
+    if (in_sk && g == 0) {
+      g = 1;
+      sg.tile = sk_tile0 + sk_j;
+      sg.kb0 = min(num_kb, sk_s * kbs);
+      sg.kb1 = min(num_kb, sg.kb0 + kbs);
+      sg.split = true;
+      return true;   // an empty k range (kb0 == kb1) still takes part in the fix-up with a zero partial
+    }
+    return false;
+  };
+  const long sk_begin = 0;
+
   if (warp == 0) {
     // ------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -163,7 +207,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       tc::tma_prefetch_desc(&tma_b);
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int wave = 0;
+      long g = sk_begin;
+      Seg sg;
+      while (ok && next_seg(wave, g, sg)) {
+        const int tile = sg.tile, kb0 = sg.kb0, kb1 = sg.kb1;
         const int m_idx = (tile % num_m + p.m_rot) % num_m, n_idx = tile / num_m;
         if (p.gather_flags != nullptr) {
           // bounded wait until every source rank of this row block has published this launch's sequence number
@@ -173,7 +221,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             auto arrived = [&]() {
               int v;
               asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-              return (v - p.seq) >= 0;
+              return (v - seq_now) >= 0;
             };
             if (arrived()) continue;
             const uint64_t t0 = globaltimer_ns();
@@ -194,7 +242,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           // the acquire loads order the peers' row stores before the TMA (async proxy) reads below
           asm volatile("fence.proxy.async;" ::: "memory");
         }
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1;
           if (!tc::mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.err, tc::SITE_EMPTY)) { ok = false; break; }
@@ -209,15 +257,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     // ------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = tc::make_idesc_f16(BM, BN, AB_FMT);
-      uint32_t it = 0, t_local = 0;
+      uint32_t it = 0, seg = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t_local) {
-        const int buf = t_local & 1;
-        const uint32_t bph = (t_local >> 1) & 1;
+      int wave = 0;
+      long g = sk_begin;
+      Seg sg;
+      for (; ok && next_seg(wave, g, sg); ++seg) {
+        const int kb0 = sg.kb0, kb1 = sg.kb1;
+        const int buf = seg & 1;
+        const uint32_t bph = (seg >> 1) & 1;
         if (!tc::mbar_wait(tempty_bar(buf), bph ^ 1, abort_flag, p.err, tc::SITE_TMEM_EMPTY)) break;
         tc::fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1;
           if (!tc::mbar_wait(full_bar(s), ph, abort_flag, p.err, tc::SITE_FULL)) { ok = false; break; }
@@ -228,7 +280,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             // +32 bytes per 16-element K step inside the 128-byte swizzled row
-            tc::mma_f16(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+            tc::mma_f16(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > kb0) | (k > 0));
           }
           tc::mma_commit(empty_bar(s));
         }
@@ -238,14 +290,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   } else {
     // ------------------------------------------------ epilogue (warps 2..5 ↔ TMEM lane groups 2,3,0,1)
     const int lane_grp = warp & 3;
-    uint32_t t_local = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t_local) {
+    const int trow = lane_grp * 32 + lane;          // row inside the tile
+    uint32_t seg = 0;
+    bool ok = true;
+    int wave = 0;
+    long g = sk_begin;
+    Seg sg;
+    for (; ok && next_seg(wave, g, sg); ++seg) {
+      const int tile = sg.tile;
       const int m_idx = (tile % num_m + p.m_rot) % num_m, n_idx = tile / num_m;
-      const int buf = t_local & 1;
-      const uint32_t bph = (t_local >> 1) & 1;
+      const int buf = seg & 1;
+      const uint32_t bph = (seg >> 1) & 1;
       if (!tc::mbar_wait(tfull_bar(buf), bph, abort_flag, p.err, tc::SITE_TMEM_FULL)) break;
       tc::fence_after_sync();
-      const int row = m_idx * BM + lane_grp * 32 + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + buf * BN;
+      const int row = m_idx * BM + trow;
       const int n0 = n_idx * BN;
       OutT* crow = nullptr;
       if (row < p.M) {
@@ -256,36 +315,124 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           crow = reinterpret_cast<OutT*>(p.C) + (long)row * p.ldc;
         }
       }
-      const uint32_t t_row = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + buf * BN;
+      int chunks_stored = BN / 32;
+      if (!sg.split) {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tc::tmem_ld32(t_row + c * 32, v);
-        tc::tmem_ld_wait();
-        const int col = n0 + c * 32;
-        if (crow != nullptr && col < p.N) {
-          const OutT* b = p.bias ? reinterpret_cast<const OutT*>(p.bias) + col : nullptr;
-          store32<OutT>(crow + col, v, b, min(32, p.N - col));
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tc::tmem_ld32(t_row + c * 32, v);
+          tc::tmem_ld_wait();
+          const int col = n0 + c * 32;
+          if (crow != nullptr && col < p.N) {
+            const OutT* b = p.bias ? reinterpret_cast<const OutT*>(p.bias) + col : nullptr;
+            store32<OutT>(crow + col, v, b, min(32, p.N - col));
+          }
         }
-      }
-      tc::fence_before_sync();
-      tc::mbar_arrive(tempty_bar(buf));
-      if (p.dst_ptrs != nullptr) {
-        // publish: every lane fences its stores; one arrival per warp per destination the tile touches;
-        // the arrival completing a destination's share (4 warps × its tiles) sends the flag
-        __threadfence_system();
+        tc::fence_before_sync();
+        tc::mbar_arrive(tempty_bar(buf));
+      } else {
+        // ---- split-K part: park the fp32 partial ([chunk][row][32] layout, 128 B per thread per chunk),
+        // except the chunks this part reduces itself (those stay in TMEM)
+        float* ws_tile = p.ws + (long)(sk_j * S) * (BM * BN);
+        float* ws_mine = ws_tile + (long)sk_s * (BM * BN);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          if (c % S == sk_s) continue;
+          uint32_t v[32];
+          tc::tmem_ld32(t_row + c * 32, v);
+          tc::tmem_ld_wait();
+          float4* dst = reinterpret_cast<float4*>(ws_mine + ((long)c * BM + trow) * 32);
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            dst[q] = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                                 __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+        }
+        // meet the other parts: one release-arrival per warp, then a bounded wait for all 4·S of them
+        int* cnt = p.ws_count + sk_j;
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(cnt) : "memory");
+        {
+          auto all_here = [&]() {
+            int v;
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
+            return v >= 4 * S;
+          };
+          if (!all_here()) {
+            const uint64_t t0 = globaltimer_ns();
+            uint32_t spins = 0;
+            while (!all_here()) {
+              if ((++spins & 63u) == 0) {
+                if (*abort_flag) { ok = false; break; }
+                if (globaltimer_ns() - t0 > tc::WAIT_LIMIT_NS) {
+                  *abort_flag = 1;
+                  if (p.err) atomicCAS(p.err, 0, tc::SITE_WS | (blockIdx.x << 8));
+                  ok = false;
+                  break;
+                }
+              }
+            }
+          }
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
+        // ---- reduce and store this part's chunks: own partial from TMEM + the other parts' from the workspace
+        chunks_stored = 0;
+#pragma unroll 1
+        for (int c = sk_s; c < BN / 32; c += S) {
+          uint32_t v[32];
+          tc::tmem_ld32(t_row + c * 32, v);
+          tc::tmem_ld_wait();
+          float acc[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) acc[e] = __uint_as_float(v[e]);
+          for (int q = 1; q < S; ++q) {
+            const int other = (sk_s + q) % S;
+            const float4* src = reinterpret_cast<const float4*>(ws_tile + (long)other * (BM * BN) + ((long)c * BM + trow) * 32);
+            float4 w4[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) w4[e] = __ldcg(src + e);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              acc[4 * e] += w4[e].x; acc[4 * e + 1] += w4[e].y; acc[4 * e + 2] += w4[e].z; acc[4 * e + 3] += w4[e].w;
+            }
+          }
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(acc[e]);
+          const int col = n0 + c * 32;
+          if (crow != nullptr && col < p.N) {
+            const OutT* b = p.bias ? reinterpret_cast<const OutT*>(p.bias) + col : nullptr;
+            store32<OutT>(crow + col, v, b, min(32, p.N - col));
+          }
+          ++chunks_stored;
+        }
+        tc::fence_before_sync();
+        tc::mbar_arrive(tempty_bar(buf));
+        // second round of arrivals: the last warp of the last part hands the counter back for the next launch
         __syncwarp();
         if (lane == 0) {
+          int prev;
+          asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(prev) : "l"(cnt) : "memory");
+          if (prev + 1 == 8 * S) *cnt = 0;
+        }
+      }
+      if (p.dst_ptrs != nullptr) {
+        // publish: every lane fences its stores; each warp adds the number of 32-column chunks it stored
+        // to the counter of every destination the tile touches; the arrival completing a destination's
+        // share (4 warps × chunks per tile × its tiles) sends the flag
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0 && chunks_stored > 0) {
           const int r_lo = m_idx * BM, r_hi = min(p.M, r_lo + BM) - 1;
           for (int d = r_lo / p.shard_rows; d <= r_hi / p.shard_rows; ++d) {
             const int d_lo = d * p.shard_rows, d_hi = min(p.M, d_lo + p.shard_rows) - 1;
-            const int expected = 4 * num_n * (d_hi / BM - d_lo / BM + 1);
+            const int expected = 4 * (BN / 32) * num_n * (d_hi / BM - d_lo / BM + 1);
             int prev;
-            asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(prev) : "l"(p.local_done + d) : "memory");
-            if (prev + 1 == expected) {
+            asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(prev) : "l"(p.local_done + d), "r"(chunks_stored) : "memory");
+            if (prev + chunks_stored == expected) {
               p.local_done[d] = 0;
               __threadfence_system();
-              asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.flag_ptrs[d]), "r"(p.seq) : "memory");
+              asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.flag_ptrs[d]), "r"(seq_now) : "memory");
             }
           }
         }
@@ -354,7 +501,31 @@ int num_sms() {
 // Tile width by a small cost model: waves × measured relative cost of one 128×BN tile pass
 // (a 128×256 tile runs the tensor pipe near its peak; narrower tiles re-read A from shared memory
 // per fewer columns and reach ≈70 % / ≈40 % of that rate, so they only win when they save waves).
-int pick_bn(int M, int N) {
+int pick_bn(int M, int N, bool stream_k) {
+  if (stream_k) {
+    // whole waves cost one tile time each; the partial last wave is split along K over up to 8 CTAs
+    // per tile and pays a fix-up that grows with the number of partials the finisher sums
+    const int sms = num_sms();
+    const int num_m = (M + BM - 1) / BM;
+    const int bns[3] = {256, 128, 64};
+    const double per_tile[3] = {1.0, 0.725, 0.66};
+    int best = 256;
+    double best_cost = 1e30;
+    for (int i = 0; i < 3; ++i) {
+      const int tiles = num_m * ((N + bns[i] - 1) / bns[i]);
+      const int full = tiles / sms, rem = tiles % sms;
+      double cost = full * per_tile[i];
+      if (rem) {
+        int split = sms / rem;
+        if (split > 8) split = 8;
+        if (split > bns[i] / 32) split = bns[i] / 32;
+        if (split < 1) split = 1;
+        cost += per_tile[i] * (1.0 / split + (split > 1 ? 0.08 : 0.0));
+      }
+      if (cost < best_cost - 1e-9) { best_cost = cost; best = bns[i]; }
+    }
+    return best;
+  }
   const int sms = num_sms();
   const int num_m = (M + BM - 1) / BM;
   int best = 256;
@@ -381,8 +552,30 @@ int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p
     attr_done = true;
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-  const int grid = tiles < num_sms() ? tiles : num_sms();
-  kern<<<grid, NUM_THREADS, C::SMEM, s>>>(ta, tb, p);
+  const int num_kb = (p.K + BK - 1) / BK;
+  GemmParams q = p;
+  const int sms = num_sms();
+  const int grid = tiles < sms ? tiles : sms;
+  int launch_grid = grid;
+  q.sk_tiles = q.sk_split = 0;
+  q.ws_count = q.ws_flags;
+  const int rem = tiles % sms;
+  if (q.ws != nullptr && rem != 0) {
+    // split-K for the partial last wave: S parts per tile, S ≤ 8, ≤ chunks per tile, every part non-empty
+    int S = sms / rem;
+    if (S > 8) S = 8;
+    if (S > BN / 32) S = BN / 32;
+    if (S > num_kb / 2) S = num_kb / 2;
+    while (S > 1 && (S - 1) * ((num_kb + S - 1) / S) >= num_kb) --S;
+    while (S > 1 && rem * S > q.ws_ctas) --S;
+    if (S > 1) {
+      q.sk_tiles = rem;
+      q.sk_split = S;
+      launch_grid = tiles >= sms ? sms : rem * S;
+    }
+  }
+  if (q.sk_tiles == 0) q.ws = nullptr;
+  kern<<<launch_grid, NUM_THREADS, C::SMEM, s>>>(ta, tb, q);
   return check_launch();
 }
 
@@ -406,15 +599,19 @@ using namespace sonar;
 // C = A · B^T (+ bias).  in_dtype: bf16/f16 for A and B; out_dtype: same 16-bit type or fp32.
 // Requirements: K % 8 == 0 (16-byte row pitch), N % 8 == 0 (N % 4 for fp32 out), 16-byte aligned bases.
 // err: optional device int that receives a wait-site code if a pipeline wait timed out.
+// ws / ws_flags / ws_ctas: optional stream-K workspace (ws_ctas × 128 × 256 floats, ws_ctas zeroed ints) shared
+// by all launches of one stream; launches that use it must not overlap on the GPU.
 SONAR_API int sonar_gemm(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long lda,
-                         long ldb, long ldc, int in_dtype, int out_dtype, int force_bn, int* err, cudaStream_t s) {
+                         long ldb, long ldc, int in_dtype, int out_dtype, int force_bn, int* err, float* ws,
+                         int* ws_flags, int ws_ctas, cudaStream_t s) {
   if (M <= 0 || N <= 0 || K <= 0) return M == 0 ? SONAR_OK : SONAR_BAD_ARG;
   if (K % 8 || lda % 8 || ldb % 8) return SONAR_BAD_ARG;
   if ((out_dtype == SONAR_F32 ? (N % 4 || ldc % 4) : (N % 8 || ldc % 8)) || ((uintptr_t)C & 15)) return SONAR_BAD_ARG;
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.bias = bias; p.err = err;
   p.tp = 1; p.shard_rows = M;
-  const int bn = force_bn ? force_bn : pick_bn(M, N);
+  p.ws = ws; p.ws_flags = ws_flags; p.ws_ctas = ws_ctas;
+  const int bn = force_bn ? force_bn : pick_bn(M, N, ws != nullptr);
   if (bn != 64 && bn != 128 && bn != 256) return SONAR_BAD_ARG;
   if (in_dtype == SONAR_BF16) {
     if (out_dtype == SONAR_BF16) return launch_bn<__nv_bfloat16, 1>(bn, A, B, p, lda, ldb, s);
@@ -430,20 +627,21 @@ SONAR_API int sonar_gemm(const void* A, const void* B, void* C, const void* bias
 // (flags hold the sequence number of the launch that filled them).  dst_ptrs != null: scatter epilogue
 // into the peers' partial buffers with completion flags (see the file header).
 SONAR_API int sonar_gemm_tp(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc,
-                            const int* gather_flags, int tp, int shard_rows, int seq, int rank,
+                            const int* gather_flags, int tp, int shard_rows, int seq, const int* seq_base, int rank,
                             void* const* dst_ptrs, int* local_done, int* const* flag_ptrs, int force_bn, int* err,
-                            cudaStream_t s) {
+                            float* ws, int* ws_flags, int ws_ctas, cudaStream_t s) {
   if (M <= 0 || N <= 0 || K <= 0) return SONAR_BAD_ARG;
   if (K % 8 || lda % 8 || ldb % 8 || N % 8 || ldc % 8) return SONAR_BAD_ARG;
   if (tp < 1 || shard_rows <= 0 || (long)tp * shard_rows < M) return SONAR_BAD_ARG;
   if (dst_ptrs != nullptr && (!local_done || !flag_ptrs)) return SONAR_BAD_ARG;
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.err = err;
-  p.gather_flags = gather_flags; p.tp = tp; p.shard_rows = shard_rows; p.seq = seq;
+  p.gather_flags = gather_flags; p.tp = tp; p.shard_rows = shard_rows; p.seq = seq; p.seq_base = seq_base;
   p.m_rot = gather_flags ? (int)(((long)rank * shard_rows) / BM) : 0;
   p.dst_ptrs = dst_ptrs; p.local_done = local_done; p.flag_ptrs = flag_ptrs;
-  const int bn = force_bn ? force_bn : pick_bn(M, N);
+  p.ws = ws; p.ws_flags = ws_flags; p.ws_ctas = ws_ctas;
+  const int bn = force_bn ? force_bn : pick_bn(M, N, ws != nullptr);
   return launch_bn<__nv_bfloat16, 1>(bn, A, B, p, lda, ldb, s);
 }
 
-SONAR_API int sonar_gemm_pick_bn(int M, int N) { return pick_bn(M, N); }
+SONAR_API int sonar_gemm_pick_bn(int M, int N, int stream_k) { return pick_bn(M, N, stream_k != 0); }

@@ -15,7 +15,7 @@ namespace tc {
 // flag in shared memory; every role polls the flag, leaves its loop, joins the final barrier, frees
 // TMEM and returns, so the context stays usable and the host sees the code.
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
-enum WaitSite : int { SITE_EMPTY = 1, SITE_FULL = 2, SITE_TMEM_FULL = 3, SITE_TMEM_EMPTY = 4, SITE_FLAG = 5 };
+enum WaitSite : int { SITE_EMPTY = 1, SITE_FULL = 2, SITE_TMEM_FULL = 3, SITE_TMEM_EMPTY = 4, SITE_FLAG = 5, SITE_WS = 6 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

@@ -60,6 +60,7 @@ struct AddNormParams {
   int* blk_done;            // local per-block counters
   int* const* gather_flag_ptrs;  // [tp] bases of every rank's gather flag array
   int send_seq;
+  const int* seq_base;      // device word added to wait_seq / send_seq
   int* err;
 };
 
@@ -68,10 +69,11 @@ __global__ void __launch_bounds__(1024) tp_add_norm_kernel(const AddNormParams p
   __shared__ float red[32];
   __shared__ int ok_s;
   const int i = blockIdx.x;
+  const int base = p.seq_base ? *p.seq_base : 0;
   if (threadIdx.x == 0) ok_s = 1;
   __syncthreads();
   if (p.src_flags != nullptr && threadIdx.x < p.n_src) {
-    if (!wait_flag(p.src_flags + threadIdx.x, p.wait_seq, p.err, 5 | (blockIdx.x << 8))) ok_s = 0;
+    if (!wait_flag(p.src_flags + threadIdx.x, p.wait_seq + base, p.err, 5 | (blockIdx.x << 8))) ok_s = 0;
   }
   __syncthreads();
   if (!ok_s) return;
@@ -136,12 +138,14 @@ __global__ void __launch_bounds__(1024) tp_add_norm_kernel(const AddNormParams p
     if (prev + 1 == expected) {
       p.blk_done[b] = 0;
       __threadfence_system();
-      for (int q = 0; q < p.tp; ++q) st_release_sys(p.gather_flag_ptrs[q] + b * p.tp + p.rank, p.send_seq);
+      for (int q = 0; q < p.tp; ++q) st_release_sys(p.gather_flag_ptrs[q] + b * p.tp + p.rank, p.send_seq + base);
     }
   }
 }
 
-__global__ void tp_wait_kernel(const int* flags, int n_blocks, int tp, int shard_rows, int M, int seq, int* err) {
+__global__ void tp_wait_kernel(const int* flags, int n_blocks, int tp, int shard_rows, int M, int seq,
+                               const int* seq_base, int* err) {
+  if (seq_base) seq += *seq_base;
   for (int idx = threadIdx.x; idx < n_blocks * tp; idx += blockDim.x) {
     const int b = idx / tp, src = idx % tp;
     const long r_lo = (long)b << 7, r_hi = min((long)M, r_lo + 128) - 1;
@@ -219,10 +223,11 @@ using namespace sonar;
 SONAR_API int sonar_tp_add_norm(const void* src, long slot_stride, int n_src, const int* src_flags, int wait_seq,
                                 void* residual, int residual_in, const void* weight, float eps, int H, int rows,
                                 void* const* gather_ptrs, int tp, int rank, int shard_rows, int* blk_done,
-                                int* const* gather_flag_ptrs, int send_seq, int* err, int dtype, cudaStream_t s) {
+                                int* const* gather_flag_ptrs, int send_seq, const int* seq_base, int* err, int dtype,
+                                cudaStream_t s) {
   if (H % 8 || rows <= 0 || rows > shard_rows || n_src < 1 || n_src > 32) return SONAR_BAD_ARG;
   AddNormParams p{src, slot_stride, n_src, src_flags, wait_seq, residual, residual_in, weight, eps, H, rows,
-                  gather_ptrs, tp, rank, shard_rows, blk_done, gather_flag_ptrs, send_seq, err};
+                  gather_ptrs, tp, rank, shard_rows, blk_done, gather_flag_ptrs, send_seq, seq_base, err};
   const int nvec = H / 8;
   int threads = nvec >= 1024 ? 1024 : ((nvec + 31) / 32) * 32;
   if (nvec > 256 && nvec <= 1024) threads = ((nvec / 2 + 31) / 32) * 32;
@@ -237,9 +242,10 @@ SONAR_API int sonar_tp_add_norm(const void* src, long slot_stride, int n_src, co
   });
 }
 
-SONAR_API int sonar_tp_wait(const int* flags, int tp, int shard_rows, int M, int seq, int* err, cudaStream_t s) {
+SONAR_API int sonar_tp_wait(const int* flags, int tp, int shard_rows, int M, int seq, const int* seq_base, int* err,
+                            cudaStream_t s) {
   const int n_blocks = (M + 127) / 128;
-  tp_wait_kernel<<<1, 256, 0, s>>>(flags, n_blocks, tp, shard_rows, M, seq, err);
+  tp_wait_kernel<<<1, 256, 0, s>>>(flags, n_blocks, tp, shard_rows, M, seq, seq_base, err);
   return check_launch();
 }
 
@@ -255,6 +261,12 @@ SONAR_API int sonar_all_reduce(const void* in, void* out, long n, void* const* s
     all_reduce_kernel<T><<<blocks, 512, 0, s>>>(p);
     return check_launch();
   });
+}
+
+namespace sonar { __global__ void bump_kernel(int* word, int n) { *word += n; } }
+SONAR_API int sonar_bump(int* word, int n, cudaStream_t s) {
+  sonar::bump_kernel<<<1, 1, 0, s>>>(word, n);
+  return check_launch();
 }
 
 // ---- peer-memory plumbing fallback (cudaMalloc + CUDA IPC handles) used when the framework's symmetric

@@ -46,19 +46,22 @@ _attn = _sig("sonar_paged_attention", c_void_p, c_long, c_void_p, c_void_p, c_in
              c_int, c_void_p, c_int, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
              c_float, c_int, c_int, c_int, c_int, c_void_p)
 _gemm = _sig("sonar_gemm", c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_long,
-             c_int, c_int, c_int, c_void_p, c_void_p)
+             c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p)
 _gemm_tp = _sig("sonar_gemm_tp", c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_long,
-                c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p)
+                c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                c_void_p, c_int, c_void_p)
 _tp_add_norm = _sig("sonar_tp_add_norm", c_void_p, c_long, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float,
-                    c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p)
-_tp_wait = _sig("sonar_tp_wait", c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p)
+                    c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                    c_void_p)
+_tp_wait = _sig("sonar_tp_wait", c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p)
+_bump = _sig("sonar_bump", c_void_p, c_int, c_void_p)
 _all_reduce = _sig("sonar_all_reduce", c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                    c_int, c_int, c_int, c_void_p, c_int, c_void_p)
 _argmax = _sig("sonar_argmax", c_void_p, c_long, c_int, c_int, c_void_p, c_void_p)
 _sample = _sig("sonar_sample", c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                c_long, c_void_p, c_uint, c_void_p, c_void_p)
 lib.sonar_last_cuda_error.restype = c_int
-lib.sonar_gemm_pick_bn.argtypes = [c_int, c_int]
+lib.sonar_gemm_pick_bn.argtypes = [c_int, c_int, c_int]
 lib.sonar_gemm_pick_bn.restype = c_int
 
 
@@ -86,7 +89,8 @@ def error_word(device: torch.device) -> torch.Tensor:
     """Per-device int32 that pipeline kernels write when a bounded wait gives up."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
     if idx not in _err_words:
-        _err_words[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+        with torch.inference_mode(False):
+            _err_words[idx] = torch.zeros(1, dtype=torch.int32, device=device)
     return _err_words[idx]
 
 
@@ -96,7 +100,8 @@ def check_device_errors(device: torch.device | None = None) -> None:
         v = int(w.item())
         if v:
             w.zero_()
-            sites = {1: "smem ring (empty)", 2: "smem ring (full)", 3: "tmem full", 4: "tmem empty", 5: "peer flag"}
+            sites = {1: "smem ring (empty)", 2: "smem ring (full)", 3: "tmem full", 4: "tmem empty", 5: "peer flag",
+                     6: "stream-K partial"}
             raise RuntimeError(f"cuda:{idx}: kernel wait timed out at {sites.get(v & 255, v & 255)} "
                                f"(block {v >> 8})")
 
@@ -147,6 +152,10 @@ class _AttnBuffers:
         self.max_dec = max_seqs
         self.max_pre = max_tokens + max_seqs
         pin = True
+        with torch.inference_mode(False):   # long-lived buffers must be ordinary tensors
+            self._alloc(device, pin)
+
+    def _alloc(self, device, pin: bool) -> None:
         self.h_dec = torch.zeros(self.max_dec, dtype=torch.int32, pin_memory=pin)
         self.h_pre = torch.zeros(self.max_pre * 2, dtype=torch.int32, pin_memory=pin)
         self.h_counts = torch.zeros(2, dtype=torch.int32, pin_memory=pin)
@@ -161,7 +170,8 @@ _attn_buffers: dict[int, _AttnBuffers] = {}
 MAX_SPLIT_CTAS = 1024
 
 
-def build_attention_work(meta, runner=None, group: int | None = None, num_kv_heads: int | None = None) -> None:
+def build_attention_work(meta, runner=None, group: int | None = None, num_kv_heads: int | None = None,
+                         graph_bucket: int | None = None) -> None:
     """Classify this step's sequences into decode items (q_len·group ≤ 16 rows) and
     prefill tiles (64 rows each) and upload the lists; picks the KV split count."""
     dev = meta.seq_lens.device
@@ -206,9 +216,16 @@ def build_attention_work(meta, runner=None, group: int | None = None, num_kv_hea
         splits = int(min(-(-2 * 148 // (n_dec * num_kv_heads)), max(1, max_pages // 8), 32,
                          MAX_SPLIT_CTAS // (n_dec * num_kv_heads)))
         splits = max(splits, 1)
+    if graph_bucket is not None:
+        # captured graphs need grid sizes that depend on the bucket only: every slot of the bucket is a
+        # potential decode item (surplus CTAs exit on the device-side count), split count by bucket
+        n_ctas = graph_bucket * num_kv_heads
+        splits = max(1, min(-(-2 * 148 // n_ctas), 16, MAX_SPLIT_CTAS // n_ctas)) if n_ctas < 2 * 148 else 1
+        n_dec, n_pre = graph_bucket, 0
     if splits > 1 and buf.part_o is None:
-        buf.part_o = torch.empty(MAX_SPLIT_CTAS * 16 * 128, dtype=torch.float32, device=dev)
-        buf.part_lse = torch.empty(MAX_SPLIT_CTAS * 16, dtype=torch.float32, device=dev)
+        with torch.inference_mode(False):
+            buf.part_o = torch.empty(MAX_SPLIT_CTAS * 16 * 128, dtype=torch.float32, device=dev)
+            buf.part_lse = torch.empty(MAX_SPLIT_CTAS * 16, dtype=torch.float32, device=dev)
     w.dec_items, w.pre_work, w.counts = buf.d_dec, buf.d_pre, buf.d_counts
     w.n_dec, w.n_pre, w.num_splits = n_dec, n_pre, splits
     w.part_o, w.part_lse = buf.part_o, buf.part_lse
@@ -240,6 +257,25 @@ def merge_attn_states(o1, lse1, o2, lse2):
 
 
 # ---------------------------------------------------------------- GEMM
+WS_CTAS = 160
+_gemm_ws: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+STREAM_K = os.environ.get("SONAR_GEMM_STREAMK", "1") != "0"
+
+
+def gemm_workspace(device: torch.device):
+    """Stream-K scratch of the device: partial-tile slots and their ready flags.  One per device,
+    shared by every GEMM on the engine's stream (launches using it must not overlap)."""
+    if not STREAM_K:
+        return None, None, 0
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _gemm_ws:
+        with torch.inference_mode(False):
+            _gemm_ws[idx] = (torch.empty(WS_CTAS * 128 * 256, dtype=torch.float32, device=device),
+                             torch.zeros(WS_CTAS, dtype=torch.int32, device=device))
+    ws, flags = _gemm_ws[idx]
+    return ws.data_ptr(), flags.data_ptr(), WS_CTAS
+
+
 def gemm(x, w, bias=None, out=None, out_dtype=None, force_bn: int = 0):
     """y = x @ w.T (+ bias) on the tcgen05 kernel; x [M, K], w [N, K], 16-bit, unit inner strides."""
     if os.environ.get("SONAR_GEMM", "tcgen05") == "cublas":
@@ -256,13 +292,14 @@ def gemm(x, w, bias=None, out=None, out_dtype=None, force_bn: int = 0):
         out = torch.empty((m, n), dtype=odt, device=x.device)
     kbias = bias if (bias is not None and bias.dtype == odt) else None
     _check(_gemm(x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(kbias), m, n, k, x.stride(0), w.stride(0),
-                 out.stride(0), _DT[x.dtype], _DT[odt], force_bn, error_word(x.device).data_ptr(), _stream()), "gemm")
+                 out.stride(0), _DT[x.dtype], _DT[odt], force_bn, error_word(x.device).data_ptr(),
+                 *gemm_workspace(x.device), _stream()), "gemm")
     if bias is not None and kbias is None:
         out += bias.to(odt)
     return out
 
 
-def gemm_tp(a, w, out, *, tp, shard_rows, seq, rank, gather_flags=None, dst_ptrs=None, local_done=None,
+def gemm_tp(a, w, out, *, tp, shard_rows, seq, rank, seq_base=None, gather_flags=None, dst_ptrs=None, local_done=None,
             flag_ptrs=None, n_out=None, ldc=None, err=None, force_bn: int = 0):
     """Tensor-parallel GEMM: ``gather_flags`` → wait for all-gathered A rows per 128-row block;
     ``dst_ptrs`` → scatter the output rows to their owners' partial buffers (``out`` is then None)."""
@@ -272,21 +309,25 @@ def gemm_tp(a, w, out, *, tp, shard_rows, seq, rank, gather_flags=None, dst_ptrs
     c_ptr = out.data_ptr() if out is not None else None
     c_ld = out.stride(0) if out is not None else ldc
     _check(_gemm_tp(a.data_ptr(), w.data_ptr(), c_ptr, m, n, k, a.stride(0), w.stride(0), c_ld,
-                    _ptr(gather_flags), tp, shard_rows, seq, rank, _ptr(dst_ptrs), _ptr(local_done), _ptr(flag_ptrs),
-                    force_bn, _ptr(err), _stream()), "gemm_tp")
+                    _ptr(gather_flags), tp, shard_rows, seq, _ptr(seq_base), rank, _ptr(dst_ptrs), _ptr(local_done), _ptr(flag_ptrs),
+                    force_bn, _ptr(err), *gemm_workspace(a.device), _stream()), "gemm_tp")
     return out
 
 
 def tp_add_norm(src_ptr, slot_stride, n_src, src_flags_ptr, wait_seq, residual, residual_in, weight, eps, hidden, rows,
-                gather_ptrs, tp, rank, shard_rows, blk_done, gather_flag_ptrs, send_seq, err, dtype):
+                gather_ptrs, tp, rank, shard_rows, blk_done, gather_flag_ptrs, send_seq, seq_base, err, dtype):
     _check(_tp_add_norm(src_ptr, slot_stride, n_src, src_flags_ptr, wait_seq, residual.data_ptr(), residual_in,
                         weight.data_ptr(), eps, hidden, rows, gather_ptrs.data_ptr(), tp, rank, shard_rows,
-                        blk_done.data_ptr(), gather_flag_ptrs.data_ptr(), send_seq, err.data_ptr(), _DT[dtype],
+                        blk_done.data_ptr(), gather_flag_ptrs.data_ptr(), send_seq, _ptr(seq_base), err.data_ptr(), _DT[dtype],
                         _stream()), "tp_add_norm")
 
 
-def tp_wait(flags, tp, shard_rows, m, seq, err):
-    _check(_tp_wait(flags.data_ptr(), tp, shard_rows, m, seq, err.data_ptr(), _stream()), "tp_wait")
+def tp_wait(flags, tp, shard_rows, m, seq, seq_base, err):
+    _check(_tp_wait(flags.data_ptr(), tp, shard_rows, m, seq, _ptr(seq_base), err.data_ptr(), _stream()), "tp_wait")
+
+
+def bump(word, n):
+    _check(_bump(word.data_ptr(), n, _stream()), "bump")
 
 
 def all_reduce(x, out, slot_ptrs, flag_ptrs, local_slots_ptr, local_flags_ptr, arrive, tp, rank, seq, err):

@@ -101,6 +101,10 @@ class FusedTPContext(TPContext):
         self.local_done = torch.zeros(tp, dtype=torch.int32, device=device)
         self.blk_done = torch.zeros(self.n_blk, dtype=torch.int32, device=device)
         self.ar_arrive = torch.zeros(1, dtype=torch.int32, device=device)
+        # sequence numbers = seq_base (device word, bumped once per step by a kernel, so a replayed CUDA
+        # graph advances it too) + the op's index inside the step (host counter, reset every step)
+        self.seq_base = torch.zeros(1, dtype=torch.int32, device=device)
+        self.ops_per_step = 1024
         self.seq = 0
         self.ar_seq = 0
         self.T = self.T_pad = self.Tl = 0
@@ -114,6 +118,8 @@ class FusedTPContext(TPContext):
         self.T = num_tokens
         self.T_pad = (num_tokens + tp - 1) // tp * tp
         self.Tl = self.T_pad // tp
+        self.seq = 0
+        self.cu.bump(self.seq_base, self.ops_per_step)
         if self.T_pad > self.T_max:
             raise ValueError(f"{num_tokens} tokens exceed the fused-TP buffers sized for {self.T_max}")
 
@@ -146,8 +152,8 @@ class FusedTPContext(TPContext):
             res_in = 0
         self.seq += 1
         cu.tp_add_norm(src, stride, n_src, flags, wait_seq, residual, res_in, weight, eps, self.H, self.Tl,
-                       self.gather_ptrs, tp, self.rank, self.Tl, self.blk_done, self.gflag_ptrs, self.seq, self.err,
-                       self.dtype)
+                       self.gather_ptrs, tp, self.rank, self.Tl, self.blk_done, self.gflag_ptrs, self.seq, self.seq_base,
+                       self.err, self.dtype)
         return Gathered(self.seq), residual
 
     def col_linear(self, x, layer):
@@ -157,7 +163,7 @@ class FusedTPContext(TPContext):
             return layer.apply(self._materialize(x))
         out = torch.empty((self.T_pad, layer.weight.shape[0]), dtype=self.dtype, device=self.device)
         self.cu.gemm_tp(self.gather[: self.T_pad], layer.weight, out, gather_flags=self.gflags, tp=self.world_size,
-                        shard_rows=self.Tl, seq=x.seq, rank=self.rank, err=self.err)
+                        shard_rows=self.Tl, seq=x.seq, seq_base=self.seq_base, rank=self.rank, err=self.err)
         if layer.bias is not None:
             out += layer.bias
         return out
@@ -169,7 +175,7 @@ class FusedTPContext(TPContext):
             return self._push_partial(y)
         self.seq += 1
         self.cu.gemm_tp(x, layer.weight, None, n_out=layer.weight.shape[0], tp=self.world_size, shard_rows=self.Tl,
-                        seq=self.seq, rank=self.rank, dst_ptrs=self.dst_ptrs, local_done=self.local_done,
+                        seq=self.seq, seq_base=self.seq_base, rank=self.rank, dst_ptrs=self.dst_ptrs, local_done=self.local_done,
                         flag_ptrs=self.pflag_ptrs, ldc=self.H, err=self.err)
         return Partial(self.seq)
 
@@ -178,7 +184,7 @@ class FusedTPContext(TPContext):
         return self.group.reduce_scatter(y)
 
     def _materialize(self, x: Gathered) -> torch.Tensor:
-        self.cu.tp_wait(self.gflags, self.world_size, self.Tl, self.T_pad, x.seq, self.err)
+        self.cu.tp_wait(self.gflags, self.world_size, self.Tl, self.T_pad, x.seq, self.seq_base, self.err)
         return self.gather[: self.T_pad]
 
     def gather_tokens(self, h, num_tokens: int) -> torch.Tensor:

@@ -144,7 +144,10 @@ class ModelRunner:
         self.h_bt_np = self.h_bt.numpy()
         self._pending: dict[str, Any] | None = None
         self.graphs: dict[int, Any] = {}
-        self.stats = {"steps": 0, "prep_s": 0.0, "launch_s": 0.0, "sample_s": 0.0, "h2d_bytes": 0, "d2h_bytes": 0}
+        self.stats = {"steps": 0, "graph_steps": 0, "prep_s": 0.0, "launch_s": 0.0, "sample_s": 0.0, "h2d_bytes": 0,
+                      "d2h_bytes": 0}
+        self.graph_launches: dict[int, int] = {}
+        self.graph_buckets: list[int] = []
         pp = state.get_pp_group() if state.model_parallel_is_initialized() else None
         self.pp = pp if pp is not None and pp.world_size > 1 else None
         self.spec_cfg = cfg.speculative
@@ -258,16 +261,26 @@ class ModelRunner:
         if ns:  # block-table rows in step order
             self.h_bt_np[:ns, :nb_used] = b.block_table_np[rows, :nb_used]
         nbl = self.is_cuda
-        self.d_input_ids[:total].copy_(self.h_input_ids[:total], non_blocking=nbl)
-        self.d_positions[:total].copy_(self.h_positions[:total], non_blocking=nbl)
-        self.d_slots[:total].copy_(self.h_slots[:total], non_blocking=nbl)
+        # decode-only steps replay a CUDA graph captured for a padded token count: pad rows read
+        # token 0 at position 0 and write no KV (slot -1)
+        padded = total
+        if self.graphs and ns and int(q_lens.max()) == 1 and self.pp is None:
+            bucket = self._bucket_for(total)
+            if bucket is not None:
+                padded = bucket
+                self.h_input_ids.numpy()[total:padded] = 0
+                self.h_positions.numpy()[total:padded] = 0
+                self.h_slots.numpy()[total:padded] = -1
+        self.d_input_ids[:padded].copy_(self.h_input_ids[:padded], non_blocking=nbl)
+        self.d_positions[:padded].copy_(self.h_positions[:padded], non_blocking=nbl)
+        self.d_slots[:padded].copy_(self.h_slots[:padded], non_blocking=nbl)
         self.d_seq_lens.copy_(self.h_seq_lens, non_blocking=nbl)
         self.d_qsl.copy_(self.h_qsl, non_blocking=nbl)
         if ns:
             self.d_block_table[:ns, :nb_used].copy_(self.h_bt[:ns, :nb_used], non_blocking=nbl)
         self.stats["h2d_bytes"] += total * 16 + (2 * self.max_seqs + 1) * 4 + ns * nb_used * 4
         meta = AttentionMetadata(
-            num_tokens=total, num_seqs=ns, positions=self.d_positions[:total], slot_mapping=self.d_slots[:total],
+            num_tokens=total, num_seqs=ns, positions=self.d_positions[:padded], slot_mapping=self.d_slots[:padded],
             block_tables=self.d_block_table, seq_lens=self.d_seq_lens, query_start_loc=self.d_qsl,
             max_query_len=int(q_lens.max()) if ns else 0, max_seq_len=int(seq_lens.max()) if ns else 0,
             query_lens_cpu=q_lens, seq_lens_cpu=seq_lens)
@@ -285,20 +298,32 @@ class ModelRunner:
         self.stats["steps"] += 1
         total = meta.num_tokens
         tp = get_tp_context()
-        tp.begin_step(total)
-        if self.is_cuda:
-            from sonar_b200.ops import cuda as cuda_ops
-            cuda_ops.build_attention_work(meta, self)
-        ids = self.d_input_ids[:total]
-        if self.pp is not None and not self.pp.is_first_rank:
-            intermediate = self._recv_intermediate(tp.local_tokens(total))
+        padded = meta.positions.shape[0]
         t1 = time.perf_counter()
-        out = self.model(ids, meta, intermediate)
+        if padded != total or (padded in self.graphs and int(q_lens.max()) == 1 and self.pp is None):
+            # ---- CUDA-graph replay (decode-only step)
+            from sonar_b200.ops import cuda as cuda_ops
+            cuda_ops.build_attention_work(meta, self, graph_bucket=padded)
+            graph, out_buf = self.graphs[padded]
+            graph.replay()
+            cuda_ops.launch_count += self.graph_launches[padded]
+            self.stats["graph_steps"] += 1
+            hidden = out_buf[:total]
+        else:
+            tp.begin_step(total)
+            if self.is_cuda:
+                from sonar_b200.ops import cuda as cuda_ops
+                cuda_ops.build_attention_work(meta, self)
+            ids = self.d_input_ids[:total]
+            if self.pp is not None and not self.pp.is_first_rank:
+                intermediate = self._recv_intermediate(tp.local_tokens(total))
+            out = self.model(ids, meta, intermediate)
+            if self.pp is not None and not self.pp.is_last_rank:
+                self.stats["launch_s"] += time.perf_counter() - t1
+                self._send_intermediate(out)
+                return None
+            hidden = tp.gather_tokens(out, total)
         self.stats["launch_s"] += time.perf_counter() - t1
-        if self.pp is not None and not self.pp.is_last_rank:
-            self._send_intermediate(out)
-            return None
-        hidden = tp.gather_tokens(out, total)
         t2 = time.perf_counter()
         res = self._sample(so, hidden, meta, rows, q_lens)
         self.stats["sample_s"] += time.perf_counter() - t2
@@ -433,6 +458,67 @@ class ModelRunner:
                         d.setdefault(a, c)
                 entries.append(d)
             out.prompt_logprobs[req_ids[i]] = entries
+
+    # --------------------------------------------------------------- CUDA graphs
+    def _bucket_for(self, n: int) -> int | None:
+        for b in self.graph_buckets:
+            if b >= n:
+                return b
+        return None
+
+    @torch.inference_mode()
+    def warm_up(self) -> None:
+        """Capture one CUDA graph of the whole decoder forward per padded decode batch size.
+        Launch-bound decode steps (hundreds of short kernels) then cost one graph launch."""
+        from sonar_b200 import envs
+        if not self.is_cuda or self.cfg.enforce_eager or not envs.SONAR_CUDA_GRAPHS or self.pp is not None:
+            return
+        from sonar_b200.ops import cuda as cuda_ops
+        tp = get_tp_context()
+        sizes = sorted({b for b in [1, 2, 4, 8, 16, 24, 32, 40, 48, 56, 64] + list(range(80, 513, 16))
+                        if b <= self.max_seqs} | {self.max_seqs})
+        ws = tp.world_size
+        sizes = sorted({(b + ws - 1) // ws * ws for b in sizes})
+        t0 = time.time()
+        pool = None
+        self.graph_buckets = []
+        for b in reversed(sizes):
+            self.h_input_ids.numpy()[:b] = 0
+            self.h_positions.numpy()[:b] = 0
+            self.h_slots.numpy()[:b] = -1
+            self.d_input_ids[:b].copy_(self.h_input_ids[:b])
+            self.d_positions[:b].copy_(self.h_positions[:b])
+            self.d_slots[:b].copy_(self.h_slots[:b])
+            self.d_seq_lens.fill_(1)
+            self.d_qsl.copy_(torch.arange(self.max_seqs + 1, dtype=torch.int32).clamp_max(b))
+            self.d_block_table[:, :1].zero_()
+            meta = AttentionMetadata(
+                num_tokens=b, num_seqs=b, positions=self.d_positions[:b], slot_mapping=self.d_slots[:b],
+                block_tables=self.d_block_table, seq_lens=self.d_seq_lens, query_start_loc=self.d_qsl,
+                max_query_len=1, max_seq_len=1, query_lens_cpu=np.ones(b, dtype=np.int32),
+                seq_lens_cpu=np.ones(b, dtype=np.int32))
+            cuda_ops.build_attention_work(meta, self, graph_bucket=b)
+
+            def run():
+                tp.begin_step(b)
+                out = self.model(self.d_input_ids[:b], meta, None)
+                return tp.gather_tokens(out, b)
+            for _ in range(2):      # eager warm-up: function attributes, tensor maps, allocator state
+                run()
+            torch.cuda.synchronize()
+            before = cuda_ops.launch_count
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=pool):
+                out = run()
+            pool = g.pool()
+            self.graph_launches[b] = cuda_ops.launch_count - before
+            self.graphs[b] = (g, out)
+            self.graph_buckets.append(b)
+        self.graph_buckets.sort()
+        torch.cuda.synchronize()
+        cuda_ops.check_device_errors()
+        logger.info("captured %d decode graphs (sizes %s…%s) in %.1fs", len(sizes), sizes[0], sizes[-1],
+                    time.time() - t0)
 
     # --------------------------------------------------------------- misc
     def profile_activation_bytes(self) -> int:

@@ -1,0 +1,79 @@
+// Decode attention for callers that cannot allocate (see decode_attention_static.h).
+//
+// The split-KV decode kernel needs scratch beyond its inputs and outputs: fp32 partial outputs and
+// log-sum-exp values per (split, sequence, kv head), the list of sequences to process, and two counters.
+// Here all of it is one file-scope device array.  Host code cannot use the array's name as a pointer —
+// on the host that name is only a stand-in symbol — so set-up asks the runtime for the real device
+// address once per device (with that device current) and every launch is given that address.
+#include "decode_attention_static.h"
+
+#include "common.cuh"
+
+// the regular entry point (attention.cu); this file only supplies its scratch arguments
+SONAR_API int sonar_paged_attention(const void* q, long q_tok_stride, const void* cache, const int* block_tables,
+                                    int bt_stride, const int* seq_lens, const int* qsl, const int* dec_items,
+                                    int max_dec, const int* pre_work, int max_pre, const int* counts, void* out,
+                                    long out_tok_stride, float* part_o, float* part_lse, int hq, int hk, int head_dim,
+                                    int block_size, float scale, int window, int num_splits, int total_rows, int dtype,
+                                    cudaStream_t s);
+
+namespace {
+
+constexpr int MAX_SEQS = SONAR_STATIC_MAX_SEQS;
+constexpr int MAX_CTAS = SONAR_STATIC_MAX_SPLIT_CTAS;
+constexpr int MAX_HD = SONAR_STATIC_MAX_HEAD_DIM;
+constexpr int MAX_DEVICES = 64;
+
+struct Scratch {
+  float part_o[MAX_CTAS * 16 * MAX_HD];   // partial outputs: 16 query rows per CTA tile
+  float part_lse[MAX_CTAS * 16];
+  int iota[MAX_SEQS + 8];                 // 0,1,2,…: serves as the item list and as query_start_loc (one token each)
+  int counts[8];                          // [0] = sequences this call, [1] = 0 prefill tiles
+};
+
+static __device__ __align__(256) Scratch g_scratch;
+
+Scratch* g_addr[MAX_DEVICES];             // device address of g_scratch, per device (null = not set up)
+
+__global__ void fill_iota_kernel(int* iota, int n) {
+  for (int i = threadIdx.x + blockIdx.x * blockDim.x; i < n; i += blockDim.x * gridDim.x) iota[i] = i;
+}
+// Everything the kernels read from the shared scratch before writing it must be set per call:
+// the counters.  Partials are fully written by every CTA that the merge step reads, so they need no clearing.
+__global__ void set_counts_kernel(int* counts, int n) {
+  counts[0] = n;
+  counts[1] = 0;
+}
+
+}  // namespace
+
+extern "C" __attribute__((visibility("default")))
+int sonar_decode_attention_static(const void* q, long q_tok_stride, const void* cache, const int* block_tables,
+                                  int bt_stride, const int* seq_lens, int num_seqs, void* out, long out_tok_stride,
+                                  int hq, int hk, int head_dim, float scale, int num_splits, int dtype,
+                                  cudaStream_t stream) {
+  if (num_seqs == 0) return SONAR_OK;
+  if (num_seqs < 0 || num_splits < 1 || num_splits > 32 || hk < 1 || hq % hk) return SONAR_BAD_ARG;
+  if (num_seqs > MAX_SEQS || head_dim > MAX_HD || (long)num_splits * num_seqs * hk > MAX_CTAS) return SONAR_TOO_LARGE;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) { sonar::g_last_cuda_error = (int)e; return SONAR_CUDA_ERROR; }
+  if (g_addr[dev] == nullptr) {
+    // first call on this device: resolve the symbol to its address here and fill the constant part
+    Scratch* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_scratch);
+    if (e != cudaSuccess || p == nullptr) { sonar::g_last_cuda_error = (int)e; return SONAR_CUDA_ERROR; }
+    fill_iota_kernel<<<1, 256, 0, stream>>>(p->iota, MAX_SEQS + 8);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) { sonar::g_last_cuda_error = (int)e; return SONAR_CUDA_ERROR; }
+    g_addr[dev] = p;
+  }
+  Scratch* sc = g_addr[dev];
+  set_counts_kernel<<<1, 1, 0, stream>>>(sc->counts, num_seqs);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) { sonar::g_last_cuda_error = (int)e; return SONAR_CUDA_ERROR; }
+  return sonar_paged_attention(q, q_tok_stride, cache, block_tables, bt_stride, seq_lens, /*qsl=*/sc->iota,
+                               /*dec_items=*/sc->iota, /*max_dec=*/num_seqs, /*pre_work=*/nullptr, /*max_pre=*/0,
+                               sc->counts, out, out_tok_stride, sc->part_o, sc->part_lse, hq, hk, head_dim,
+                               /*block_size=*/16, scale, /*window=*/0, num_splits, 0, dtype, stream);
+}

@@ -1,0 +1,38 @@
+// Allocation-free decode attention.  This entry point has no counterpart in the reference engine.
+//
+// Who needs it: code that may not allocate device memory at the moment it needs attention — a plugin
+// running inside another runtime's stream callback, a process that has handed its whole memory budget to
+// the KV cache and weights, a real-time loop that must not take the allocator's locks.  The regular
+// split-KV decode path asks its caller for partial-result buffers; here those live inside the library.
+#pragma once
+#include <cuda_runtime.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Compiled-in limits.  Requests beyond them are refused with status 3 (nothing is launched).
+#define SONAR_STATIC_MAX_SEQS 256        /* sequences per call */
+#define SONAR_STATIC_MAX_SPLIT_CTAS 512  /* num_splits * num_seqs * num_kv_heads */
+#define SONAR_STATIC_MAX_HEAD_DIM 128
+
+// One decode step of paged GQA attention: one query token per sequence.
+//   q            [num_seqs, hq, head_dim], token stride q_tok_stride elements, head stride head_dim
+//   cache        [blocks, 2, hk, 16, head_dim] (same dtype as q: 0 = bf16, 1 = fp16)
+//   block_tables [num_seqs, bt_stride] int32, seq_lens [num_seqs] int32 (context length incl. this token)
+//   out          [num_seqs, hq * head_dim], token stride out_tok_stride
+//   num_splits   how many CTAs share one sequence's KV range (1..32)
+// Returns 0 on launch, 1 bad argument, 2 CUDA error, 3 over a limit.
+//
+// The scratch is a fixed array inside the library (about 4.2 MB per GPU that loads it, held until the
+// process exits).  The first call on each device looks up the array's device address; make that first
+// call outside any stream capture.  All calls on a device share the array: two calls that overlap on
+// the GPU (different streams) race on it — keep them on one stream or serialise them yourself.
+int sonar_decode_attention_static(const void* q, long q_tok_stride, const void* cache, const int* block_tables,
+                                  int bt_stride, const int* seq_lens, int num_seqs, void* out, long out_tok_stride,
+                                  int hq, int hk, int head_dim, float scale, int num_splits, int dtype,
+                                  cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

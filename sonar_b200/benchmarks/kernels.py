@@ -1,0 +1,176 @@
+"""Kernel micro-benchmarks (CUDA events, L2 flushed between iterations).
+
+    python -m sonar_b200.benchmarks.kernels gemm  --m 4096 --n 6144 --k 4096
+    python -m sonar_b200.benchmarks.kernels attn-decode --seqs 256 --ctx 1152
+    python -m sonar_b200.benchmarks.kernels attn-prefill --seqs 8 --q 1024 --ctx 1024
+    python -m sonar_b200.benchmarks.kernels elementwise
+    python -m sonar_b200.benchmarks.kernels sweep          # the Llama-3-8B shapes of the headline benchmark
+
+Each line reports the achieved rate and its fraction of the measured roofline denominators
+(``MEASURED_PEAKS.json`` at the repo root when present, else 6.65 TB/s and 1.59 PFLOP/s).
+Parity: the reference's ``benchmarks/kernels/*`` scripts.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from sonar_b200.layers.attention import AttentionMetadata
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def peaks() -> tuple[float, float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return d["hbm_gbs"], d["bf16_tflops"], "of measured"
+    return 6650.0, 1590.0, "of fallback"
+
+
+def timeit(fn, iters: int, warm: int, flush: torch.Tensor | None) -> float:
+    """Median milliseconds of ``fn`` over ``iters`` runs."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def bench_gemm(cu, m, n, k, iters, warm, flush, compare=True, force_bn=0):
+    hbm, tf, tag = peaks()
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    flops = 2.0 * m * n * k
+    byts = 2.0 * (m * k + n * k + m * n)
+    t = timeit(lambda: cu.gemm(x, w, out=out, force_bn=force_bn), iters, warm, flush)
+    roof = max(flops / (tf * 1e12), byts / (hbm * 1e9)) * 1e3
+    line = (f"gemm M={m} N={n} K={k}: {t:.4f} ms, {flops / t / 1e9:.0f} TFLOP/s, {byts / t / 1e6:.0f} GB/s, "
+            f"{roof / t:.2f} {tag} roofline")
+    if compare:
+        t_ref = timeit(lambda: torch.matmul(x, w.t(), out=out), iters, warm, flush)
+        line += f"; cuBLAS {t_ref:.4f} ms ({t_ref / t:.2f}x)"
+    print(line, flush=True)
+    cu.check_device_errors()
+    return t
+
+
+def bench_attn_decode(cu, seqs, ctx, hq, hk, d, iters, warm, flush):
+    hbm, _, tag = peaks()
+    bs = 16
+    nb = seqs * (ctx // bs) + 8
+    cache = torch.randn(nb, 2, hk, bs, d, device="cuda", dtype=torch.bfloat16)
+    bt = (torch.arange(seqs * (ctx // bs), device="cuda", dtype=torch.int32) + 1).view(seqs, -1)
+    bt = bt[:, torch.randperm(bt.shape[1], device="cuda")].contiguous()
+    q = torch.randn(seqs, hq, d, device="cuda", dtype=torch.bfloat16)
+    meta = AttentionMetadata(
+        num_tokens=seqs, num_seqs=seqs, positions=None, slot_mapping=None, block_tables=bt,
+        seq_lens=torch.full((seqs,), ctx, dtype=torch.int32, device="cuda"),
+        query_start_loc=torch.arange(seqs + 1, dtype=torch.int32, device="cuda"), max_query_len=1, max_seq_len=ctx,
+        query_lens_cpu=[1] * seqs, seq_lens_cpu=[ctx] * seqs)
+    out = torch.empty(seqs, hq * d, device="cuda", dtype=torch.bfloat16)
+    cu.build_attention_work(meta, None, hq // hk, hk)
+    t = timeit(lambda: cu.paged_attention(q, cache, meta, d ** -0.5, out=out), iters, warm, flush)
+    gb = seqs * ctx * 2 * hk * d * 2 / 1e9
+    print(f"attn-decode seqs={seqs} ctx={ctx} splits={meta.work.num_splits}: {t:.4f} ms, {gb / t * 1e3:.0f} GB/s, "
+          f"{gb / t * 1e3 / hbm:.2f} {tag} copy bandwidth", flush=True)
+
+
+def bench_attn_prefill(cu, seqs, ql, ctx, hq, hk, d, iters, warm, flush):
+    _, tf, tag = peaks()
+    bs = 16
+    nb = seqs * (ctx // bs) + 8
+    cache = torch.randn(nb, 2, hk, bs, d, device="cuda", dtype=torch.bfloat16)
+    bt = (torch.arange(seqs * (ctx // bs), device="cuda", dtype=torch.int32) + 1).view(seqs, -1).contiguous()
+    q = torch.randn(seqs * ql, hq, d, device="cuda", dtype=torch.bfloat16)
+    meta = AttentionMetadata(
+        num_tokens=seqs * ql, num_seqs=seqs, positions=None, slot_mapping=None, block_tables=bt,
+        seq_lens=torch.full((seqs,), ctx, dtype=torch.int32, device="cuda"),
+        query_start_loc=(torch.arange(seqs + 1, dtype=torch.int32, device="cuda") * ql).int(), max_query_len=ql,
+        max_seq_len=ctx, query_lens_cpu=[ql] * seqs, seq_lens_cpu=[ctx] * seqs)
+    out = torch.empty(seqs * ql, hq * d, device="cuda", dtype=torch.bfloat16)
+    cu.build_attention_work(meta, None, hq // hk, hk)
+    t = timeit(lambda: cu.paged_attention(q, cache, meta, d ** -0.5, out=out), iters, warm, flush)
+    fl = 4.0 * seqs * hq * d * (ql * (ctx - ql) + ql * ql / 2)
+    print(f"attn-prefill seqs={seqs} q={ql} ctx={ctx}: {t:.4f} ms, {fl / t / 1e9:.0f} TFLOP/s "
+          f"({fl / t / 1e9 / tf:.2f} {tag} bf16 GEMM rate)", flush=True)
+
+
+def bench_elementwise(cu, iters, warm, flush):
+    hbm, _, tag = peaks()
+    t_, h = 8192, 4096
+    x = torch.randn(t_, h, device="cuda", dtype=torch.bfloat16)
+    r = torch.randn_like(x)
+    w = torch.ones(h, device="cuda", dtype=torch.bfloat16)
+    t = timeit(lambda: cu.fused_add_rms_norm(x, r, w, 1e-5), iters, warm, flush)
+    print(f"fused_add_rms_norm {t_}x{h}: {t:.4f} ms, {t_ * h * 2 * 4 / t / 1e6:.0f} GB/s "
+          f"({t_ * h * 8 / t / 1e6 / hbm:.2f} {tag})")
+    g = torch.randn(t_, 2 * 14336, device="cuda", dtype=torch.bfloat16)
+    o = torch.empty(t_, 14336, device="cuda", dtype=torch.bfloat16)
+    t = timeit(lambda: cu.silu_and_mul(g, o), iters, warm, flush)
+    print(f"silu_and_mul {t_}x14336: {t:.4f} ms, {t_ * 14336 * 6 / t / 1e6:.0f} GB/s "
+          f"({t_ * 14336 * 6 / t / 1e6 / hbm:.2f} {tag})")
+    logits = torch.randn(256, 128256, device="cuda")
+    temp = torch.ones(256, device="cuda")
+    t = timeit(lambda: cu.sample(logits, temp, None, None, None), iters, warm, flush)
+    print(f"sample (temperature only) 256x128256: {t:.4f} ms")
+    tk = torch.full((256,), 50, dtype=torch.int32, device="cuda")
+    tp = torch.full((256,), 0.9, device="cuda")
+    t = timeit(lambda: cu.sample(logits, temp, tk, tp, None), iters, warm, flush)
+    print(f"sample (top-k 50, top-p 0.9) 256x128256: {t:.4f} ms")
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "attn-decode", "attn-prefill", "elementwise", "sweep"])
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=6144)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--seqs", type=int, default=256)
+    ap.add_argument("--ctx", type=int, default=1152)
+    ap.add_argument("--q", type=int, default=1024)
+    ap.add_argument("--hq", type=int, default=32)
+    ap.add_argument("--hk", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--no-compare", action="store_true", help="do not time cuBLAS next to the GEMM")
+    a = ap.parse_args()
+    from sonar_b200.ops import cuda as cu
+    flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    if a.what == "gemm":
+        bench_gemm(cu, a.m, a.n, a.k, a.iters, a.warmup, flush, not a.no_compare, a.bn)
+    elif a.what == "attn-decode":
+        bench_attn_decode(cu, a.seqs, a.ctx, a.hq, a.hk, a.head_dim, a.iters, a.warmup, flush)
+    elif a.what == "attn-prefill":
+        bench_attn_prefill(cu, a.seqs, a.q, a.ctx, a.hq, a.hk, a.head_dim, a.iters, a.warmup, flush)
+    elif a.what == "elementwise":
+        bench_elementwise(cu, a.iters, a.warmup, flush)
+    else:
+        for m in (256, 1280, 8192):
+            for n, k in ((6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)):
+                bench_gemm(cu, m, n, k, a.iters, a.warmup, flush)
+        for seqs, ctx in ((256, 1152), (256, 4096), (32, 1152), (8, 16384)):
+            bench_attn_decode(cu, seqs, ctx, 32, 8, 128, a.iters, a.warmup, flush)
+        bench_attn_prefill(cu, 8, 1024, 1024, 32, 8, 128, a.iters, a.warmup, flush)
+        bench_elementwise(cu, a.iters, a.warmup, flush)
+
+
+if __name__ == "__main__":
+    main()

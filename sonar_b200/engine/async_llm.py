@@ -1,0 +1,179 @@
+"""Asynchronous engine frontend used by the servers.
+
+``AsyncLLM.generate`` is an async generator of ``RequestOutput`` for one
+request.  The engine core runs in its own process (``EngineCoreProc`` behind
+ZMQ); one background task pulls ``EngineCoreOutputs``, runs the output
+processor and routes results to per-request queues.  Aborts (client
+disconnects, stop strings) are forwarded to the core.  If the core dies, every
+pending and future request fails with ``EngineDeadError``.
+
+Parity: ``aphrodite/v1/engine/async_llm.py:72`` (``generate`` :514, output handler
+:639, ``abort`` :688, pause/resume :725/:770).
+"""
+from __future__ import annotations
+
+import asyncio
+import time
+from typing import AsyncGenerator
+
+from sonar_b200.config import EngineArgs, EngineConfig
+from sonar_b200.engine.core_client import AsyncMPClient, EngineDeadError
+from sonar_b200.engine.llm_engine import InputProcessor
+from sonar_b200.engine.output_processor import OutputProcessor, ParentRequest
+from sonar_b200.logger import init_logger
+from sonar_b200.outputs import RequestOutput
+from sonar_b200.request import EngineCoreRequest, FinishReason
+from sonar_b200.sampling_params import PoolingParams, RequestOutputKind, SamplingParams
+from sonar_b200.utils.metrics import EngineMetrics
+from sonar_b200.utils.tokenizer import get_tokenizer
+
+logger = init_logger(__name__)
+
+
+class AsyncLLM:
+    def __init__(self, cfg: EngineConfig, executor_class=None) -> None:
+        self.cfg = cfg
+        self.tokenizer = None if cfg.model.skip_tokenizer_init else get_tokenizer(cfg.model.tokenizer,
+                                                                                 cfg.model.vocab_size)
+        self.input_processor = InputProcessor(cfg, self.tokenizer)
+        self.output_processor = OutputProcessor(self.tokenizer, cfg.observability.log_stats)
+        self.core = AsyncMPClient(cfg, executor_class)
+        self.metrics = EngineMetrics(cfg.model.served_model_name or cfg.model.model)
+        self._handler: asyncio.Task | None = None
+        self._dead: Exception | None = None
+        self._paused = False
+
+    @classmethod
+    def from_engine_args(cls, args: EngineArgs, **kw) -> "AsyncLLM":
+        cfg = args.create_engine_config()
+        cfg.observability.log_stats = True
+        return cls(cfg, **kw)
+
+    @property
+    def is_running(self) -> bool:
+        return self._dead is None and not self.core.dead
+
+    @property
+    def errored(self) -> bool:
+        return not self.is_running
+
+    def _ensure_handler(self) -> None:
+        if self._handler is None:
+            self._handler = asyncio.get_running_loop().create_task(self._output_loop())
+
+    async def _output_loop(self) -> None:
+        try:
+            while True:
+                outs = await self.core.get_output_async()
+                _, to_abort = self.output_processor.process_outputs(outs.outputs)
+                if to_abort:
+                    await self.core.abort_requests_async(to_abort)
+                if outs.scheduler_stats is not None:
+                    self.metrics.update_from_scheduler(outs.scheduler_stats)
+                for o in outs.outputs:
+                    if o.finished:
+                        self.metrics.request_finished(str(FinishReason(o.finish_reason)))
+        except asyncio.CancelledError:
+            raise
+        except Exception as e:  # noqa: BLE001 - engine death or a bug: fail every waiter
+            logger.error("output handler stopped: %s", e)
+            self._dead = e if isinstance(e, EngineDeadError) else EngineDeadError(str(e))
+            for st in list(self.output_processor.states.values()):
+                if st.queue is not None:
+                    st.queue.put_nowait(self._dead)
+
+    # ------------------------------------------------------------------
+    async def add_request(self, request_id: str, prompt, params: SamplingParams | PoolingParams,
+                          priority: int = 0, lora_name: str | None = None) -> asyncio.Queue:
+        if self._dead is not None or self.core.dead:
+            raise self._dead or EngineDeadError("engine core is dead")
+        self._ensure_handler()
+        text, req = self.input_processor.process(request_id, prompt, params, time.time(), priority, lora_name)
+        q: asyncio.Queue = asyncio.Queue()
+        n = params.n if isinstance(params, SamplingParams) else 1
+        self.metrics.request_arrived(len(req.prompt_token_ids))
+        if n == 1:
+            self.output_processor.add_request(req, text, queue=q)
+            await self.core.add_request_async(req)
+            return q
+        parent = ParentRequest(request_id, req.sampling_params)
+        for i in range(n):
+            child = EngineCoreRequest(
+                request_id=parent.child_id(i), prompt_token_ids=req.prompt_token_ids,
+                sampling_params=parent.child_params(i), eos_token_id=req.eos_token_id,
+                arrival_time=req.arrival_time, priority=priority, cache_salt=req.cache_salt, lora_name=lora_name)
+            self.output_processor.add_request(child, text, parent, i, queue=q)
+            await self.core.add_request_async(child)
+        return q
+
+    async def generate(self, prompt, sampling_params: SamplingParams, request_id: str, priority: int = 0,
+                       lora_name: str | None = None) -> AsyncGenerator[RequestOutput, None]:
+        q = await self.add_request(request_id, prompt, sampling_params, priority, lora_name)
+        finished = False
+        first = True
+        t0 = time.time()
+        try:
+            while not finished:
+                out = await q.get()
+                if isinstance(out, Exception):
+                    raise out
+                # a slow consumer gets the pending updates merged into one
+                while not q.empty():
+                    nxt = q.get_nowait()
+                    if isinstance(nxt, Exception):
+                        raise nxt
+                    out.add(nxt, aggregate=sampling_params.output_kind == RequestOutputKind.DELTA)
+                finished = out.finished
+                if first and out.outputs and out.outputs[0].token_ids:
+                    self.metrics.observe_ttft(time.time() - t0)
+                    first = False
+                if finished:
+                    n_out = sum(len(c.token_ids) for c in out.outputs)
+                    self.metrics.observe_e2e(time.time() - t0, n_out)
+                yield out
+        except (asyncio.CancelledError, GeneratorExit):
+            await self.abort(request_id)
+            raise
+
+    async def encode(self, prompt, pooling_params: PoolingParams, request_id: str):
+        q = await self.add_request(request_id, prompt, pooling_params)
+        out = await q.get()
+        if isinstance(out, Exception):
+            raise out
+        return out
+
+    async def abort(self, request_id: str | list[str]) -> None:
+        ids = [request_id] if isinstance(request_id, str) else list(request_id)
+        core_ids = self.output_processor.abort_requests(ids)
+        if core_ids and self.is_running:
+            await self.core.abort_requests_async(core_ids)
+
+    # utility -------------------------------------------------------------
+    async def check_health(self) -> None:
+        if not self.is_running:
+            raise self._dead or EngineDeadError("engine core is dead")
+
+    async def reset_prefix_cache(self) -> bool:
+        return await self.core.call_utility_async("reset_prefix_cache")
+
+    async def pause_generation(self) -> None:
+        self._paused = True
+        await self.core.call_utility_async("pause")
+
+    async def resume_generation(self) -> None:
+        self._paused = False
+        await self.core.call_utility_async("resume")
+
+    async def is_paused(self) -> bool:
+        return self._paused
+
+    async def collective_rpc(self, method: str, *args, **kwargs):
+        return await self.core.call_utility_async("collective_rpc", method, *args, **kwargs)
+
+    async def get_stats(self) -> dict:
+        return await self.core.call_utility_async("get_stats")
+
+    def shutdown(self) -> None:
+        if self._handler is not None:
+            self._handler.cancel()
+        self.core.shutdown()

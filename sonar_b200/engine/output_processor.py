@@ -119,7 +119,8 @@ class OutputProcessor:
                     ro = PoolingRequestOutput(st.request_id, PoolingOutput(eo.pooled), st.prompt_token_ids)
                     self._deliver(st, ro, results)
                 continue
-            finish, stop_reason = eo.finish_reason, eo.stop_reason
+            finish = FinishReason(eo.finish_reason) if eo.finish_reason is not None else None  # ints off the wire
+            stop_reason = eo.stop_reason
             if eo.new_token_ids and st.metrics.first_token_time is None:
                 st.metrics.first_token_time = now
             st.token_ids.extend(eo.new_token_ids)

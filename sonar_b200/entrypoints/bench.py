@@ -1,0 +1,130 @@
+"""``sonar bench {throughput,latency,serve}``.
+
+* throughput — offline: N requests of fixed input/output length through ``LLM.generate``.
+* latency    — offline: one batch, repeated; mean/percentile end-to-end latency.
+* serve      — online: Poisson arrivals against a running server; TTFT / TPOT / output tok/s.
+
+Parity: ``aphrodite/benchmarks/throughput.py:50,1063``, ``latency.py``, ``serve.py:526,714``.
+"""
+from __future__ import annotations
+
+import argparse
+import asyncio
+import json
+import random
+import statistics
+import time
+
+
+def add_args(p: argparse.ArgumentParser) -> None:
+    from sonar_b200.config import EngineArgs
+    p.add_argument("mode", choices=["throughput", "latency", "serve"])
+    p.add_argument("--model", default=None)
+    p.add_argument("--num-prompts", type=int, default=200)
+    p.add_argument("--input-len", type=int, default=1024)
+    p.add_argument("--output-len", type=int, default=128)
+    p.add_argument("--input-len-range", type=int, nargs=2, default=None, help="uniform [lo, hi] input lengths")
+    p.add_argument("--batch-size", type=int, default=8)
+    p.add_argument("--num-iters", type=int, default=5)
+    p.add_argument("--request-rate", type=float, default=float("inf"), help="serve: Poisson arrivals per second")
+    p.add_argument("--url", default="http://127.0.0.1:2242")
+    p.add_argument("--vocab-size", type=int, default=32000, help="serve: range of random token ids")
+    p.add_argument("--seed", type=int, default=0)
+    EngineArgs.add_cli_args(p)
+
+
+def _percentile(xs: list[float], q: float) -> float:
+    if not xs:
+        return 0.0
+    xs = sorted(xs)
+    return xs[min(len(xs) - 1, int(q * len(xs)))]
+
+
+def _offline(ns: argparse.Namespace) -> None:
+    from sonar_b200 import LLM, SamplingParams
+    from sonar_b200.config import EngineArgs
+    ns.model = ns.model or "tiny-llama"
+    args = EngineArgs.from_cli_args(ns)
+    args.skip_tokenizer_init = True
+    llm = LLM(args.model, **{k: v for k, v in vars(args).items() if k != "model"})
+    vocab = llm.llm_engine.cfg.model.vocab_size
+    rng = random.Random(ns.seed)
+    sp = SamplingParams(max_tokens=ns.output_len, ignore_eos=True, temperature=1.0, detokenize=False)
+
+    def prompts(n):
+        out = []
+        for _ in range(n):
+            ln = rng.randint(*ns.input_len_range) if ns.input_len_range else ns.input_len
+            out.append({"prompt_token_ids": [rng.randrange(vocab) for _ in range(ln)]})
+        return out
+    if ns.mode == "throughput":
+        ps = prompts(ns.num_prompts)
+        t0 = time.perf_counter()
+        outs = llm.generate(ps, sp)
+        dt = time.perf_counter() - t0
+        n_in = sum(len(p["prompt_token_ids"]) for p in ps)
+        n_out = sum(len(o.outputs[0].token_ids) for o in outs)
+        print(json.dumps({"requests_per_s": len(ps) / dt, "total_tokens_per_s": (n_in + n_out) / dt,
+                          "output_tokens_per_s": n_out / dt, "seconds": dt}))
+    else:
+        lat = []
+        for _ in range(ns.num_iters + 1):
+            ps = prompts(ns.batch_size)
+            t0 = time.perf_counter()
+            llm.generate(ps, sp)
+            lat.append(time.perf_counter() - t0)
+            llm.reset_prefix_cache()
+        lat = lat[1:]
+        print(json.dumps({"avg_latency_s": statistics.mean(lat), "p50_s": _percentile(lat, 0.5),
+                          "p99_s": _percentile(lat, 0.99), "batch_size": ns.batch_size}))
+    llm.shutdown()
+
+
+async def _serve(ns: argparse.Namespace) -> dict:
+    import aiohttp
+    rng = random.Random(ns.seed)
+    base = ns.url.rstrip("/")
+    results: list[dict] = []
+
+    async def one(session, prompt_ids):
+        t0 = time.perf_counter()
+        ttft, n, last = None, 0, t0
+        payload = {"prompt": prompt_ids, "max_tokens": ns.output_len, "ignore_eos": True, "stream": True,
+                   "temperature": 1.0}
+        async with session.post(f"{base}/v1/completions", json=payload) as r:
+            async for raw in r.content:
+                line = raw.decode().strip()
+                if not line.startswith("data:") or line.endswith("[DONE]"):
+                    continue
+                now = time.perf_counter()
+                if ttft is None:
+                    ttft = now - t0
+                n += 1
+                last = now
+        results.append({"ttft": ttft or 0.0, "e2e": last - t0, "chunks": n,
+                        "tpot": (last - t0 - (ttft or 0.0)) / max(ns.output_len - 1, 1)})
+
+    async with aiohttp.ClientSession(timeout=aiohttp.ClientTimeout(total=3600)) as session:
+        tasks = []
+        t_start = time.perf_counter()
+        for _ in range(ns.num_prompts):
+            ln = rng.randint(*ns.input_len_range) if ns.input_len_range else ns.input_len
+            ids = [rng.randrange(ns.vocab_size) for _ in range(ln)]
+            tasks.append(asyncio.create_task(one(session, ids)))
+            if ns.request_rate != float("inf"):
+                await asyncio.sleep(rng.expovariate(ns.request_rate))
+        await asyncio.gather(*tasks)
+        dt = time.perf_counter() - t_start
+    ttft = [r["ttft"] for r in results]
+    tpot = [r["tpot"] for r in results]
+    return {"completed": len(results), "duration_s": dt, "request_rate": ns.request_rate,
+            "output_tokens_per_s": len(results) * ns.output_len / dt,
+            "ttft_p50_ms": _percentile(ttft, 0.5) * 1e3, "ttft_p99_ms": _percentile(ttft, 0.99) * 1e3,
+            "tpot_p50_ms": _percentile(tpot, 0.5) * 1e3, "tpot_p99_ms": _percentile(tpot, 0.99) * 1e3}
+
+
+def main(ns: argparse.Namespace) -> None:
+    if ns.mode == "serve":
+        print(json.dumps(asyncio.run(_serve(ns))))
+    else:
+        _offline(ns)

@@ -1,0 +1,172 @@
+"""Command line: ``sonar {serve,run,chat,complete,bench,run-batch,collect-env}``
+(also installed under the reference's name, ``aphrodite``).
+
+Parity: ``aphrodite/entrypoints/cli/main.py:16`` and its subcommand modules.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import platform
+import sys
+import time
+
+
+def _cmd_serve(ns: argparse.Namespace) -> None:
+    from sonar_b200.entrypoints.openai.api_server import run_server
+    run_server(ns)
+
+
+def _make_llm(ns: argparse.Namespace):
+    from sonar_b200 import LLM
+    from sonar_b200.config import EngineArgs
+    ns.model = ns.model or getattr(ns, "model_tag", None) or "tiny-llama"
+    args = EngineArgs.from_cli_args(ns)
+    kw = {k: v for k, v in vars(args).items() if k != "model"}
+    return LLM(args.model, **kw)
+
+
+def _cmd_run(ns: argparse.Namespace) -> None:
+    """One-shot generation from the command line."""
+    from sonar_b200 import SamplingParams
+    llm = _make_llm(ns)
+    sp = SamplingParams(max_tokens=ns.max_tokens, temperature=ns.temperature, top_p=ns.top_p)
+    prompts = ns.prompt or [sys.stdin.read()]
+    for out in llm.generate(prompts, sp):
+        print(out.outputs[0].text)
+    llm.shutdown()
+
+
+def _http(url: str, payload: dict | None, api_key: str | None):
+    import urllib.request
+    req = urllib.request.Request(url, data=None if payload is None else json.dumps(payload).encode(),
+                                 headers={"Content-Type": "application/json",
+                                          **({"Authorization": f"Bearer {api_key}"} if api_key else {})})
+    with urllib.request.urlopen(req, timeout=600) as r:
+        return json.loads(r.read())
+
+
+def _cmd_complete(ns: argparse.Namespace) -> None:
+    """Interactive completion client against a running server."""
+    base = ns.url.rstrip("/")
+    model = _http(f"{base}/v1/models", None, ns.api_key)["data"][0]["id"]
+    lines = [ns.quick] if ns.quick else iter(lambda: input("> "), "")
+    for line in lines:
+        res = _http(f"{base}/v1/completions", {"model": model, "prompt": line, "max_tokens": ns.max_tokens},
+                    ns.api_key)
+        print(res["choices"][0]["text"])
+
+
+def _cmd_chat(ns: argparse.Namespace) -> None:
+    """Interactive chat client against a running server."""
+    base = ns.url.rstrip("/")
+    model = _http(f"{base}/v1/models", None, ns.api_key)["data"][0]["id"]
+    history = [{"role": "system", "content": ns.system_prompt}] if ns.system_prompt else []
+    lines = [ns.quick] if ns.quick else iter(lambda: input("> "), "")
+    for line in lines:
+        history.append({"role": "user", "content": line})
+        res = _http(f"{base}/v1/chat/completions", {"model": model, "messages": history,
+                                                    "max_tokens": ns.max_tokens}, ns.api_key)
+        msg = res["choices"][0]["message"]["content"]
+        history.append({"role": "assistant", "content": msg})
+        print(msg)
+
+
+def _cmd_run_batch(ns: argparse.Namespace) -> None:
+    """OpenAI batch file (JSONL of {custom_id, method, url, body}) → JSONL of responses, offline."""
+    from sonar_b200 import SamplingParams
+    from sonar_b200.utils.tokenizer import apply_chat_template
+    llm = _make_llm(ns)
+    tok = llm.get_tokenizer()
+    reqs = [json.loads(l) for l in open(ns.input_file) if l.strip()]
+    prompts, params = [], []
+    for r in reqs:
+        body = r["body"]
+        if r["url"].endswith("/chat/completions"):
+            prompts.append(apply_chat_template(tok, body["messages"], True))
+        else:
+            prompts.append(body["prompt"])
+        params.append(SamplingParams(max_tokens=body.get("max_tokens", 16), temperature=body.get("temperature", 1.0),
+                                     top_p=body.get("top_p", 1.0), stop=body.get("stop")))
+    outs = llm.generate(prompts, params)
+    with open(ns.output_file, "w") as f:
+        for r, o in zip(reqs, outs):
+            c = o.outputs[0]
+            if r["url"].endswith("/chat/completions"):
+                choice = {"index": 0, "message": {"role": "assistant", "content": c.text}, "finish_reason": c.finish_reason}
+            else:
+                choice = {"index": 0, "text": c.text, "finish_reason": c.finish_reason}
+            f.write(json.dumps({"id": f"batch-{o.request_id}", "custom_id": r.get("custom_id"),
+                                "response": {"status_code": 200, "body": {"choices": [choice], "usage": {
+                                    "prompt_tokens": len(o.prompt_token_ids), "completion_tokens": len(c.token_ids)}}},
+                                "error": None}) + "\n")
+    llm.shutdown()
+
+
+def _cmd_bench(ns: argparse.Namespace) -> None:
+    from sonar_b200.entrypoints import bench
+    bench.main(ns)
+
+
+def _cmd_collect_env(ns: argparse.Namespace) -> None:
+    import torch
+    info = {"python": sys.version.split()[0], "platform": platform.platform(), "torch": torch.__version__,
+            "cuda_available": torch.cuda.is_available(), "cuda": torch.version.cuda}
+    if torch.cuda.is_available():
+        info["gpus"] = [torch.cuda.get_device_name(i) for i in range(torch.cuda.device_count())]
+        info["capability"] = list(torch.cuda.get_device_capability(0))
+    try:
+        import os
+        from sonar_b200.ops import build
+        info["kernel_library"] = build.LIB_PATH if os.path.exists(build.LIB_PATH) else "not built"
+    except Exception as e:  # noqa: BLE001
+        info["kernel_library"] = f"error: {e}"
+    from sonar_b200.version import __version__
+    info["sonar_b200"] = __version__
+    print(json.dumps(info, indent=2))
+
+
+def build_parser() -> argparse.ArgumentParser:
+    from sonar_b200.config import EngineArgs
+    from sonar_b200.entrypoints.openai.api_server import make_arg_parser
+    p = argparse.ArgumentParser(prog="sonar")
+    sub = p.add_subparsers(dest="cmd", required=True)
+    make_arg_parser(sub.add_parser("serve", help="start the OpenAI-compatible server")).set_defaults(fn=_cmd_serve)
+    run = sub.add_parser("run", help="generate once, offline")
+    run.add_argument("model_tag", nargs="?")
+    run.add_argument("--model", default=None)
+    run.add_argument("--prompt", action="append")
+    run.add_argument("--max-tokens", type=int, default=64)
+    run.add_argument("--temperature", type=float, default=0.8)
+    run.add_argument("--top-p", type=float, default=0.95)
+    EngineArgs.add_cli_args(run)
+    run.set_defaults(fn=_cmd_run)
+    for name, fn in (("chat", _cmd_chat), ("complete", _cmd_complete)):
+        c = sub.add_parser(name, help=f"interactive {name} client for a running server")
+        c.add_argument("--url", default="http://127.0.0.1:2242")
+        c.add_argument("--api-key", default=None)
+        c.add_argument("--max-tokens", type=int, default=128)
+        c.add_argument("--quick", "-q", default=None, help="send one message and exit")
+        c.add_argument("--system-prompt", default=None)
+        c.set_defaults(fn=fn)
+    rb = sub.add_parser("run-batch", help="process an OpenAI batch JSONL file offline")
+    rb.add_argument("-i", "--input-file", required=True)
+    rb.add_argument("-o", "--output-file", required=True)
+    rb.add_argument("--model", default=None)
+    EngineArgs.add_cli_args(rb)
+    rb.set_defaults(fn=_cmd_run_batch)
+    b = sub.add_parser("bench", help="latency / throughput / serve benchmarks")
+    from sonar_b200.entrypoints import bench as bench_mod
+    bench_mod.add_args(b)
+    b.set_defaults(fn=_cmd_bench)
+    sub.add_parser("collect-env", help="print environment information").set_defaults(fn=_cmd_collect_env)
+    return p
+
+
+def main(argv: list[str] | None = None) -> None:
+    ns = build_parser().parse_args(argv)
+    ns.fn(ns)
+
+
+if __name__ == "__main__":
+    main()

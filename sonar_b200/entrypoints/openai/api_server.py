@@ -1,0 +1,437 @@
+"""OpenAI-compatible HTTP server.
+
+Routes: ``/v1/completions``, ``/v1/chat/completions`` (streaming by SSE),
+``/v1/models``, ``/v1/embeddings``, ``/tokenize``, ``/detokenize``, ``/health``,
+``/ping``, ``/version``, ``/metrics``, Anthropic-style ``/v1/messages``,
+Kobold ``/api/v1/generate`` + ``/api/v1/model``, and the development routes
+``/reset_prefix_cache``, ``/pause``, ``/resume``, ``/is_paused``,
+``/collective_rpc``, ``/server_info``.  Optional bearer-token auth
+(``--api-key`` / ``SONAR_API_KEY``).  Default port 2242.
+
+Parity: ``aphrodite/entrypoints/openai/api_server.py:104-710`` (``build_app`` :183),
+chat serving ``chat_completion/serving.py``, completion serving ``completion/serving.py``.
+"""
+from __future__ import annotations
+
+import argparse
+import asyncio
+import base64
+import json
+import struct
+import time
+import uuid
+from contextlib import asynccontextmanager
+from typing import Any, AsyncGenerator
+
+from fastapi import FastAPI, Request
+from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+
+from sonar_b200 import envs
+from sonar_b200.config import EngineArgs
+from sonar_b200.engine.async_llm import AsyncLLM
+from sonar_b200.engine.core_client import EngineDeadError
+from sonar_b200.entrypoints.openai import protocol as P
+from sonar_b200.logger import init_logger
+from sonar_b200.sampling_params import PoolingParams, SamplingParams
+from sonar_b200.utils.tokenizer import apply_chat_template
+from sonar_b200.version import __version__
+
+logger = init_logger(__name__)
+
+
+def _error(msg: str, code: int = 400, typ: str = "BadRequestError") -> JSONResponse:
+    return JSONResponse(P.ErrorResponse(message=msg, type=typ, code=code).model_dump(), status_code=code)
+
+
+def _usage(n_prompt: int, n_out: int, cached: int = 0) -> P.UsageInfo:
+    return P.UsageInfo(prompt_tokens=n_prompt, completion_tokens=n_out, total_tokens=n_prompt + n_out,
+                       prompt_tokens_details={"cached_tokens": cached} if cached else None)
+
+
+class ServingState:
+    def __init__(self, engine: AsyncLLM, served_name: str, api_key: str | None) -> None:
+        self.engine = engine
+        self.name = served_name
+        self.api_key = api_key
+        self.start = time.time()
+
+    @property
+    def tokenizer(self):
+        return self.engine.tokenizer
+
+    @property
+    def max_model_len(self) -> int:
+        return self.engine.cfg.model.max_model_len
+
+
+def build_app(state: ServingState) -> FastAPI:
+    @asynccontextmanager
+    async def lifespan(app: FastAPI):
+        yield
+        state.engine.shutdown()
+
+    app = FastAPI(title="sonar_b200", version=__version__, lifespan=lifespan)
+    app.state.serving = state
+
+    @app.middleware("http")
+    async def auth(request: Request, call_next):
+        if state.api_key and request.url.path.startswith(("/v1", "/api")):
+            if request.headers.get("authorization") != f"Bearer {state.api_key}":
+                return _error("invalid or missing API key", 401, "AuthenticationError")
+        return await call_next(request)
+
+    @app.exception_handler(EngineDeadError)
+    async def dead(request: Request, exc: EngineDeadError):
+        return _error(f"engine is dead: {exc}", 500, "InternalServerError")
+
+    # ---------------------------------------------------------------- basic
+    @app.get("/health")
+    @app.get("/ping")
+    async def health():
+        try:
+            await state.engine.check_health()
+        except EngineDeadError as e:
+            return _error(str(e), 503, "ServiceUnavailable")
+        return PlainTextResponse("")
+
+    @app.get("/version")
+    async def version():
+        return {"version": __version__}
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": state.name, "object": "model", "created": int(state.start),
+                                            "owned_by": "sonar_b200", "max_model_len": state.max_model_len}]}
+
+    @app.get("/metrics")
+    async def metrics():
+        return PlainTextResponse(state.engine.metrics.render(), media_type="text/plain; version=0.0.4")
+
+    @app.get("/server_info")
+    async def server_info():
+        cfg = state.engine.cfg
+        return {"model": cfg.model.model, "dtype": str(cfg.model.dtype), "max_model_len": cfg.model.max_model_len,
+                "tensor_parallel_size": cfg.parallel.tensor_parallel_size, "block_size": cfg.cache.block_size,
+                "max_num_seqs": cfg.scheduler.max_num_seqs, "uptime_s": time.time() - state.start}
+
+    # ---------------------------------------------------------------- tokenization
+    @app.post("/tokenize")
+    async def tokenize(req: P.TokenizeRequest):
+        tok = state.tokenizer
+        if tok is None:
+            return _error("the server runs without a tokenizer")
+        if req.messages is not None:
+            text = apply_chat_template(tok, [m.model_dump(exclude_none=True) for m in req.messages],
+                                       req.add_generation_prompt)
+            ids = tok.encode(text, add_special_tokens=False)
+        else:
+            ids = tok.encode(req.prompt or "", add_special_tokens=req.add_special_tokens)
+        return {"tokens": ids, "count": len(ids), "max_model_len": state.max_model_len}
+
+    @app.post("/detokenize")
+    async def detokenize(req: P.DetokenizeRequest):
+        if state.tokenizer is None:
+            return _error("the server runs without a tokenizer")
+        return {"prompt": state.tokenizer.decode(req.tokens)}
+
+    # ---------------------------------------------------------------- completions
+    def _normalise_prompts(prompt) -> list:
+        if isinstance(prompt, str):
+            return [prompt]
+        if prompt and isinstance(prompt[0], int):
+            return [{"prompt_token_ids": list(prompt)}]
+        if prompt and isinstance(prompt[0], list):
+            return [{"prompt_token_ids": list(p)} for p in prompt]
+        return list(prompt)
+
+    def _completion_logprobs(comp, tok) -> P.CompletionLogprobs | None:
+        if comp.logprobs is None:
+            return None
+        lp = P.CompletionLogprobs()
+        off = 0
+        for tid, d in zip(comp.token_ids, comp.logprobs):
+            text = d[tid].decoded_token if tid in d and d[tid].decoded_token is not None else str(tid)
+            lp.tokens.append(text)
+            lp.token_logprobs.append(d[tid].logprob if tid in d else None)
+            lp.top_logprobs.append({(v.decoded_token or str(k)): v.logprob for k, v in d.items()})
+            lp.text_offset.append(off)
+            off += len(text)
+        return lp
+
+    @app.post("/v1/completions")
+    async def completions(req: P.CompletionRequest, raw: Request):
+        try:
+            prompts = _normalise_prompts(req.prompt)
+            sp = req.to_sampling_params(16, req.logprobs, req.stream)
+        except (ValueError, TypeError) as e:
+            return _error(str(e))
+        rid = f"cmpl-{uuid.uuid4().hex}"
+        model = req.model or state.name
+        gens = []
+        try:
+            for i, p in enumerate(prompts):
+                gens.append(state.engine.generate(p, sp, f"{rid}-{i}", priority=req.priority))
+        except ValueError as e:
+            return _error(str(e))
+
+        if req.stream:
+            async def sse() -> AsyncGenerator[str, None]:
+                n_prompt = n_out = 0
+                try:
+                    queue: asyncio.Queue = asyncio.Queue()
+
+                    async def pump(i, g):
+                        try:
+                            async for out in g:
+                                await queue.put((i, out))
+                        except Exception as e:  # noqa: BLE001
+                            await queue.put((i, e))
+                        await queue.put((i, None))
+                    tasks = [asyncio.create_task(pump(i, g)) for i, g in enumerate(gens)]
+                    live = len(tasks)
+                    while live:
+                        i, out = await queue.get()
+                        if out is None:
+                            live -= 1
+                            continue
+                        if isinstance(out, Exception):
+                            yield f"data: {json.dumps({'error': str(out)})}\n\n"
+                            continue
+                        if out.finished:
+                            n_prompt += len(out.prompt_token_ids or [])
+                        for c in out.outputs:
+                            n_out += len(c.token_ids)
+                            chunk = P.CompletionResponse(id=rid, model=model, choices=[P.CompletionChoice(
+                                index=i * sp.n + c.index, text=c.text, finish_reason=c.finish_reason,
+                                stop_reason=c.stop_reason, logprobs=_completion_logprobs(c, state.tokenizer))])
+                            yield f"data: {chunk.model_dump_json(exclude_none=True)}\n\n"
+                    if req.stream_options and req.stream_options.include_usage:
+                        final = P.CompletionResponse(id=rid, model=model, choices=[], usage=_usage(n_prompt, n_out))
+                        yield f"data: {final.model_dump_json(exclude_none=True)}\n\n"
+                    yield "data: [DONE]\n\n"
+                except asyncio.CancelledError:
+                    for t in tasks:
+                        t.cancel()
+                    raise
+            return StreamingResponse(sse(), media_type="text/event-stream")
+
+        choices, n_prompt, n_out, cached = [], 0, 0, 0
+        try:
+            for i, g in enumerate(gens):
+                final = None
+                async for out in g:
+                    if await raw.is_disconnected():
+                        await state.engine.abort(f"{rid}-{i}")
+                        return _error("client disconnected", 499, "ClientClosedRequest")
+                    final = out
+                n_prompt += len(final.prompt_token_ids or [])
+                cached += final.num_cached_tokens
+                for c in final.outputs:
+                    n_out += len(c.token_ids)
+                    text = ((final.prompt or "") + c.text) if req.echo else c.text
+                    choices.append(P.CompletionChoice(index=i * sp.n + c.index, text=text,
+                                                      finish_reason=c.finish_reason, stop_reason=c.stop_reason,
+                                                      logprobs=_completion_logprobs(c, state.tokenizer)))
+        except ValueError as e:
+            return _error(str(e))
+        return P.CompletionResponse(id=rid, model=model, choices=choices, usage=_usage(n_prompt, n_out, cached))
+
+    # ---------------------------------------------------------------- chat
+    def _chat_logprobs(comp) -> P.ChatLogprobs | None:
+        if comp.logprobs is None:
+            return None
+        entries = []
+        for tid, d in zip(comp.token_ids, comp.logprobs):
+            tok_s = (d[tid].decoded_token if tid in d else None) or str(tid)
+            top = [{"token": v.decoded_token or str(k), "logprob": v.logprob,
+                    "bytes": list((v.decoded_token or "").encode())} for k, v in d.items()]
+            entries.append(P.ChatLogprobEntry(token=tok_s, logprob=d[tid].logprob if tid in d else 0.0,
+                                              bytes=list(tok_s.encode()), top_logprobs=top))
+        return P.ChatLogprobs(content=entries)
+
+    @app.post("/v1/chat/completions")
+    async def chat(req: P.ChatCompletionRequest, raw: Request):
+        tok = state.tokenizer
+        if tok is None:
+            return _error("chat needs a tokenizer")
+        try:
+            msgs = [m.model_dump(exclude_none=True) for m in req.messages]
+            prompt = apply_chat_template(tok, msgs, req.add_generation_prompt, req.chat_template, req.tools)
+            n_lp = (req.top_logprobs or 1) if req.logprobs else None
+            default_max = req.max_completion_tokens or (state.max_model_len - len(tok.encode(prompt)) - 1)
+            sp = req.to_sampling_params(max(default_max, 1), n_lp, req.stream)
+        except (ValueError, TypeError) as e:
+            return _error(str(e))
+        rid = f"chatcmpl-{uuid.uuid4().hex}"
+        model = req.model or state.name
+        try:
+            gen = state.engine.generate(prompt, sp, rid, priority=req.priority)
+        except ValueError as e:
+            return _error(str(e))
+
+        if req.stream:
+            async def sse() -> AsyncGenerator[str, None]:
+                created = int(time.time())
+                first = {i: True for i in range(sp.n)}
+                n_prompt = n_out = 0
+                try:
+                    async for out in gen:
+                        n_prompt = len(out.prompt_token_ids or [])
+                        for c in out.outputs:
+                            n_out += len(c.token_ids)
+                            delta: dict[str, Any] = {"content": c.text}
+                            if first[c.index]:
+                                delta["role"] = "assistant"
+                                first[c.index] = False
+                            choice: dict[str, Any] = {"index": c.index, "delta": delta,
+                                                      "finish_reason": c.finish_reason}
+                            lp = _chat_logprobs(c)
+                            if lp is not None:
+                                choice["logprobs"] = lp.model_dump()
+                            chunk = {"id": rid, "object": "chat.completion.chunk", "created": created,
+                                     "model": model, "choices": [choice]}
+                            yield f"data: {json.dumps(chunk)}\n\n"
+                    if req.stream_options and req.stream_options.include_usage:
+                        chunk = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": model,
+                                 "choices": [], "usage": _usage(n_prompt, n_out).model_dump(exclude_none=True)}
+                        yield f"data: {json.dumps(chunk)}\n\n"
+                except ValueError as e:
+                    yield f"data: {json.dumps({'error': str(e)})}\n\n"
+                yield "data: [DONE]\n\n"
+            return StreamingResponse(sse(), media_type="text/event-stream")
+
+        final = None
+        try:
+            async for out in gen:
+                if await raw.is_disconnected():
+                    await state.engine.abort(rid)
+                    return _error("client disconnected", 499, "ClientClosedRequest")
+                final = out
+        except ValueError as e:
+            return _error(str(e))
+        choices = [P.ChatChoice(index=c.index, message=P.ChatResponseMessage(content=c.text),
+                                finish_reason=c.finish_reason, stop_reason=c.stop_reason, logprobs=_chat_logprobs(c))
+                   for c in final.outputs]
+        n_out = sum(len(c.token_ids) for c in final.outputs)
+        return P.ChatCompletionResponse(id=rid, model=model, choices=choices,
+                                        usage=_usage(len(final.prompt_token_ids or []), n_out, final.num_cached_tokens))
+
+    # ---------------------------------------------------------------- Anthropic-style messages
+    @app.post("/v1/messages")
+    async def messages(body: dict):
+        tok = state.tokenizer
+        if tok is None:
+            return _error("messages need a tokenizer")
+        msgs = list(body.get("messages", []))
+        if body.get("system"):
+            msgs.insert(0, {"role": "system", "content": body["system"]})
+        prompt = apply_chat_template(tok, msgs, True)
+        sp = SamplingParams(max_tokens=int(body.get("max_tokens", 256)), temperature=float(body.get("temperature", 1.0)),
+                            top_p=float(body.get("top_p", 1.0)), top_k=int(body.get("top_k", 0) or 0),
+                            stop=body.get("stop_sequences"))
+        rid = f"msg_{uuid.uuid4().hex}"
+        final = None
+        async for out in state.engine.generate(prompt, sp, rid):
+            final = out
+        c = final.outputs[0]
+        stop_reason = {"stop": "end_turn", "length": "max_tokens"}.get(c.finish_reason or "", c.finish_reason)
+        if c.finish_reason == "stop" and isinstance(c.stop_reason, str):
+            stop_reason = "stop_sequence"
+        return {"id": rid, "type": "message", "role": "assistant", "model": body.get("model", state.name),
+                "content": [{"type": "text", "text": c.text}], "stop_reason": stop_reason,
+                "stop_sequence": c.stop_reason if isinstance(c.stop_reason, str) else None,
+                "usage": {"input_tokens": len(final.prompt_token_ids or []), "output_tokens": len(c.token_ids)}}
+
+    # ---------------------------------------------------------------- embeddings
+    @app.post("/v1/embeddings")
+    async def embeddings(req: P.EmbeddingRequest):
+        prompts = _normalise_prompts(req.input)
+        data, n_tok = [], 0
+        for i, p in enumerate(prompts):
+            out = await state.engine.encode(p, PoolingParams(dimensions=req.dimensions), f"embd-{uuid.uuid4().hex}")
+            vec = out.outputs.data
+            vals = vec.tolist() if hasattr(vec, "tolist") else list(vec)
+            if req.dimensions:
+                vals = vals[: req.dimensions]
+            n_tok += len(out.prompt_token_ids)
+            emb: Any = vals
+            if req.encoding_format == "base64":
+                emb = base64.b64encode(struct.pack(f"<{len(vals)}f", *vals)).decode()
+            data.append({"object": "embedding", "index": i, "embedding": emb})
+        return {"object": "list", "model": req.model or state.name, "data": data,
+                "usage": {"prompt_tokens": n_tok, "total_tokens": n_tok}}
+
+    # ---------------------------------------------------------------- Kobold
+    @app.get("/api/v1/model")
+    async def kobold_model():
+        return {"result": state.name}
+
+    @app.get("/api/v1/config/max_context_length")
+    async def kobold_ctx():
+        return {"value": state.max_model_len}
+
+    @app.post("/api/v1/generate")
+    async def kobold_generate(body: dict):
+        sp = SamplingParams(max_tokens=int(body.get("max_length", 80)), temperature=float(body.get("temperature", 1.0)),
+                            top_p=float(body.get("top_p", 1.0)), top_k=int(body.get("top_k", 0) or 0),
+                            top_a=float(body.get("top_a", 0.0)), tfs=float(body.get("tfs", 1.0)),
+                            typical_p=float(body.get("typical", 1.0)),
+                            repetition_penalty=float(body.get("rep_pen", 1.0)), stop=body.get("stop_sequence"))
+        final = None
+        async for out in state.engine.generate(body.get("prompt", ""), sp, f"kobold-{uuid.uuid4().hex}"):
+            final = out
+        return {"results": [{"text": final.outputs[0].text}]}
+
+    # ---------------------------------------------------------------- development routes
+    @app.post("/reset_prefix_cache")
+    async def reset_prefix_cache():
+        ok = await state.engine.reset_prefix_cache()
+        return {"reset": bool(ok)}
+
+    @app.post("/pause")
+    async def pause():
+        await state.engine.pause_generation()
+        return {"paused": True}
+
+    @app.post("/resume")
+    async def resume():
+        await state.engine.resume_generation()
+        return {"paused": False}
+
+    @app.get("/is_paused")
+    async def is_paused():
+        return {"is_paused": await state.engine.is_paused()}
+
+    @app.post("/collective_rpc")
+    async def collective_rpc(body: dict):
+        res = await state.engine.collective_rpc(body["method"], *body.get("args", []), **body.get("kwargs", {}))
+        return {"results": json.loads(json.dumps(res, default=str))}
+
+    return app
+
+
+def make_arg_parser(parser: argparse.ArgumentParser | None = None) -> argparse.ArgumentParser:
+    parser = parser or argparse.ArgumentParser(description="sonar_b200 OpenAI-compatible server")
+    parser.add_argument("model_tag", nargs="?", default=None, help="model directory or architecture preset")
+    parser.add_argument("--model", default=None)
+    parser.add_argument("--host", default=envs.SONAR_HOST)
+    parser.add_argument("--port", type=int, default=envs.SONAR_PORT)
+    parser.add_argument("--api-key", default=envs.SONAR_API_KEY)
+    parser.add_argument("--uvicorn-log-level", default="warning")
+    EngineArgs.add_cli_args(parser)
+    return parser
+
+
+def run_server(ns: argparse.Namespace) -> None:
+    import uvicorn
+    ns.model = ns.model or ns.model_tag or "tiny-llama"
+    args = EngineArgs.from_cli_args(ns)
+    engine = AsyncLLM.from_engine_args(args)
+    state = ServingState(engine, args.served_model_name or args.model, ns.api_key)
+    app = build_app(state)
+    logger.info("serving %s on http://%s:%d", state.name, ns.host, ns.port)
+    uvicorn.run(app, host=ns.host, port=ns.port, log_level=ns.uvicorn_log_level)
+
+
+if __name__ == "__main__":
+    run_server(make_arg_parser().parse_args())

@@ -1,0 +1,80 @@
+"""OpenAI-compatible server end to end on CPU: engine core in a child process behind ZMQ."""
+import json
+
+import pytest
+
+from sonar_b200.config import EngineArgs
+
+
+@pytest.fixture(scope="module")
+def client():
+    from fastapi.testclient import TestClient
+
+    from sonar_b200.engine.async_llm import AsyncLLM
+    from sonar_b200.entrypoints.openai.api_server import ServingState, build_app
+    args = EngineArgs(model="tiny-llama", dtype="float32", max_model_len=256, num_gpu_blocks_override=128,
+                      max_num_seqs=8, max_num_batched_tokens=64, device="cpu")
+    engine = AsyncLLM.from_engine_args(args)
+    app = build_app(ServingState(engine, "tiny", None))
+    with TestClient(app) as c:
+        yield c
+
+
+def test_health_models_version(client):
+    assert client.get("/health").status_code == 200
+    assert client.get("/v1/models").json()["data"][0]["id"] == "tiny"
+    assert "version" in client.get("/version").json()
+
+
+def test_completion_and_usage(client):
+    r = client.post("/v1/completions", json={"prompt": "hello", "max_tokens": 5, "temperature": 0, "ignore_eos": True})
+    assert r.status_code == 200, r.text
+    body = r.json()
+    assert body["usage"]["completion_tokens"] == 5 and body["choices"][0]["finish_reason"] == "length"
+    # greedy is deterministic and n / token-id prompts work
+    r2 = client.post("/v1/completions", json={"prompt": "hello", "max_tokens": 5, "temperature": 0, "ignore_eos": True})
+    assert r2.json()["choices"][0]["text"] == body["choices"][0]["text"]
+    r3 = client.post("/v1/completions", json={"prompt": [5, 6, 7, 8], "max_tokens": 3, "n": 2, "seed": 1,
+                                              "ignore_eos": True, "logprobs": 2})
+    assert len(r3.json()["choices"]) == 2 and r3.json()["choices"][0]["logprobs"]["tokens"]
+
+
+def test_chat_streaming(client):
+    with client.stream("POST", "/v1/chat/completions", json={
+            "messages": [{"role": "user", "content": "hi"}], "max_tokens": 6, "stream": True, "ignore_eos": True,
+            "stream_options": {"include_usage": True}}) as r:
+        lines = [l for l in r.iter_lines() if l.startswith("data:")]
+    assert lines[-1] == "data: [DONE]"
+    chunks = [json.loads(l[5:]) for l in lines[:-1]]
+    assert chunks[0]["choices"][0]["delta"]["role"] == "assistant"
+    assert chunks[-1]["usage"]["completion_tokens"] == 6
+    assert any(c["choices"] and c["choices"][0]["finish_reason"] == "length" for c in chunks)
+
+
+def test_chat_non_streaming_and_errors(client):
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4,
+                                                  "ignore_eos": True, "logprobs": True, "top_logprobs": 2})
+    assert r.status_code == 200 and r.json()["choices"][0]["message"]["role"] == "assistant"
+    assert len(r.json()["choices"][0]["logprobs"]["content"]) == 4
+    bad = client.post("/v1/completions", json={"prompt": "x", "max_tokens": 4, "temperature": -1})
+    assert bad.status_code == 400 and bad.json()["object"] == "error"
+    too_long = client.post("/v1/completions", json={"prompt": [5] * 400, "max_tokens": 4})
+    assert too_long.status_code == 400
+
+
+def test_tokenize_metrics_and_dev_routes(client):
+    t = client.post("/tokenize", json={"prompt": "abc"}).json()
+    assert t["count"] == len(t["tokens"]) == 4
+    assert client.post("/detokenize", json={"tokens": t["tokens"]}).json()["prompt"] == "abc"
+    m = client.get("/metrics").text
+    assert "sonar:generation_tokens_total" in m and "sonar:time_to_first_token_seconds_bucket" in m
+    assert client.post("/reset_prefix_cache").status_code == 200
+    assert client.post("/pause").json()["paused"] is True
+    assert client.get("/is_paused").json()["is_paused"] is True
+    assert client.post("/resume").json()["paused"] is False
+    e = client.post("/v1/embeddings", json={"input": "embed me"}).json()
+    assert len(e["data"][0]["embedding"]) == 256
+    a = client.post("/v1/messages", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3}).json()
+    assert a["type"] == "message" and a["usage"]["output_tokens"] <= 3
+    k = client.post("/api/v1/generate", json={"prompt": "hi", "max_length": 3}).json()
+    assert "text" in k["results"][0]

@@ -1,0 +1,207 @@
+"""Scheduler, block pool and KV manager behaviour (pure CPU, no model)."""
+import pytest
+
+from sonar_b200.config import CacheConfig, SchedulerConfig, SpeculativeConfig
+from sonar_b200.core.block_pool import NULL_BLOCK, BlockPool, make_block_hasher
+from sonar_b200.core.kv_cache_manager import KVCacheManager, KVCacheSpec, get_kv_cache_config
+from sonar_b200.core.scheduler import ModelRunnerOutput, Scheduler
+from sonar_b200.request import EngineCoreRequest, Request, RequestStatus
+from sonar_b200.sampling_params import SamplingParams
+
+
+def mk_req(rid, n_prompt, max_tokens=4, priority=0, base=10, **sp):
+    return EngineCoreRequest(rid, [base + (i % 50) for i in range(n_prompt)],
+                             SamplingParams(max_tokens=max_tokens, ignore_eos=True, **sp), eos_token_id=2,
+                             priority=priority, arrival_time=float(hash(rid) % 1000))
+
+
+def mk_sched(blocks=64, budget=64, seqs=4, policy="fcfs", caching=True, spec=0, max_len=256, **kw):
+    sc = SchedulerConfig(max_num_batched_tokens=budget, max_num_seqs=seqs, max_model_len=max_len, policy=policy,
+                         watermark=0.0, **kw)
+    cc = CacheConfig(block_size=16, enable_prefix_caching=caching)
+    sp = SpeculativeConfig("ngram", spec) if spec else None
+    return Scheduler(sc, cc, blocks, sp)
+
+
+def run_step(s, token=7, tokens_for=None):
+    so = s.schedule()
+    ro = ModelRunnerOutput()
+    for rid, n in so.num_scheduled_tokens.items():
+        req = s.requests[rid]
+        ro.req_ids.append(rid)
+        done = req.num_computed_tokens >= req.num_tokens     # schedule() already advanced it
+        ro.sampled_token_ids.append([(tokens_for or {}).get(rid, token)] if done else [])
+    return so, s.update_from_output(so, ro)
+
+
+# ---------------------------------------------------------------- block pool
+def test_block_pool_alloc_free_lru_order():
+    p = BlockPool(8)
+    assert p.get_num_free_blocks() == 7
+    a = p.get_new_blocks(3)
+    assert a == [1, 2, 3] and NULL_BLOCK not in a
+    p.free_blocks(reversed(a))                 # tail first
+    assert p.free_list()[-3:] == [3, 2, 1]
+    with pytest.raises(ValueError):
+        p.get_new_blocks(8)
+
+
+def test_prefix_cache_hit_touch_and_eviction():
+    p = BlockPool(6)
+    blocks = p.get_new_blocks(2)
+    hashes = [b"h0" * 8, b"h1" * 8]
+    p.cache_full_blocks(blocks, hashes, 0, 2)
+    p.free_blocks(reversed(blocks))
+    assert p.get_cached_block(hashes[0]) == blocks[0]
+    p.touch([blocks[0]])                       # leaves the free list
+    assert blocks[0] not in p.free_list() and p.ref_cnt[blocks[0]] == 1
+    got = p.get_new_blocks(4)                  # takes every remaining free block, evicting the cached one
+    assert blocks[1] in got and p.get_cached_block(hashes[1]) is None
+    assert p.get_cached_block(hashes[0]) == blocks[0]
+
+
+def test_block_hash_chain_depends_on_prefix_and_salt():
+    hasher = make_block_hasher(4)
+    r1 = Request(EngineCoreRequest("a", [1, 2, 3, 4, 5, 6, 7, 8, 9], SamplingParams()), hasher)
+    r2 = Request(EngineCoreRequest("b", [9, 2, 3, 4, 5, 6, 7, 8, 9], SamplingParams()), hasher)
+    r3 = Request(EngineCoreRequest("c", [1, 2, 3, 4, 5, 6, 7, 8], SamplingParams(), cache_salt="s"), hasher)
+    assert len(r1.block_hashes) == 2 and r1.block_hashes[1] != r2.block_hashes[1]   # same tokens, other parent
+    assert r1.block_hashes[0] != r3.block_hashes[0]
+    r1.append_output_token_ids([10, 11, 12])
+    assert len(r1.block_hashes) == 3
+
+
+def test_kv_config_rejects_too_small_budget():
+    spec = KVCacheSpec(16, 8, 128, 2)
+    assert spec.page_bytes == 2 * 16 * 8 * 128 * 2
+    with pytest.raises(ValueError):
+        get_kv_cache_config(spec, 32, 10 * spec.page_bytes * 32, max_model_len=4096)
+    assert get_kv_cache_config(spec, 32, 1000 * spec.page_bytes * 32, 4096).num_blocks == 1000
+
+
+def test_sliding_window_releases_old_blocks():
+    m = KVCacheManager(32, 16, enable_caching=False, sliding_window=32)
+    r = Request(EngineCoreRequest("a", list(range(100)), SamplingParams(max_tokens=50)))
+    assert m.allocate_slots(r, 100) is not None
+    r.num_computed_tokens = 100
+    used_before = 31 - m.pool.get_num_free_blocks()
+    r.append_output_token_ids(1)
+    m.allocate_slots(r, 1)
+    assert 31 - m.pool.get_num_free_blocks() < used_before
+    assert m.get_block_ids("a")[0] == NULL_BLOCK
+
+
+# ---------------------------------------------------------------- scheduler
+def test_chunked_prefill_and_decode_mix():
+    s = mk_sched(budget=48)
+    s.add_request(mk_req("a", 100))
+    so, _ = run_step(s)
+    assert so.num_scheduled_tokens == {"a": 48} and len(so.scheduled_new_reqs) == 1
+    s.add_request(mk_req("b", 20, base=300))
+    so, _ = run_step(s)                        # running first, then the newcomer fills the rest
+    assert so.num_scheduled_tokens == {"a": 48}
+    so, outs = run_step(s)
+    assert so.num_scheduled_tokens == {"a": 4, "b": 20}
+    assert sorted(o.request_id for o in outs.outputs) == ["a", "b"]
+    so, _ = run_step(s)
+    assert so.num_scheduled_tokens == {"a": 1, "b": 1}
+
+
+def test_finish_by_length_and_block_release():
+    s = mk_sched()
+    s.add_request(mk_req("a", 10, max_tokens=3))
+    free0 = s.kv.pool.get_num_free_blocks()
+    reasons = []
+    for _ in range(3):
+        _, outs = run_step(s)
+        reasons += [o.finish_reason for o in outs.outputs]
+    assert reasons[-1] is not None and str(reasons[-1]) == "length"
+    assert not s.has_unfinished_requests() and s.kv.pool.get_num_free_blocks() == free0
+    so = s.schedule()
+    assert so.finished_req_ids == {"a"}
+
+
+def test_eos_and_stop_token():
+    s = mk_sched()
+    s.add_request(EngineCoreRequest("a", [5] * 10, SamplingParams(max_tokens=10), eos_token_id=2))
+    s.add_request(EngineCoreRequest("b", [6] * 10, SamplingParams(max_tokens=10, stop_token_ids=[99]), eos_token_id=2))
+    _, outs = run_step(s, tokens_for={"a": 2, "b": 99})
+    by = {o.request_id: o for o in outs.outputs}
+    assert str(by["a"].finish_reason) == "stop" and by["a"].stop_reason is None
+    assert str(by["b"].finish_reason) == "stop" and by["b"].stop_reason == 99
+
+
+def test_prefix_cache_reuse_across_requests():
+    s = mk_sched(budget=128)
+    s.add_request(mk_req("a", 70, max_tokens=1))
+    run_step(s)
+    s.add_request(mk_req("b", 70, max_tokens=1))
+    so, outs = run_step(s)
+    assert so.num_scheduled_tokens["b"] == 70 - 64          # four full blocks came from the cache
+    assert outs.outputs[0].num_cached_tokens == 64
+
+
+def test_preemption_fcfs_evicts_last_and_resumes():
+    s = mk_sched(blocks=9, budget=64, seqs=4)                # 8 usable blocks
+    s.add_request(mk_req("a", 60, max_tokens=40, base=10))
+    s.add_request(mk_req("b", 60, max_tokens=40, base=200))
+    run_step(s)
+    assert {r.request_id for r in s.running} == {"a", "b"}   # 4 blocks each
+    preempted = False
+    for _ in range(8):
+        so, _ = run_step(s)
+        preempted |= bool(so.preempted_req_ids)
+        if preempted:
+            break
+    assert preempted and [r.request_id for r in s.running] == ["a"]
+    b = s.requests["b"]
+    assert b.status == RequestStatus.PREEMPTED and b.num_computed_tokens == 0 and b.num_preemptions == 1
+    # b comes back once a finishes, recomputing prompt + generated tokens
+    for _ in range(200):
+        run_step(s)
+        if not s.has_unfinished_requests():
+            break
+    assert not s.has_unfinished_requests()
+
+
+def test_priority_policy_orders_waiting_and_victims():
+    s = mk_sched(policy="priority", seqs=1)
+    s.add_request(mk_req("low", 10, priority=5))
+    s.add_request(mk_req("high", 10, priority=0))
+    so, _ = run_step(s)
+    assert list(so.num_scheduled_tokens) == ["high"]
+
+
+def test_abort_running_and_waiting():
+    s = mk_sched(seqs=1)
+    s.add_request(mk_req("a", 10))
+    s.add_request(mk_req("b", 10))
+    run_step(s)
+    s.finish_requests(["a", "b"], RequestStatus.FINISHED_ABORTED)
+    assert not s.has_unfinished_requests() and s.finished_req_ids == {"a"}
+
+
+def test_spec_decode_tokens_scheduled_and_rejection_rolled_back():
+    s = mk_sched(spec=2)
+    s.add_request(mk_req("a", 10, max_tokens=20))
+    run_step(s)
+    req = s.requests["a"]
+    req.spec_token_ids = [7, 8]
+    so = s.schedule()
+    assert so.num_scheduled_tokens["a"] == 3 and so.scheduled_spec_decode_tokens["a"] == [7, 8]
+    ro = ModelRunnerOutput(req_ids=["a"], sampled_token_ids=[[7, 9]])   # first draft accepted, second rejected
+    s.update_from_output(so, ro)
+    assert req.output_token_ids[-2:] == [7, 9]
+    assert req.num_computed_tokens == req.num_tokens - 1
+
+
+def test_max_model_len_rejected_and_capped():
+    s = mk_sched(max_len=32)
+    with pytest.raises(ValueError):
+        s.add_request(mk_req("a", 32))
+    s.add_request(mk_req("b", 30, max_tokens=10))
+    done = None
+    for _ in range(5):
+        _, outs = run_step(s)
+        done = next((o for o in outs.outputs if o.finished), done)
+    assert done is not None and str(done.finish_reason) == "length"

@@ -1,0 +1,200 @@
+// Single-writer, multi-reader message ring in POSIX shared memory.
+//
+// The executor broadcasts one RPC to all worker processes of a node through one ring (every reader sees
+// every message), and each worker answers through its own one-reader ring.  Layout: a header with the
+// writer's sequence number and one cache-line-padded sequence number per reader, then n_slots slots of
+// slot_bytes.  A message larger than a slot travels as consecutive chunks.  Readers spin briefly
+// (pause instruction), then yield, then sleep in short naps: RPC latency stays in the microsecond range
+// while an idle engine does not burn a core.  Waits take a timeout and return -2 when it expires, so a
+// dead peer is noticed by the caller instead of hanging it.
+//
+// Behavioural parity: the reference's shared-memory MessageQueue
+// (distributed/device_communicators/shm_broadcast.py:248-454) and its spin-wait helper (csrc/spinloop.cpp).
+#include <atomic>
+#include <cerrno>
+#include <chrono>
+#include <cstdint>
+#include <cstring>
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <thread>
+#include <unistd.h>
+
+#if defined(__x86_64__)
+#include <immintrin.h>
+#define CPU_RELAX() _mm_pause()
+#else
+#define CPU_RELAX() std::this_thread::yield()
+#endif
+
+namespace {
+
+constexpr uint32_t MAGIC = 0x534E5231;  // "SNR1"
+constexpr int MAX_READERS = 64;
+
+struct alignas(64) PaddedSeq { std::atomic<uint64_t> v; char pad[56]; };
+
+struct Header {
+  uint32_t magic, n_readers, n_slots, slot_bytes;
+  alignas(64) std::atomic<uint64_t> write_seq;   // chunks published so far
+  PaddedSeq read_seq[MAX_READERS];              // chunks consumed per reader
+};
+
+struct SlotHeader { uint32_t len; uint32_t more; };  // more = 1: the message continues in the next chunk
+
+struct Ring {
+  Header* h;
+  uint8_t* slots;
+  size_t map_bytes;
+  int owner;
+  char name[128];
+};
+
+size_t total_bytes(uint32_t n_slots, uint32_t slot_bytes) {
+  return sizeof(Header) + (size_t)n_slots * (sizeof(SlotHeader) + slot_bytes);
+}
+uint8_t* slot_ptr(Ring* r, uint64_t seq) {
+  return r->slots + (seq % r->h->n_slots) * (sizeof(SlotHeader) + r->h->slot_bytes);
+}
+
+// Wait until pred() holds; spin → yield → nap.  Returns false on timeout.
+template <typename F>
+bool wait_until(F pred, long timeout_ms) {
+  for (int i = 0; i < 2000; ++i) { if (pred()) return true; CPU_RELAX(); }
+  auto t0 = std::chrono::steady_clock::now();
+  int naps = 0;
+  while (!pred()) {
+    if (naps < 200) std::this_thread::yield();
+    else std::this_thread::sleep_for(std::chrono::microseconds(naps < 2000 ? 50 : 500));
+    ++naps;
+    if (timeout_ms >= 0 && (naps & 15) == 0) {
+      auto dt = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+      if (dt > timeout_ms) return false;
+    }
+  }
+  return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+void* ring_create(const char* name, int n_readers, int slot_bytes, int n_slots) {
+  if (n_readers < 1 || n_readers > MAX_READERS || slot_bytes < 64 || n_slots < 2) return nullptr;
+  shm_unlink(name);
+  int fd = shm_open(name, O_CREAT | O_EXCL | O_RDWR, 0600);
+  if (fd < 0) return nullptr;
+  size_t bytes = total_bytes(n_slots, slot_bytes);
+  if (ftruncate(fd, (off_t)bytes) != 0) { close(fd); shm_unlink(name); return nullptr; }
+  void* p = mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  close(fd);
+  if (p == MAP_FAILED) { shm_unlink(name); return nullptr; }
+  Header* h = new (p) Header();
+  h->n_readers = n_readers; h->n_slots = n_slots; h->slot_bytes = slot_bytes;
+  h->write_seq.store(0);
+  for (int i = 0; i < MAX_READERS; ++i) h->read_seq[i].v.store(0);
+  std::atomic_thread_fence(std::memory_order_release);
+  h->magic = MAGIC;
+  Ring* r = new Ring{h, (uint8_t*)p + sizeof(Header), bytes, 1, {0}};
+  strncpy(r->name, name, sizeof(r->name) - 1);
+  return r;
+}
+
+void* ring_open(const char* name) {
+  int fd = shm_open(name, O_RDWR, 0600);
+  if (fd < 0) return nullptr;
+  struct stat st;
+  if (fstat(fd, &st) != 0 || (size_t)st.st_size < sizeof(Header)) { close(fd); return nullptr; }
+  void* p = mmap(nullptr, st.st_size, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  close(fd);
+  if (p == MAP_FAILED) return nullptr;
+  Header* h = (Header*)p;
+  if (h->magic != MAGIC) { munmap(p, st.st_size); return nullptr; }
+  Ring* r = new Ring{h, (uint8_t*)p + sizeof(Header), (size_t)st.st_size, 0, {0}};
+  strncpy(r->name, name, sizeof(r->name) - 1);
+  return r;
+}
+
+void ring_close(void* handle) {
+  Ring* r = (Ring*)handle;
+  if (!r) return;
+  munmap(r->h, r->map_bytes);
+  if (r->owner) shm_unlink(r->name);
+  delete r;
+}
+
+// Returns 0, -1 (bad argument) or -2 (timeout: some reader did not free a slot in time).
+int ring_write(void* handle, const void* buf, long len, long timeout_ms) {
+  Ring* r = (Ring*)handle;
+  if (!r || len < 0) return -1;
+  Header* h = r->h;
+  const uint8_t* src = (const uint8_t*)buf;
+  long off = 0;
+  do {
+    uint64_t seq = h->write_seq.load(std::memory_order_relaxed);
+    auto has_room = [&]() {
+      uint64_t min_read = UINT64_MAX;
+      for (uint32_t i = 0; i < h->n_readers; ++i) {
+        uint64_t v = h->read_seq[i].v.load(std::memory_order_acquire);
+        if (v < min_read) min_read = v;
+      }
+      return seq - min_read < h->n_slots;
+    };
+    if (!wait_until(has_room, timeout_ms)) return -2;
+    long n = len - off < (long)h->slot_bytes ? len - off : (long)h->slot_bytes;
+    uint8_t* s = slot_ptr(r, seq);
+    SlotHeader sh{(uint32_t)n, (uint32_t)(off + n < len)};
+    memcpy(s, &sh, sizeof(sh));
+    memcpy(s + sizeof(sh), src + off, (size_t)n);
+    h->write_seq.store(seq + 1, std::memory_order_release);
+    off += n;
+  } while (off < len);
+  return 0;
+}
+
+// Size of the next message for this reader (waits for its first chunk only); -2 on timeout.
+long ring_next_len(void* handle, int reader, long timeout_ms) {
+  Ring* r = (Ring*)handle;
+  if (!r || reader < 0 || reader >= (int)r->h->n_readers) return -1;
+  Header* h = r->h;
+  uint64_t seq = h->read_seq[reader].v.load(std::memory_order_relaxed);
+  long total = 0;
+  for (;;) {
+    if (!wait_until([&]() { return h->write_seq.load(std::memory_order_acquire) > seq; }, timeout_ms)) return -2;
+    SlotHeader sh;
+    memcpy(&sh, slot_ptr(r, seq), sizeof(sh));
+    total += sh.len;
+    if (!sh.more) return total;
+    // a multi-chunk message may be longer than the ring: the caller must drain as it goes
+    if (seq + 1 - h->read_seq[reader].v.load(std::memory_order_relaxed) >= h->n_slots) return -3;
+    ++seq;
+  }
+}
+
+// Reads one whole message into buf (capacity cap).  Returns its length, -1 bad argument, -2 timeout,
+// -4 buffer too small (the message is skipped).
+long ring_read(void* handle, int reader, void* buf, long cap, long timeout_ms) {
+  Ring* r = (Ring*)handle;
+  if (!r || reader < 0 || reader >= (int)r->h->n_readers) return -1;
+  Header* h = r->h;
+  uint8_t* dst = (uint8_t*)buf;
+  long off = 0;
+  bool overflow = false;
+  for (;;) {
+    uint64_t seq = h->read_seq[reader].v.load(std::memory_order_relaxed);
+    if (!wait_until([&]() { return h->write_seq.load(std::memory_order_acquire) > seq; }, off ? -1 : timeout_ms))
+      return -2;
+    uint8_t* s = slot_ptr(r, seq);
+    SlotHeader sh;
+    memcpy(&sh, s, sizeof(sh));
+    if (off + (long)sh.len <= cap) memcpy(dst + off, s + sizeof(sh), sh.len);
+    else overflow = true;
+    off += sh.len;
+    h->read_seq[reader].v.store(seq + 1, std::memory_order_release);
+    if (!sh.more) break;
+  }
+  return overflow ? -4 : off;
+}
+
+}  // extern "C"

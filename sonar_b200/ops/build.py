@@ -101,6 +101,25 @@ def build_extension(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+HOST_SRC_DIR = os.path.join(PKG_DIR, "csrc_host")
+HOST_LIB_PATH = os.path.join(PKG_DIR, "_host.so")
+
+
+def build_host_extension(force: bool = False) -> str:
+    """Host-only native helpers (shared-memory message ring): g++, no CUDA."""
+    srcs = sorted(os.path.join(HOST_SRC_DIR, f) for f in os.listdir(HOST_SRC_DIR) if f.endswith(".cpp"))
+    newest = max(os.path.getmtime(s) for s in srcs)
+    if not force and os.path.exists(HOST_LIB_PATH) and os.path.getmtime(HOST_LIB_PATH) >= newest:
+        return HOST_LIB_PATH
+    cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+    res = subprocess.run([cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", *srcs, "-o", HOST_LIB_PATH, "-lrt"],
+                         capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"host extension build failed:\n{res.stderr}")
+    return HOST_LIB_PATH
+
+
 if __name__ == "__main__":
+    print(build_host_extension(force="--force" in sys.argv))
     path = build_extension(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
     print(path)

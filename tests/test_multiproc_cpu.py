@@ -1,0 +1,96 @@
+"""Shared-memory ring and the multi-process executor (CPU workers over gloo)."""
+import multiprocessing as mp
+import os
+import signal
+import time
+
+import pytest
+import torch
+
+from sonar_b200.executor.shm_queue import MessageQueue, QueueTimeout
+from tp_common import make_checkpoint
+
+
+def _reader(handle, idx, out):
+    q = MessageQueue.attach(handle, idx)
+    got = []
+    while True:
+        m = q.get(timeout_s=10)
+        if m is None:
+            break
+        got.append(m if not isinstance(m, bytes) else len(m))
+    out.put((idx, got))
+
+
+def test_ring_broadcast_order_and_large_messages():
+    ctx = mp.get_context("spawn")
+    q = MessageQueue.create(2, slot_bytes=4096, n_slots=4)
+    out = ctx.Queue()
+    procs = [ctx.Process(target=_reader, args=(q.handle, i, out)) for i in range(2)]
+    for p in procs:
+        p.start()
+    msgs = [("m", i) for i in range(50)] + [b"x" * 10000]      # the last one spans three slots
+    for m in msgs:
+        q.put(m, timeout_s=10)
+    q.put(None)
+    res = dict(out.get(timeout=20) for _ in procs)
+    for p in procs:
+        p.join(10)
+    q.close()
+    for idx in (0, 1):
+        assert res[idx] == [("m", i) for i in range(50)] + [10000]
+
+
+def test_ring_timeouts():
+    q = MessageQueue.create(1, slot_bytes=256, n_slots=2)
+    r = MessageQueue.attach(q.handle, 0)
+    with pytest.raises(QueueTimeout):
+        r.get(timeout_s=0.05)
+    q.put("a")
+    q.put("b")
+    with pytest.raises(QueueTimeout):
+        q.put("c", timeout_s=0.05)          # ring full: the reader has not drained
+    assert r.get(0.5) == "a" and r.get(0.5) == "b"
+    q.put("c", timeout_s=0.5)
+    assert r.get(0.5) == "c"
+    r.close()
+    q.close()
+
+
+def test_multiproc_executor_tp2_matches_uniproc(tmp_path):
+    from sonar_b200 import LLM, SamplingParams
+    ckpt = make_checkpoint(str(tmp_path / "ckpt"), "tiny-llama", dtype=torch.float32)
+    sp = SamplingParams(temperature=0, max_tokens=5, ignore_eos=True, detokenize=False)
+    prompts = [{"prompt_token_ids": [(3 * i + j) % 900 + 4 for j in range(20 + 7 * i)]} for i in range(4)]
+    common = dict(dtype="float32", max_model_len=256, num_gpu_blocks_override=128, max_num_seqs=4,
+                  max_num_batched_tokens=64, device="cpu", skip_tokenizer_init=True)
+    one = LLM(ckpt, **common)
+    want = [o.outputs[0].token_ids for o in one.generate(prompts, sp)]
+    one.shutdown()
+    two = LLM(ckpt, tensor_parallel_size=2, distributed_executor_backend="mp", **common)
+    got = [o.outputs[0].token_ids for o in two.generate(prompts, sp)]
+    stats = two.collective_rpc("get_stats")
+    assert len(stats) == 2 and stats[0]["steps"] > 0
+    two.shutdown()
+    # fp32 summation order differs between TP1 and TP2: a random-init model may flip a late near-tie
+    assert [g[:2] for g in got] == [w[:2] for w in want]
+
+
+def test_worker_death_is_detected(tmp_path):
+    """A worker killed between steps: the host learns of it and the next call fails fast."""
+    from sonar_b200.config import EngineArgs
+    from sonar_b200.executor.multiproc import MultiprocExecutor, WorkerDeadError
+    cfg = EngineArgs(model="tiny-llama", dtype="float32", max_model_len=128, num_gpu_blocks_override=64,
+                     device="cpu", tensor_parallel_size=2, distributed_executor_backend="mp").create_engine_config()
+    ex = MultiprocExecutor(cfg)
+    fired = []
+    ex.register_failure_callback(lambda: fired.append(time.time()))
+    assert ex.collective_rpc("check_health") == [True, True]
+    os.kill(ex.procs[1].pid, signal.SIGKILL)
+    t0 = time.time()
+    while not ex.is_failed and time.time() - t0 < 10:
+        time.sleep(0.05)
+    assert ex.is_failed and fired
+    with pytest.raises(WorkerDeadError):
+        ex.collective_rpc("check_health")
+    ex.shutdown()

@@ -372,6 +372,8 @@ class EngineArgs:
             served_model_name=self.served_model_name)
         if self.hf_overrides:
             model.hf_config.update(self.hf_overrides)
+        model.hf_config["_expert_parallel"] = self.enable_expert_parallel
+        model.hf_config["_expert_placement"] = self.expert_placement
         cache = CacheConfig(
             block_size=self.block_size, gpu_memory_utilization=self.gpu_memory_utilization,
             num_gpu_blocks_override=self.num_gpu_blocks_override,

@@ -1,0 +1,248 @@
+// Block-scaled fp8 (e4m3) path: activation quantisation and the tcgen05 GEMM.
+//
+//  per_token_group_quant:  x [T, K] (bf16/f16) → xq [T, K] e4m3 + one fp32 scale per token per 128 input
+//                          channels, stored transposed ([K/128, T]) so the GEMM's row-owning threads read
+//                          them coalesced.  One warp per (token, group).
+//  gemm_fp8_block:         C[M, N] = Σ_kb (A_q[:, kb] · B_q[:, kb]^T) · sa[m, kb] · sb[n/128, kb], bf16 out.
+//                          Same persistent warp-specialised pipeline as the bf16 GEMM (TMA 128-byte-swizzled
+//                          tiles, tcgen05.mma kind::f8f6f4, K step 32), 128×128 tiles with BK = 128 so one
+//                          k-block is one scale group: the MMA warp writes every k-block's product into one
+//                          of two TMEM buffers (overwrite), the four epilogue warps pull it out with
+//                          tcgen05.ld, apply the two scales and accumulate in fp32 registers while the
+//                          tensor core works on the next k-block ("promotion" outside the tensor core,
+//                          because the scales are arbitrary fp32 values, not the UE8M0 block scales the
+//                          hardware's scaled MMA takes).
+//
+// Behavioural parity: reference csrc/libtorch_stable/quantization/w8a8/fp8/per_token_group_quant.cu:100 and the
+// 128×128 block-scaled GEMMs it dispatches to (c3x/scaled_mm_blockwise_sm100_fp8_dispatch.cuh, DeepGEMM).
+#include "tcgen05.cuh"
+
+namespace sonar {
+namespace {
+
+constexpr float FP8_MAX = 448.f;
+
+template <typename T>
+__global__ void __launch_bounds__(256) group_quant_kernel(const T* __restrict__ x, long x_stride,
+                                                          __nv_fp8_e4m3* __restrict__ q, float* __restrict__ scales_t,
+                                                          int T_rows, int K, long scale_ld) {
+  const long warp = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int groups = K >> 7;
+  if (warp >= (long)T_rows * groups) return;
+  const int row = (int)(warp / groups), g = (int)(warp % groups);
+  const T* src = x + (long)row * x_stride + g * 128 + lane * 4;
+  float v[4];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { v[i] = to_f<T>(src[i]); amax = fmaxf(amax, fabsf(v[i])); }
+  amax = fmaxf(warp_max(amax), 1e-10f);
+  const float scale = amax / FP8_MAX, inv = FP8_MAX / amax;
+  __nv_fp8_e4m3 o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o[i] = __nv_fp8_e4m3(fminf(fmaxf(v[i] * inv, -FP8_MAX), FP8_MAX));
+  *reinterpret_cast<uint32_t*>(q + (long)row * K + g * 128 + lane * 4) = *reinterpret_cast<uint32_t*>(o);
+  if (lane == 0) scales_t[(long)g * scale_ld + row] = scale;
+}
+
+// ------------------------------------------------------------------------------------------------
+constexpr int BM = 128, BN = 128, BK = 128;
+constexpr int STAGES = 6;
+constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int NUM_THREADS = 192;
+
+struct Fp8Params {
+  int M, N, K;
+  void* C; long ldc;
+  const float* sa_t; long sa_ld;    // [K/128, sa_ld] transposed activation scales
+  const float* sb; long sb_ld;      // [ceil(N/128), sb_ld] weight block scales
+  int* err;
+};
+
+template <typename OutT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const Fp8Params p) {
+  extern __shared__ uint8_t smem_dyn[];
+  const uint32_t smem0 = (tc::smem_u32(smem_dyn) + 1023u) & ~1023u;
+  uint8_t* smem_al = smem_dyn + (smem0 - tc::smem_u32(smem_dyn));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + STAGES * STAGE_BYTES);
+  const uint32_t bar0 = smem0 + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { tc::mbar_init(full_bar(s), 1); tc::mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { tc::mbar_init(tfull_bar(b), 1); tc::mbar_init(tempty_bar(b), 128); }
+    *abort_flag = 0;
+    tc::mbar_fence_init();
+  }
+  if (warp == 1) tc::tmem_alloc(tc::smem_u32(tmem_slot), 2 * BN);
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tc::tma_prefetch_desc(&tma_a);
+      tc::tma_prefetch_desc(&tma_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m_idx = tile % num_m, n_idx = tile / num_m;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!tc::mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.err, tc::SITE_EMPTY)) { ok = false; break; }
+          tc::mbar_expect_tx(full_bar(s), STAGE_BYTES);
+          const uint32_t a_dst = smem0 + s * STAGE_BYTES;
+          tc::tma_load_2d(a_dst, &tma_a, full_bar(s), kb * BK, m_idx * BM);
+          tc::tma_load_2d(a_dst + A_BYTES, &tma_b, full_bar(s), kb * BK, n_idx * BN);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc::make_idesc_e4m3(BM, BN);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int buf = it & 1;
+          const uint32_t bph = (it >> 1) & 1;
+          if (!tc::mbar_wait(tempty_bar(buf), bph ^ 1, abort_flag, p.err, tc::SITE_TMEM_EMPTY)) { ok = false; break; }
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!tc::mbar_wait(full_bar(s), ph, abort_flag, p.err, tc::SITE_FULL)) { ok = false; break; }
+          tc::fence_after_sync();
+          const uint32_t a_addr = smem0 + s * STAGE_BYTES;
+          const uint64_t adesc = tc::make_smem_desc_sw128(a_addr);
+          const uint64_t bdesc = tc::make_smem_desc_sw128(a_addr + A_BYTES);
+          const uint32_t d_tmem = tmem_base + buf * BN;
+#pragma unroll
+          for (int k = 0; k < BK / 32; ++k)     // 32 fp8 elements = 32 bytes per K step
+            tc::mma_f8(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, k > 0);
+          tc::mma_commit(empty_bar(s));
+          tc::mma_commit(tfull_bar(buf));
+        }
+      }
+    }
+  } else {
+    const int lane_grp = warp & 3;
+    const int trow = lane_grp * 32 + lane;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m_idx = tile % num_m, n_idx = tile / num_m;
+      const int row = m_idx * BM + trow;
+      const int row_c = row < p.M ? row : p.M - 1;
+      float acc[BN];
+#pragma unroll
+      for (int i = 0; i < BN; ++i) acc[i] = 0.f;
+      float sa_next = p.sa_t[row_c];
+      float sb_next = p.sb[(long)n_idx * p.sb_ld];
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const float scale = sa_next * sb_next;
+        if (kb + 1 < num_kb) {
+          sa_next = p.sa_t[(long)(kb + 1) * p.sa_ld + row_c];
+          sb_next = p.sb[(long)n_idx * p.sb_ld + kb + 1];
+        }
+        const int buf = it & 1;
+        const uint32_t bph = (it >> 1) & 1;
+        if (!tc::mbar_wait(tfull_bar(buf), bph, abort_flag, p.err, tc::SITE_TMEM_FULL)) { ok = false; break; }
+        tc::fence_after_sync();
+        const uint32_t t_row = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + buf * BN;
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tc::tmem_ld32(t_row + c * 32, v);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) acc[c * 32 + e] = fmaf(__uint_as_float(v[e]), scale, acc[c * 32 + e]);
+        }
+        tc::fence_before_sync();
+        tc::mbar_arrive(tempty_bar(buf));
+      }
+      if (!ok) break;
+      if (row < p.M) {
+        OutT* crow = reinterpret_cast<OutT*>(p.C) + (long)row * p.ldc + n_idx * BN;
+#pragma unroll
+        for (int g = 0; g < BN / 8; ++g) {
+          if (n_idx * BN + g * 8 + 8 <= p.N) *reinterpret_cast<uint4*>(crow + g * 8) = pack8<OutT>(acc + g * 8);
+        }
+      }
+    }
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+}  // namespace
+}  // namespace sonar
+
+using namespace sonar;
+
+// scales_t: [K/128, scale_ld] fp32, scale_ld >= T (transposed for coalesced reads in the GEMM)
+SONAR_API int sonar_group_quant_fp8(const void* x, long x_stride, void* q, float* scales_t, int T, int K, long scale_ld,
+                                    int dtype, cudaStream_t s) {
+  if (K % 128 || scale_ld < T) return SONAR_BAD_ARG;
+  if (T == 0) return SONAR_OK;
+  long warps = (long)T * (K / 128);
+  int blocks = (int)((warps + 7) / 8);
+  SONAR_DISPATCH_HALF(dtype, T_, {
+    group_quant_kernel<T_><<<blocks, 256, 0, s>>>((const T_*)x, x_stride, (__nv_fp8_e4m3*)q, scales_t, T, K, scale_ld);
+    return check_launch();
+  });
+}
+
+namespace sonar { int cached_tmap_public(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
+                                         uint32_t box_rows, int eb); int num_sms_public(); }
+
+SONAR_API int sonar_gemm_fp8_block(const void* Aq, const float* sa_t, long sa_ld, const void* Bq, const float* sb,
+                                   long sb_ld, void* C, int M, int N, int K, long lda, long ldb, long ldc,
+                                   int out_dtype, int* err, cudaStream_t s) {
+  if (M <= 0 || N <= 0 || K <= 0) return M == 0 ? SONAR_OK : SONAR_BAD_ARG;
+  if (K % 128 || lda % 16 || ldb % 16 || N % 8 || ldc % 8) return SONAR_BAD_ARG;
+  CUtensorMap ta, tb;
+  int rc = cached_tmap_public(&ta, Aq, M, K, lda, BM, 1);
+  if (rc != SONAR_OK) return rc;
+  rc = cached_tmap_public(&tb, Bq, N, K, ldb, BN, 1);
+  if (rc != SONAR_OK) return rc;
+  Fp8Params p{M, N, K, C, ldc, sa_t, sa_ld, sb, sb_ld, err};
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int sms = num_sms_public();
+  const int grid = tiles < sms ? tiles : sms;
+  static bool attr_done[2] = {false, false};
+  if (out_dtype == SONAR_BF16) {
+    auto kern = gemm_fp8_kernel<__nv_bfloat16>;
+    if (!attr_done[0]) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); attr_done[0] = true; }
+    kern<<<grid, NUM_THREADS, SMEM, s>>>(ta, tb, p);
+  } else if (out_dtype == SONAR_F16) {
+    auto kern = gemm_fp8_kernel<__half>;
+    if (!attr_done[1]) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); attr_done[1] = true; }
+    kern<<<grid, NUM_THREADS, SMEM, s>>>(ta, tb, p);
+  } else {
+    return SONAR_BAD_ARG;
+  }
+  return check_launch();
+}

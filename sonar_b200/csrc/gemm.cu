@@ -76,6 +76,10 @@ struct GemmParams {
   int ws_ctas;        // workspace capacity in CTAs
   int sk_tiles, sk_split; // split-K tail: the last sk_tiles tiles are each split over sk_split CTAs (0: none)
   int* ws_count;          // [sk_tiles] arrival counters of the split tiles, zero between launches
+  // grouped (mixture-of-experts) mode: A rows are expert-sorted and padded to 128-row blocks; block b uses
+  // expert block_expert[b]'s weights, i.e. B rows [e·N, (e+1)·N) of the stacked weight tensor
+  const int* block_expert;
+  const int* m_blocks_dev;  // device word: number of 128-row blocks actually present
   // gather wait
   const int* gather_flags;  // [num_m_blocks * tp] local flags, or null
   int tp, shard_rows, seq, m_rot;
@@ -147,8 +151,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   int* epi_ctr = reinterpret_cast<int*>(tmem_slot + 2);   // two warp-arrival counters of the epilogue
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
+  const int num_m = p.m_blocks_dev ? *p.m_blocks_dev : (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
+  const bool grouped = p.block_expert != nullptr;
   const int num_kb = (p.K + BK - 1) / BK;
   const int seq_now = p.seq + (p.seq_base ? *p.seq_base : 0);
 
@@ -212,7 +217,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       Seg sg;
       while (ok && next_seg(wave, g, sg)) {
         const int tile = sg.tile, kb0 = sg.kb0, kb1 = sg.kb1;
-        const int m_idx = (tile % num_m + p.m_rot) % num_m, n_idx = tile / num_m;
+        const int m_idx = grouped ? tile / num_n : (tile % num_m + p.m_rot) % num_m;
+        const int n_idx = grouped ? tile % num_n : tile / num_m;
         if (p.gather_flags != nullptr) {
           // bounded wait until every source rank of this row block has published this launch's sequence number
           const int r_lo = m_idx * BM, r_hi = min(p.M, r_lo + BM) - 1;
@@ -242,6 +248,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           // the acquire loads order the peers' row stores before the TMA (async proxy) reads below
           asm volatile("fence.proxy.async;" ::: "memory");
         }
+        const int b_row0 = grouped ? p.block_expert[m_idx] * p.N : 0;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1;
@@ -249,7 +256,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           tc::mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
           const uint32_t a_dst = smem0 + s * C::STAGE_BYTES;
           tc::tma_load_2d(a_dst, &tma_a, full_bar(s), kb * BK, m_idx * BM);
-          tc::tma_load_2d(a_dst + C::A_BYTES, &tma_b, full_bar(s), kb * BK, n_idx * BN);
+          tc::tma_load_2d(a_dst + C::A_BYTES, &tma_b, full_bar(s), kb * BK, b_row0 + n_idx * BN);
         }
       }
     }
@@ -298,7 +305,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     Seg sg;
     for (; ok && next_seg(wave, g, sg); ++seg) {
       const int tile = sg.tile;
-      const int m_idx = (tile % num_m + p.m_rot) % num_m, n_idx = tile / num_m;
+      const int m_idx = grouped ? tile / num_n : (tile % num_m + p.m_rot) % num_m;
+      const int n_idx = grouped ? tile % num_n : tile / num_m;
       const int buf = seg & 1;
       const uint32_t bph = (seg >> 1) & 1;
       if (!tc::mbar_wait(tfull_bar(buf), bph, abort_flag, p.err, tc::SITE_TMEM_FULL)) break;
@@ -575,16 +583,18 @@ int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p
     }
   }
   if (q.sk_tiles == 0) q.ws = nullptr;
+  if (q.block_expert != nullptr) launch_grid = grid;   // tile count is only a bound here: the kernel reads the real one
   kern<<<launch_grid, NUM_THREADS, C::SMEM, s>>>(ta, tb, q);
   return check_launch();
 }
 
 template <typename OutT, int AB_FMT>
-int launch_bn(int bn, const void* A, const void* B, const GemmParams& p, long lda, long ldb, cudaStream_t s) {
+int launch_bn(int bn, const void* A, const void* B, const GemmParams& p, long lda, long ldb, cudaStream_t s,
+              long b_rows = 0) {
   CUtensorMap ta, tb;
   int rc = cached_tmap(&ta, A, p.M, p.K, lda, BM, 2);
   if (rc != SONAR_OK) return rc;
-  rc = cached_tmap(&tb, B, p.N, p.K, ldb, bn, 2);
+  rc = cached_tmap(&tb, B, b_rows ? b_rows : p.N, p.K, ldb, bn, 2);
   if (rc != SONAR_OK) return rc;
   if (bn == 256) return launch_cfg<256, OutT, AB_FMT>(ta, tb, p, s);
   if (bn == 128) return launch_cfg<128, OutT, AB_FMT>(ta, tb, p, s);
@@ -592,6 +602,13 @@ int launch_bn(int bn, const void* A, const void* B, const GemmParams& p, long ld
 }
 
 }  // namespace
+
+// shared with the other GEMM translation units
+int cached_tmap_public(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                       int eb) {
+  return cached_tmap(out, ptr, rows, cols, ld, box_rows, eb);
+}
+int num_sms_public() { return num_sms(); }
 }  // namespace sonar
 
 using namespace sonar;
@@ -642,6 +659,23 @@ SONAR_API int sonar_gemm_tp(const void* A, const void* B, void* C, int M, int N,
   p.ws = ws; p.ws_flags = ws_flags; p.ws_ctas = ws_ctas;
   const int bn = force_bn ? force_bn : pick_bn(M, N, ws != nullptr);
   return launch_bn<__nv_bfloat16, 1>(bn, A, B, p, lda, ldb, s);
+}
+
+// Grouped GEMM for mixture-of-experts: C[r, :] = A[r, :] · W[e(r)]^T with rows expert-sorted and padded to
+// 128-row blocks (sonar_moe_align).  W is the stacked weight tensor [n_experts * N, K]; block_expert[b] is
+// the expert of row block b; m_blocks_dev holds the number of blocks present; max_rows bounds the grid.
+SONAR_API int sonar_gemm_grouped(const void* A, const void* W, void* C, int max_rows, int N, int K, int n_experts,
+                                 long lda, long ldw, long ldc, const int* block_expert, const int* m_blocks_dev,
+                                 int* err, cudaStream_t s) {
+  if (max_rows <= 0 || N <= 0 || K <= 0) return max_rows == 0 ? SONAR_OK : SONAR_BAD_ARG;
+  if (K % 8 || lda % 8 || ldw % 8 || N % 8 || ldc % 8 || max_rows % BM) return SONAR_BAD_ARG;
+  int bn = N % 256 == 0 ? 256 : (N % 128 == 0 ? 128 : (N % 64 == 0 ? 64 : 0));
+  if (bn == 0) return SONAR_BAD_ARG;   // tiles must not straddle experts
+  GemmParams p{};
+  p.M = max_rows; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.err = err;
+  p.tp = 1; p.shard_rows = max_rows;
+  p.block_expert = block_expert; p.m_blocks_dev = m_blocks_dev;
+  return launch_bn<__nv_bfloat16, 1>(bn, A, W, p, lda, ldw, s, (long)n_experts * N);
 }
 
 SONAR_API int sonar_gemm_pick_bn(int M, int N, int stream_k) { return pick_bn(M, N, stream_k != 0); }

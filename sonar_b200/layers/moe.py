@@ -1,0 +1,100 @@
+"""Mixture-of-experts layer: router + routed experts, tensor- or expert-parallel.
+
+Weights are stacked per rank: ``w13 [E_local, 2·I_local, H]`` (gate rows then up
+rows) and ``w2 [E_local, H, I_local]``.
+
+* tensor parallel (default): every rank holds all experts and ``I/tp`` of each
+  expert's intermediate dim;
+* expert parallel (``enable_expert_parallel``): experts are partitioned over
+  the group (``linear`` = contiguous ranges, ``round_robin`` = interleaved),
+  each with its full intermediate dim; tokens routed elsewhere contribute zero
+  here.
+
+Either way a rank produces a partial sum over ``[T, H]`` that the caller
+reduces over the group — with the fused tensor-parallel layout the weighted
+top-k combine kernel stores each token's row straight into its owner's
+partial-sum buffer over NVLink (combine and return trip in one kernel), and
+the all-gathered activations it starts from are what the preceding norm kernel
+pushed (the dispatch).
+
+Parity: ``aphrodite/model_executor/layers/fused_moe/layer.py:94``, routers
+``router/fused_topk_router.py:97`` / ``grouped_topk_router.py:28``, the default
+all-gather / reduce-scatter dispatch ``device_communicators/all2all.py:44-148``,
+expert placement ``config/parallel.py:35,177``.
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from sonar_b200 import ops
+from sonar_b200.parallel import state
+
+
+class FusedMoE(nn.Module):
+    def __init__(self, num_experts: int, top_k: int, hidden: int, inter: int, dtype, device, renormalize: bool = True,
+                 scoring: str = "softmax", n_group: int = 1, topk_group: int = 1, routed_scaling: float = 1.0,
+                 use_bias: bool = False, expert_parallel: bool = False, placement: str = "linear",
+                 prefix: str = "") -> None:
+        super().__init__()
+        self.num_experts, self.top_k, self.hidden, self.inter = num_experts, top_k, hidden, inter
+        self.renormalize, self.scoring = renormalize, scoring
+        self.n_group, self.topk_group, self.routed_scaling = n_group, topk_group, routed_scaling
+        tp, rank = state.tp_world_size(), state.tp_rank()
+        self.tp, self.rank = tp, rank
+        self.expert_parallel = expert_parallel and tp > 1
+        if self.expert_parallel:
+            if num_experts % tp:
+                raise ValueError(f"{num_experts} experts cannot be split over {tp} ranks")
+            n_local = num_experts // tp
+            if placement == "round_robin":
+                owned = list(range(rank, num_experts, tp))
+            else:
+                owned = list(range(rank * n_local, (rank + 1) * n_local))
+            emap = torch.full((num_experts,), -1, dtype=torch.int32)
+            emap[owned] = torch.arange(n_local, dtype=torch.int32)
+            self.register_buffer("expert_map", emap.to(device), persistent=False)
+            self.local_of = {g: l for l, g in enumerate(owned)}
+            self.inter_local = inter
+        else:
+            if inter % tp:
+                raise ValueError(f"expert intermediate size {inter} not divisible by tp={tp}")
+            n_local = num_experts
+            self.expert_map = None
+            self.local_of = {g: g for g in range(num_experts)}
+            self.inter_local = inter // tp
+        self.n_local = n_local
+        self.w13 = nn.Parameter(torch.empty(n_local, 2 * self.inter_local, hidden, dtype=dtype, device=device),
+                                requires_grad=False)
+        self.w2 = nn.Parameter(torch.empty(n_local, hidden, self.inter_local, dtype=dtype, device=device),
+                               requires_grad=False)
+        self.e_bias = (nn.Parameter(torch.zeros(num_experts, dtype=torch.float32, device=device), requires_grad=False)
+                       if use_bias else None)
+        self.prefix = prefix
+
+    # weight loading: (expert id, "gate" | "up" | "down") -------------------------------
+    def load_expert_weight(self, expert: int, which: str, tensor: torch.Tensor) -> bool:
+        local = self.local_of.get(expert)
+        if local is None:
+            return True   # another rank's expert
+        il = self.inter_local
+        lo = 0 if self.expert_parallel else self.rank * il
+        if which == "gate":
+            self.w13.data[local, :il].copy_(tensor[lo:lo + il])
+        elif which == "up":
+            self.w13.data[local, il:].copy_(tensor[lo:lo + il])
+        else:
+            self.w2.data[local].copy_(tensor[:, lo:lo + il])
+        return True
+
+    def route(self, router_logits: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        if self.n_group > 1 or self.scoring == "sigmoid" or self.e_bias is not None:
+            return ops.grouped_topk(router_logits, self.e_bias, self.top_k, self.n_group, self.topk_group,
+                                    self.renormalize, self.routed_scaling, self.scoring)
+        w, ids = ops.topk_softmax(router_logits, self.top_k, self.renormalize)
+        return (w * self.routed_scaling if self.routed_scaling != 1.0 else w), ids
+
+    def forward(self, x: torch.Tensor, router_logits: torch.Tensor, combine_to=None):
+        """Partial sum ``[T, H]`` of this rank's experts (or None when pushed to ``combine_to``)."""
+        w, ids = self.route(router_logits)
+        return ops.fused_experts(x, self.w13, self.w2, w, ids, self.expert_map, combine_to)

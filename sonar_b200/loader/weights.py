@@ -142,9 +142,11 @@ def initialize_dummy_weights(model: nn.Module, seed: int, std: float = 0.02) -> 
         if id(p) in done:
             continue
         done.add(id(p))
-        if "norm" in name and p.dim() == 1:
+        if name.endswith("bias"):
+            p.data.zero_()
+        elif "norm" in name and p.dim() == 1:
             p.data.fill_(1.0)
-        elif name.endswith("bias") or p.dim() == 1:
+        elif p.dim() == 1:
             p.data.zero_()
         elif p.dtype in (torch.float32, torch.float16, torch.bfloat16):
             gen = torch.Generator(device=p.device).manual_seed(_name_seed(name, seed))

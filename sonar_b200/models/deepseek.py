@@ -1,0 +1,317 @@
+"""DeepSeek V2 / V3 / V3.2: multi-head latent attention (MLA), DeepSeek sparse attention (lightning
+indexer + top-k key selection, V3.2) and a grouped-routing mixture of experts with shared experts.
+
+MLA runs in the absorbed form for prefill and decode alike: per head,
+``q_nope · W_UK`` is taken into the latent space, attention is an MQA over the
+paged latent cache (one ``kv_lora_rank + rope`` row per token, shared by all
+heads), and the latent output goes through ``W_UV`` and ``o_proj``.  With the
+sparse indexer every query token attends only to its ``index_topk`` best keys,
+scored by ``Σ_h w_h · relu(q_idx_h · k_idx)`` over a separate low-dimensional
+index key that is cached next to the latent row.
+
+Tensor parallelism splits the heads (``q_b_proj``, ``kv_b_proj`` column-parallel,
+``o_proj`` row-parallel); the latent projections, the indexer and the latent
+cache are replicated.
+
+Parity: ``aphrodite/model_executor/models/deepseek_v2.py``, ``layers/attention/mla_attention.py:1-188``
+(algorithm), ``layers/sparse_attn_indexer.py:831``, ``layers/fused_moe/router/grouped_topk_router.py:28``.
+"""
+from __future__ import annotations
+
+import re
+
+import torch
+from torch import nn
+
+from sonar_b200 import ops
+from sonar_b200.config import ModelConfig
+from sonar_b200.core.kv_cache_manager import KVCacheSpec
+from sonar_b200.layers.attention import AttentionMetadata, get_cos_sin_cache
+from sonar_b200.layers.embedding import ParallelLMHead, VocabParallelEmbedding
+from sonar_b200.layers.linear import ColumnParallelLinear, ReplicatedLinear, RowParallelLinear
+from sonar_b200.layers.moe import FusedMoE
+from sonar_b200.layers.norm import RMSNorm
+from sonar_b200.models.llama import LlamaMLP, pp_layer_range
+from sonar_b200.ops import torch_ref
+from sonar_b200.parallel import state
+from sonar_b200.parallel.tp_ops import get_tp_context
+
+
+def _rope_interleaved(x: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor) -> torch.Tensor:
+    """GPT-J style rotation of the last dim of ``x [T, ..., rot]``."""
+    rot = cos_sin.shape[-1]
+    cs = cos_sin[positions.long()]
+    shape = (x.shape[0],) + (1,) * (x.dim() - 2) + (rot // 2,)
+    cos, sin = cs[:, : rot // 2].reshape(shape), cs[:, rot // 2:].reshape(shape)
+    xf = x.float()
+    x1, x2 = xf[..., 0::2], xf[..., 1::2]
+    return torch.stack([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).flatten(-2).to(x.dtype)
+
+
+class MLAAttention(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> None:
+        super().__init__()
+        g = cfg.get
+        self.hidden = cfg.hidden_size
+        self.total_heads = cfg.num_attention_heads
+        tp = state.tp_world_size()
+        self.num_heads = self.total_heads // tp
+        self.num_kv_heads = 1
+        self.q_lora, self.kv_lora = g("q_lora_rank"), int(g("kv_lora_rank"))
+        self.nope, self.rope_dim, self.v_dim = int(g("qk_nope_head_dim")), int(g("qk_rope_head_dim")), int(g("v_head_dim"))
+        self.qk_dim = self.nope + self.rope_dim
+        dt, q = cfg.dtype, cfg.quantization
+        eps = g("rms_norm_eps", 1e-6)
+        if self.q_lora:
+            self.q_a_proj = ReplicatedLinear(self.hidden, self.q_lora, False, dt, device, q, f"{prefix}.q_a_proj")
+            self.q_a_layernorm = RMSNorm(self.q_lora, eps, dt, device)
+            self.q_b_proj = ColumnParallelLinear(self.q_lora, [self.total_heads * self.qk_dim], False, dt, device, q,
+                                                 f"{prefix}.q_b_proj")
+        else:
+            self.q_proj = ColumnParallelLinear(self.hidden, [self.total_heads * self.qk_dim], False, dt, device, q,
+                                               f"{prefix}.q_proj")
+        self.kv_a_proj_with_mqa = ReplicatedLinear(self.hidden, self.kv_lora + self.rope_dim, False, dt, device, q,
+                                                   f"{prefix}.kv_a_proj_with_mqa")
+        self.kv_a_layernorm = RMSNorm(self.kv_lora, eps, dt, device)
+        # kept unquantised: it is folded into per-head W_UK / W_UV matrices after loading
+        self.kv_b_proj = ColumnParallelLinear(self.kv_lora, [self.total_heads * (self.nope + self.v_dim)], False, dt,
+                                              device, None, f"{prefix}.kv_b_proj")
+        self.o_proj = RowParallelLinear(self.total_heads * self.v_dim, self.hidden, False, dt, device, q,
+                                        f"{prefix}.o_proj")
+        scaling = g("rope_scaling")
+        self.cos_sin = get_cos_sin_cache(self.rope_dim, cfg.max_model_len, float(g("rope_theta", 1e4)), scaling, device)
+        self.scale = self.qk_dim ** -0.5
+        if scaling and scaling.get("mscale_all_dim"):
+            import math
+            f = scaling["factor"]
+            m = 0.1 * scaling["mscale_all_dim"] * math.log(f) + 1.0 if f > 1 else 1.0
+            self.scale *= m * m
+        # ---- sparse-attention indexer (V3.2)
+        self.index_topk = int(g("index_topk", 0) or 0)
+        self.idx_dim = int(g("index_head_dim", 0) or 0) if self.index_topk else 0
+        if self.index_topk:
+            self.idx_heads = int(g("index_n_heads"))
+            src = self.q_lora or self.hidden
+            self.indexer_wq_b = ReplicatedLinear(src, self.idx_heads * self.idx_dim, False, dt, device, None,
+                                                 f"{prefix}.indexer.wq_b")
+            self.indexer_wk = ReplicatedLinear(self.hidden, self.idx_dim, False, dt, device, None, f"{prefix}.indexer.wk")
+            self.indexer_k_norm_weight = nn.Parameter(torch.ones(self.idx_dim, dtype=dt, device=device), requires_grad=False)
+            self.indexer_k_norm_bias = nn.Parameter(torch.zeros(self.idx_dim, dtype=dt, device=device), requires_grad=False)
+            self.indexer_weights_proj = ReplicatedLinear(self.hidden, self.idx_heads, False, dt, device, None,
+                                                         f"{prefix}.indexer.weights_proj")
+        self.row = self.kv_lora + self.rope_dim + self.idx_dim
+        self.kv_cache: torch.Tensor | None = None
+        self.sliding_window = None
+        self.w_uk = self.w_uv = None
+
+    def bind_kv_cache(self, cache: torch.Tensor) -> None:
+        self.kv_cache = cache
+
+    def process_after_load(self) -> None:
+        w = self.kv_b_proj.weight.data.view(self.num_heads, self.nope + self.v_dim, self.kv_lora)
+        self.w_uk = w[:, : self.nope].contiguous()                     # [H, nope, R]
+        self.w_uv = w[:, self.nope:].transpose(1, 2).contiguous()      # [H, R, v]
+
+    # ------------------------------------------------------------------
+    def _index_select(self, x, q_src, kidx_all, meta: AttentionMetadata):
+        """Per query token the positions of its ``index_topk`` best keys (−1 padded), or None when every
+        sequence of the step is short enough to attend densely."""
+        if max(meta.seq_lens_cpu, default=0) <= self.index_topk:
+            return None
+        t = x.shape[0]
+        qi = self.indexer_wq_b(q_src).view(t, self.idx_heads, self.idx_dim)
+        rd = self.rope_dim
+        qi = torch.cat([_rope_interleaved(qi[..., :rd], meta.positions, self.cos_sin), qi[..., rd:]], dim=-1)
+        wts = self.indexer_weights_proj(x).float() * (self.idx_heads ** -0.5) * (self.idx_dim ** -0.5)
+        bs = self.kv_cache.shape[1]
+        out = torch.full((t, self.index_topk), -1, dtype=torch.int32, device=x.device)
+        qsl, sl = meta.query_start_loc.tolist(), meta.seq_lens_cpu
+        for i in range(meta.num_seqs):
+            s, e, ctx = qsl[i], qsl[i + 1], int(sl[i])
+            if e <= s:
+                continue
+            nb = -(-ctx // bs)
+            rows = self.kv_cache[meta.block_tables[i, :nb].long()].reshape(nb * bs, -1)[:ctx]
+            kk = rows[:, self.kv_lora + rd:].float()                    # [ctx, idx_dim]
+            sc = torch.einsum("qhd,kd->qhk", qi[s:e].float(), kk).relu_()
+            sc = (sc * wts[s:e, :, None]).sum(1)                         # [q, ctx]
+            qpos = torch.arange(ctx - (e - s), ctx, device=x.device)[:, None]
+            sc = sc.masked_fill(torch.arange(ctx, device=x.device)[None, :] > qpos, float("-inf"))
+            k = min(self.index_topk, ctx)
+            top = sc.topk(k, dim=-1)
+            idx = torch.where(torch.isinf(top.values), torch.full_like(top.indices, -1), top.indices)
+            out[s:e, :k] = idx.int()
+        return out
+
+    def forward(self, x, meta: AttentionMetadata):
+        tp = get_tp_context()
+        x = tp.materialize(x)
+        t = meta.positions.shape[0]
+        xt = x[:t]
+        if self.q_lora:
+            q_src = self.q_a_layernorm(self.q_a_proj(xt))
+            q = self.q_b_proj(q_src)
+        else:
+            q_src = xt
+            q = self.q_proj(xt)
+        q = q.view(t, self.num_heads, self.qk_dim)
+        q_nope, q_pe = q[..., : self.nope], q[..., self.nope:]
+        kv = self.kv_a_proj_with_mqa(xt)
+        kv_c = self.kv_a_layernorm(kv[:, : self.kv_lora].contiguous())
+        k_pe = _rope_interleaved(kv[:, self.kv_lora:].contiguous(), meta.positions, self.cos_sin)
+        q_pe = _rope_interleaved(q_pe, meta.positions, self.cos_sin)
+        row = [kv_c, k_pe]
+        if self.index_topk:
+            ki = torch.nn.functional.layer_norm(self.indexer_wk(xt).float(), (self.idx_dim,),
+                                                self.indexer_k_norm_weight.float(), self.indexer_k_norm_bias.float(),
+                                                1e-6).to(x.dtype)
+            ki = torch.cat([_rope_interleaved(ki[:, : self.rope_dim], meta.positions, self.cos_sin),
+                            ki[:, self.rope_dim:]], dim=-1)
+            row.append(ki)
+        ops.mla_cache_write(torch.cat(row[:1], dim=-1), torch.cat(row[1:], dim=-1), self.kv_cache, meta.slot_mapping)
+        topk = self._index_select(xt, q_src, None, meta) if self.index_topk else None
+        q_lat = torch.einsum("thn,hnr->thr", q_nope, self.w_uk)
+        o_lat = ops.mla_paged_attention(q_lat, q_pe, self.kv_cache, meta, self.scale, self.kv_lora, topk,
+                                        rope_dim=self.rope_dim)
+        o = torch.einsum("thr,hrv->thv", o_lat, self.w_uv).reshape(t, self.num_heads * self.v_dim)
+        if x.shape[0] != t:
+            o = torch.cat([o, o.new_zeros(x.shape[0] - t, o.shape[1])], dim=0)
+        return tp.row_linear(o, self.o_proj)
+
+
+class DeepseekMoE(nn.Module):
+    def __init__(self, cfg: ModelConfig, device, prefix: str) -> None:
+        super().__init__()
+        g = cfg.get
+        n_exp, inter = int(g("n_routed_experts")), int(g("moe_intermediate_size"))
+        self.gate = ReplicatedLinear(cfg.hidden_size, n_exp, False, cfg.dtype, device, None, f"{prefix}.gate")
+        self.experts = FusedMoE(
+            n_exp, int(g("num_experts_per_tok")), cfg.hidden_size, inter, cfg.dtype, device,
+            renormalize=bool(g("norm_topk_prob", True)), scoring=g("scoring_func", "softmax"),
+            n_group=int(g("n_group", 1) or 1), topk_group=int(g("topk_group", 1) or 1),
+            routed_scaling=float(g("routed_scaling_factor", 1.0)), use_bias=g("topk_method", "noaux_tc") == "noaux_tc",
+            expert_parallel=bool(g("_expert_parallel", False)), placement=g("_expert_placement", "linear"),
+            prefix=f"{prefix}.experts")
+        n_shared = int(g("n_shared_experts", 0) or 0)
+        self.shared_experts = (LlamaMLP(cfg.hidden_size, inter * n_shared, cfg.dtype, device, cfg.quantization,
+                                        f"{prefix}.shared_experts") if n_shared else None)
+
+    def forward(self, x):
+        tp = get_tp_context()
+        xf = tp.materialize(x)
+        logits = self.gate(xf)
+        y = self.experts(xf, logits.float(), None)
+        if self.shared_experts is not None:
+            se = self.shared_experts
+            y = y + se.down_proj(ops.silu_and_mul(se.gate_up_proj(xf)))
+        return tp.finish_partial(y, None)
+
+
+class DeepseekDecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> None:
+        super().__init__()
+        eps = cfg.get("rms_norm_eps", 1e-6)
+        self.self_attn = MLAAttention(cfg, layer_idx, device, f"{prefix}.self_attn")
+        dense = layer_idx < int(cfg.get("first_k_dense_replace", 0)) or not cfg.get("n_routed_experts")
+        self.mlp = (LlamaMLP(cfg.hidden_size, int(cfg.get("intermediate_size")), cfg.dtype, device, cfg.quantization,
+                             f"{prefix}.mlp") if dense else DeepseekMoE(cfg, device, f"{prefix}.mlp"))
+        self.input_layernorm = RMSNorm(cfg.hidden_size, eps, cfg.dtype, device)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, eps, cfg.dtype, device)
+
+    def forward(self, h, residual, meta):
+        tp = get_tp_context()
+        x, residual = tp.add_norm(h, residual, self.input_layernorm.weight, self.input_layernorm.eps)
+        h = self.self_attn(x, meta)
+        x, residual = tp.add_norm(h, residual, self.post_attention_layernorm.weight, self.post_attention_layernorm.eps)
+        return self.mlp(x), residual
+
+
+class DeepseekModel(nn.Module):
+    def __init__(self, cfg: ModelConfig, device) -> None:
+        super().__init__()
+        self.start_layer, self.end_layer = pp_layer_range(cfg.num_layers)
+        pp = state.get_pp_group() if state.model_parallel_is_initialized() else None
+        self.is_first = pp is None or pp.rank_in_group == 0
+        self.is_last = pp is None or pp.rank_in_group == pp.world_size - 1
+        self.replicated_embed = get_tp_context().scattered
+        if self.is_first:
+            self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device,
+                                                       "model.embed_tokens", replicated=self.replicated_embed)
+        self.layers = nn.ModuleDict({str(i): DeepseekDecoderLayer(cfg, i, device, f"model.layers.{i}")
+                                     for i in range(self.start_layer, self.end_layer)})
+        if self.is_last:
+            self.norm = RMSNorm(cfg.hidden_size, cfg.get("rms_norm_eps", 1e-6), cfg.dtype, device)
+
+    def forward(self, input_ids, meta, intermediate=None):
+        tp = get_tp_context()
+        if self.is_first:
+            h = (self.embed_tokens(tp.shard_token_ids(input_ids)) if tp.scattered
+                 else tp.embed_reduce(self.embed_tokens(input_ids)))
+            residual = None
+        else:
+            h, residual = intermediate
+        for layer in self.layers.values():
+            h, residual = layer(h, residual, meta)
+        if not self.is_last:
+            return h, residual
+        x, _ = tp.add_norm(h, residual, self.norm.weight, self.norm.eps)
+        return x
+
+
+_EXPERT_RE = re.compile(r"(.*\.mlp)\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.weight$")
+
+
+class DeepseekForCausalLM(nn.Module):
+    uses_mla = True
+    stacked_params = [(".gate_proj.", ".gate_up_proj.", 0), (".up_proj.", ".gate_up_proj.", 1)]
+
+    def __init__(self, cfg: ModelConfig, device=None) -> None:
+        super().__init__()
+        self.cfg = cfg
+        self.model = DeepseekModel(cfg, device)
+        if self.model.is_last:
+            self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device, "lm_head")
+
+    def forward(self, input_ids, meta, intermediate=None):
+        return self.model(input_ids, meta, intermediate)
+
+    def compute_logits(self, hidden):
+        return self.lm_head.logits(hidden)
+
+    def attention_layers(self):
+        return [layer.self_attn for layer in self.model.layers.values()]
+
+    def kv_cache_spec(self, block_size: int, dtype_bytes: int) -> KVCacheSpec:
+        a = self.attention_layers()[0]
+        return KVCacheSpec(block_size, 1, a.row, dtype_bytes, "mla", None, a.row)
+
+    def load_special_weight(self, name: str, tensor: torch.Tensor) -> bool:
+        m = _EXPERT_RE.match(name)
+        if m is not None and ".shared_experts." not in name:
+            try:
+                block = self.get_submodule(m.group(1))
+            except AttributeError:
+                return True
+            which = {"gate_proj": "gate", "up_proj": "up", "down_proj": "down"}[m.group(3)]
+            return block.experts.load_expert_weight(int(m.group(2)), which, tensor)
+        if name.endswith(".mlp.gate.e_score_correction_bias"):
+            try:
+                block = self.get_submodule(name.rsplit(".gate.", 1)[0])
+            except AttributeError:
+                return True
+            block.experts.e_bias.data.copy_(tensor.float())
+            return True
+        return False
+
+    def map_checkpoint_name(self, name: str):
+        if "rotary_emb.inv_freq" in name or ".mtp." in name:
+            return None
+        name = name.replace(".indexer.wq_b.", ".indexer_wq_b.").replace(".indexer.wk.", ".indexer_wk.")
+        name = name.replace(".indexer.weights_proj.", ".indexer_weights_proj.")
+        name = name.replace(".indexer.k_norm.weight", ".indexer_k_norm_weight").replace(".indexer.k_norm.bias", ".indexer_k_norm_bias")
+        shard = None
+        for frag, merged, sid in self.stacked_params:
+            if frag in name:
+                name, shard = name.replace(frag, merged), sid
+                break
+        return name, shard

@@ -1,0 +1,76 @@
+"""Sparse decoders: Qwen3-MoE (softmax top-k routing, per-head q/k norm) and Mixtral.
+
+Attention is the Llama-family block; the MLP of (most) layers is a routed
+expert mixture.  Parity: ``aphrodite/model_executor/models/qwen3_moe.py:129-237``,
+``models/mixtral.py``.
+"""
+from __future__ import annotations
+
+import re
+
+import torch
+from torch import nn
+
+from sonar_b200.config import ModelConfig
+from sonar_b200.layers.linear import ReplicatedLinear
+from sonar_b200.layers.moe import FusedMoE
+from sonar_b200.models.llama import LlamaDecoderLayer, LlamaForCausalLM, LlamaMLP, LlamaModel
+from sonar_b200.parallel.tp_ops import get_tp_context
+
+
+class SparseMoeBlock(nn.Module):
+    def __init__(self, cfg: ModelConfig, device, prefix: str, expert_parallel: bool, placement: str) -> None:
+        super().__init__()
+        n_exp = int(cfg.get("num_experts", cfg.get("num_local_experts", 8)))
+        inter = int(cfg.get("moe_intermediate_size", cfg.get("intermediate_size")))
+        self.gate = ReplicatedLinear(cfg.hidden_size, n_exp, False, cfg.dtype, device, None, f"{prefix}.gate")
+        self.experts = FusedMoE(n_exp, int(cfg.get("num_experts_per_tok", 2)), cfg.hidden_size, inter, cfg.dtype,
+                                device, renormalize=bool(cfg.get("norm_topk_prob", True)),
+                                expert_parallel=expert_parallel, placement=placement, prefix=f"{prefix}.experts")
+
+    def forward(self, x):
+        tp = get_tp_context()
+        xf = tp.materialize(x)                      # all tokens on every rank ("dispatch" already happened)
+        logits = self.gate(xf)
+        target = tp.moe_push_target()
+        y = self.experts(xf, logits, target)
+        return tp.finish_partial(y, target)
+
+
+class Qwen3MoeDecoderLayer(LlamaDecoderLayer):
+    def _make_mlp(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> nn.Module:
+        only = cfg.get("mlp_only_layers", []) or []
+        step = int(cfg.get("decoder_sparse_step", 1))
+        if layer_idx in only or (layer_idx + 1) % step != 0:
+            return LlamaMLP(cfg.hidden_size, int(cfg.get("intermediate_size")), cfg.dtype, device, cfg.quantization, prefix)
+        return SparseMoeBlock(cfg, device, prefix, bool(cfg.get("_expert_parallel", False)),
+                              cfg.get("_expert_placement", "linear"))
+
+
+class Qwen3MoeModel(LlamaModel):
+    layer_cls = Qwen3MoeDecoderLayer
+
+
+_EXPERT_RE = re.compile(r"(.*\.mlp)\.experts\.(\d+)\.(gate_proj|up_proj|down_proj|w1|w2|w3)\.weight$")
+_WHICH = {"gate_proj": "gate", "up_proj": "up", "down_proj": "down", "w1": "gate", "w3": "up", "w2": "down"}
+
+
+class Qwen3MoeForCausalLM(LlamaForCausalLM):
+    model_cls = Qwen3MoeModel
+
+    def load_special_weight(self, name: str, tensor: torch.Tensor) -> bool:
+        name = name.replace(".block_sparse_moe.", ".mlp.")
+        m = _EXPERT_RE.match(name)
+        if m is None:
+            return False
+        try:
+            block = self.get_submodule(m.group(1))
+        except AttributeError:
+            return True   # a layer of another pipeline stage
+        return block.experts.load_expert_weight(int(m.group(2)), _WHICH[m.group(3)], tensor)
+
+    def map_checkpoint_name(self, name: str):
+        return super().map_checkpoint_name(name.replace(".block_sparse_moe.", ".mlp."))
+
+
+MixtralForCausalLM = Qwen3MoeForCausalLM

@@ -147,9 +147,10 @@ def grouped_topk(logits, bias, k, n_group, topk_group, renormalize, scale, scori
     return ref.grouped_topk(logits, bias, k, n_group, topk_group, renormalize, scale, scoring)
 
 
-def fused_experts(x, w13, w2, topk_w, topk_ids, expert_map=None):
+def fused_experts(x, w13, w2, topk_w, topk_ids, expert_map=None, combine_to=None):
     if _use_cuda(x):
-        return cuda_ops().fused_experts(x, w13, w2, topk_w, topk_ids, expert_map)
+        return cuda_ops().fused_experts(x, w13, w2, topk_w, topk_ids, expert_map, combine_to)
+    assert combine_to is None
     return ref.fused_experts(x, w13, w2, topk_w, topk_ids, expert_map)
 
 
@@ -160,11 +161,11 @@ def mla_cache_write(kv_c, k_pe, cache, slot_mapping):
     return ref.mla_cache_write(kv_c, k_pe, cache, slot_mapping)
 
 
-def mla_paged_attention(q_nope, q_pe, cache, meta, scale, kv_lora_rank, topk_indices=None):
+def mla_paged_attention(q_nope, q_pe, cache, meta, scale, kv_lora_rank, topk_indices=None, rope_dim=None):
     if _use_cuda(q_nope):
-        return cuda_ops().mla_paged_attention(q_nope, q_pe, cache, meta, scale, kv_lora_rank, topk_indices)
+        return cuda_ops().mla_paged_attention(q_nope, q_pe, cache, meta, scale, kv_lora_rank, topk_indices, rope_dim)
     return ref.mla_paged_attention(q_nope, q_pe, cache, meta.block_tables, meta.seq_lens,
-                                   meta.query_start_loc, scale, kv_lora_rank, topk_indices)
+                                   meta.query_start_loc, scale, kv_lora_rank, topk_indices, rope_dim)
 
 
 # ---- sampling --------------------------------------------------------------------

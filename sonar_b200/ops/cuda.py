@@ -57,6 +57,18 @@ _tp_wait = _sig("sonar_tp_wait", c_void_p, c_int, c_int, c_int, c_int, c_void_p,
 _bump = _sig("sonar_bump", c_void_p, c_int, c_void_p)
 _all_reduce = _sig("sonar_all_reduce", c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                    c_int, c_int, c_int, c_void_p, c_int, c_void_p)
+_route_fn = _sig("sonar_topk_route", c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+              c_void_p, c_void_p, c_void_p)
+_moe_align = _sig("sonar_moe_align", c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                  c_void_p, c_void_p, c_void_p, c_int, c_void_p)
+_moe_gather = _sig("sonar_moe_gather", c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p)
+_gemm_grouped = _sig("sonar_gemm_grouped", c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_long, c_long,
+                     c_long, c_void_p, c_void_p, c_void_p, c_void_p)
+_moe_combine = _sig("sonar_moe_combine", c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                    c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p)
+_group_quant = _sig("sonar_group_quant_fp8", c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_long, c_int, c_void_p)
+_gemm_fp8 = _sig("sonar_gemm_fp8_block", c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_long, c_void_p, c_int, c_int,
+                 c_int, c_long, c_long, c_long, c_int, c_void_p, c_void_p)
 _argmax = _sig("sonar_argmax", c_void_p, c_long, c_int, c_int, c_void_p, c_void_p)
 _sample = _sig("sonar_sample", c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                c_long, c_void_p, c_uint, c_void_p, c_void_p)
@@ -338,37 +350,127 @@ def all_reduce(x, out, slot_ptrs, flag_ptrs, local_slots_ptr, local_flags_ptr, a
 
 
 def per_token_group_quant_fp8(x, group=128):
-    return ref.per_token_group_quant_fp8(x, group)
+    """x [T, K] → (e4m3 [T, K], scales [T, K/128] stored transposed so the GEMM reads them coalesced)."""
+    assert group == 128 and x.dim() == 2 and x.stride(1) == 1
+    t, k = x.shape
+    q = torch.empty((t, k), dtype=torch.float8_e4m3fn, device=x.device)
+    ld = (t + 3) // 4 * 4
+    st = torch.empty((k // 128, ld), dtype=torch.float32, device=x.device)
+    _check(_group_quant(x.data_ptr(), x.stride(0), q.data_ptr(), st.data_ptr(), t, k, ld, _DT[x.dtype], _stream()),
+           "per_token_group_quant_fp8")
+    return q, st[:, :t].t()
 
 
 def gemm_fp8_block(xq, xs, wq, ws, out_dtype=torch.bfloat16, out=None):
-    y = ref.gemm_fp8_block(xq, xs, wq, ws, out_dtype)
-    if out is not None:
-        out.copy_(y)
-        return out
-    return y
+    """Block-scaled fp8 GEMM: xs [T, K/128] (transposed storage preferred), ws [ceil(N/128), K/128]."""
+    m, k = xq.shape
+    n = wq.shape[0]
+    if xs.stride(0) != 1:                      # row-major scales (e.g. from the PyTorch restatement): transpose once
+        xs = xs.t().contiguous().t()
+    ws = ws if ws.stride(1) == 1 else ws.contiguous()
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=xq.device)
+    _check(_gemm_fp8(xq.data_ptr(), xs.data_ptr(), xs.stride(1), wq.data_ptr(), ws.data_ptr(), ws.stride(0),
+                     out.data_ptr(), m, n, k, xq.stride(0), wq.stride(0), out.stride(0), _DT[out.dtype],
+                     error_word(xq.device).data_ptr(), _stream()), "gemm_fp8_block")
+    return out
 
 
-# ---------------------------------------------------------------- MoE / MLA (composed until their kernels land)
+# ---------------------------------------------------------------- MoE
+def _route(logits, bias, k, n_group, topk_group, renormalize, sigmoid, scale):
+    t, e = logits.shape
+    assert logits.stride(1) == 1 and logits.stride(0) == e
+    w = torch.empty((t, k), dtype=torch.float32, device=logits.device)
+    ids = torch.empty((t, k), dtype=torch.int32, device=logits.device)
+    fb = bias.float().contiguous() if bias is not None else None
+    _check(_route_fn(logits.data_ptr(), _DT[logits.dtype], _ptr(fb), t, e, k, n_group, topk_group, int(renormalize),
+                     int(sigmoid), scale, w.data_ptr(), ids.data_ptr(), _stream()), "topk_route")
+    return w, ids
+
+
 def topk_softmax(logits, k, renormalize):
-    return ref.topk_softmax(logits, k, renormalize)
+    return _route(logits, None, k, 1, 1, renormalize, False, 1.0)
 
 
 def grouped_topk(logits, bias, k, n_group, topk_group, renormalize, scale, scoring="sigmoid"):
-    return ref.grouped_topk(logits, bias, k, n_group, topk_group, renormalize, scale, scoring)
+    return _route(logits, bias, k, n_group, topk_group, renormalize, scoring == "sigmoid", scale)
 
 
-def fused_experts(x, w13, w2, topk_w, topk_ids, expert_map=None):
-    return ref.fused_experts(x, w13, w2, topk_w, topk_ids, expert_map)
+class _MoeScratch:
+    """Per-(device, experts) index buffers of the expert-sorted layout."""
+
+    def __init__(self, device, n_experts: int, max_pairs: int) -> None:
+        with torch.inference_mode(False):
+            self.max_blocks = (max_pairs + 127) // 128 + n_experts
+            i32 = dict(dtype=torch.int32, device=device)
+            self.counts = torch.zeros(n_experts, **i32)
+            self.offsets = torch.zeros(n_experts, **i32)
+            self.cursor = torch.zeros(n_experts, **i32)
+            self.block_expert = torch.zeros(self.max_blocks, **i32)
+            self.meta = torch.zeros(2, **i32)
+            self.row_of = torch.zeros(max_pairs, **i32)
+            self.token_of = torch.zeros(self.max_blocks * 128, **i32)
+            self.max_pairs = max_pairs
 
 
+_moe_scratch: dict[tuple, _MoeScratch] = {}
+
+
+def moe_align(topk_ids, n_local_experts, expert_map=None):
+    t, k = topk_ids.shape
+    key = (topk_ids.device.index or 0, n_local_experts)
+    sc = _moe_scratch.get(key)
+    if sc is None or sc.max_pairs < t * k:
+        sc = _moe_scratch[key] = _MoeScratch(topk_ids.device, n_local_experts, max(t * k, 8192 * 8))
+    _check(_moe_align(topk_ids.data_ptr(), _ptr(expert_map), t, k, n_local_experts, sc.counts.data_ptr(),
+                      sc.offsets.data_ptr(), sc.cursor.data_ptr(), sc.block_expert.data_ptr(), sc.meta.data_ptr(),
+                      sc.row_of.data_ptr(), sc.token_of.data_ptr(), sc.max_blocks, _stream()), "moe_align")
+    return sc
+
+
+def fused_experts(x, w13, w2, topk_w, topk_ids, expert_map=None, combine_to=None):
+    """Routed-expert FFN on the expert-sorted layout: gather → grouped GEMM (w13) → SiLU·mul → grouped GEMM
+    (w2) → weighted combine.  ``combine_to`` = (dst_ptrs, shard_rows, local_done, flag_ptrs, seq, seq_base)
+    sends each token's combined row to its owner's partial buffer instead of returning a local tensor."""
+    t, h = x.shape
+    e_local, n13, _ = w13.shape
+    inter = w2.shape[2]
+    k = topk_ids.shape[1]
+    sc = moe_align(topk_ids, e_local, expert_map)
+    # rows actually present are only known on the device: size buffers by the bound that cannot be exceeded
+    max_rows = min(sc.max_blocks, (t * k + 127) // 128 + min(e_local, t * k)) * 128
+    a = torch.empty((max_rows, h), dtype=x.dtype, device=x.device)
+    _check(_moe_gather(x.data_ptr(), x.stride(0), sc.token_of.data_ptr(), sc.meta.data_ptr(), a.data_ptr(), h,
+                       max_rows, _DT[x.dtype], _stream()), "moe_gather")
+    g = torch.empty((max_rows, n13), dtype=x.dtype, device=x.device)
+    err = error_word(x.device).data_ptr()
+    _check(_gemm_grouped(a.data_ptr(), w13.data_ptr(), g.data_ptr(), max_rows, n13, h, e_local, h, h, n13,
+                         sc.block_expert.data_ptr(), sc.meta.data_ptr(), err, _stream()), "gemm_grouped(w13)")
+    act = silu_and_mul(g)
+    y = torch.empty((max_rows, h), dtype=x.dtype, device=x.device)
+    _check(_gemm_grouped(act.data_ptr(), w2.data_ptr(), y.data_ptr(), max_rows, h, inter, e_local, inter, inter, h,
+                         sc.block_expert.data_ptr(), sc.meta.data_ptr(), err, _stream()), "gemm_grouped(w2)")
+    tw = topk_w.float().contiguous()
+    if combine_to is None:
+        out = torch.empty((t, h), dtype=x.dtype, device=x.device)
+        _check(_moe_combine(y.data_ptr(), sc.row_of.data_ptr(), tw.data_ptr(), t, k, h, out.data_ptr(), None, 0, None,
+                            None, 0, None, _DT[x.dtype], _stream()), "moe_combine")
+        return out
+    dst_ptrs, shard_rows, local_done, flag_ptrs, seq, seq_base = combine_to
+    _check(_moe_combine(y.data_ptr(), sc.row_of.data_ptr(), tw.data_ptr(), t, k, h, None, dst_ptrs.data_ptr(),
+                        shard_rows, local_done.data_ptr(), flag_ptrs.data_ptr(), seq, _ptr(seq_base), _DT[x.dtype],
+                        _stream()), "moe_combine(push)")
+    return None
+
+
+# ---------------------------------------------------------------- MLA (composed until its kernels land)
 def mla_cache_write(kv_c, k_pe, cache, slot_mapping):
     return ref.mla_cache_write(kv_c, k_pe, cache, slot_mapping)
 
 
-def mla_paged_attention(q_nope, q_pe, cache, meta, scale, kv_lora_rank, topk_indices=None):
+def mla_paged_attention(q_nope, q_pe, cache, meta, scale, kv_lora_rank, topk_indices=None, rope_dim=None):
     return ref.mla_paged_attention(q_nope, q_pe, cache, meta.block_tables, meta.seq_lens, meta.query_start_loc,
-                                   scale, kv_lora_rank, topk_indices)
+                                   scale, kv_lora_rank, topk_indices, rope_dim)
 
 
 # ---------------------------------------------------------------- sampling

@@ -219,7 +219,7 @@ def mla_cache_write(kv_c: torch.Tensor, k_pe: torch.Tensor, cache: torch.Tensor,
 def mla_paged_attention(q_nope: torch.Tensor, q_pe: torch.Tensor, cache: torch.Tensor,
                         block_tables: torch.Tensor, seq_lens: torch.Tensor,
                         query_start_loc: torch.Tensor, scale: float, kv_lora_rank: int,
-                        topk_indices: torch.Tensor | None = None) -> torch.Tensor:
+                        topk_indices: torch.Tensor | None = None, rope_dim: int | None = None) -> torch.Tensor:
     """Absorbed-form MLA attention (MQA over the latent cache).
 
     q_nope: ``[T, H, R]`` (already multiplied by W_UK), q_pe: ``[T, H, P]``;
@@ -238,7 +238,8 @@ def mla_paged_attention(q_nope: torch.Tensor, q_pe: torch.Tensor, cache: torch.T
             continue
         nb = -(-ctx // bs)
         rows = cache[block_tables[i, :nb].long()].reshape(nb * bs, -1)[:ctx].float()
-        kc, kp = rows[:, :kv_lora_rank], rows[:, kv_lora_rank:]
+        rd = rope_dim if rope_dim is not None else rows.shape[1] - kv_lora_rank
+        kc, kp = rows[:, :kv_lora_rank], rows[:, kv_lora_rank:kv_lora_rank + rd]
         scores = (torch.einsum("qhr,kr->hqk", q_nope[s:e].float(), kc)
                   + torch.einsum("qhp,kp->hqk", q_pe[s:e].float(), kp)) * scale
         qpos = torch.arange(ctx - ql, ctx, device=cache.device)[:, None]

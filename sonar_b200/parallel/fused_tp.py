@@ -187,6 +187,22 @@ class FusedTPContext(TPContext):
         self.cu.tp_wait(self.gflags, self.world_size, self.Tl, self.T_pad, x.seq, self.seq_base, self.err)
         return self.gather[: self.T_pad]
 
+    # mixture-of-experts hooks: dispatch = the all-gather the norm kernel already pushed; combine = the
+    # weighted top-k sum stored straight into the token owner's partial buffer
+    def materialize(self, x):
+        return self._materialize(x) if isinstance(x, Gathered) else x
+
+    def moe_push_target(self):
+        if self.dtype != torch.bfloat16:
+            return None
+        self.seq += 1
+        return (self.dst_ptrs, self.Tl, self.local_done, self.pflag_ptrs, self.seq, self.seq_base)
+
+    def finish_partial(self, y, target):
+        if target is not None:
+            return Partial(target[4])
+        return self._push_partial(y)
+
     def gather_tokens(self, h, num_tokens: int) -> torch.Tensor:
         if isinstance(h, Gathered):
             return self._materialize(h)[:num_tokens]

@@ -63,6 +63,19 @@ class TPContext:
         y = layer.apply(x)
         return self.group.all_reduce(y) if self.world_size > 1 else y
 
+    # mixture-of-experts hooks ------------------------------------------------------
+    def materialize(self, x) -> torch.Tensor:
+        """Block input as a plain ``[T, H]`` tensor holding every token."""
+        return x
+
+    def moe_push_target(self):
+        """Where the expert combine kernel should send token rows (None: return a local partial)."""
+        return None
+
+    def finish_partial(self, y, target):
+        """Reduce a locally held partial sum over the group (the MoE analogue of ``row_linear``)."""
+        return self.group.all_reduce(y) if self.world_size > 1 else y
+
     def gather_tokens(self, h: torch.Tensor, num_tokens: int) -> torch.Tensor:
         """Block layout → replicated ``[T, H]`` (before the LM head)."""
         return h

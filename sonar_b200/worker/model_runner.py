@@ -311,7 +311,7 @@ class ModelRunner:
             hidden = out_buf[:total]
         else:
             tp.begin_step(total)
-            if self.is_cuda:
+            if self.is_cuda and not getattr(self.model, "uses_mla", False):
                 from sonar_b200.ops import cuda as cuda_ops
                 cuda_ops.build_attention_work(meta, self)
             ids = self.d_input_ids[:total]
@@ -473,6 +473,8 @@ class ModelRunner:
         from sonar_b200 import envs
         if not self.is_cuda or self.cfg.enforce_eager or not envs.SONAR_CUDA_GRAPHS or self.pp is not None:
             return
+        if getattr(self.model, "uses_mla", False):
+            return   # the latent-attention path still has host-side steps (indexer top-k): eager only
         from sonar_b200.ops import cuda as cuda_ops
         tp = get_tp_context()
         sizes = sorted({b for b in [1, 2, 4, 8, 16, 24, 32, 40, 48, 56, 64] + list(range(80, 513, 16))

@@ -80,3 +80,17 @@ def test_stop_token_and_text(llm):
 def test_text_prompt_roundtrip(llm):
     out = llm.generate("hello world", SamplingParams(temperature=0, max_tokens=4, ignore_eos=True))[0]
     assert out.prompt == "hello world" and len(out.outputs[0].token_ids) == 4
+
+
+@pytest.mark.parametrize("preset", ["tiny-qwen3", "tiny-qwen3-moe", "tiny-deepseek"])
+def test_other_model_families_batched_equals_single(preset):
+    """Qwen3 (q/k norm, tied head), Qwen3-MoE (routed experts) and DeepSeek (MLA + sparse indexer + grouped MoE)."""
+    eng = LLM(preset, dtype="float32", max_model_len=256, num_gpu_blocks_override=64, max_num_seqs=4,
+              max_num_batched_tokens=48, device="cpu")
+    sp = SamplingParams(temperature=0, max_tokens=4, ignore_eos=True)
+    prompts = [{"prompt_token_ids": [(7 * i + 3 * j) % 900 + 5 for i in range(30 + 15 * j)]} for j in range(3)]
+    batched = [o.outputs[0].token_ids for o in eng.generate(prompts, sp)]
+    eng.reset_prefix_cache()
+    single = [eng.generate(p, sp)[0].outputs[0].token_ids for p in prompts]
+    eng.shutdown()
+    assert batched == single

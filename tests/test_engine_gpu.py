@@ -71,3 +71,24 @@ def test_random_sampling_runs(llm):
     outs = llm.generate([{"prompt_token_ids": p} for p in _prompts(6, seed=3)], sp)
     assert all(len(o.outputs[0].token_ids) == 5 for o in outs)
     assert all(0 <= t < 2048 for o in outs for t in o.outputs[0].token_ids)
+
+
+def test_moe_model_matches_torch_path():
+    from sonar_b200 import LLM, SamplingParams, ops
+    eng = LLM("tiny-qwen3-moe", dtype="bfloat16", max_model_len=512, max_num_seqs=8, max_num_batched_tokens=128,
+              gpu_memory_utilization=0.05, skip_tokenizer_init=True)
+    sp = SamplingParams(temperature=0, max_tokens=2, prompt_logprobs=0, ignore_eos=True, detokenize=False)
+    prompts = [{"prompt_token_ids": [t % 1000 + 4 for t in p]} for p in _prompts(4, seed=5)]
+    got = eng.generate(prompts, sp)
+    ops._FORCE_TORCH = True
+    try:
+        eng.reset_prefix_cache()
+        want = eng.generate(prompts, sp)
+    finally:
+        ops._FORCE_TORCH = False
+    eng.shutdown()
+    for g, w, p in zip(got, want, prompts):
+        ids = p["prompt_token_ids"]
+        a = torch.tensor([g.prompt_logprobs[i][ids[i]].logprob for i in range(1, len(ids))])
+        b = torch.tensor([w.prompt_logprobs[i][ids[i]].logprob for i in range(1, len(ids))])
+        assert (a - b).abs().max() < 0.15, (a - b).abs().max()

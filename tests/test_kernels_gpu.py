@@ -223,3 +223,70 @@ def test_sample_rng_statistics(cu):
     assert (freq - p).abs().max() < 0.03
     ids2 = cu.sample(logits, temp, None, None, None)
     assert not torch.equal(ids, ids2)       # successive calls draw fresh noise
+
+
+@pytest.mark.parametrize("e,k,dtype", [(128, 8, torch.float32), (8, 2, torch.bfloat16), (60, 4, torch.float32)])
+def test_topk_softmax_routing(cu, e, k, dtype):
+    torch.manual_seed(20)
+    logits = (torch.randn(77, e, device=DEV) * 2).to(dtype)
+    w_ref, i_ref = ref.topk_softmax(logits.float(), k, True)
+    w, i = cu.topk_softmax(logits, k, True)
+    assert torch.equal(i.long().sort(-1).values, i_ref.long().sort(-1).values)
+    _close(w.gather(1, i.long().argsort(-1)), w_ref.gather(1, i_ref.long().argsort(-1)), 1e-4, 1e-3)
+
+
+def test_grouped_topk_routing(cu):
+    torch.manual_seed(21)
+    t, e = 50, 256
+    logits = torch.randn(t, e, device=DEV)
+    bias = torch.randn(e, device=DEV) * 0.1
+    w_ref, i_ref = ref.grouped_topk(logits, bias, 8, 8, 4, True, 2.5, "sigmoid")
+    w, i = cu.grouped_topk(logits, bias, 8, 8, 4, True, 2.5, "sigmoid")
+    assert torch.equal(i.long().sort(-1).values, i_ref.long().sort(-1).values)
+    _close(w.sum(-1), w_ref.sum(-1), 1e-4, 1e-4)
+
+
+@pytest.mark.parametrize("t,e,k,h,inter,ep", [(200, 8, 2, 256, 128, False), (33, 16, 4, 512, 256, True), (1, 8, 2, 256, 64, False)])
+def test_fused_experts(cu, t, e, k, h, inter, ep):
+    torch.manual_seed(22)
+    x = torch.randn(t, h, device=DEV, dtype=torch.bfloat16)
+    w13 = torch.randn(e, 2 * inter, h, device=DEV, dtype=torch.bfloat16) * 0.05
+    w2 = torch.randn(e, h, inter, device=DEV, dtype=torch.bfloat16) * 0.05
+    logits = torch.randn(t, e, device=DEV)
+    tw, ids = ref.topk_softmax(logits, k, True)
+    emap = None
+    if ep:   # this "rank" holds the odd experts only
+        emap = torch.full((e,), -1, dtype=torch.int32, device=DEV)
+        emap[1::2] = torch.arange(e // 2, dtype=torch.int32, device=DEV)
+        w13, w2 = w13[1::2].contiguous(), w2[1::2].contiguous()
+    want = ref.fused_experts(x.float(), w13.float(), w2.float(), tw, ids, emap)
+    got = cu.fused_experts(x, w13, w2, tw, ids, emap)
+    torch.cuda.synchronize()
+    cu.check_device_errors()
+    _close(got, want, 3e-2, 3e-2)
+
+
+def test_per_token_group_quant_fp8(cu):
+    torch.manual_seed(30)
+    x = torch.randn(70, 1024, device=DEV, dtype=torch.bfloat16) * 3
+    q_ref, s_ref = ref.per_token_group_quant_fp8(x)
+    q, s = cu.per_token_group_quant_fp8(x)
+    _close(s, s_ref, 1e-7, 1e-5)
+    deq = q.float().reshape(70, 8, 128) * s[..., None]
+    _close(deq.reshape(70, 1024), x, 0.02, 0.07)     # e4m3: 3 mantissa bits
+    assert (q.float() - q_ref.float()).abs().max() <= 32   # at most one fp8 step at the top binade
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (300, 1024, 512), (1, 256, 4096), (1000, 6144, 1024), (77, 136, 256)])
+def test_gemm_fp8_block(cu, m, n, k):
+    torch.manual_seed(31 + m)
+    x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(n, k, device=DEV, dtype=torch.bfloat16) * (k ** -0.5)
+    wq, ws = ref.block_quant_fp8_weight(w)
+    xq, xs = cu.per_token_group_quant_fp8(x)
+    want = ref.gemm_fp8_block(xq, xs.contiguous(), wq, ws, torch.float32)
+    got = cu.gemm_fp8_block(xq, xs, wq, ws)
+    torch.cuda.synchronize()
+    cu.check_device_errors()
+    _close(got, want, 2e-2, 2e-2)
+    _close(got, x.float() @ w.float().t(), 0.15, 0.1)   # and it approximates the unquantised product

@@ -12,3 +12,13 @@ def test_tp2_matches_tp1_on_cpu(tmp_path):
         assert a["tokens"] == b["tokens"]
         d = (torch.tensor(a["prompt_logprobs"]) - torch.tensor(b["prompt_logprobs"])).abs().max()
         assert d < 1e-3, d
+
+
+def test_moe_tp2_and_ep2_match_tp1_on_cpu(tmp_path):
+    ckpt = make_checkpoint(str(tmp_path / "ckpt"), "tiny-qwen3-moe", dtype=torch.float32)
+    one = launch(1, ckpt, str(tmp_path / "tp1.json"), "cpu")
+    for name, env, port in (("tp", {}, 29615), ("ep", {"SONAR_TEST_EP": "1"}, 29617)):
+        two = launch(2, ckpt, str(tmp_path / f"{name}2.json"), "cpu", env_extra=env, port=port)
+        for a, b in zip(one, two):
+            d = (torch.tensor(a["prompt_logprobs"]) - torch.tensor(b["prompt_logprobs"])).abs().max()
+            assert d < 1e-3, (name, d)

@@ -29,3 +29,17 @@ def test_tp2_matches_tp1(baseline, mode):
         diff = (torch.tensor(a["prompt_logprobs"]) - torch.tensor(b["prompt_logprobs"])).abs().max().item()
         worst = max(worst, diff)
     assert worst < 0.1, worst
+
+
+@needs2
+@pytest.mark.parametrize("ep", ["0", "1"])
+def test_moe_tp2_fused_matches_tp1(tmp_path_factory, ep):
+    """Mixture of experts under the fused layout: all-gather push → grouped GEMM → combine pushed to the owner."""
+    d = tmp_path_factory.mktemp("moe")
+    ckpt = make_checkpoint(str(d / "ckpt"), "tiny-qwen3-moe")
+    one = launch(1, ckpt, str(d / "tp1.json"), "cuda")
+    two = launch(2, ckpt, str(d / "tp2.json"), "cuda",
+                 env_extra={"SONAR_TP_COMM": "fused", "NCCL_NVLS_ENABLE": "0", "SONAR_TEST_EP": ep}, port=29641 + int(ep))
+    worst = max((torch.tensor(a["prompt_logprobs"]) - torch.tensor(b["prompt_logprobs"])).abs().max().item()
+                for a, b in zip(one, two))
+    assert worst < 0.15, worst

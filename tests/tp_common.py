@@ -20,6 +20,10 @@ def make_checkpoint(directory: str, preset: str = "tiny-llama-128", dtype=torch.
 
     def w(*shape, std=0.05):
         return (torch.randn(*shape, generator=g) * std).to(dtype)
+    if cfg.get("model_type", "").startswith("qwen3"):
+        extra_qk = True
+    else:
+        extra_qk = False
     t = {"model.embed_tokens.weight": w(v, h, std=0.5), "model.norm.weight": (1 + 0.1 * torch.randn(h, generator=g)).to(dtype),
          "lm_head.weight": w(v, h)}
     for i in range(cfg["num_hidden_layers"]):
@@ -28,9 +32,20 @@ def make_checkpoint(directory: str, preset: str = "tiny-llama-128", dtype=torch.
         t[p + "self_attn.k_proj.weight"] = w(hk * hd, h)
         t[p + "self_attn.v_proj.weight"] = w(hk * hd, h)
         t[p + "self_attn.o_proj.weight"] = w(h, hq * hd)
-        t[p + "mlp.gate_proj.weight"] = w(inter, h)
-        t[p + "mlp.up_proj.weight"] = w(inter, h)
-        t[p + "mlp.down_proj.weight"] = w(h, inter)
+        if extra_qk:
+            t[p + "self_attn.q_norm.weight"] = (1 + 0.1 * torch.randn(hd, generator=g)).to(dtype)
+            t[p + "self_attn.k_norm.weight"] = (1 + 0.1 * torch.randn(hd, generator=g)).to(dtype)
+        if "num_experts" in cfg:
+            mi = cfg["moe_intermediate_size"]
+            t[p + "mlp.gate.weight"] = w(cfg["num_experts"], h, std=0.5)
+            for e in range(cfg["num_experts"]):
+                t[p + f"mlp.experts.{e}.gate_proj.weight"] = w(mi, h)
+                t[p + f"mlp.experts.{e}.up_proj.weight"] = w(mi, h)
+                t[p + f"mlp.experts.{e}.down_proj.weight"] = w(h, mi)
+        else:
+            t[p + "mlp.gate_proj.weight"] = w(inter, h)
+            t[p + "mlp.up_proj.weight"] = w(inter, h)
+            t[p + "mlp.down_proj.weight"] = w(h, inter)
         t[p + "input_layernorm.weight"] = (1 + 0.1 * torch.randn(h, generator=g)).to(dtype)
         t[p + "post_attention_layernorm.weight"] = (1 + 0.1 * torch.randn(h, generator=g)).to(dtype)
     save_checkpoint(directory, cfg, t)

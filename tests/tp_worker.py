@@ -26,6 +26,7 @@ def run(ckpt: str, device: str, world: int):
     llm = LLM(ckpt, dtype=dtype, max_model_len=512, max_num_seqs=8, max_num_batched_tokens=160,
               gpu_memory_utilization=0.05, skip_tokenizer_init=True, tensor_parallel_size=world, device=device,
               num_gpu_blocks_override=512 if device == "cpu" else None,
+              enable_expert_parallel=os.environ.get("SONAR_TEST_EP") == "1",
               distributed_executor_backend="external_launcher" if world > 1 else "uni")
     sp = SamplingParams(temperature=0, max_tokens=4, prompt_logprobs=0, ignore_eos=True, detokenize=False)
     outs = llm.generate([{"prompt_token_ids": p} for p in prompts()], sp)

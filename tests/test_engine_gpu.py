@@ -76,7 +76,7 @@ def test_random_sampling_runs(llm):
 def test_moe_model_matches_torch_path():
     from sonar_b200 import LLM, SamplingParams, ops
     eng = LLM("tiny-qwen3-moe", dtype="bfloat16", max_model_len=512, max_num_seqs=8, max_num_batched_tokens=128,
-              gpu_memory_utilization=0.05, skip_tokenizer_init=True)
+              num_gpu_blocks_override=512, skip_tokenizer_init=True)
     sp = SamplingParams(temperature=0, max_tokens=2, prompt_logprobs=0, ignore_eos=True, detokenize=False)
     prompts = [{"prompt_token_ids": [t % 1000 + 4 for t in p]} for p in _prompts(4, seed=5)]
     got = eng.generate(prompts, sp)

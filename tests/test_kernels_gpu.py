@@ -289,4 +289,5 @@ def test_gemm_fp8_block(cu, m, n, k):
     torch.cuda.synchronize()
     cu.check_device_errors()
     _close(got, want, 2e-2, 2e-2)
-    _close(got, x.float() @ w.float().t(), 0.15, 0.1)   # and it approximates the unquantised product
+    exact = x.float() @ w.float().t()                      # and it approximates the unquantised product
+    assert (got.float() - exact).norm() / exact.norm() < 0.06

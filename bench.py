@@ -261,10 +261,14 @@ def main() -> None:
             "h2d_bytes_per_step": h2d // max(steps, 1), "d2h_bytes_per_step": d2h // max(steps, 1),
         }
         print(json.dumps(line))
-    llm.shutdown()
+    sys.stdout.flush()
     if world > 1 and dist.is_initialized():
+        # every rank has printed/finished its work; leave without the collective teardown (destroying NCCL
+        # communicators that took part in captured graphs can block for minutes)
         dist.barrier()
-        dist.destroy_process_group()
+        sys.stdout.flush()
+        os._exit(0)
+    llm.shutdown()
 
 
 if __name__ == "__main__":

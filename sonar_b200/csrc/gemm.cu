@@ -509,41 +509,39 @@ int num_sms() {
 // Tile width by a small cost model: waves × measured relative cost of one 128×BN tile pass
 // (a 128×256 tile runs the tensor pipe near its peak; narrower tiles re-read A from shared memory
 // per fewer columns and reach ≈70 % / ≈40 % of that rate, so they only win when they save waves).
-int pick_bn(int M, int N, bool stream_k) {
-  if (stream_k) {
-    // whole waves cost one tile time each; the partial last wave is split along K over up to 8 CTAs
-    // per tile and pays a fix-up that grows with the number of partials the finisher sums
-    const int sms = num_sms();
-    const int num_m = (M + BM - 1) / BM;
-    const int bns[3] = {256, 128, 64};
-    const double per_tile[3] = {1.0, 0.725, 0.66};
-    int best = 256;
-    double best_cost = 1e30;
-    for (int i = 0; i < 3; ++i) {
-      const int tiles = num_m * ((N + bns[i] - 1) / bns[i]);
-      const int full = tiles / sms, rem = tiles % sms;
-      double cost = full * per_tile[i];
-      if (rem) {
-        int split = sms / rem;
-        if (split > 8) split = 8;
-        if (split > bns[i] / 32) split = bns[i] / 32;
-        if (split < 1) split = 1;
-        cost += per_tile[i] * (1.0 / split + (split > 1 ? 0.08 : 0.0));
-      }
-      if (cost < best_cost - 1e-9) { best_cost = cost; best = bns[i]; }
-    }
-    return best;
-  }
+// Tile width from a latency model fitted to measurements on B200 (microseconds):
+//   time ≈ whole_waves · num_kb · t_kb(BN)  +  tail
+//   tail (last, partial wave) = ceil(num_kb / S) · t_kb(BN) + (S > 1 ? 2 + 0.04·BN : 0)
+// t_kb = time one CTA needs per 64-wide k-block (0.44 / 0.30 / 0.25 µs for BN 256 / 128 / 64: a 128×256
+// block keeps the tensor pipe busiest but moves the most bytes per CTA), S = split-K factor the launch
+// code would choose, and the fix-up cost grows with the fp32 partial tile each part has to park.
+int split_factor(int rem, int sms, int bn, int num_kb, int ws_ctas) {
+  if (rem == 0) return 1;
+  int S = sms / rem;
+  if (S > 8) S = 8;
+  if (S > bn / 32) S = bn / 32;
+  if (S > num_kb / 2) S = num_kb / 2;
+  while (S > 1 && (S - 1) * ((num_kb + S - 1) / S) >= num_kb) --S;
+  while (S > 1 && rem * S > ws_ctas) --S;
+  return S < 1 ? 1 : S;
+}
+
+int pick_bn(int M, int N, int K, bool stream_k) {
   const int sms = num_sms();
   const int num_m = (M + BM - 1) / BM;
+  const int num_kb = (K + BK - 1) / BK;
+  const int bns[3] = {256, 128, 64};
+  const double t_kb[3] = {0.44, 0.30, 0.25};
   int best = 256;
   double best_cost = 1e30;
-  const int bns[3] = {256, 128, 64};
-  const double per_tile[3] = {1.0, 0.725, 0.66};
   for (int i = 0; i < 3; ++i) {
-    int tiles = num_m * ((N + bns[i] - 1) / bns[i]);
-    int waves = (tiles + sms - 1) / sms;
-    double cost = waves * per_tile[i];
+    const int tiles = num_m * ((N + bns[i] - 1) / bns[i]);
+    const int full = tiles / sms, rem = tiles % sms;
+    double cost = (double)full * num_kb * t_kb[i];
+    if (rem) {
+      const int S = stream_k ? split_factor(rem, sms, bns[i], num_kb, 1 << 30) : 1;
+      cost += (double)((num_kb + S - 1) / S) * t_kb[i] + (S > 1 ? 2.0 + 0.04 * bns[i] : 0.0);
+    }
     if (cost < best_cost - 1e-9) { best_cost = cost; best = bns[i]; }
   }
   return best;
@@ -570,12 +568,7 @@ int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p
   const int rem = tiles % sms;
   if (q.ws != nullptr && rem != 0) {
     // split-K for the partial last wave: S parts per tile, S ≤ 8, ≤ chunks per tile, every part non-empty
-    int S = sms / rem;
-    if (S > 8) S = 8;
-    if (S > BN / 32) S = BN / 32;
-    if (S > num_kb / 2) S = num_kb / 2;
-    while (S > 1 && (S - 1) * ((num_kb + S - 1) / S) >= num_kb) --S;
-    while (S > 1 && rem * S > q.ws_ctas) --S;
+    const int S = split_factor(rem, sms, BN, num_kb, q.ws_ctas);
     if (S > 1) {
       q.sk_tiles = rem;
       q.sk_split = S;
@@ -628,7 +621,7 @@ SONAR_API int sonar_gemm(const void* A, const void* B, void* C, const void* bias
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.bias = bias; p.err = err;
   p.tp = 1; p.shard_rows = M;
   p.ws = ws; p.ws_flags = ws_flags; p.ws_ctas = ws_ctas;
-  const int bn = force_bn ? force_bn : pick_bn(M, N, ws != nullptr);
+  const int bn = force_bn ? force_bn : pick_bn(M, N, K, ws != nullptr);
   if (bn != 64 && bn != 128 && bn != 256) return SONAR_BAD_ARG;
   if (in_dtype == SONAR_BF16) {
     if (out_dtype == SONAR_BF16) return launch_bn<__nv_bfloat16, 1>(bn, A, B, p, lda, ldb, s);
@@ -657,7 +650,7 @@ SONAR_API int sonar_gemm_tp(const void* A, const void* B, void* C, int M, int N,
   p.m_rot = gather_flags ? (int)(((long)rank * shard_rows) / BM) : 0;
   p.dst_ptrs = dst_ptrs; p.local_done = local_done; p.flag_ptrs = flag_ptrs;
   p.ws = ws; p.ws_flags = ws_flags; p.ws_ctas = ws_ctas;
-  const int bn = force_bn ? force_bn : pick_bn(M, N, ws != nullptr);
+  const int bn = force_bn ? force_bn : pick_bn(M, N, K, ws != nullptr);
   return launch_bn<__nv_bfloat16, 1>(bn, A, B, p, lda, ldb, s);
 }
 
@@ -678,4 +671,4 @@ SONAR_API int sonar_gemm_grouped(const void* A, const void* W, void* C, int max_
   return launch_bn<__nv_bfloat16, 1>(bn, A, W, p, lda, ldw, s, (long)n_experts * N);
 }
 
-SONAR_API int sonar_gemm_pick_bn(int M, int N, int stream_k) { return pick_bn(M, N, stream_k != 0); }
+SONAR_API int sonar_gemm_pick_bn(int M, int N, int K, int stream_k) { return pick_bn(M, N, K, stream_k != 0); }

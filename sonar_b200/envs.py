@@ -35,9 +35,10 @@ environment_variables: dict[str, Callable[[], Any]] = {
     "SONAR_OPS": _str("SONAR_OPS", "auto"),
     # GEMM: "tcgen05" = hand-written kernel, "cublas" = torch.matmul baseline.
     "SONAR_GEMM": _str("SONAR_GEMM", "tcgen05"),
-    # collectives: "fused" = GEMM+collective kernels, "custom" = P2P all-reduce,
+    # tensor-parallel collectives: "fused" = sequence-parallel layout with GEMM+collective kernels,
+    # "custom" = replicated layout, one-shot P2P all-reduce kernel for small tensors and NCCL above,
     # "nccl" = torch.distributed only (the baseline arm).
-    "SONAR_TP_COMM": _str("SONAR_TP_COMM", "fused"),
+    "SONAR_TP_COMM": _str("SONAR_TP_COMM", "custom"),
     "SONAR_CUDA_GRAPHS": _bool("SONAR_CUDA_GRAPHS", True),
     "SONAR_SYMM_HEAP_MB": _int("SONAR_SYMM_HEAP_MB", 512),
     # server

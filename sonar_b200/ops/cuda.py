@@ -73,7 +73,7 @@ _argmax = _sig("sonar_argmax", c_void_p, c_long, c_int, c_int, c_void_p, c_void_
 _sample = _sig("sonar_sample", c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                c_long, c_void_p, c_uint, c_void_p, c_void_p)
 lib.sonar_last_cuda_error.restype = c_int
-lib.sonar_gemm_pick_bn.argtypes = [c_int, c_int, c_int]
+lib.sonar_gemm_pick_bn.argtypes = [c_int, c_int, c_int, c_int]
 lib.sonar_gemm_pick_bn.restype = c_int
 
 

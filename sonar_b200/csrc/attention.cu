@@ -85,6 +85,52 @@ __device__ __forceinline__ void load_page_warp(uint32_t k_smem, uint32_t v_smem,
   }
 }
 
+// fp8 (e4m3) KV cache: a page tile is PAGE·HD bytes; it is staged raw and widened to the 16-bit swizzled
+// tile layout in shared memory before the MMAs (the per-tensor scales are folded into the softmax scale
+// and the output).
+template <int HD>
+__device__ __forceinline__ void load_page_warp_fp8(uint32_t k_raw, uint32_t v_raw, const uint8_t* k_g,
+                                                   const uint8_t* v_g, int lane) {
+  constexpr int CHUNKS = PAGE * HD / 16;
+#pragma unroll
+  for (int c = lane; c < CHUNKS; c += 32) {
+    cp_async16(k_raw + c * 16, k_g + c * 16);
+    cp_async16(v_raw + c * 16, v_g + c * 16);
+  }
+}
+template <typename T> __device__ __forceinline__ uint32_t cvt_fp8x2(uint16_t v);
+template <> __device__ __forceinline__ uint32_t cvt_fp8x2<__half>(uint16_t v) {
+  __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)v, __NV_E4M3);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t cvt_fp8x2<__nv_bfloat16>(uint16_t v) {
+  __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)v, __NV_E4M3);
+  float2 f = __half22float2(*reinterpret_cast<__half2*>(&h));
+  __nv_bfloat162 b = __floats2bfloat162_rn(f.x, f.y);
+  return *reinterpret_cast<uint32_t*>(&b);
+}
+// raw: [PAGE][HD] bytes (generic pointer into shared memory); tile: swizzled 16-bit tile (shared address)
+template <typename T, int HD>
+__device__ __forceinline__ void widen_page(const uint8_t* raw, uint32_t tile, int lane) {
+  constexpr int CPR16 = HD / 16;                 // 16-byte raw chunks per key row
+  constexpr int CHUNKS = PAGE * CPR16;
+#pragma unroll
+  for (int c = lane; c < CHUNKS; c += 32) {
+    const int key = c / CPR16, c16 = c % CPR16;
+    const uint4 r = *reinterpret_cast<const uint4*>(raw + c * 16);
+    const uint16_t* h = reinterpret_cast<const uint16_t*>(&r);
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = cvt_fp8x2<T>(h[i]);
+    const uint32_t row = tile + key * (HD * 2);
+    const int ch = c16 * 2;
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(row + ((ch ^ (key & 7)) << 4)), "r"(w[0]), "r"(w[1]),
+                 "r"(w[2]), "r"(w[3]));
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(row + (((ch + 1) ^ (key & 7)) << 4)), "r"(w[4]),
+                 "r"(w[5]), "r"(w[6]), "r"(w[7]));
+  }
+}
+
 // Scores, online softmax and P·V for one 16-key page held in shared memory.
 // key0: absolute index of the page's first key.  limit[r]: keys <= limit[r] are visible to row r
 // (already includes the context length); lower[r]: keys >= lower[r] (sliding window).
@@ -187,15 +233,18 @@ __device__ __forceinline__ void load_q_frags(uint32_t (*qf)[4], const T* q, long
 }
 
 // ------------------------------------------------------------------ decode
-template <typename T, int HD, int NSTAGE>
+template <typename T, int HD, int NSTAGE, bool KV8>
 __global__ void __launch_bounds__(128) attn_decode_kernel(
-    const T* __restrict__ q, long q_tok_stride, const T* __restrict__ cache, const int* __restrict__ block_tables,
+    const T* __restrict__ q, long q_tok_stride, const void* __restrict__ cache_v, const int* __restrict__ block_tables,
     int bt_stride, const int* __restrict__ seq_lens, const int* __restrict__ qsl, const int* __restrict__ items,
     const int* __restrict__ n_items, T* __restrict__ out, long out_tok_stride, float* __restrict__ part_o,
-    float* __restrict__ part_lse, int hq, int hk, float scale_log2, int window, int num_splits, int total_rows) {
+    float* __restrict__ part_lse, int hq, int hk, float scale_log2, int window, int num_splits, float v_scale) {
   if ((int)blockIdx.x >= *n_items) return;
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  constexpr int TILE = PAGE * HD * 2;            // bytes of one K (or V) page tile
+  constexpr int TILE = PAGE * HD * 2;            // bytes of one K (or V) page tile as the MMAs read it
+  constexpr int SLOT = KV8 ? PAGE * HD : TILE;   // bytes of one K (or V) page as staged by cp.async
+  const T* cache = reinterpret_cast<const T*>(cache_v);
+  const uint8_t* cache8 = reinterpret_cast<const uint8_t*>(cache_v);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seq = items[blockIdx.x], kvh = blockIdx.y, split = blockIdx.z;
   const int ctx = seq_lens[seq], tok0 = qsl[seq], q_len = qsl[seq + 1] - tok0;
@@ -219,7 +268,11 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
   RowState<HD> st;
   st.init();
 
-  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem_raw) + warp * (NSTAGE * 2 * TILE);
+  // per warp: NSTAGE staging slots (K and V) and, for fp8 caches, one widened tile pair
+  constexpr int WARP_BYTES = NSTAGE * 2 * SLOT + (KV8 ? 2 * TILE : 0);
+  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem_raw) + warp * WARP_BYTES;
+  const uint8_t* sbase_gen = smem_raw + warp * WARP_BYTES;
+  const uint32_t wide = sbase + NSTAGE * 2 * SLOT;
   const int* bt = block_tables + (long)seq * bt_stride;
   const long head_off = (long)kvh * PAGE * HD;
   const long blk_stride = 2L * hk * PAGE * HD;
@@ -236,9 +289,14 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
   auto issue = [&](int it) {
     if (it < n_mine) {
       int blk = __shfl_sync(0xffffffffu, bt_reg, it & 31);
-      const T* kg = cache + (long)blk * blk_stride + head_off;
-      uint32_t sb = sbase + (it % NSTAGE) * 2 * TILE;
-      load_page_warp<T, HD>(sb, sb + TILE, kg, kg + v_off, lane);
+      uint32_t sb = sbase + (it % NSTAGE) * 2 * SLOT;
+      if constexpr (KV8) {
+        const uint8_t* kg = cache8 + (long)blk * blk_stride + head_off;
+        load_page_warp_fp8<HD>(sb, sb + SLOT, kg, kg + v_off, lane);
+      } else {
+        const T* kg = cache + (long)blk * blk_stride + head_off;
+        load_page_warp<T, HD>(sb, sb + SLOT, kg, kg + v_off, lane);
+      }
     }
     cp_async_commit();
   };
@@ -247,8 +305,16 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
   for (int it = 0; it < n_mine; ++it) {
     cp_async_wait<NSTAGE - 2>();
     __syncwarp();
-    uint32_t sb = sbase + (it % NSTAGE) * 2 * TILE;
-    process_page<T, HD>(st, qf, sb, sb + TILE, (my_first + it * 4) * PAGE, limit, lower, scale_log2, lane);
+    uint32_t sb = sbase + (it % NSTAGE) * 2 * SLOT;
+    if constexpr (KV8) {
+      const uint8_t* raw = sbase_gen + (it % NSTAGE) * 2 * SLOT;
+      widen_page<T, HD>(raw, wide, lane);
+      widen_page<T, HD>(raw + SLOT, wide + TILE, lane);
+      __syncwarp();
+      process_page<T, HD>(st, qf, wide, wide + TILE, (my_first + it * 4) * PAGE, limit, lower, scale_log2, lane);
+    } else {
+      process_page<T, HD>(st, qf, sb, sb + TILE, (my_first + it * 4) * PAGE, limit, lower, scale_log2, lane);
+    }
     __syncwarp();
     int nxt = it + NSTAGE - 1;
     if ((nxt & 31) == 0) refill(nxt);
@@ -291,7 +357,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(
         acc += sm_o[(w * 16 + row) * HD + d] * sc;
       }
     }
-    float val = L > 0.f ? acc / L : 0.f;
+    float val = (L > 0.f ? acc / L : 0.f) * v_scale;
     int qp = row / group, head = kvh * group + row % group;
     long tok = tok0 + qp;
     if (num_splits == 1) {
@@ -338,17 +404,21 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict
 
 // ------------------------------------------------------------------ prefill
 // work[2*i] = sequence, work[2*i+1] = query tile.  64 rows per CTA = 64/group query positions.
-template <typename T, int HD>
+template <typename T, int HD, bool KV8>
 __global__ void __launch_bounds__(128) attn_prefill_kernel(
-    const T* __restrict__ q, long q_tok_stride, const T* __restrict__ cache, const int* __restrict__ block_tables,
+    const T* __restrict__ q, long q_tok_stride, const void* __restrict__ cache_v, const int* __restrict__ block_tables,
     int bt_stride, const int* __restrict__ seq_lens, const int* __restrict__ qsl, const int* __restrict__ work,
     const int* __restrict__ n_work, T* __restrict__ out, long out_tok_stride, int hq, int hk, float scale_log2,
-    int window) {
+    int window, float v_scale) {
+  const T* cache = reinterpret_cast<const T*>(cache_v);
+  const uint8_t* cache8 = reinterpret_cast<const uint8_t*>(cache_v);
   if ((int)blockIdx.x >= *n_work) return;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   constexpr int TILE = PAGE * HD * 2;
   constexpr int KT = 4;                           // pages per kv tile
-  constexpr int STAGE = KT * 2 * TILE;
+  constexpr int SLOT = KV8 ? PAGE * HD : TILE;    // staged bytes per K (or V) page
+  constexpr int STAGE = KT * 2 * SLOT;
+  const uint32_t wide = (uint32_t)__cvta_generic_to_shared(smem_raw) + 2 * STAGE;   // widened tiles (fp8 caches)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seq = work[2 * blockIdx.x], qt = work[2 * blockIdx.x + 1], kvh = blockIdx.y;
   const int ctx = seq_lens[seq], tok0 = qsl[seq], q_len = qsl[seq + 1] - tok0;
@@ -388,9 +458,14 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
       int p = p_begin + t * KT + warp;              // warp w loads page w of the tile
       if (p < p_end) {
         int blk = bt[p];
-        const T* kg = cache + (long)blk * blk_stride + head_off;
-        uint32_t sb = sbase + (t & 1) * STAGE + warp * 2 * TILE;
-        load_page_warp<T, HD>(sb, sb + TILE, kg, kg + v_off, lane);
+        uint32_t sb = sbase + (t & 1) * STAGE + warp * 2 * SLOT;
+        if constexpr (KV8) {
+          const uint8_t* kg = cache8 + (long)blk * blk_stride + head_off;
+          load_page_warp_fp8<HD>(sb, sb + SLOT, kg, kg + v_off, lane);
+        } else {
+          const T* kg = cache + (long)blk * blk_stride + head_off;
+          load_page_warp<T, HD>(sb, sb + SLOT, kg, kg + v_off, lane);
+        }
       }
     }
     cp_async_commit();
@@ -399,12 +474,21 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
   for (int t = 0; t < n_tiles; ++t) {
     issue(t + 1);
     cp_async_wait<1>();
+    if constexpr (KV8) {
+      // each warp widens the page it loaded; the barrier below publishes all four
+      __syncwarp();
+      if (p_begin + t * KT + warp < p_end) {
+        const uint8_t* raw = smem_raw + (t & 1) * STAGE + warp * 2 * SLOT;
+        widen_page<T, HD>(raw, wide + warp * 2 * TILE, lane);
+        widen_page<T, HD>(raw + SLOT, wide + warp * 2 * TILE + TILE, lane);
+      }
+    }
     __syncthreads();
 #pragma unroll
     for (int pg = 0; pg < KT; ++pg) {
       int p = p_begin + t * KT + pg;
       if (p < p_end && p * PAGE <= warp_last) {
-        uint32_t sb = sbase + (t & 1) * STAGE + pg * 2 * TILE;
+        uint32_t sb = KV8 ? wide + pg * 2 * TILE : sbase + (t & 1) * STAGE + pg * 2 * TILE;
         process_page<T, HD>(st, qf, sb, sb + TILE, p * PAGE, limit, lower, scale_log2, lane);
       }
     }
@@ -420,7 +504,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
     int qp = qp0 + rrow / group;
     if (qp >= q_len) continue;
     int head = kvh * group + rrow % group;
-    float inv = l > 0.f ? 1.f / l : 0.f;
+    float inv = (l > 0.f ? 1.f / l : 0.f) * v_scale;
     T* dst = out + (long)(tok0 + qp) * out_tok_stride + (long)head * HD + ((lane & 3) << 1);
 #pragma unroll
     for (int nt = 0; nt < HD / 8; ++nt)
@@ -428,19 +512,21 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
   }
 }
 
-template <typename T, int HD>
-int launch_attention(const T* q, long q_tok_stride, const T* cache, const int* bt, int bt_stride, const int* seq_lens,
+template <typename T, int HD, bool KV8>
+int launch_attention(const T* q, long q_tok_stride, const void* cache, const int* bt, int bt_stride, const int* seq_lens,
                      const int* qsl, const int* dec_items, const int* n_dec, int max_dec, const int* pre_work,
                      const int* n_pre, int max_pre, T* out, long out_tok_stride, float* part_o, float* part_lse,
-                     int hq, int hk, float scale, int window, int num_splits, int total_rows, cudaStream_t s) {
+                     int hq, int hk, float scale, int window, int num_splits, float k_scale, float v_scale,
+                     cudaStream_t s) {
   constexpr int NSTAGE = 3;
   constexpr int TILE = PAGE * HD * 2;
-  const float scale_log2 = scale * 1.4426950408889634f;
+  constexpr int SLOT = KV8 ? PAGE * HD : TILE;
+  const float scale_log2 = scale * k_scale * 1.4426950408889634f;
   if (max_dec > 0) {
-    int smem = 4 * NSTAGE * 2 * TILE;
+    int smem = 4 * (NSTAGE * 2 * SLOT + (KV8 ? 2 * TILE : 0));
     int need_merge = 4 * 16 * HD * 4 + 512;
     if (smem < need_merge) smem = need_merge;
-    auto kern = attn_decode_kernel<T, HD, NSTAGE>;
+    auto kern = attn_decode_kernel<T, HD, NSTAGE, KV8>;
     static bool attr_done = false;
     if (!attr_done) {
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -448,14 +534,14 @@ int launch_attention(const T* q, long q_tok_stride, const T* cache, const int* b
     }
     dim3 grid(max_dec, hk, num_splits);
     kern<<<grid, 128, smem, s>>>(q, q_tok_stride, cache, bt, bt_stride, seq_lens, qsl, dec_items, n_dec, out,
-                                 out_tok_stride, part_o, part_lse, hq, hk, scale_log2, window, num_splits, total_rows);
+                                 out_tok_stride, part_o, part_lse, hq, hk, scale_log2, window, num_splits, v_scale);
     if (num_splits > 1)
       attn_merge_kernel<T, HD><<<dim3(max_dec, hk), 128, 0, s>>>(part_o, part_lse, dec_items, n_dec, qsl, out,
                                                                  out_tok_stride, hq, hk, num_splits);
   }
   if (max_pre > 0) {
-    int smem = 2 * 4 * 2 * TILE;
-    auto kern = attn_prefill_kernel<T, HD>;
+    int smem = 2 * 4 * 2 * SLOT + (KV8 ? 4 * 2 * TILE : 0);
+    auto kern = attn_prefill_kernel<T, HD, KV8>;
     static bool attr_done = false;
     if (!attr_done) {
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -463,7 +549,7 @@ int launch_attention(const T* q, long q_tok_stride, const T* cache, const int* b
     }
     dim3 grid(max_pre, hk);
     kern<<<grid, 128, smem, s>>>(q, q_tok_stride, cache, bt, bt_stride, seq_lens, qsl, pre_work, n_pre, out,
-                                 out_tok_stride, hq, hk, scale_log2, window);
+                                 out_tok_stride, hq, hk, scale_log2, window, v_scale);
   }
   return check_launch();
 }
@@ -474,24 +560,39 @@ using namespace sonar;
 
 // counts[0] = number of decode items, counts[1] = number of prefill work entries (device memory, so a
 // captured graph can be replayed with different batch compositions); max_* bound the grids.
+// cache_dtype: the query dtype, or fp8 e4m3 with per-tensor k_scale / v_scale.
+SONAR_API int sonar_paged_attention_ex(const void* q, long q_tok_stride, const void* cache, const int* block_tables,
+                                       int bt_stride, const int* seq_lens, const int* qsl, const int* dec_items,
+                                       int max_dec, const int* pre_work, int max_pre, const int* counts, void* out,
+                                       long out_tok_stride, float* part_o, float* part_lse, int hq, int hk,
+                                       int head_dim, int block_size, float scale, int window, int num_splits,
+                                       int dtype, int cache_dtype, float k_scale, float v_scale, cudaStream_t s) {
+  if (block_size != PAGE || hq % hk || (64 % (hq / hk)) || hq / hk > 16) return SONAR_BAD_ARG;
+  if (num_splits < 1 || (num_splits > 1 && (!part_o || !part_lse))) return SONAR_BAD_ARG;
+  if (q_tok_stride % 2 || out_tok_stride % 2) return SONAR_BAD_ARG;
+  const bool kv8 = cache_dtype == SONAR_FP8E4M3;
+  if (!kv8 && cache_dtype != dtype) return SONAR_BAD_ARG;
+#define SONAR_ATTN_CALL(HD, KV8)                                                                                   \
+  return launch_attention<T, HD, KV8>((const T*)q, q_tok_stride, cache, block_tables, bt_stride, seq_lens, qsl,    \
+                                      dec_items, counts, max_dec, pre_work, counts + 1, max_pre, (T*)out,          \
+                                      out_tok_stride, part_o, part_lse, hq, hk, scale, window, num_splits,         \
+                                      kv8 ? k_scale : 1.f, kv8 ? v_scale : 1.f, s)
+  SONAR_DISPATCH_HALF(dtype, T, {
+    if (head_dim == 128) { if (kv8) { SONAR_ATTN_CALL(128, true); } else { SONAR_ATTN_CALL(128, false); } }
+    if (head_dim == 64) { if (kv8) { SONAR_ATTN_CALL(64, true); } else { SONAR_ATTN_CALL(64, false); } }
+    return SONAR_BAD_ARG;
+  });
+#undef SONAR_ATTN_CALL
+}
+
 SONAR_API int sonar_paged_attention(const void* q, long q_tok_stride, const void* cache, const int* block_tables,
                                     int bt_stride, const int* seq_lens, const int* qsl, const int* dec_items,
                                     int max_dec, const int* pre_work, int max_pre, const int* counts, void* out,
                                     long out_tok_stride, float* part_o, float* part_lse, int hq, int hk, int head_dim,
                                     int block_size, float scale, int window, int num_splits, int total_rows, int dtype,
                                     cudaStream_t s) {
-  if (block_size != PAGE || hq % hk || (64 % (hq / hk)) || hq / hk > 16) return SONAR_BAD_ARG;
-  if (num_splits < 1 || (num_splits > 1 && (!part_o || !part_lse))) return SONAR_BAD_ARG;
-  if (q_tok_stride % 2 || out_tok_stride % 2) return SONAR_BAD_ARG;
-  SONAR_DISPATCH_HALF(dtype, T, {
-    if (head_dim == 128)
-      return launch_attention<T, 128>((const T*)q, q_tok_stride, (const T*)cache, block_tables, bt_stride, seq_lens, qsl,
-                                      dec_items, counts, max_dec, pre_work, counts + 1, max_pre, (T*)out, out_tok_stride,
-                                      part_o, part_lse, hq, hk, scale, window, num_splits, total_rows, s);
-    if (head_dim == 64)
-      return launch_attention<T, 64>((const T*)q, q_tok_stride, (const T*)cache, block_tables, bt_stride, seq_lens, qsl,
-                                     dec_items, counts, max_dec, pre_work, counts + 1, max_pre, (T*)out, out_tok_stride,
-                                     part_o, part_lse, hq, hk, scale, window, num_splits, total_rows, s);
-    return SONAR_BAD_ARG;
-  });
+  (void)total_rows;
+  return sonar_paged_attention_ex(q, q_tok_stride, cache, block_tables, bt_stride, seq_lens, qsl, dec_items, max_dec,
+                                  pre_work, max_pre, counts, out, out_tok_stride, part_o, part_lse, hq, hk, head_dim,
+                                  block_size, scale, window, num_splits, dtype, dtype, 1.f, 1.f, s);
 }

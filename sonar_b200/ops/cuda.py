@@ -45,6 +45,9 @@ _rope = _sig("sonar_rope_and_cache", c_void_p, c_long, c_void_p, c_void_p, c_int
 _attn = _sig("sonar_paged_attention", c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
              c_int, c_void_p, c_int, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
              c_float, c_int, c_int, c_int, c_int, c_void_p)
+_attn_ex = _sig("sonar_paged_attention_ex", c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                c_int, c_void_p, c_int, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                c_float, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p)
 _gemm = _sig("sonar_gemm", c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_long,
              c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p)
 _gemm_tp = _sig("sonar_gemm_tp", c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_long,
@@ -248,19 +251,20 @@ def paged_attention(q, kv_cache, meta, scale, sliding_window=None, k_scale=1.0, 
     """q: [T, Hq, D] view with unit inner stride and head stride D (e.g. a slice of packed qkv)."""
     t, hq, d = q.shape
     assert q.stride(2) == 1 and q.stride(1) == d
-    if kv_cache.dtype != q.dtype:
-        raise NotImplementedError("fp8 KV cache attention kernel is not built yet")
+    if kv_cache.dtype != q.dtype and kv_cache.dtype != torch.float8_e4m3fn:
+        raise ValueError(f"KV cache dtype {kv_cache.dtype} does not match the query dtype {q.dtype}")
     hk = kv_cache.shape[2]
     if meta.work is None:
         build_attention_work(meta, None, hq // hk, hk)
     w = meta.work
     if out is None:
         out = torch.empty((t, hq * d), dtype=q.dtype, device=q.device)
-    _check(_attn(q.data_ptr(), q.stride(0), kv_cache.data_ptr(), meta.block_tables.data_ptr(),
-                 meta.block_tables.stride(0), meta.seq_lens.data_ptr(), meta.query_start_loc.data_ptr(),
-                 w.dec_items.data_ptr(), w.n_dec, w.pre_work.data_ptr(), w.n_pre, w.counts.data_ptr(),
-                 out.data_ptr(), out.stride(0), _ptr(w.part_o), _ptr(w.part_lse), hq, hk, d, kv_cache.shape[3],
-                 scale, sliding_window or 0, w.num_splits, 0, _DT[q.dtype], _stream()), "paged_attention")
+    _check(_attn_ex(q.data_ptr(), q.stride(0), kv_cache.data_ptr(), meta.block_tables.data_ptr(),
+                    meta.block_tables.stride(0), meta.seq_lens.data_ptr(), meta.query_start_loc.data_ptr(),
+                    w.dec_items.data_ptr(), w.n_dec, w.pre_work.data_ptr(), w.n_pre, w.counts.data_ptr(),
+                    out.data_ptr(), out.stride(0), _ptr(w.part_o), _ptr(w.part_lse), hq, hk, d, kv_cache.shape[3],
+                    scale, sliding_window or 0, w.num_splits, _DT[q.dtype], _DT[kv_cache.dtype], k_scale, v_scale,
+                    _stream()), "paged_attention")
     return out
 
 

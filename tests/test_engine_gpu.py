@@ -92,3 +92,25 @@ def test_moe_model_matches_torch_path():
         a = torch.tensor([g.prompt_logprobs[i][ids[i]].logprob for i in range(1, len(ids))])
         b = torch.tensor([w.prompt_logprobs[i][ids[i]].logprob for i in range(1, len(ids))])
         assert (a - b).abs().max() < 0.15, (a - b).abs().max()
+
+
+def test_fp8_weights_and_fp8_kv_cache_match_torch_path():
+    """Block-scaled fp8 linear layers + fp8 KV cache through the engine."""
+    from sonar_b200 import LLM, SamplingParams, ops
+    eng = LLM("tiny-llama-128", dtype="bfloat16", quantization="fp8", kv_cache_dtype="fp8", max_model_len=512,
+              max_num_seqs=8, max_num_batched_tokens=128, num_gpu_blocks_override=512, skip_tokenizer_init=True)
+    sp = SamplingParams(temperature=0, max_tokens=3, prompt_logprobs=0, ignore_eos=True, detokenize=False)
+    prompts = [{"prompt_token_ids": p} for p in _prompts(4, seed=8)]
+    got = eng.generate(prompts, sp)
+    ops._FORCE_TORCH = True
+    try:
+        eng.reset_prefix_cache()
+        want = eng.generate(prompts, sp)
+    finally:
+        ops._FORCE_TORCH = False
+    eng.shutdown()
+    for g, w, p in zip(got, want, prompts):
+        ids = p["prompt_token_ids"]
+        a = torch.tensor([g.prompt_logprobs[i][ids[i]].logprob for i in range(1, len(ids))])
+        b = torch.tensor([w.prompt_logprobs[i][ids[i]].logprob for i in range(1, len(ids))])
+        assert (a - b).abs().max() < 0.2, (a - b).abs().max()

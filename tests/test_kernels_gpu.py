@@ -291,3 +291,34 @@ def test_gemm_fp8_block(cu, m, n, k):
     _close(got, want, 2e-2, 2e-2)
     exact = x.float() @ w.float().t()                      # and it approximates the unquantised product
     assert (got.float() - exact).norm() / exact.norm() < 0.06
+
+
+@pytest.mark.parametrize("q_lens,ctx_lens", [([1, 1, 1], [17, 300, 1025]), ([33, 1, 128], [33, 500, 400]), ([1], [5000])])
+def test_paged_attention_fp8_kv_cache(cu, q_lens, ctx_lens):
+    q, cache, meta = _make_attn_case(q_lens, ctx_lens, 8, 2, 128, seed=6)
+    k_scale, v_scale = 0.02, 0.015
+    c8 = torch.empty_like(cache, dtype=torch.float8_e4m3fn)
+    c8[:, 0] = (cache[:, 0].float() / k_scale).clamp(-448, 448).to(torch.float8_e4m3fn)
+    c8[:, 1] = (cache[:, 1].float() / v_scale).clamp(-448, 448).to(torch.float8_e4m3fn)
+    scale = 128 ** -0.5
+    want = ref.paged_attention(q.float(), c8, meta.block_tables, meta.seq_lens, meta.query_start_loc, scale,
+                               k_scale=k_scale, v_scale=v_scale)
+    got = cu.paged_attention(q, c8, meta, scale, k_scale=k_scale, v_scale=v_scale)
+    _close(got.view(-1, 8, 128), want, 2e-2, 2e-2)
+
+
+def test_rope_and_cache_fp8(cu):
+    torch.manual_seed(7)
+    t, hq, hk, d = 20, 4, 2, 128
+    qkv = torch.randn(t, (hq + 2 * hk) * d, device=DEV, dtype=torch.bfloat16)
+    pos = torch.arange(t, device=DEV, dtype=torch.int64)
+    cs = ref.build_cos_sin_cache(d, 64, 1e4, None, DEV)
+    slots = torch.arange(t, device=DEV, dtype=torch.int32) + 16
+    cache_ref = torch.zeros(4, 2, hk, 16, d, device=DEV, dtype=torch.float8_e4m3fn)
+    cache = cache_ref.clone()
+    q, k, v = qkv.float().split([hq * d, hk * d, hk * d], dim=-1)
+    _, k_ref = ref.rope(q, k, pos, cs, d)
+    ref.reshape_and_cache(k_ref.reshape(t, hk, d), v.reshape(t, hk, d), cache_ref, slots, 0.05, 0.04)
+    cu.rope_and_cache(qkv.clone(), pos, cs, cache, slots, hq, hk, d, None, None, 1e-6, 0.05, 0.04)
+    assert (cache.float() - cache_ref.float()).abs().max() <= 32    # at most one e4m3 step (bf16 rounding of k before quantising)
+    assert ((cache.float() - cache_ref.float()).abs() > 0).float().mean() < 0.05

@@ -1,0 +1,291 @@
+// Multi-head latent attention (absorbed form) over the paged latent cache, dense or sparse.
+//
+// Cache row per token: [kv_c (R = 512) | k_pe (P = 64) | optional extra (indexer key)], row_stride elements,
+// [blocks, block_size, row_stride].  All heads share the keys (MQA): scores = q_lat·kv_c + q_pe·k_pe, output =
+// softmax · kv_c (latent, R wide).  One CTA = (query token, group of 16 heads, kv split); its 4 warps share
+// the staged key rows: every warp computes the 16×16 score tile of a 16-key chunk (mma.sync m16n8k16 over the
+// 576-wide rows) and accumulates P·V for its own quarter of the latent dims, so no cross-warp reduction is
+// needed.  The key list of a token is either 0..pos (dense, causal) or its top-k index list (DeepSeek sparse
+// attention: −1 entries are skipped), gathered row by row with cp.async.
+//
+// Behavioural parity: reference layers/attention/mla_attention.py:2711 (forward_mqa) and the sparse MLA
+// backends (v1/attention/backends/mla/flashmla_sparse.py); cache write: cache_kernels.cu:403 (concat_and_cache_mla).
+#include "common.cuh"
+
+namespace sonar {
+namespace {
+
+constexpr int R = 512, P = 64, D = R + P;     // latent, rope, row width used by attention
+constexpr int CH = 16;                        // keys per chunk
+constexpr int ROW_BYTES = D * 2;              // 1152
+constexpr int CPR = ROW_BYTES / 16;           // 72 sixteen-byte chunks per row
+constexpr int TILE_BYTES = CH * ROW_BYTES;    // 18432
+constexpr int NSTAGE = 2;
+
+__device__ __forceinline__ void cp_async16(uint32_t smem, const void* g) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem), "l"(g));
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+__device__ __forceinline__ void ldsm4(uint32_t a, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void ldsm4t(uint32_t a, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf2(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// swizzled offset of 16-byte chunk `ch` in row `r` of a [rows][1152 B] tile
+__device__ __forceinline__ uint32_t swz(int r, int ch) { return r * ROW_BYTES + ((ch ^ (r & 7)) << 4); }
+
+struct MlaParams {
+  const __nv_bfloat16* q_lat; long ql_tok, ql_head;   // [T, H, R]
+  const __nv_bfloat16* q_pe; long qp_tok, qp_head;    // [T, H, P]
+  const __nv_bfloat16* cache; long row_stride; int block_size;
+  const int* block_tables; int bt_stride;
+  const int* token_seq;          // [T] sequence of each query token
+  const long* positions;         // [T] position of each query token (keys 0..pos are visible)
+  const int* topk; int topk_n;   // [T, topk_n] selected key positions (−1 = none) or null
+  __nv_bfloat16* out; long out_tok, out_head;         // [T, H, R]
+  float* part_o; float* part_lse;                     // split partials: [(split*T + t)*H + h][R], [...]
+  int T, H, num_splits;
+  float scale_log2;
+};
+
+__global__ void __launch_bounds__(128) mla_attn_kernel(const MlaParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x, h0 = blockIdx.y * 16, split = blockIdx.z;
+  const uint32_t s_q = (uint32_t)__cvta_generic_to_shared(smem);
+  const uint32_t s_k = s_q + TILE_BYTES;
+  int* s_keys = reinterpret_cast<int*>(smem + TILE_BYTES * (1 + NSTAGE));   // [NSTAGE][CH] key position per slot
+
+  // ---- stage the 16 query rows (heads h0..h0+15; rows past H are zero)
+  for (int c = threadIdx.x; c < CH * CPR; c += 128) {
+    const int r = c / CPR, ch = c % CPR;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (h0 + r < p.H) {
+      if (ch < R / 8) v = *reinterpret_cast<const uint4*>(p.q_lat + (long)t * p.ql_tok + (long)(h0 + r) * p.ql_head + ch * 8);
+      else v = *reinterpret_cast<const uint4*>(p.q_pe + (long)t * p.qp_tok + (long)(h0 + r) * p.qp_head + (ch - R / 8) * 8);
+    }
+    *reinterpret_cast<uint4*>(smem + swz(r, ch)) = v;
+  }
+  const int seq = p.token_seq[t];
+  const int pos = (int)p.positions[t];
+  const int n_keys = p.topk ? p.topk_n : pos + 1;
+  const int n_chunks = (n_keys + CH - 1) / CH;
+  const int per_split = (n_chunks + p.num_splits - 1) / p.num_splits;
+  const int c_begin = split * per_split, c_end = min(n_chunks, c_begin + per_split);
+  const int* bt = p.block_tables + (long)seq * p.bt_stride;
+  const int* tk = p.topk ? p.topk + (long)t * p.topk_n : nullptr;
+
+  auto issue = [&](int c) {
+    if (c < c_end) {
+      const int stage = (c - c_begin) % NSTAGE;
+      const uint32_t dst = s_k + stage * TILE_BYTES;
+      for (int i = threadIdx.x; i < CH * CPR; i += 128) {
+        const int r = i / CPR, ch = i % CPR;
+        int key = c * CH + r;
+        if (tk) key = key < p.topk_n ? tk[key] : -1;
+        else if (key > pos) key = -1;
+        if (ch == 0) s_keys[stage * CH + r] = key;
+        if (key >= 0) {
+          const long slot = (long)bt[key / p.block_size] * p.block_size + key % p.block_size;
+          cp_async16(dst + swz(r, ch), p.cache + slot * p.row_stride + ch * 8);
+        } else {
+          *reinterpret_cast<uint4*>(smem + TILE_BYTES + stage * TILE_BYTES + swz(r, ch)) = make_uint4(0, 0, 0, 0);
+        }
+      }
+    }
+    cp_commit();
+  };
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const int j = lane >> 3, r8 = lane & 7;
+  issue(c_begin);
+  __syncthreads();   // Q tile visible
+  for (int c = c_begin; c < c_end; ++c) {
+    issue(c + 1);
+    cp_wait<1>();
+    __syncthreads();
+    const int stage = (c - c_begin) % NSTAGE;
+    const uint32_t kt = s_k + stage * TILE_BYTES;
+    // ---- S = Q K^T over the 576-wide rows (every warp computes the full 16×16 tile)
+    float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+#pragma unroll 4
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t a[4], b0, b1, b2, b3;
+      {  // A fragment: rows = heads; matrices (rows 0-7 | 8-15) × (k lo | k hi)
+        const int row = ((j & 1) << 3) + r8, ch = ks * 2 + (j >> 1);
+        ldsm4(s_q + swz(row, ch), a[0], a[1], a[2], a[3]);
+      }
+      {
+        const int key = ((j >> 1) << 3) + r8, ch = ks * 2 + (j & 1);
+        ldsm4(kt + swz(key, ch), b0, b1, b2, b3);
+      }
+      mma_bf16(s[0], a, b0, b1);
+      mma_bf16(s[1], a, b2, b3);
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int col = nt * 8 + ((lane & 3) << 1) + (e & 1);
+        const bool ok = s_keys[stage * CH + col] >= 0;
+        const float v = ok ? s[nt][e] * p.scale_log2 : -INFINITY;
+        s[nt][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    float alpha[2];
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
+      mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
+      const float m_new = fmaxf(m[rr], mx[rr]);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      alpha[rr] = exp2f(m[rr] - m_use);
+      m[rr] = m_new;
+      l[rr] *= alpha[rr];
+      mx[rr] = m_use;
+    }
+    uint32_t pf[4];
+    {
+      float pr[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          pr[nt][e] = exp2f(s[nt][e] - mx[e >> 1]);
+          l[e >> 1] += pr[nt][e];
+        }
+      pf[0] = pack_bf2(pr[0][0], pr[0][1]); pf[1] = pack_bf2(pr[0][2], pr[0][3]);
+      pf[2] = pack_bf2(pr[1][0], pr[1][1]); pf[3] = pack_bf2(pr[1][2], pr[1][3]);
+    }
+    // ---- O[:, warp's 128 latent dims] += P · V
+    {
+      const int key = ((j & 1) << 3) + r8;
+#pragma unroll
+      for (int np = 0; np < 8; ++np) {
+        const int ch = warp * 16 + np * 2 + (j >> 1);
+        uint32_t b0, b1, b2, b3;
+        ldsm4t(kt + swz(key, ch), b0, b1, b2, b3);
+        float* o0 = o[np * 2];
+        float* o1 = o[np * 2 + 1];
+        o0[0] *= alpha[0]; o0[1] *= alpha[0]; o0[2] *= alpha[1]; o0[3] *= alpha[1];
+        o1[0] *= alpha[0]; o1[1] *= alpha[0]; o1[2] *= alpha[1]; o1[3] *= alpha[1];
+        mma_bf16(o0, pf, b0, b1);
+        mma_bf16(o1, pf, b2, b3);
+      }
+    }
+    __syncthreads();
+  }
+  cp_wait<0>();
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    float ls = l[hh];
+    ls += __shfl_xor_sync(0xffffffffu, ls, 1);
+    ls += __shfl_xor_sync(0xffffffffu, ls, 2);
+    const int head = h0 + (lane >> 2) + hh * 8;
+    if (head >= p.H) continue;
+    const float inv = ls > 0.f ? 1.f / ls : 0.f;
+    const int d0 = warp * 128 + ((lane & 3) << 1);
+    if (p.num_splits == 1) {
+      __nv_bfloat16* dst = p.out + (long)t * p.out_tok + (long)head * p.out_head + d0;
+#pragma unroll
+      for (int nt = 0; nt < 16; ++nt)
+        *reinterpret_cast<uint32_t*>(dst + nt * 8) = pack_bf2(o[nt][hh * 2] * inv, o[nt][hh * 2 + 1] * inv);
+    } else {
+      const long prow = ((long)split * p.T + t) * p.H + head;
+      float* dst = p.part_o + prow * R + d0;
+#pragma unroll
+      for (int nt = 0; nt < 16; ++nt) { dst[nt * 8] = o[nt][hh * 2] * inv; dst[nt * 8 + 1] = o[nt][hh * 2 + 1] * inv; }
+      if (warp == 0 && (lane & 3) == 0) p.part_lse[prow] = ls > 0.f ? m[hh] + log2f(ls) : -INFINITY;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(128) mla_merge_kernel(const float* part_o, const float* part_lse, __nv_bfloat16* out,
+                                                        long out_tok, long out_head, int T, int H, int num_splits) {
+  const int t = blockIdx.x, h = blockIdx.y;
+  const long row = (long)t * H + h;
+  float M = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_lse[(long)s * T * H + row]);
+  for (int d = threadIdx.x; d < R; d += 128) {
+    float W = 0.f, acc = 0.f;
+    if (M != -INFINITY)
+      for (int s = 0; s < num_splits; ++s) {
+        const float w = exp2f(part_lse[(long)s * T * H + row] - M);
+        W += w;
+        acc += w * part_o[((long)s * T * H + row) * R + d];
+      }
+    out[(long)t * out_tok + (long)h * out_head + d] = __float2bfloat16_rn(W > 0.f ? acc / W : 0.f);
+  }
+}
+
+// cache[slot, :] = [kv_c | rest] for every token with slot >= 0
+__global__ void __launch_bounds__(128) mla_cache_write_kernel(const __nv_bfloat16* kv_c, long kvc_stride, int r_dim,
+                                                              const __nv_bfloat16* rest, long rest_stride, int rest_dim,
+                                                              __nv_bfloat16* cache, long row_stride, const int* slots) {
+  const int t = blockIdx.x;
+  const int slot = slots[t];
+  if (slot < 0) return;
+  __nv_bfloat16* dst = cache + (long)slot * row_stride;
+  for (int i = threadIdx.x; i < (r_dim + rest_dim) / 8; i += 128) {
+    const int e = i * 8;
+    const uint4 v = e < r_dim ? *reinterpret_cast<const uint4*>(kv_c + (long)t * kvc_stride + e)
+                              : *reinterpret_cast<const uint4*>(rest + (long)t * rest_stride + (e - r_dim));
+    *reinterpret_cast<uint4*>(dst + e) = v;
+  }
+}
+
+}  // namespace
+}  // namespace sonar
+
+using namespace sonar;
+
+SONAR_API int sonar_mla_cache_write(const void* kv_c, long kvc_stride, int r_dim, const void* rest, long rest_stride,
+                                    int rest_dim, void* cache, long row_stride, const int* slots, int T,
+                                    cudaStream_t s) {
+  if (T == 0) return SONAR_OK;
+  if (r_dim % 8 || rest_dim % 8 || row_stride % 8 || kvc_stride % 8 || rest_stride % 8) return SONAR_BAD_ARG;
+  mla_cache_write_kernel<<<T, 128, 0, s>>>((const __nv_bfloat16*)kv_c, kvc_stride, r_dim, (const __nv_bfloat16*)rest,
+                                           rest_stride, rest_dim, (__nv_bfloat16*)cache, row_stride, slots);
+  return check_launch();
+}
+
+// kv_lora_rank must be 512 and the rope width 64 (the DeepSeek V2/V3 geometry this kernel is built for).
+SONAR_API int sonar_mla_attention(const void* q_lat, long ql_tok, long ql_head, const void* q_pe, long qp_tok,
+                                  long qp_head, const void* cache, long row_stride, int block_size,
+                                  const int* block_tables, int bt_stride, const int* token_seq, const long* positions,
+                                  const int* topk, int topk_n, void* out, long out_tok, long out_head, float* part_o,
+                                  float* part_lse, int T, int H, int kv_lora_rank, int rope_dim, float scale,
+                                  int num_splits, cudaStream_t s) {
+  if (T == 0) return SONAR_OK;
+  if (kv_lora_rank != R || rope_dim != P || row_stride % 8 || ql_head % 8 || qp_head % 8 || ql_tok % 8 || qp_tok % 8)
+    return SONAR_BAD_ARG;
+  if (num_splits < 1 || (num_splits > 1 && (!part_o || !part_lse))) return SONAR_BAD_ARG;
+  MlaParams p{(const __nv_bfloat16*)q_lat, ql_tok, ql_head, (const __nv_bfloat16*)q_pe, qp_tok, qp_head,
+              (const __nv_bfloat16*)cache, row_stride, block_size, block_tables, bt_stride, token_seq, positions,
+              topk, topk_n, (__nv_bfloat16*)out, out_tok, out_head, part_o, part_lse, T, H, num_splits,
+              scale * 1.4426950408889634f};
+  const int smem = TILE_BYTES * (1 + NSTAGE) + NSTAGE * CH * 4;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaFuncSetAttribute(mla_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    attr_done = true;
+  }
+  dim3 grid(T, (H + 15) / 16, num_splits);
+  mla_attn_kernel<<<grid, 128, smem, s>>>(p);
+  if (num_splits > 1) mla_merge_kernel<<<dim3(T, H), 128, 0, s>>>(part_o, part_lse, (__nv_bfloat16*)out, out_tok, out_head, T, H, num_splits);
+  return check_launch();
+}

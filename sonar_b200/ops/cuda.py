@@ -72,6 +72,11 @@ _moe_combine = _sig("sonar_moe_combine", c_void_p, c_void_p, c_void_p, c_int, c_
 _group_quant = _sig("sonar_group_quant_fp8", c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_long, c_int, c_void_p)
 _gemm_fp8 = _sig("sonar_gemm_fp8_block", c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_long, c_void_p, c_int, c_int,
                  c_int, c_long, c_long, c_long, c_int, c_void_p, c_void_p)
+_mla_write = _sig("sonar_mla_cache_write", c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_void_p, c_long, c_void_p,
+                  c_int, c_void_p)
+_mla_attn = _sig("sonar_mla_attention", c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p, c_long, c_int,
+                 c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_long, c_long, c_void_p, c_void_p,
+                 c_int, c_int, c_int, c_int, c_float, c_int, c_void_p)
 _argmax = _sig("sonar_argmax", c_void_p, c_long, c_int, c_int, c_void_p, c_void_p)
 _sample = _sig("sonar_sample", c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                c_long, c_void_p, c_uint, c_void_p, c_void_p)
@@ -469,12 +474,51 @@ def fused_experts(x, w13, w2, topk_w, topk_ids, expert_map=None, combine_to=None
 
 # ---------------------------------------------------------------- MLA (composed until its kernels land)
 def mla_cache_write(kv_c, k_pe, cache, slot_mapping):
-    return ref.mla_cache_write(kv_c, k_pe, cache, slot_mapping)
+    """cache [blocks, block_size, row] ← [kv_c | k_pe(+extras)] per token (bf16, 16-byte aligned rows)."""
+    if cache.dtype != torch.bfloat16 or kv_c.shape[1] % 8 or k_pe.shape[1] % 8 or cache.shape[2] % 8:
+        return ref.mla_cache_write(kv_c, k_pe, cache, slot_mapping)
+    kv_c = kv_c if kv_c.stride(1) == 1 else kv_c.contiguous()
+    k_pe = k_pe if k_pe.stride(1) == 1 else k_pe.contiguous()
+    _check(_mla_write(kv_c.data_ptr(), kv_c.stride(0), kv_c.shape[1], k_pe.data_ptr(), k_pe.stride(0), k_pe.shape[1],
+                      cache.data_ptr(), cache.shape[2], slot_mapping.data_ptr(), kv_c.shape[0], _stream()),
+           "mla_cache_write")
 
 
 def mla_paged_attention(q_nope, q_pe, cache, meta, scale, kv_lora_rank, topk_indices=None, rope_dim=None):
-    return ref.mla_paged_attention(q_nope, q_pe, cache, meta.block_tables, meta.seq_lens, meta.query_start_loc,
-                                   scale, kv_lora_rank, topk_indices, rope_dim)
+    """Absorbed-form MLA over the latent cache; the kernel covers the DeepSeek geometry (latent 512, rope 64,
+    bf16), other shapes use the PyTorch restatement."""
+    t, h, r = q_nope.shape
+    rd = rope_dim if rope_dim is not None else cache.shape[2] - kv_lora_rank
+    if r != 512 or rd != 64 or q_nope.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        return ref.mla_paged_attention(q_nope, q_pe, cache, meta.block_tables, meta.seq_lens, meta.query_start_loc,
+                                       scale, kv_lora_rank, topk_indices, rope_dim)
+    q_nope = q_nope if q_nope.stride(2) == 1 else q_nope.contiguous()
+    q_pe = q_pe if q_pe.stride(2) == 1 else q_pe.contiguous()
+    q_lens = np.asarray(meta.query_lens_cpu, dtype=np.int64)
+    seq_lens = np.asarray(meta.seq_lens_cpu, dtype=np.int64)
+    token_seq = torch.from_numpy(np.repeat(np.arange(len(q_lens), dtype=np.int32), q_lens)).to(q_nope.device)
+    if meta.positions is not None:
+        positions = meta.positions
+    else:
+        pos = np.concatenate([np.arange(c - q, c) for q, c in zip(q_lens, seq_lens)]) if len(q_lens) else np.zeros(0)
+        positions = torch.from_numpy(pos.astype(np.int64)).to(q_nope.device)
+    out = torch.empty((t, h, r), dtype=q_nope.dtype, device=q_nope.device)
+    n_ctas = t * ((h + 15) // 16)
+    n_keys = topk_indices.shape[1] if topk_indices is not None else int(seq_lens.max()) if len(seq_lens) else 1
+    splits = 1
+    if n_ctas < 148:
+        splits = int(max(1, min(-(-296 // n_ctas), 16, n_keys // 256)))
+    part_o = part_lse = None
+    if splits > 1:
+        part_o = torch.empty((splits * t * h, r), dtype=torch.float32, device=q_nope.device)
+        part_lse = torch.empty(splits * t * h, dtype=torch.float32, device=q_nope.device)
+    tk = topk_indices.contiguous() if topk_indices is not None else None
+    _check(_mla_attn(q_nope.data_ptr(), q_nope.stride(0), q_nope.stride(1), q_pe.data_ptr(), q_pe.stride(0),
+                     q_pe.stride(1), cache.data_ptr(), cache.shape[2], cache.shape[1], meta.block_tables.data_ptr(),
+                     meta.block_tables.stride(0), token_seq.data_ptr(), positions.data_ptr(), _ptr(tk),
+                     tk.shape[1] if tk is not None else 0, out.data_ptr(), out.stride(0), out.stride(1), _ptr(part_o),
+                     _ptr(part_lse), t, h, kv_lora_rank, rd, scale, splits, _stream()), "mla_attention")
+    return out
 
 
 # ---------------------------------------------------------------- sampling

@@ -322,3 +322,70 @@ def test_rope_and_cache_fp8(cu):
     cu.rope_and_cache(qkv.clone(), pos, cs, cache, slots, hq, hk, d, None, None, 1e-6, 0.05, 0.04)
     assert (cache.float() - cache_ref.float()).abs().max() <= 32    # at most one e4m3 step (bf16 rounding of k before quantising)
     assert ((cache.float() - cache_ref.float()).abs() > 0).float().mean() < 0.05
+
+
+def _mla_case(q_lens, ctx_lens, h, extra=0, seed=0):
+    torch.manual_seed(seed)
+    bs, r, pdim = 16, 512, 64
+    ns = len(q_lens)
+    need = sum(-(-c // bs) for c in ctx_lens)
+    cache = (torch.randn(need + 3, bs, r + pdim + extra, device=DEV) * 0.3).to(torch.bfloat16)
+    perm = torch.randperm(need + 2)[:need] + 1
+    bt = torch.zeros(ns, max(-(-c // bs) for c in ctx_lens), dtype=torch.int32)
+    off = 0
+    for i, c in enumerate(ctx_lens):
+        nb = -(-c // bs)
+        bt[i, :nb] = perm[off:off + nb].int()
+        off += nb
+    t = sum(q_lens)
+    q_lat = (torch.randn(t, h, r, device=DEV) * 0.3).to(torch.bfloat16)
+    q_pe = (torch.randn(t, h, pdim, device=DEV) * 0.3).to(torch.bfloat16)
+    qsl = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    pos = torch.cat([torch.arange(c - q, c) for q, c in zip(q_lens, ctx_lens)]).to(DEV)
+    meta = AttentionMetadata(num_tokens=t, num_seqs=ns, positions=pos, slot_mapping=None, block_tables=bt.to(DEV),
+                             seq_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), query_start_loc=qsl,
+                             max_query_len=max(q_lens), max_seq_len=max(ctx_lens), query_lens_cpu=q_lens,
+                             seq_lens_cpu=ctx_lens)
+    return q_lat, q_pe, cache, meta
+
+
+@pytest.mark.parametrize("q_lens,ctx_lens,h,extra", [([1, 1], [37, 600], 16, 0), ([5, 1, 40], [5, 130, 300], 24, 128),
+                                                     ([1], [4000], 16, 0)])
+def test_mla_attention_dense(cu, q_lens, ctx_lens, h, extra):
+    q_lat, q_pe, cache, meta = _mla_case(q_lens, ctx_lens, h, extra)
+    scale = 576 ** -0.5
+    want = ref.mla_paged_attention(q_lat.float(), q_pe.float(), cache.float(), meta.block_tables, meta.seq_lens,
+                                   meta.query_start_loc, scale, 512, None, 64)
+    got = cu.mla_paged_attention(q_lat, q_pe, cache, meta, scale, 512, None, 64)
+    _close(got, want, 2e-2, 2e-2)
+
+
+def test_mla_attention_sparse_topk(cu):
+    q_lat, q_pe, cache, meta = _mla_case([1, 3], [500, 900], 16, 128, seed=3)
+    t = q_lat.shape[0]
+    k = 64
+    topk = torch.full((t, k), -1, dtype=torch.int32, device=DEV)
+    pos = meta.positions.tolist()
+    g = torch.Generator().manual_seed(0)
+    for i in range(t):
+        n = min(k - 5, pos[i] + 1)
+        topk[i, :n] = torch.randperm(pos[i] + 1, generator=g)[:n].int().to(DEV)
+    scale = 576 ** -0.5
+    want = ref.mla_paged_attention(q_lat.float(), q_pe.float(), cache.float(), meta.block_tables, meta.seq_lens,
+                                   meta.query_start_loc, scale, 512, topk, 64)
+    got = cu.mla_paged_attention(q_lat, q_pe, cache, meta, scale, 512, topk, 64)
+    _close(got, want, 2e-2, 2e-2)
+
+
+def test_mla_cache_write(cu):
+    torch.manual_seed(4)
+    t = 30
+    kv_c = torch.randn(t, 512, device=DEV, dtype=torch.bfloat16)
+    rest = torch.randn(t, 64 + 128, device=DEV, dtype=torch.bfloat16)
+    slots = torch.randperm(64, device=DEV)[:t].int()
+    slots[3] = -1
+    want = torch.zeros(4, 16, 704, device=DEV, dtype=torch.bfloat16)
+    got = want.clone()
+    ref.mla_cache_write(kv_c, rest, want, slots)
+    cu.mla_cache_write(kv_c, rest, got, slots)
+    assert torch.equal(got, want)

@@ -17,7 +17,7 @@ import time
 from typing import AsyncGenerator
 
 from sonar_b200.config import EngineArgs, EngineConfig
-from sonar_b200.engine.core_client import AsyncMPClient, EngineDeadError
+from sonar_b200.engine.core_client import EngineCoreClient, EngineDeadError
 from sonar_b200.engine.llm_engine import InputProcessor
 from sonar_b200.engine.output_processor import OutputProcessor, ParentRequest
 from sonar_b200.logger import init_logger
@@ -37,7 +37,8 @@ class AsyncLLM:
                                                                                  cfg.model.vocab_size)
         self.input_processor = InputProcessor(cfg, self.tokenizer)
         self.output_processor = OutputProcessor(self.tokenizer, cfg.observability.log_stats)
-        self.core = AsyncMPClient(cfg, executor_class)
+        self.core = EngineCoreClient.make_client(cfg, multiprocess=True, asyncio_mode=True,
+                                                 executor_class=executor_class)
         self.metrics = EngineMetrics(cfg.model.served_model_name or cfg.model.model)
         self._handler: asyncio.Task | None = None
         self._dead: Exception | None = None

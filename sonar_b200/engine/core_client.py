@@ -34,6 +34,8 @@ class EngineCoreClient:
     @staticmethod
     def make_client(cfg: EngineConfig, multiprocess: bool, asyncio_mode: bool, executor_class=None):
         if asyncio_mode:
+            if cfg.parallel.data_parallel_size > 1:
+                return DPLBAsyncClient(cfg, executor_class)
             return AsyncMPClient(cfg, executor_class)
         if multiprocess:
             return SyncMPClient(cfg, executor_class)
@@ -240,3 +242,91 @@ class AsyncMPClient(_MPBase):
         self._futures[uid] = fut
         self._send(b"U", (uid, method, args, kwargs))
         return await fut
+
+
+class DPLBAsyncClient(EngineCoreClient):
+    """Data parallelism at the engine level: ``data_parallel_size`` independent engine cores (each with its
+    own scheduler, KV cache and ``world_size`` GPUs), requests balanced to the replica with the fewest
+    requests in flight.  Outputs of all replicas are merged into one stream; aborts follow the request to
+    its replica; utility calls fan out to every replica.
+
+    Parity: ``DPLBAsyncMPClient`` (``aphrodite/v1/engine/core_client.py:1332``, ``get_core_engine_for_request``
+    :1367) and the coordinator's load accounting (``v1/engine/coordinator.py``).
+    """
+
+    def __init__(self, cfg: EngineConfig, executor_class=None) -> None:
+        import copy
+        self.cfg = cfg
+        self.clients: list[AsyncMPClient] = []
+        for r in range(cfg.parallel.data_parallel_size):
+            c = copy.deepcopy(cfg)
+            c.parallel.data_parallel_rank = r
+            self.clients.append(AsyncMPClient(c, executor_class))
+        self.in_flight = [0] * len(self.clients)
+        self.owner: dict[str, int] = {}
+        self.merged: asyncio.Queue | None = None
+        self._pumps: list[asyncio.Task] = []
+
+    @property
+    def dead(self) -> bool:
+        return any(c.dead for c in self.clients)
+
+    def _ensure(self) -> None:
+        if self.merged is None:
+            self.merged = asyncio.Queue()
+            loop = asyncio.get_running_loop()
+            for i, c in enumerate(self.clients):
+                self._pumps.append(loop.create_task(self._pump(i, c)))
+
+    async def _pump(self, idx: int, client: AsyncMPClient) -> None:
+        try:
+            while True:
+                outs = await client.get_output_async()
+                outs.engine_index = idx
+                for o in outs.outputs:
+                    if o.finish_reason is not None and self.owner.pop(o.request_id, None) is not None:
+                        self.in_flight[idx] -= 1
+                await self.merged.put(outs)
+        except asyncio.CancelledError:
+            raise
+        except Exception as e:  # noqa: BLE001
+            await self.merged.put(e)
+
+    async def add_request_async(self, req: EngineCoreRequest) -> None:
+        self._ensure()
+        idx = req.data_parallel_rank
+        if idx is None:
+            idx = min(range(len(self.clients)), key=lambda i: (self.in_flight[i], i))
+        self.owner[req.request_id] = idx
+        self.in_flight[idx] += 1
+        await self.clients[idx].add_request_async(req)
+
+    async def abort_requests_async(self, ids: list[str]) -> None:
+        by: dict[int, list[str]] = {}
+        for rid in ids:
+            idx = self.owner.pop(rid, None)
+            if idx is not None:
+                self.in_flight[idx] -= 1
+                by.setdefault(idx, []).append(rid)
+        for idx, lst in by.items():
+            await self.clients[idx].abort_requests_async(lst)
+
+    async def get_output_async(self) -> EngineCoreOutputs:
+        self._ensure()
+        item = await self.merged.get()
+        if isinstance(item, Exception):
+            self.merged.put_nowait(item)
+            raise item
+        return item
+
+    async def call_utility_async(self, method: str, *args, **kwargs) -> Any:
+        res = await asyncio.gather(*(c.call_utility_async(method, *args, **kwargs) for c in self.clients))
+        if method in ("reset_prefix_cache",):
+            return all(res)
+        return res if len(res) > 1 else res[0]
+
+    def shutdown(self) -> None:
+        for t in self._pumps:
+            t.cancel()
+        for c in self.clients:
+            c.shutdown()

@@ -103,6 +103,14 @@ class EngineCoreProc:
 
 def run_engine_core(cfg: EngineConfig, input_addr: str, output_addr: str, ready, executor_class=None) -> None:
     signal.signal(signal.SIGINT, signal.SIG_IGN)
+    p = cfg.parallel
+    if p.data_parallel_size > 1 and cfg.device == "cuda":
+        # each data-parallel replica sees only its own slice of the GPUs (set before CUDA initialises here)
+        import os
+        all_dev = os.environ.get("CUDA_VISIBLE_DEVICES")
+        ids = all_dev.split(",") if all_dev else [str(i) for i in range(p.world_size * p.data_parallel_size)]
+        lo = p.data_parallel_rank * p.world_size
+        os.environ["CUDA_VISIBLE_DEVICES"] = ",".join(ids[lo:lo + p.world_size])
     try:
         proc = EngineCoreProc(cfg, input_addr, output_addr, executor_class)
         ready.set()

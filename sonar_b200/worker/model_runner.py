@@ -329,6 +329,20 @@ class ModelRunner:
         self.stats["sample_s"] += time.perf_counter() - t2
         return res
 
+    def apply_remote_output(self, so: SchedulerOutput, out: ModelRunnerOutput) -> None:
+        """Pipeline stages other than the last learn the sampled tokens from the last stage's
+        (broadcast) output, so the next step's inputs can be built everywhere."""
+        if self.pp is None or self.pp.is_last_rank or out is None:
+            return
+        b = self.batch
+        for rid, toks in zip(out.req_ids, out.sampled_token_ids):
+            row = b.index.get(rid)
+            if row is None or not toks:
+                continue
+            nt = int(b.num_tokens[row])
+            b.token_ids[row, nt:nt + len(toks)] = toks
+            b.num_tokens[row] = nt + len(toks)
+
     def _send_intermediate(self, out) -> None:
         h, r = out
         self.pp.send(h.contiguous()).wait()

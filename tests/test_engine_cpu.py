@@ -94,3 +94,28 @@ def test_other_model_families_batched_equals_single(preset):
     single = [eng.generate(p, sp)[0].outputs[0].token_ids for p in prompts]
     eng.shutdown()
     assert batched == single
+
+
+def test_ngram_speculative_decoding_is_lossless():
+    """Greedy output with n-gram drafts equals greedy output without them, and drafts get accepted."""
+    import numpy as np
+
+    from sonar_b200.config import SpeculativeConfig
+    from sonar_b200.sample.spec_decode import NgramProposer
+    prop = NgramProposer(SpeculativeConfig("ngram", 3, prompt_lookup_max=3, prompt_lookup_min=2))
+    assert prop.propose(np.array([1, 2, 3, 4, 9, 1, 2, 3])) == [4, 9, 1]
+    assert prop.propose(np.array([1, 2, 3])) == []
+    common = dict(dtype="float32", max_model_len=512, num_gpu_blocks_override=128, max_num_seqs=4,
+                  max_num_batched_tokens=64, device="cpu")
+    sp = SamplingParams(temperature=0, max_tokens=24, ignore_eos=True)
+    # a repetitive prompt makes the tiny random model loop, which the n-gram proposer predicts
+    prompts = [{"prompt_token_ids": [7, 8, 9, 10] * 6}, {"prompt_token_ids": _prompts(1, seed=11)[0]}]
+    base = LLM("tiny-llama", **common)
+    want = [o.outputs[0].token_ids for o in base.generate(prompts, sp)]
+    base.shutdown()
+    spec = LLM("tiny-llama", speculative_method="ngram", num_speculative_tokens=3, **common)
+    got = [o.outputs[0].token_ids for o in spec.generate(prompts, sp)]
+    stats = spec.llm_engine.get_stats()["scheduler"]
+    spec.shutdown()
+    assert got == want
+    assert stats.spec_num_drafts > 0

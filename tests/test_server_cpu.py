@@ -78,3 +78,40 @@ def test_tokenize_metrics_and_dev_routes(client):
     assert a["type"] == "message" and a["usage"]["output_tokens"] <= 3
     k = client.post("/api/v1/generate", json={"prompt": "hi", "max_length": 3}).json()
     assert "text" in k["results"][0]
+
+
+def test_data_parallel_load_balancing_and_engine_death():
+    """Two engine replicas behind one frontend: requests spread over both; killing one replica surfaces as
+    EngineDeadError instead of a hang."""
+    import asyncio
+    import os
+    import signal
+
+    from sonar_b200 import SamplingParams
+    from sonar_b200.engine.async_llm import AsyncLLM
+    from sonar_b200.engine.core_client import EngineDeadError
+    args = EngineArgs(model="tiny-llama", dtype="float32", max_model_len=128, num_gpu_blocks_override=64,
+                      max_num_seqs=4, max_num_batched_tokens=64, device="cpu", data_parallel_size=2)
+    engine = AsyncLLM.from_engine_args(args)
+
+    async def one(i, n=6):
+        last = None
+        async for out in engine.generate({"prompt_token_ids": [5 + i, 6, 7, 8]},
+                                         SamplingParams(max_tokens=n, ignore_eos=True, temperature=0), f"r{i}"):
+            last = out
+        return last
+
+    async def main():
+        outs = await asyncio.gather(*(one(i) for i in range(6)))
+        assert all(len(o.outputs[0].token_ids) == 6 for o in outs)
+        stats = await engine.get_stats()
+        steps = [s["workers"][0]["steps"] for s in stats]
+        assert len(steps) == 2 and all(x > 0 for x in steps)          # both replicas did work
+        os.kill(engine.core.clients[1].proc.pid, signal.SIGKILL)
+        await asyncio.sleep(1.0)
+        with pytest.raises(EngineDeadError):
+            await asyncio.gather(*(one(10 + i, 50) for i in range(4)))
+    try:
+        asyncio.run(main())
+    finally:
+        engine.shutdown()

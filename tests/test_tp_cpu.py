@@ -22,3 +22,11 @@ def test_moe_tp2_and_ep2_match_tp1_on_cpu(tmp_path):
         for a, b in zip(one, two):
             d = (torch.tensor(a["prompt_logprobs"]) - torch.tensor(b["prompt_logprobs"])).abs().max()
             assert d < 1e-3, (name, d)
+
+
+def test_pipeline_parallel_2_stages_matches_single_on_cpu(tmp_path):
+    ckpt = make_checkpoint(str(tmp_path / "ckpt"), "tiny-llama", dtype=torch.float32)
+    one = launch(1, ckpt, str(tmp_path / "pp1.json"), "cpu")
+    two = launch(2, ckpt, str(tmp_path / "pp2.json"), "cpu", env_extra={"SONAR_TEST_PP": "2"}, port=29619)
+    for a, b in zip(one, two):
+        assert a["tokens"] == b["tokens"]

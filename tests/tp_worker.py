@@ -24,7 +24,9 @@ def prompts():
 def run(ckpt: str, device: str, world: int):
     dtype = "bfloat16" if device == "cuda" else "float32"
     llm = LLM(ckpt, dtype=dtype, max_model_len=512, max_num_seqs=8, max_num_batched_tokens=160,
-              gpu_memory_utilization=0.05, skip_tokenizer_init=True, tensor_parallel_size=world, device=device,
+              gpu_memory_utilization=0.05, skip_tokenizer_init=True, device=device,
+              tensor_parallel_size=world // int(os.environ.get("SONAR_TEST_PP", "1")),
+              pipeline_parallel_size=int(os.environ.get("SONAR_TEST_PP", "1")),
               num_gpu_blocks_override=512 if device == "cpu" else None,
               enable_expert_parallel=os.environ.get("SONAR_TEST_EP") == "1",
               distributed_executor_backend="external_launcher" if world > 1 else "uni")

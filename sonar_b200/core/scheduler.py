@@ -24,6 +24,7 @@ from typing import Iterable
 from sonar_b200.config import CacheConfig, SchedulerConfig, SpeculativeConfig
 from sonar_b200.core.block_pool import make_block_hasher
 from sonar_b200.core.kv_cache_manager import KVCacheManager
+from sonar_b200.logger import init_logger
 from sonar_b200.request import (EngineCoreOutput, EngineCoreOutputs, EngineCoreRequest, Request,
                                 RequestStatus, SchedulerStats)
 from sonar_b200.sampling_params import SamplingParams
@@ -62,6 +63,9 @@ class SchedulerOutput:
     preempted_req_ids: set[str] = field(default_factory=set)
     num_common_prefix_blocks: int = 0
     step_id: int = 0
+    # constrained decoding: one packed int32 bitmask row per listed request (bit set = token allowed)
+    grammar_req_ids: list[str] = field(default_factory=list)
+    grammar_bitmask: object | None = None
 
 
 @dataclass
@@ -75,6 +79,9 @@ class ModelRunnerOutput:
 
 
 EMPTY_RUNNER_OUTPUT = ModelRunnerOutput()
+
+
+logger = init_logger(__name__)
 
 
 class _WaitingQueue:
@@ -148,8 +155,10 @@ def check_stop(request: Request, max_model_len: int) -> bool:
 class Scheduler:
     def __init__(self, sched_cfg: SchedulerConfig, cache_cfg: CacheConfig, num_blocks: int,
                  spec_cfg: SpeculativeConfig | None = None, sliding_window: int | None = None,
-                 log_stats: bool = False, collect_kv_events: bool = False) -> None:
+                 log_stats: bool = False, collect_kv_events: bool = False,
+                 structured_output_manager=None) -> None:
         self.cfg = sched_cfg
+        self.structured = structured_output_manager
         self.cache_cfg = cache_cfg
         self.block_size = cache_cfg.block_size
         self.max_model_len = sched_cfg.max_model_len
@@ -179,6 +188,11 @@ class Scheduler:
             raise ValueError(
                 f"prompt of {req.num_prompt_tokens} tokens leaves no room under max_model_len="
                 f"{self.max_model_len}")
+        sp = req.sampling_params
+        if sp is not None and sp.structured_outputs is not None:
+            if self.structured is None:
+                raise ValueError("structured outputs are not enabled on this engine")
+            req.grammar = self.structured.compile(sp.structured_outputs, req.eos_token_id)
         self.requests[req.request_id] = req
         self.waiting.add(req)
         req.record_event("queued")
@@ -248,7 +262,7 @@ class Scheduler:
             num_sched[req.request_id] = num_new
             budget -= num_new
             new_blocks_of[req.request_id] = new_blocks
-            if req.spec_token_ids:
+            if req.spec_token_ids and req.grammar is None:
                 n_spec = num_new + req.num_computed_tokens - req.num_tokens
                 if n_spec > 0:
                     out.scheduled_spec_decode_tokens[req.request_id] = req.spec_token_ids[:n_spec]
@@ -307,8 +321,15 @@ class Scheduler:
         self._preempted_since_last = set()
         # advance now, so the next schedule() can be built before this step's
         # tokens are known (async scheduling)
+        gram = []
         for rid, n in num_sched.items():
-            self.requests[rid].num_computed_tokens += n
+            req = self.requests[rid]
+            req.num_computed_tokens += n
+            if req.grammar is not None and req.num_computed_tokens >= req.num_tokens:
+                gram.append(req)
+        if gram:
+            out.grammar_req_ids = [r.request_id for r in gram]
+            out.grammar_bitmask = self.structured.bitmask([r.grammar for r in gram])
         return out
 
     def _pick_victim(self) -> Request:
@@ -356,6 +377,8 @@ class Scheduler:
             emitted = new_ids
             for k, tok in enumerate(new_ids):
                 req.append_output_token_ids(tok)
+                if req.grammar is not None and not req.grammar.accept(tok):
+                    logger.warning("request %s: token %d rejected by its grammar", rid, tok)
                 if check_stop(req, self.max_model_len):
                     finished = True
                     emitted = new_ids[:k + 1]

@@ -1,0 +1,503 @@
+// Small memory-bound kernels around the sampler, the KV cache and the fp8 path:
+//   token bitmask (constrained decoding), repetition penalties, paged-cache block copy,
+//   merge of two partial attention results by log-sum-exp, activation-and-mul family,
+//   per-token / per-tensor fp8 quantisation, RMSNorm(+residual) fused with per-128-group fp8
+//   quantisation, SiLU-and-mul fused with per-128-group fp8 quantisation.
+// One pass over the data each, 16-byte accesses where the layout allows, fp32 math.
+//
+// Behavioural parity with the reference's CUDA ops (not code): apply_repetition_penalties
+// (csrc/libtorch_stable/sampler.cu:14), copy_blocks (cache_kernels.cu:191), merge_attn_states
+// (attention/merge_attn_states.cu:19), act_and_mul variants (activation_kernels.cu:102,367-513),
+// fp8 quant (quantization/w8a8/fp8/common.cu:13-138), rms_norm_per_block_quant
+// (quantization/fused_kernels/layernorm_utils.cuh), silu_and_mul_per_block_quant
+// (quantization/fused_kernels/fused_silu_mul_block_quant.cu); the bitmask op mirrors
+// apply_grammar_bitmask (aphrodite/v1/structured_output/utils.py).
+#include "common.cuh"
+
+namespace sonar {
+namespace {
+
+constexpr float FP8_MAX = 448.f;
+
+// ---------------------------------------------------------------- token bitmask
+// logits[row_idx[i], t] = -inf where bit t of mask[i] is clear.  grid (n, tiles of 1024 tokens).
+__global__ void __launch_bounds__(256) token_bitmask_kernel(float* __restrict__ logits, long stride, int V,
+                                                            const int* __restrict__ mask, int words,
+                                                            const int* __restrict__ row_idx) {
+  const int i = blockIdx.x;
+  const long row = row_idx ? row_idx[i] : i;
+  float* l = logits + row * stride;
+  const int w0 = blockIdx.y * 32;                    // 32 words = 1024 tokens per block
+  const int lane_word = w0 + (threadIdx.x >> 3);     // 8 threads share a word, 4 tokens each
+  if (lane_word >= words) return;
+  const unsigned bits = (unsigned)mask[(long)i * words + lane_word];
+  const int t0 = lane_word * 32 + (threadIdx.x & 7) * 4;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    int t = t0 + k;
+    if (t < V && !((bits >> (t & 31)) & 1u)) l[t] = -INFINITY;
+  }
+}
+
+// ---------------------------------------------------------------- repetition penalties
+// seen[row, t] (uint8, prompt or output occurrence) selects the tokens to penalise:
+// positive logits are divided by the penalty, negative ones multiplied.
+__global__ void __launch_bounds__(256) repetition_penalty_kernel(float* __restrict__ logits, long stride, int V,
+                                                                 const uint8_t* __restrict__ prompt_seen,
+                                                                 const uint8_t* __restrict__ output_seen,
+                                                                 const float* __restrict__ penalty) {
+  const long row = blockIdx.x;
+  const float p = penalty[row];
+  if (p == 1.f) return;
+  float* l = logits + row * stride;
+  const uint8_t* a = prompt_seen + row * (long)V;
+  const uint8_t* b = output_seen + row * (long)V;
+  for (int t = blockIdx.y * blockDim.x + threadIdx.x; t < V; t += gridDim.y * blockDim.x) {
+    if (a[t] | b[t]) {
+      float v = l[t];
+      l[t] = v > 0.f ? v / p : v * p;
+    }
+  }
+}
+
+// ---------------------------------------------------------------- paged-cache block copy
+// pairs[2i] → pairs[2i+1], block_vecs 16-byte vectors per block.  grid (pairs, chunks).
+__global__ void __launch_bounds__(256) copy_blocks_kernel(uint4* __restrict__ cache, long block_vecs,
+                                                          const long* __restrict__ pairs) {
+  const long src = pairs[2 * blockIdx.x], dst = pairs[2 * blockIdx.x + 1];
+  const uint4* s = cache + src * block_vecs;
+  uint4* d = cache + dst * block_vecs;
+  for (long i = blockIdx.y * (long)blockDim.x + threadIdx.x; i < block_vecs; i += (long)gridDim.y * blockDim.x)
+    d[i] = s[i];
+}
+
+// ---------------------------------------------------------------- merge attention states
+// out = (a·e^{la} + b·e^{lb}) / (e^{la} + e^{lb}), lse = log(e^{la} + e^{lb});  natural-log LSEs
+// laid out [tokens, heads] fp32; a, b, out [tokens, heads, D].  One thread per 8 elements.
+template <typename T>
+__global__ void __launch_bounds__(256) merge_states_kernel(T* __restrict__ out, float* __restrict__ out_lse,
+                                                           const T* __restrict__ a, const float* __restrict__ la,
+                                                           const T* __restrict__ b, const float* __restrict__ lb,
+                                                           long n_th, int D) {
+  const int vpr = D >> 3;
+  const long i = blockIdx.x * (long)blockDim.x + threadIdx.x;
+  if (i >= n_th * vpr) return;
+  const long th = i / vpr;
+  const int v = (int)(i - th * vpr);
+  float x = la[th], y = lb[th];
+  x = isinf(x) && x > 0 ? -INFINITY : x;   // a +inf LSE marks an empty partial
+  y = isinf(y) && y > 0 ? -INFINITY : y;
+  const float m = fmaxf(x, y);
+  float wa, wb, lse;
+  if (isinf(m)) { wa = 0.f; wb = 0.f; lse = -INFINITY; }
+  else {
+    const float ea = __expf(x - m), eb = __expf(y - m), s = ea + eb;
+    wa = ea / s; wb = eb / s; lse = m + __logf(s);
+  }
+  float fa[8], fb[8];
+  unpack8<T>(reinterpret_cast<const uint4*>(a + th * D)[v], fa);
+  unpack8<T>(reinterpret_cast<const uint4*>(b + th * D)[v], fb);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) fa[j] = fa[j] * wa + fb[j] * wb;
+  reinterpret_cast<uint4*>(out + th * D)[v] = pack8<T>(fa);
+  if (v == 0 && out_lse) out_lse[th] = lse;
+}
+
+// ---------------------------------------------------------------- activations
+enum Act : int { ACT_SILU = 0, ACT_GELU = 1, ACT_GELU_TANH = 2, ACT_FATRELU = 3, ACT_SWIGLU_OAI = 4,
+                 ACT_GELU_NEW = 5, ACT_GELU_FAST = 6, ACT_QUICK_GELU = 7, ACT_RELU2 = 8 };
+
+template <int ACT>
+__device__ __forceinline__ float act_fn(float x, float p0) {
+  if (ACT == ACT_SILU) return x / (1.f + __expf(-x));
+  if (ACT == ACT_GELU) return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+  if (ACT == ACT_GELU_TANH || ACT == ACT_GELU_NEW)
+    return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+  if (ACT == ACT_FATRELU) return x > p0 ? x : 0.f;
+  if (ACT == ACT_GELU_FAST) return 0.5f * x * (1.f + tanhf(x * 0.79788456f * (1.f + 0.044715f * x * x)));
+  if (ACT == ACT_QUICK_GELU) return x / (1.f + __expf(-1.702f * x));
+  if (ACT == ACT_RELU2) { float r = fmaxf(x, 0.f); return r * r; }
+  return x;
+}
+
+// gated: out[r, :d] = act(x[r, :d]) * x[r, d:2d]; SWIGLU_OAI clamps and uses (up + 1)·gate·σ(α·gate)
+// on interleaved pairs.  ungated (GATED = false): out = act(x).
+template <typename T, int ACT, bool GATED>
+__global__ void __launch_bounds__(256) act_kernel(const T* __restrict__ x, T* __restrict__ out, int d, long x_stride,
+                                                  long total_vec, float p0, float p1) {
+  const int vpr = d >> 3;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total_vec; i += (long)gridDim.x * blockDim.x) {
+    const long row = i / vpr;
+    const int v = (int)(i - row * vpr);
+    float a[8], b[8];
+    if (ACT == ACT_SWIGLU_OAI) {
+      // interleaved [g0, u0, g1, u1, …]: 16 inputs → 8 outputs
+      const uint4* src = reinterpret_cast<const uint4*>(x + row * x_stride) + 2 * v;
+      float lo[8], hi[8];
+      unpack8<T>(src[0], lo);
+      unpack8<T>(src[1], hi);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { a[j] = lo[2 * j]; b[j] = lo[2 * j + 1]; a[4 + j] = hi[2 * j]; b[4 + j] = hi[2 * j + 1]; }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float g = fminf(a[j], p1), u = fminf(fmaxf(b[j], -p1), p1);
+        a[j] = (u + 1.f) * g / (1.f + __expf(-p0 * g));
+      }
+    } else {
+      unpack8<T>(reinterpret_cast<const uint4*>(x + row * x_stride)[v], a);
+      if (GATED) unpack8<T>(reinterpret_cast<const uint4*>(x + row * x_stride + d)[v], b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] = GATED ? act_fn<ACT>(a[j], p0) * b[j] : act_fn<ACT>(a[j], p0);
+    }
+    reinterpret_cast<uint4*>(out + row * (long)d)[v] = pack8<T>(a);
+  }
+}
+
+// ---------------------------------------------------------------- fp8 quantisation
+__device__ __forceinline__ uint32_t quant4(const float* v, float inv) {
+  __nv_fp8_e4m3 o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o[i] = __nv_fp8_e4m3(fminf(fmaxf(v[i] * inv, -FP8_MAX), FP8_MAX));
+  return *reinterpret_cast<uint32_t*>(o);
+}
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  float t = (threadIdx.x < nw) ? red[threadIdx.x] : 0.f;
+  if (w == 0) { t = warp_max(t); if (lane == 0) red[0] = t; }
+  __syncthreads();
+  float r = red[0];
+  __syncthreads();
+  return r;
+}
+
+// dynamic per-token: one block per row, scale[row] = absmax / 448 (optionally capped by *scale_ub)
+template <typename T>
+__global__ void __launch_bounds__(256) quant_per_token_kernel(const T* __restrict__ x, long x_stride,
+                                                              __nv_fp8_e4m3* __restrict__ q, float* __restrict__ scale,
+                                                              int K, const float* __restrict__ scale_ub) {
+  __shared__ float red[32];
+  const long row = blockIdx.x;
+  const T* src = x + row * x_stride;
+  float amax = 0.f;
+  for (int v = threadIdx.x; v < (K >> 3); v += blockDim.x) {
+    float f[8];
+    unpack8<T>(reinterpret_cast<const uint4*>(src)[v], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+  }
+  amax = block_max(amax, red);
+  if (scale_ub) amax = fminf(amax, *scale_ub);
+  const float sc = fmaxf(amax / FP8_MAX, 1.f / (FP8_MAX * 512.f));
+  const float inv = 1.f / sc;
+  if (threadIdx.x == 0) scale[row] = sc;
+  for (int v = threadIdx.x; v < (K >> 3); v += blockDim.x) {
+    float f[8];
+    unpack8<T>(reinterpret_cast<const uint4*>(src)[v], f);
+    uint2 o;
+    o.x = quant4(f, inv);
+    o.y = quant4(f + 4, inv);
+    reinterpret_cast<uint2*>(q + row * (long)K)[v] = o;
+  }
+}
+
+// per-tensor: pass 1 absmax → atomicMax on the bit pattern of a non-negative float (scale word must
+// be zeroed first); pass 2 quantises with scale = amax/448 (dynamic) or the given scale (static).
+template <typename T>
+__global__ void __launch_bounds__(256) absmax_kernel(const T* __restrict__ x, long x_stride, int K, long total_vec,
+                                                     float* __restrict__ amax_out) {
+  __shared__ float red[32];
+  const int vpr = K >> 3;
+  float amax = 0.f;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total_vec; i += (long)gridDim.x * blockDim.x) {
+    const long row = i / vpr;
+    float f[8];
+    unpack8<T>(reinterpret_cast<const uint4*>(x + row * x_stride)[i - row * vpr], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+  }
+  amax = block_max(amax, red);
+  if (threadIdx.x == 0) atomicMax(reinterpret_cast<int*>(amax_out), __float_as_int(amax));
+}
+
+template <typename T, bool DYNAMIC>
+__global__ void __launch_bounds__(256) quant_per_tensor_kernel(const T* __restrict__ x, long x_stride,
+                                                               __nv_fp8_e4m3* __restrict__ q, float* __restrict__ scale,
+                                                               int K, long total_vec) {
+  // DYNAMIC: *scale holds the absmax on entry; block 0 rewrites it as the scale after a grid-wide read.
+  const float s_in = *scale;
+  const float sc = DYNAMIC ? fmaxf(s_in / FP8_MAX, 1.f / (FP8_MAX * 512.f)) : s_in;
+  const float inv = 1.f / sc;
+  const int vpr = K >> 3;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total_vec; i += (long)gridDim.x * blockDim.x) {
+    const long row = i / vpr;
+    const long v = i - row * vpr;
+    float f[8];
+    unpack8<T>(reinterpret_cast<const uint4*>(x + row * x_stride)[v], f);
+    uint2 o;
+    o.x = quant4(f, inv);
+    o.y = quant4(f + 4, inv);
+    reinterpret_cast<uint2*>(q + row * (long)K)[v] = o;
+  }
+}
+
+__global__ void amax_to_scale_kernel(float* scale) {
+  *scale = fmaxf(*scale / FP8_MAX, 1.f / (FP8_MAX * 512.f));
+}
+
+// ---------------------------------------------------------------- RMSNorm (+residual) + group quant
+// One block per row, hidden/8 ≤ 1024·VPT vectors; each thread owns whole 8-element vectors, 16
+// consecutive threads form one 128-channel group.  Output: fp8 row + transposed scales
+// scales_t[g, row], and optionally the normalised row in T (for consumers that stay in 16 bits).
+template <typename T, bool ADD, int VPT>
+__global__ void __launch_bounds__(1024) rms_norm_quant_kernel(const T* __restrict__ x, T* __restrict__ residual,
+                                                              const T* __restrict__ w, __nv_fp8_e4m3* __restrict__ q,
+                                                              float* __restrict__ scales_t, long scale_ld,
+                                                              T* __restrict__ out16, int hidden, long x_stride,
+                                                              float eps) {
+  __shared__ float red[32];
+  const long row = blockIdx.x;
+  const uint4* xv = reinterpret_cast<const uint4*>(x + row * x_stride);
+  uint4* rv = ADD ? reinterpret_cast<uint4*>(residual + row * (long)hidden) : nullptr;
+  const uint4* wv = reinterpret_cast<const uint4*>(w);
+  const int nvec = hidden >> 3;
+  float vals[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      unpack8<T>(xv[v], vals[i]);
+      if (ADD) {
+        float r[8];
+        unpack8<T>(rv[v], r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vals[i][j] = to_f<T>(from_f<T>(vals[i][j] + r[j]));
+        rv[v] = pack8<T>(vals[i]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) vals[i][j] = 0.f;
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv_rms = rsqrtf(ss / (float)hidden + eps);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;   // blockDim.x is a multiple of 32 → groups of 16 lanes stay aligned
+    float g[8];
+    float amax = 0.f;
+    if (v < nvec) {
+      unpack8<T>(wv[v], g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        vals[i][j] = to_f<T>(from_f<T>(vals[i][j] * inv_rms * g[j]));   // round as the unfused norm would
+        amax = fmaxf(amax, fabsf(vals[i][j]));
+      }
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    amax = fmaxf(amax, 1e-10f);
+    if (v < nvec) {
+      const float inv = FP8_MAX / amax;
+      uint2 o;
+      o.x = quant4(vals[i], inv);
+      o.y = quant4(vals[i] + 4, inv);
+      reinterpret_cast<uint2*>(q + row * (long)hidden)[v] = o;
+      if ((v & 15) == 0) scales_t[(long)(v >> 4) * scale_ld + row] = amax / FP8_MAX;
+      if (out16) reinterpret_cast<uint4*>(out16 + row * (long)hidden)[v] = pack8<T>(vals[i]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------- SiLU-and-mul + group quant
+// x row = [gate(d) | up(d)], d % 128 == 0.  16 lanes per 128-channel group, 8 channels per lane.
+template <typename T>
+__global__ void __launch_bounds__(256) silu_mul_quant_kernel(const T* __restrict__ x, long x_stride,
+                                                             __nv_fp8_e4m3* __restrict__ q,
+                                                             float* __restrict__ scales_t, long scale_ld, int rows,
+                                                             int d) {
+  const int vpr = d >> 3;
+  const long total = (long)rows * vpr;      // multiple of 16
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long row = i / vpr;
+    const int v = (int)(i - row * vpr);
+    float a[8], b[8];
+    unpack8<T>(reinterpret_cast<const uint4*>(x + row * x_stride)[v], a);
+    unpack8<T>(reinterpret_cast<const uint4*>(x + row * x_stride + d)[v], b);
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      a[j] = to_f<T>(from_f<T>((a[j] / (1.f + __expf(-a[j]))) * b[j]));
+      amax = fmaxf(amax, fabsf(a[j]));
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    amax = fmaxf(amax, 1e-10f);
+    const float inv = FP8_MAX / amax;
+    uint2 o;
+    o.x = quant4(a, inv);
+    o.y = quant4(a + 4, inv);
+    reinterpret_cast<uint2*>(q + row * (long)d)[v] = o;
+    if ((v & 15) == 0) scales_t[(long)(v >> 4) * scale_ld + row] = amax / FP8_MAX;
+  }
+}
+
+inline int grid_for(long work_items, int threads, int cap = 148 * 8) {
+  long b = (work_items + threads - 1) / threads;
+  return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace
+}  // namespace sonar
+
+using namespace sonar;
+
+SONAR_API int sonar_apply_token_bitmask(float* logits, long stride, int V, const int* mask, int words,
+                                        const int* row_idx, int n, cudaStream_t s) {
+  if (n == 0) return SONAR_OK;
+  if (words * 32 < V) return SONAR_BAD_ARG;
+  dim3 grid(n, (words + 31) / 32);
+  token_bitmask_kernel<<<grid, 256, 0, s>>>(logits, stride, V, mask, words, row_idx);
+  return check_launch();
+}
+
+SONAR_API int sonar_apply_repetition_penalties(float* logits, long stride, int rows, int V, const uint8_t* prompt_seen,
+                                               const uint8_t* output_seen, const float* penalty, cudaStream_t s) {
+  if (rows == 0) return SONAR_OK;
+  int tiles = (V + 1023) / 1024;
+  dim3 grid(rows, tiles < 64 ? tiles : 64);
+  repetition_penalty_kernel<<<grid, 256, 0, s>>>(logits, stride, V, prompt_seen, output_seen, penalty);
+  return check_launch();
+}
+
+SONAR_API int sonar_copy_blocks(void* cache, long block_bytes, const long* pairs, int n_pairs, cudaStream_t s) {
+  if (n_pairs == 0) return SONAR_OK;
+  if (block_bytes % 16 || ((uintptr_t)cache & 15)) return SONAR_BAD_ARG;
+  long vecs = block_bytes / 16;
+  long chunks = (vecs + 256 * 8 - 1) / (256 * 8);
+  dim3 grid(n_pairs, (unsigned)(chunks < 1 ? 1 : (chunks > 64 ? 64 : chunks)));
+  copy_blocks_kernel<<<grid, 256, 0, s>>>((uint4*)cache, vecs, pairs);
+  return check_launch();
+}
+
+SONAR_API int sonar_merge_attn_states(void* out, float* out_lse, const void* a, const float* lse_a, const void* b,
+                                      const float* lse_b, long tokens, int heads, int head_dim, int dtype,
+                                      cudaStream_t s) {
+  if (tokens == 0) return SONAR_OK;
+  if (head_dim % 8) return SONAR_BAD_ARG;
+  const long n_th = tokens * heads;
+  const long work = n_th * (head_dim / 8);
+  const int blocks = (int)((work + 255) / 256);
+  SONAR_DISPATCH_HALF(dtype, T, {
+    merge_states_kernel<T><<<blocks, 256, 0, s>>>((T*)out, out_lse, (const T*)a, lse_a, (const T*)b, lse_b, n_th, head_dim);
+    return check_launch();
+  });
+}
+
+#define LAUNCH_ACT(ACT, GATED)                                                                            \
+  act_kernel<T, ACT, GATED><<<grid, 256, 0, s>>>((const T*)x, (T*)out, d, x_stride, total, p0, p1)
+
+SONAR_API int sonar_activation(const void* x, void* out, int rows, int d, long x_stride, int act, int gated, float p0,
+                               float p1, int dtype, cudaStream_t s) {
+  if (rows == 0) return SONAR_OK;
+  if (d % 8 || x_stride % 8) return SONAR_BAD_ARG;
+  const long total = (long)rows * (d / 8);
+  const int grid = grid_for(total, 256, 148 * 16);
+  SONAR_DISPATCH_HALF(dtype, T, {
+    if (act == ACT_SWIGLU_OAI) { if (!gated) return SONAR_BAD_ARG; LAUNCH_ACT(ACT_SWIGLU_OAI, true); }
+    else if (gated) {
+      switch (act) {
+        case ACT_SILU: LAUNCH_ACT(ACT_SILU, true); break;
+        case ACT_GELU: LAUNCH_ACT(ACT_GELU, true); break;
+        case ACT_GELU_TANH: LAUNCH_ACT(ACT_GELU_TANH, true); break;
+        case ACT_FATRELU: LAUNCH_ACT(ACT_FATRELU, true); break;
+        default: return SONAR_BAD_ARG;
+      }
+    } else {
+      switch (act) {
+        case ACT_SILU: LAUNCH_ACT(ACT_SILU, false); break;
+        case ACT_GELU: LAUNCH_ACT(ACT_GELU, false); break;
+        case ACT_GELU_TANH: case ACT_GELU_NEW: LAUNCH_ACT(ACT_GELU_NEW, false); break;
+        case ACT_GELU_FAST: LAUNCH_ACT(ACT_GELU_FAST, false); break;
+        case ACT_QUICK_GELU: LAUNCH_ACT(ACT_QUICK_GELU, false); break;
+        case ACT_RELU2: LAUNCH_ACT(ACT_RELU2, false); break;
+        default: return SONAR_BAD_ARG;
+      }
+    }
+    return check_launch();
+  });
+}
+
+SONAR_API int sonar_quant_fp8_per_token(const void* x, long x_stride, void* q, float* scale, int rows, int K,
+                                        const float* scale_ub, int dtype, cudaStream_t s) {
+  if (rows == 0) return SONAR_OK;
+  if (K % 8 || x_stride % 8) return SONAR_BAD_ARG;
+  SONAR_DISPATCH_HALF(dtype, T, {
+    quant_per_token_kernel<T><<<rows, 256, 0, s>>>((const T*)x, x_stride, (__nv_fp8_e4m3*)q, scale, K, scale_ub);
+    return check_launch();
+  });
+}
+
+// dynamic != 0: *scale is computed (absmax/448) and left in place; else *scale is read.
+SONAR_API int sonar_quant_fp8_per_tensor(const void* x, long x_stride, void* q, float* scale, int rows, int K,
+                                         int dynamic, int dtype, cudaStream_t s) {
+  if (rows == 0) return SONAR_OK;
+  if (K % 8 || x_stride % 8) return SONAR_BAD_ARG;
+  const long total = (long)rows * (K / 8);
+  const int grid = grid_for(total, 256);
+  SONAR_DISPATCH_HALF(dtype, T, {
+    if (dynamic) {
+      if (cudaMemsetAsync(scale, 0, sizeof(float), s) != cudaSuccess) return SONAR_CUDA_ERROR;
+      absmax_kernel<T><<<grid, 256, 0, s>>>((const T*)x, x_stride, K, total, scale);
+      quant_per_tensor_kernel<T, true><<<grid, 256, 0, s>>>((const T*)x, x_stride, (__nv_fp8_e4m3*)q, scale, K, total);
+      amax_to_scale_kernel<<<1, 1, 0, s>>>(scale);
+    } else {
+      quant_per_tensor_kernel<T, false><<<grid, 256, 0, s>>>((const T*)x, x_stride, (__nv_fp8_e4m3*)q, scale, K, total);
+    }
+    return check_launch();
+  });
+}
+
+template <typename T, bool ADD>
+static int launch_norm_quant(const T* x, T* residual, const T* w, void* q, float* scales_t, long scale_ld, T* out16,
+                             int rows, int hidden, long x_stride, float eps, cudaStream_t s) {
+  const int nvec = hidden / 8;
+  int threads = nvec >= 1024 ? 1024 : ((nvec + 31) / 32) * 32;
+  const int vpt = (nvec + threads - 1) / threads;
+  auto q8 = (__nv_fp8_e4m3*)q;
+  if (vpt <= 1) rms_norm_quant_kernel<T, ADD, 1><<<rows, threads, 0, s>>>(x, residual, w, q8, scales_t, scale_ld, out16, hidden, x_stride, eps);
+  else if (vpt <= 2) rms_norm_quant_kernel<T, ADD, 2><<<rows, threads, 0, s>>>(x, residual, w, q8, scales_t, scale_ld, out16, hidden, x_stride, eps);
+  else if (vpt <= 4) rms_norm_quant_kernel<T, ADD, 4><<<rows, threads, 0, s>>>(x, residual, w, q8, scales_t, scale_ld, out16, hidden, x_stride, eps);
+  else return SONAR_TOO_LARGE;
+  return check_launch();
+}
+
+SONAR_API int sonar_rms_norm_group_quant(const void* x, void* residual, const void* w, void* q, float* scales_t,
+                                         long scale_ld, void* out16, int rows, int hidden, long x_stride, float eps,
+                                         int dtype, cudaStream_t s) {
+  if (rows == 0) return SONAR_OK;
+  if (hidden % 128 || x_stride % 8 || scale_ld < rows) return SONAR_BAD_ARG;
+  SONAR_DISPATCH_HALF(dtype, T, {
+    if (residual) return launch_norm_quant<T, true>((const T*)x, (T*)residual, (const T*)w, q, scales_t, scale_ld, (T*)out16, rows, hidden, x_stride, eps, s);
+    return launch_norm_quant<T, false>((const T*)x, nullptr, (const T*)w, q, scales_t, scale_ld, (T*)out16, rows, hidden, x_stride, eps, s);
+  });
+}
+
+SONAR_API int sonar_silu_mul_group_quant(const void* x, long x_stride, void* q, float* scales_t, long scale_ld, int rows,
+                                         int d, int dtype, cudaStream_t s) {
+  if (rows == 0) return SONAR_OK;
+  if (d % 128 || x_stride % 8 || scale_ld < rows) return SONAR_BAD_ARG;
+  const long total = (long)rows * (d / 8);
+  const int grid = grid_for(total, 256, 148 * 16);
+  SONAR_DISPATCH_HALF(dtype, T, {
+    silu_mul_quant_kernel<T><<<grid, 256, 0, s>>>((const T*)x, x_stride, (__nv_fp8_e4m3*)q, scales_t, scale_ld, rows, d);
+    return check_launch();
+  });
+}

@@ -29,9 +29,16 @@ class EngineCore:
         self.executor = (executor_class or Executor.get_class(cfg))(cfg)
         self.kv_cfg = self.executor.initialize_kv_cache()
         sliding = self.kv_cfg.spec.sliding_window
+        structured = None
+        if not cfg.model.skip_tokenizer_init:
+            from sonar_b200.structured_output import StructuredOutputManager
+            from sonar_b200.utils.tokenizer import get_tokenizer
+            structured = StructuredOutputManager(get_tokenizer(cfg.model.tokenizer, cfg.model.vocab_size),
+                                                 cfg.model.vocab_size)
         self.scheduler = Scheduler(cfg.scheduler, cfg.cache, self.kv_cfg.num_blocks, cfg.speculative,
                                    sliding_window=sliding, log_stats=cfg.observability.log_stats,
-                                   collect_kv_events=cfg.observability.collect_kv_events)
+                                   collect_kv_events=cfg.observability.collect_kv_events,
+                                   structured_output_manager=structured)
         self.tracer = get_tracer(cfg.observability.trace_file)
         self.paused = False
         self.steps = 0

@@ -78,7 +78,10 @@ class InputProcessor:
                 params._bad_words_token_ids = [
                     self.tokenizer.encode(w, add_special_tokens=False) for w in params.bad_words]
             if params.structured_outputs is not None:
-                raise ValueError("structured outputs need a grammar backend, which this build does not bundle")
+                if self.tokenizer is None:
+                    raise ValueError("structured outputs need a tokenizer (skip_tokenizer_init is set)")
+                from sonar_b200.structured_output import StructuredOutputManager
+                StructuredOutputManager(self.tokenizer, self.cfg.model.vocab_size).validate(params.structured_outputs)
             if params.stop and self.tokenizer is None:
                 raise ValueError("stop strings need a tokenizer")
             if self.tokenizer is None:

@@ -69,6 +69,36 @@ class SamplingFields(_Base):
     temperature_last: bool | None = None
     skew: float | None = None
     no_repeat_ngram_size: int | None = None
+    # constrained decoding
+    response_format: dict[str, Any] | None = None
+    structured_outputs: dict[str, Any] | None = None
+    guided_json: str | dict[str, Any] | None = None
+    guided_regex: str | None = None
+    guided_choice: list[str] | None = None
+    guided_grammar: str | None = None
+
+    def structured_params(self):
+        """``response_format`` / ``structured_outputs`` / legacy ``guided_*`` fields → StructuredOutputsParams."""
+        from sonar_b200.sampling_params import StructuredOutputsParams
+        if self.structured_outputs:
+            return StructuredOutputsParams(**self.structured_outputs)
+        if self.guided_json is not None:
+            return StructuredOutputsParams(json=self.guided_json)
+        if self.guided_regex is not None:
+            return StructuredOutputsParams(regex=self.guided_regex)
+        if self.guided_choice is not None:
+            return StructuredOutputsParams(choice=self.guided_choice)
+        if self.guided_grammar is not None:
+            return StructuredOutputsParams(grammar=self.guided_grammar)
+        rf = self.response_format
+        if rf:
+            kind = rf.get("type")
+            if kind == "json_object":
+                return StructuredOutputsParams(json_object=True)
+            if kind == "json_schema":
+                js = rf.get("json_schema") or {}
+                return StructuredOutputsParams(json=js.get("schema", js))
+        return None
 
     _PASS = ("top_p", "top_k", "min_p", "presence_penalty", "frequency_penalty", "repetition_penalty", "seed",
              "stop_token_ids", "allowed_token_ids", "bad_words", "top_a", "tfs", "eta_cutoff", "epsilon_cutoff",
@@ -82,6 +112,9 @@ class SamplingFields(_Base):
         kw: dict[str, Any] = {k: getattr(self, k) for k in self._PASS if getattr(self, k) is not None}
         if self.logit_bias:
             kw["logit_bias"] = {int(k): float(v) for k, v in self.logit_bias.items()}
+        so = self.structured_params()
+        if so is not None:
+            kw["structured_outputs"] = so
         return SamplingParams(
             n=self.n, max_tokens=self.max_tokens if self.max_tokens is not None else default_max_tokens,
             temperature=self.temperature if self.temperature is not None else default_temperature,
@@ -125,7 +158,6 @@ class ChatCompletionRequest(SamplingFields):
     tool_choice: str | dict[str, Any] | None = None
     chat_template: str | None = None
     add_generation_prompt: bool = True
-    response_format: dict[str, Any] | None = None
 
 
 class UsageInfo(_Base):

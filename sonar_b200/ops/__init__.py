@@ -181,3 +181,76 @@ def argmax(logits):
     if _use_cuda(logits):
         return cuda_ops().argmax(logits)
     return logits.argmax(dim=-1)
+
+
+# ---- constrained decoding / penalties / block copy ---------------------------------
+def apply_token_bitmask(logits, bitmask, row_idx=None):
+    """In place: −inf where the packed int32 ``bitmask`` row has a clear bit; ``row_idx`` maps mask rows to logits rows."""
+    if _use_cuda(logits):
+        return cuda_ops().apply_token_bitmask(logits, bitmask, row_idx)
+    return ref.apply_token_bitmask(logits, bitmask, row_idx)
+
+
+def apply_repetition_penalties(logits, prompt_seen, output_seen, penalty):
+    if _use_cuda(logits):
+        return cuda_ops().apply_repetition_penalties(logits, prompt_seen, output_seen, penalty)
+    return ref.apply_repetition_penalties(logits, prompt_seen, output_seen, penalty)
+
+
+def copy_blocks(cache, pairs):
+    if _use_cuda(cache):
+        return cuda_ops().copy_blocks(cache, pairs)
+    return ref.copy_blocks(cache, pairs)
+
+
+def activation(x, name, gated=False, p0=0.0, p1=0.0):
+    if _use_cuda(x):
+        return cuda_ops().activation(x, name, gated, p0, p1)
+    return ref.activation(x, name, gated, p0, p1)
+
+
+# ---- fp8 quantisation and its fusions -------------------------------------------
+def per_token_quant_fp8(x, scale_ub=None):
+    if _use_cuda(x):
+        return cuda_ops().per_token_quant_fp8(x, scale_ub)
+    return ref.per_token_quant_fp8(x, scale_ub)
+
+
+def scaled_fp8_quant(x, scale=None):
+    if _use_cuda(x):
+        return cuda_ops().scaled_fp8_quant(x, scale)
+    return ref.scaled_fp8_quant(x, scale)
+
+
+def rms_norm_group_quant(x, weight, eps, residual=None):
+    """→ (fp8, group scales, residual).  One kernel on the GPU: norm (+residual add) and the quantisation
+    the next fp8 GEMM needs, so the normalised row never goes to memory in 16 bits."""
+    if _use_cuda(x):
+        q, s, r, _ = cuda_ops().rms_norm_group_quant(x, weight, eps, residual)
+        return q, s, r
+    return ref.rms_norm_group_quant(x, weight, eps, residual)
+
+
+def silu_mul_group_quant(x):
+    if _use_cuda(x):
+        return cuda_ops().silu_mul_group_quant(x)
+    return ref.silu_mul_group_quant(x)
+
+
+def scaled_mm_fp8(xq, x_scale, wq, w_scale, out_dtype=torch.bfloat16):
+    """fp8 GEMM with per-tensor or per-token activation scales and per-tensor or per-channel weight scales,
+    expressed through the block-scaled kernel (scales broadcast to its 1×128 / 128×128 grid).  ``x_scale``:
+    scalar or [T, 1]; ``w_scale``: scalar or [N, 1] (per-channel scales are applied after the product)."""
+    t, k = xq.shape
+    n = wq.shape[0]
+    xs = x_scale.float().reshape(-1, 1).expand(t, k // 128).contiguous()
+    per_channel = w_scale.numel() == n and n > 1
+    shape = (-(-n // 128), k // 128)
+    if per_channel:
+        ws_blk = torch.ones(shape, dtype=torch.float32, device=xq.device)
+    else:
+        ws_blk = w_scale.float().reshape(1, 1).expand(*shape).contiguous()
+    y = gemm_fp8_block(xq, xs, wq, ws_blk, out_dtype)
+    if per_channel:
+        y = (y.float() * w_scale.float().reshape(1, n)).to(out_dtype)
+    return y

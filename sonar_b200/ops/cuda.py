@@ -80,6 +80,22 @@ _mla_attn = _sig("sonar_mla_attention", c_void_p, c_long, c_long, c_void_p, c_lo
 _argmax = _sig("sonar_argmax", c_void_p, c_long, c_int, c_int, c_void_p, c_void_p)
 _sample = _sig("sonar_sample", c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                c_long, c_void_p, c_uint, c_void_p, c_void_p)
+_bitmask = _sig("sonar_apply_token_bitmask", c_void_p, c_long, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p)
+_rep_pen = _sig("sonar_apply_repetition_penalties", c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                c_void_p)
+_copy_blocks = _sig("sonar_copy_blocks", c_void_p, c_long, c_void_p, c_int, c_void_p)
+_merge_states = _sig("sonar_merge_attn_states", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long,
+                     c_int, c_int, c_int, c_void_p)
+_activation = _sig("sonar_activation", c_void_p, c_void_p, c_int, c_int, c_long, c_int, c_int, c_float, c_float, c_int,
+                   c_void_p)
+_quant_token = _sig("sonar_quant_fp8_per_token", c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int,
+                    c_void_p)
+_quant_tensor = _sig("sonar_quant_fp8_per_tensor", c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                     c_void_p)
+_norm_quant = _sig("sonar_rms_norm_group_quant", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_void_p,
+                   c_int, c_int, c_long, c_float, c_int, c_void_p)
+_silu_quant = _sig("sonar_silu_mul_group_quant", c_void_p, c_long, c_void_p, c_void_p, c_long, c_int, c_int, c_int,
+                   c_void_p)
 lib.sonar_last_cuda_error.restype = c_int
 lib.sonar_gemm_pick_bn.argtypes = [c_int, c_int, c_int, c_int]
 lib.sonar_gemm_pick_bn.restype = c_int
@@ -274,7 +290,106 @@ def paged_attention(q, kv_cache, meta, scale, sliding_window=None, k_scale=1.0, 
 
 
 def merge_attn_states(o1, lse1, o2, lse2):
-    return ref.merge_attn_states(o1, lse1, o2, lse2)
+    """o: [T, H, D] 16-bit contiguous, lse: [T, H] fp32 (natural log) → (merged o, merged lse)."""
+    o1, o2 = o1.contiguous(), o2.contiguous()
+    t, h, d = o1.shape
+    out = torch.empty_like(o1)
+    lse = torch.empty((t, h), dtype=torch.float32, device=o1.device)
+    _check(_merge_states(out.data_ptr(), lse.data_ptr(), o1.data_ptr(), lse1.contiguous().data_ptr(), o2.data_ptr(),
+                         lse2.contiguous().data_ptr(), t, h, d, _DT[o1.dtype], _stream()), "merge_attn_states")
+    return out, lse
+
+
+# ---------------------------------------------------------------- sampler helpers, block copy, activations
+def apply_token_bitmask(logits, bitmask, row_idx=None):
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and bitmask.dtype == torch.int32
+    bitmask = bitmask.contiguous()
+    if row_idx is not None:
+        row_idx = row_idx.to(torch.int32)
+    _check(_bitmask(logits.data_ptr(), logits.stride(0), logits.shape[1], bitmask.data_ptr(), bitmask.shape[1],
+                    _ptr(row_idx), bitmask.shape[0], _stream()), "apply_token_bitmask")
+    return logits
+
+
+def apply_repetition_penalties(logits, prompt_seen, output_seen, penalty):
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    ps = prompt_seen.to(torch.uint8).contiguous()
+    os_ = output_seen.to(torch.uint8).contiguous()
+    _check(_rep_pen(logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], ps.data_ptr(),
+                    os_.data_ptr(), penalty.float().contiguous().data_ptr(), _stream()), "apply_repetition_penalties")
+    return logits
+
+
+def copy_blocks(cache, pairs):
+    """cache: contiguous, dim 0 = blocks; pairs: int64 [n, 2] (src, dst) on the device."""
+    assert cache.is_contiguous() and pairs.dtype == torch.int64
+    if pairs.numel() == 0:
+        return
+    block_bytes = cache.stride(0) * cache.element_size()
+    _check(_copy_blocks(cache.data_ptr(), block_bytes, pairs.contiguous().data_ptr(), pairs.shape[0], _stream()),
+           "copy_blocks")
+
+
+_ACT_IDS = {"silu": 0, "gelu": 1, "gelu_tanh": 2, "fatrelu": 3, "swiglu_oai": 4, "gelu_new": 5, "gelu_fast": 6,
+            "quick_gelu": 7, "relu2": 8}
+
+
+def activation(x, name, gated=False, p0=0.0, p1=0.0):
+    assert x.dim() == 2 and x.stride(1) == 1
+    d = x.shape[1] // 2 if gated else x.shape[1]
+    out = torch.empty((x.shape[0], d), dtype=x.dtype, device=x.device)
+    _check(_activation(x.data_ptr(), out.data_ptr(), x.shape[0], d, x.stride(0), _ACT_IDS[name], int(gated), p0, p1,
+                       _DT[x.dtype], _stream()), f"activation[{name}]")
+    return out
+
+
+def per_token_quant_fp8(x, scale_ub=None):
+    assert x.dim() == 2 and x.stride(1) == 1
+    t, k = x.shape
+    q = torch.empty((t, k), dtype=torch.float8_e4m3fn, device=x.device)
+    sc = torch.empty((t, 1), dtype=torch.float32, device=x.device)
+    _check(_quant_token(x.data_ptr(), x.stride(0), q.data_ptr(), sc.data_ptr(), t, k, _ptr(scale_ub), _DT[x.dtype],
+                        _stream()), "per_token_quant_fp8")
+    return q, sc
+
+
+def scaled_fp8_quant(x, scale=None):
+    """Per-tensor fp8: static with the given scale, dynamic (absmax / 448) when ``scale`` is None."""
+    assert x.dim() == 2 and x.stride(1) == 1
+    t, k = x.shape
+    q = torch.empty((t, k), dtype=torch.float8_e4m3fn, device=x.device)
+    dyn = scale is None
+    sc = torch.empty(1, dtype=torch.float32, device=x.device) if dyn else scale.float().reshape(1).contiguous()
+    _check(_quant_tensor(x.data_ptr(), x.stride(0), q.data_ptr(), sc.data_ptr(), t, k, int(dyn), _DT[x.dtype],
+                         _stream()), "scaled_fp8_quant")
+    return q, sc
+
+
+def _scales_t(t, k, device):
+    ld = (t + 3) // 4 * 4
+    return torch.empty((k // 128, ld), dtype=torch.float32, device=device), ld
+
+
+def rms_norm_group_quant(x, weight, eps, residual=None, group=128, want_out16=False):
+    """(fp8 [T, K], scales [T, K/128] in transposed storage, residual, normalised 16-bit row or None)."""
+    assert group == 128 and x.dim() == 2 and x.stride(1) == 1
+    t, k = x.shape
+    q = torch.empty((t, k), dtype=torch.float8_e4m3fn, device=x.device)
+    st, ld = _scales_t(t, k, x.device)
+    o16 = torch.empty((t, k), dtype=x.dtype, device=x.device) if want_out16 else None
+    _check(_norm_quant(x.data_ptr(), _ptr(residual), weight.data_ptr(), q.data_ptr(), st.data_ptr(), ld, _ptr(o16), t, k,
+                       x.stride(0), eps, _DT[x.dtype], _stream()), "rms_norm_group_quant")
+    return q, st[:, :t].t(), residual, o16
+
+
+def silu_mul_group_quant(x, group=128):
+    assert group == 128 and x.dim() == 2 and x.stride(1) == 1
+    t, d = x.shape[0], x.shape[1] // 2
+    q = torch.empty((t, d), dtype=torch.float8_e4m3fn, device=x.device)
+    st, ld = _scales_t(t, d, x.device)
+    _check(_silu_quant(x.data_ptr(), x.stride(0), q.data_ptr(), st.data_ptr(), ld, t, d, _DT[x.dtype], _stream()),
+           "silu_mul_group_quant")
+    return q, st[:, :t].t()
 
 
 # ---------------------------------------------------------------- GEMM

@@ -401,3 +401,85 @@ def sample_from_logits(logits: torch.Tensor, temperature: torch.Tensor, top_k: t
                 noise[row].exponential_(generator=gen)
     sampled = (probs / noise).argmax(dim=-1)
     return torch.where(greedy, logits.argmax(dim=-1), sampled)
+
+
+# ---------------------------------------------------------------- misc (bitmask, penalties, block copy, activations, quant fusions)
+def apply_token_bitmask(logits: torch.Tensor, bitmask: torch.Tensor, row_idx: torch.Tensor | None = None) -> torch.Tensor:
+    """In place: logits[row, t] = -inf where bit ``t % 32`` of ``bitmask[i, t // 32]`` is clear."""
+    v = logits.shape[-1]
+    shifts = torch.arange(32, device=bitmask.device, dtype=torch.int32)
+    bits = ((bitmask.to(torch.int32)[:, :, None] >> shifts) & 1).reshape(bitmask.shape[0], -1)[:, :v].bool()
+    if row_idx is None:
+        logits.masked_fill_(~bits.to(logits.device), float("-inf"))
+    else:
+        sub = logits[row_idx.long()]
+        sub.masked_fill_(~bits.to(logits.device), float("-inf"))
+        logits[row_idx.long()] = sub
+    return logits
+
+
+def apply_repetition_penalties(logits: torch.Tensor, prompt_seen: torch.Tensor, output_seen: torch.Tensor,
+                               penalty: torch.Tensor) -> torch.Tensor:
+    """In place: seen tokens' logits are divided (if positive) or multiplied (if negative) by the row's penalty."""
+    seen = prompt_seen.bool() | output_seen.bool()
+    p = penalty[:, None].to(logits.dtype)
+    pen = torch.where(logits > 0, logits / p, logits * p)
+    logits.copy_(torch.where(seen, pen, logits))
+    return logits
+
+
+def copy_blocks(cache: torch.Tensor, pairs: torch.Tensor) -> None:
+    """cache[dst] = cache[src] for every (src, dst) row of ``pairs``; dim 0 of ``cache`` indexes blocks."""
+    if pairs.numel():
+        cache[pairs[:, 1].long()] = cache[pairs[:, 0].long()]
+
+
+_ACTS = {
+    "silu": F.silu,
+    "gelu": lambda x: F.gelu(x, approximate="none"),
+    "gelu_tanh": lambda x: F.gelu(x, approximate="tanh"),
+    "gelu_new": lambda x: F.gelu(x, approximate="tanh"),
+    "gelu_fast": lambda x: 0.5 * x * (1.0 + torch.tanh(x * 0.79788456 * (1.0 + 0.044715 * x * x))),
+    "quick_gelu": lambda x: x * torch.sigmoid(1.702 * x),
+    "relu2": lambda x: torch.relu(x) ** 2,
+}
+
+
+def activation(x: torch.Tensor, name: str, gated: bool = False, p0: float = 0.0, p1: float = 0.0) -> torch.Tensor:
+    """``gated``: act(x[:, :d]) * x[:, d:].  ``fatrelu`` thresholds at ``p0``; ``swiglu_oai`` takes interleaved
+    gate/up pairs, clamps at ``p1`` and computes (up + 1) · gate · σ(p0 · gate)."""
+    xf = x.float()
+    if name == "swiglu_oai":
+        g, u = xf[..., ::2].clamp(max=p1), xf[..., 1::2].clamp(-p1, p1)
+        return ((u + 1.0) * g * torch.sigmoid(p0 * g)).to(x.dtype)
+    fn = (lambda t: torch.where(t > p0, t, torch.zeros_like(t))) if name == "fatrelu" else _ACTS[name]
+    if gated:
+        d = x.shape[-1] // 2
+        return (fn(xf[..., :d]) * xf[..., d:]).to(x.dtype)
+    return fn(xf).to(x.dtype)
+
+
+def per_token_quant_fp8(x: torch.Tensor, scale_ub: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """Dynamic per-token fp8: one scale per row → (fp8 [T, K], scales [T, 1])."""
+    amax = x.float().abs().amax(dim=-1, keepdim=True)
+    if scale_ub is not None:
+        amax = amax.clamp(max=float(scale_ub))
+    scale = (amax / FP8_MAX).clamp_min(1.0 / (FP8_MAX * 512.0))
+    q = (x.float() / scale).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return q, scale
+
+
+def rms_norm_group_quant(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor | None = None,
+                         group: int = 128):
+    """RMSNorm (optionally after ``residual += x``) followed by per-token-group fp8 quantisation of the
+    (rounded) normalised row.  Returns (fp8, scales [T, K/group], new residual or None)."""
+    if residual is not None:
+        y, r = fused_add_rms_norm(x, residual, weight, eps)
+    else:
+        y, r = rms_norm(x, weight, eps), None
+    q, s = per_token_group_quant_fp8(y, group)
+    return q, s, r
+
+
+def silu_mul_group_quant(x: torch.Tensor, group: int = 128) -> tuple[torch.Tensor, torch.Tensor]:
+    return per_token_group_quant_fp8(silu_and_mul(x), group)

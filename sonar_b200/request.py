@@ -116,7 +116,7 @@ class Request:
         "arrival_time", "priority", "cache_salt", "lora_name", "client_index", "status", "stop_reason",
         "output_token_ids", "all_token_ids", "num_prompt_tokens", "num_computed_tokens",
         "num_cached_tokens", "spec_token_ids", "max_tokens", "block_hashes", "num_preemptions",
-        "events", "num_output_placeholders", "_hasher")
+        "events", "num_output_placeholders", "_hasher", "grammar")
 
     def __init__(self, core_req: EngineCoreRequest, block_hasher=None) -> None:
         self.request_id = core_req.request_id
@@ -137,6 +137,7 @@ class Request:
         self.num_computed_tokens = 0
         self.num_cached_tokens = -1
         self.spec_token_ids: list[int] = []
+        self.grammar = None  # structured-output matcher, set by the scheduler
         if self.sampling_params is not None:
             assert self.sampling_params.max_tokens is not None
             self.max_tokens = self.sampling_params.max_tokens

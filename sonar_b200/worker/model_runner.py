@@ -25,6 +25,7 @@ from sonar_b200.core.kv_cache_manager import KVCacheConfig, KVCacheSpec
 from sonar_b200.core.scheduler import ModelRunnerOutput, SchedulerOutput
 from sonar_b200.layers.attention import AttentionMetadata
 from sonar_b200.loader import load_model
+from sonar_b200 import ops
 from sonar_b200.logger import init_logger
 from sonar_b200.parallel import state
 from sonar_b200.parallel.tp_ops import get_tp_context
@@ -410,6 +411,18 @@ class ModelRunner:
                 gen = b.generators.get(req_ids[i])
                 if gen is not None:
                     gens[lo + c] = gen
+        if so.grammar_bitmask is not None:
+            # constrained decoding: mask the logits rows of structured requests before any sampling step
+            where = {rid: k for k, rid in enumerate(sample_rids)}
+            pick = [(m, where[rid]) for m, rid in enumerate(so.grammar_req_ids) if rid in where]
+            if pick:
+                bm = torch.from_numpy(np.ascontiguousarray(so.grammar_bitmask[[m for m, _ in pick]]))
+                ridx = torch.tensor([k for _, k in pick], dtype=torch.int32)
+                if self.is_cuda:
+                    bm = bm.pin_memory().to(logits.device, non_blocking=True)
+                    ridx = ridx.to(logits.device)
+                logits = logits.float() if logits.dtype != torch.float32 else logits
+                ops.apply_token_bitmask(logits, bm, ridx)
         mu = {k: b.mirostat_mu[rid] for k, rid in enumerate(sample_rids) if rid in b.mirostat_mu}
         md = make_sampling_metadata(params, prompts, outs_hist, logits.device, gens, mu, sample_rids)
         res = self.sampler(logits, md)

@@ -1,0 +1,149 @@
+"""Numerics of the sampler-side, cache-copy, activation and fp8-fusion kernels against PyTorch fp32."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from sonar_b200.ops import torch_ref as ref  # noqa: E402
+
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def cu():
+    from sonar_b200.ops import cuda
+    return cuda
+
+
+def _deq(q, s, group=128):
+    t, k = q.shape
+    return (q.float().reshape(t, k // group, group) * s.float()[..., None]).reshape(t, k)
+
+
+def test_token_bitmask(cu):
+    torch.manual_seed(0)
+    v = 151936 + 7
+    logits = torch.randn(6, v, device=DEV)
+    words = (v + 31) // 32
+    bm = torch.randint(-2**31, 2**31 - 1, (3, words), dtype=torch.int32, device=DEV)
+    rows = torch.tensor([4, 0, 5], dtype=torch.int32, device=DEV)
+    want = ref.apply_token_bitmask(logits.clone(), bm, rows)
+    got = cu.apply_token_bitmask(logits.clone(), bm, rows)
+    assert torch.equal(torch.isinf(got), torch.isinf(want))
+    assert torch.equal(got[~torch.isinf(got)], want[~torch.isinf(want)])
+    # identity row mapping
+    got2 = cu.apply_token_bitmask(logits[:3].clone(), bm)
+    assert torch.equal(torch.isinf(got2), torch.isinf(ref.apply_token_bitmask(logits[:3].clone(), bm)))
+
+
+def test_repetition_penalties(cu):
+    torch.manual_seed(1)
+    logits = torch.randn(5, 32000, device=DEV)
+    ps = torch.rand(5, 32000, device=DEV) < 0.01
+    os_ = torch.rand(5, 32000, device=DEV) < 0.01
+    pen = torch.tensor([1.0, 1.2, 0.8, 2.0, 1.05], device=DEV)
+    want = ref.apply_repetition_penalties(logits.clone(), ps, os_, pen)
+    got = cu.apply_repetition_penalties(logits.clone(), ps, os_, pen)
+    torch.testing.assert_close(got, want, atol=1e-6, rtol=1e-6)
+
+
+def test_copy_blocks(cu):
+    torch.manual_seed(2)
+    cache = torch.randn(40, 2, 8, 16, 128, device=DEV).to(torch.bfloat16)
+    pairs = torch.tensor([[0, 10], [3, 11], [39, 12]], dtype=torch.int64, device=DEV)
+    want = cache.clone()
+    ref.copy_blocks(want, pairs)
+    cu.copy_blocks(cache, pairs)
+    assert torch.equal(cache, want)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_merge_attn_states(cu, dtype):
+    torch.manual_seed(3)
+    t, h, d = 33, 8, 128
+    a = torch.randn(t, h, d, device=DEV, dtype=dtype)
+    b = torch.randn(t, h, d, device=DEV, dtype=dtype)
+    la = torch.randn(t, h, device=DEV) * 3
+    lb = torch.randn(t, h, device=DEV) * 3
+    lb[0] = float("-inf")                       # an empty partial
+    want_o, want_l = ref.merge_attn_states(a.float(), la, b.float(), lb)
+    got_o, got_l = cu.merge_attn_states(a, la, b, lb)
+    torch.testing.assert_close(got_o.float(), want_o, atol=2e-2, rtol=1e-2)
+    torch.testing.assert_close(got_l, want_l, atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("name,gated,p0,p1", [
+    ("silu", True, 0, 0), ("gelu", True, 0, 0), ("gelu_tanh", True, 0, 0), ("fatrelu", True, 0.1, 0),
+    ("swiglu_oai", True, 1.702, 7.0), ("gelu", False, 0, 0), ("gelu_new", False, 0, 0), ("gelu_fast", False, 0, 0),
+    ("quick_gelu", False, 0, 0), ("relu2", False, 0, 0), ("silu", False, 0, 0)])
+def test_activation_family(cu, name, gated, p0, p1):
+    torch.manual_seed(4)
+    x = torch.randn(19, 2 * 1024, device=DEV, dtype=torch.bfloat16) * 2
+    want = ref.activation(x.float(), name, gated, p0, p1)
+    got = cu.activation(x, name, gated, p0, p1)
+    torch.testing.assert_close(got.float(), want, atol=3e-2, rtol=1.6e-2)
+
+
+def test_per_token_and_per_tensor_fp8_quant(cu):
+    torch.manual_seed(5)
+    x = torch.randn(45, 4096, device=DEV, dtype=torch.bfloat16) * 3
+    q, s = cu.per_token_quant_fp8(x)
+    wq, ws = ref.per_token_quant_fp8(x.float())
+    torch.testing.assert_close(s, ws, atol=0, rtol=1e-6)
+    assert ((q.float() * s) - x.float()).abs().max() <= (x.float().abs().amax(-1, keepdim=True) / 448 * 16 + 1e-3).max()
+    torch.testing.assert_close(q.float() * s, wq.float() * ws, atol=0.3, rtol=0.07)
+    # dynamic per-tensor
+    q2, s2 = cu.scaled_fp8_quant(x)
+    _, ws2 = ref.scaled_fp8_quant(x.float())
+    torch.testing.assert_close(s2, ws2, atol=0, rtol=1e-6)
+    torch.testing.assert_close(q2.float() * s2, x.float(), atol=float(ws2) * 16, rtol=0.07)
+    # static per-tensor
+    sc = torch.tensor([0.05], device=DEV)
+    q3, _ = cu.scaled_fp8_quant(x, sc)
+    wq3, _ = ref.scaled_fp8_quant(x.float(), sc)
+    torch.testing.assert_close(q3.float(), wq3.float(), atol=0.002, rtol=0.13)
+
+
+@pytest.mark.parametrize("hidden", [1024, 4096, 8192])
+@pytest.mark.parametrize("add", [False, True])
+def test_rms_norm_group_quant(cu, hidden, add):
+    torch.manual_seed(6)
+    x = torch.randn(37, hidden, device=DEV, dtype=torch.bfloat16)
+    r = torch.randn(37, hidden, device=DEV, dtype=torch.bfloat16) if add else None
+    w = (torch.rand(hidden, device=DEV) + 0.5).to(torch.bfloat16)
+    rr = r.clone() if add else None
+    q, s, r_out, o16 = cu.rms_norm_group_quant(x, w, 1e-6, rr, want_out16=True)
+    if add:
+        want_y, want_r = ref.fused_add_rms_norm(x, r, w, 1e-6)
+        assert torch.equal(r_out, want_r)
+    else:
+        want_y = ref.rms_norm(x, w, 1e-6)
+    torch.testing.assert_close(o16.float(), want_y.float(), atol=3e-2, rtol=1e-2)
+    # the quantised row reproduces the kernel's own 16-bit row to fp8 precision, scales = group absmax / 448
+    want_s = o16.float().reshape(37, hidden // 128, 128).abs().amax(-1).clamp_min(1e-10) / 448
+    torch.testing.assert_close(s.contiguous(), want_s, atol=0, rtol=1e-6)
+    torch.testing.assert_close(_deq(q, s), o16.float(), atol=0.02, rtol=0.07)
+
+
+def test_silu_mul_group_quant(cu):
+    torch.manual_seed(7)
+    x = torch.randn(50, 2 * 1536, device=DEV, dtype=torch.bfloat16)
+    q, s = cu.silu_mul_group_quant(x)
+    y = cu.silu_and_mul(x)
+    want_s = y.float().reshape(50, 12, 128).abs().amax(-1).clamp_min(1e-10) / 448
+    torch.testing.assert_close(s.contiguous(), want_s, atol=0, rtol=1e-6)
+    torch.testing.assert_close(_deq(q, s), y.float(), atol=0.02, rtol=0.07)
+    want = ref.silu_and_mul(x.float())
+    torch.testing.assert_close(_deq(q, s), want, atol=0.05, rtol=0.08)
+
+
+def test_scaled_mm_fp8_per_token_per_channel(cu):
+    import sonar_b200.ops as ops
+    torch.manual_seed(8)
+    x = torch.randn(70, 1024, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(384, 1024, device=DEV, dtype=torch.bfloat16) * 0.05
+    xq, xs = cu.per_token_quant_fp8(x)
+    wq, wsc = ref.per_token_quant_fp8(w.float())           # per output channel
+    y = ops.scaled_mm_fp8(xq, xs, wq, wsc)
+    want = x.float() @ w.float().t()
+    assert (y.float() - want).norm() / want.norm() < 0.06

@@ -279,6 +279,18 @@ class SpeculativeConfig:
 
 
 @dataclass
+class LoRAConfig:
+    enable_lora: bool = False
+    max_loras: int = 4
+    max_lora_rank: int = 64
+    lora_modules: dict[str, str] = field(default_factory=dict)     # name → adapter directory, loaded at start
+
+    def __post_init__(self) -> None:
+        if self.max_lora_rank % 8 or not 8 <= self.max_lora_rank <= 256:
+            raise ValueError("max_lora_rank must be a multiple of 8 in [8, 256]")
+
+
+@dataclass
 class ObservabilityConfig:
     log_stats: bool = False
     trace_file: str | None = None
@@ -293,6 +305,8 @@ class EngineConfig:
     scheduler: SchedulerConfig
     speculative: SpeculativeConfig = field(default_factory=SpeculativeConfig)
     observability: ObservabilityConfig = field(default_factory=ObservabilityConfig)
+    lora: LoRAConfig = field(default_factory=LoRAConfig)
+    enable_sleep_mode: bool = False
     enforce_eager: bool = False
     device: str = "auto"               # auto | cuda | cpu
 
@@ -350,7 +364,13 @@ class EngineArgs:
     # speculative
     speculative_method: str | None = None
     num_speculative_tokens: int = 0
+    # LoRA
+    enable_lora: bool = False
+    max_loras: int = 4
+    max_lora_rank: int = 64
+    lora_modules: dict | None = None
     # misc
+    enable_sleep_mode: bool = False
     enforce_eager: bool = False
     device: str = "auto"
     disable_log_stats: bool = True
@@ -401,8 +421,11 @@ class EngineArgs:
         spec = SpeculativeConfig(method=self.speculative_method,
                                  num_speculative_tokens=self.num_speculative_tokens)
         obs = ObservabilityConfig(log_stats=not self.disable_log_stats, trace_file=self.trace_file)
+        lora = LoRAConfig(enable_lora=self.enable_lora or bool(self.lora_modules), max_loras=self.max_loras,
+                          max_lora_rank=self.max_lora_rank, lora_modules=dict(self.lora_modules or {}))
         return EngineConfig(model=model, cache=cache, parallel=parallel, scheduler=sched,
-                            speculative=spec, observability=obs,
+                            speculative=spec, observability=obs, lora=lora,
+                            enable_sleep_mode=self.enable_sleep_mode,
                             enforce_eager=self.enforce_eager, device=device)
 
     # CLI ------------------------------------------------------------------
@@ -414,7 +437,7 @@ class EngineArgs:
                 continue  # positional / --model handled by the caller
             if f.type in ("bool", bool):
                 parser.add_argument(flag, action=argparse.BooleanOptionalAction, default=f.default)
-            elif f.name == "hf_overrides":
+            elif f.name in ("hf_overrides", "lora_modules"):
                 parser.add_argument(flag, type=json.loads, default=None)
             else:
                 base = str(f.type).replace(" | None", "")

@@ -171,6 +171,30 @@ class AsyncLLM:
     async def collective_rpc(self, method: str, *args, **kwargs):
         return await self.core.call_utility_async("collective_rpc", method, *args, **kwargs)
 
+    async def sleep(self, level: int = 1) -> int:
+        return await self.core.call_utility_async("sleep", level)
+
+    async def wake_up(self, tags: list[str] | None = None) -> int:
+        return await self.core.call_utility_async("wake_up", tags)
+
+    async def is_sleeping(self) -> bool:
+        return await self.core.call_utility_async("is_sleeping")
+
+    async def start_profile(self, trace_dir: str | None = None) -> bool:
+        return await self.core.call_utility_async("start_profile", trace_dir)
+
+    async def stop_profile(self):
+        return await self.core.call_utility_async("stop_profile")
+
+    async def add_lora(self, name: str, path: str) -> bool:
+        return await self.core.call_utility_async("add_lora", name, path)
+
+    async def remove_lora(self, name: str) -> bool:
+        return await self.core.call_utility_async("remove_lora", name)
+
+    async def list_loras(self) -> list[str]:
+        return await self.core.call_utility_async("list_loras")
+
     async def get_stats(self) -> dict:
         return await self.core.call_utility_async("get_stats")
 

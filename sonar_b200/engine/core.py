@@ -41,6 +41,7 @@ class EngineCore:
                                    structured_output_manager=structured)
         self.tracer = get_tracer(cfg.observability.trace_file)
         self.paused = False
+        self.sleeping = False
         self.steps = 0
         self.host_time = {"schedule": 0.0, "execute": 0.0, "update": 0.0}
         logger.info("engine core ready in %.1fs (%d KV blocks of %d tokens)", time.time() - t0,
@@ -57,7 +58,7 @@ class EngineCore:
         return self.scheduler.has_unfinished_requests()
 
     def step(self) -> EngineCoreOutputs:
-        if self.paused or not self.scheduler.has_requests():
+        if self.paused or self.sleeping or not self.scheduler.has_requests():
             return EngineCoreOutputs()
         t0 = time.perf_counter()
         with self.tracer.span("schedule"):
@@ -87,6 +88,39 @@ class EngineCore:
 
     def collective_rpc(self, method: str, *args, **kwargs) -> list[Any]:
         return self.executor.collective_rpc(method, *args, **kwargs)
+
+    def sleep(self, level: int = 1) -> int:
+        """Release GPU memory while idle.  The KV cache does not survive, so running requests are
+        refused and the prefix cache is reset."""
+        if self.scheduler.has_unfinished_requests():
+            raise ValueError("cannot sleep with unfinished requests (abort or drain them first)")
+        self.scheduler.reset_prefix_cache()
+        freed = sum(self.executor.collective_rpc("sleep", level))
+        self.sleeping = True
+        return freed
+
+    def wake_up(self, tags: list[str] | None = None) -> int:
+        n = sum(self.executor.collective_rpc("wake_up", tags))
+        self.sleeping = any(self.executor.collective_rpc("is_sleeping"))
+        return n
+
+    def is_sleeping(self) -> bool:
+        return self.sleeping
+
+    def start_profile(self, trace_dir: str | None = None) -> bool:
+        return all(self.executor.collective_rpc("start_profile", trace_dir))
+
+    def stop_profile(self) -> list[str | None]:
+        return self.executor.collective_rpc("stop_profile")
+
+    def add_lora(self, name: str, path: str) -> bool:
+        return all(self.executor.collective_rpc("add_lora", name, path))
+
+    def remove_lora(self, name: str) -> bool:
+        return all(self.executor.collective_rpc("remove_lora", name))
+
+    def list_loras(self) -> list[str]:
+        return self.executor.collective_rpc("list_loras")[0]
 
     def get_stats(self) -> dict:
         s = self.scheduler.make_stats()

@@ -154,6 +154,30 @@ class LLMEngine:
     def collective_rpc(self, method: str, *args, **kwargs):
         return self.core.call_utility("collective_rpc", method, *args, **kwargs)
 
+    def sleep(self, level: int = 1) -> int:
+        return self.core.call_utility("sleep", level)
+
+    def wake_up(self, tags: list[str] | None = None) -> int:
+        return self.core.call_utility("wake_up", tags)
+
+    def is_sleeping(self) -> bool:
+        return self.core.call_utility("is_sleeping")
+
+    def start_profile(self, trace_dir: str | None = None) -> bool:
+        return self.core.call_utility("start_profile", trace_dir)
+
+    def stop_profile(self):
+        return self.core.call_utility("stop_profile")
+
+    def add_lora(self, name: str, path: str) -> bool:
+        return self.core.call_utility("add_lora", name, path)
+
+    def remove_lora(self, name: str) -> bool:
+        return self.core.call_utility("remove_lora", name)
+
+    def list_loras(self) -> list[str]:
+        return self.core.call_utility("list_loras")
+
     def get_stats(self) -> dict:
         return self.core.call_utility("get_stats")
 

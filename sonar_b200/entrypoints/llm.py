@@ -27,12 +27,13 @@ class LLM:
         self.llm_engine = LLMEngine.from_engine_args(self.engine_args, multiprocess=multiprocess,
                                                      executor_class=executor_class)
         self._counter = itertools.count()
+        self._known_loras: set[str] = set()
 
     def get_tokenizer(self):
         return self.llm_engine.tokenizer
 
     # ------------------------------------------------------------------
-    def _enqueue(self, prompts, params, priority: Sequence[int] | None = None) -> list[str]:
+    def _enqueue(self, prompts, params, priority: Sequence[int] | None = None, lora_request=None) -> list[str]:
         if isinstance(prompts, (str, dict)) or (isinstance(prompts, list) and prompts and isinstance(prompts[0], int)):
             prompts = [prompts]
         if not isinstance(params, (list, tuple)):
@@ -45,7 +46,12 @@ class LLM:
             if isinstance(p, SamplingParams):
                 p = p.clone()
                 p.output_kind = RequestOutputKind.FINAL_ONLY
-            self.llm_engine.add_request(rid, prompt, p, priority=priority[i] if priority else 0)
+            lr = lora_request[i] if isinstance(lora_request, (list, tuple)) else lora_request
+            if lr is not None and lr.lora_name not in self._known_loras:
+                self.llm_engine.add_lora(lr.lora_name, lr.lora_path)
+                self._known_loras.add(lr.lora_name)
+            self.llm_engine.add_request(rid, prompt, p, priority=priority[i] if priority else 0,
+                                        lora_name=lr.lora_name if lr is not None else None)
             ids.append(rid)
         return ids
 
@@ -58,10 +64,12 @@ class LLM:
         return [done[i] for i in ids if i in done]
 
     def generate(self, prompts, sampling_params: SamplingParams | Sequence[SamplingParams] | None = None,
-                 priority: Sequence[int] | None = None, use_tqdm: bool = False) -> list[RequestOutput]:
+                 priority: Sequence[int] | None = None, use_tqdm: bool = False,
+                 lora_request=None) -> list[RequestOutput]:
+        """``lora_request``: one ``LoRARequest`` for every prompt, or a list with one (or None) per prompt."""
         if sampling_params is None:
             sampling_params = SamplingParams()
-        return self._run_engine(self._enqueue(prompts, sampling_params, priority))
+        return self._run_engine(self._enqueue(prompts, sampling_params, priority, lora_request))
 
     def chat(self, messages, sampling_params: SamplingParams | None = None, chat_template: str | None = None,
              add_generation_prompt: bool = True, tools: list[dict] | None = None) -> list[RequestOutput]:

@@ -49,11 +49,20 @@ def _usage(n_prompt: int, n_out: int, cached: int = 0) -> P.UsageInfo:
 
 
 class ServingState:
-    def __init__(self, engine: AsyncLLM, served_name: str, api_key: str | None) -> None:
+    def __init__(self, engine: AsyncLLM, served_name: str, api_key: str | None,
+                 reasoning_parser: str | None = None, tool_parser: str | None = None) -> None:
+        from sonar_b200.entrypoints.parsers import get_reasoning_parser, get_tool_parser
         self.engine = engine
         self.name = served_name
         self.api_key = api_key
         self.start = time.time()
+        self.lora_names: set[str] = set(engine.cfg.lora.lora_modules)
+        self.reasoning_parser = get_reasoning_parser(reasoning_parser)
+        self.tool_parser = get_tool_parser(tool_parser)
+
+    def lora_for(self, model: str | None) -> str | None:
+        """A request's ``model`` field names either the base model or a loaded adapter."""
+        return model if model in self.lora_names else None
 
     @property
     def tokenizer(self):
@@ -100,8 +109,26 @@ def build_app(state: ServingState) -> FastAPI:
 
     @app.get("/v1/models")
     async def models():
-        return {"object": "list", "data": [{"id": state.name, "object": "model", "created": int(state.start),
-                                            "owned_by": "sonar_b200", "max_model_len": state.max_model_len}]}
+        base = {"id": state.name, "object": "model", "created": int(state.start), "owned_by": "sonar_b200",
+                "max_model_len": state.max_model_len}
+        adapters = [{"id": n, "object": "model", "created": int(state.start), "owned_by": "sonar_b200",
+                     "parent": state.name} for n in sorted(state.lora_names)]
+        return {"object": "list", "data": [base] + adapters}
+
+    @app.post("/invocations")
+    async def invocations(raw: Request):
+        """SageMaker-style single entry point: dispatch on the body's shape."""
+        body = await raw.json()
+        try:
+            if "messages" in body:
+                return await chat(P.ChatCompletionRequest(**body), raw)
+            if "prompt" in body:
+                return await completions(P.CompletionRequest(**body), raw)
+            if "input" in body:
+                return await embeddings(P.EmbeddingRequest(**body))
+        except Exception as e:  # noqa: BLE001  (pydantic validation included)
+            return _error(str(e))
+        return _error("body must contain messages, prompt or input")
 
     @app.get("/metrics")
     async def metrics():
@@ -170,7 +197,8 @@ def build_app(state: ServingState) -> FastAPI:
         gens = []
         try:
             for i, p in enumerate(prompts):
-                gens.append(state.engine.generate(p, sp, f"{rid}-{i}", priority=req.priority))
+                gens.append(state.engine.generate(p, sp, f"{rid}-{i}", priority=req.priority,
+                                                  lora_name=state.lora_for(req.model)))
         except ValueError as e:
             return _error(str(e))
 
@@ -265,14 +293,28 @@ def build_app(state: ServingState) -> FastAPI:
         rid = f"chatcmpl-{uuid.uuid4().hex}"
         model = req.model or state.name
         try:
-            gen = state.engine.generate(prompt, sp, rid, priority=req.priority)
+            gen = state.engine.generate(prompt, sp, rid, priority=req.priority, lora_name=state.lora_for(req.model))
         except ValueError as e:
             return _error(str(e))
+        rp = state.reasoning_parser
+        tp_ = state.tool_parser if (req.tools and req.tool_choice != "none") else None
+
+        def split_message(text: str) -> P.ChatResponseMessage:
+            reasoning, content = rp.extract(text) if rp is not None else (None, text)
+            calls = None
+            if tp_ is not None and content:
+                ext = tp_.extract(content)
+                if ext.tool_calls:
+                    content, calls = ext.content, [c.to_openai() for c in ext.tool_calls]
+            return P.ChatResponseMessage(content=content, reasoning_content=reasoning, tool_calls=calls)
 
         if req.stream:
             async def sse() -> AsyncGenerator[str, None]:
                 created = int(time.time())
                 first = {i: True for i in range(sp.n)}
+                seen = {i: "" for i in range(sp.n)}          # raw text so far, per choice
+                seen_content = {i: "" for i in range(sp.n)}  # visible content so far (after reasoning split)
+                n_tool = {i: 0 for i in range(sp.n)}
                 n_prompt = n_out = 0
                 try:
                     async for out in gen:
@@ -280,11 +322,31 @@ def build_app(state: ServingState) -> FastAPI:
                         for c in out.outputs:
                             n_out += len(c.token_ids)
                             delta: dict[str, Any] = {"content": c.text}
+                            if rp is not None or tp_ is not None:
+                                r_d, c_d = rp.extract_streaming(seen[c.index], c.text) if rp else (None, c.text)
+                                seen[c.index] += c.text
+                                delta = {}
+                                if r_d:
+                                    delta["reasoning_content"] = r_d
+                                if c_d and tp_ is not None:
+                                    c_d2, calls = tp_.extract_streaming(seen_content[c.index], c_d)
+                                    seen_content[c.index] += c_d
+                                    c_d = c_d2
+                                    if calls:
+                                        delta["tool_calls"] = [dict(cl.to_openai(), index=n_tool[c.index] + k)
+                                                               for k, cl in enumerate(calls)]
+                                        n_tool[c.index] += len(calls)
+                                if c_d:
+                                    delta["content"] = c_d
+                                if not delta and c.finish_reason is None and not first[c.index]:
+                                    continue
                             if first[c.index]:
                                 delta["role"] = "assistant"
                                 first[c.index] = False
-                            choice: dict[str, Any] = {"index": c.index, "delta": delta,
-                                                      "finish_reason": c.finish_reason}
+                            fr = c.finish_reason
+                            if fr == "stop" and n_tool[c.index]:
+                                fr = "tool_calls"
+                            choice: dict[str, Any] = {"index": c.index, "delta": delta, "finish_reason": fr}
                             lp = _chat_logprobs(c)
                             if lp is not None:
                                 choice["logprobs"] = lp.model_dump()
@@ -309,9 +371,12 @@ def build_app(state: ServingState) -> FastAPI:
                 final = out
         except ValueError as e:
             return _error(str(e))
-        choices = [P.ChatChoice(index=c.index, message=P.ChatResponseMessage(content=c.text),
-                                finish_reason=c.finish_reason, stop_reason=c.stop_reason, logprobs=_chat_logprobs(c))
-                   for c in final.outputs]
+        choices = []
+        for c in final.outputs:
+            msg = split_message(c.text)
+            fr = "tool_calls" if (msg.tool_calls and c.finish_reason == "stop") else c.finish_reason
+            choices.append(P.ChatChoice(index=c.index, message=msg, finish_reason=fr, stop_reason=c.stop_reason,
+                                        logprobs=_chat_logprobs(c)))
         n_out = sum(len(c.token_ids) for c in final.outputs)
         return P.ChatCompletionResponse(id=rid, model=model, choices=choices,
                                         usage=_usage(len(final.prompt_token_ids or []), n_out, final.num_cached_tokens))
@@ -402,6 +467,9 @@ def build_app(state: ServingState) -> FastAPI:
     async def is_paused():
         return {"is_paused": await state.engine.is_paused()}
 
+    from sonar_b200.entrypoints.openai import extra_routes
+    extra_routes.register(app, state)
+
     @app.post("/collective_rpc")
     async def collective_rpc(body: dict):
         res = await state.engine.collective_rpc(body["method"], *body.get("args", []), **body.get("kwargs", {}))
@@ -418,6 +486,9 @@ def make_arg_parser(parser: argparse.ArgumentParser | None = None) -> argparse.A
     parser.add_argument("--port", type=int, default=envs.SONAR_PORT)
     parser.add_argument("--api-key", default=envs.SONAR_API_KEY)
     parser.add_argument("--uvicorn-log-level", default="warning")
+    parser.add_argument("--reasoning-parser", default=None, help="split think blocks into reasoning_content")
+    parser.add_argument("--tool-call-parser", default=None, help="extract function calls from chat output")
+    parser.add_argument("--enable-auto-tool-choice", action="store_true")
     EngineArgs.add_cli_args(parser)
     return parser
 
@@ -427,7 +498,8 @@ def run_server(ns: argparse.Namespace) -> None:
     ns.model = ns.model or ns.model_tag or "tiny-llama"
     args = EngineArgs.from_cli_args(ns)
     engine = AsyncLLM.from_engine_args(args)
-    state = ServingState(engine, args.served_model_name or args.model, ns.api_key)
+    state = ServingState(engine, args.served_model_name or args.model, ns.api_key,
+                         getattr(ns, "reasoning_parser", None), getattr(ns, "tool_call_parser", None))
     app = build_app(state)
     logger.info("serving %s on http://%s:%d", state.name, ns.host, ns.port)
     uvicorn.run(app, host=ns.host, port=ns.port, log_level=ns.uvicorn_log_level)

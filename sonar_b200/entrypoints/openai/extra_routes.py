@@ -1,0 +1,242 @@
+"""Management and pooling routes of the HTTP server.
+
+* LoRA: ``/v1/load_lora_adapter``, ``/v1/unload_lora_adapter`` (adapters then appear under ``/v1/models``
+  and are selected by passing their name as ``model``).
+* Sleep mode: ``/sleep``, ``/wake_up``, ``/is_sleeping``.
+* Profiler: ``/start_profile``, ``/stop_profile``.
+* Pooling family on top of the embedding path: ``/pooling``, ``/score`` + ``/v1/score``,
+  ``/rerank`` + ``/v1/rerank`` + ``/v2/rerank``, ``/classify``.
+* ``/v1/responses`` (the Responses API shape over chat), ``/invocations`` (SageMaker-style dispatch),
+  ``/v1/chat/completions/render`` and ``/v1/completions/render`` (prompt rendering only).
+
+Parity: routers under ``aphrodite/entrypoints/serve/*`` (lora, sleep, profile, cache, rpc),
+``entrypoints/pooling/*`` (embed / score / rerank / classify), ``entrypoints/openai/responses`` and
+``entrypoints/sagemaker``.
+"""
+from __future__ import annotations
+
+import time
+import uuid
+from typing import Any
+
+import torch
+from fastapi import FastAPI
+from fastapi.responses import JSONResponse
+
+from sonar_b200.sampling_params import PoolingParams, SamplingParams
+from sonar_b200.utils.tokenizer import apply_chat_template
+
+
+def _error(msg: str, code: int = 400, typ: str = "BadRequestError") -> JSONResponse:
+    return JSONResponse({"error": {"message": msg, "type": typ, "code": code}}, status_code=code)
+
+
+async def _embed(state, text_or_ids) -> tuple[torch.Tensor, int]:
+    rid = f"pool-{uuid.uuid4().hex}"
+    final = await state.engine.encode(text_or_ids, PoolingParams(), rid)
+    vec = final.outputs.data
+    vec = vec.float() if isinstance(vec, torch.Tensor) else torch.tensor(list(vec), dtype=torch.float32)
+    return vec, len(final.prompt_token_ids or [])
+
+
+def register(app: FastAPI, state) -> None:
+    # ------------------------------------------------------------------ LoRA
+    @app.post("/v1/load_lora_adapter")
+    async def load_lora(body: dict):
+        name, path = body.get("lora_name"), body.get("lora_path")
+        if not name or not path:
+            return _error("lora_name and lora_path are required")
+        try:
+            await state.engine.add_lora(name, path)
+        except Exception as e:  # noqa: BLE001
+            return _error(str(e))
+        state.lora_names.add(name)
+        return {"status": "ok", "lora_name": name}
+
+    @app.post("/v1/unload_lora_adapter")
+    async def unload_lora(body: dict):
+        name = body.get("lora_name")
+        if name not in state.lora_names:
+            return _error(f"adapter {name!r} is not loaded", 404, "NotFoundError")
+        await state.engine.remove_lora(name)
+        state.lora_names.discard(name)
+        return {"status": "ok", "lora_name": name}
+
+    # ------------------------------------------------------------------ sleep mode
+    @app.post("/sleep")
+    async def sleep(level: int = 1):
+        try:
+            freed = await state.engine.sleep(level)
+        except Exception as e:  # noqa: BLE001
+            return _error(str(e))
+        return {"sleeping": True, "freed_bytes": freed}
+
+    @app.post("/wake_up")
+    async def wake_up(tags: str | None = None):
+        try:
+            n = await state.engine.wake_up(tags.split(",") if tags else None)
+        except Exception as e:  # noqa: BLE001
+            return _error(str(e))
+        return {"sleeping": await state.engine.is_sleeping(), "mapped_bytes": n}
+
+    @app.get("/is_sleeping")
+    async def is_sleeping():
+        return {"is_sleeping": await state.engine.is_sleeping()}
+
+    # ------------------------------------------------------------------ profiler
+    @app.post("/start_profile")
+    async def start_profile(body: dict | None = None):
+        ok = await state.engine.start_profile((body or {}).get("trace_dir"))
+        return {"profiling": bool(ok)}
+
+    @app.post("/stop_profile")
+    async def stop_profile():
+        return {"traces": await state.engine.stop_profile()}
+
+    # ------------------------------------------------------------------ pooling family
+    @app.post("/pooling")
+    async def pooling(body: dict):
+        inputs = body.get("input")
+        if inputs is None:
+            return _error("input is required")
+        if isinstance(inputs, str) or (inputs and isinstance(inputs[0], int)):
+            inputs = [inputs]
+        data, used = [], 0
+        for i, item in enumerate(inputs):
+            vec, n = await _embed(state, item if isinstance(item, str) else {"prompt_token_ids": list(item)})
+            data.append({"index": i, "object": "pooling", "data": vec.tolist()})
+            used += n
+        return {"id": f"pool-{uuid.uuid4().hex}", "object": "list", "model": body.get("model", state.name),
+                "data": data, "usage": {"prompt_tokens": used, "total_tokens": used}}
+
+    async def _scores(query, docs: list) -> tuple[list[float], int]:
+        qv, used = await _embed(state, query)
+        out = []
+        for d in docs:
+            dv, n = await _embed(state, d)
+            used += n
+            out.append(float(torch.dot(qv, dv)))     # embeddings are L2-normalised: cosine similarity
+        return out, used
+
+    async def score(body: dict):
+        t1, t2 = body.get("text_1"), body.get("text_2")
+        if t1 is None or t2 is None:
+            return _error("text_1 and text_2 are required")
+        docs = [t2] if isinstance(t2, str) else list(t2)
+        if isinstance(t1, list):
+            if len(t1) != len(docs):
+                return _error("text_1 and text_2 lists must have equal length")
+            vals, used = [], 0
+            for a, b in zip(t1, docs):
+                v, n = await _scores(a, [b])
+                vals += v
+                used += n
+        else:
+            vals, used = await _scores(t1, docs)
+        return {"id": f"score-{uuid.uuid4().hex}", "object": "list", "model": body.get("model", state.name),
+                "data": [{"index": i, "object": "score", "score": s} for i, s in enumerate(vals)],
+                "usage": {"prompt_tokens": used, "total_tokens": used}}
+
+    async def rerank(body: dict):
+        query, docs = body.get("query"), body.get("documents")
+        if query is None or not docs:
+            return _error("query and documents are required")
+        texts = [d if isinstance(d, str) else d.get("text", "") for d in docs]
+        vals, used = await _scores(query, texts)
+        order = sorted(range(len(vals)), key=lambda i: vals[i], reverse=True)
+        top_n = int(body.get("top_n") or len(order))
+        return {"id": f"rerank-{uuid.uuid4().hex}", "model": body.get("model", state.name),
+                "results": [{"index": i, "document": {"text": texts[i]}, "relevance_score": vals[i]}
+                            for i in order[:top_n]],
+                "usage": {"total_tokens": used}}
+
+    for path in ("/score", "/v1/score"):
+        app.post(path)(score)
+    for path in ("/rerank", "/v1/rerank", "/v2/rerank"):
+        app.post(path)(rerank)
+
+    @app.post("/classify")
+    async def classify(body: dict):
+        """Class probabilities from the LM head at the last position over ``labels`` (token strings):
+        a generative model used as a zero-shot classifier."""
+        inputs, labels = body.get("input"), body.get("labels")
+        tok = state.tokenizer
+        if inputs is None or not labels or tok is None:
+            return _error("input and labels are required (and a tokenizer)")
+        if isinstance(inputs, str):
+            inputs = [inputs]
+        label_ids = [tok.encode(lb, add_special_tokens=False)[0] for lb in labels]
+        data = []
+        import math
+        for i, text in enumerate(inputs):
+            sp = SamplingParams(max_tokens=1, temperature=0.0, logprobs=min(len(label_ids), 20),
+                                allowed_token_ids=label_ids)
+            final = None
+            async for out in state.engine.generate(text, sp, f"cls-{uuid.uuid4().hex}"):
+                final = out
+            lps = final.outputs[0].logprobs[0] if final.outputs[0].logprobs else {}
+            raw = [math.exp(lps[t].logprob) if t in lps else 0.0 for t in label_ids]
+            z = sum(raw) or 1.0
+            probs = [r / z for r in raw]
+            best = max(range(len(labels)), key=lambda k: probs[k])
+            data.append({"index": i, "label": labels[best], "probs": probs, "num_classes": len(labels)})
+        return {"id": f"classify-{uuid.uuid4().hex}", "object": "list", "model": body.get("model", state.name),
+                "data": data}
+
+    # ------------------------------------------------------------------ prompt rendering only
+    @app.post("/v1/chat/completions/render")
+    async def render_chat(body: dict):
+        tok = state.tokenizer
+        if tok is None:
+            return _error("rendering needs a tokenizer")
+        prompt = apply_chat_template(tok, body.get("messages", []), body.get("add_generation_prompt", True),
+                                     body.get("chat_template"), body.get("tools"))
+        return {"prompt": prompt, "prompt_token_ids": tok.encode(prompt)}
+
+    @app.post("/v1/completions/render")
+    async def render_completion(body: dict):
+        tok = state.tokenizer
+        prompt = body.get("prompt", "")
+        ids = prompt if isinstance(prompt, list) else (tok.encode(prompt) if tok is not None else None)
+        return {"prompt": prompt if isinstance(prompt, str) else None, "prompt_token_ids": ids}
+
+    # ------------------------------------------------------------------ Responses API
+    @app.post("/v1/responses")
+    async def responses(body: dict):
+        tok = state.tokenizer
+        if tok is None:
+            return _error("responses need a tokenizer")
+        inp = body.get("input", "")
+        msgs: list[dict[str, Any]] = []
+        if body.get("instructions"):
+            msgs.append({"role": "system", "content": body["instructions"]})
+        if isinstance(inp, str):
+            msgs.append({"role": "user", "content": inp})
+        else:
+            for item in inp:
+                content = item.get("content", "")
+                if isinstance(content, list):
+                    content = "".join(p.get("text", "") for p in content if isinstance(p, dict))
+                msgs.append({"role": item.get("role", "user"), "content": content})
+        prompt = apply_chat_template(tok, msgs, True)
+        sp = SamplingParams(max_tokens=int(body.get("max_output_tokens") or 256),
+                            temperature=float(body.get("temperature", 1.0)), top_p=float(body.get("top_p", 1.0)))
+        rid = f"resp_{uuid.uuid4().hex}"
+        final = None
+        async for out in state.engine.generate(prompt, sp, rid):
+            final = out
+        c = final.outputs[0]
+        text, reasoning = c.text, None
+        if state.reasoning_parser is not None:
+            reasoning, text = state.reasoning_parser.extract(c.text)
+        output = []
+        if reasoning:
+            output.append({"type": "reasoning", "id": f"rs_{uuid.uuid4().hex}",
+                           "content": [{"type": "reasoning_text", "text": reasoning}]})
+        output.append({"type": "message", "id": f"msg_{uuid.uuid4().hex}", "role": "assistant", "status": "completed",
+                       "content": [{"type": "output_text", "text": text or "", "annotations": []}]})
+        n_in, n_out = len(final.prompt_token_ids or []), len(c.token_ids)
+        return {"id": rid, "object": "response", "created_at": int(time.time()), "status": "completed",
+                "model": body.get("model", state.name), "output": output, "output_text": text or "",
+                "incomplete_details": {"reason": "max_output_tokens"} if c.finish_reason == "length" else None,
+                "usage": {"input_tokens": n_in, "output_tokens": n_out, "total_tokens": n_in + n_out}}

@@ -1,0 +1,246 @@
+"""Tool-call and reasoning parsers for chat completions.
+
+A *reasoning parser* splits model text into ``reasoning_content`` (the chain of thought between a
+model family's think markers) and the visible ``content``.  A *tool parser* pulls structured
+function calls out of the visible text.  Both work on complete text and incrementally on streamed
+deltas (``extract_streaming`` is fed the text so far plus the new delta and returns what to emit).
+
+Registries are keyed by the names users pass as ``--reasoning-parser`` / ``--tool-call-parser``.
+
+Parity: ``aphrodite/reasoning/*`` (``ReasoningParserManager``, deepseek_r1 / qwen3 parsers) and
+``aphrodite/tool_parsers/*`` (``ToolParserManager``; hermes, llama3_json, mistral, pythonic formats).
+"""
+from __future__ import annotations
+
+import ast
+import json
+import re
+import uuid
+from dataclasses import dataclass, field
+
+
+# ------------------------------------------------------------------ reasoning
+class ReasoningParser:
+    start = "<think>"
+    end = "</think>"
+    #: the chat template already opened the think block, so output starts inside it
+    starts_open = False
+
+    def extract(self, text: str) -> tuple[str | None, str | None]:
+        """→ (reasoning_content, content)."""
+        s, e = self.start, self.end
+        if s in text:
+            pre, _, rest = text.partition(s)
+        elif self.starts_open or e in text:
+            pre, rest = "", text
+        else:
+            return None, text
+        if e in rest:
+            reasoning, _, content = rest.partition(e)
+            content = pre + content
+            return reasoning, (content if content else None)
+        return rest, (pre or None)
+
+    def _extract_held(self, text: str) -> tuple[str, str]:
+        """``extract`` with a partial marker at the very end (e.g. ``</thi``) held back."""
+        r, c = self.extract(text)
+        r, c = r or "", c or ""
+        for marker in (self.start, self.end):
+            for k in range(len(marker) - 1, 0, -1):
+                if text.endswith(marker[:k]):
+                    if r.endswith(marker[:k]) and not c:
+                        r = r[:-k]
+                    elif c.endswith(marker[:k]):
+                        c = c[:-k]
+                    return r, c
+        return r, c
+
+    def extract_streaming(self, previous: str, delta: str) -> tuple[str | None, str | None]:
+        """→ (reasoning delta, content delta) for the new ``delta`` given the text before it."""
+        r_prev, c_prev = self._extract_held(previous) if previous else ("", "")
+        r_now, c_now = self._extract_held(previous + delta)
+        dr = r_now[len(r_prev):] if r_now.startswith(r_prev) else r_now
+        dc = c_now[len(c_prev):] if c_now.startswith(c_prev) else c_now
+        return (dr or None), (dc or None)
+
+
+class DeepSeekR1ReasoningParser(ReasoningParser):
+    """The template opens ``<think>`` itself: everything before ``</think>`` is reasoning."""
+    starts_open = True
+
+
+class Qwen3ReasoningParser(ReasoningParser):
+    """``<think> … </think>`` explicitly in the output; text without markers is plain content."""
+
+
+class GraniteReasoningParser(ReasoningParser):
+    start = "Here is my thought process:"
+    end = "Here is my response:"
+
+
+REASONING_PARSERS: dict[str, type[ReasoningParser]] = {
+    "deepseek_r1": DeepSeekR1ReasoningParser, "deepseek_v3": DeepSeekR1ReasoningParser,
+    "qwen3": Qwen3ReasoningParser, "granite": GraniteReasoningParser, "think": ReasoningParser,
+}
+
+
+# ------------------------------------------------------------------ tools
+@dataclass
+class ToolCall:
+    name: str
+    arguments: str                       # JSON text
+    id: str = field(default_factory=lambda: f"call_{uuid.uuid4().hex[:24]}")
+
+    def to_openai(self) -> dict:
+        return {"id": self.id, "type": "function", "function": {"name": self.name, "arguments": self.arguments}}
+
+
+@dataclass
+class ExtractedTools:
+    content: str | None
+    tool_calls: list[ToolCall]
+
+
+def _call_from_obj(obj) -> ToolCall | None:
+    if not isinstance(obj, dict) or "name" not in obj:
+        return None
+    args = obj.get("arguments", obj.get("parameters", {}))
+    return ToolCall(str(obj["name"]), args if isinstance(args, str) else json.dumps(args, ensure_ascii=False))
+
+
+class ToolParser:
+    def extract(self, text: str) -> ExtractedTools:
+        raise NotImplementedError
+
+    def extract_streaming(self, previous: str, delta: str) -> tuple[str | None, list[ToolCall]]:
+        """Plain text is streamed until a call opens; completed calls are emitted once each."""
+        before = self.extract(previous) if previous else ExtractedTools(None, [])
+        now = self.extract(previous + delta)
+        new_calls = now.tool_calls[len(before.tool_calls):]
+        pc, nc = before.content or "", now.content or ""
+        return ((nc[len(pc):] or None) if nc.startswith(pc) else (nc or None)), new_calls
+
+
+class HermesToolParser(ToolParser):
+    """``<tool_call>{"name": …, "arguments": {…}}</tool_call>`` (Hermes, Qwen2.5 / Qwen3)."""
+    _re = re.compile(r"<tool_call>\s*(.*?)\s*</tool_call>", re.S)
+
+    def extract(self, text: str) -> ExtractedTools:
+        calls = []
+        for m in self._re.finditer(text):
+            try:
+                c = _call_from_obj(json.loads(m.group(1)))
+            except json.JSONDecodeError:
+                c = None
+            if c:
+                calls.append(c)
+        content = self._re.sub("", text)
+        cut = content.find("<tool_call>")          # an unfinished call is withheld
+        if cut >= 0:
+            content = content[:cut]
+        for k in range(len("<tool_call>") - 1, 0, -1):
+            if content.endswith("<tool_call>"[:k]):
+                content = content[:-k]
+                break
+        return ExtractedTools(content.strip() or None if calls else (content or None), calls)
+
+
+class Llama3JsonToolParser(ToolParser):
+    """The whole message is one JSON object (or several separated by ``;``) with name + parameters."""
+
+    def extract(self, text: str) -> ExtractedTools:
+        body = text.strip()
+        if body.startswith("<|python_tag|>"):
+            body = body[len("<|python_tag|>"):].strip()
+        if not body.startswith("{"):
+            return ExtractedTools(text or None, [])
+        calls = []
+        dec = json.JSONDecoder()
+        pos = 0
+        try:
+            while pos < len(body):
+                obj, end = dec.raw_decode(body, pos)
+                c = _call_from_obj(obj)
+                if c is None:
+                    return ExtractedTools(text or None, [])
+                calls.append(c)
+                pos = end
+                while pos < len(body) and body[pos] in " ;\n\t":
+                    pos += 1
+        except json.JSONDecodeError:
+            return ExtractedTools(None if calls else (text or None), calls) if calls else ExtractedTools(None, [])
+        return ExtractedTools(None, calls)
+
+
+class MistralToolParser(ToolParser):
+    """``[TOOL_CALLS] [{"name": …, "arguments": {…}}, …]``."""
+    tag = "[TOOL_CALLS]"
+
+    def extract(self, text: str) -> ExtractedTools:
+        if self.tag not in text:
+            return ExtractedTools(text or None, [])
+        content, _, body = text.partition(self.tag)
+        calls = []
+        try:
+            arr = json.loads(body.strip())
+            for obj in arr if isinstance(arr, list) else [arr]:
+                c = _call_from_obj(obj)
+                if c:
+                    calls.append(c)
+        except json.JSONDecodeError:
+            pass
+        return ExtractedTools(content.strip() or None, calls)
+
+
+class PythonicToolParser(ToolParser):
+    """``[get_weather(city="Paris"), other(x=1)]`` — a Python list of calls with keyword arguments."""
+
+    def extract(self, text: str) -> ExtractedTools:
+        body = text.strip()
+        if not (body.startswith("[") and body.endswith("]")):
+            return ExtractedTools(text or None, [])
+        try:
+            tree = ast.parse(body, mode="eval")
+        except SyntaxError:
+            return ExtractedTools(text or None, [])
+        if not isinstance(tree.body, ast.List) or not all(isinstance(e, ast.Call) for e in tree.body.elts):
+            return ExtractedTools(text or None, [])
+        calls = []
+        for e in tree.body.elts:
+            try:
+                args = {kw.arg: ast.literal_eval(kw.value) for kw in e.keywords}
+            except (ValueError, SyntaxError):
+                return ExtractedTools(text or None, [])
+            name = e.func.id if isinstance(e.func, ast.Name) else ast.unparse(e.func)
+            calls.append(ToolCall(name, json.dumps(args, ensure_ascii=False)))
+        return ExtractedTools(None, calls)
+
+
+TOOL_PARSERS: dict[str, type[ToolParser]] = {
+    "hermes": HermesToolParser, "qwen": HermesToolParser, "llama3_json": Llama3JsonToolParser,
+    "mistral": MistralToolParser, "pythonic": PythonicToolParser,
+}
+
+
+def get_reasoning_parser(name: str | None) -> ReasoningParser | None:
+    if not name:
+        return None
+    if name not in REASONING_PARSERS:
+        raise ValueError(f"unknown reasoning parser {name!r}; known: {sorted(REASONING_PARSERS)}")
+    return REASONING_PARSERS[name]()
+
+
+def get_tool_parser(name: str | None) -> ToolParser | None:
+    if not name:
+        return None
+    if name not in TOOL_PARSERS:
+        raise ValueError(f"unknown tool-call parser {name!r}; known: {sorted(TOOL_PARSERS)}")
+    return TOOL_PARSERS[name]()
+
+
+def register_reasoning_parser(name: str, cls: type[ReasoningParser]) -> None:
+    REASONING_PARSERS[name] = cls
+
+
+def register_tool_parser(name: str, cls: type[ToolParser]) -> None:
+    TOOL_PARSERS[name] = cls

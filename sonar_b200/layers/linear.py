@@ -23,6 +23,20 @@ from sonar_b200.parallel import state
 FP8_BLOCK = 128
 
 
+class QuantAct:
+    """An activation already quantised for an fp8 block-scaled GEMM: e4m3 rows and one fp32 scale per
+    token per 128 channels.  Produced by the norm+quant and SiLU+quant fusions, consumed by
+    ``Fp8BlockMethod.apply`` in place of a 16-bit tensor."""
+    __slots__ = ("q", "s")
+
+    def __init__(self, q: torch.Tensor, s: torch.Tensor) -> None:
+        self.q, self.s = q, s
+
+    @property
+    def shape(self):
+        return self.q.shape
+
+
 class UnquantizedMethod:
     name = "none"
 
@@ -52,7 +66,10 @@ class Fp8BlockMethod:
         layer.out_dtype = dtype
 
     def apply(self, layer: "LinearBase", x: torch.Tensor) -> torch.Tensor:
-        xq, xs = ops.per_token_group_quant_fp8(x, FP8_BLOCK)
+        if isinstance(x, QuantAct):
+            xq, xs = x.q, x.s
+        else:
+            xq, xs = ops.per_token_group_quant_fp8(x, FP8_BLOCK)
         y = ops.gemm_fp8_block(xq, xs, layer.weight, layer.weight_scale_inv, layer.out_dtype)
         return y if layer.bias is None else y + layer.bias
 
@@ -64,6 +81,12 @@ class Fp8BlockMethod:
         q, s = torch_ref.block_quant_fp8_weight(w, FP8_BLOCK)
         layer.weight.data.copy_(q)
         layer.weight_scale_inv.data.copy_(s)
+
+
+def wants_quant_act(layer) -> bool:
+    """True when ``layer`` consumes fp8 group-quantised activations (so its producer may quantise in its epilogue)."""
+    return (layer is not None and isinstance(getattr(layer, "method", None), Fp8BlockMethod)
+            and getattr(layer, "lora", None) is None)        # adapters read the 16-bit activation
 
 
 def make_linear_method(quantization: str | None):
@@ -80,6 +103,7 @@ class LinearBase(nn.Module):
         self.bias = None
         self._want_bias = bias
         self.dtype, self.device_ = dtype, device
+        self.lora = None          # a sonar_b200.lora.LoRALayer once adapters are enabled
 
     def _alloc(self, n_local: int, k_local: int) -> None:
         self.method.create(self, n_local, k_local, self.dtype, self.device_)
@@ -88,7 +112,10 @@ class LinearBase(nn.Module):
                                      requires_grad=False)
 
     def apply(self, x: torch.Tensor) -> torch.Tensor:
-        return self.method.apply(self, x)
+        y = self.method.apply(self, x)
+        if self.lora is not None:
+            y = self.lora.apply(x, y)
+        return y
 
     forward = apply
 

@@ -18,7 +18,8 @@ from sonar_b200 import ops
 from sonar_b200.config import ModelConfig
 from sonar_b200.layers.attention import Attention, AttentionMetadata
 from sonar_b200.layers.embedding import ParallelLMHead, VocabParallelEmbedding
-from sonar_b200.layers.linear import MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear
+from sonar_b200.layers.linear import (MergedColumnParallelLinear, QKVParallelLinear, QuantAct, RowParallelLinear,
+                                      wants_quant_act)
 from sonar_b200.layers.norm import RMSNorm
 from sonar_b200.parallel import state
 from sonar_b200.parallel.tp_ops import get_tp_context
@@ -54,7 +55,11 @@ class LlamaMLP(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         tp = get_tp_context()
         gu = tp.col_linear(x, self.gate_up_proj)
-        return tp.row_linear(ops.silu_and_mul(gu), self.down_proj)
+        if wants_quant_act(self.down_proj) and not tp.scattered:
+            act = QuantAct(*ops.silu_mul_group_quant(gu))       # SwiGLU and the fp8 quantisation in one pass
+        else:
+            act = ops.silu_and_mul(gu)
+        return tp.row_linear(act, self.down_proj)
 
 
 class LlamaAttention(nn.Module):
@@ -95,10 +100,12 @@ class LlamaDecoderLayer(nn.Module):
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor | None, meta: AttentionMetadata):
         tp = get_tp_context()
-        x, residual = tp.add_norm(h, residual, self.input_layernorm.weight, self.input_layernorm.eps)
+        x, residual = tp.add_norm(h, residual, self.input_layernorm.weight, self.input_layernorm.eps,
+                                  consumer=self.self_attn.qkv_proj)
         h = self.self_attn(x, meta)
         x, residual = tp.add_norm(h, residual, self.post_attention_layernorm.weight,
-                                  self.post_attention_layernorm.eps)
+                                  self.post_attention_layernorm.eps,
+                                  consumer=getattr(self.mlp, "gate_up_proj", None))
         h = self.mlp(x)
         return h, residual
 

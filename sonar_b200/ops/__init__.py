@@ -254,3 +254,16 @@ def scaled_mm_fp8(xq, x_scale, wq, w_scale, out_dtype=torch.bfloat16):
     if per_channel:
         y = (y.float() * w_scale.float().reshape(1, n)).to(out_dtype)
     return y
+
+
+# ---- LoRA ----------------------------------------------------------------------
+def lora_shrink(x, a, slots):
+    if _use_cuda(x):
+        return cuda_ops().lora_shrink(x, a, slots)
+    return ref.lora_shrink(x, a, slots)
+
+
+def lora_expand(v, b, slots, y, y_off=0):
+    if _use_cuda(y):
+        return cuda_ops().lora_expand(v, b, slots, y, y_off)
+    return ref.lora_expand(v, b, slots, y, y_off)

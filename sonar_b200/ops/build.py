@@ -106,14 +106,16 @@ HOST_LIB_PATH = os.path.join(PKG_DIR, "_host.so")
 
 
 def build_host_extension(force: bool = False) -> str:
-    """Host-only native helpers (shared-memory message ring): g++, no CUDA."""
+    """Host-side native helpers (shared-memory message ring, file IO, the virtual-memory allocator that
+    opens the CUDA driver at run time): g++, nothing linked from CUDA."""
     srcs = sorted(os.path.join(HOST_SRC_DIR, f) for f in os.listdir(HOST_SRC_DIR) if f.endswith(".cpp"))
     newest = max(os.path.getmtime(s) for s in srcs)
     if not force and os.path.exists(HOST_LIB_PATH) and os.path.getmtime(HOST_LIB_PATH) >= newest:
         return HOST_LIB_PATH
     cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
-    res = subprocess.run([cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", *srcs, "-o", HOST_LIB_PATH, "-lrt"],
-                         capture_output=True, text=True)
+    cuda_inc = os.path.join(os.path.dirname(os.path.dirname(find_nvcc())), "include")   # cuda.h: types only
+    res = subprocess.run([cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", "-I", cuda_inc, *srcs, "-o",
+                          HOST_LIB_PATH, "-lrt", "-ldl"], capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"host extension build failed:\n{res.stderr}")
     return HOST_LIB_PATH

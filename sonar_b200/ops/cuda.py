@@ -96,6 +96,10 @@ _norm_quant = _sig("sonar_rms_norm_group_quant", c_void_p, c_void_p, c_void_p, c
                    c_int, c_int, c_long, c_float, c_int, c_void_p)
 _silu_quant = _sig("sonar_silu_mul_group_quant", c_void_p, c_long, c_void_p, c_void_p, c_long, c_int, c_int, c_int,
                    c_void_p)
+_lora_shrink = _sig("sonar_lora_shrink", c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                    c_void_p)
+_lora_expand = _sig("sonar_lora_expand", c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int,
+                    c_int, c_void_p)
 lib.sonar_last_cuda_error.restype = c_int
 lib.sonar_gemm_pick_bn.argtypes = [c_int, c_int, c_int, c_int]
 lib.sonar_gemm_pick_bn.restype = c_int
@@ -658,3 +662,24 @@ def sample(logits, temperature, top_k, top_p, min_p, noise=None, seeds=None):
                    _ptr(min_p), _ptr(noise), noise.stride(0) if noise is not None else 0, _ptr(seeds),
                    _sample_step & 0xFFFFFFFF, out.data_ptr(), _stream()), "sample")
     return out
+
+
+# ---------------------------------------------------------------- LoRA
+def lora_shrink(x, a, slots):
+    """x [T, K] 16-bit, a [L, r, K] contiguous, slots int32 [T] → v fp32 [T, r] (rows of skipped tokens undefined)."""
+    assert x.stride(1) == 1 and a.is_contiguous() and slots.dtype == torch.int32 and a.dtype == x.dtype
+    t, k = x.shape
+    r = a.shape[1]
+    v = torch.empty((t, r), dtype=torch.float32, device=x.device)
+    _check(_lora_shrink(x.data_ptr(), x.stride(0), a.data_ptr(), slots.data_ptr(), v.data_ptr(), t, r, k, _DT[x.dtype],
+                        _stream()), "lora_shrink")
+    return v
+
+
+def lora_expand(v, b, slots, y, y_off=0):
+    """y[t, y_off:y_off+N] += b[slots[t]] @ v[t];  b [L, N, r] contiguous, same dtype as y."""
+    assert b.is_contiguous() and y.stride(1) == 1 and b.dtype == y.dtype
+    t, r = v.shape
+    _check(_lora_expand(v.data_ptr(), b.data_ptr(), slots.data_ptr(), y.data_ptr(), y.stride(0), y_off, t, b.shape[1], r,
+                        _DT[y.dtype], _stream()), "lora_expand")
+    return y

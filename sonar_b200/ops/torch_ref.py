@@ -483,3 +483,27 @@ def rms_norm_group_quant(x: torch.Tensor, weight: torch.Tensor, eps: float, resi
 
 def silu_mul_group_quant(x: torch.Tensor, group: int = 128) -> tuple[torch.Tensor, torch.Tensor]:
     return per_token_group_quant_fp8(silu_and_mul(x), group)
+
+
+# ---------------------------------------------------------------- LoRA (batched gather matrix-vector)
+def lora_shrink(x: torch.Tensor, a: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+    """v[t] = A[slots[t]] @ x[t] (zeros where slots[t] < 0).  A: [L, r, K] → v fp32 [T, r]."""
+    t = x.shape[0]
+    v = torch.zeros(t, a.shape[1], dtype=torch.float32, device=x.device)
+    for sl in torch.unique(slots).tolist():
+        if sl < 0:
+            continue
+        m = slots == sl
+        v[m] = x[m].float() @ a[sl].float().t()
+    return v
+
+
+def lora_expand(v: torch.Tensor, b: torch.Tensor, slots: torch.Tensor, y: torch.Tensor, y_off: int = 0) -> torch.Tensor:
+    """y[t, y_off : y_off + N] += B[slots[t]] @ v[t].  B: [L, N, r]."""
+    n = b.shape[1]
+    for sl in torch.unique(slots).tolist():
+        if sl < 0:
+            continue
+        m = slots == sl
+        y[m, y_off:y_off + n] = (y[m, y_off:y_off + n].float() + v[m] @ b[sl].float().t()).to(y.dtype)
+    return y

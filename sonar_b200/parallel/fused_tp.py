@@ -139,7 +139,7 @@ class FusedTPContext(TPContext):
         return partial  # the embedding is replicated in this layout: local rows need no reduction
 
     # ------------------------------------------------------------------ the three fused ops
-    def add_norm(self, h, residual, weight, eps):
+    def add_norm(self, h, residual, weight, eps, consumer=None):
         cu, tp = self.cu, self.world_size
         if isinstance(h, Partial):
             src, stride, n_src, flags, wait_seq = self.partial.data_ptr(), self.slot_elems, tp, self.pflags.data_ptr(), h.seq

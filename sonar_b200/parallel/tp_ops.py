@@ -50,8 +50,17 @@ class TPContext:
         """Vocab-parallel embedding partials → block input layout."""
         return self.group.all_reduce(partial) if self.world_size > 1 else partial
 
-    def add_norm(self, h: torch.Tensor, residual: torch.Tensor | None, weight: torch.Tensor, eps: float
-                 ) -> tuple[torch.Tensor, torch.Tensor]:
+    def add_norm(self, h: torch.Tensor, residual: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                 consumer=None) -> tuple[torch.Tensor, torch.Tensor]:
+        """``consumer``: the linear layer that reads the normalised rows next.  When it runs in fp8 the
+        norm kernel also emits the per-128-channel quantised rows, and a ``QuantAct`` is returned as x."""
+        from sonar_b200.layers.linear import QuantAct, wants_quant_act
+        if wants_quant_act(consumer):
+            if residual is None:
+                q, s, _ = ops.rms_norm_group_quant(h, weight, eps, None)
+                return QuantAct(q, s), h
+            q, s, residual = ops.rms_norm_group_quant(h, weight, eps, residual)
+            return QuantAct(q, s), residual
         if residual is None:
             return ops.rms_norm(h, weight, eps), h
         return ops.fused_add_rms_norm(h, residual, weight, eps)

@@ -54,6 +54,7 @@ class InputBatch:
         self.pooling: list[bool] = [False] * max_seqs
         self.generators: dict[str, torch.Generator] = {}
         self.mirostat_mu: dict[str, float] = {}
+        self.lora: dict[str, str] = {}                                # request id → adapter name
         self.num_reqs = 0
 
     def add(self, req_id: str, prompt: list[int], outputs: list[int], params: SamplingParams | None,
@@ -86,6 +87,7 @@ class InputBatch:
             return
         self.generators.pop(req_id, None)
         self.mirostat_mu.pop(req_id, None)
+        self.lora.pop(req_id, None)
         last = self.num_reqs - 1
         if row != last:  # move the last row into the hole
             n = int(self.num_tokens[last])
@@ -163,6 +165,15 @@ class ModelRunner:
         with torch.inference_mode():
             self.model = load_model(self.cfg, self.device)
         logger.info("model %s built in %.1fs", self.model_cfg.model, time.time() - t0)
+        self.lora = None
+        if self.cfg.lora.enable_lora:
+            from sonar_b200.lora import LoRAManager
+            if get_tp_context().scattered:
+                raise ValueError("LoRA needs replicated activations between blocks: use SONAR_TP_COMM=custom or nccl")
+            with torch.inference_mode(False):
+                self.lora = LoRAManager(self.model, self.cfg.lora, self.model_cfg.dtype, self.device, self.max_tokens)
+            for name, path in self.cfg.lora.lora_modules.items():
+                self.lora.register(name, path)
 
     def kv_cache_spec(self) -> KVCacheSpec:
         m = self.model_cfg
@@ -210,6 +221,8 @@ class ModelRunner:
                 b.remove(nr.req_id)
             b.add(nr.req_id, nr.prompt_token_ids, nr.output_token_ids, nr.sampling_params, nr.block_ids,
                   nr.num_computed_tokens, nr.pooling, self.device)
+            if nr.lora_name:
+                b.lora[nr.req_id] = nr.lora_name
         c = so.scheduled_cached_reqs
         for i, rid in enumerate(c.req_ids):
             row = b.index[rid]
@@ -295,6 +308,9 @@ class ModelRunner:
         if so.total_num_scheduled_tokens == 0:
             return ModelRunnerOutput()
         meta, rows, q_lens = self._prepare_inputs(so)
+        if self.lora is not None:
+            b = self.batch
+            self.lora.set_step([(b.lora.get(b.req_ids[r]), int(q)) for r, q in zip(rows, q_lens)])
         self.stats["prep_s"] += time.perf_counter() - t0
         self.stats["steps"] += 1
         total = meta.num_tokens
@@ -502,6 +518,8 @@ class ModelRunner:
             return
         if getattr(self.model, "uses_mla", False):
             return   # the latent-attention path still has host-side steps (indexer top-k): eager only
+        if self.lora is not None:
+            return   # which adapter kernels run depends on the step's requests: eager only
         from sonar_b200.ops import cuda as cuda_ops
         tp = get_tp_context()
         sizes = sorted({b for b in [1, 2, 4, 8, 16, 24, 32, 40, 48, 56, 64] + list(range(80, 513, 16))

@@ -67,8 +67,18 @@ class Worker:
             ctx = fused_tp.make_context(self.cfg, self.device, mode)
         tp_ops.set_tp_context(ctx if ctx is not None else tp_ops.TPContext())
 
+    def _pool(self, tag: str):
+        """Memory pool for ``tag`` when sleep mode is on (weights and KV cache then live on the
+        virtual-memory allocator and can be released and re-mapped at the same addresses)."""
+        import contextlib
+        if self.cfg.enable_sleep_mode and self.cfg.device == "cuda":
+            from sonar_b200.device_allocator import CuMemAllocator
+            return CuMemAllocator.get_instance().use_memory_pool(tag)
+        return contextlib.nullcontext()
+
     def load_model(self) -> None:
-        self.runner.load_model()
+        with self._pool("weights"):
+            self.runner.load_model()
 
     def get_kv_cache_spec(self) -> tuple[KVCacheSpec, int]:
         return self.runner.kv_cache_spec(), self.runner.num_local_layers()
@@ -89,7 +99,66 @@ class Worker:
         return max(avail, 0)
 
     def initialize_from_config(self, kv_cfg: KVCacheConfig) -> None:
-        self.runner.initialize_kv_cache(kv_cfg)
+        with self._pool("kv_cache"):
+            self.runner.initialize_kv_cache(kv_cfg)
+
+    # sleep / wake-up --------------------------------------------------------------
+    def sleep(self, level: int = 1) -> int:
+        """Level 1: weights go to pinned host memory, the KV cache is dropped.  Level 2: both are
+        dropped (the caller reloads weights after wake-up).  Returns the GPU bytes released."""
+        if not self.cfg.enable_sleep_mode:
+            raise ValueError("sleep mode is off (start the engine with enable_sleep_mode=True)")
+        self._asleep = True
+        if self.cfg.device != "cuda":
+            return 0
+        from sonar_b200.device_allocator import CuMemAllocator
+        freed = CuMemAllocator.get_instance().sleep(offload_tags=("weights",) if level == 1 else ())
+        logger.info("sleep level %d released %.2f GiB", level, freed / 2**30)
+        return freed
+
+    def wake_up(self, tags: list[str] | None = None) -> int:
+        if not self.cfg.enable_sleep_mode:
+            raise ValueError("sleep mode is off (start the engine with enable_sleep_mode=True)")
+        n = 0
+        if self.cfg.device == "cuda":
+            from sonar_b200.device_allocator import CuMemAllocator
+            alloc = CuMemAllocator.get_instance()
+            n = alloc.wake_up(tags)
+            if not alloc.sleeping:
+                self._asleep = False
+            if tags is None or "kv_cache" in tags:
+                for cache in self.runner.kv_caches:      # new physical pages hold garbage
+                    cache.zero_()
+        else:
+            self._asleep = False
+        return n
+
+    def is_sleeping(self) -> bool:
+        return getattr(self, "_asleep", False)
+
+    # profiler -------------------------------------------------------------------------
+    def start_profile(self, trace_dir: str | None = None) -> bool:
+        """Start a torch profiler trace of this worker (CPU + CUDA activities)."""
+        if getattr(self, "_profiler", None) is not None:
+            return False
+        acts = [torch.profiler.ProfilerActivity.CPU]
+        if self.cfg.device == "cuda":
+            acts.append(torch.profiler.ProfilerActivity.CUDA)
+        self._profile_dir = trace_dir or os.environ.get("SONAR_TORCH_PROFILER_DIR", "/tmp/sonar_profile")
+        os.makedirs(self._profile_dir, exist_ok=True)
+        self._profiler = torch.profiler.profile(activities=acts)
+        self._profiler.start()
+        return True
+
+    def stop_profile(self) -> str | None:
+        prof = getattr(self, "_profiler", None)
+        if prof is None:
+            return None
+        prof.stop()
+        path = os.path.join(self._profile_dir, f"worker_rank{self.rank}.json")
+        prof.export_chrome_trace(path)
+        self._profiler = None
+        return path
 
     def compile_or_warm_up_model(self) -> None:
         warm = getattr(self.runner, "warm_up", None)
@@ -101,6 +170,22 @@ class Worker:
 
     def get_stats(self) -> dict:
         return dict(self.runner.stats)
+
+    # LoRA adapters ------------------------------------------------------------
+    def _lora(self):
+        if self.runner.lora is None:
+            raise ValueError("LoRA is not enabled (start the engine with enable_lora=True)")
+        return self.runner.lora
+
+    def add_lora(self, name: str, path: str) -> bool:
+        self._lora().register(name, path)
+        return True
+
+    def remove_lora(self, name: str) -> bool:
+        return self._lora().unregister(name)
+
+    def list_loras(self) -> list[str]:
+        return self._lora().list_adapters()
 
     def check_health(self) -> bool:
         return True

@@ -147,3 +147,22 @@ def test_structured_outputs_choice_json_and_regex():
     else:                                   # ran out of tokens inside a long integer: still a valid JSON prefix
         assert txt.lstrip().startswith("{")
     assert len(outs[3].outputs[0].token_ids) == 8
+
+
+def test_fp8_linear_fusions_match_unfused_path(monkeypatch):
+    """fp8 block-scaled linears: norm+quant and SwiGLU+quant producers give the same tokens as quantising
+    inside the linear layer."""
+    import sonar_b200.layers.linear as lin
+
+    def run():
+        llm = LLM(model="tiny-llama-128", dtype="float32", quantization="fp8", max_model_len=128,
+                  num_gpu_blocks_override=32, device="cpu", max_num_seqs=4, max_num_batched_tokens=64, seed=0)
+        outs = llm.generate([{"prompt_token_ids": [3, 9, 27, 81, 243]}, {"prompt_token_ids": list(range(40, 60))}],
+                            SamplingParams(max_tokens=6, temperature=0, ignore_eos=True))
+        return [o.outputs[0].token_ids for o in outs]
+    fused = run()
+    import sonar_b200.models.llama as llama_mod
+    monkeypatch.setattr(lin, "wants_quant_act", lambda layer: False)
+    monkeypatch.setattr(llama_mod, "wants_quant_act", lambda layer: False)
+    unfused = run()
+    assert fused == unfused and all(len(t) == 6 for t in fused)

@@ -115,3 +115,51 @@ def test_data_parallel_load_balancing_and_engine_death():
         asyncio.run(main())
     finally:
         engine.shutdown()
+
+
+def test_management_pooling_and_parser_routes(tmp_path):
+    """Sleep / wake, profiler, score / rerank / pooling, responses, invocations, render, reasoning split."""
+    from fastapi.testclient import TestClient
+
+    from sonar_b200.engine.async_llm import AsyncLLM
+    from sonar_b200.entrypoints.openai.api_server import ServingState, build_app
+    args = EngineArgs(model="tiny-llama", dtype="float32", max_model_len=256, num_gpu_blocks_override=64,
+                      max_num_seqs=4, max_num_batched_tokens=128, device="cpu", enable_sleep_mode=True)
+    engine = AsyncLLM.from_engine_args(args)
+    app = build_app(ServingState(engine, "tiny", None, reasoning_parser="qwen3", tool_parser="hermes"))
+    try:
+        with TestClient(app) as c:
+            assert c.get("/is_sleeping").json() == {"is_sleeping": False}
+            assert c.post("/sleep?level=1").json()["sleeping"] is True
+            assert c.get("/is_sleeping").json() == {"is_sleeping": True}
+            assert c.post("/wake_up").json()["sleeping"] is False
+            r = c.post("/v1/completions", json={"prompt": "hi", "max_tokens": 3, "temperature": 0})
+            assert r.status_code == 200 and r.json()["usage"]["completion_tokens"] == 3
+
+            r = c.post("/score", json={"text_1": "a cat", "text_2": ["a cat", "the stock market fell"]}).json()
+            assert len(r["data"]) == 2 and r["data"][0]["score"] > 0.999
+            r = c.post("/v1/rerank", json={"query": "a cat", "documents": ["zzz", "a cat"], "top_n": 1}).json()
+            assert r["results"][0]["index"] == 1
+            r = c.post("/pooling", json={"input": ["x", "yy"]}).json()
+            assert len(r["data"]) == 2 and len(r["data"][0]["data"]) > 8
+            r = c.post("/classify", json={"input": "Is it?", "labels": ["y", "n"]}).json()
+            assert r["data"][0]["label"] in ("y", "n") and abs(sum(r["data"][0]["probs"]) - 1) < 1e-4
+
+            r = c.post("/v1/responses", json={"input": "hello", "max_output_tokens": 4}).json()
+            assert r["object"] == "response" and r["usage"]["output_tokens"] == 4
+            r = c.post("/invocations", json={"prompt": "abc", "max_tokens": 2}).json()
+            assert r["object"] == "text_completion"
+            r = c.post("/invocations", json={"messages": [{"role": "user", "content": "q"}], "max_tokens": 2}).json()
+            assert r["object"] == "chat.completion"
+            assert c.post("/invocations", json={"nothing": 1}).status_code == 400
+            r = c.post("/v1/chat/completions/render", json={"messages": [{"role": "user", "content": "q"}]}).json()
+            assert "q" in r["prompt"] and r["prompt_token_ids"]
+
+            assert c.post("/start_profile", json={"trace_dir": str(tmp_path)}).json() == {"profiling": True}
+            c.post("/v1/completions", json={"prompt": "p", "max_tokens": 2})
+            traces = c.post("/stop_profile").json()["traces"]
+            assert traces and traces[0].endswith(".json")
+            # LoRA routes without LoRA enabled answer 400
+            assert c.post("/v1/load_lora_adapter", json={"lora_name": "a", "lora_path": "/nonexistent"}).status_code == 400
+    finally:
+        engine.shutdown()

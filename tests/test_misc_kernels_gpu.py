@@ -91,7 +91,7 @@ def test_per_token_and_per_tensor_fp8_quant(cu):
     wq, ws = ref.per_token_quant_fp8(x.float())
     torch.testing.assert_close(s, ws, atol=0, rtol=1e-6)
     assert ((q.float() * s) - x.float()).abs().max() <= (x.float().abs().amax(-1, keepdim=True) / 448 * 16 + 1e-3).max()
-    torch.testing.assert_close(q.float() * s, wq.float() * ws, atol=0.3, rtol=0.07)
+    torch.testing.assert_close(q.float() * s, wq.float() * ws, atol=0.3, rtol=0.13)   # one e4m3 step: x·(1/s) vs x/s
     # dynamic per-tensor
     q2, s2 = cu.scaled_fp8_quant(x)
     _, ws2 = ref.scaled_fp8_quant(x.float())
@@ -147,3 +147,48 @@ def test_scaled_mm_fp8_per_token_per_channel(cu):
     y = ops.scaled_mm_fp8(xq, xs, wq, wsc)
     want = x.float() @ w.float().t()
     assert (y.float() - want).norm() / want.norm() < 0.06
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_lora_shrink_expand(cu, dtype):
+    torch.manual_seed(9)
+    t, k, n, r, slots_n = 37, 1024, 768, 16, 3
+    x = torch.randn(t, k, device=DEV, dtype=dtype)
+    a = (torch.randn(slots_n, r, k, device=DEV) * 0.05).to(dtype)
+    b = (torch.randn(slots_n, n, r, device=DEV) * 0.05).to(dtype)
+    slots = torch.randint(-1, slots_n, (t,), device=DEV, dtype=torch.int32)
+    y0 = torch.randn(t, 2 * n, device=DEV, dtype=dtype)
+    v = cu.lora_shrink(x, a, slots)
+    want_v = ref.lora_shrink(x, a, slots)
+    live = slots >= 0
+    torch.testing.assert_close(v[live], want_v[live], atol=2e-2, rtol=2e-2)
+    y = y0.clone()
+    cu.lora_expand(want_v, b, slots, y, n)
+    want_y = ref.lora_expand(want_v, b, slots, y0.clone().float(), n)
+    torch.testing.assert_close(y.float(), want_y, atol=3e-2, rtol=2e-2)
+    assert torch.equal(y[:, :n], y0[:, :n]) and torch.equal(y[~live], y0[~live])
+
+
+def test_cumem_sleep_wake_keeps_addresses_and_weights():
+    from sonar_b200.device_allocator import CuMemAllocator
+    alloc = CuMemAllocator.get_instance()
+    assert alloc.available
+    with alloc.use_memory_pool("weights"):
+        w = torch.randn(64 << 20, device=DEV)                  # 256 MiB
+    with alloc.use_memory_pool("kv_cache"):
+        kv = torch.ones(32 << 20, device=DEV)                  # 128 MiB
+    keep = w.clone()
+    ptr_w, ptr_kv = w.data_ptr(), kv.data_ptr()
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    freed = alloc.sleep(offload_tags=("weights",))
+    free1, _ = torch.cuda.mem_get_info()
+    assert freed >= (384 << 20) and free1 - free0 >= (300 << 20)
+    st = alloc.stats()
+    assert st["mapped_bytes"] == 0 and st["host_copy_bytes"] >= (256 << 20)
+    assert alloc.wake_up() == freed
+    assert w.data_ptr() == ptr_w and kv.data_ptr() == ptr_kv
+    assert torch.equal(w, keep)                                 # offloaded pool restored
+    kv.zero_()                                                  # discarded pool is usable again
+    assert float(kv.sum()) == 0.0
+    del w, kv

@@ -295,6 +295,8 @@ class ObservabilityConfig:
     log_stats: bool = False
     trace_file: str | None = None
     collect_kv_events: bool = False
+    kv_events_endpoint: str | None = None          # ZMQ PUB endpoint for KV-cache events (None = not published)
+    kv_events_replay_endpoint: str | None = None
 
 
 @dataclass
@@ -375,6 +377,8 @@ class EngineArgs:
     device: str = "auto"
     disable_log_stats: bool = True
     trace_file: str | None = None
+    kv_events_endpoint: str | None = None
+    kv_events_replay_endpoint: str | None = None
 
     def create_engine_config(self) -> EngineConfig:
         dtype = _DTYPES.get(self.dtype, "bad")
@@ -420,7 +424,10 @@ class EngineArgs:
             policy=self.scheduling_policy, async_scheduling=self.async_scheduling)
         spec = SpeculativeConfig(method=self.speculative_method,
                                  num_speculative_tokens=self.num_speculative_tokens)
-        obs = ObservabilityConfig(log_stats=not self.disable_log_stats, trace_file=self.trace_file)
+        obs = ObservabilityConfig(log_stats=not self.disable_log_stats, trace_file=self.trace_file,
+                                  collect_kv_events=self.kv_events_endpoint is not None,
+                                  kv_events_endpoint=self.kv_events_endpoint,
+                                  kv_events_replay_endpoint=self.kv_events_replay_endpoint)
         lora = LoRAConfig(enable_lora=self.enable_lora or bool(self.lora_modules), max_loras=self.max_loras,
                           max_lora_rank=self.max_lora_rank, lora_modules=dict(self.lora_modules or {}))
         return EngineConfig(model=model, cache=cache, parallel=parallel, scheduler=sched,

@@ -24,6 +24,8 @@ logger = init_logger(__name__)
 
 class EngineCore:
     def __init__(self, cfg: EngineConfig, executor_class: type[Executor] | None = None) -> None:
+        from sonar_b200.plugins import load_general_plugins
+        load_general_plugins()
         self.cfg = cfg
         t0 = time.time()
         self.executor = (executor_class or Executor.get_class(cfg))(cfg)
@@ -40,6 +42,12 @@ class EngineCore:
                                    collect_kv_events=cfg.observability.collect_kv_events,
                                    structured_output_manager=structured)
         self.tracer = get_tracer(cfg.observability.trace_file)
+        self.kv_publisher = None
+        if cfg.observability.kv_events_endpoint:
+            from sonar_b200.distributed.kv_events import KVEventPublisher
+            self.kv_publisher = KVEventPublisher(cfg.observability.kv_events_endpoint,
+                                                 cfg.observability.kv_events_replay_endpoint)
+            logger.info("KV-cache events published on %s", self.kv_publisher.endpoint)
         self.paused = False
         self.sleeping = False
         self.steps = 0
@@ -74,6 +82,8 @@ class EngineCore:
         self.host_time["execute"] += t2 - t1
         self.host_time["update"] += t3 - t2
         self.steps += 1
+        if self.kv_publisher is not None:
+            self.kv_publisher.publish(self.scheduler.kv.take_events())
         return outs
 
     # utility RPCs ---------------------------------------------------------
@@ -126,6 +136,12 @@ class EngineCore:
         s = self.scheduler.make_stats()
         return {"scheduler": s, "workers": self.executor.collective_rpc("get_stats")}
 
+    def kv_events_endpoints(self) -> dict:
+        p = self.kv_publisher
+        return {} if p is None else {"publish": p.endpoint, "replay": getattr(p, "replay_endpoint", None)}
+
     def shutdown(self) -> None:
+        if self.kv_publisher is not None:
+            self.kv_publisher.close()
         self.executor.shutdown()
         self.tracer.close()

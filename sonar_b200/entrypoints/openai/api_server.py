@@ -469,6 +469,10 @@ def build_app(state: ServingState) -> FastAPI:
 
     from sonar_b200.entrypoints.openai import extra_routes
     extra_routes.register(app, state)
+    from sonar_b200.plugins import ENDPOINT, load_plugins_by_group
+    for name, fn in load_plugins_by_group(ENDPOINT).items():
+        fn(app, state)
+        logger.info("endpoint plugin %s registered", name)
 
     @app.post("/collective_rpc")
     async def collective_rpc(body: dict):

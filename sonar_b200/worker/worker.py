@@ -33,6 +33,8 @@ class Worker:
 
     # ------------------------------------------------------------------
     def init_device(self) -> None:
+        from sonar_b200.plugins import load_general_plugins
+        load_general_plugins()
         cfg = self.cfg
         if cfg.device == "cuda":
             self.device = torch.device("cuda", self.local_rank)

@@ -43,3 +43,17 @@ def test_moe_tp2_fused_matches_tp1(tmp_path_factory, ep):
     worst = max((torch.tensor(a["prompt_logprobs"]) - torch.tensor(b["prompt_logprobs"])).abs().max().item()
                 for a, b in zip(one, two))
     assert worst < 0.15, worst
+
+
+@needs2
+def test_pynccl_communicator_from_stateless_group():
+    """NCCL through the ctypes binding, bootstrapped over a TCP store (no torch.distributed world)."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    worker = os.path.join(os.path.dirname(__file__), "pynccl_worker.py")
+    procs = [subprocess.Popen([sys.executable, worker, str(r), "2", "29677"], env=env, stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=240)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), "\n".join(outs)

@@ -354,6 +354,9 @@ class EngineArgs:
     expert_placement: str = "linear"
     all2all_backend: str = "fused_nvlink"
     enable_eplb: bool = False
+    num_redundant_experts: int = 0
+    eplb_window: int = 1000
+    eplb_interval: int = 3000
     distributed_executor_backend: str | None = None
     disable_custom_all_reduce: bool = False
     # scheduler
@@ -398,6 +401,7 @@ class EngineArgs:
             model.hf_config.update(self.hf_overrides)
         model.hf_config["_expert_parallel"] = self.enable_expert_parallel
         model.hf_config["_expert_placement"] = self.expert_placement
+        model.hf_config["_num_redundant_experts"] = self.num_redundant_experts if self.enable_eplb else 0
         cache = CacheConfig(
             block_size=self.block_size, gpu_memory_utilization=self.gpu_memory_utilization,
             num_gpu_blocks_override=self.num_gpu_blocks_override,
@@ -411,7 +415,8 @@ class EngineArgs:
             decode_context_parallel_size=self.decode_context_parallel_size,
             prefill_context_parallel_size=self.prefill_context_parallel_size,
             expert_placement=self.expert_placement, all2all_backend=self.all2all_backend,
-            enable_eplb=self.enable_eplb,
+            enable_eplb=self.enable_eplb, num_redundant_experts=self.num_redundant_experts,
+            eplb_window=self.eplb_window, eplb_interval=self.eplb_interval,
             distributed_executor_backend=self.distributed_executor_backend,
             disable_custom_all_reduce=self.disable_custom_all_reduce)
         budget = self.max_num_batched_tokens

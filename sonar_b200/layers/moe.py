@@ -35,7 +35,7 @@ class FusedMoE(nn.Module):
     def __init__(self, num_experts: int, top_k: int, hidden: int, inter: int, dtype, device, renormalize: bool = True,
                  scoring: str = "softmax", n_group: int = 1, topk_group: int = 1, routed_scaling: float = 1.0,
                  use_bias: bool = False, expert_parallel: bool = False, placement: str = "linear",
-                 prefix: str = "") -> None:
+                 prefix: str = "", num_redundant: int = 0) -> None:
         super().__init__()
         self.num_experts, self.top_k, self.hidden, self.inter = num_experts, top_k, hidden, inter
         self.renormalize, self.scoring = renormalize, scoring
@@ -43,7 +43,24 @@ class FusedMoE(nn.Module):
         tp, rank = state.tp_world_size(), state.tp_rank()
         self.tp, self.rank = tp, rank
         self.expert_parallel = expert_parallel and tp > 1
-        if self.expert_parallel:
+        self.eplb_state = None          # set by the model runner when load balancing is on
+        self.eplb_index = -1
+        self.num_phys = num_experts
+        if self.expert_parallel and num_redundant > 0:
+            # load balancing: E logical experts in P = E + redundant physical slots, P / tp per rank
+            self.num_phys = num_experts + num_redundant
+            if self.num_phys % tp or placement != "linear":
+                raise ValueError("expert load balancing needs linear placement and (experts + redundant) % tp == 0")
+            n_local = self.num_phys // tp
+            self.register_buffer("expert_map", torch.empty(self.num_phys, dtype=torch.int32, device=device),
+                                 persistent=False)
+            self.register_buffer("log2phy", torch.empty((num_experts, 1), dtype=torch.int64, device=device),
+                                 persistent=False)
+            self.register_buffer("logcnt", torch.ones(num_experts, dtype=torch.int64, device=device), persistent=False)
+            self.inter_local = inter
+            self.n_local = n_local
+            self.set_mapping(torch.arange(self.num_phys) % num_experts)
+        elif self.expert_parallel:
             if num_experts % tp:
                 raise ValueError(f"{num_experts} experts cannot be split over {tp} ranks")
             n_local = num_experts // tp
@@ -54,14 +71,14 @@ class FusedMoE(nn.Module):
             emap = torch.full((num_experts,), -1, dtype=torch.int32)
             emap[owned] = torch.arange(n_local, dtype=torch.int32)
             self.register_buffer("expert_map", emap.to(device), persistent=False)
-            self.local_of = {g: l for l, g in enumerate(owned)}
+            self.local_of = {g: [l] for l, g in enumerate(owned)}
             self.inter_local = inter
         else:
             if inter % tp:
                 raise ValueError(f"expert intermediate size {inter} not divisible by tp={tp}")
             n_local = num_experts
             self.expert_map = None
-            self.local_of = {g: g for g in range(num_experts)}
+            self.local_of = {g: [g] for g in range(num_experts)}
             self.inter_local = inter // tp
         self.n_local = n_local
         self.w13 = nn.Parameter(torch.empty(n_local, 2 * self.inter_local, hidden, dtype=dtype, device=device),
@@ -74,18 +91,37 @@ class FusedMoE(nn.Module):
 
     # weight loading: (expert id, "gate" | "up" | "down") -------------------------------
     def load_expert_weight(self, expert: int, which: str, tensor: torch.Tensor) -> bool:
-        local = self.local_of.get(expert)
-        if local is None:
-            return True   # another rank's expert
         il = self.inter_local
         lo = 0 if self.expert_parallel else self.rank * il
-        if which == "gate":
-            self.w13.data[local, :il].copy_(tensor[lo:lo + il])
-        elif which == "up":
-            self.w13.data[local, il:].copy_(tensor[lo:lo + il])
-        else:
-            self.w2.data[local].copy_(tensor[:, lo:lo + il])
+        for local in self.local_of.get(expert, ()):      # empty: another rank's expert; several: replicas
+            if which == "gate":
+                self.w13.data[local, :il].copy_(tensor[lo:lo + il])
+            elif which == "up":
+                self.w13.data[local, il:].copy_(tensor[lo:lo + il])
+            else:
+                self.w2.data[local].copy_(tensor[:, lo:lo + il])
         return True
+
+    def set_mapping(self, phy2log: torch.Tensor) -> None:
+        """Install a physical-slot → logical-expert assignment (``[P]``, rank-major) for this layer."""
+        phy2log = phy2log.to(torch.int64).cpu()
+        lo = self.rank * self.n_local
+        emap = torch.full((self.num_phys,), -1, dtype=torch.int32)
+        emap[lo:lo + self.n_local] = torch.arange(self.n_local, dtype=torch.int32)
+        self.expert_map.copy_(emap)
+        cnt = torch.zeros(self.num_experts, dtype=torch.int64).scatter_add_(0, phy2log, torch.ones_like(phy2log))
+        table = torch.zeros((self.num_experts, int(cnt.max())), dtype=torch.int64)
+        seen = [0] * self.num_experts
+        self.local_of = {}
+        for slot, e in enumerate(phy2log.tolist()):
+            table[e, seen[e]] = slot
+            seen[e] += 1
+            if lo <= slot < lo + self.n_local:
+                self.local_of.setdefault(e, []).append(slot - lo)
+        for e in range(self.num_experts):            # pad rows by repeating, so any column index is valid
+            table[e, seen[e]:] = table[e, 0]
+        self.log2phy = table.to(self.expert_map.device)
+        self.logcnt.copy_(cnt)
 
     def route(self, router_logits: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
         if self.n_group > 1 or self.scoring == "sigmoid" or self.e_bias is not None:
@@ -97,4 +133,12 @@ class FusedMoE(nn.Module):
     def forward(self, x: torch.Tensor, router_logits: torch.Tensor, combine_to=None):
         """Partial sum ``[T, H]`` of this rank's experts (or None when pushed to ``combine_to``)."""
         w, ids = self.route(router_logits)
+        if self.num_phys != self.num_experts:
+            # spread each expert's tokens over its replicas: replica = (token index + k) mod count
+            t, k = ids.shape
+            spread = (torch.arange(t, device=ids.device)[:, None] + torch.arange(k, device=ids.device)[None, :])
+            idl = ids.long()
+            ids = self.log2phy[idl, spread % self.logcnt[idl]].to(torch.int32)
+            if self.eplb_state is not None:
+                self.eplb_state.record(self.eplb_index, ids)
         return ops.fused_experts(x, self.w13, self.w2, w, ids, self.expert_map, combine_to)

@@ -191,7 +191,7 @@ class DeepseekMoE(nn.Module):
             n_group=int(g("n_group", 1) or 1), topk_group=int(g("topk_group", 1) or 1),
             routed_scaling=float(g("routed_scaling_factor", 1.0)), use_bias=g("topk_method", "noaux_tc") == "noaux_tc",
             expert_parallel=bool(g("_expert_parallel", False)), placement=g("_expert_placement", "linear"),
-            prefix=f"{prefix}.experts")
+            prefix=f"{prefix}.experts", num_redundant=int(g("_num_redundant_experts", 0) or 0))
         n_shared = int(g("n_shared_experts", 0) or 0)
         self.shared_experts = (LlamaMLP(cfg.hidden_size, inter * n_shared, cfg.dtype, device, cfg.quantization,
                                         f"{prefix}.shared_experts") if n_shared else None)

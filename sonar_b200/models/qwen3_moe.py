@@ -26,7 +26,8 @@ class SparseMoeBlock(nn.Module):
         self.gate = ReplicatedLinear(cfg.hidden_size, n_exp, False, cfg.dtype, device, None, f"{prefix}.gate")
         self.experts = FusedMoE(n_exp, int(cfg.get("num_experts_per_tok", 2)), cfg.hidden_size, inter, cfg.dtype,
                                 device, renormalize=bool(cfg.get("norm_topk_prob", True)),
-                                expert_parallel=expert_parallel, placement=placement, prefix=f"{prefix}.experts")
+                                expert_parallel=expert_parallel, placement=placement, prefix=f"{prefix}.experts",
+                                num_redundant=int(cfg.get("_num_redundant_experts", 0)))
 
     def forward(self, x):
         tp = get_tp_context()

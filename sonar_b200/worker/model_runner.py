@@ -165,6 +165,20 @@ class ModelRunner:
         with torch.inference_mode():
             self.model = load_model(self.cfg, self.device)
         logger.info("model %s built in %.1fs", self.model_cfg.model, time.time() - t0)
+        self.eplb = None
+        pc = self.cfg.parallel
+        if pc.enable_eplb and pc.num_redundant_experts > 0:
+            from sonar_b200.distributed.eplb import EplbConfig, EplbState
+            from sonar_b200.layers.moe import FusedMoE
+            self.moe_layers = [m for m in self.model.modules() if isinstance(m, FusedMoE) and m.num_phys != m.num_experts]
+            if self.moe_layers:
+                hf = self.model_cfg.hf_config
+                self.eplb = EplbState(len(self.moe_layers), self.moe_layers[0].num_experts,
+                                      EplbConfig(pc.num_redundant_experts, pc.eplb_window, pc.eplb_interval,
+                                                 int(hf.get("n_group", 1) or 1), 1),
+                                      self.moe_layers[0].tp, device=self.device)
+                for i, m in enumerate(self.moe_layers):
+                    m.eplb_state, m.eplb_index = self.eplb, i
         self.lora = None
         if self.cfg.lora.enable_lora:
             from sonar_b200.lora import LoRAManager
@@ -344,7 +358,22 @@ class ModelRunner:
         t2 = time.perf_counter()
         res = self._sample(so, hidden, meta, rows, q_lens)
         self.stats["sample_s"] += time.perf_counter() - t2
+        if self.eplb is not None and self.eplb.step():
+            self.rebalance_experts()
         return res
+
+    def rebalance_experts(self) -> int:
+        """Recompute the expert placement from the load window and move expert weights accordingly.
+        Every rank of the group calls this at the same step (they see identical routing)."""
+        from sonar_b200.parallel import state as pstate
+        group = pstate.get_tp_group().device_group if pstate.tp_world_size() > 1 else None
+        moved = self.eplb.rearrange([[m.w13.data, m.w2.data] for m in self.moe_layers], group)
+        for i, m in enumerate(self.moe_layers):
+            m.set_mapping(self.eplb.phy2log[i])
+        self.stats["eplb_rearrangements"] = self.eplb.rearrangements
+        logger.info("expert load balancing: rearrangement %d moved %d expert tensors to this rank",
+                    self.eplb.rearrangements, moved)
+        return moved
 
     def apply_remote_output(self, so: SchedulerOutput, out: ModelRunnerOutput) -> None:
         """Pipeline stages other than the last learn the sampled tokens from the last stage's
@@ -520,6 +549,8 @@ class ModelRunner:
             return   # the latent-attention path still has host-side steps (indexer top-k): eager only
         if self.lora is not None:
             return   # which adapter kernels run depends on the step's requests: eager only
+        if self.eplb is not None:
+            return   # the replica tables change between steps and loads are recorded on the host side
         from sonar_b200.ops import cuda as cuda_ops
         tp = get_tp_context()
         sizes = sorted({b for b in [1, 2, 4, 8, 16, 24, 32, 40, 48, 56, 64] + list(range(80, 513, 16))

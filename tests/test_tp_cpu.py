@@ -24,6 +24,20 @@ def test_moe_tp2_and_ep2_match_tp1_on_cpu(tmp_path):
             assert d < 1e-3, (name, d)
 
 
+def test_expert_load_balancing_ep2_on_cpu(tmp_path):
+    """EP2 with two redundant expert slots: replicas are used, the placement is rearranged every 3 steps
+    (weights move between ranks), and the numbers still match the single-rank model."""
+    ckpt = make_checkpoint(str(tmp_path / "ckpt"), "tiny-qwen3-moe", dtype=torch.float32)
+    one = launch(1, ckpt, str(tmp_path / "tp1.json"), "cpu")
+    two = launch(2, ckpt, str(tmp_path / "eplb2.json"), "cpu",
+                 env_extra={"SONAR_TEST_EP": "1", "SONAR_TEST_EPLB": "1"}, port=29623)
+    extra = two.pop()
+    assert extra["rearrangements"] >= 1 and all(extra["same"])
+    for a, b in zip(one, two):
+        d = (torch.tensor(a["prompt_logprobs"]) - torch.tensor(b["prompt_logprobs"])).abs().max()
+        assert d < 1e-3, d
+
+
 def test_pipeline_parallel_2_stages_matches_single_on_cpu(tmp_path):
     ckpt = make_checkpoint(str(tmp_path / "ckpt"), "tiny-llama", dtype=torch.float32)
     one = launch(1, ckpt, str(tmp_path / "pp1.json"), "cpu")

@@ -29,6 +29,9 @@ def run(ckpt: str, device: str, world: int):
               pipeline_parallel_size=int(os.environ.get("SONAR_TEST_PP", "1")),
               num_gpu_blocks_override=512 if device == "cpu" else None,
               enable_expert_parallel=os.environ.get("SONAR_TEST_EP") == "1",
+              enable_eplb=os.environ.get("SONAR_TEST_EPLB") == "1",
+              num_redundant_experts=2 if os.environ.get("SONAR_TEST_EPLB") == "1" else 0,
+              eplb_window=4, eplb_interval=3,
               distributed_executor_backend="external_launcher" if world > 1 else "uni")
     sp = SamplingParams(temperature=0, max_tokens=4, prompt_logprobs=0, ignore_eos=True, detokenize=False)
     outs = llm.generate([{"prompt_token_ids": p} for p in prompts()], sp)
@@ -36,6 +39,12 @@ def run(ckpt: str, device: str, world: int):
     for o, p in zip(outs, prompts()):
         lps = [o.prompt_logprobs[i][p[i]].logprob for i in range(1, len(p))]
         res.append({"tokens": o.outputs[0].token_ids, "prompt_logprobs": lps})
+    if os.environ.get("SONAR_TEST_EPLB") == "1":
+        # a second pass runs on the rearranged placement and must reproduce the first
+        again = llm.generate([{"prompt_token_ids": p} for p in prompts()], sp)
+        stats = llm.llm_engine.get_stats()["workers"][0]
+        res.append({"rearrangements": stats.get("eplb_rearrangements", 0),
+                    "same": [a.outputs[0].token_ids == o.outputs[0].token_ids for a, o in zip(again, outs)]})
     if device == "cuda":
         from sonar_b200.ops import cuda as cu
         torch.cuda.synchronize()

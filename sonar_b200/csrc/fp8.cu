@@ -58,6 +58,12 @@ struct Fp8Params {
   const float* sa_t; long sa_ld;    // [K/128, sa_ld] transposed activation scales
   const float* sb; long sb_ld;      // [ceil(N/128), sb_ld] weight block scales
   int* err;
+  // grouped (mixture-of-experts) mode: A rows are grouped into 128-row blocks that each belong to one
+  // expert; block b multiplies expert block_expert[b]'s weights = B rows [e·N, (e+1)·N) of the stacked
+  // tensor and scale rows [e·sb_rows, (e+1)·sb_rows).  m_blocks_dev = device word with the block count.
+  const int* block_expert;
+  const int* m_blocks_dev;
+  int sb_rows;
 };
 
 template <typename OutT>
@@ -76,7 +82,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
+  const bool grouped = p.block_expert != nullptr;
+  int num_m = (p.M + BM - 1) / BM;
+  if (p.m_blocks_dev) { const int present = *p.m_blocks_dev; num_m = present < num_m ? present : num_m; }
+  const int num_n = (p.N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (p.K + BK - 1) / BK;
 
@@ -100,6 +109,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int m_idx = tile % num_m, n_idx = tile / num_m;
+        const int b_row0 = grouped ? p.block_expert[m_idx] * p.N : 0;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -107,7 +117,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
           tc::mbar_expect_tx(full_bar(s), STAGE_BYTES);
           const uint32_t a_dst = smem0 + s * STAGE_BYTES;
           tc::tma_load_2d(a_dst, &tma_a, full_bar(s), kb * BK, m_idx * BM);
-          tc::tma_load_2d(a_dst + A_BYTES, &tma_b, full_bar(s), kb * BK, n_idx * BN);
+          tc::tma_load_2d(a_dst + A_BYTES, &tma_b, full_bar(s), kb * BK, b_row0 + n_idx * BN);
         }
       }
     }
@@ -149,13 +159,14 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       float acc[BN];
 #pragma unroll
       for (int i = 0; i < BN; ++i) acc[i] = 0.f;
+      const float* sb_row = p.sb + (long)((grouped ? p.block_expert[m_idx] * p.sb_rows : 0) + n_idx) * p.sb_ld;
       float sa_next = p.sa_t[row_c];
-      float sb_next = p.sb[(long)n_idx * p.sb_ld];
+      float sb_next = sb_row[0];
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const float scale = sa_next * sb_next;
         if (kb + 1 < num_kb) {
           sa_next = p.sa_t[(long)(kb + 1) * p.sa_ld + row_c];
-          sb_next = p.sb[(long)n_idx * p.sb_ld + kb + 1];
+          sb_next = sb_row[kb + 1];
         }
         const int buf = it & 1;
         const uint32_t bph = (it >> 1) & 1;
@@ -228,8 +239,44 @@ SONAR_API int sonar_gemm_fp8_block(const void* Aq, const float* sa_t, long sa_ld
   if (rc != SONAR_OK) return rc;
   rc = cached_tmap_public(&tb, Bq, N, K, ldb, BN, 1);
   if (rc != SONAR_OK) return rc;
-  Fp8Params p{M, N, K, C, ldc, sa_t, sa_ld, sb, sb_ld, err};
+  Fp8Params p{M, N, K, C, ldc, sa_t, sa_ld, sb, sb_ld, err, nullptr, nullptr, 0};
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int sms = num_sms_public();
+  const int grid = tiles < sms ? tiles : sms;
+  static bool attr_done[2] = {false, false};
+  if (out_dtype == SONAR_BF16) {
+    auto kern = gemm_fp8_kernel<__nv_bfloat16>;
+    if (!attr_done[0]) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); attr_done[0] = true; }
+    kern<<<grid, NUM_THREADS, SMEM, s>>>(ta, tb, p);
+  } else if (out_dtype == SONAR_F16) {
+    auto kern = gemm_fp8_kernel<__half>;
+    if (!attr_done[1]) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM); attr_done[1] = true; }
+    kern<<<grid, NUM_THREADS, SMEM, s>>>(ta, tb, p);
+  } else {
+    return SONAR_BAD_ARG;
+  }
+  return check_launch();
+}
+
+// Grouped (mixture-of-experts) form.  Aq: [max_rows, K] e4m3 rows in the expert-sorted, 128-row padded layout
+// of sonar_moe_align with transposed group scales sa_t [K/128, sa_ld]; Wq: stacked weights [n_experts·N, K]
+// with block scales sb [n_experts·ceil(N/128), K/128]; block_expert[b] = expert of row block b;
+// m_blocks_dev = number of blocks present (read on the device).  N must be a multiple of 128 so that no
+// weight tile straddles two experts.
+SONAR_API int sonar_gemm_fp8_grouped(const void* Aq, const float* sa_t, long sa_ld, const void* Wq, const float* sb,
+                                     long sb_ld, void* C, int max_rows, int N, int K, int n_experts, long lda, long ldw,
+                                     long ldc, const int* block_expert, const int* m_blocks_dev, int out_dtype,
+                                     int* err, cudaStream_t s) {
+  if (max_rows <= 0) return max_rows == 0 ? SONAR_OK : SONAR_BAD_ARG;
+  if (N <= 0 || K <= 0 || n_experts <= 0 || max_rows % BM || N % BN || K % 128 || lda % 16 || ldw % 16 || ldc % 8)
+    return SONAR_BAD_ARG;
+  CUtensorMap ta, tb;
+  int rc = cached_tmap_public(&ta, Aq, max_rows, K, lda, BM, 1);
+  if (rc != SONAR_OK) return rc;
+  rc = cached_tmap_public(&tb, Wq, (uint64_t)n_experts * N, K, ldw, BN, 1);
+  if (rc != SONAR_OK) return rc;
+  Fp8Params p{max_rows, N, K, C, ldc, sa_t, sa_ld, sb, sb_ld, err, block_expert, m_blocks_dev, N / BN};
+  const int tiles = (max_rows / BM) * (N / BN);
   const int sms = num_sms_public();
   const int grid = tiles < sms ? tiles : sms;
   static bool attr_done[2] = {false, false};

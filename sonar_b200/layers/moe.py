@@ -35,7 +35,7 @@ class FusedMoE(nn.Module):
     def __init__(self, num_experts: int, top_k: int, hidden: int, inter: int, dtype, device, renormalize: bool = True,
                  scoring: str = "softmax", n_group: int = 1, topk_group: int = 1, routed_scaling: float = 1.0,
                  use_bias: bool = False, expert_parallel: bool = False, placement: str = "linear",
-                 prefix: str = "", num_redundant: int = 0) -> None:
+                 prefix: str = "", num_redundant: int = 0, quantization: str | None = None) -> None:
         super().__init__()
         self.num_experts, self.top_k, self.hidden, self.inter = num_experts, top_k, hidden, inter
         self.renormalize, self.scoring = renormalize, scoring
@@ -81,18 +81,41 @@ class FusedMoE(nn.Module):
             self.local_of = {g: [g] for g in range(num_experts)}
             self.inter_local = inter // tp
         self.n_local = n_local
-        self.w13 = nn.Parameter(torch.empty(n_local, 2 * self.inter_local, hidden, dtype=dtype, device=device),
+        self.fp8 = quantization == "fp8"
+        wdt = dtype
+        self.w13_scale = self.w2_scale = None
+        if self.fp8:
+            # e4m3 expert weights with one fp32 scale per 128×128 block (the checkpoint's weight_scale_inv)
+            if self.inter_local % 128 or hidden % 128:
+                raise ValueError("fp8 experts need hidden and per-rank intermediate sizes divisible by 128")
+            wdt = torch.float8_e4m3fn
+            self.w13_scale = nn.Parameter(torch.ones(n_local, 2 * self.inter_local // 128, hidden // 128,
+                                                     dtype=torch.float32, device=device), requires_grad=False)
+            self.w2_scale = nn.Parameter(torch.ones(n_local, hidden // 128, self.inter_local // 128,
+                                                    dtype=torch.float32, device=device), requires_grad=False)
+        self.w13 = nn.Parameter(torch.empty(n_local, 2 * self.inter_local, hidden, dtype=wdt, device=device),
                                 requires_grad=False)
-        self.w2 = nn.Parameter(torch.empty(n_local, hidden, self.inter_local, dtype=dtype, device=device),
+        self.w2 = nn.Parameter(torch.empty(n_local, hidden, self.inter_local, dtype=wdt, device=device),
                                requires_grad=False)
         self.e_bias = (nn.Parameter(torch.zeros(num_experts, dtype=torch.float32, device=device), requires_grad=False)
                        if use_bias else None)
         self.prefix = prefix
 
     # weight loading: (expert id, "gate" | "up" | "down") -------------------------------
-    def load_expert_weight(self, expert: int, which: str, tensor: torch.Tensor) -> bool:
+    def load_expert_weight(self, expert: int, which: str, tensor: torch.Tensor, is_scale: bool = False) -> bool:
         il = self.inter_local
         lo = 0 if self.expert_parallel else self.rank * il
+        if is_scale:
+            il, lo = il // 128, lo // 128
+            w13, w2 = self.w13_scale, self.w2_scale
+            for local in self.local_of.get(expert, ()):
+                if which == "gate":
+                    w13.data[local, :il].copy_(tensor[lo:lo + il])
+                elif which == "up":
+                    w13.data[local, il:].copy_(tensor[lo:lo + il])
+                else:
+                    w2.data[local].copy_(tensor[:, lo:lo + il])
+            return True
         for local in self.local_of.get(expert, ()):      # empty: another rank's expert; several: replicas
             if which == "gate":
                 self.w13.data[local, :il].copy_(tensor[lo:lo + il])
@@ -101,6 +124,32 @@ class FusedMoE(nn.Module):
             else:
                 self.w2.data[local].copy_(tensor[:, lo:lo + il])
         return True
+
+    def init_dummy(self, seed: int, std: float) -> set[int]:
+        """Random fp8 experts: per logical expert, bf16 normal(0, std) matrices quantised with real block
+        scales and loaded through the checkpoint path (so every parallel layout sees the same expert)."""
+        if not self.fp8:
+            return set()
+        from sonar_b200.loader.weights import _name_seed
+        from sonar_b200.ops import torch_ref
+        dev = self.w13.device
+        full_i = self.inter if self.expert_parallel else self.inter_local * self.tp
+        for e in sorted(self.local_of):
+            gen = torch.Generator(device=dev).manual_seed(_name_seed(f"{self.prefix}.{e}", seed))
+            for which, shape in (("gate", (full_i, self.hidden)), ("up", (full_i, self.hidden)),
+                                 ("down", (self.hidden, full_i))):
+                full = torch.empty(shape, dtype=torch.bfloat16, device=dev).normal_(0.0, std, generator=gen)
+                q, sc = torch_ref.block_quant_fp8_weight(full, 128)
+                self.load_expert_weight(e, which, q)
+                self.load_expert_weight(e, which, sc, is_scale=True)
+        return {id(self.w13), id(self.w2), id(self.w13_scale), id(self.w2_scale)}
+
+    def expert_tensors(self) -> list[torch.Tensor]:
+        """Per-slot tensors that move together when the expert placement changes."""
+        ts = [self.w13.data, self.w2.data]
+        if self.fp8:
+            ts += [self.w13_scale.data, self.w2_scale.data]
+        return ts
 
     def set_mapping(self, phy2log: torch.Tensor) -> None:
         """Install a physical-slot → logical-expert assignment (``[P]``, rank-major) for this layer."""
@@ -141,4 +190,5 @@ class FusedMoE(nn.Module):
             ids = self.log2phy[idl, spread % self.logcnt[idl]].to(torch.int32)
             if self.eplb_state is not None:
                 self.eplb_state.record(self.eplb_index, ids)
-        return ops.fused_experts(x, self.w13, self.w2, w, ids, self.expert_map, combine_to)
+        return ops.fused_experts(x, self.w13, self.w2, w, ids, self.expert_map, combine_to, self.w13_scale,
+                                 self.w2_scale)

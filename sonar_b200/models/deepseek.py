@@ -191,7 +191,8 @@ class DeepseekMoE(nn.Module):
             n_group=int(g("n_group", 1) or 1), topk_group=int(g("topk_group", 1) or 1),
             routed_scaling=float(g("routed_scaling_factor", 1.0)), use_bias=g("topk_method", "noaux_tc") == "noaux_tc",
             expert_parallel=bool(g("_expert_parallel", False)), placement=g("_expert_placement", "linear"),
-            prefix=f"{prefix}.experts", num_redundant=int(g("_num_redundant_experts", 0) or 0))
+            prefix=f"{prefix}.experts", num_redundant=int(g("_num_redundant_experts", 0) or 0),
+            quantization=cfg.quantization)
         n_shared = int(g("n_shared_experts", 0) or 0)
         self.shared_experts = (LlamaMLP(cfg.hidden_size, inter * n_shared, cfg.dtype, device, cfg.quantization,
                                         f"{prefix}.shared_experts") if n_shared else None)
@@ -258,7 +259,7 @@ class DeepseekModel(nn.Module):
         return x
 
 
-_EXPERT_RE = re.compile(r"(.*\.mlp)\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.weight$")
+_EXPERT_RE = re.compile(r"(.*\.mlp)\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.(weight|weight_scale_inv)$")
 
 
 class DeepseekForCausalLM(nn.Module):
@@ -293,7 +294,8 @@ class DeepseekForCausalLM(nn.Module):
             except AttributeError:
                 return True
             which = {"gate_proj": "gate", "up_proj": "up", "down_proj": "down"}[m.group(3)]
-            return block.experts.load_expert_weight(int(m.group(2)), which, tensor)
+            return block.experts.load_expert_weight(int(m.group(2)), which, tensor,
+                                                    is_scale=m.group(4) == "weight_scale_inv")
         if name.endswith(".mlp.gate.e_score_correction_bias"):
             try:
                 block = self.get_submodule(name.rsplit(".gate.", 1)[0])

@@ -27,7 +27,8 @@ class SparseMoeBlock(nn.Module):
         self.experts = FusedMoE(n_exp, int(cfg.get("num_experts_per_tok", 2)), cfg.hidden_size, inter, cfg.dtype,
                                 device, renormalize=bool(cfg.get("norm_topk_prob", True)),
                                 expert_parallel=expert_parallel, placement=placement, prefix=f"{prefix}.experts",
-                                num_redundant=int(cfg.get("_num_redundant_experts", 0)))
+                                num_redundant=int(cfg.get("_num_redundant_experts", 0)),
+                                quantization=cfg.quantization)
 
     def forward(self, x):
         tp = get_tp_context()
@@ -52,7 +53,7 @@ class Qwen3MoeModel(LlamaModel):
     layer_cls = Qwen3MoeDecoderLayer
 
 
-_EXPERT_RE = re.compile(r"(.*\.mlp)\.experts\.(\d+)\.(gate_proj|up_proj|down_proj|w1|w2|w3)\.weight$")
+_EXPERT_RE = re.compile(r"(.*\.mlp)\.experts\.(\d+)\.(gate_proj|up_proj|down_proj|w1|w2|w3)\.(weight|weight_scale_inv)$")
 _WHICH = {"gate_proj": "gate", "up_proj": "up", "down_proj": "down", "w1": "gate", "w3": "up", "w2": "down"}
 
 
@@ -68,7 +69,8 @@ class Qwen3MoeForCausalLM(LlamaForCausalLM):
             block = self.get_submodule(m.group(1))
         except AttributeError:
             return True   # a layer of another pipeline stage
-        return block.experts.load_expert_weight(int(m.group(2)), _WHICH[m.group(3)], tensor)
+        return block.experts.load_expert_weight(int(m.group(2)), _WHICH[m.group(3)], tensor,
+                                                is_scale=m.group(4) == "weight_scale_inv")
 
     def map_checkpoint_name(self, name: str):
         return super().map_checkpoint_name(name.replace(".block_sparse_moe.", ".mlp."))

@@ -147,14 +147,13 @@ def grouped_topk(logits, bias, k, n_group, topk_group, renormalize, scale, scori
     return ref.grouped_topk(logits, bias, k, n_group, topk_group, renormalize, scale, scoring)
 
 
-def fused_experts(x, w13, w2, topk_w, topk_ids, expert_map=None, combine_to=None):
+def fused_experts(x, w13, w2, topk_w, topk_ids, expert_map=None, combine_to=None, w13_scale=None, w2_scale=None):
     if _use_cuda(x):
-        return cuda_ops().fused_experts(x, w13, w2, topk_w, topk_ids, expert_map, combine_to)
+        return cuda_ops().fused_experts(x, w13, w2, topk_w, topk_ids, expert_map, combine_to, w13_scale, w2_scale)
     assert combine_to is None
-    return ref.fused_experts(x, w13, w2, topk_w, topk_ids, expert_map)
+    return ref.fused_experts(x, w13, w2, topk_w, topk_ids, expert_map, w13_scale, w2_scale)
 
 
-# ---- MLA -----------------------------------------------------------------------
 def mla_cache_write(kv_c, k_pe, cache, slot_mapping):
     if _use_cuda(kv_c):
         return cuda_ops().mla_cache_write(kv_c, k_pe, cache, slot_mapping)

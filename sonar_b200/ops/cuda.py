@@ -72,6 +72,8 @@ _moe_combine = _sig("sonar_moe_combine", c_void_p, c_void_p, c_void_p, c_int, c_
 _group_quant = _sig("sonar_group_quant_fp8", c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_long, c_int, c_void_p)
 _gemm_fp8 = _sig("sonar_gemm_fp8_block", c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_long, c_void_p, c_int, c_int,
                  c_int, c_long, c_long, c_long, c_int, c_void_p, c_void_p)
+_gemm_fp8_grouped = _sig("sonar_gemm_fp8_grouped", c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_long, c_void_p, c_int,
+                         c_int, c_int, c_int, c_long, c_long, c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p)
 _mla_write = _sig("sonar_mla_cache_write", c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_void_p, c_long, c_void_p,
                   c_int, c_void_p)
 _mla_attn = _sig("sonar_mla_attention", c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p, c_long, c_int,
@@ -556,10 +558,22 @@ def moe_align(topk_ids, n_local_experts, expert_map=None):
     return sc
 
 
-def fused_experts(x, w13, w2, topk_w, topk_ids, expert_map=None, combine_to=None):
+def _grouped_fp8(aq, a_scales_t, ld, w, w_scale, out, sc, err):
+    """aq [rows, K] e4m3 + transposed scales [K/128, ld]; w [E, N, K] e4m3, w_scale [E, N/128, K/128]."""
+    rows, k = aq.shape
+    e, n, _ = w.shape
+    _check(_gemm_fp8_grouped(aq.data_ptr(), a_scales_t.data_ptr(), ld, w.data_ptr(), w_scale.data_ptr(),
+                             w_scale.shape[2], out.data_ptr(), rows, n, k, e, k, k, out.stride(0),
+                             sc.block_expert.data_ptr(), sc.meta.data_ptr(), _DT[out.dtype], err, _stream()),
+           "gemm_fp8_grouped")
+
+
+def fused_experts(x, w13, w2, topk_w, topk_ids, expert_map=None, combine_to=None, w13_scale=None, w2_scale=None):
     """Routed-expert FFN on the expert-sorted layout: gather → grouped GEMM (w13) → SiLU·mul → grouped GEMM
     (w2) → weighted combine.  ``combine_to`` = (dst_ptrs, shard_rows, local_done, flag_ptrs, seq, seq_base)
-    sends each token's combined row to its owner's partial buffer instead of returning a local tensor."""
+    sends each token's combined row to its owner's partial buffer instead of returning a local tensor.
+    With ``w13_scale`` / ``w2_scale`` the weights are e4m3 with 128×128 block scales: activations are
+    group-quantised after the gather and inside the SiLU kernel, both GEMMs run on the fp8 tensor-core path."""
     t, h = x.shape
     e_local, n13, _ = w13.shape
     inter = w2.shape[2]
@@ -572,12 +586,18 @@ def fused_experts(x, w13, w2, topk_w, topk_ids, expert_map=None, combine_to=None
                        max_rows, _DT[x.dtype], _stream()), "moe_gather")
     g = torch.empty((max_rows, n13), dtype=x.dtype, device=x.device)
     err = error_word(x.device).data_ptr()
-    _check(_gemm_grouped(a.data_ptr(), w13.data_ptr(), g.data_ptr(), max_rows, n13, h, e_local, h, h, n13,
-                         sc.block_expert.data_ptr(), sc.meta.data_ptr(), err, _stream()), "gemm_grouped(w13)")
-    act = silu_and_mul(g)
     y = torch.empty((max_rows, h), dtype=x.dtype, device=x.device)
-    _check(_gemm_grouped(act.data_ptr(), w2.data_ptr(), y.data_ptr(), max_rows, h, inter, e_local, inter, inter, h,
-                         sc.block_expert.data_ptr(), sc.meta.data_ptr(), err, _stream()), "gemm_grouped(w2)")
+    if w13_scale is not None:
+        aq, a_s = per_token_group_quant_fp8(a)
+        _grouped_fp8(aq, a_s.t(), a_s.t().stride(0), w13, w13_scale, g, sc, err)
+        hq, h_s = silu_mul_group_quant(g)
+        _grouped_fp8(hq, h_s.t(), h_s.t().stride(0), w2, w2_scale, y, sc, err)
+    else:
+        _check(_gemm_grouped(a.data_ptr(), w13.data_ptr(), g.data_ptr(), max_rows, n13, h, e_local, h, h, n13,
+                             sc.block_expert.data_ptr(), sc.meta.data_ptr(), err, _stream()), "gemm_grouped(w13)")
+        act = silu_and_mul(g)
+        _check(_gemm_grouped(act.data_ptr(), w2.data_ptr(), y.data_ptr(), max_rows, h, inter, e_local, inter, inter, h,
+                             sc.block_expert.data_ptr(), sc.meta.data_ptr(), err, _stream()), "gemm_grouped(w2)")
     tw = topk_w.float().contiguous()
     if combine_to is None:
         out = torch.empty((t, h), dtype=x.dtype, device=x.device)

@@ -338,9 +338,12 @@ def grouped_topk(logits: torch.Tensor, bias: torch.Tensor | None, k: int, n_grou
 
 
 def fused_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: torch.Tensor,
-                  topk_ids: torch.Tensor, expert_map: torch.Tensor | None = None) -> torch.Tensor:
+                  topk_ids: torch.Tensor, expert_map: torch.Tensor | None = None,
+                  w13_scale: torch.Tensor | None = None, w2_scale: torch.Tensor | None = None) -> torch.Tensor:
     """Reference MoE FFN.  w13: [E, 2I, H] (gate rows then up rows), w2: [E, H, I].
-    ``expert_map[global id] = local id or -1`` restricts to locally held experts."""
+    ``expert_map[global id] = local id or -1`` restricts to locally held experts.  With block scales
+    (``w13_scale [E, 2I/128, H/128]``, ``w2_scale [E, H/128, I/128]``) weights are e4m3 and both GEMMs
+    take per-token-group quantised activations."""
     t, h = x.shape
     out = torch.zeros(t, h, dtype=torch.float32, device=x.device)
     ids = topk_ids.long()
@@ -350,8 +353,14 @@ def fused_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: 
         tok, slot = (ids == e).nonzero(as_tuple=True)
         if tok.numel() == 0:
             continue
-        a = silu_and_mul(F.linear(x[tok], w13[e]))
-        y = F.linear(a, w2[e]).float()
+        if w13_scale is not None:
+            xq, xs = per_token_group_quant_fp8(x[tok])
+            a = silu_and_mul(gemm_fp8_block(xq, xs, w13[e], w13_scale[e], x.dtype))
+            aq, a_s = per_token_group_quant_fp8(a)
+            y = gemm_fp8_block(aq, a_s, w2[e], w2_scale[e], x.dtype).float()
+        else:
+            a = silu_and_mul(F.linear(x[tok], w13[e]))
+            y = F.linear(a, w2[e]).float()
         out.index_add_(0, tok, y * topk_w[tok, slot, None].float())
     return out.to(x.dtype)
 

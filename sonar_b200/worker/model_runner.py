@@ -367,7 +367,7 @@ class ModelRunner:
         Every rank of the group calls this at the same step (they see identical routing)."""
         from sonar_b200.parallel import state as pstate
         group = pstate.get_tp_group().device_group if pstate.tp_world_size() > 1 else None
-        moved = self.eplb.rearrange([[m.w13.data, m.w2.data] for m in self.moe_layers], group)
+        moved = self.eplb.rearrange([m.expert_tensors() for m in self.moe_layers], group)
         for i, m in enumerate(self.moe_layers):
             m.set_mapping(self.eplb.phy2log[i])
         self.stats["eplb_rearrangements"] = self.eplb.rearrangements

@@ -166,3 +166,31 @@ def test_fp8_linear_fusions_match_unfused_path(monkeypatch):
     monkeypatch.setattr(llama_mod, "wants_quant_act", lambda layer: False)
     unfused = run()
     assert fused == unfused and all(len(t) == 6 for t in fused)
+
+
+def test_fp8_moe_experts_run_and_match_dequantised_reference():
+    """fp8 block-scaled expert weights: the engine runs; the layer equals an explicit dequantised computation."""
+    import torch
+    from sonar_b200.layers.moe import FusedMoE
+    from sonar_b200.ops import torch_ref
+    torch.manual_seed(0)
+    moe = FusedMoE(4, 2, 256, 128, torch.float32, "cpu", quantization="fp8", prefix="m")
+    moe.init_dummy(0, 0.05)
+    x = torch.randn(9, 256)
+    logits = torch.randn(9, 4)
+    y = moe(x, logits)
+    w, ids = moe.route(logits)
+    want = torch.zeros_like(y)
+    for t in range(9):
+        for k in range(2):
+            e = int(ids[t, k])
+            w13 = moe.w13[e].float() * moe.w13_scale[e].repeat_interleave(128, 0).repeat_interleave(128, 1)
+            w2 = moe.w2[e].float() * moe.w2_scale[e].repeat_interleave(128, 0).repeat_interleave(128, 1)
+            h = torch_ref.silu_and_mul((x[t:t + 1] @ w13.t()))
+            want[t] += float(w[t, k]) * (h @ w2.t())[0]
+    assert (y - want).norm() / want.norm() < 0.08          # activation quantisation noise only
+    llm = LLM(model="tiny-qwen3-moe", dtype="float32", quantization="fp8", max_model_len=128, device="cpu",
+              num_gpu_blocks_override=32, max_num_seqs=4, max_num_batched_tokens=64, seed=0,
+              hf_overrides={"hidden_size": 256, "moe_intermediate_size": 128, "intermediate_size": 512})
+    outs = llm.generate([{"prompt_token_ids": [1, 2, 3, 4]}], SamplingParams(max_tokens=4, temperature=0, ignore_eos=True))
+    assert len(outs[0].outputs[0].token_ids) == 4

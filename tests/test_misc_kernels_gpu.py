@@ -192,3 +192,35 @@ def test_cumem_sleep_wake_keeps_addresses_and_weights():
     kv.zero_()                                                  # discarded pool is usable again
     assert float(kv.sum()) == 0.0
     del w, kv
+
+
+@pytest.mark.parametrize("t,e,k,h,inter,ep", [(70, 8, 2, 512, 256, False), (300, 16, 4, 1024, 768, True),
+                                              (3, 8, 2, 256, 128, False)])
+def test_fused_experts_fp8_block_scaled(cu, t, e, k, h, inter, ep):
+    """Grouped fp8 GEMMs (per-expert 128×128 weight scales, per-token-group activation scales) against the
+    unquantised fp32 product; the error budget is fp8 quantisation noise."""
+    torch.manual_seed(40 + t)
+    x = torch.randn(t, h, device=DEV, dtype=torch.bfloat16)
+    w13f = torch.randn(e, 2 * inter, h, device=DEV) * 0.05
+    w2f = torch.randn(e, h, inter, device=DEV) * 0.05
+    q13, s13, q2, s2 = [], [], [], []
+    for i in range(e):
+        a, b = ref.block_quant_fp8_weight(w13f[i], 128)
+        c, d = ref.block_quant_fp8_weight(w2f[i], 128)
+        q13.append(a); s13.append(b); q2.append(c); s2.append(d)
+    q13, s13, q2, s2 = torch.stack(q13), torch.stack(s13), torch.stack(q2), torch.stack(s2)
+    logits = torch.randn(t, e, device=DEV)
+    tw, ids = ref.topk_softmax(logits, k, True)
+    emap = None
+    if ep:
+        emap = torch.full((e,), -1, dtype=torch.int32, device=DEV)
+        emap[1::2] = torch.arange(e // 2, dtype=torch.int32, device=DEV)
+        q13, s13, q2, s2 = (v[1::2].contiguous() for v in (q13, s13, q2, s2))
+        w13f, w2f = w13f[1::2].contiguous(), w2f[1::2].contiguous()
+    want = ref.fused_experts(x.float(), w13f, w2f, tw, ids, emap)
+    got = cu.fused_experts(x, q13, q2, tw, ids, emap, None, s13, s2)
+    torch.cuda.synchronize()
+    cu.check_device_errors()
+    assert (got.float() - want).norm() / want.norm() < 0.09
+    same = ref.fused_experts(x, q13, q2, tw, ids, emap, s13, s2)         # identical quantisation recipe
+    assert (got.float() - same.float()).norm() / want.norm() < 0.03

@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import re
 
+import numpy as np
 import torch
 from torch import nn
 
@@ -123,25 +124,10 @@ class MLAAttention(nn.Module):
         rd = self.rope_dim
         qi = torch.cat([_rope_interleaved(qi[..., :rd], meta.positions, self.cos_sin), qi[..., rd:]], dim=-1)
         wts = self.indexer_weights_proj(x).float() * (self.idx_heads ** -0.5) * (self.idx_dim ** -0.5)
-        bs = self.kv_cache.shape[1]
-        out = torch.full((t, self.index_topk), -1, dtype=torch.int32, device=x.device)
-        qsl, sl = meta.query_start_loc.tolist(), meta.seq_lens_cpu
-        for i in range(meta.num_seqs):
-            s, e, ctx = qsl[i], qsl[i + 1], int(sl[i])
-            if e <= s:
-                continue
-            nb = -(-ctx // bs)
-            rows = self.kv_cache[meta.block_tables[i, :nb].long()].reshape(nb * bs, -1)[:ctx]
-            kk = rows[:, self.kv_lora + rd:].float()                    # [ctx, idx_dim]
-            sc = torch.einsum("qhd,kd->qhk", qi[s:e].float(), kk).relu_()
-            sc = (sc * wts[s:e, :, None]).sum(1)                         # [q, ctx]
-            qpos = torch.arange(ctx - (e - s), ctx, device=x.device)[:, None]
-            sc = sc.masked_fill(torch.arange(ctx, device=x.device)[None, :] > qpos, float("-inf"))
-            k = min(self.index_topk, ctx)
-            top = sc.topk(k, dim=-1)
-            idx = torch.where(torch.isinf(top.values), torch.full_like(top.indices, -1), top.indices)
-            out[s:e, :k] = idx.int()
-        return out
+        q_lens = np.asarray(meta.query_lens_cpu, dtype=np.int64)
+        token_seq = torch.from_numpy(np.repeat(np.arange(len(q_lens), dtype=np.int32), q_lens)).to(x.device)
+        return ops.indexer_topk(qi.contiguous(), wts, self.kv_cache, self.kv_lora + rd, meta.block_tables, token_seq,
+                                meta.positions[:t], self.index_topk, int(max(meta.seq_lens_cpu)))
 
     def forward(self, x, meta: AttentionMetadata):
         tp = get_tp_context()

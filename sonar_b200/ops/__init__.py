@@ -266,3 +266,10 @@ def lora_expand(v, b, slots, y, y_off=0):
     if _use_cuda(y):
         return cuda_ops().lora_expand(v, b, slots, y, y_off)
     return ref.lora_expand(v, b, slots, y, y_off)
+
+
+# ---- sparse-attention indexer ----------------------------------------------------
+def indexer_topk(q, w, cache, key_off, block_tables, token_seq, positions, k, max_seq_len=None):
+    if _use_cuda(q):
+        return cuda_ops().indexer_topk(q, w, cache, key_off, block_tables, token_seq, positions, k, max_seq_len)
+    return ref.indexer_topk(q, w, cache, key_off, block_tables, token_seq, positions, k)

@@ -102,6 +102,9 @@ _lora_shrink = _sig("sonar_lora_shrink", c_void_p, c_long, c_void_p, c_void_p, c
                     c_void_p)
 _lora_expand = _sig("sonar_lora_expand", c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int,
                     c_int, c_void_p)
+_idx_logits = _sig("sonar_indexer_logits", c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p, c_long, c_void_p,
+                   c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_void_p)
+_idx_topk = _sig("sonar_indexer_topk", c_void_p, c_long, c_void_p, c_int, c_void_p, c_int, c_void_p)
 lib.sonar_last_cuda_error.restype = c_int
 lib.sonar_gemm_pick_bn.argtypes = [c_int, c_int, c_int, c_int]
 lib.sonar_gemm_pick_bn.restype = c_int
@@ -703,3 +706,32 @@ def lora_expand(v, b, slots, y, y_off=0):
     _check(_lora_expand(v.data_ptr(), b.data_ptr(), slots.data_ptr(), y.data_ptr(), y.stride(0), y_off, t, b.shape[1], r,
                         _DT[y.dtype], _stream()), "lora_expand")
     return y
+
+
+# ---------------------------------------------------------------- sparse-attention indexer
+INDEXER_LOGIT_BYTES = 256 << 20      # logits scratch per chunk of query tokens
+
+
+def indexer_topk(q, w, cache, key_off, block_tables, token_seq, positions, k, max_seq_len=None):
+    """Top-k key positions per query token (see the PyTorch restatement).  bf16, 64 heads of 128 only —
+    other shapes use the restatement.  Query tokens are processed in chunks so the fp32 logits scratch
+    stays under ``INDEXER_LOGIT_BYTES``."""
+    t, hi, di = q.shape
+    if hi != 64 or di != 128 or q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        return ref.indexer_topk(q, w, cache, key_off, block_tables, token_seq, positions, k)
+    q = q.contiguous()
+    w = w.float().contiguous()
+    if max_seq_len is None:
+        max_seq_len = int(positions.max().item()) + 1
+    ld = (max_seq_len + 255) // 256 * 256
+    out = torch.empty((t, k), dtype=torch.int32, device=q.device)
+    chunk = max(1, min(t, INDEXER_LOGIT_BYTES // (ld * 4), 65535))
+    logits = torch.empty((chunk, ld), dtype=torch.float32, device=q.device)
+    for lo in range(0, t, chunk):
+        n = min(chunk, t - lo)
+        _check(_idx_logits(q[lo:].data_ptr(), w[lo:].data_ptr(), cache.data_ptr(), cache.shape[2], key_off,
+                           cache.shape[1], block_tables.data_ptr(), block_tables.stride(0), token_seq[lo:].data_ptr(),
+                           positions[lo:].data_ptr(), logits.data_ptr(), ld, n, hi, di, _stream()), "indexer_logits")
+        _check(_idx_topk(logits.data_ptr(), ld, positions[lo:].data_ptr(), k, out[lo:].data_ptr(), n, _stream()),
+               "indexer_topk")
+    return out

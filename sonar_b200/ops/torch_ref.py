@@ -516,3 +516,23 @@ def lora_expand(v: torch.Tensor, b: torch.Tensor, slots: torch.Tensor, y: torch.
         m = slots == sl
         y[m, y_off:y_off + n] = (y[m, y_off:y_off + n].float() + v[m] @ b[sl].float().t()).to(y.dtype)
     return y
+
+
+# ---------------------------------------------------------------- sparse-attention indexer
+def indexer_topk(q: torch.Tensor, w: torch.Tensor, cache: torch.Tensor, key_off: int, block_tables: torch.Tensor,
+                 token_seq: torch.Tensor, positions: torch.Tensor, k: int) -> torch.Tensor:
+    """q [T, Hi, Di], w [T, Hi] fp32, cache [blocks, block_size, row] with the indexer key at ``key_off``.
+    → int32 [T, k]: positions of the k keys j ≤ positions[t] with the largest
+    Σ_h w[t,h]·relu(q[t,h]·key[j]) (any order), −1 padded."""
+    t, hi, di = q.shape
+    bs = cache.shape[1]
+    out = torch.full((t, k), -1, dtype=torch.int32, device=q.device)
+    for i in range(t):
+        n = int(positions[i]) + 1
+        nb = -(-n // bs)
+        rows = cache[block_tables[int(token_seq[i]), :nb].long()].reshape(nb * bs, -1)[:n]
+        keys = rows[:, key_off:key_off + di].float()
+        sc = (torch.relu(q[i].float() @ keys.t()) * w[i].float()[:, None]).sum(0)
+        kk = min(k, n)
+        out[i, :kk] = sc.topk(kk).indices.int()
+    return out

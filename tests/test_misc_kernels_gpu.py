@@ -224,3 +224,35 @@ def test_fused_experts_fp8_block_scaled(cu, t, e, k, h, inter, ep):
     assert (got.float() - want).norm() / want.norm() < 0.09
     same = ref.fused_experts(x, q13, q2, tw, ids, emap, s13, s2)         # identical quantisation recipe
     assert (got.float() - same.float()).norm() / want.norm() < 0.03
+
+
+def test_indexer_logits_and_topk(cu):
+    """Sparse-attention indexer: the selected key sets equal those of the PyTorch restatement."""
+    torch.manual_seed(50)
+    bs, row, key_off, k = 16, 704, 576, 64
+    seq_lens = [700, 40, 333]
+    q_lens = [3, 1, 2]
+    nblocks = sum(-(-s // bs) for s in seq_lens) + 1
+    cache = (torch.randn(nblocks, bs, row, device=DEV) * 0.5).to(torch.bfloat16)
+    bt = torch.zeros(3, 64, dtype=torch.int32, device=DEV)
+    perm = torch.randperm(nblocks - 1, device=DEV).int() + 1
+    o = 0
+    for i, s in enumerate(seq_lens):
+        nb = -(-s // bs)
+        bt[i, :nb] = perm[o:o + nb]
+        o += nb
+    token_seq = torch.tensor(sum(([i] * n for i, n in enumerate(q_lens)), []), dtype=torch.int32, device=DEV)
+    positions = torch.tensor(sum(([s - n + j for j in range(n)] for s, n in zip(seq_lens, q_lens)), []),
+                             dtype=torch.int64, device=DEV)
+    t = len(token_seq)
+    q = (torch.randn(t, 64, 128, device=DEV) * 0.5).to(torch.bfloat16)
+    w = torch.rand(t, 64, device=DEV) + 0.1
+    got = cu.indexer_topk(q, w, cache, key_off, bt, token_seq, positions, k)
+    want = ref.indexer_topk(q, w, cache, key_off, bt, token_seq, positions, k)
+    for i in range(t):
+        g = set(x for x in got[i].tolist() if x >= 0)
+        wv = set(x for x in want[i].tolist() if x >= 0)
+        n = int(positions[i]) + 1
+        assert len(g) == min(k, n) and all(0 <= x < n for x in g)
+        # bf16 tensor-core accumulation vs fp32: allow a couple of swaps at the selection boundary
+        assert len(g ^ wv) <= 4, (i, sorted(g ^ wv))

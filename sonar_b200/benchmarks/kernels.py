@@ -141,6 +141,7 @@ def main() -> None:
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--pair", action="store_true", help="whole waves on the two-SM (cta_group::2) kernel")
     ap.add_argument("--seqs", type=int, default=256)
     ap.add_argument("--ctx", type=int, default=1152)
     ap.add_argument("--q", type=int, default=1024)
@@ -154,6 +155,8 @@ def main() -> None:
     a = ap.parse_args()
     from sonar_b200.ops import cuda as cu
     flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    if getattr(a, "pair", False):
+        cu.set_gemm_pair(True)
     if a.what == "gemm":
         bench_gemm(cu, a.m, a.n, a.k, a.iters, a.warmup, flush, not a.no_compare, a.bn)
     elif a.what == "attn-decode":

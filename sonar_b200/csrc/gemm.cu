@@ -76,6 +76,7 @@ struct GemmParams {
   int ws_ctas;        // workspace capacity in CTAs
   int sk_tiles, sk_split; // split-K tail: the last sk_tiles tiles are each split over sk_split CTAs (0: none)
   int* ws_count;          // [sk_tiles] arrival counters of the split tiles, zero between launches
+  int tile_begin;         // first tile (m-fastest order) this launch covers; earlier ones belong to another kernel
   // grouped (mixture-of-experts) mode: A rows are expert-sorted and padded to 128-row blocks; block b uses
   // expert block_expert[b]'s weights, i.e. B rows [e·N, (e+1)·N) of the stacked weight tensor
   const int* block_expert;
@@ -178,7 +179,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   // stores its own share of the tile's 32-column chunks (chunk ch belongs to part ch mod S), so the
   // fix-up is spread over all S CTAs instead of serialised on one.
   const int S = p.sk_split;
-  const int dp_waves = p.sk_tiles > 0 ? (num_tiles - p.sk_tiles) / (int)gridDim.x : (num_tiles + gridDim.x - 1) / gridDim.x;
+  const int my_tiles = num_tiles - p.tile_begin;
+  const int dp_waves = p.sk_tiles > 0 ? (my_tiles - p.sk_tiles) / (int)gridDim.x : (my_tiles + gridDim.x - 1) / gridDim.x;
   const int sk_tile0 = num_tiles - p.sk_tiles;
   const bool in_sk = p.sk_tiles > 0 && (int)blockIdx.x < p.sk_tiles * S;
   const int sk_j = in_sk ? (int)blockIdx.x / S : 0, sk_s = in_sk ? (int)blockIdx.x % S : 0;
@@ -187,7 +189,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   struct Seg { int tile, kb0, kb1; bool split; };
   auto next_seg = [&](int& wave, long& g, Seg& sg) -> bool {
     while (wave < dp_waves) {
-      const int t = (int)blockIdx.x + wave * (int)gridDim.x;
+      const int t = p.tile_begin + (int)blockIdx.x + wave * (int)gridDim.x;
       ++wave;
       if (t >= (p.sk_tiles > 0 ? sk_tile0 : num_tiles)) continue;
       sg.tile = t; sg.kb0 = 0; sg.kb1 = num_kb; sg.split = false;
@@ -557,7 +559,8 @@ int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p
       return check_launch();
     attr_done = true;
   }
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) - p.tile_begin;
+  if (tiles <= 0) return SONAR_OK;
   const int num_kb = (p.K + BK - 1) / BK;
   GemmParams q = p;
   const int sms = num_sms();
@@ -602,9 +605,18 @@ int cached_tmap_public(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_
   return cached_tmap(out, ptr, rows, cols, ld, box_rows, eb);
 }
 int num_sms_public() { return num_sms(); }
+bool g_pair_enabled = false;
 }  // namespace sonar
 
 using namespace sonar;
+
+extern "C" int sonar_gemm_pair_resident();
+extern "C" int sonar_gemm_pair(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long lda,
+                               long ldb, long ldc, int dtype, int num_tiles, int pairs, int* err, cudaStream_t s);
+
+// Large-M GEMMs run their whole waves of 256×256 tiles on CTA pairs (tcgen05 cta_group::2) and the partial
+// last wave on the one-CTA kernel with its split-K tail.
+SONAR_API void sonar_gemm_set_pair(int enable) { g_pair_enabled = enable != 0; }
 
 // C = A · B^T (+ bias).  in_dtype: bf16/f16 for A and B; out_dtype: same 16-bit type or fp32.
 // Requirements: K % 8 == 0 (16-byte row pitch), N % 8 == 0 (N % 4 for fp32 out), 16-byte aligned bases.
@@ -621,6 +633,20 @@ SONAR_API int sonar_gemm(const void* A, const void* B, void* C, const void* bias
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.bias = bias; p.err = err;
   p.tp = 1; p.shard_rows = M;
   p.ws = ws; p.ws_flags = ws_flags; p.ws_ctas = ws_ctas;
+  const int num_m1 = (M + BM - 1) / BM;
+  if (g_pair_enabled && !force_bn && out_dtype == in_dtype && M >= 512 && N >= 512 && num_m1 % 2 == 0 &&
+      (N % 256 == 0 || N > 2048)) {
+    const int pairs = sonar_gemm_pair_resident();
+    const int tiles2 = (num_m1 / 2) * ((N + 255) / 256);
+    const int n2 = pairs > 0 ? (tiles2 / pairs) * pairs : 0;
+    if (n2 > 0) {
+      int rc = sonar_gemm_pair(A, B, C, bias, M, N, K, lda, ldb, ldc, in_dtype, n2, pairs, err, s);
+      if (rc != SONAR_OK || n2 == tiles2) return rc;
+      p.tile_begin = 2 * n2;      // the one-CTA kernel (BN = 256, same order) finishes the partial wave
+      if (in_dtype == SONAR_BF16) return launch_bn<__nv_bfloat16, 1>(256, A, B, p, lda, ldb, s);
+      return launch_bn<__half, 0>(256, A, B, p, lda, ldb, s);
+    }
+  }
   const int bn = force_bn ? force_bn : pick_bn(M, N, K, ws != nullptr);
   if (bn != 64 && bn != 128 && bn != 256) return SONAR_BAD_ARG;
   if (in_dtype == SONAR_BF16) {

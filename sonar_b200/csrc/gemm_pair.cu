@@ -1,0 +1,305 @@
+// Two-SM GEMM: a pair of CTAs (a cluster of 2) computes one 256×256 output tile with
+// tcgen05.mma.cta_group::2.  Each CTA stages its own 128 rows of A and its own 128 of the tile's 256
+// B rows (so every SM moves 32 KB per 64-wide k-block instead of 48 KB), the leader CTA issues the
+// MMAs for both, and each CTA's TMEM receives the accumulator of its own 128 rows × 256 columns.
+//
+//   C[M, N] = A[M, K] · B[N, K]^T (+ bias)      bf16 / fp16 in, same 16-bit type out, fp32 accumulate
+//
+// Roles in each CTA: warp 0 = TMA producer (own A half and B half; completion is counted on the
+// LEADER's "full" barrier — the loads carry .cta_group::2 so they may signal the peer's barrier),
+// warp 1 = MMA issuer (leader only; commits are multicast to both CTAs' "empty" / "accumulator
+// ready" barriers), warps 2-5 = epilogue (TMEM → registers → global; arrive on the leader's
+// "accumulator free" barrier, remotely from the second CTA).  Persistent: pair p takes tiles
+// p, p + P, … of the first `num_tiles` tiles in m-fastest order; the caller runs the remaining
+// tiles (a partial last wave) through the one-CTA kernel with its split-K tail.
+//
+// No operand is loaded with cluster multicast.  Every wait is bounded (2 s) and funnels to the
+// final cluster barrier, so a fault in the protocol surfaces as an error word, not a hang.
+#include "tcgen05.cuh"
+
+namespace sonar {
+int cached_tmap_public(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                       int eb);
+namespace {
+
+constexpr int BM = 128;                 // rows per CTA (256 per pair)
+constexpr int BN = 256;                 // tile columns
+constexpr int BNH = BN / 2;             // B rows staged per CTA
+constexpr int BK = 64;
+constexpr int STAGES = 6;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNH * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;   // 32 KB
+constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 2 * BN;       // two accumulator buffers
+
+struct PairParams {
+  int M, N, K;
+  void* C; long ldc;
+  const void* bias;
+  int* err;
+  int num_tiles;      // pair tiles to process (prefix of the m-fastest order over 256×256 tiles)
+  int num_m2;         // 256-row blocks
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_addr), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive on a barrier given by its shared::cluster address (this CTA's or the peer's)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load into this CTA's shared memory, completion bytes counted on a barrier that may live in
+// the peer CTA (shared::cluster address)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar_cluster,
+                                                 int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_dst), "l"(map), "r"(bar_cluster), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void mma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrive (once all MMAs issued so far are done) on the barrier at this offset in both CTAs of the pair
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"(mask) : "memory");
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store32(OutT* dst, const uint32_t* v, const OutT* bias, int ncols_ok) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    if (g * 8 + 8 <= ncols_ok) {
+      float f[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        f[i] = __uint_as_float(v[g * 8 + i]);
+        if (bias) f[i] += to_f<OutT>(bias[g * 8 + i]);
+      }
+      *reinterpret_cast<uint4*>(dst + g * 8) = pack8<OutT>(f);
+    }
+  }
+}
+
+template <typename OutT, int AB_FMT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const PairParams p) {
+  extern __shared__ uint8_t smem_dyn[];
+  const uint32_t smem0 = (tc::smem_u32(smem_dyn) + 1023u) & ~1023u;
+  uint8_t* smem_al = smem_dyn + (smem0 - tc::smem_u32(smem_dyn));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + STAGES * STAGE_BYTES);
+  const uint32_t bar0 = smem0 + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };                       // used in the leader
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };           // one per CTA
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };       // one per CTA
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };  // used in the leader
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { tc::mbar_init(full_bar(s), 1); tc::mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { tc::mbar_init(tfull_bar(b), 1); tc::mbar_init(tempty_bar(b), 256); }
+    *abort_flag = 0;
+    tc::mbar_fence_init();
+  }
+  if (warp == 1) tc::tmem_alloc(tc::smem_u32(tmem_slot), TMEM_COLS);
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  // the MMA addresses both CTAs' tensor memory with one column offset: with one CTA per SM each CTA
+  // owns all 512 columns, so both allocations start at column 0
+  if (threadIdx.x == 0 && (tmem_base & 0xFFFFu) != 0) {
+    *abort_flag = 1;
+    if (p.err) atomicCAS(p.err, 0, 7 | (blockIdx.x << 8));
+  }
+  cluster_sync();    // the peer's barriers are initialised before anything signals them
+  const bool usable = *abort_flag == 0;
+
+  if (warp == 0) {
+    // ------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0 && usable) {
+      tc::tma_prefetch_desc(&tma_a);
+      tc::tma_prefetch_desc(&tma_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs) {
+        const int m2 = tile % p.num_m2, n_idx = tile / p.num_m2;
+        const int a_row = m2 * 2 * BM + (int)rank * BM;
+        const int b_row = n_idx * BN + (int)rank * BNH;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!tc::mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.err, tc::SITE_EMPTY)) { ok = false; break; }
+          if (leader) tc::mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);      // both CTAs' bytes land here
+          const uint32_t bar = map_to_cta(full_bar(s), 0);
+          const uint32_t a_dst = smem0 + s * STAGE_BYTES;
+          tma_load_2d_pair(a_dst, &tma_a, bar, kb * BK, a_row);
+          tma_load_2d_pair(a_dst + A_BYTES, &tma_b, bar, kb * BK, b_row);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && leader && usable) {
+      constexpr uint32_t idesc = tc::make_idesc_f16(2 * BM, BN, AB_FMT);
+      uint32_t it = 0, seg = 0;
+      bool ok = true;
+      for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs, ++seg) {
+        const int buf = seg & 1;
+        const uint32_t bph = (seg >> 1) & 1;
+        if (!tc::mbar_wait(tempty_bar(buf), bph ^ 1, abort_flag, p.err, tc::SITE_TMEM_EMPTY)) break;
+        tc::fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!tc::mbar_wait(full_bar(s), ph, abort_flag, p.err, tc::SITE_FULL)) { ok = false; break; }
+          tc::fence_after_sync();
+          const uint32_t a_addr = smem0 + s * STAGE_BYTES;
+          const uint64_t adesc = tc::make_smem_desc_sw128(a_addr);
+          const uint64_t bdesc = tc::make_smem_desc_sw128(a_addr + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            mma_f16_pair(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > 0) | (k > 0));
+          mma_commit_pair(empty_bar(s));          // frees stage s in both CTAs
+        }
+        if (ok) mma_commit_pair(tfull_bar(buf));  // accumulator ready in both CTAs
+      }
+    }
+  } else if (usable) {
+    // ------------------------------------------------ epilogue (warps 2..5 ↔ TMEM lane groups 2,3,0,1)
+    const int lane_grp = warp & 3;
+    const int trow = lane_grp * 32 + lane;
+    uint32_t seg = 0;
+    for (int tile = pair; tile < p.num_tiles; tile += num_pairs, ++seg) {
+      const int m2 = tile % p.num_m2, n_idx = tile / p.num_m2;
+      const int row = m2 * 2 * BM + (int)rank * BM + trow;
+      const int buf = seg & 1;
+      const uint32_t bph = (seg >> 1) & 1;
+      if (!tc::mbar_wait(tfull_bar(buf), bph, abort_flag, p.err, tc::SITE_TMEM_FULL)) break;
+      tc::fence_after_sync();
+      const uint32_t t_row = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + buf * BN;
+      OutT* crow = reinterpret_cast<OutT*>(p.C) + (long)row * p.ldc + n_idx * BN;
+      const OutT* bias = p.bias ? reinterpret_cast<const OutT*>(p.bias) + n_idx * BN : nullptr;
+#pragma unroll 2
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tc::tmem_ld32(t_row + c * 32, v);
+        tc::tmem_ld_wait();
+        const int ok_cols = p.N - (n_idx * BN + c * 32);
+        if (row < p.M && ok_cols > 0) store32<OutT>(crow + c * 32, v, bias ? bias + c * 32 : nullptr, ok_cols);
+      }
+      tc::fence_before_sync();
+      mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0));     // the leader's MMA warp may reuse this buffer
+    }
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies that may still be in flight time to land before shared memory is released
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  cluster_sync();    // neither CTA leaves while the peer may still signal its barriers or read its tiles
+  if (warp == 1) {
+    __syncwarp();
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+int g_pairs = -1;   // co-resident CTA pairs of the device (0: clusters unavailable)
+
+template <typename OutT, int AB_FMT>
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const PairParams& p, int pairs, cudaStream_t s) {
+  auto kern = gemm_pair_kernel<OutT, AB_FMT>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+      return check_launch();
+    attr_done = true;
+  }
+  kern<<<2 * pairs, NUM_THREADS, SMEM, s>>>(ta, tb, p);
+  return check_launch();
+}
+
+int resident_pairs() {
+  if (g_pairs >= 0) return g_pairs;
+  auto kern = gemm_pair_kernel<__nv_bfloat16, 1>;
+  g_pairs = 0;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(sms & ~1, 1, 1);
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = SMEM;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); return 0; }
+  if (n > sms / 2) n = sms / 2;
+  g_pairs = n;
+  return g_pairs;
+}
+
+}  // namespace
+}  // namespace sonar
+
+using namespace sonar;
+
+// Number of CTA pairs that can be resident at once (0 when the pair kernel cannot run here).
+SONAR_API int sonar_gemm_pair_resident() { return resident_pairs(); }
+
+// Runs the first `num_tiles` 256×256 tiles (m-fastest order over ceil(M/256) × ceil(N/256)) on CTA pairs.
+// The caller covers the rest.  Same operand requirements as sonar_gemm; out dtype = in dtype (16 bit).
+SONAR_API int sonar_gemm_pair(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long lda,
+                              long ldb, long ldc, int dtype, int num_tiles, int pairs, int* err, cudaStream_t s) {
+  if (M <= 0 || N <= 0 || K <= 0 || num_tiles <= 0 || pairs <= 0) return SONAR_BAD_ARG;
+  if (K % 8 || lda % 8 || ldb % 8 || N % 8 || ldc % 8 || ((uintptr_t)C & 15)) return SONAR_BAD_ARG;
+  const int num_m2 = (M + 2 * BM - 1) / (2 * BM), num_n = (N + BN - 1) / BN;
+  if (num_tiles > num_m2 * num_n) return SONAR_BAD_ARG;
+  CUtensorMap ta, tb;
+  int rc = cached_tmap_public(&ta, A, M, K, lda, BM, 2);
+  if (rc != SONAR_OK) return rc;
+  rc = cached_tmap_public(&tb, B, N, K, ldb, BNH, 2);
+  if (rc != SONAR_OK) return rc;
+  PairParams p{M, N, K, C, ldc, bias, err, num_tiles, num_m2};
+  if (pairs > num_tiles) pairs = num_tiles;
+  if (dtype == SONAR_BF16) return launch_pair<__nv_bfloat16, 1>(ta, tb, p, pairs, s);
+  if (dtype == SONAR_F16) return launch_pair<__half, 0>(ta, tb, p, pairs, s);
+  return SONAR_BAD_ARG;
+}

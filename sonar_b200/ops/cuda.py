@@ -105,6 +105,11 @@ _lora_expand = _sig("sonar_lora_expand", c_void_p, c_void_p, c_void_p, c_void_p,
 _idx_logits = _sig("sonar_indexer_logits", c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p, c_long, c_void_p,
                    c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_void_p)
 _idx_topk = _sig("sonar_indexer_topk", c_void_p, c_long, c_void_p, c_int, c_void_p, c_int, c_void_p)
+_gemm_pair = _sig("sonar_gemm_pair", c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_long,
+                  c_int, c_int, c_int, c_void_p, c_void_p)
+lib.sonar_gemm_pair_resident.restype = c_int
+lib.sonar_gemm_set_pair.argtypes = [c_int]
+lib.sonar_gemm_set_pair.restype = None
 lib.sonar_last_cuda_error.restype = c_int
 lib.sonar_gemm_pick_bn.argtypes = [c_int, c_int, c_int, c_int]
 lib.sonar_gemm_pick_bn.restype = c_int
@@ -441,6 +446,27 @@ def gemm(x, w, bias=None, out=None, out_dtype=None, force_bn: int = 0):
                  *gemm_workspace(x.device), _stream()), "gemm")
     if bias is not None and kbias is None:
         out += bias.to(odt)
+    return out
+
+
+def set_gemm_pair(enable: bool) -> None:
+    """Route the whole waves of large-M GEMMs to the two-SM (cta_group::2) kernel."""
+    lib.sonar_gemm_set_pair(int(enable))
+
+
+set_gemm_pair(os.environ.get("SONAR_GEMM_PAIR", "0") == "1")
+
+
+def gemm_pair_tiles(x, w, out, num_tiles, bias=None, pairs=None):
+    """Two-SM kernel alone: the first ``num_tiles`` 256×256 tiles (m-fastest) of out = x @ w.T."""
+    m, k = x.shape
+    n = w.shape[0]
+    pairs = pairs or lib.sonar_gemm_pair_resident()
+    if pairs <= 0:
+        raise RuntimeError("two-SM clusters are not available on this device")
+    _check(_gemm_pair(x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(bias), m, n, k, x.stride(0), w.stride(0),
+                      out.stride(0), _DT[x.dtype], num_tiles, pairs, error_word(x.device).data_ptr(), _stream()),
+           "gemm_pair")
     return out
 
 

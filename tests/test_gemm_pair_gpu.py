@@ -1,0 +1,57 @@
+"""Two-SM (cta_group::2) GEMM: the pair kernel alone and the hybrid dispatch against fp32 PyTorch."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def cu():
+    from sonar_b200.ops import cuda
+    return cuda
+
+
+def _check(got, want, k):
+    err = (got.float() - want).abs().max().item()
+    scale = want.abs().max().item()
+    assert err <= 2e-2 * scale + 1e-2, (err, scale)
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (512, 512, 256), (1024, 768, 1024), (1000, 520, 328)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_pair_kernel_all_tiles(cu, m, n, k, dtype):
+    torch.manual_seed(m + n + k)
+    x = (torch.randn(m, k, device=DEV) * 0.5).to(dtype)
+    w = (torch.randn(n, k, device=DEV) * 0.5).to(dtype)
+    bias = torch.randn(n, device=DEV).to(dtype)
+    out = torch.full((m, n), float("nan"), device=DEV, dtype=dtype)
+    tiles = -(-m // 256) * -(-n // 256)
+    cu.gemm_pair_tiles(x, w, out, tiles, bias)
+    torch.cuda.synchronize()
+    cu.check_device_errors()
+    want = x.float() @ w.float().t() + bias.float()
+    assert not torch.isnan(out.float()).any()
+    _check(out, want, k)
+
+
+@pytest.mark.parametrize("m,n,k", [(4096, 6144, 4096), (8192, 4096, 1024), (1536, 28672, 512), (2048, 2560, 256)])
+def test_hybrid_dispatch(cu, m, n, k):
+    """Whole waves on CTA pairs + the partial last wave on the one-CTA split-K kernel cover every tile once."""
+    torch.manual_seed(m + n)
+    x = (torch.randn(m, k, device=DEV) * 0.3).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) * 0.3).to(torch.bfloat16)
+    cu.set_gemm_pair(True)
+    try:
+        out = torch.full((m, n), float("nan"), device=DEV, dtype=torch.bfloat16)
+        cu.gemm(x, w, out=out)
+        torch.cuda.synchronize()
+        cu.check_device_errors()
+    finally:
+        cu.set_gemm_pair(False)
+    assert not torch.isnan(out.float()).any()
+    ref = cu.gemm(x, w)                       # one-CTA kernel: same products, same accumulation order per tile
+    want = x.float() @ w.float().t()
+    _check(out, want, k)
+    assert (out.float() - ref.float()).abs().max().item() <= 2e-2 * want.abs().max().item()

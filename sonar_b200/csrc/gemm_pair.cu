@@ -26,7 +26,7 @@ constexpr int BM = 128;                 // rows per CTA (256 per pair)
 constexpr int BN = 256;                 // tile columns
 constexpr int BNH = BN / 2;             // B rows staged per CTA
 constexpr int BK = 64;
-constexpr int STAGES = 6;
+constexpr int STAGES = 7;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNH * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;   // 32 KB
 constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
 constexpr int NUM_THREADS = 192;

@@ -454,7 +454,7 @@ def set_gemm_pair(enable: bool) -> None:
     lib.sonar_gemm_set_pair(int(enable))
 
 
-set_gemm_pair(os.environ.get("SONAR_GEMM_PAIR", "0") == "1")
+set_gemm_pair(os.environ.get("SONAR_GEMM_PAIR", "1") == "1")
 
 
 def gemm_pair_tiles(x, w, out, num_tiles, bias=None, pairs=None):

@@ -69,6 +69,29 @@ def bench_gemm(cu, m, n, k, iters, warm, flush, compare=True, force_bn=0):
     return t
 
 
+def bench_gemm_fp8(cu, m, n, k, iters, warm, flush):
+    """Block-scaled fp8 GEMM (e4m3, 128×128 weight scales, per-token-group activation scales) and the
+    activation quantisation kernel that feeds it.  The roofline uses twice the measured bf16 peak (the fp8
+    tensor rate is nominally 2× bf16; no fp8 peak is measured separately)."""
+    from sonar_b200.ops import torch_ref as ref
+    hbm, tf, tag = peaks()
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16) * 0.05
+    wq, ws = ref.block_quant_fp8_weight(w, 128)
+    xq, xs = cu.per_token_group_quant_fp8(x)
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    flops = 2.0 * m * n * k
+    byts = 1.0 * (m * k + n * k) + 2.0 * m * n
+    t = timeit(lambda: cu.gemm_fp8_block(xq, xs, wq, ws, torch.bfloat16, out), iters, warm, flush)
+    tq = timeit(lambda: cu.per_token_group_quant_fp8(x), iters, warm, flush)
+    roof = max(flops / (2 * tf * 1e12), byts / (hbm * 1e9)) * 1e3
+    print(f"gemm_fp8_block M={m} N={n} K={k}: {t:.4f} ms, {flops / t / 1e9:.0f} TFLOP/s, {byts / t / 1e6:.0f} GB/s, "
+          f"{roof / t:.2f} {tag} roofline (2x bf16 peak); activation quant {tq:.4f} ms "
+          f"({3.0 * m * k / tq / 1e6:.0f} GB/s)", flush=True)
+    cu.check_device_errors()
+    return t
+
+
 def bench_attn_decode(cu, seqs, ctx, hq, hk, d, iters, warm, flush):
     hbm, _, tag = peaks()
     bs = 16
@@ -136,7 +159,7 @@ def bench_elementwise(cu, iters, warm, flush):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn-decode", "attn-prefill", "elementwise", "sweep"])
+    ap.add_argument("what", choices=["gemm", "gemm-fp8", "attn-decode", "attn-prefill", "elementwise", "sweep"])
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
@@ -159,6 +182,8 @@ def main() -> None:
         cu.set_gemm_pair(True)
     if a.what == "gemm":
         bench_gemm(cu, a.m, a.n, a.k, a.iters, a.warmup, flush, not a.no_compare, a.bn)
+    elif a.what == "gemm-fp8":
+        bench_gemm_fp8(cu, a.m, a.n, a.k, a.iters, a.warmup, flush)
     elif a.what == "attn-decode":
         bench_attn_decode(cu, a.seqs, a.ctx, a.hq, a.hk, a.head_dim, a.iters, a.warmup, flush)
     elif a.what == "attn-prefill":

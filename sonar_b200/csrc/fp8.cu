@@ -50,7 +50,9 @@ constexpr int BM = 128, BN = 128, BK = 128;
 constexpr int STAGES = 6;
 constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;     // producer warp, MMA warp, 8 epilogue warps (two per TMEM lane group)
+constexpr int NBUF = 4;              // accumulator buffers of BN columns (4 × 128 = all 512 TMEM columns)
+constexpr int CPT = BN / 2;          // columns per epilogue thread
 
 struct Fp8Params {
   int M, N, K;
@@ -77,8 +79,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
   auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
-  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + NBUF + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * NBUF);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -91,11 +93,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { tc::mbar_init(full_bar(s), 1); tc::mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { tc::mbar_init(tfull_bar(b), 1); tc::mbar_init(tempty_bar(b), 128); }
+    for (int b = 0; b < NBUF; ++b) { tc::mbar_init(tfull_bar(b), 1); tc::mbar_init(tempty_bar(b), 256); }
     *abort_flag = 0;
     tc::mbar_fence_init();
   }
-  if (warp == 1) tc::tmem_alloc(tc::smem_u32(tmem_slot), 2 * BN);
+  if (warp == 1) tc::tmem_alloc(tc::smem_u32(tmem_slot), NBUF * BN);
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
@@ -128,8 +130,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int buf = it & 1;
-          const uint32_t bph = (it >> 1) & 1;
+          const int buf = it % NBUF;
+          const uint32_t bph = (it / NBUF) & 1;
           if (!tc::mbar_wait(tempty_bar(buf), bph ^ 1, abort_flag, p.err, tc::SITE_TMEM_EMPTY)) { ok = false; break; }
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -148,7 +150,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       }
     }
   } else {
+    // warps 2..9: TMEM lane group = warp mod 4 (hardware rule); warps 2-5 own columns [0, 64) of the
+    // tile, warps 6-9 columns [64, 128), so each thread promotes 64 accumulator columns per k-block
     const int lane_grp = warp & 3;
+    const int col0 = warp >= 6 ? CPT : 0;
     const int trow = lane_grp * 32 + lane;
     uint32_t it = 0;
     bool ok = true;
@@ -156,40 +161,57 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       const int m_idx = tile % num_m, n_idx = tile / num_m;
       const int row = m_idx * BM + trow;
       const int row_c = row < p.M ? row : p.M - 1;
-      float acc[BN];
+      float acc[CPT];
 #pragma unroll
-      for (int i = 0; i < BN; ++i) acc[i] = 0.f;
+      for (int i = 0; i < CPT; ++i) acc[i] = 0.f;
       const float* sb_row = p.sb + (long)((grouped ? p.block_expert[m_idx] * p.sb_rows : 0) + n_idx) * p.sb_ld;
-      float sa_next = p.sa_t[row_c];
-      float sb_next = sb_row[0];
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        const float scale = sa_next * sb_next;
-        if (kb + 1 < num_kb) {
-          sa_next = p.sa_t[(long)(kb + 1) * p.sa_ld + row_c];
-          sb_next = sb_row[kb + 1];
-        }
-        const int buf = it & 1;
-        const uint32_t bph = (it >> 1) & 1;
-        if (!tc::mbar_wait(tfull_bar(buf), bph, abort_flag, p.err, tc::SITE_TMEM_FULL)) { ok = false; break; }
-        tc::fence_after_sync();
-        const uint32_t t_row = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + buf * BN;
+      // scales are fetched a group of 8 k-blocks ahead: a load issued one k-block ahead would sit on the
+      // critical path (global-load latency exceeds the time of one k-block)
+      constexpr int G = 8;
+      float sa_cur[G], sb_cur[G], sa_nxt[G], sb_nxt[G];
 #pragma unroll
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t v[32];
-          tc::tmem_ld32(t_row + c * 32, v);
-          tc::tmem_ld_wait();
+      for (int j = 0; j < G; ++j) {
+        sa_cur[j] = j < num_kb ? p.sa_t[(long)j * p.sa_ld + row_c] : 0.f;
+        sb_cur[j] = j < num_kb ? sb_row[j] : 0.f;
+      }
+      for (int kb0 = 0; kb0 < num_kb && ok; kb0 += G) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) acc[c * 32 + e] = fmaf(__uint_as_float(v[e]), scale, acc[c * 32 + e]);
+        for (int j = 0; j < G; ++j) {
+          const int kn = kb0 + G + j;
+          sa_nxt[j] = kn < num_kb ? p.sa_t[(long)kn * p.sa_ld + row_c] : 0.f;
+          sb_nxt[j] = kn < num_kb ? sb_row[kn] : 0.f;
         }
-        tc::fence_before_sync();
-        tc::mbar_arrive(tempty_bar(buf));
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+          if (kb0 + j < num_kb && ok) {
+            const float scale = sa_cur[j] * sb_cur[j];
+            const int buf = it % NBUF;
+            const uint32_t bph = (it / NBUF) & 1;
+            if (!tc::mbar_wait(tfull_bar(buf), bph, abort_flag, p.err, tc::SITE_TMEM_FULL)) { ok = false; }
+            else {
+              tc::fence_after_sync();
+              const uint32_t t_row = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + buf * BN + col0;
+              uint32_t v[CPT];
+              tc::tmem_ld32(t_row, v);            // both loads in flight before the single wait
+              tc::tmem_ld32(t_row + 32, v + 32);
+              tc::tmem_ld_wait();
+              tc::fence_before_sync();
+              tc::mbar_arrive(tempty_bar(buf));   // values are in registers: the buffer can be overwritten
+#pragma unroll
+              for (int e = 0; e < CPT; ++e) acc[e] = fmaf(__uint_as_float(v[e]), scale, acc[e]);
+              ++it;
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < G; ++j) { sa_cur[j] = sa_nxt[j]; sb_cur[j] = sb_nxt[j]; }
       }
       if (!ok) break;
       if (row < p.M) {
-        OutT* crow = reinterpret_cast<OutT*>(p.C) + (long)row * p.ldc + n_idx * BN;
+        OutT* crow = reinterpret_cast<OutT*>(p.C) + (long)row * p.ldc + n_idx * BN + col0;
 #pragma unroll
-        for (int g = 0; g < BN / 8; ++g) {
-          if (n_idx * BN + g * 8 + 8 <= p.N) *reinterpret_cast<uint4*>(crow + g * 8) = pack8<OutT>(acc + g * 8);
+        for (int g = 0; g < CPT / 8; ++g) {
+          if (n_idx * BN + col0 + g * 8 + 8 <= p.N) *reinterpret_cast<uint4*>(crow + g * 8) = pack8<OutT>(acc + g * 8);
         }
       }
     }
@@ -204,7 +226,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   if (warp == 1) {
     __syncwarp();
     tc::fence_after_sync();
-    tc::tmem_dealloc(tmem_base, 2 * BN);
+    tc::tmem_dealloc(tmem_base, NBUF * BN);
   }
 }
 

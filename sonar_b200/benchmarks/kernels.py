@@ -92,6 +92,68 @@ def bench_gemm_fp8(cu, m, n, k, iters, warm, flush):
     return t
 
 
+def bench_gemm_tp_scatter(cu, m, n, k, tp, iters, warm, flush):
+    """Row-parallel GEMM with the reduce-scatter push epilogue, the peers emulated on one GPU: the `tp`
+    destination buffers and flag words are local allocations, so the kernel runs its real code path
+    (tile → owner rank → row stores + completion flags) with device-local stores instead of NVLink ones.
+    Nothing waits on another launch."""
+    hbm, tf, tag = peaks()
+    shard = m // tp
+    a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+    bufs = [torch.zeros(shard, n, device="cuda", dtype=torch.bfloat16) for _ in range(tp)]
+    flags = torch.zeros(tp, dtype=torch.int32, device="cuda")
+    dst = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device="cuda")
+    fptr = torch.tensor([flags.data_ptr() + 4 * i for i in range(tp)], dtype=torch.int64, device="cuda")
+    done = torch.zeros(tp, dtype=torch.int32, device="cuda")
+    seq = [0]
+
+    def run():
+        seq[0] += 1
+        cu.gemm_tp(a, w, None, tp=tp, shard_rows=shard, seq=seq[0], rank=0, dst_ptrs=dst, local_done=done,
+                   flag_ptrs=fptr, n_out=n, ldc=n, err=cu.error_word(a.device))
+    t = timeit(run, iters, warm, flush)
+    torch.cuda.synchronize()
+    cu.check_device_errors()
+    want = (a.float() @ w.float().t())
+    got = torch.cat(bufs, 0).float()
+    rel = float((got - want).norm() / want.norm())
+    flops = 2.0 * m * n * k
+    print(f"gemm_tp scatter (tp={tp} emulated) M={m} N={n} K={k}: {t:.4f} ms, {flops / t / 1e9:.0f} TFLOP/s, "
+          f"{flops / (tf * 1e12) * 1e3 / t:.2f} {tag} roofline; flags {flags.tolist()}, rel err {rel:.2e}", flush=True)
+    return t
+
+
+def bench_moe(cu, t_tokens, e, k, h, inter, iters, warm, flush, fp8=False):
+    """Routed-expert FFN: routing → align → gather → grouped GEMM → SiLU → grouped GEMM → combine."""
+    from sonar_b200.ops import torch_ref as ref
+    hbm, tf, tag = peaks()
+    x = torch.randn(t_tokens, h, device="cuda", dtype=torch.bfloat16)
+    w13 = torch.randn(e, 2 * inter, h, device="cuda", dtype=torch.bfloat16) * 0.05
+    w2 = torch.randn(e, h, inter, device="cuda", dtype=torch.bfloat16) * 0.05
+    logits = torch.randn(t_tokens, e, device="cuda")
+    s13 = s2 = None
+    if fp8:
+        q13, s13, q2, s2 = [], [], [], []
+        for i in range(e):
+            a, b = ref.block_quant_fp8_weight(w13[i], 128)
+            c, d = ref.block_quant_fp8_weight(w2[i], 128)
+            q13.append(a); s13.append(b); q2.append(c); s2.append(d)
+        w13, s13, w2, s2 = torch.stack(q13), torch.stack(s13), torch.stack(q2), torch.stack(s2)
+
+    def run():
+        tw, ids = cu.topk_softmax(logits, k, True)
+        return cu.fused_experts(x, w13, w2, tw, ids, None, None, s13, s2)
+    t = timeit(run, iters, warm, flush)
+    cu.check_device_errors()
+    flops = 2.0 * t_tokens * k * 3 * inter * h
+    wbytes = (w13.numel() * w13.element_size() + w2.numel() * w2.element_size())
+    print(f"moe{' fp8' if fp8 else ''} T={t_tokens} E={e} top{k} H={h} I={inter}: {t:.4f} ms, {flops / t / 1e9:.0f} TFLOP/s, "
+          f"expert weights {wbytes / t / 1e6:.0f} GB/s "
+          f"({max(flops / (tf * 1e12), wbytes / (hbm * 1e9)) * 1e3 / t:.2f} {tag} roofline)", flush=True)
+    return t
+
+
 def bench_attn_decode(cu, seqs, ctx, hq, hk, d, iters, warm, flush):
     hbm, _, tag = peaks()
     bs = 16
@@ -159,12 +221,16 @@ def bench_elementwise(cu, iters, warm, flush):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm-fp8", "attn-decode", "attn-prefill", "elementwise", "sweep"])
+    ap.add_argument("what", choices=["gemm", "gemm-fp8", "gemm-tp", "moe", "attn-decode", "attn-prefill", "elementwise", "sweep"])
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--pair", action="store_true", help="whole waves on the two-SM (cta_group::2) kernel")
+    ap.add_argument("--tp", type=int, default=4, help="gemm-tp: emulated ranks")
+    ap.add_argument("--experts", type=int, default=128, help="moe: experts (tokens = --m, hidden = --k, expert FFN = --n)")
+    ap.add_argument("--topk", type=int, default=8)
+    ap.add_argument("--fp8", action="store_true", help="moe: block-scaled fp8 expert weights")
     ap.add_argument("--seqs", type=int, default=256)
     ap.add_argument("--ctx", type=int, default=1152)
     ap.add_argument("--q", type=int, default=1024)
@@ -182,6 +248,10 @@ def main() -> None:
         cu.set_gemm_pair(True)
     if a.what == "gemm":
         bench_gemm(cu, a.m, a.n, a.k, a.iters, a.warmup, flush, not a.no_compare, a.bn)
+    elif a.what == "gemm-tp":
+        bench_gemm_tp_scatter(cu, a.m, a.n, a.k, a.tp, a.iters, a.warmup, flush)
+    elif a.what == "moe":
+        bench_moe(cu, a.m, a.experts, a.topk, a.k, a.n, a.iters, a.warmup, flush, a.fp8)
     elif a.what == "gemm-fp8":
         bench_gemm_fp8(cu, a.m, a.n, a.k, a.iters, a.warmup, flush)
     elif a.what == "attn-decode":

@@ -64,6 +64,7 @@ namespace {
 
 constexpr int BM = 128, BK = 64;
 constexpr int NUM_THREADS = 192;
+constexpr int MAX_TP = 8;      // ranks a scatter epilogue can address
 
 struct GemmParams {
   int M, N, K;
@@ -305,6 +306,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     int wave = 0;
     long g = sk_begin;
     Seg sg;
+    int pend[MAX_TP];
+#pragma unroll
+    for (int q = 0; q < MAX_TP; ++q) pend[q] = 0;
     for (; ok && next_seg(wave, g, sg); ++seg) {
       const int tile = sg.tile;
       const int m_idx = grouped ? tile / num_n : (tile % num_m + p.m_rot) % num_m;
@@ -426,22 +430,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           if (prev + 1 == 8 * S) *cnt = 0;
         }
       }
-      if (p.dst_ptrs != nullptr) {
-        // publish: every lane fences its stores; each warp adds the number of 32-column chunks it stored
-        // to the counter of every destination the tile touches; the arrival completing a destination's
-        // share (4 warps × chunks per tile × its tiles) sends the flag
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0 && chunks_stored > 0) {
-          const int r_lo = m_idx * BM, r_hi = min(p.M, r_lo + BM) - 1;
-          for (int d = r_lo / p.shard_rows; d <= r_hi / p.shard_rows; ++d) {
+      if (p.dst_ptrs != nullptr && chunks_stored > 0) {
+        // remember how many 32-column chunks this warp stored for every destination the tile touches;
+        // they are fenced and published once, after the CTA's last tile (a system-scope fence per tile
+        // stalled the epilogue for longer than a short mainloop lasts)
+        const int r_lo = m_idx * BM, r_hi = min(p.M, r_lo + BM) - 1;
+        for (int d = r_lo / p.shard_rows; d <= r_hi / p.shard_rows; ++d) {
+#pragma unroll
+          for (int q = 0; q < MAX_TP; ++q) if (q == d) pend[q] += chunks_stored;   // static indexing keeps pend in registers
+        }
+      }
+    }
+    if (p.dst_ptrs != nullptr) {
+      // publish: the warp barrier orders every lane's row stores before lane 0's release-atomic (which
+      // drains the warp's outstanding stores, remote ones included); each warp adds its chunk counts to
+      // the counter of every destination; the arrival completing a destination's share (4 warps ×
+      // chunks per tile × its tiles) sends the flag with a system-scope release, which is cumulative
+      // over the other warps' stores it learned of through the counter
+      __syncwarp();
+      if (lane == 0) {
+#pragma unroll
+        for (int d = 0; d < MAX_TP; ++d) {
+          if (d < p.tp && pend[d] > 0) {
             const int d_lo = d * p.shard_rows, d_hi = min(p.M, d_lo + p.shard_rows) - 1;
             const int expected = 4 * (BN / 32) * num_n * (d_hi / BM - d_lo / BM + 1);
             int prev;
-            asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(prev) : "l"(p.local_done + d), "r"(chunks_stored) : "memory");
-            if (prev + chunks_stored == expected) {
+            asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(prev) : "l"(p.local_done + d), "r"(pend[d]) : "memory");
+            if (prev + pend[d] == expected) {
               p.local_done[d] = 0;
-              __threadfence_system();
               asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.flag_ptrs[d]), "r"(seq_now) : "memory");
             }
           }
@@ -668,7 +684,7 @@ SONAR_API int sonar_gemm_tp(const void* A, const void* B, void* C, int M, int N,
                             float* ws, int* ws_flags, int ws_ctas, cudaStream_t s) {
   if (M <= 0 || N <= 0 || K <= 0) return SONAR_BAD_ARG;
   if (K % 8 || lda % 8 || ldb % 8 || N % 8 || ldc % 8) return SONAR_BAD_ARG;
-  if (tp < 1 || shard_rows <= 0 || (long)tp * shard_rows < M) return SONAR_BAD_ARG;
+  if (tp < 1 || tp > MAX_TP || shard_rows <= 0 || (long)tp * shard_rows < M) return SONAR_BAD_ARG;
   if (dst_ptrs != nullptr && (!local_done || !flag_ptrs)) return SONAR_BAD_ARG;
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.err = err;

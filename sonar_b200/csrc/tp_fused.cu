@@ -126,9 +126,13 @@ __global__ void __launch_bounds__(1024) tp_add_norm_kernel(const AddNormParams p
       }
     }
   }
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
+    // ordering: the block barrier orders every thread's stores before this thread's release-atomic
+    // (gpu scope: it completes only after the block's outstanding stores, remote ones included, are
+    // acknowledged); the arrival that completes the count publishes with a system-scope release store,
+    // which is cumulative over everything it learned of through the counter.  A system-scope fence per
+    // block measured ≈ 6 µs on this machine and is not needed for that chain.
     const int b = (int)(grow >> 7);
     const long lo = max((long)p.rank * p.shard_rows, (long)b << 7);
     const long hi = min((long)p.rank * p.shard_rows + p.rows, ((long)b + 1) << 7);
@@ -137,7 +141,6 @@ __global__ void __launch_bounds__(1024) tp_add_norm_kernel(const AddNormParams p
     asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(prev) : "l"(p.blk_done + b) : "memory");
     if (prev + 1 == expected) {
       p.blk_done[b] = 0;
-      __threadfence_system();
       for (int q = 0; q < p.tp; ++q) st_release_sys(p.gather_flag_ptrs[q] + b * p.tp + p.rank, p.send_seq + base);
     }
   }
@@ -181,15 +184,18 @@ __global__ void __launch_bounds__(512) all_reduce_kernel(const AllReduceParams p
       reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.slot_ptrs[dst]) + (long)p.rank * p.n)[v] = x;
     }
   }
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
     ok_s = 1;
+    // ordering: the block barrier orders every thread's stores before this thread's release-atomic
+    // (gpu scope: it completes only after the block's outstanding stores, remote ones included, are
+    // acknowledged); the arrival that completes the count publishes with a system-scope release store,
+    // which is cumulative over everything it learned of through the counter.  A system-scope fence per
+    // block measured ≈ 6 µs on this machine and is not needed for that chain.
     int prev;
     asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(prev) : "l"(p.arrive) : "memory");
     if (prev + 1 == (int)gridDim.x) {
       *p.arrive = 0;
-      __threadfence_system();
       for (int q = 0; q < p.tp; ++q) st_release_sys(p.flag_ptrs[q] + p.rank, p.seq);
     }
   }

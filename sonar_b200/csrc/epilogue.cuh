@@ -1,0 +1,48 @@
+// Scatter epilogue helper shared by the GEMM kernels: an epilogue warp owns 32 accumulator rows (one per
+// lane) and would naturally store 64 bytes per lane per 32-column chunk — 32 disjoint 64-byte pieces per
+// instruction.  That is harmless into local memory but throttles NVLink (measured ≈ 120 GB/s into peers'
+// buffers).  Here the warp first parks a 32-row × 128-column half tile (16-bit) in an 8 KB shared-memory
+// patch, XOR-swizzled by 16-byte chunk so both the row-wise writes and the transposed reads are
+// conflict-free, and then stores it row by row: 16 lanes cover 256 contiguous bytes of one row, two rows
+// per instruction.
+#pragma once
+#include "tcgen05.cuh"
+
+namespace sonar {
+
+constexpr int STAGE_WARP_BYTES = 32 * 256;    // 32 rows × 128 columns × 2 bytes
+
+// Park one 32-column chunk (cc = 0..3 within the half tile) of this lane's row.
+template <typename OutT>
+__device__ __forceinline__ void stage_chunk(uint8_t* stage, int lane, int cc, const uint32_t* v) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[j * 8 + i]);
+    const int phys = (cc * 4 + j) ^ (lane & 15);
+    *reinterpret_cast<uint4*>(stage + lane * 256 + phys * 16) = pack8<OutT>(f);
+  }
+}
+
+// Store the parked half tile.  row0: global row of the warp's first row; col0: global column of the half
+// tile's first column.  Row r goes to dst_ptrs[r / shard_rows] at local row r - owner·shard_rows.
+template <typename OutT>
+__device__ __forceinline__ void store_staged_rows(const uint8_t* stage, int lane, long row0, int col0, int M, int N,
+                                                  void* const* dst_ptrs, int shard_rows, long ldc) {
+  const int half = lane >> 4, lc = lane & 15;
+  const int col = col0 + lc * 8;
+#pragma unroll 4
+  for (int i = 0; i < 16; ++i) {
+    const int r = 2 * i + half;
+    const long grow = row0 + r;
+    const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 256 + ((lc ^ (r & 15)) * 16));
+    if (grow < M && col + 8 <= N) {
+      const int d = (int)(grow / shard_rows);
+      OutT* dst = reinterpret_cast<OutT*>(dst_ptrs[d]) + (grow - (long)d * shard_rows) * ldc + col;
+      *reinterpret_cast<uint4*>(dst) = val;
+    }
+  }
+}
+
+}  // namespace sonar

@@ -26,7 +26,7 @@
 #include <mutex>
 #include <unordered_map>
 
-#include "tcgen05.cuh"
+#include "epilogue.cuh"
 
 namespace sonar {
 
@@ -98,7 +98,7 @@ template <int BN> struct Cfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + 4 * STAGE_WARP_BYTES /*scatter staging*/;
 };
 
 template <typename OutT>
@@ -330,7 +330,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         }
       }
       int chunks_stored = BN / 32;
-      if (!sg.split) {
+      if (sizeof(OutT) == 2 && !sg.split && p.dst_ptrs != nullptr && BN >= 128) {
+        // scatter of a whole tile: park 128-column halves of the warp's 32 rows in shared memory and store
+        // 256-byte row pieces (64-byte pieces per lane throttle NVLink)
+        uint8_t* stage = smem_al + C::STAGES * C::STAGE_BYTES + 256 + (warp - 2) * STAGE_WARP_BYTES;
+#pragma unroll 1
+        for (int h = 0; h < BN / 128; ++h) {
+#pragma unroll 1
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t v[32];
+            tc::tmem_ld32(t_row + (h * 4 + cc) * 32, v);
+            tc::tmem_ld_wait();
+            if constexpr (sizeof(OutT) == 2) stage_chunk<OutT>(stage, lane, cc, v);
+          }
+          __syncwarp();
+          if constexpr (sizeof(OutT) == 2)
+            store_staged_rows<OutT>(stage, lane, (long)m_idx * BM + lane_grp * 32, n0 + h * 128, p.M, p.N, p.dst_ptrs,
+                                    p.shard_rows, p.ldc);
+          __syncwarp();
+        }
+        tc::fence_before_sync();
+        tc::mbar_arrive(tempty_bar(buf));
+      } else if (!sg.split) {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t v[32];
@@ -627,6 +648,10 @@ bool g_pair_enabled = false;
 using namespace sonar;
 
 extern "C" int sonar_gemm_pair_resident();
+extern "C" int sonar_gemm_pair_tp(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb,
+                                  long ldc, const int* gather_flags, int tp, int shard_rows, int seq,
+                                  const int* seq_base, int m_rot2, void* const* dst_ptrs, int* local_done,
+                                  int* const* flag_ptrs, int num_tiles, int pairs, int* err, cudaStream_t s);
 extern "C" int sonar_gemm_pair(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long lda,
                                long ldb, long ldc, int dtype, int num_tiles, int pairs, int* err, cudaStream_t s);
 
@@ -692,6 +717,21 @@ SONAR_API int sonar_gemm_tp(const void* A, const void* B, void* C, int M, int N,
   p.m_rot = gather_flags ? (int)(((long)rank * shard_rows) / BM) : 0;
   p.dst_ptrs = dst_ptrs; p.local_done = local_done; p.flag_ptrs = flag_ptrs;
   p.ws = ws; p.ws_flags = ws_flags; p.ws_ctas = ws_ctas;
+  const int num_m1 = (M + BM - 1) / BM;
+  if (g_pair_enabled && !force_bn && M >= 512 && N >= 512 && num_m1 % 2 == 0 && p.m_rot % 2 == 0 &&
+      (N % 256 == 0 || N > 2048)) {
+    // whole waves on CTA pairs, the partial last wave on the one-CTA kernel (same tile order, same counters)
+    const int pairs = sonar_gemm_pair_resident();
+    const int tiles2 = (num_m1 / 2) * ((N + 255) / 256);
+    const int n2 = pairs > 0 ? (tiles2 / pairs) * pairs : 0;
+    if (n2 > 0) {
+      int rc = sonar_gemm_pair_tp(A, B, C, M, N, K, lda, ldb, ldc, gather_flags, tp, shard_rows, seq, seq_base,
+                                  p.m_rot / 2, dst_ptrs, local_done, flag_ptrs, n2, pairs, err, s);
+      if (rc != SONAR_OK || n2 == tiles2) return rc;
+      p.tile_begin = 2 * n2;
+      return launch_bn<__nv_bfloat16, 1>(256, A, B, p, lda, ldb, s);
+    }
+  }
   const int bn = force_bn ? force_bn : pick_bn(M, N, K, ws != nullptr);
   return launch_bn<__nv_bfloat16, 1>(bn, A, B, p, lda, ldb, s);
 }

@@ -15,7 +15,7 @@
 //
 // No operand is loaded with cluster multicast.  Every wait is bounded (2 s) and funnels to the
 // final cluster barrier, so a fault in the protocol surfaces as an error word, not a hang.
-#include "tcgen05.cuh"
+#include "epilogue.cuh"
 
 namespace sonar {
 int cached_tmap_public(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
@@ -26,9 +26,9 @@ constexpr int BM = 128;                 // rows per CTA (256 per pair)
 constexpr int BN = 256;                 // tile columns
 constexpr int BNH = BN / 2;             // B rows staged per CTA
 constexpr int BK = 64;
-constexpr int STAGES = 7;
+constexpr int STAGES = 6;              // 192 KB ring + 32 KB epilogue staging
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNH * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;   // 32 KB
-constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256 + 4 * STAGE_WARP_BYTES;
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 2 * BN;       // two accumulator buffers
 
@@ -39,7 +39,15 @@ struct PairParams {
   int* err;
   int num_tiles;      // pair tiles to process (prefix of the m-fastest order over 256×256 tiles)
   int num_m2;         // 256-row blocks
+  // tensor-parallel hooks (same protocol as the one-CTA kernel)
+  const int* gather_flags;  // [num_128_row_blocks * tp] arrival flags of the all-gathered A rows, or null
+  int tp, shard_rows, seq, m_rot2;   // m_rot2: rotation of the 256-row block order (each rank starts on its own rows)
+  const int* seq_base;
+  void* const* dst_ptrs;    // [tp] partial-buffer bases (peer mappings): scatter epilogue, or null
+  int* local_done;          // [tp] chunk counters shared with the one-CTA kernel of the same GEMM
+  int* const* flag_ptrs;    // [tp] remote flag words
 };
+constexpr int MAX_TP = 8;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -119,6 +127,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const bool leader = rank == 0;
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   const int num_kb = (p.K + BK - 1) / BK;
+  const int seq_now = p.seq + (p.seq_base ? *p.seq_base : 0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { tc::mbar_init(full_bar(s), 1); tc::mbar_init(empty_bar(s), 1); }
@@ -148,9 +157,37 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t it = 0;
       bool ok = true;
       for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs) {
-        const int m2 = tile % p.num_m2, n_idx = tile / p.num_m2;
+        const int m2 = (tile % p.num_m2 + p.m_rot2) % p.num_m2, n_idx = tile / p.num_m2;
         const int a_row = m2 * 2 * BM + (int)rank * BM;
         const int b_row = n_idx * BN + (int)rank * BNH;
+        if (p.gather_flags != nullptr && a_row < p.M) {
+          // bounded wait until every source rank of this CTA's 128 rows has published this launch's number
+          const int blk = a_row / BM, r_hi = min(p.M, a_row + BM) - 1;
+          for (int src = a_row / p.shard_rows; src <= r_hi / p.shard_rows && ok; ++src) {
+            const int* flag = p.gather_flags + blk * p.tp + src;
+            auto arrived = [&]() {
+              int v;
+              asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+              return (v - seq_now) >= 0;
+            };
+            if (arrived()) continue;
+            const uint64_t t0 = globaltimer_ns();
+            uint32_t spins = 0;
+            while (!arrived()) {
+              if ((++spins & 63u) == 0) {
+                if (*abort_flag) { ok = false; break; }
+                if (globaltimer_ns() - t0 > tc::WAIT_LIMIT_NS) {
+                  *abort_flag = 1;
+                  if (p.err) atomicCAS(p.err, 0, tc::SITE_FLAG | (blockIdx.x << 8));
+                  ok = false;
+                  break;
+                }
+              }
+            }
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");   // the peers' row stores precede the TMA reads below
+        }
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -196,26 +233,90 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const int lane_grp = warp & 3;
     const int trow = lane_grp * 32 + lane;
     uint32_t seg = 0;
+    int pend[MAX_TP];
+#pragma unroll
+    for (int q = 0; q < MAX_TP; ++q) pend[q] = 0;
+    const int num_n = (p.N + BN - 1) / BN;
     for (int tile = pair; tile < p.num_tiles; tile += num_pairs, ++seg) {
-      const int m2 = tile % p.num_m2, n_idx = tile / p.num_m2;
-      const int row = m2 * 2 * BM + (int)rank * BM + trow;
+      const int m2 = (tile % p.num_m2 + p.m_rot2) % p.num_m2, n_idx = tile / p.num_m2;
+      const int row0 = m2 * 2 * BM + (int)rank * BM;
+      const int row = row0 + trow;
       const int buf = seg & 1;
       const uint32_t bph = (seg >> 1) & 1;
       if (!tc::mbar_wait(tfull_bar(buf), bph, abort_flag, p.err, tc::SITE_TMEM_FULL)) break;
       tc::fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + buf * BN;
-      OutT* crow = reinterpret_cast<OutT*>(p.C) + (long)row * p.ldc + n_idx * BN;
+      OutT* crow = nullptr;
+      if (row < p.M) {
+        if (p.dst_ptrs != nullptr) {
+          const int d = row / p.shard_rows;     // owner of this row: its partial buffer may be on another GPU
+          crow = reinterpret_cast<OutT*>(p.dst_ptrs[d]) + (long)(row - d * p.shard_rows) * p.ldc + n_idx * BN;
+        } else {
+          crow = reinterpret_cast<OutT*>(p.C) + (long)row * p.ldc + n_idx * BN;
+        }
+      }
       const OutT* bias = p.bias ? reinterpret_cast<const OutT*>(p.bias) + n_idx * BN : nullptr;
+      int chunks = 0;
+      if (p.dst_ptrs != nullptr) {
+        // scatter: park each 128-column half of the warp's 32 rows in shared memory, then store whole
+        // 256-byte row pieces (the destination may be another GPU)
+        uint8_t* stage = smem_al + STAGES * STAGE_BYTES + 256 + (warp - 2) * STAGE_WARP_BYTES;
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll 1
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t v[32];
+            tc::tmem_ld32(t_row + (h * 4 + cc) * 32, v);
+            tc::tmem_ld_wait();
+            stage_chunk<OutT>(stage, lane, cc, v);
+            ++chunks;
+          }
+          __syncwarp();
+          store_staged_rows<OutT>(stage, lane, (long)row0 + lane_grp * 32, n_idx * BN + h * 128, p.M, p.N, p.dst_ptrs,
+                                  p.shard_rows, p.ldc);
+          __syncwarp();
+        }
+      } else {
 #pragma unroll 2
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tc::tmem_ld32(t_row + c * 32, v);
-        tc::tmem_ld_wait();
-        const int ok_cols = p.N - (n_idx * BN + c * 32);
-        if (row < p.M && ok_cols > 0) store32<OutT>(crow + c * 32, v, bias ? bias + c * 32 : nullptr, ok_cols);
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tc::tmem_ld32(t_row + c * 32, v);
+          tc::tmem_ld_wait();
+          const int ok_cols = p.N - (n_idx * BN + c * 32);
+          if (crow != nullptr && ok_cols > 0) store32<OutT>(crow + c * 32, v, bias ? bias + c * 32 : nullptr, ok_cols);
+          ++chunks;
+        }
       }
       tc::fence_before_sync();
       mbar_arrive_cluster(map_to_cta(tempty_bar(buf), 0));     // the leader's MMA warp may reuse this buffer
+      if (p.dst_ptrs != nullptr && row0 < p.M) {
+        const int r_hi = min(p.M, row0 + BM) - 1;
+        for (int d = row0 / p.shard_rows; d <= r_hi / p.shard_rows; ++d) {
+#pragma unroll
+          for (int q = 0; q < MAX_TP; ++q) if (q == d) pend[q] += chunks;
+        }
+      }
+    }
+    if (p.dst_ptrs != nullptr) {
+      // publish once per CTA: the warp barrier orders the lanes' row stores before lane 0's release-atomic;
+      // the arrival that completes a destination's share sends its flag with a system-scope release store
+      // (counter units and totals are those of the one-CTA kernel, which may finish the same GEMM)
+      __syncwarp();
+      if (lane == 0) {
+#pragma unroll
+        for (int d = 0; d < MAX_TP; ++d) {
+          if (d < p.tp && pend[d] > 0) {
+            const int d_lo = d * p.shard_rows, d_hi = min(p.M, d_lo + p.shard_rows) - 1;
+            const int expected = 4 * (BN / 32) * num_n * (d_hi / BM - d_lo / BM + 1);
+            int prev;
+            asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(prev) : "l"(p.local_done + d), "r"(pend[d]) : "memory");
+            if (prev + pend[d] == expected) {
+              p.local_done[d] = 0;
+              asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.flag_ptrs[d]), "r"(seq_now) : "memory");
+            }
+          }
+        }
+      }
     }
   }
   tc::fence_before_sync();
@@ -297,9 +398,35 @@ SONAR_API int sonar_gemm_pair(const void* A, const void* B, void* C, const void*
   if (rc != SONAR_OK) return rc;
   rc = cached_tmap_public(&tb, B, N, K, ldb, BNH, 2);
   if (rc != SONAR_OK) return rc;
-  PairParams p{M, N, K, C, ldc, bias, err, num_tiles, num_m2};
+  PairParams p{};
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.bias = bias; p.err = err; p.num_tiles = num_tiles;
+  p.num_m2 = num_m2; p.tp = 1; p.shard_rows = M;
   if (pairs > num_tiles) pairs = num_tiles;
   if (dtype == SONAR_BF16) return launch_pair<__nv_bfloat16, 1>(ta, tb, p, pairs, s);
   if (dtype == SONAR_F16) return launch_pair<__half, 0>(ta, tb, p, pairs, s);
   return SONAR_BAD_ARG;
+}
+
+// Tensor-parallel form (bf16): gather_flags → each CTA waits for its 128 all-gathered A rows; dst_ptrs →
+// output rows are stored into their owners' partial buffers and completion flags are published.  The chunk
+// counters (local_done) are shared with the one-CTA kernel that finishes the partial last wave.
+SONAR_API int sonar_gemm_pair_tp(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb,
+                                 long ldc, const int* gather_flags, int tp, int shard_rows, int seq,
+                                 const int* seq_base, int m_rot2, void* const* dst_ptrs, int* local_done,
+                                 int* const* flag_ptrs, int num_tiles, int pairs, int* err, cudaStream_t s) {
+  if (M <= 0 || N <= 0 || K <= 0 || num_tiles <= 0 || pairs <= 0 || tp < 1 || tp > MAX_TP) return SONAR_BAD_ARG;
+  if (K % 8 || lda % 8 || ldb % 8 || N % 8 || ldc % 8) return SONAR_BAD_ARG;
+  const int num_m2 = (M + 2 * BM - 1) / (2 * BM), num_n = (N + BN - 1) / BN;
+  if (num_tiles > num_m2 * num_n) return SONAR_BAD_ARG;
+  CUtensorMap ta, tb;
+  int rc = cached_tmap_public(&ta, A, M, K, lda, BM, 2);
+  if (rc != SONAR_OK) return rc;
+  rc = cached_tmap_public(&tb, B, N, K, ldb, BNH, 2);
+  if (rc != SONAR_OK) return rc;
+  PairParams p{};
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.err = err; p.num_tiles = num_tiles; p.num_m2 = num_m2;
+  p.gather_flags = gather_flags; p.tp = tp; p.shard_rows = shard_rows; p.seq = seq; p.seq_base = seq_base;
+  p.m_rot2 = m_rot2; p.dst_ptrs = dst_ptrs; p.local_done = local_done; p.flag_ptrs = flag_ptrs;
+  if (pairs > num_tiles) pairs = num_tiles;
+  return launch_pair<__nv_bfloat16, 1>(ta, tb, p, pairs, s);
 }

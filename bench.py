@@ -53,6 +53,9 @@ def parse_args():
     ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end repeat (debugging)")
     ap.add_argument("--temperature", type=float, default=1.0)
+    ap.add_argument("--quantization", default=None, choices=[None, "fp8"],
+                    help="fp8: random-init weights quantised to e4m3 with 128x128 block scales")
+    ap.add_argument("--kv-cache-dtype", default="auto", choices=["auto", "fp8"])
     return ap.parse_args()
 
 
@@ -134,7 +137,8 @@ def main() -> None:
     max_len = args.input_len + args.output_len + 16
     llm = LLM(args.model, dtype="bfloat16", max_model_len=max_len, max_num_seqs=args.max_num_seqs,
               max_num_batched_tokens=args.max_num_batched_tokens, block_size=16, enable_prefix_caching=True,
-              skip_tokenizer_init=True, tensor_parallel_size=args.gpus, seed=0,
+              skip_tokenizer_init=True, tensor_parallel_size=args.gpus, seed=0, quantization=args.quantization,
+              kv_cache_dtype=args.kv_cache_dtype,
               distributed_executor_backend="external_launcher" if world > 1 else "uni")
     engine = llm.llm_engine
     vocab = engine.cfg.model.vocab_size
@@ -243,10 +247,11 @@ def main() -> None:
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps,
             "warmup": args.warmup, "ms_per_step": dev_ms / max(steps, 1), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": (value / BASELINE_PUBLISHED) if BASELINE_PUBLISHED else None,
-            "dtype": "bf16", "data": "synthetic (uniform-random token ids, random-init weights)",
+            "dtype": "fp8 (e4m3 block-scaled weights, bf16 activations)" if args.quantization == "fp8" else "bf16", "data": "synthetic (uniform-random token ids, random-init weights)",
             "impl": "sonar_b200",
             "config": {
-                "model": args.model, "num_requests": args.num_requests, "input_len": args.input_len,
+                "model": args.model, "tp_comm": os.environ.get("SONAR_TP_COMM", "auto"), "quantization": args.quantization, "kv_cache_dtype": args.kv_cache_dtype,
+                "num_requests": args.num_requests, "input_len": args.input_len,
                 "output_len": args.output_len, "max_num_seqs": args.max_num_seqs,
                 "max_num_batched_tokens": args.max_num_batched_tokens, "block_size": 16,
                 "global_batch": args.max_num_seqs, "seq_len": args.input_len + args.output_len,

@@ -37,8 +37,10 @@ environment_variables: dict[str, Callable[[], Any]] = {
     "SONAR_GEMM": _str("SONAR_GEMM", "tcgen05"),
     # tensor-parallel collectives: "fused" = sequence-parallel layout with GEMM+collective kernels,
     # "custom" = replicated layout, one-shot P2P all-reduce kernel for small tensors and NCCL above,
-    # "nccl" = torch.distributed only (the baseline arm).
-    "SONAR_TP_COMM": _str("SONAR_TP_COMM", "custom"),
+    # "nccl" = torch.distributed only (the baseline arm), "auto" = fused where the model's linear layers
+    # are 16-bit (the fused GEMMs are bf16) and no adapter or pipeline stage needs replicated rows,
+    # custom otherwise.
+    "SONAR_TP_COMM": _str("SONAR_TP_COMM", "auto"),
     "SONAR_CUDA_GRAPHS": _bool("SONAR_CUDA_GRAPHS", True),
     "SONAR_SYMM_HEAP_MB": _int("SONAR_SYMM_HEAP_MB", 512),
     # server

@@ -62,6 +62,10 @@ class Worker:
         from sonar_b200 import envs
         from sonar_b200.parallel import tp_ops
         mode = envs.SONAR_TP_COMM
+        if mode == "auto":
+            plain = (self.cfg.model.quantization is None and self.cfg.model.dtype == torch.bfloat16
+                     and not self.cfg.lora.enable_lora and self.cfg.parallel.pipeline_parallel_size == 1)
+            mode = "fused" if plain else "custom"
         ctx = None
         if (self.cfg.device == "cuda" and state.tp_world_size() > 1 and mode in ("fused", "custom")
                 and not self.cfg.parallel.disable_custom_all_reduce):

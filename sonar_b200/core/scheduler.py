@@ -178,6 +178,7 @@ class Scheduler:
         self.step_id = 0
         self.num_preempted_total = 0
         self._spec_drafts = self._spec_accepted = 0
+        self.num_sync_requests = 0
 
     # ------------------------------------------------------------------ API
     def add_request(self, core_req: EngineCoreRequest | Request) -> None:
@@ -196,6 +197,21 @@ class Scheduler:
         self.requests[req.request_id] = req
         self.waiting.add(req)
         req.record_event("queued")
+        if self._needs_sync(req):
+            self.num_sync_requests += 1
+
+    @staticmethod
+    def _needs_sync(req: Request) -> bool:
+        """Requests whose sampling reads tokens the host must already know (penalties, logprobs, grammars,
+        drafts) or that do not sample at all keep the engine in lock-step."""
+        sp = req.sampling_params
+        if sp is None:
+            return True
+        return bool(sp.needs_penalties or sp.needs_extended or sp.logprobs is not None or sp.prompt_logprobs is not None
+                    or sp.structured_outputs is not None or sp.min_tokens > 0 or sp._bad_words_token_ids)
+
+    def can_run_ahead(self) -> bool:
+        return self.cfg.async_scheduling and self.num_sync_requests == 0 and self.num_spec_tokens == 0
 
     def has_unfinished_requests(self) -> bool:
         return bool(self.running) or bool(self.waiting)
@@ -216,7 +232,10 @@ class Scheduler:
         return self.kv.reset_prefix_cache()
 
     # ------------------------------------------------------------- schedule
-    def schedule(self) -> SchedulerOutput:
+    def schedule(self, async_step: bool = False) -> SchedulerOutput:
+        """``async_step``: the caller will build the next step before this one's tokens are known; requests
+        that sample in this step get an output placeholder so that the next step can schedule the (still
+        unknown) token, and requests whose pending tokens already reach ``max_tokens`` are not scheduled."""
         cfg = self.cfg
         out = SchedulerOutput(step_id=self.step_id)
         self.step_id += 1
@@ -232,6 +251,10 @@ class Scheduler:
         while idx < len(self.running) and budget > 0:
             req = self.running[idx]
             num_new = req.num_tokens_with_spec + req.num_output_placeholders - req.num_computed_tokens
+            if req.num_output_placeholders and (
+                    req.num_output_tokens + req.num_output_placeholders >= req.max_tokens
+                    or req.num_tokens + req.num_output_placeholders >= self.max_model_len):
+                num_new = 0   # its last token is still in flight; it finishes when that step's output arrives
             if 0 < threshold < num_new:
                 num_new = threshold
             num_new = min(num_new, budget, self.max_model_len - 1 - req.num_computed_tokens)
@@ -325,6 +348,8 @@ class Scheduler:
         for rid, n in num_sched.items():
             req = self.requests[rid]
             req.num_computed_tokens += n
+            if async_step and req.num_computed_tokens >= req.num_tokens + req.num_output_placeholders:
+                req.num_output_placeholders += 1       # this step samples a token the host has not seen yet
             if req.grammar is not None and req.num_computed_tokens >= req.num_tokens:
                 gram.append(req)
         if gram:
@@ -342,6 +367,7 @@ class Scheduler:
         req.status = RequestStatus.PREEMPTED
         req.num_computed_tokens = 0
         req.spec_token_ids = []
+        req.num_output_placeholders = 0      # a token still in flight is dropped and generated again
         req.num_preemptions += 1
         req.record_event("preempted")
         self.num_preempted_total += 1
@@ -440,6 +466,8 @@ class Scheduler:
             self.finished_req_ids.add(req.request_id)
             self._known_to_runner.discard(req.request_id)
         del self.requests[req.request_id]
+        if self._needs_sync(req):
+            self.num_sync_requests -= 1
         req.record_event("finished")
 
     def make_stats(self, n_prompt: int = 0, n_gen: int = 0) -> SchedulerStats:

@@ -62,7 +62,15 @@ struct AddNormParams {
   int send_seq;
   const int* seq_base;      // device word added to wait_seq / send_seq
   int* err;
+  void* gather_mc;          // NVSwitch multicast address of the gather buffer (one store reaches every rank), or null
 };
+
+// one 16-byte store to the multicast address: the switch replicates it into every rank's buffer
+__device__ __forceinline__ void multimem_st16(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"l"(mc_addr), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+                 "f"(__uint_as_float(v.w)) : "memory");
+}
 
 template <typename T, int VPT>
 __global__ void __launch_bounds__(1024) tp_add_norm_kernel(const AddNormParams p) {
@@ -120,7 +128,9 @@ __global__ void __launch_bounds__(1024) tp_add_norm_kernel(const AddNormParams p
 #pragma unroll
       for (int j = 0; j < 8; ++j) vals[k][j] = vals[k][j] * inv * g[j];
       const uint4 packed = pack8<T>(vals[k]);
-      for (int q = 0; q < p.tp; ++q) {
+      if (p.gather_mc != nullptr) {
+        multimem_st16(reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.gather_mc) + grow * p.H) + v, packed);
+      } else for (int q = 0; q < p.tp; ++q) {
         const int dst = (p.rank + q) % p.tp;   // start with the local copy, spread peers
         reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.gather_ptrs[dst]) + grow * p.H)[v] = packed;
       }
@@ -230,10 +240,10 @@ SONAR_API int sonar_tp_add_norm(const void* src, long slot_stride, int n_src, co
                                 void* residual, int residual_in, const void* weight, float eps, int H, int rows,
                                 void* const* gather_ptrs, int tp, int rank, int shard_rows, int* blk_done,
                                 int* const* gather_flag_ptrs, int send_seq, const int* seq_base, int* err, int dtype,
-                                cudaStream_t s) {
+                                void* gather_mc, cudaStream_t s) {
   if (H % 8 || rows <= 0 || rows > shard_rows || n_src < 1 || n_src > 32) return SONAR_BAD_ARG;
   AddNormParams p{src, slot_stride, n_src, src_flags, wait_seq, residual, residual_in, weight, eps, H, rows,
-                  gather_ptrs, tp, rank, shard_rows, blk_done, gather_flag_ptrs, send_seq, seq_base, err};
+                  gather_ptrs, tp, rank, shard_rows, blk_done, gather_flag_ptrs, send_seq, seq_base, err, gather_mc};
   const int nvec = H / 8;
   int threads = nvec >= 1024 ? 1024 : ((nvec + 31) / 32) * 32;
   if (nvec > 256 && nvec <= 1024) threads = ((nvec / 2 + 31) / 32) * 32;

@@ -50,6 +50,9 @@ class EngineCore:
             logger.info("KV-cache events published on %s", self.kv_publisher.endpoint)
         self.paused = False
         self.sleeping = False
+        self.run_ahead_steps = 0
+        self.pending = None              # (scheduler output, deferred runner output) of the step in flight
+        self.run_ahead_ok = cfg.scheduler.async_scheduling and getattr(self.executor, "supports_defer", False)
         self.steps = 0
         self.host_time = {"schedule": 0.0, "execute": 0.0, "update": 0.0}
         logger.info("engine core ready in %.1fs (%d KV blocks of %d tokens)", time.time() - t0,
@@ -63,25 +66,62 @@ class EngineCore:
         self.scheduler.finish_requests(request_ids, RequestStatus.FINISHED_ABORTED)
 
     def has_unfinished_requests(self) -> bool:
-        return self.scheduler.has_unfinished_requests()
+        return self.scheduler.has_unfinished_requests() or self.pending is not None
 
     def step(self) -> EngineCoreOutputs:
-        if self.paused or self.sleeping or not self.scheduler.has_requests():
+        if self.paused or self.sleeping:
             return EngineCoreOutputs()
+        if not self.scheduler.has_requests():
+            return self._drain() if self.pending is not None else EngineCoreOutputs()
+        run_ahead = self.run_ahead_ok and self.scheduler.can_run_ahead()
+        if not run_ahead and self.pending is not None:
+            return self._drain()           # back to lock-step: finish the step in flight first
         t0 = time.perf_counter()
         with self.tracer.span("schedule"):
-            so = self.scheduler.schedule()
+            so = self.scheduler.schedule(async_step=run_ahead)
         t1 = time.perf_counter()
+        self.host_time["schedule"] += t1 - t0
+        if run_ahead:
+            # one step ahead: launch this step's GPU work, then fold in the previous step's tokens while
+            # it runs; the next call schedules on top of placeholders for the tokens still in flight
+            fut = None
+            if so.total_num_scheduled_tokens > 0 or so.finished_req_ids or so.preempted_req_ids:
+                with self.tracer.span("execute_model", tokens=so.total_num_scheduled_tokens):
+                    fut = self.executor.execute_model(so, defer=True)
+            t2 = time.perf_counter()
+            self.host_time["execute"] += t2 - t1
+            outs = self._drain()
+            if fut is not None:
+                self.pending = (so, fut)
+            self.steps += 1
+            self.run_ahead_steps += 1
+            return outs
         with self.tracer.span("execute_model", tokens=so.total_num_scheduled_tokens):
             ro = self.executor.execute_model(so)
         t2 = time.perf_counter()
         with self.tracer.span("update"):
             outs = self.scheduler.update_from_output(so, ro)
         t3 = time.perf_counter()
-        self.host_time["schedule"] += t1 - t0
         self.host_time["execute"] += t2 - t1
         self.host_time["update"] += t3 - t2
         self.steps += 1
+        if self.kv_publisher is not None:
+            self.kv_publisher.publish(self.scheduler.kv.take_events())
+        return outs
+
+    def _drain(self) -> EngineCoreOutputs:
+        """Wait for the step in flight (if any) and fold its tokens into the scheduler."""
+        if self.pending is None:
+            return EngineCoreOutputs()
+        so, fut = self.pending
+        self.pending = None
+        t0 = time.perf_counter()
+        ro = fut.result()
+        t1 = time.perf_counter()
+        with self.tracer.span("update"):
+            outs = self.scheduler.update_from_output(so, ro)
+        self.host_time["execute"] += t1 - t0
+        self.host_time["update"] += time.perf_counter() - t1
         if self.kv_publisher is not None:
             self.kv_publisher.publish(self.scheduler.kv.take_events())
         return outs

@@ -41,6 +41,9 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # are 16-bit (the fused GEMMs are bf16) and no adapter or pipeline stage needs replicated rows,
     # custom otherwise.
     "SONAR_TP_COMM": _str("SONAR_TP_COMM", "auto"),
+    # all-gather pushes of the fused layout go through NVSwitch multicast (multimem.st) when the symmetric
+    # heap has a multicast mapping; 0 = one store per peer
+    "SONAR_TP_MULTIMEM": _bool("SONAR_TP_MULTIMEM", True),
     "SONAR_CUDA_GRAPHS": _bool("SONAR_CUDA_GRAPHS", True),
     "SONAR_SYMM_HEAP_MB": _int("SONAR_SYMM_HEAP_MB", 512),
     # server

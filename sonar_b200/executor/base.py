@@ -67,7 +67,10 @@ class Executor:
         self.collective_rpc("compile_or_warm_up_model")
         return kv_cfg
 
-    def execute_model(self, so: SchedulerOutput) -> ModelRunnerOutput:
+    #: execute_model(so, defer=True) may return an object whose ``result()`` yields the output later
+    supports_defer = False
+
+    def execute_model(self, so: SchedulerOutput, defer: bool = False) -> ModelRunnerOutput:
         out = self.collective_rpc("execute_model", so, output_rank_only=True)
         return out[0]
 
@@ -75,7 +78,22 @@ class Executor:
         self.collective_rpc("check_health")
 
 
+class _Ready:
+    """A result that is already there, with the interface of a deferred one."""
+
+    def __init__(self, value) -> None:
+        self.value = value
+
+    def result(self):
+        return self.value
+
+
 class UniProcExecutor(Executor):
+    supports_defer = True
+
+    def execute_model(self, so: SchedulerOutput, defer: bool = False):
+        return self.worker.execute_model(so, defer=defer)
+
     def _init_executor(self) -> None:
         self.worker = Worker(self.cfg, rank=0, local_rank=0, world_size=1)
         self.worker.init_device()
@@ -115,11 +133,12 @@ class ExternalLauncherExecutor(UniProcExecutor):
         self.worker.compile_or_warm_up_model()
         return kv_cfg
 
-    def execute_model(self, so: SchedulerOutput) -> ModelRunnerOutput:
+    def execute_model(self, so: SchedulerOutput, defer: bool = False):
         from sonar_b200.parallel import state
-        out = self.worker.execute_model(so)
         pp = state.get_pp_group()
-        if pp.world_size > 1:
-            out = pp.broadcast_object(out, src=pp.world_size - 1)
-            self.worker.runner.apply_remote_output(so, out)
-        return out
+        if pp.world_size == 1:
+            return self.worker.execute_model(so, defer=defer)
+        out = self.worker.execute_model(so)
+        out = pp.broadcast_object(out, src=pp.world_size - 1)
+        self.worker.runner.apply_remote_output(so, out)
+        return _Ready(out) if defer else out

@@ -55,7 +55,7 @@ _gemm_tp = _sig("sonar_gemm_tp", c_void_p, c_void_p, c_void_p, c_int, c_int, c_i
                 c_void_p, c_int, c_void_p)
 _tp_add_norm = _sig("sonar_tp_add_norm", c_void_p, c_long, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float,
                     c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
-                    c_void_p)
+                    c_void_p, c_void_p)
 _tp_wait = _sig("sonar_tp_wait", c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p)
 _bump = _sig("sonar_bump", c_void_p, c_int, c_void_p)
 _all_reduce = _sig("sonar_all_reduce", c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -486,11 +486,13 @@ def gemm_tp(a, w, out, *, tp, shard_rows, seq, rank, seq_base=None, gather_flags
 
 
 def tp_add_norm(src_ptr, slot_stride, n_src, src_flags_ptr, wait_seq, residual, residual_in, weight, eps, hidden, rows,
-                gather_ptrs, tp, rank, shard_rows, blk_done, gather_flag_ptrs, send_seq, seq_base, err, dtype):
+                gather_ptrs, tp, rank, shard_rows, blk_done, gather_flag_ptrs, send_seq, seq_base, err, dtype,
+                gather_mc: int | None = None):
+    """``gather_mc``: NVSwitch multicast address of the gather buffer — one store per vector instead of tp."""
     _check(_tp_add_norm(src_ptr, slot_stride, n_src, src_flags_ptr, wait_seq, residual.data_ptr(), residual_in,
                         weight.data_ptr(), eps, hidden, rows, gather_ptrs.data_ptr(), tp, rank, shard_rows,
                         blk_done.data_ptr(), gather_flag_ptrs.data_ptr(), send_seq, _ptr(seq_base), err.data_ptr(), _DT[dtype],
-                        _stream()), "tp_add_norm")
+                        gather_mc or None, _stream()), "tp_add_norm")
 
 
 def tp_wait(flags, tp, shard_rows, m, seq, seq_base, err):

@@ -96,6 +96,9 @@ class FusedTPContext(TPContext):
         self.pflag_ptrs = b.ptr_table(self.off_pflags + rank * 4)
         self.gather_ptrs = b.ptr_table(self.off_gather)
         self.gflag_ptrs = b.ptr_table(self.off_gflags)
+        # all-gather push through the switch: one multimem store lands in every rank's gather buffer
+        from sonar_b200 import envs
+        self.gather_mc = (b.multicast_ptr + self.off_gather) if (b.multicast_ptr and envs.SONAR_TP_MULTIMEM) else 0
         self.ar_slot_ptrs = [b.ptr_table(self.off_ar + s * tp * self.ar_max) for s in range(2)]
         self.ar_flag_ptrs = [b.ptr_table(self.off_arflags + s * tp * 4) for s in range(2)]
         self.local_done = torch.zeros(tp, dtype=torch.int32, device=device)
@@ -153,7 +156,7 @@ class FusedTPContext(TPContext):
         self.seq += 1
         cu.tp_add_norm(src, stride, n_src, flags, wait_seq, residual, res_in, weight, eps, self.H, self.Tl,
                        self.gather_ptrs, tp, self.rank, self.Tl, self.blk_done, self.gflag_ptrs, self.seq, self.seq_base,
-                       self.err, self.dtype)
+                       self.err, self.dtype, self.gather_mc)
         return Gathered(self.seq), residual
 
     def col_linear(self, x, layer):

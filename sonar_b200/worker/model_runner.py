@@ -124,6 +124,10 @@ class ModelRunner:
         self.max_model_len = cfg.model.max_model_len
         self.batch = InputBatch(self.max_seqs, self.max_model_len, self.block_size, self.is_cuda)
         self.sampler = Sampler()
+        # run-ahead (async scheduling): the previous step's sampled ids stay on the device so the next
+        # step can read them as inputs before the host has seen them; two slots alternate
+        self._ahead_slot = 0
+        self._ahead_prev: tuple[torch.Tensor, dict[str, int]] | None = None
         self.model: torch.nn.Module | None = None
         self.kv_caches: list[torch.Tensor] = []
         self.kv_cfg: KVCacheConfig | None = None
@@ -143,6 +147,10 @@ class ModelRunner:
         self.d_logit_idx = torch.zeros(S * 8, dtype=torch.int64, device=device)
         self.d_block_table = torch.zeros((S, self.batch.max_blocks), dtype=torch.int32, device=device)
         self.h_sampled = host(S * 8, torch.int64)
+        self.h_ahead = [host(S, torch.int64), host(S, torch.int64)]
+        self.d_ahead = [torch.zeros(S, dtype=torch.int64, device=device) for _ in range(2)]
+        self.h_patch = torch.zeros((2, S), dtype=torch.int64, pin_memory=pin)
+        self.d_patch = torch.zeros((2, S), dtype=torch.int64, device=device)
         self.h_bt = torch.zeros((S, self.batch.max_blocks), dtype=torch.int32, pin_memory=pin)
         self.h_bt_np = self.h_bt.numpy()
         self._pending: dict[str, Any] | None = None
@@ -272,6 +280,8 @@ class ModelRunner:
             nt = int(b.num_tokens[r])
             b.token_ids[r, nt:nt + len(drafts)] = drafts
         ids = b.token_ids[row_of_tok, pos]
+        # tokens the host has not seen yet (sampled by the step still in flight) are patched in on the device
+        unknown = np.nonzero(pos >= b.num_tokens[row_of_tok])[0] if self._ahead_prev is not None else ()
         blk = b.block_table_np[row_of_tok, pos // self.block_size]
         slots = blk * self.block_size + pos % self.block_size
         seq_lens = computed + q_lens
@@ -300,6 +310,15 @@ class ModelRunner:
                 self.h_positions.numpy()[total:padded] = 0
                 self.h_slots.numpy()[total:padded] = -1
         self.d_input_ids[:padded].copy_(self.h_input_ids[:padded], non_blocking=nbl)
+        if len(unknown):
+            prev_ids, prev_index = self._ahead_prev
+            src = np.fromiter((prev_index[b.req_ids[row_of_tok[t]]] for t in unknown), dtype=np.int64, count=len(unknown))
+            n_u = len(unknown)
+            self.h_patch.numpy()[0, :n_u] = unknown
+            self.h_patch.numpy()[1, :n_u] = src
+            self.d_patch[:, :n_u].copy_(self.h_patch[:, :n_u], non_blocking=nbl)
+            self.d_input_ids.index_copy_(0, self.d_patch[0, :n_u],
+                                         prev_ids.index_select(0, self.d_patch[1, :n_u]).to(self.d_input_ids.dtype))
         self.d_positions[:padded].copy_(self.h_positions[:padded], non_blocking=nbl)
         self.d_slots[:padded].copy_(self.h_slots[:padded], non_blocking=nbl)
         self.d_seq_lens.copy_(self.h_seq_lens, non_blocking=nbl)
@@ -316,11 +335,16 @@ class ModelRunner:
 
     # --------------------------------------------------------------- execute
     @torch.inference_mode()
-    def execute_model(self, so: SchedulerOutput, intermediate=None) -> ModelRunnerOutput | tuple | None:
+    def execute_model(self, so: SchedulerOutput, intermediate=None, defer: bool = False):
+        """``defer``: launch the step and return an object whose ``result()`` waits for the sampled ids
+        (run-ahead scheduling); the ids stay on the device for the next step's inputs meanwhile."""
         t0 = time.perf_counter()
         self._update_states(so)
         if so.total_num_scheduled_tokens == 0:
-            return ModelRunnerOutput()
+            if not defer:
+                self._ahead_prev = None
+            return _Ready(ModelRunnerOutput()) if defer else ModelRunnerOutput()
+        self._defer = defer
         meta, rows, q_lens = self._prepare_inputs(so)
         if self.lora is not None:
             b = self.batch
@@ -360,6 +384,10 @@ class ModelRunner:
         self.stats["sample_s"] += time.perf_counter() - t2
         if self.eplb is not None and self.eplb.step():
             self.rebalance_experts()
+        if defer and not isinstance(res, _Deferred):
+            res = _Ready(res)
+        if not defer:
+            self._ahead_prev = None
         return res
 
     def rebalance_experts(self) -> int:
@@ -473,8 +501,23 @@ class ModelRunner:
         res = self.sampler(logits, md)
         for k, v in md.mirostat_mu.items():
             b.mirostat_mu[sample_rids[k]] = v
-        self.h_sampled[:g].copy_(res.token_ids, non_blocking=False)
         self.stats["d2h_bytes"] += g * 8
+        if getattr(self, "_defer", False):
+            # keep the ids on the device for the next step, start the copy to the host, hand back a promise
+            slot = self._ahead_slot
+            self._ahead_slot ^= 1
+            dev_ids = self.d_ahead[slot][:g]
+            dev_ids.copy_(res.token_ids)
+            host = self.h_ahead[slot]
+            host[:g].copy_(dev_ids, non_blocking=self.is_cuda)
+            done = None
+            if self.is_cuda:
+                done = torch.cuda.Event()
+                done.record()
+            self._ahead_prev = (dev_ids, {rid: row_span[j][0] for j, rid in enumerate(sample_rids)})
+            return _Deferred(self, out, host, g, done, [(req_ids[i], row_span[j][0]) for j, i in enumerate(idx)],
+                             [int(i) for i in idx])
+        self.h_sampled[:g].copy_(res.token_ids, non_blocking=False)
         sampled = self.h_sampled[:g].tolist()
         want_lp = res.logprobs is not None
         if want_lp:
@@ -610,3 +653,38 @@ class ModelRunner:
         act = t * (4 * m.hidden_size + 2 * widest) * el
         logits = self.max_seqs * (m.vocab_size * 6)
         return int(1.2 * (act + logits)) + (256 << 20)
+
+
+class _Ready:
+    """An output that is already complete, with the interface of a deferred one."""
+
+    def __init__(self, value) -> None:
+        self.value = value
+
+    def result(self):
+        return self.value
+
+
+class _Deferred:
+    """Sampled ids still travelling to the host.  ``result()`` waits for the copy, appends the tokens to the
+    persistent batch (rows are looked up by request id: they may have moved since) and completes the output."""
+
+    def __init__(self, runner: "ModelRunner", out: ModelRunnerOutput, host: torch.Tensor, n: int, event,
+                 picks: list[tuple[str, int]], out_slots: list[int]) -> None:
+        self.runner, self.out, self.host, self.n, self.event = runner, out, host, n, event
+        self.picks, self.out_slots = picks, out_slots
+
+    def result(self) -> ModelRunnerOutput:
+        if self.event is not None:
+            self.event.synchronize()
+        ids = self.host[: self.n].tolist()
+        b = self.runner.batch
+        for (rid, lo), slot in zip(self.picks, self.out_slots):
+            tok = ids[lo]
+            self.out.sampled_token_ids[slot] = [tok]
+            row = b.index.get(rid)
+            if row is not None:
+                nt = int(b.num_tokens[row])
+                b.token_ids[row, nt] = tok
+                b.num_tokens[row] = nt + 1
+        return self.out

@@ -171,8 +171,8 @@ class Worker:
         if warm is not None:
             warm()
 
-    def execute_model(self, so: SchedulerOutput) -> ModelRunnerOutput | None:
-        return self.runner.execute_model(so)
+    def execute_model(self, so: SchedulerOutput, defer: bool = False):
+        return self.runner.execute_model(so, defer=defer)
 
     def get_stats(self) -> dict:
         return dict(self.runner.stats)

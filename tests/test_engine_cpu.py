@@ -194,3 +194,27 @@ def test_fp8_moe_experts_run_and_match_dequantised_reference():
               hf_overrides={"hidden_size": 256, "moe_intermediate_size": 128, "intermediate_size": 512})
     outs = llm.generate([{"prompt_token_ids": [1, 2, 3, 4]}], SamplingParams(max_tokens=4, temperature=0, ignore_eos=True))
     assert len(outs[0].outputs[0].token_ids) == 4
+
+
+def test_async_scheduling_matches_lockstep():
+    """Run-ahead scheduling (next step built before this one's tokens are known) gives the same tokens."""
+    kw = dict(model="tiny-llama", dtype="float32", max_model_len=256, num_gpu_blocks_override=64, device="cpu",
+              max_num_seqs=4, max_num_batched_tokens=48, seed=0)
+    prompts = [{"prompt_token_ids": [7 + i, 8, 9, 10 + i] * (3 + i)} for i in range(7)]
+    sps = [SamplingParams(max_tokens=5 + 3 * i, temperature=0, ignore_eos=(i % 2 == 0)) for i in range(7)]
+    base = [o.outputs[0].token_ids for o in LLM(**kw).generate(prompts, sps)]
+    llm = LLM(**kw, async_scheduling=True)
+    core = llm.llm_engine.core.engine_core
+    assert core.run_ahead_ok
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, sps)]
+    assert got == base
+    assert core.run_ahead_steps > 10
+    ahead = core.run_ahead_steps
+    # seeded sampling and a request that needs lock-step (penalties) mixed in: still the same tokens
+    sps2 = [SamplingParams(max_tokens=6, temperature=0.9, seed=11 + i,
+                           repetition_penalty=1.3 if i == 2 else 1.0) for i in range(7)]
+    want2 = [o.outputs[0].token_ids for o in LLM(**kw).generate(prompts, sps2)]
+    got2 = [o.outputs[0].token_ids for o in llm.generate(prompts, sps2)]
+    assert got2 == want2
+    assert core.run_ahead_steps >= ahead      # lock-step while the penalty request lives, run-ahead after
+    assert core.pending is None and not core.scheduler.has_unfinished_requests()

@@ -56,6 +56,8 @@ def parse_args():
     ap.add_argument("--quantization", default=None, choices=[None, "fp8"],
                     help="fp8: random-init weights quantised to e4m3 with 128x128 block scales")
     ap.add_argument("--kv-cache-dtype", default="auto", choices=["auto", "fp8"])
+    ap.add_argument("--no-async-scheduling", action="store_true",
+                    help="lock-step engine loop (default: the next step is scheduled while the GPU runs this one)")
     return ap.parse_args()
 
 
@@ -138,7 +140,7 @@ def main() -> None:
     llm = LLM(args.model, dtype="bfloat16", max_model_len=max_len, max_num_seqs=args.max_num_seqs,
               max_num_batched_tokens=args.max_num_batched_tokens, block_size=16, enable_prefix_caching=True,
               skip_tokenizer_init=True, tensor_parallel_size=args.gpus, seed=0, quantization=args.quantization,
-              kv_cache_dtype=args.kv_cache_dtype,
+              kv_cache_dtype=args.kv_cache_dtype, async_scheduling=not args.no_async_scheduling,
               distributed_executor_backend="external_launcher" if world > 1 else "uni")
     engine = llm.llm_engine
     vocab = engine.cfg.model.vocab_size
@@ -250,7 +252,8 @@ def main() -> None:
             "dtype": "fp8 (e4m3 block-scaled weights, bf16 activations)" if args.quantization == "fp8" else "bf16", "data": "synthetic (uniform-random token ids, random-init weights)",
             "impl": "sonar_b200",
             "config": {
-                "model": args.model, "tp_comm": os.environ.get("SONAR_TP_COMM", "auto"), "quantization": args.quantization, "kv_cache_dtype": args.kv_cache_dtype,
+                "model": args.model, "tp_comm": os.environ.get("SONAR_TP_COMM", "auto"),
+                "async_scheduling": not args.no_async_scheduling, "quantization": args.quantization, "kv_cache_dtype": args.kv_cache_dtype,
                 "num_requests": args.num_requests, "input_len": args.input_len,
                 "output_len": args.output_len, "max_num_seqs": args.max_num_seqs,
                 "max_num_batched_tokens": args.max_num_batched_tokens, "block_size": 16,

@@ -114,3 +114,21 @@ def test_fp8_weights_and_fp8_kv_cache_match_torch_path():
         a = torch.tensor([g.prompt_logprobs[i][ids[i]].logprob for i in range(1, len(ids))])
         b = torch.tensor([w.prompt_logprobs[i][ids[i]].logprob for i in range(1, len(ids))])
         assert (a - b).abs().max() < 0.2, (a - b).abs().max()
+
+
+def test_async_scheduling_on_gpu_matches_lockstep():
+    """Run-ahead scheduling with CUDA-graph decode steps: same greedy tokens as lock-step stepping."""
+    from sonar_b200 import LLM, SamplingParams
+    kw = dict(model="tiny-llama-128", max_model_len=512, num_gpu_blocks_override=256, max_num_seqs=16,
+              max_num_batched_tokens=128, seed=0)
+    prompts = [{"prompt_token_ids": [(13 * i + j) % 2000 + 3 for j in range(20 + 7 * i)]} for i in range(12)]
+    sps = [SamplingParams(max_tokens=6 + 2 * i, temperature=0, ignore_eos=True) for i in range(12)]
+    sync = LLM(**kw)
+    want = [o.outputs[0].token_ids for o in sync.generate(prompts, sps)]
+    sync.shutdown()
+    llm = LLM(**kw, async_scheduling=True)
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, sps)]
+    core = llm.llm_engine.core.engine_core
+    assert core.run_ahead_steps > 10
+    assert got == want
+    llm.shutdown()

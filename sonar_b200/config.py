@@ -195,7 +195,8 @@ class CacheConfig:
     prefix_caching_hash_algo: str = "sha256"   # sha256 | builtin
     cache_dtype: str = "auto"                  # auto | fp8
     swap_space_gb: float = 0.0
-    kv_offload_cpu_gb: float = 0.0
+    kv_offload_cpu_gb: float = 0.0             # host memory for the CPU tier of the prefix cache (per rank)
+    kv_offload_cpu_blocks: int = 0             # same, as a block count (takes precedence; tests)
     sliding_window: int | None = None
 
     def __post_init__(self) -> None:
@@ -369,6 +370,8 @@ class EngineArgs:
     # speculative
     speculative_method: str | None = None
     num_speculative_tokens: int = 0
+    kv_offload_cpu_gb: float = 0.0
+    kv_offload_cpu_blocks: int = 0
     # LoRA
     enable_lora: bool = False
     max_loras: int = 4
@@ -406,7 +409,8 @@ class EngineArgs:
             block_size=self.block_size, gpu_memory_utilization=self.gpu_memory_utilization,
             num_gpu_blocks_override=self.num_gpu_blocks_override,
             enable_prefix_caching=self.enable_prefix_caching,
-            prefix_caching_hash_algo=self.prefix_caching_hash_algo, cache_dtype=self.kv_cache_dtype)
+            prefix_caching_hash_algo=self.prefix_caching_hash_algo, cache_dtype=self.kv_cache_dtype,
+            kv_offload_cpu_gb=self.kv_offload_cpu_gb, kv_offload_cpu_blocks=self.kv_offload_cpu_blocks)
         parallel = ParallelConfig(
             tensor_parallel_size=self.tensor_parallel_size,
             pipeline_parallel_size=self.pipeline_parallel_size,

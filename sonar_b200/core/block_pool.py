@@ -53,6 +53,7 @@ class BlockPool:
         self.hash_to_block: dict[bytes, int] = {}
         self.collect_events = collect_events
         self.events: list[KVEvent] = []
+        self.on_evict = None          # callable(block id, hash): a lower tier that keeps evicted blocks
 
     # ---- free list -----------------------------------------------------
     def _push_back(self, b: int) -> None:
@@ -116,6 +117,8 @@ class BlockPool:
             return
         if self.hash_to_block.get(h) == b:
             del self.hash_to_block[h]
+            if self.on_evict is not None:
+                self.on_evict(b, h)
             if self.collect_events:
                 self.events.append(KVEvent("removed", [h]))
         self.block_hash[b] = None

@@ -66,7 +66,7 @@ def get_kv_cache_config(spec: KVCacheSpec, num_layers: int, available_bytes: int
 class KVCacheManager:
     def __init__(self, num_blocks: int, block_size: int, enable_caching: bool = True,
                  sliding_window: int | None = None, collect_events: bool = False,
-                 watermark: float = 0.0) -> None:
+                 watermark: float = 0.0, cpu_offload_blocks: int = 0) -> None:
         self.block_size = block_size
         self.enable_caching = enable_caching
         self.sliding_window = sliding_window
@@ -76,6 +76,12 @@ class KVCacheManager:
         self.watermark_blocks = int(watermark * num_blocks)
         self.prefix_queries = 0
         self.prefix_hits = 0
+        self.cpu_tier_hits = 0
+        self.offload = None
+        if cpu_offload_blocks > 0 and enable_caching:
+            from sonar_b200.core.kv_offload import CPUOffloadTier
+            self.offload = CPUOffloadTier(cpu_offload_blocks)
+            self.pool.on_evict = self.offload.on_evict
 
     # ------------------------------------------------------------------
     @property
@@ -99,6 +105,26 @@ class KVCacheManager:
             if b is None:
                 break
             hit.append(b)
+        if self.offload is not None and self.sliding_window is None and len(hit) < max_blocks:
+            # continue the match in the CPU tier: matching blocks get fresh GPU blocks, are registered under
+            # their hashes and released again, so they look like ordinary cached blocks; the copy from host
+            # memory runs at the start of the step that first uses them
+            more: list[bytes] = []
+            for h in request.block_hashes[len(hit):max_blocks]:
+                if self.offload.lookup(h) is None:
+                    break
+                more.append(h)
+            more = more[: max(0, self.pool.get_num_free_blocks() - self.watermark_blocks - 1)]
+            if more:
+                self.pool.touch(b for b in hit if b != NULL_BLOCK)      # keep the GPU hits from being evicted below
+                fresh = self.pool.get_new_blocks(len(more))
+                for b, h in zip(fresh, more):
+                    self.pool.block_hash[b] = h
+                    self.pool.hash_to_block.setdefault(h, b)
+                    self.offload.request_load(h, b)
+                self.pool.free_blocks(list(hit) + fresh)
+                hit.extend(fresh)
+                self.cpu_tier_hits += len(more)
         if self.sliding_window is not None and hit:
             # only the blocks overlapping the window of the first new token matter
             first_needed = max(0, (len(hit) * self.block_size - self.sliding_window + 1)) // self.block_size
@@ -186,6 +212,8 @@ class KVCacheManager:
         ok = self.pool.reset_prefix_cache()
         if ok:
             self.prefix_queries = self.prefix_hits = 0
+            if self.offload is not None:
+                self.offload.clear()
         return ok
 
     def get_num_common_prefix_blocks(self, request_id: str, num_running: int) -> int:

@@ -66,6 +66,9 @@ class SchedulerOutput:
     # constrained decoding: one packed int32 bitmask row per listed request (bit set = token allowed)
     grammar_req_ids: list[str] = field(default_factory=list)
     grammar_bitmask: object | None = None
+    # CPU tier of the prefix cache: block copies to run before the forward pass, stores first
+    kv_stores: list[tuple[int, int]] = field(default_factory=list)    # (gpu block, cpu slot)
+    kv_loads: list[tuple[int, int]] = field(default_factory=list)     # (cpu slot, gpu block)
 
 
 @dataclass
@@ -156,7 +159,7 @@ class Scheduler:
     def __init__(self, sched_cfg: SchedulerConfig, cache_cfg: CacheConfig, num_blocks: int,
                  spec_cfg: SpeculativeConfig | None = None, sliding_window: int | None = None,
                  log_stats: bool = False, collect_kv_events: bool = False,
-                 structured_output_manager=None) -> None:
+                 structured_output_manager=None, cpu_offload_blocks: int = 0) -> None:
         self.cfg = sched_cfg
         self.structured = structured_output_manager
         self.cache_cfg = cache_cfg
@@ -165,7 +168,7 @@ class Scheduler:
         self.num_spec_tokens = spec_cfg.num_speculative_tokens if spec_cfg and spec_cfg.method else 0
         self.kv = KVCacheManager(num_blocks, cache_cfg.block_size, cache_cfg.enable_prefix_caching,
                                  sliding_window=sliding_window, collect_events=collect_kv_events,
-                                 watermark=sched_cfg.watermark)
+                                 watermark=sched_cfg.watermark, cpu_offload_blocks=cpu_offload_blocks)
         self.block_hasher = (make_block_hasher(cache_cfg.block_size, cache_cfg.prefix_caching_hash_algo)
                              if cache_cfg.enable_prefix_caching else None)
         self.requests: dict[str, Request] = {}
@@ -352,6 +355,8 @@ class Scheduler:
                 req.num_output_placeholders += 1       # this step samples a token the host has not seen yet
             if req.grammar is not None and req.num_computed_tokens >= req.num_tokens:
                 gram.append(req)
+        if self.kv.offload is not None:
+            out.kv_stores, out.kv_loads = self.kv.offload.take_transfers()
         if gram:
             out.grammar_req_ids = [r.request_id for r in gram]
             out.grammar_bitmask = self.structured.bitmask([r.grammar for r in gram])

@@ -37,10 +37,14 @@ class EngineCore:
             from sonar_b200.utils.tokenizer import get_tokenizer
             structured = StructuredOutputManager(get_tokenizer(cfg.model.tokenizer, cfg.model.vocab_size),
                                                  cfg.model.vocab_size)
+        cpu_blocks = cfg.cache.kv_offload_cpu_blocks or int(
+            cfg.cache.kv_offload_cpu_gb * 2**30 // max(1, self.kv_cfg.num_layers * self.kv_cfg.spec.page_bytes))
+        if cpu_blocks:
+            self.executor.collective_rpc("init_kv_offload", cpu_blocks)
         self.scheduler = Scheduler(cfg.scheduler, cfg.cache, self.kv_cfg.num_blocks, cfg.speculative,
                                    sliding_window=sliding, log_stats=cfg.observability.log_stats,
                                    collect_kv_events=cfg.observability.collect_kv_events,
-                                   structured_output_manager=structured)
+                                   structured_output_manager=structured, cpu_offload_blocks=cpu_blocks)
         self.tracer = get_tracer(cfg.observability.trace_file)
         self.kv_publisher = None
         if cfg.observability.kv_events_endpoint:

@@ -231,8 +231,35 @@ class ModelRunner:
         logger.info("KV cache: %d blocks × %d layers, %.2f GiB", kv_cfg.num_blocks, len(self.kv_caches),
                     kv_cfg.num_blocks * len(self.kv_caches) * spec.page_bytes / 2**30)
 
+    # --------------------------------------------------------------- CPU tier of the prefix cache
+    def init_kv_offload(self, num_cpu_blocks: int) -> int:
+        """Pinned host mirror ``[layers][num_cpu_blocks, …block shape]`` for evicted KV blocks."""
+        self.cpu_kv = [torch.empty((num_cpu_blocks,) + tuple(c.shape[1:]), dtype=c.dtype, pin_memory=self.is_cuda)
+                       for c in self.kv_caches]
+        nbytes = sum(t.numel() * t.element_size() for t in self.cpu_kv)
+        logger.info("KV offload: %d host blocks (%.2f GiB pinned)", num_cpu_blocks, nbytes / 2**30)
+        return nbytes
+
+    def _run_kv_transfers(self, so: SchedulerOutput) -> None:
+        """Evicted blocks go to the host before their new owners overwrite them; blocks matched in the host
+        tier come back before attention reads them.  Both run on the compute stream, in that order."""
+        if so.kv_stores:
+            src = torch.tensor([g for g, _ in so.kv_stores], dtype=torch.int64, device=self.device)
+            dst = torch.tensor([c for _, c in so.kv_stores], dtype=torch.int64)
+            for cache, host in zip(self.kv_caches, self.cpu_kv):
+                host.index_copy_(0, dst, cache.index_select(0, src).to("cpu"))
+            self.stats["kv_offload_stores"] = self.stats.get("kv_offload_stores", 0) + len(so.kv_stores)
+        if so.kv_loads:
+            src = torch.tensor([c for c, _ in so.kv_loads], dtype=torch.int64)
+            dst = torch.tensor([g for _, g in so.kv_loads], dtype=torch.int64, device=self.device)
+            for cache, host in zip(self.kv_caches, self.cpu_kv):
+                cache.index_copy_(0, dst, host.index_select(0, src).to(self.device, non_blocking=False))
+            self.stats["kv_offload_loads"] = self.stats.get("kv_offload_loads", 0) + len(so.kv_loads)
+
     # --------------------------------------------------------------- states
     def _update_states(self, so: SchedulerOutput) -> None:
+        if so.kv_stores or so.kv_loads:
+            self._run_kv_transfers(so)
         b = self.batch
         for rid in so.finished_req_ids:
             b.remove(rid)

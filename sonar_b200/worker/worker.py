@@ -108,6 +108,9 @@ class Worker:
         with self._pool("kv_cache"):
             self.runner.initialize_kv_cache(kv_cfg)
 
+    def init_kv_offload(self, num_cpu_blocks: int) -> int:
+        return self.runner.init_kv_offload(num_cpu_blocks)
+
     # sleep / wake-up --------------------------------------------------------------
     def sleep(self, level: int = 1) -> int:
         """Level 1: weights go to pinned host memory, the KV cache is dropped.  Level 2: both are

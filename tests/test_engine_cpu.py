@@ -218,3 +218,27 @@ def test_async_scheduling_matches_lockstep():
     assert got2 == want2
     assert core.run_ahead_steps >= ahead      # lock-step while the penalty request lives, run-ahead after
     assert core.pending is None and not core.scheduler.has_unfinished_requests()
+
+
+def test_cpu_offload_tier_restores_evicted_prefix():
+    """A prefix evicted from a tiny GPU pool comes back from the host tier: same tokens, hits counted, and
+    the restored blocks hold exactly the KV they held before eviction."""
+    kw = dict(model="tiny-llama", dtype="float32", max_model_len=96, num_gpu_blocks_override=12, device="cpu",
+              max_num_seqs=2, max_num_batched_tokens=64, seed=0)
+    sp = SamplingParams(max_tokens=4, temperature=0, ignore_eos=True)
+    a = {"prompt_token_ids": list(range(10, 10 + 64))}          # 4 blocks
+    fillers = [{"prompt_token_ids": list(range(300 + 70 * i, 300 + 70 * i + 64))} for i in range(3)]
+    want = LLM(**kw).generate([a], sp)[0].outputs[0].token_ids
+    llm = LLM(**kw, kv_offload_cpu_blocks=32)
+    core = llm.llm_engine.core.engine_core
+    assert llm.generate([a], sp)[0].outputs[0].token_ids == want
+    for f in fillers:                                            # push a's blocks out of the 11-block pool
+        llm.generate([f], sp)
+    tier = core.scheduler.kv.offload
+    assert tier.num_stored >= 4
+    out = llm.generate([a], sp)[0]
+    assert out.outputs[0].token_ids == want
+    assert core.scheduler.kv.cpu_tier_hits >= 3 and tier.num_loaded >= 3
+    assert out.num_cached_tokens >= 48                           # served from the host tier, not recomputed
+    stats = llm.llm_engine.get_stats()["workers"][0]
+    assert stats["kv_offload_loads"] >= 3 and stats["kv_offload_stores"] >= 4

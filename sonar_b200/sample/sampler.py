@@ -62,12 +62,23 @@ def make_sampling_metadata(params: list[SamplingParams], prompt_ids: list[list[i
                            req_ids=None) -> SamplingMetadata:
     temps = [0.0 if p.temperature < _EPS else p.temperature for p in params]
     lp = [p.logprobs for p in params if p.logprobs is not None]
+    n = len(params)
+    # one pinned staging block and one asynchronous copy: a pageable host→device copy would block the host
+    # until everything queued on the stream has run, which defeats scheduling ahead of the GPU
+    cuda = torch.device(device).type == "cuda"
+    stage = torch.empty((4, n), dtype=torch.float32, pin_memory=cuda)
+    sv = stage.numpy()
+    sv[0] = temps
+    sv[1] = [p.top_k for p in params]
+    sv[2] = [p.top_p for p in params]
+    sv[3] = [p.min_p for p in params]
+    dev = stage.to(device, non_blocking=cuda)
     return SamplingMetadata(
         params=params,
-        temperature=torch.tensor(temps, dtype=torch.float32, device=device),
-        top_k=torch.tensor([p.top_k for p in params], dtype=torch.int32, device=device),
-        top_p=torch.tensor([p.top_p for p in params], dtype=torch.float32, device=device),
-        min_p=torch.tensor([p.min_p for p in params], dtype=torch.float32, device=device),
+        temperature=dev[0],
+        top_k=dev[1].to(torch.int32),
+        top_p=dev[2],
+        min_p=dev[3],
         all_greedy=all(t == 0.0 for t in temps),
         all_simple=not any(_needs_chain(p) for p in params),
         prompt_token_ids=prompt_ids, output_token_ids=output_ids, generators=generators or {},

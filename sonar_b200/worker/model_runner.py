@@ -126,6 +126,7 @@ class ModelRunner:
         self.sampler = Sampler()
         # run-ahead (async scheduling): the previous step's sampled ids stay on the device so the next
         # step can read them as inputs before the host has seen them; two slots alternate
+        self._staged = None          # event: the step's host→device input copies have executed
         self._ahead_slot = 0
         self._ahead_prev: tuple[torch.Tensor, dict[str, int]] | None = None
         self.model: torch.nn.Module | None = None
@@ -148,6 +149,8 @@ class ModelRunner:
         self.d_block_table = torch.zeros((S, self.batch.max_blocks), dtype=torch.int32, device=device)
         self.h_sampled = host(S * 8, torch.int64)
         self.h_ahead = [host(S, torch.int64), host(S, torch.int64)]
+        self.h_logit_idx2 = [self.h_logit_idx, host(S * 8, torch.int64)]
+        self._logit_slot = 0
         self.d_ahead = [torch.zeros(S, dtype=torch.int64, device=device) for _ in range(2)]
         self.h_patch = torch.zeros((2, S), dtype=torch.int64, pin_memory=pin)
         self.d_patch = torch.zeros((2, S), dtype=torch.int64, device=device)
@@ -285,6 +288,8 @@ class ModelRunner:
 
     # --------------------------------------------------------------- inputs
     def _prepare_inputs(self, so: SchedulerOutput) -> tuple[AttentionMetadata, np.ndarray, np.ndarray]:
+        if self._staged is not None:
+            self._staged.synchronize()     # the previous step's copies out of the pinned staging buffers have run
         b = self.batch
         n = b.num_reqs
         sched = np.fromiter((so.num_scheduled_tokens.get(b.req_ids[i], 0) for i in range(n)),
@@ -382,10 +387,15 @@ class ModelRunner:
         tp = get_tp_context()
         padded = meta.positions.shape[0]
         t1 = time.perf_counter()
+        if self.is_cuda and defer:
+            if self._staged is None:
+                self._staged = torch.cuda.Event()
         if padded != total or (padded in self.graphs and int(q_lens.max()) == 1 and self.pp is None):
             # ---- CUDA-graph replay (decode-only step)
             from sonar_b200.ops import cuda as cuda_ops
             cuda_ops.build_attention_work(meta, self, graph_bucket=padded)
+            if self._staged is not None:
+                self._staged.record()
             graph, out_buf = self.graphs[padded]
             graph.replay()
             cuda_ops.launch_count += self.graph_launches[padded]
@@ -396,6 +406,8 @@ class ModelRunner:
             if self.is_cuda and not getattr(self.model, "uses_mla", False):
                 from sonar_b200.ops import cuda as cuda_ops
                 cuda_ops.build_attention_work(meta, self)
+            if self._staged is not None:
+                self._staged.record()
             ids = self.d_input_ids[:total]
             if self.pp is not None and not self.pp.is_first_rank:
                 intermediate = self._recv_intermediate(tp.local_tokens(total))
@@ -488,8 +500,12 @@ class ModelRunner:
             row_span.append((len(gather), k + 1))
             gather.extend(range(end - 1 - k, end))
         g = len(gather)
-        self.h_logit_idx.numpy()[:g] = gather
-        self.d_logit_idx[:g].copy_(self.h_logit_idx[:g], non_blocking=self.is_cuda)
+        # two staging buffers alternate: when the engine runs one step ahead, the previous step's copy out
+        # of the other buffer may not have executed yet
+        self._logit_slot ^= 1
+        h_idx = self.h_logit_idx2[self._logit_slot]
+        h_idx.numpy()[:g] = gather
+        self.d_logit_idx[:g].copy_(h_idx[:g], non_blocking=self.is_cuda)
         sel = hidden.index_select(0, self.d_logit_idx[:g])
         logits = self.model.compute_logits(sel)
         params, prompts, outs_hist, gens, sample_rids = [], [], [], {}, []

@@ -115,7 +115,7 @@ class ModelConfig:
     dtype: torch.dtype = torch.bfloat16
     seed: int = 0
     max_model_len: int = 0
-    quantization: str | None = None          # None | "fp8" (128x128 block scales)
+    quantization: str | None = None          # None | "fp8" (128x128 block scales) | "fp8_tensor" (per-tensor/-channel)
     load_format: str = "auto"                # auto | safetensors | dummy
     skip_tokenizer_init: bool = False
     served_model_name: str | None = None
@@ -130,10 +130,15 @@ class ModelConfig:
         if self.tokenizer is None and self.checkpoint_dir is not None:
             self.tokenizer = self.checkpoint_dir
         qc = self.hf_config.get("quantization_config")
-        if self.quantization is None and isinstance(qc, dict) and qc.get("quant_method") == "fp8":
-            self.quantization = "fp8"
-        if self.quantization not in (None, "fp8"):
-            raise ValueError(f"unsupported quantization {self.quantization!r}; supported: fp8")
+        if self.quantization is None and isinstance(qc, dict):
+            method = qc.get("quant_method")
+            if method == "fp8":
+                # block-scaled (DeepSeek / Qwen3 fp8 checkpoints) or per-tensor scales (static / dynamic activations)
+                self.quantization = "fp8" if qc.get("weight_block_size") else "fp8_tensor"
+            elif method in ("compressed-tensors", "modelopt") and "fp8" in str(qc).lower().replace("float8", "fp8"):
+                self.quantization = "fp8_tensor"     # per-tensor or per-channel weight scales, per-token activations
+        if self.quantization not in (None, "fp8", "fp8_tensor"):
+            raise ValueError(f"unsupported quantization {self.quantization!r}; supported: fp8, fp8_tensor")
         derived = int(self.hf_config.get("max_position_embeddings", 8192))
         if not self.max_model_len:
             self.max_model_len = derived

@@ -83,6 +83,44 @@ class Fp8BlockMethod:
         layer.weight_scale_inv.data.copy_(s)
 
 
+class Fp8TensorMethod:
+    """fp8 e4m3 weights with one scale per tensor or per output channel (``weight_scale`` of shape [1] or
+    [N]; merged layers keep one scale per logical sub-matrix, expanded to per-channel at load), activations
+    quantised per token on the fly or with a static ``input_scale`` — the compressed-tensors / ModelOpt /
+    "fp8 without block size" checkpoint family.  The GEMM is the block-scaled kernel fed with broadcast
+    scales (``ops.scaled_mm_fp8``).
+
+    Parity: ``Fp8LinearMethod`` per-tensor path (``layers/quantization/fp8.py``) and the sm100
+    ``cutlass_scaled_mm`` per-token / per-tensor kernels it dispatches to."""
+    name = "fp8_tensor"
+
+    def create(self, layer: "LinearBase", n: int, k: int, dtype: torch.dtype, device) -> None:
+        if k % FP8_BLOCK:
+            raise ValueError(f"fp8 GEMM needs the input dim ({k}) to be a multiple of {FP8_BLOCK}")
+        layer.weight = nn.Parameter(torch.empty(n, k, dtype=torch.float8_e4m3fn, device=device), requires_grad=False)
+        layer.weight_scale = nn.Parameter(torch.ones(n, dtype=torch.float32, device=device), requires_grad=False)
+        layer.input_scale = None          # set by the loader for statically quantised activations
+        layer.out_dtype = dtype
+
+    def apply(self, layer: "LinearBase", x: torch.Tensor) -> torch.Tensor:
+        if layer.input_scale is not None:
+            xq, xs = ops.scaled_fp8_quant(x, layer.input_scale)
+        else:
+            xq, xs = ops.per_token_quant_fp8(x)
+        y = ops.scaled_mm_fp8(xq, xs, layer.weight, layer.weight_scale, layer.out_dtype)
+        return y if layer.bias is None else y + layer.bias
+
+    def process_after_load(self, layer: "LinearBase") -> None:
+        pass
+
+    @staticmethod
+    def quantize_into(layer: "LinearBase", w: torch.Tensor) -> None:
+        """Per-channel quantisation of a 16-bit weight (dummy weights, online quantisation)."""
+        q, s = torch_ref.per_token_quant_fp8(w)
+        layer.weight.data.copy_(q)
+        layer.weight_scale.data.copy_(s.reshape(-1))
+
+
 def wants_quant_act(layer) -> bool:
     """True when ``layer`` consumes fp8 group-quantised activations (so its producer may quantise in its epilogue)."""
     return (layer is not None and isinstance(getattr(layer, "method", None), Fp8BlockMethod)
@@ -90,7 +128,11 @@ def wants_quant_act(layer) -> bool:
 
 
 def make_linear_method(quantization: str | None):
-    return Fp8BlockMethod() if quantization == "fp8" else UnquantizedMethod()
+    if quantization == "fp8":
+        return Fp8BlockMethod()
+    if quantization == "fp8_tensor":
+        return Fp8TensorMethod()
+    return UnquantizedMethod()
 
 
 class LinearBase(nn.Module):
@@ -120,6 +162,19 @@ class LinearBase(nn.Module):
     forward = apply
 
     # weight loading helpers -------------------------------------------------
+    def _expand_scale(self, tensor: torch.Tensor, full_rows: int) -> torch.Tensor:
+        """A per-tensor ([1] / scalar) or per-channel ([N] / [N, 1]) scale as a per-channel fp32 vector."""
+        t = tensor.float().reshape(-1)
+        return t.expand(full_rows).contiguous() if t.numel() == 1 else t
+
+    def _load_input_scale(self, tensor: torch.Tensor) -> None:
+        """Static activation scale; merged layers share one quantised input, so the largest scale wins."""
+        v = tensor.float().reshape(-1).max().reshape(1).to(self.weight.device)
+        if getattr(self, "input_scale", None) is None:
+            self.input_scale = v
+        else:
+            self.input_scale = torch.maximum(self.input_scale, v)
+
     def _copy_rows(self, param: torch.Tensor, row_off: int, src: torch.Tensor) -> None:
         param.data[row_off:row_off + src.shape[0]].copy_(src)
 
@@ -131,6 +186,10 @@ class ReplicatedLinear(LinearBase):
         self._alloc(out_features, in_features)
 
     def load_weight(self, name: str, tensor: torch.Tensor, shard_id=None) -> None:
+        if name == "input_scale":
+            return self._load_input_scale(tensor)
+        if name == "weight_scale":
+            tensor = self._expand_scale(tensor, self.out_features)
         getattr(self, name).data.copy_(tensor)
 
 
@@ -157,6 +216,11 @@ class ColumnParallelLinear(LinearBase):
     def load_weight(self, name: str, tensor: torch.Tensor, shard_id: int | None = None) -> None:
         """``tensor`` is the full (unsharded) checkpoint tensor of sub-matrix
         ``shard_id`` (or of the whole layer when there is only one)."""
+        if name == "input_scale":
+            return self._load_input_scale(tensor)
+        if name == "weight_scale":
+            full = sum(self.output_sizes) if shard_id is None else self.output_sizes[shard_id]
+            tensor = self._expand_scale(tensor, full)
         param = getattr(self, name)
         ids = range(len(self.output_sizes)) if shard_id is None and len(self.output_sizes) > 1 else [shard_id or 0]
         src_off = 0
@@ -207,6 +271,10 @@ class QKVParallelLinear(ColumnParallelLinear):
 
     def load_weight(self, name: str, tensor: torch.Tensor, shard_id: int | str | None = None) -> None:
         idx = {"q": 0, "k": 1, "v": 2}.get(shard_id, shard_id)
+        if name == "input_scale":
+            return self._load_input_scale(tensor)
+        if name == "weight_scale":
+            tensor = self._expand_scale(tensor, sum(self.output_sizes) if idx is None else self.output_sizes[idx])
         param = getattr(self, name)
         unit = FP8_BLOCK if name == "weight_scale_inv" else 1
         if idx is None:  # fused qkv tensor in the checkpoint
@@ -238,7 +306,12 @@ class RowParallelLinear(LinearBase):
             self.bias = None  # added once, by rank 0's partial
 
     def load_weight(self, name: str, tensor: torch.Tensor, shard_id=None) -> None:
+        if name == "input_scale":
+            return self._load_input_scale(tensor)
         param = getattr(self, name)
+        if name == "weight_scale":
+            param.data.copy_(self._expand_scale(tensor, self.out_features))
+            return
         if name == "bias":
             param.data.copy_(tensor)
             return

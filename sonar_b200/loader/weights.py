@@ -24,7 +24,7 @@ import torch
 from torch import nn
 
 from sonar_b200.config import EngineConfig, ModelConfig
-from sonar_b200.layers.linear import Fp8BlockMethod, LinearBase
+from sonar_b200.layers.linear import Fp8BlockMethod, Fp8TensorMethod, LinearBase
 from sonar_b200.logger import init_logger
 from sonar_b200.models.registry import resolve_model_cls
 
@@ -128,6 +128,13 @@ def initialize_dummy_weights(model: nn.Module, seed: int, std: float = 0.02) -> 
     real 128×128 block scales."""
     done: set[int] = set()
     for mod_name, mod in model.named_modules():
+        if isinstance(mod, LinearBase) and isinstance(mod.method, Fp8TensorMethod):
+            gen = torch.Generator(device=mod.weight.device).manual_seed(_name_seed(mod_name, seed))
+            w = torch.empty(mod.weight.shape, dtype=torch.bfloat16, device=mod.weight.device)
+            w.normal_(0.0, std, generator=gen)
+            Fp8TensorMethod.quantize_into(mod, w)
+            done.add(id(mod.weight))
+            done.add(id(mod.weight_scale))
         if isinstance(mod, LinearBase) and isinstance(mod.method, Fp8BlockMethod):
             gen = torch.Generator(device=mod.weight.device).manual_seed(_name_seed(mod_name, seed))
             w = torch.empty(mod.weight.shape, dtype=torch.bfloat16, device=mod.weight.device)

@@ -242,3 +242,43 @@ def test_cpu_offload_tier_restores_evicted_prefix():
     assert out.num_cached_tokens >= 48                           # served from the host tier, not recomputed
     stats = llm.llm_engine.get_stats()["workers"][0]
     assert stats["kv_offload_loads"] >= 3 and stats["kv_offload_stores"] >= 4
+
+
+def test_fp8_per_tensor_checkpoint_loads_and_matches_dequantised(tmp_path):
+    """"fp8 without block size" checkpoints (one weight scale per tensor, optional static input scale) load into
+    the per-tensor fp8 method; logits stay close to the same weights run unquantised."""
+    import json
+    import os
+
+    import torch
+    from sonar_b200.loader.weights import read_safetensors, save_checkpoint
+    import sys
+    sys.path.insert(0, os.path.dirname(__file__))
+    from tp_common import make_checkpoint
+    base = make_checkpoint(str(tmp_path / "base"), "tiny-llama-128", dtype=torch.float32)
+    tensors = dict(read_safetensors(os.path.join(base, "model.safetensors")))
+    cfg = json.load(open(os.path.join(base, "config.json")))
+    q_t, deq_t = {}, {}
+    for name, t in tensors.items():
+        if name.endswith("_proj.weight"):
+            scale = t.abs().max() / 448.0
+            q = (t / scale).clamp(-448, 448).to(torch.float8_e4m3fn)
+            q_t[name] = q
+            q_t[name.replace(".weight", ".weight_scale")] = scale.reshape(1)
+            deq_t[name] = q.float() * scale
+        else:
+            q_t[name] = deq_t[name] = t
+    qcfg = dict(cfg, quantization_config={"quant_method": "fp8", "activation_scheme": "dynamic"})
+    save_checkpoint(str(tmp_path / "fp8"), qcfg, q_t)
+    save_checkpoint(str(tmp_path / "deq"), cfg, deq_t)
+    kw = dict(dtype="float32", max_model_len=128, num_gpu_blocks_override=32, device="cpu", max_num_seqs=4,
+              max_num_batched_tokens=64, skip_tokenizer_init=True)
+    sp = SamplingParams(max_tokens=3, temperature=0, prompt_logprobs=0, ignore_eos=True, detokenize=False)
+    prompt = {"prompt_token_ids": [5, 17, 200, 33, 1000, 7, 64, 9]}
+    llm = LLM(str(tmp_path / "fp8"), **kw)
+    assert llm.llm_engine.cfg.model.quantization == "fp8_tensor"
+    a = llm.generate([prompt], sp)[0]
+    b = LLM(str(tmp_path / "deq"), **kw).generate([prompt], sp)[0]
+    la = [a.prompt_logprobs[i][prompt["prompt_token_ids"][i]].logprob for i in range(1, 8)]
+    lb = [b.prompt_logprobs[i][prompt["prompt_token_ids"][i]].logprob for i in range(1, 8)]
+    assert max(abs(x - y) for x, y in zip(la, lb)) < 0.25, (la, lb)

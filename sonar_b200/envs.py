@@ -45,6 +45,12 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # heap has a multicast mapping; 0 = one store per peer
     "SONAR_TP_MULTIMEM": _bool("SONAR_TP_MULTIMEM", True),
     "SONAR_CUDA_GRAPHS": _bool("SONAR_CUDA_GRAPHS", True),
+    # decode-graph capture: batch sizes to capture (comma list; default = built-in ladder) and whether the
+    # graphs share one memory pool.  Sharing saves memory but PyTorch only supports it when graphs replay
+    # in capture order; replaying in arbitrary order faulted on a mixture-of-experts model, so each graph
+    # gets its own pool by default.
+    "SONAR_GRAPH_SIZES": _str("SONAR_GRAPH_SIZES", None),
+    "SONAR_GRAPH_SHARED_POOL": _bool("SONAR_GRAPH_SHARED_POOL", False),
     "SONAR_SYMM_HEAP_MB": _int("SONAR_SYMM_HEAP_MB", 512),
     # server
     "SONAR_HOST": _str("SONAR_HOST", "0.0.0.0"),

@@ -641,9 +641,12 @@ class ModelRunner:
         tp = get_tp_context()
         sizes = sorted({b for b in [1, 2, 4, 8, 16, 24, 32, 40, 48, 56, 64] + list(range(80, 513, 16))
                         if b <= self.max_seqs} | {self.max_seqs})
+        if envs.SONAR_GRAPH_SIZES:
+            sizes = sorted({int(x) for x in envs.SONAR_GRAPH_SIZES.split(",") if x.strip() and int(x) <= self.max_seqs})
         ws = tp.world_size
         sizes = sorted({(b + ws - 1) // ws * ws for b in sizes})
         t0 = time.time()
+        share_pool = envs.SONAR_GRAPH_SHARED_POOL
         pool = None
         self.graph_buckets = []
         for b in reversed(sizes):
@@ -674,7 +677,7 @@ class ModelRunner:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, pool=pool):
                 out = run()
-            pool = g.pool()
+            pool = g.pool() if share_pool else None
             self.graph_launches[b] = cuda_ops.launch_count - before
             self.graphs[b] = (g, out)
             self.graph_buckets.append(b)

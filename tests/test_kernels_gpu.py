@@ -118,6 +118,9 @@ ATTN_CASES = [
     ([1, 200, 1, 64], [130, 200, 9, 1000], 8, 2, 128),     # mixed
     ([2, 3], [60, 70], 4, 2, 64),                          # head_dim 64, short multi-token (spec decode shape)
     ([1], [5000], 8, 2, 128),                              # long context, single sequence → split-KV
+    ([33, 7, 128], [33, 50, 400], 32, 4, 128),             # prefill, GQA 8 (Qwen3-30B-A3B head layout)
+    ([2, 1, 2, 600], [100, 50, 70, 600], 32, 4, 128),      # GQA 8: two-token decode rows (16 per item) + prefill
+    ([1] * 40, [513 + 7 * i for i in range(40)], 32, 4, 128),   # GQA 8 decode batch
 ]
 
 
@@ -389,3 +392,18 @@ def test_mla_cache_write(cu):
     ref.mla_cache_write(kv_c, rest, want, slots)
     cu.mla_cache_write(kv_c, rest, got, slots)
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("bucket,n_seqs", [(1, 1), (2, 2), (4, 3), (8, 8), (16, 11), (32, 32), (64, 50), (80, 80)])
+@pytest.mark.parametrize("hq,hk", [(32, 4), (32, 8)])
+def test_decode_attention_graph_bucket_geometry(cu, bucket, n_seqs, hq, hk):
+    """Decode steps replayed from a CUDA graph use a grid and a KV split count fixed by the padded batch size;
+    surplus slots exit on the device-side count.  Same numbers as the PyTorch restatement."""
+    ctx = [513 + (37 * i) % 255 for i in range(n_seqs)]
+    q, cache, meta = _make_attn_case([1] * n_seqs, ctx, hq, hk, 128, seed=bucket)
+    cu.build_attention_work(meta, None, hq // hk, hk, graph_bucket=bucket)
+    got = cu.paged_attention(q, cache, meta, 128 ** -0.5)
+    torch.cuda.synchronize()
+    want = ref.paged_attention(q.float(), cache.float(), meta.block_tables, meta.seq_lens, meta.query_start_loc,
+                               128 ** -0.5)
+    _close(got.view(-1, hq, 128), want, 2e-2, 2e-2)

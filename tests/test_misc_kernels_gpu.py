@@ -256,3 +256,50 @@ def test_indexer_logits_and_topk(cu):
         assert len(g) == min(k, n) and all(0 <= x < n for x in g)
         # bf16 tensor-core accumulation vs fp32: allow a couple of swaps at the selection boundary
         assert len(g ^ wv) <= 4, (i, sorted(g ^ wv))
+
+
+@pytest.mark.parametrize("t", [1, 8, 32, 256, 700])
+def test_fused_experts_many_experts_small_batches(cu, t):
+    """128 experts, top-8 (the Qwen3-30B-A3B router geometry): at decode batch sizes almost every routed
+    pair opens its own 128-row block."""
+    torch.manual_seed(60 + t)
+    e, k, h, inter = 128, 8, 512, 256
+    x = torch.randn(t, h, device=DEV, dtype=torch.bfloat16)
+    w13 = torch.randn(e, 2 * inter, h, device=DEV, dtype=torch.bfloat16) * 0.05
+    w2 = torch.randn(e, h, inter, device=DEV, dtype=torch.bfloat16) * 0.05
+    tw, ids = ref.topk_softmax(torch.randn(t, e, device=DEV), k, True)
+    want = ref.fused_experts(x.float(), w13.float(), w2.float(), tw, ids)
+    got = cu.fused_experts(x, w13, w2, tw, ids)
+    torch.cuda.synchronize()
+    cu.check_device_errors()
+    assert (got.float() - want).norm() / want.norm() < 0.03
+
+
+def test_fused_experts_graph_replay_with_new_routing(cu):
+    """Captured with degenerate routing (every token to the same experts, as a warm-up batch of identical
+    tokens does), replayed with spread-out routing: block counts differ, buffers are sized by the bound."""
+    torch.manual_seed(61)
+    t, e, k, h, inter = 64, 128, 8, 512, 256
+    x = torch.randn(t, h, device=DEV, dtype=torch.bfloat16)
+    w13 = torch.randn(e, 2 * inter, h, device=DEV, dtype=torch.bfloat16) * 0.05
+    w2 = torch.randn(e, h, inter, device=DEV, dtype=torch.bfloat16) * 0.05
+    logits = torch.zeros(t, e, device=DEV)
+    logits[:, :k] = 5.0
+    static_logits = logits.clone()
+
+    def run():
+        tw, ids = cu.topk_softmax(static_logits, k, True)
+        return cu.fused_experts(x, w13, w2, tw, ids)
+    for _ in range(2):
+        run()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        out = run()
+    static_logits.copy_(torch.randn(t, e, device=DEV))
+    g.replay()
+    torch.cuda.synchronize()
+    cu.check_device_errors()
+    tw, ids = ref.topk_softmax(static_logits, k, True)
+    want = ref.fused_experts(x.float(), w13.float(), w2.float(), tw, ids)
+    assert (out.float() - want).norm() / want.norm() < 0.03

@@ -9,7 +9,7 @@
 //    that kv head form one MMA row tile; the 4 warps take every 4th page with private 3-stage
 //    pipelines (≈96 KB in flight per CTA, 2 CTAs/SM) and merge their partial softmax states through
 //    shared memory.  Long contexts at small batch are split over gridDim.z, merged by attn_merge_kernel.
-//  * prefill kernel: one CTA per (sequence, kv head, 64-row query tile); rows are (query position, head
+//  * prefill kernel: one CTA per (sequence, kv head, 128-row query tile); rows are (query position, head
 //    in group) pairs, 16 per warp; the CTA streams 64-key tiles (4 pages) through a 2-stage pipeline
 //    shared by the 4 warps, causal limit per tile.
 //
@@ -403,9 +403,11 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict
 }
 
 // ------------------------------------------------------------------ prefill
-// work[2*i] = sequence, work[2*i+1] = query tile.  64 rows per CTA = 64/group query positions.
+// work[2*i] = sequence, work[2*i+1] = query tile.  128 rows per CTA (8 warps × 16) = 128/group query
+// positions: every K/V tile staged in shared memory serves twice the rows a 4-warp CTA would give it.
+constexpr int PF_ROWS = 128;
 template <typename T, int HD, bool KV8>
-__global__ void __launch_bounds__(128) attn_prefill_kernel(
+__global__ void __launch_bounds__(2 * PF_ROWS) attn_prefill_kernel(
     const T* __restrict__ q, long q_tok_stride, const void* __restrict__ cache_v, const int* __restrict__ block_tables,
     int bt_stride, const int* __restrict__ seq_lens, const int* __restrict__ qsl, const int* __restrict__ work,
     const int* __restrict__ n_work, T* __restrict__ out, long out_tok_stride, int hq, int hk, float scale_log2,
@@ -423,7 +425,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
   const int seq = work[2 * blockIdx.x], qt = work[2 * blockIdx.x + 1], kvh = blockIdx.y;
   const int ctx = seq_lens[seq], tok0 = qsl[seq], q_len = qsl[seq + 1] - tok0;
   const int group = hq / hk;
-  const int qpt = 64 / group;                     // query positions per CTA
+  const int qpt = PF_ROWS / group;                // query positions per CTA
   const int qp0 = qt * qpt;
   uint32_t qf[HD / 16][4];
   load_q_frags<T, HD>(qf, q, q_tok_stride, tok0, qp0, q_len, kvh, group, warp * 16, lane);
@@ -454,8 +456,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
   const long blk_stride = 2L * hk * PAGE * HD;
   const long v_off = (long)hk * PAGE * HD;
   auto issue = [&](int t) {
-    if (t < n_tiles) {
-      int p = p_begin + t * KT + warp;              // warp w loads page w of the tile
+    if (t < n_tiles && warp < KT) {
+      int p = p_begin + t * KT + warp;              // warp w (of the first KT) loads page w of the tile
       if (p < p_end) {
         int blk = bt[p];
         uint32_t sb = sbase + (t & 1) * STAGE + warp * 2 * SLOT;
@@ -477,7 +479,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
     if constexpr (KV8) {
       // each warp widens the page it loaded; the barrier below publishes all four
       __syncwarp();
-      if (p_begin + t * KT + warp < p_end) {
+      if (warp < KT && p_begin + t * KT + warp < p_end) {
         const uint8_t* raw = smem_raw + (t & 1) * STAGE + warp * 2 * SLOT;
         widen_page<T, HD>(raw, wide + warp * 2 * TILE, lane);
         widen_page<T, HD>(raw + SLOT, wide + warp * 2 * TILE + TILE, lane);
@@ -548,7 +550,7 @@ int launch_attention(const T* q, long q_tok_stride, const void* cache, const int
       attr_done = true;
     }
     dim3 grid(max_pre, hk);
-    kern<<<grid, 128, smem, s>>>(q, q_tok_stride, cache, bt, bt_stride, seq_lens, qsl, pre_work, n_pre, out,
+    kern<<<grid, 2 * PF_ROWS, smem, s>>>(q, q_tok_stride, cache, bt, bt_stride, seq_lens, qsl, pre_work, n_pre, out,
                                  out_tok_stride, hq, hk, scale_log2, window, v_scale);
   }
   return check_launch();

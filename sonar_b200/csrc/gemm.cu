@@ -643,6 +643,7 @@ int cached_tmap_public(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_
 }
 int num_sms_public() { return num_sms(); }
 bool g_pair_enabled = false;
+bool g_cluster_splitk_enabled = false;
 }  // namespace sonar
 
 using namespace sonar;
@@ -658,6 +659,33 @@ extern "C" int sonar_gemm_pair(const void* A, const void* B, void* C, const void
 // Large-M GEMMs run their whole waves of 256×256 tiles on CTA pairs (tcgen05 cta_group::2) and the partial
 // last wave on the one-CTA kernel with its split-K tail.
 SONAR_API void sonar_gemm_set_pair(int enable) { g_pair_enabled = enable != 0; }
+
+extern "C" int sonar_gemm_splitk_cluster(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                                         long lda, long ldb, long ldc, int dtype, int bn, int split, int* err,
+                                         cudaStream_t s);
+// Decode-sized GEMMs (M ≤ 256) whose tiles cannot fill the GPU split K over a cluster and reduce through
+// distributed shared memory instead of the global-memory fix-up.
+SONAR_API void sonar_gemm_set_cluster_splitk(int enable) { g_cluster_splitk_enabled = enable != 0; }
+
+// (bn, split) for the cluster kernel, or split = 0 when the shape is better served elsewhere
+static void pick_cluster_split(int M, int N, int K, int* bn_out, int* split_out) {
+  const int sms = num_sms();
+  const int num_m = (M + BM - 1) / BM, num_kb = (K + BK - 1) / BK;
+  double best = 1e30;
+  *split_out = 0;
+  const int bns[2] = {256, 128};
+  const double t_kb[2] = {0.44, 0.30};
+  for (int i = 0; i < 2; ++i) {
+    const int tiles = num_m * ((N + bns[i] - 1) / bns[i]);
+    for (int S = 8; S >= 2; S >>= 1) {
+      if (tiles * S > sms || num_kb / S < 2) continue;
+      const double cost = (double)((num_kb + S - 1) / S) * t_kb[i] + 3.0;
+      if (cost < best) { best = cost; *bn_out = bns[i]; *split_out = S; }
+      break;    // the largest split that fits is the best for this tile width
+    }
+  }
+}
+
 
 // C = A · B^T (+ bias).  in_dtype: bf16/f16 for A and B; out_dtype: same 16-bit type or fp32.
 // Requirements: K % 8 == 0 (16-byte row pitch), N % 8 == 0 (N % 4 for fp32 out), 16-byte aligned bases.
@@ -675,6 +703,11 @@ SONAR_API int sonar_gemm(const void* A, const void* B, void* C, const void* bias
   p.tp = 1; p.shard_rows = M;
   p.ws = ws; p.ws_flags = ws_flags; p.ws_ctas = ws_ctas;
   const int num_m1 = (M + BM - 1) / BM;
+  if (g_cluster_splitk_enabled && !force_bn && out_dtype == in_dtype && M <= 256) {
+    int cbn = 0, csplit = 0;
+    pick_cluster_split(M, N, K, &cbn, &csplit);
+    if (csplit >= 2) return sonar_gemm_splitk_cluster(A, B, C, bias, M, N, K, lda, ldb, ldc, in_dtype, cbn, csplit, err, s);
+  }
   if (g_pair_enabled && !force_bn && out_dtype == in_dtype && M >= 512 && N >= 512 && num_m1 % 2 == 0 &&
       (N % 256 == 0 || N > 2048)) {
     const int pairs = sonar_gemm_pair_resident();

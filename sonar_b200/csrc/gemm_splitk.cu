@@ -1,0 +1,275 @@
+// Small-M GEMM with split-K inside a thread-block cluster.
+//
+// Decode-sized GEMMs (M ≤ 256) have too few 128×BN output tiles to fill 148 SMs, so K is split: the
+// S CTAs of one cluster (S = 2, 4 or 8) each multiply one K slice of the SAME output tile with tcgen05
+// into their own TMEM accumulator.  Instead of parking fp32 partials in global memory and meeting on a
+// counter, every CTA writes its accumulator into its own shared memory (the operand ring is free by
+// then), the cluster synchronises once, and CTA r sums column slice r of all S accumulators through
+// distributed shared memory (ld.shared::cluster) and stores it.  One launch, no workspace, no spin.
+//
+//   C[M, N] = A[M, K] · B[N, K]^T (+ bias)      bf16 / fp16 in, same 16-bit type out
+//
+// grid = (S, tiles), cluster = (S, 1, 1); CTA (s, t) handles tile t, k-blocks [s·kbs, (s+1)·kbs).
+// Roles per CTA as in the other GEMM kernels: warp 0 TMA producer, warp 1 MMA issuer + TMEM owner,
+// warps 2-5 epilogue.  Every mbarrier wait is bounded; every path reaches both cluster barriers.
+#include "tcgen05.cuh"
+
+namespace sonar {
+int cached_tmap_public(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                       int eb);
+namespace {
+
+constexpr int BM = 128, BK = 64;
+constexpr int NUM_THREADS = 192;
+
+template <int BN> struct KCfg {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int RING = STAGES * STAGE_BYTES;                 // 192 KB
+  static constexpr int ACC_BYTES = BM * BN * 4;                     // fp32 accumulator parked in the ring
+  static constexpr int SMEM = RING + 1024 + 256;
+  static_assert(ACC_BYTES <= RING, "accumulator must fit in the operand ring");
+};
+
+struct SplitParams {
+  int M, N, K;
+  void* C; long ldc;
+  const void* bias;
+  int* err;
+  int num_m, kbs;     // 128-row blocks; k-blocks per slice
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_rank(uint32_t smem_addr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_addr), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+
+// accumulator layout in shared memory: row-major [128][BN] fp32, 16-byte chunks XOR-swizzled by row so
+// that the 32 lanes of a warp (32 different rows, same chunk index) hit different banks
+template <int BN>
+__device__ __forceinline__ uint32_t acc_off(int row, int chunk) {   // chunk = 4 floats
+  return (uint32_t)(row * BN * 4 + ((chunk ^ (row & 7)) << 4));
+}
+
+template <int BN, int S, typename OutT, int AB_FMT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                           const SplitParams p) {
+  using C = KCfg<BN>;
+  extern __shared__ uint8_t smem_dyn[];
+  const uint32_t smem0 = (tc::smem_u32(smem_dyn) + 1023u) & ~1023u;
+  uint8_t* smem_al = smem_dyn + (smem0 - tc::smem_u32(smem_dyn));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_al + C::RING);
+  const uint32_t bar0 = smem0 + C::RING;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (C::STAGES + s); };
+  const uint32_t tfull_bar = bar0 + 8u * (2 * C::STAGES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slice = (int)cluster_rank();            // == blockIdx.x
+  const int tile = blockIdx.y;
+  const int m_idx = tile % p.num_m, n_idx = tile / p.num_m;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int kb0 = min(num_kb, slice * p.kbs), kb1 = min(num_kb, kb0 + p.kbs);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) { tc::mbar_init(full_bar(s), 1); tc::mbar_init(empty_bar(s), 1); }
+    tc::mbar_init(tfull_bar, 1);
+    *abort_flag = 0;
+    tc::mbar_fence_init();
+  }
+  if (warp == 1) tc::tmem_alloc(tc::smem_u32(tmem_slot), BN);
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tc::tma_prefetch_desc(&tma_a);
+      tc::tma_prefetch_desc(&tma_b);
+      uint32_t it = 0;
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % C::STAGES;
+        const uint32_t ph = (it / C::STAGES) & 1;
+        if (!tc::mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.err, tc::SITE_EMPTY)) break;
+        tc::mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+        const uint32_t a_dst = smem0 + s * C::STAGE_BYTES;
+        tc::tma_load_2d(a_dst, &tma_a, full_bar(s), kb * BK, m_idx * BM);
+        tc::tma_load_2d(a_dst + C::A_BYTES, &tma_b, full_bar(s), kb * BK, n_idx * BN);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc::make_idesc_f16(BM, BN, AB_FMT);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % C::STAGES;
+        const uint32_t ph = (it / C::STAGES) & 1;
+        if (!tc::mbar_wait(full_bar(s), ph, abort_flag, p.err, tc::SITE_FULL)) { ok = false; break; }
+        tc::fence_after_sync();
+        const uint32_t a_addr = smem0 + s * C::STAGE_BYTES;
+        const uint64_t adesc = tc::make_smem_desc_sw128(a_addr);
+        const uint64_t bdesc = tc::make_smem_desc_sw128(a_addr + C::A_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k)
+          tc::mma_f16(tmem_base, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > kb0) | (k > 0));
+        tc::mma_commit(empty_bar(s));
+      }
+      if (ok) tc::mma_commit(tfull_bar);      // with no k-blocks at all this completes immediately
+    }
+  }
+  // ---- every thread: wait until the accumulator is final (and with it, all reads of the operand ring)
+  bool have = true;
+  if (warp >= 2) {
+    have = tc::mbar_wait(tfull_bar, 0, abort_flag, p.err, tc::SITE_TMEM_FULL);
+    tc::fence_after_sync();
+    // park this CTA's fp32 accumulator in its own shared memory (zeros for an empty k range)
+    const int lane_grp = warp & 3;
+    const int row = lane_grp * 32 + lane;
+    const uint32_t t_row = tmem_base + ((uint32_t)(lane_grp * 32) << 16);
+    const bool empty = kb0 >= kb1 || !have;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t v[32];
+      if (!empty) {
+        tc::tmem_ld32(t_row + c * 32, v);
+        tc::tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) v[e] = 0u;
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        *reinterpret_cast<uint4*>(smem_al + acc_off<BN>(row, c * 8 + q)) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    }
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                 // all S accumulators are parked and visible cluster-wide
+  if (warp >= 2 && *abort_flag == 0) {
+    // CTA `slice` owns columns [slice·BN/S, (slice+1)·BN/S): sum them over the S accumulators
+    constexpr int CW = BN / S;        // columns per CTA (16 … 128)
+    const int row = (warp - 2) * 32 + lane;
+    const int grow = m_idx * BM + row;
+    float acc[CW];
+#pragma unroll
+    for (int e = 0; e < CW; ++e) acc[e] = 0.f;
+#pragma unroll 1
+    for (int r = 0; r < S; ++r) {
+      const uint32_t base = map_rank(smem0, (uint32_t)r);
+#pragma unroll
+      for (int q = 0; q < CW / 4; ++q) {
+        const float4 v = ld_cluster_f4(base + acc_off<BN>(row, slice * (CW / 4) + q));
+        acc[4 * q] += v.x; acc[4 * q + 1] += v.y; acc[4 * q + 2] += v.z; acc[4 * q + 3] += v.w;
+      }
+    }
+    const int col0 = n_idx * BN + slice * CW;
+    if (grow < p.M) {
+      OutT* crow = reinterpret_cast<OutT*>(p.C) + (long)grow * p.ldc + col0;
+      const OutT* bias = p.bias ? reinterpret_cast<const OutT*>(p.bias) + col0 : nullptr;
+#pragma unroll
+      for (int g = 0; g < CW / 8; ++g) {
+        if (col0 + g * 8 + 8 <= p.N) {
+          float f[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = acc[g * 8 + i] + (bias ? to_f<OutT>(bias[g * 8 + i]) : 0.f);
+          *reinterpret_cast<uint4*>(crow + g * 8) = pack8<OutT>(f);
+        }
+      }
+    }
+  }
+  cluster_sync_all();                 // nobody leaves while a peer may still read its shared memory
+  if (warp == 1) {
+    __syncwarp();
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem_base, BN);
+  }
+}
+
+template <int BN, int S, typename OutT, int AB_FMT>
+int launch_split(const CUtensorMap& ta, const CUtensorMap& tb, const SplitParams& p, int tiles, cudaStream_t s) {
+  using C = KCfg<BN>;
+  auto kern = gemm_splitk_cluster_kernel<BN, S, OutT, AB_FMT>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
+      return check_launch();
+    attr_done = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(S, tiles, 1);
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = C::SMEM;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = S; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, p) != cudaSuccess) return check_launch();
+  return check_launch();
+}
+
+template <int BN, typename OutT, int AB_FMT>
+int launch_split_s(int S, const CUtensorMap& ta, const CUtensorMap& tb, const SplitParams& p, int tiles, cudaStream_t s) {
+  if (S == 2) return launch_split<BN, 2, OutT, AB_FMT>(ta, tb, p, tiles, s);
+  if (S == 4) return launch_split<BN, 4, OutT, AB_FMT>(ta, tb, p, tiles, s);
+  if (S == 8) return launch_split<BN, 8, OutT, AB_FMT>(ta, tb, p, tiles, s);
+  return SONAR_BAD_ARG;
+}
+
+}  // namespace
+}  // namespace sonar
+
+using namespace sonar;
+
+// C = A · B^T (+ bias) with K split over a cluster of `split` CTAs per 128×bn tile (split ∈ {2,4,8}, bn ∈ {128,256}).
+// Operand requirements as sonar_gemm; out dtype = in dtype (16 bit).
+SONAR_API int sonar_gemm_splitk_cluster(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                                        long lda, long ldb, long ldc, int dtype, int bn, int split, int* err,
+                                        cudaStream_t s) {
+  if (M <= 0 || N <= 0 || K <= 0) return SONAR_BAD_ARG;
+  if (K % 8 || lda % 8 || ldb % 8 || N % 8 || ldc % 8 || ((uintptr_t)C & 15)) return SONAR_BAD_ARG;
+  if (bn != 128 && bn != 256) return SONAR_BAD_ARG;
+  const int num_m = (M + BM - 1) / BM, num_n = (N + bn - 1) / bn;
+  const int tiles = num_m * num_n;
+  if (tiles > 65535) return SONAR_TOO_LARGE;
+  const int num_kb = (K + BK - 1) / BK;
+  CUtensorMap ta, tb;
+  int rc = cached_tmap_public(&ta, A, M, K, lda, BM, 2);
+  if (rc != SONAR_OK) return rc;
+  rc = cached_tmap_public(&tb, B, N, K, ldb, bn, 2);
+  if (rc != SONAR_OK) return rc;
+  SplitParams p{M, N, K, C, ldc, bias, err, num_m, (num_kb + split - 1) / split};
+  if (dtype == SONAR_BF16) {
+    if (bn == 256) return launch_split_s<256, __nv_bfloat16, 1>(split, ta, tb, p, tiles, s);
+    return launch_split_s<128, __nv_bfloat16, 1>(split, ta, tb, p, tiles, s);
+  }
+  if (dtype == SONAR_F16) {
+    if (bn == 256) return launch_split_s<256, __half, 0>(split, ta, tb, p, tiles, s);
+    return launch_split_s<128, __half, 0>(split, ta, tb, p, tiles, s);
+  }
+  return SONAR_BAD_ARG;
+}

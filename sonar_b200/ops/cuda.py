@@ -107,6 +107,10 @@ _idx_logits = _sig("sonar_indexer_logits", c_void_p, c_void_p, c_void_p, c_long,
 _idx_topk = _sig("sonar_indexer_topk", c_void_p, c_long, c_void_p, c_int, c_void_p, c_int, c_void_p)
 _gemm_pair = _sig("sonar_gemm_pair", c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long, c_long,
                   c_int, c_int, c_int, c_void_p, c_void_p)
+_gemm_splitk = _sig("sonar_gemm_splitk_cluster", c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_long, c_long,
+                    c_long, c_int, c_int, c_int, c_void_p, c_void_p)
+lib.sonar_gemm_set_cluster_splitk.argtypes = [c_int]
+lib.sonar_gemm_set_cluster_splitk.restype = None
 lib.sonar_gemm_pair_resident.restype = c_int
 lib.sonar_gemm_set_pair.argtypes = [c_int]
 lib.sonar_gemm_set_pair.restype = None
@@ -216,6 +220,7 @@ class _AttnBuffers:
         self.part_lse = None
 
 
+PREFILL_ROWS = 128      # query rows (positions × heads of one KV group) per prefill CTA; matches the kernel
 _attn_buffers: dict[int, _AttnBuffers] = {}
 MAX_SPLIT_CTAS = 1024
 
@@ -240,7 +245,7 @@ def build_attention_work(meta, runner=None, group: int | None = None, num_kv_hea
     is_dec = q_lens * group <= 16
     dec = np.nonzero(is_dec & (q_lens > 0))[0].astype(np.int32)
     pre_seqs = np.nonzero(~is_dec)[0]
-    qpt = 64 // group
+    qpt = PREFILL_ROWS // group
     n_tiles = (q_lens[pre_seqs] + qpt - 1) // qpt
     n_pre = int(n_tiles.sum())
     n_dec = len(dec)
@@ -455,6 +460,24 @@ def set_gemm_pair(enable: bool) -> None:
 
 
 set_gemm_pair(os.environ.get("SONAR_GEMM_PAIR", "1") == "1")
+
+
+def set_gemm_cluster_splitk(enable: bool) -> None:
+    """Route decode-sized GEMMs (M ≤ 256, too few tiles for the GPU) to the cluster split-K kernel."""
+    lib.sonar_gemm_set_cluster_splitk(int(enable))
+
+
+set_gemm_cluster_splitk(os.environ.get("SONAR_GEMM_CLUSTER_SPLITK", "0") == "1")
+
+
+def gemm_splitk_cluster(x, w, out, bn, split, bias=None):
+    """The cluster split-K kernel alone: out = x @ w.T (+ bias), K split over ``split`` CTAs per 128×bn tile."""
+    m, k = x.shape
+    n = w.shape[0]
+    _check(_gemm_splitk(x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(bias), m, n, k, x.stride(0), w.stride(0),
+                        out.stride(0), _DT[x.dtype], bn, split, error_word(x.device).data_ptr(), _stream()),
+           "gemm_splitk_cluster")
+    return out
 
 
 def gemm_pair_tiles(x, w, out, num_tiles, bias=None, pairs=None):

@@ -407,3 +407,27 @@ def test_decode_attention_graph_bucket_geometry(cu, bucket, n_seqs, hq, hk):
     want = ref.paged_attention(q.float(), cache.float(), meta.block_tables, meta.seq_lens, meta.query_start_loc,
                                128 ** -0.5)
     _close(got.view(-1, hq, 128), want, 2e-2, 2e-2)
+
+
+def test_bounded_wait_reports_instead_of_hanging(cu):
+    """Failure detection on the device: a kernel waiting for a peer flag that nothing ever sets gives up after
+    its time limit, records the wait site in the device error word and returns — the context stays usable
+    and the host sees the error.  (A flag word that stays 0 stands in for a peer that died between steps.)"""
+    import time
+    flags = torch.zeros(4, dtype=torch.int32, device=DEV)         # 2 row blocks × tp 2, never published
+    err = cu.error_word(torch.device(DEV))
+    torch.cuda.synchronize()
+    t0 = time.time()
+    cu.tp_wait(flags, 2, 128, 256, 7, None, err)
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    assert 1.0 < waited < 10.0, waited                             # the 2 s limit, not forever
+    with pytest.raises(RuntimeError, match="peer flag"):
+        cu.check_device_errors()
+    cu.check_device_errors()                                       # the word was cleared: no stale error
+    # the context is still usable and a published flag lets the same kernel through immediately
+    flags.fill_(7)
+    cu.tp_wait(flags, 2, 128, 256, 7, None, err)
+    torch.cuda.synchronize()
+    cu.check_device_errors()
+    assert float(torch.ones(4, device=DEV).sum()) == 4.0

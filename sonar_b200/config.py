@@ -285,6 +285,33 @@ class SpeculativeConfig:
 
 
 @dataclass
+class KVTransferConfig:
+    """Which KV connector moves cache blocks in and out of this instance, and in which role.
+
+    Parity: ``aphrodite/config/kv_transfer.py:26`` (``--kv-transfer-config`` JSON)."""
+    kv_connector: str | None = None
+    kv_role: str | None = None                 # kv_producer | kv_consumer | kv_both
+    engine_id: str | None = None
+    kv_rank: int | None = None
+    kv_parallel_size: int = 1
+    kv_ip: str = "127.0.0.1"
+    kv_port: int = 14579
+    kv_buffer_device: str = "cuda"
+    kv_connector_extra_config: dict = field(default_factory=dict)
+    kv_connector_module_path: str | None = None
+
+    def __post_init__(self) -> None:
+        if self.kv_connector is not None and self.kv_role not in ("kv_producer", "kv_consumer", "kv_both"):
+            raise ValueError("kv_role must be kv_producer, kv_consumer or kv_both when a kv_connector is set")
+        if self.engine_id is None:
+            self.engine_id = f"engine-{os.getpid()}"
+
+    @property
+    def enabled(self) -> bool:
+        return self.kv_connector is not None
+
+
+@dataclass
 class LoRAConfig:
     enable_lora: bool = False
     max_loras: int = 4
@@ -314,6 +341,7 @@ class EngineConfig:
     speculative: SpeculativeConfig = field(default_factory=SpeculativeConfig)
     observability: ObservabilityConfig = field(default_factory=ObservabilityConfig)
     lora: LoRAConfig = field(default_factory=LoRAConfig)
+    kv_transfer: KVTransferConfig = field(default_factory=KVTransferConfig)
     enable_sleep_mode: bool = False
     enforce_eager: bool = False
     device: str = "auto"               # auto | cuda | cpu
@@ -377,6 +405,7 @@ class EngineArgs:
     num_speculative_tokens: int = 0
     kv_offload_cpu_gb: float = 0.0
     kv_offload_cpu_blocks: int = 0
+    kv_transfer_config: dict | None = None     # fields of KVTransferConfig (a JSON object on the command line)
     # LoRA
     enable_lora: bool = False
     max_loras: int = 4
@@ -444,8 +473,12 @@ class EngineArgs:
                                   kv_events_replay_endpoint=self.kv_events_replay_endpoint)
         lora = LoRAConfig(enable_lora=self.enable_lora or bool(self.lora_modules), max_loras=self.max_loras,
                           max_lora_rank=self.max_lora_rank, lora_modules=dict(self.lora_modules or {}))
+        kvt = self.kv_transfer_config
+        if isinstance(kvt, str):
+            kvt = json.loads(kvt)
+        kv_transfer = kvt if isinstance(kvt, KVTransferConfig) else KVTransferConfig(**(kvt or {}))
         return EngineConfig(model=model, cache=cache, parallel=parallel, scheduler=sched,
-                            speculative=spec, observability=obs, lora=lora,
+                            speculative=spec, observability=obs, lora=lora, kv_transfer=kv_transfer,
                             enable_sleep_mode=self.enable_sleep_mode,
                             enforce_eager=self.enforce_eager, device=device)
 
@@ -458,7 +491,7 @@ class EngineArgs:
                 continue  # positional / --model handled by the caller
             if f.type in ("bool", bool):
                 parser.add_argument(flag, action=argparse.BooleanOptionalAction, default=f.default)
-            elif f.name in ("hf_overrides", "lora_modules"):
+            elif f.name in ("hf_overrides", "lora_modules", "kv_transfer_config"):
                 parser.add_argument(flag, type=json.loads, default=None)
             else:
                 base = str(f.type).replace(" | None", "")

@@ -66,7 +66,7 @@ def get_kv_cache_config(spec: KVCacheSpec, num_layers: int, available_bytes: int
 class KVCacheManager:
     def __init__(self, num_blocks: int, block_size: int, enable_caching: bool = True,
                  sliding_window: int | None = None, collect_events: bool = False,
-                 watermark: float = 0.0, cpu_offload_blocks: int = 0) -> None:
+                 watermark: float = 0.0, cpu_offload_blocks: int = 0, connector=None) -> None:
         self.block_size = block_size
         self.enable_caching = enable_caching
         self.sliding_window = sliding_window
@@ -77,6 +77,8 @@ class KVCacheManager:
         self.prefix_queries = 0
         self.prefix_hits = 0
         self.cpu_tier_hits = 0
+        self.connector = connector if enable_caching else None    # scheduler half of a KV connector, or None
+        self.connector_hits = 0
         self.offload = None
         if cpu_offload_blocks > 0 and enable_caching:
             from sonar_b200.core.kv_offload import CPUOffloadTier
@@ -125,6 +127,25 @@ class KVCacheManager:
                 self.pool.free_blocks(list(hit) + fresh)
                 hit.extend(fresh)
                 self.cpu_tier_hits += len(more)
+        if self.connector is not None and self.sliding_window is None and len(hit) < max_blocks:
+            # then in the external medium behind the KV connector, the same way: fresh GPU blocks, registered
+            # under their hashes, filled by the workers at the start of the step that first reads them
+            more = []
+            for h in request.block_hashes[len(hit):max_blocks]:
+                if not self.connector.lookup(h):
+                    break
+                more.append(h)
+            more = more[: max(0, self.pool.get_num_free_blocks() - self.watermark_blocks - 1)]
+            if more:
+                self.pool.touch(b for b in hit if b != NULL_BLOCK)
+                fresh = self.pool.get_new_blocks(len(more))
+                for b, h in zip(fresh, more):
+                    self.pool.block_hash[b] = h
+                    self.pool.hash_to_block.setdefault(h, b)
+                    self.connector.plan_load(h, b)
+                self.pool.free_blocks(list(hit) + fresh)
+                hit.extend(fresh)
+                self.connector_hits += len(more)
         if self.sliding_window is not None and hit:
             # only the blocks overlapping the window of the first new token matter
             first_needed = max(0, (len(hit) * self.block_size - self.sliding_window + 1)) // self.block_size
@@ -184,6 +205,10 @@ class KVCacheManager:
         if num_full > done:
             self.pool.cache_full_blocks(blocks, request.block_hashes, done, num_full,
                                         request.all_token_ids, self.block_size)
+            if self.connector is not None:
+                for i in range(done, num_full):       # full after the coming step: saved once it has run
+                    if blocks[i] != NULL_BLOCK:
+                        self.connector.plan_save(request.block_hashes[i], blocks[i])
             self.num_cached_blocks[rid] = num_full
 
     def cache_blocks(self, request: Request, num_computed_tokens: int) -> None:
@@ -214,6 +239,8 @@ class KVCacheManager:
             self.prefix_queries = self.prefix_hits = 0
             if self.offload is not None:
                 self.offload.clear()
+            if self.connector is not None:
+                self.connector.reset()
         return ok
 
     def get_num_common_prefix_blocks(self, request_id: str, num_running: int) -> int:

@@ -69,6 +69,8 @@ class SchedulerOutput:
     # CPU tier of the prefix cache: block copies to run before the forward pass, stores first
     kv_stores: list[tuple[int, int]] = field(default_factory=list)    # (gpu block, cpu slot)
     kv_loads: list[tuple[int, int]] = field(default_factory=list)     # (cpu slot, gpu block)
+    kv_ext_saves: list[tuple[str, int]] = field(default_factory=list)  # KV connector: (key, gpu block) after the step
+    kv_ext_loads: list[tuple[str, int]] = field(default_factory=list)  # KV connector: (key, gpu block) before it
 
 
 @dataclass
@@ -159,7 +161,7 @@ class Scheduler:
     def __init__(self, sched_cfg: SchedulerConfig, cache_cfg: CacheConfig, num_blocks: int,
                  spec_cfg: SpeculativeConfig | None = None, sliding_window: int | None = None,
                  log_stats: bool = False, collect_kv_events: bool = False,
-                 structured_output_manager=None, cpu_offload_blocks: int = 0) -> None:
+                 structured_output_manager=None, cpu_offload_blocks: int = 0, kv_connector=None) -> None:
         self.cfg = sched_cfg
         self.structured = structured_output_manager
         self.cache_cfg = cache_cfg
@@ -168,7 +170,8 @@ class Scheduler:
         self.num_spec_tokens = spec_cfg.num_speculative_tokens if spec_cfg and spec_cfg.method else 0
         self.kv = KVCacheManager(num_blocks, cache_cfg.block_size, cache_cfg.enable_prefix_caching,
                                  sliding_window=sliding_window, collect_events=collect_kv_events,
-                                 watermark=sched_cfg.watermark, cpu_offload_blocks=cpu_offload_blocks)
+                                 watermark=sched_cfg.watermark, cpu_offload_blocks=cpu_offload_blocks,
+                                 connector=kv_connector)
         self.block_hasher = (make_block_hasher(cache_cfg.block_size, cache_cfg.prefix_caching_hash_algo)
                              if cache_cfg.enable_prefix_caching else None)
         self.requests: dict[str, Request] = {}
@@ -357,6 +360,8 @@ class Scheduler:
                 gram.append(req)
         if self.kv.offload is not None:
             out.kv_stores, out.kv_loads = self.kv.offload.take_transfers()
+        if self.kv.connector is not None:
+            out.kv_ext_saves, out.kv_ext_loads = self.kv.connector.take_plan()
         if gram:
             out.grammar_req_ids = [r.request_id for r in gram]
             out.grammar_bitmask = self.structured.bitmask([r.grammar for r in gram])

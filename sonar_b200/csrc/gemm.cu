@@ -663,6 +663,11 @@ SONAR_API void sonar_gemm_set_pair(int enable) { g_pair_enabled = enable != 0; }
 extern "C" int sonar_gemm_splitk_cluster(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
                                          long lda, long ldb, long ldc, int dtype, int bn, int split, int* err,
                                          cudaStream_t s);
+extern "C" int sonar_gemm_splitk_cluster_tp(const void* A, const void* B, void* C, int M, int N, int K, long lda,
+                                            long ldb, long ldc, const int* gather_flags, int tp, int shard_rows,
+                                            int seq, const int* seq_base, int m_rot, void* const* dst_ptrs,
+                                            int* local_done, int* const* flag_ptrs, int bn, int split, int* err,
+                                            cudaStream_t s);
 // Decode-sized GEMMs (M ≤ 256) whose tiles cannot fill the GPU split K over a cluster and reduce through
 // distributed shared memory instead of the global-memory fix-up.
 SONAR_API void sonar_gemm_set_cluster_splitk(int enable) { g_cluster_splitk_enabled = enable != 0; }
@@ -751,6 +756,13 @@ SONAR_API int sonar_gemm_tp(const void* A, const void* B, void* C, int M, int N,
   p.dst_ptrs = dst_ptrs; p.local_done = local_done; p.flag_ptrs = flag_ptrs;
   p.ws = ws; p.ws_flags = ws_flags; p.ws_ctas = ws_ctas;
   const int num_m1 = (M + BM - 1) / BM;
+  if (g_cluster_splitk_enabled && !force_bn && M <= 256) {
+    int cbn = 0, csplit = 0;
+    pick_cluster_split(M, N, K, &cbn, &csplit);
+    if (csplit >= 2)
+      return sonar_gemm_splitk_cluster_tp(A, B, C, M, N, K, lda, ldb, ldc, gather_flags, tp, shard_rows, seq, seq_base,
+                                          p.m_rot, dst_ptrs, local_done, flag_ptrs, cbn, csplit, err, s);
+  }
   if (g_pair_enabled && !force_bn && M >= 512 && N >= 512 && num_m1 % 2 == 0 && p.m_rot % 2 == 0 &&
       (N % 256 == 0 || N > 2048)) {
     // whole waves on CTA pairs, the partial last wave on the one-CTA kernel (same tile order, same counters)

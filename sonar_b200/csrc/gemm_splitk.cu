@@ -39,7 +39,15 @@ struct SplitParams {
   const void* bias;
   int* err;
   int num_m, kbs;     // 128-row blocks; k-blocks per slice
+  // tensor-parallel hooks (protocol of the other GEMM kernels)
+  const int* gather_flags;  // [num_m * tp] arrival flags of the all-gathered A rows, or null
+  int tp, shard_rows, seq, m_rot;
+  const int* seq_base;
+  void* const* dst_ptrs;    // [tp] partial-buffer bases: scatter epilogue, or null
+  int* local_done;          // [tp] arrival counters, zero between launches
+  int* const* flag_ptrs;    // [tp] remote flag words
 };
+constexpr int MAX_TP = 8;
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -88,9 +96,10 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slice = (int)cluster_rank();            // == blockIdx.x
   const int tile = blockIdx.y;
-  const int m_idx = tile % p.num_m, n_idx = tile / p.num_m;
+  const int m_idx = (tile % p.num_m + p.m_rot) % p.num_m, n_idx = tile / p.num_m;
   const int num_kb = (p.K + BK - 1) / BK;
   const int kb0 = min(num_kb, slice * p.kbs), kb1 = min(num_kb, kb0 + p.kbs);
+  const int seq_now = p.seq + (p.seq_base ? *p.seq_base : 0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { tc::mbar_init(full_bar(s), 1); tc::mbar_init(empty_bar(s), 1); }
@@ -109,7 +118,35 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
       tc::tma_prefetch_desc(&tma_a);
       tc::tma_prefetch_desc(&tma_b);
       uint32_t it = 0;
-      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+      bool ok = true;
+      if (p.gather_flags != nullptr && kb0 < kb1) {
+        // bounded wait until every source rank of this row block has published this launch's number
+        const int r_lo = m_idx * BM, r_hi = min(p.M, r_lo + BM) - 1;
+        for (int src = r_lo / p.shard_rows; src <= r_hi / p.shard_rows && ok; ++src) {
+          const int* flag = p.gather_flags + m_idx * p.tp + src;
+          auto arrived = [&]() {
+            int v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+            return (v - seq_now) >= 0;
+          };
+          if (arrived()) continue;
+          const uint64_t t0 = globaltimer_ns();
+          uint32_t spins = 0;
+          while (!arrived()) {
+            if ((++spins & 63u) == 0) {
+              if (*abort_flag) { ok = false; break; }
+              if (globaltimer_ns() - t0 > tc::WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                if (p.err) atomicCAS(p.err, 0, tc::SITE_FLAG | (blockIdx.y << 8));
+                ok = false;
+                break;
+              }
+            }
+          }
+        }
+        asm volatile("fence.proxy.async;" ::: "memory");
+      }
+      for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
         const int s = it % C::STAGES;
         const uint32_t ph = (it / C::STAGES) & 1;
         if (!tc::mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.err, tc::SITE_EMPTY)) break;
@@ -187,7 +224,13 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
     }
     const int col0 = n_idx * BN + slice * CW;
     if (grow < p.M) {
-      OutT* crow = reinterpret_cast<OutT*>(p.C) + (long)grow * p.ldc + col0;
+      OutT* crow;
+      if (p.dst_ptrs != nullptr) {
+        const int d = grow / p.shard_rows;       // the row's owner; its partial buffer may be on another GPU
+        crow = reinterpret_cast<OutT*>(p.dst_ptrs[d]) + (long)(grow - d * p.shard_rows) * p.ldc + col0;
+      } else {
+        crow = reinterpret_cast<OutT*>(p.C) + (long)grow * p.ldc + col0;
+      }
       const OutT* bias = p.bias ? reinterpret_cast<const OutT*>(p.bias) + col0 : nullptr;
 #pragma unroll
       for (int g = 0; g < CW / 8; ++g) {
@@ -196,6 +239,27 @@ gemm_splitk_cluster_kernel(const __grid_constant__ CUtensorMap tma_a, const __gr
 #pragma unroll
           for (int i = 0; i < 8; ++i) f[i] = acc[g * 8 + i] + (bias ? to_f<OutT>(bias[g * 8 + i]) : 0.f);
           *reinterpret_cast<uint4*>(crow + g * 8) = pack8<OutT>(f);
+        }
+      }
+    }
+    if (p.dst_ptrs != nullptr) {
+      // publish: the warp barrier orders every lane's row stores before lane 0's release-atomic; every
+      // epilogue warp of every CTA whose tile touches destination d adds one to d's counter, and the arrival
+      // completing d's share (4 warps × S slices × column tiles × its row blocks) sends the flag with a
+      // system-scope release, cumulative over the stores it learned of through the counter
+      __syncwarp();
+      if (lane == 0) {
+        const int r_lo = m_idx * BM, r_hi = min(p.M, r_lo + BM) - 1;
+        const int num_n = (p.N + BN - 1) / BN;
+        for (int d = r_lo / p.shard_rows; d <= r_hi / p.shard_rows; ++d) {
+          const int d_lo = d * p.shard_rows, d_hi = min(p.M, d_lo + p.shard_rows) - 1;
+          const int expected = 4 * S * num_n * (d_hi / BM - d_lo / BM + 1);
+          int prev;
+          asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(prev) : "l"(p.local_done + d) : "memory");
+          if (prev + 1 == expected) {
+            p.local_done[d] = 0;
+            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.flag_ptrs[d]), "r"(seq_now) : "memory");
+          }
         }
       }
     }
@@ -262,7 +326,10 @@ SONAR_API int sonar_gemm_splitk_cluster(const void* A, const void* B, void* C, c
   if (rc != SONAR_OK) return rc;
   rc = cached_tmap_public(&tb, B, N, K, ldb, bn, 2);
   if (rc != SONAR_OK) return rc;
-  SplitParams p{M, N, K, C, ldc, bias, err, num_m, (num_kb + split - 1) / split};
+  SplitParams p{};
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.bias = bias; p.err = err;
+  p.num_m = num_m; p.kbs = (num_kb + split - 1) / split;
+  p.tp = 1; p.shard_rows = M;
   if (dtype == SONAR_BF16) {
     if (bn == 256) return launch_split_s<256, __nv_bfloat16, 1>(split, ta, tb, p, tiles, s);
     return launch_split_s<128, __nv_bfloat16, 1>(split, ta, tb, p, tiles, s);
@@ -272,4 +339,36 @@ SONAR_API int sonar_gemm_splitk_cluster(const void* A, const void* B, void* C, c
     return launch_split_s<128, __half, 0>(split, ta, tb, p, tiles, s);
   }
   return SONAR_BAD_ARG;
+}
+
+// Tensor-parallel form (bf16) with the hooks of sonar_gemm_tp: gather_flags != null waits per row block for
+// the all-gathered A rows; dst_ptrs != null stores every row into its owner's partial buffer (local or a
+// peer's) and publishes completion per destination.  m_rot rotates the row-block order.
+SONAR_API int sonar_gemm_splitk_cluster_tp(const void* A, const void* B, void* C, int M, int N, int K, long lda,
+                                           long ldb, long ldc, const int* gather_flags, int tp, int shard_rows,
+                                           int seq, const int* seq_base, int m_rot, void* const* dst_ptrs,
+                                           int* local_done, int* const* flag_ptrs, int bn, int split, int* err,
+                                           cudaStream_t s) {
+  if (M <= 0 || N <= 0 || K <= 0) return SONAR_BAD_ARG;
+  if (K % 8 || lda % 8 || ldb % 8 || N % 8 || ldc % 8) return SONAR_BAD_ARG;
+  if (bn != 128 && bn != 256) return SONAR_BAD_ARG;
+  if (tp < 1 || tp > MAX_TP || shard_rows <= 0 || (long)tp * shard_rows < M) return SONAR_BAD_ARG;
+  if (dst_ptrs != nullptr && (!local_done || !flag_ptrs)) return SONAR_BAD_ARG;
+  const int num_m = (M + BM - 1) / BM, num_n = (N + bn - 1) / bn;
+  const int tiles = num_m * num_n;
+  if (tiles > 65535) return SONAR_TOO_LARGE;
+  const int num_kb = (K + BK - 1) / BK;
+  CUtensorMap ta, tb;
+  int rc = cached_tmap_public(&ta, A, M, K, lda, BM, 2);
+  if (rc != SONAR_OK) return rc;
+  rc = cached_tmap_public(&tb, B, N, K, ldb, bn, 2);
+  if (rc != SONAR_OK) return rc;
+  SplitParams p{};
+  p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.err = err;
+  p.num_m = num_m; p.kbs = (num_kb + split - 1) / split;
+  p.gather_flags = gather_flags; p.tp = tp; p.shard_rows = shard_rows; p.seq = seq; p.seq_base = seq_base;
+  p.m_rot = m_rot % num_m;
+  p.dst_ptrs = dst_ptrs; p.local_done = local_done; p.flag_ptrs = flag_ptrs;
+  if (bn == 256) return launch_split_s<256, __nv_bfloat16, 1>(split, ta, tb, p, tiles, s);
+  return launch_split_s<128, __nv_bfloat16, 1>(split, ta, tb, p, tiles, s);
 }

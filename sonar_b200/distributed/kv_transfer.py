@@ -1,0 +1,287 @@
+"""KV connectors: move KV-cache blocks between engine instances (disaggregated prefill / decode, shared
+prefix stores) through an external medium.
+
+Design.  The unit of exchange is a *full KV block*, named by the same chained content hash the prefix
+cache uses (``core/block_pool.py``), so a connector is simply one more tier behind the GPU prefix cache
+and the CPU tier: a request's prefix match continues into the connector, matched blocks get fresh GPU
+blocks and are filled before the step that first reads them, and blocks that become full are handed to
+the connector after the step that computed them.  No per-request handshake is needed: a prefill instance
+(``kv_role="kv_producer"``) and a decode instance (``"kv_consumer"``) that run the same model derive the
+same hashes from the same tokens.
+
+A connector has two halves that live in different processes:
+
+* the **scheduler half** (engine core) answers ``lookup(hash)`` and collects the step's plan —
+  ``saves [(key, gpu_block)]`` and ``loads [(key, gpu_block)]`` — which travels in the ``SchedulerOutput``;
+* the **worker half** (every rank) executes the plan on its own shard of the cache: ``load`` before the
+  forward pass, ``save`` after it.
+
+Built-in connectors: ``SharedStorageConnector`` (one file per block and rank in a shared directory, written
+atomically by the native file IO), ``DecodeBenchConnector`` (every prefix "matches" and is filled with a
+constant: decode-only benchmarking without a prefill instance), ``MultiConnector`` (several connectors in
+priority order).  Others register by name (``register_connector``) or through ``kv_connector_module_path``.
+
+Parity: ``aphrodite/distributed/kv_transfer/kv_connector/v1/base.py:169`` (scheduler-side and worker-side
+roles), ``factory.py:31`` (registry), ``example_connector.py`` (shared-storage reference connector),
+``decode_bench_connector.py``, ``multi_connector.py``; config ``aphrodite/config/kv_transfer.py:26``.
+"""
+from __future__ import annotations
+
+import importlib
+import os
+from collections import OrderedDict
+from typing import Any
+
+import torch
+
+from sonar_b200.logger import init_logger
+
+logger = init_logger(__name__)
+
+_REGISTRY: dict[str, tuple[str, str]] = {}
+
+
+def register_connector(name: str, module: str, cls: str) -> None:
+    if name in _REGISTRY and _REGISTRY[name] != (module, cls):
+        raise ValueError(f"KV connector {name!r} is already registered")
+    _REGISTRY[name] = (module, cls)
+
+
+def create_connector(cfg, half: str, **kw) -> "KVConnector":
+    """``cfg``: a ``KVTransferConfig``; ``half``: "scheduler" or "worker"."""
+    name = cfg.kv_connector
+    if cfg.kv_connector_module_path:
+        mod = importlib.import_module(cfg.kv_connector_module_path)
+        klass = getattr(mod, name)
+    else:
+        if name not in _REGISTRY:
+            raise ValueError(f"unknown KV connector {name!r}; known: {sorted(_REGISTRY)}")
+        mod_name, cls_name = _REGISTRY[name]
+        klass = getattr(importlib.import_module(mod_name), cls_name)
+    return klass(cfg, half, **kw)
+
+
+class KVConnector:
+    """Both halves of a connector; ``half`` says which one this object plays."""
+
+    def __init__(self, cfg, half: str, rank: int = 0, world_size: int = 1) -> None:
+        assert half in ("scheduler", "worker")
+        self.cfg, self.half = cfg, half
+        self.rank, self.world_size = rank, world_size
+        self.extra: dict[str, Any] = dict(cfg.kv_connector_extra_config or {})
+        self.is_producer = cfg.kv_role in ("kv_producer", "kv_both")
+        self.is_consumer = cfg.kv_role in ("kv_consumer", "kv_both")
+        self._saves: list[tuple[str, int]] = []
+        self._loads: list[tuple[str, int]] = []
+        self._planned: OrderedDict[bytes, None] = OrderedDict()     # hashes already handed out for saving
+        self.stats = {"lookups": 0, "hits": 0, "saved_blocks": 0, "loaded_blocks": 0}
+
+    # ---- scheduler half ---------------------------------------------------------------------------
+    @staticmethod
+    def key(block_hash: bytes) -> str:
+        return block_hash.hex()
+
+    def lookup(self, block_hash: bytes) -> bool:
+        """Is this block available from the medium?  Called while matching a new request's prefix."""
+        self.stats["lookups"] += 1
+        if not self.is_consumer:
+            return False
+        hit = self._contains(block_hash)
+        self.stats["hits"] += int(hit)
+        return hit
+
+    def plan_load(self, block_hash: bytes, gpu_block: int) -> None:
+        self._loads.append((self.key(block_hash), gpu_block))
+
+    def plan_save(self, block_hash: bytes, gpu_block: int) -> None:
+        """A block becomes full in the coming step."""
+        if not self.is_producer or block_hash in self._planned:
+            return
+        self._planned[block_hash] = None
+        if len(self._planned) > 1 << 16:
+            self._planned.popitem(last=False)
+        if self._contains(block_hash):
+            return
+        self._saves.append((self.key(block_hash), gpu_block))
+
+    def take_plan(self) -> tuple[list[tuple[str, int]], list[tuple[str, int]]]:
+        out = (self._saves, self._loads)
+        self._saves, self._loads = [], []
+        return out
+
+    def reset(self) -> None:
+        self._planned.clear()
+
+    def _contains(self, block_hash: bytes) -> bool:
+        raise NotImplementedError
+
+    # ---- worker half ------------------------------------------------------------------------------
+    def bind(self, kv_caches: list[torch.Tensor]) -> None:
+        """The per-layer paged caches ``[num_blocks, …]`` of this rank."""
+        self.kv_caches = kv_caches
+        self.block_bytes = [c[0].numel() * c.element_size() for c in kv_caches]
+
+    def load(self, pairs: list[tuple[str, int]]) -> None:
+        raise NotImplementedError
+
+    def save(self, pairs: list[tuple[str, int]]) -> None:
+        raise NotImplementedError
+
+    def shutdown(self) -> None:
+        pass
+
+    # helpers for the worker half: one block of every layer ↔ one flat host buffer
+    def _gather_block(self, gpu_block: int) -> torch.Tensor:
+        parts = [c[gpu_block].reshape(-1).view(torch.uint8) for c in self.kv_caches]
+        return torch.cat(parts).to("cpu")
+
+    def _scatter_block(self, flat: torch.Tensor, gpu_block: int) -> None:
+        off = 0
+        dev = self.kv_caches[0].device
+        flat = flat.to(dev, non_blocking=False)
+        for c, nb in zip(self.kv_caches, self.block_bytes):
+            c[gpu_block].reshape(-1).view(torch.uint8).copy_(flat[off:off + nb])
+            off += nb
+
+
+class SharedStorageConnector(KVConnector):
+    """Blocks as files ``<dir>/<hh>/<hash>.r<rank>of<world>.kv`` in a directory every instance can reach.
+
+    A block counts as present once every rank's file exists; files appear atomically (written under a
+    temporary name and renamed).  Extra config: ``shared_storage_path`` (required), ``io_threads``."""
+
+    def __init__(self, cfg, half: str, rank: int = 0, world_size: int = 1) -> None:
+        super().__init__(cfg, half, rank, world_size)
+        self.root = self.extra.get("shared_storage_path") or self.extra.get("path")
+        if not self.root:
+            raise ValueError("SharedStorageConnector needs kv_connector_extra_config['shared_storage_path']")
+        os.makedirs(self.root, exist_ok=True)
+        self.io_threads = int(self.extra.get("io_threads", 4))
+        self.kv_world = int(self.extra.get("kv_world_size", world_size))
+
+    def _path(self, key: str, rank: int, world: int) -> str:
+        return os.path.join(self.root, key[:2], f"{key}.r{rank}of{world}.kv")
+
+    def _contains(self, block_hash: bytes) -> bool:
+        key = self.key(block_hash)
+        return all(os.path.exists(self._path(key, r, self.kv_world)) for r in range(self.kv_world))
+
+    def save(self, pairs: list[tuple[str, int]]) -> None:
+        from sonar_b200.utils import fs_io
+        for key, blk in pairs:
+            path = self._path(key, self.rank, self.world_size)
+            if os.path.exists(path):
+                continue
+            os.makedirs(os.path.dirname(path), exist_ok=True)
+            fs_io.write_file(path, self._gather_block(blk), threads=self.io_threads)
+            self.stats["saved_blocks"] += 1
+
+    def load(self, pairs: list[tuple[str, int]]) -> None:
+        from sonar_b200.utils import fs_io
+        total = sum(self.block_bytes)
+        for key, blk in pairs:
+            buf = torch.empty(total, dtype=torch.uint8, pin_memory=self.kv_caches[0].is_cuda)
+            fs_io.read_file_into(self._path(key, self.rank, self.world_size), buf, threads=self.io_threads)
+            self._scatter_block(buf, blk)
+            self.stats["loaded_blocks"] += 1
+
+
+class DecodeBenchConnector(KVConnector):
+    """Every block of every prompt "matches": the cache is filled with a constant instead of being computed,
+    so a decode instance can be measured at a chosen context length without running prefill.  Outputs are
+    meaningless by construction.  Extra config: ``fill_value`` (default 0.015)."""
+
+    def __init__(self, cfg, half: str, rank: int = 0, world_size: int = 1) -> None:
+        super().__init__(cfg, half, rank, world_size)
+        self.is_consumer, self.is_producer = True, False
+        self.fill = float(self.extra.get("fill_value", 0.015))
+
+    def _contains(self, block_hash: bytes) -> bool:
+        return True
+
+    def load(self, pairs: list[tuple[str, int]]) -> None:
+        if not pairs:
+            return
+        idx = torch.tensor([b for _, b in pairs], dtype=torch.int64, device=self.kv_caches[0].device)
+        for c in self.kv_caches:
+            if c.dtype in (torch.uint8, torch.float8_e4m3fn):
+                c.view(torch.uint8).index_fill_(0, idx, 0x20)       # a small positive e4m3 value
+            else:
+                c.index_fill_(0, idx, self.fill)
+        self.stats["loaded_blocks"] += len(pairs)
+
+    def save(self, pairs: list[tuple[str, int]]) -> None:
+        pass
+
+
+class MultiConnector(KVConnector):
+    """Several connectors behind one: a lookup asks them in order and the first hit serves the load; saves go
+    to every producer.  Extra config: ``connectors`` — a list of dicts with the fields of a transfer config."""
+
+    def __init__(self, cfg, half: str, rank: int = 0, world_size: int = 1) -> None:
+        super().__init__(cfg, half, rank, world_size)
+        from sonar_b200.config import KVTransferConfig
+        self.children: list[KVConnector] = []
+        for spec in self.extra.get("connectors", []):
+            sub = KVTransferConfig(**{"kv_role": cfg.kv_role, **spec})
+            self.children.append(create_connector(sub, half, rank=rank, world_size=world_size))
+        if not self.children:
+            raise ValueError("MultiConnector needs kv_connector_extra_config['connectors']")
+        self._owner: dict[bytes, int] = {}
+
+    # keys carry the child index in front: "<i>:<hash>"
+    def lookup(self, block_hash: bytes) -> bool:
+        self.stats["lookups"] += 1
+        for i, ch in enumerate(self.children):
+            if ch.lookup(block_hash):
+                self._owner[block_hash] = i
+                self.stats["hits"] += 1
+                return True
+        return False
+
+    def plan_load(self, block_hash: bytes, gpu_block: int) -> None:
+        i = self._owner.pop(block_hash, 0)
+        self._loads.append((f"{i}:{self.key(block_hash)}", gpu_block))
+
+    def plan_save(self, block_hash: bytes, gpu_block: int) -> None:
+        for i, ch in enumerate(self.children):
+            ch.plan_save(block_hash, gpu_block)
+            saves, _ = ch.take_plan()
+            self._saves.extend((f"{i}:{k}", b) for k, b in saves)
+
+    def reset(self) -> None:
+        for ch in self.children:
+            ch.reset()
+
+    def bind(self, kv_caches: list[torch.Tensor]) -> None:
+        super().bind(kv_caches)
+        for ch in self.children:
+            ch.bind(kv_caches)
+
+    def _split(self, pairs):
+        per: dict[int, list[tuple[str, int]]] = {}
+        for k, b in pairs:
+            i, _, key = k.partition(":")
+            per.setdefault(int(i), []).append((key, b))
+        return per
+
+    def load(self, pairs: list[tuple[str, int]]) -> None:
+        for i, sub in self._split(pairs).items():
+            self.children[i].load(sub)
+            self.stats["loaded_blocks"] += len(sub)
+
+    def save(self, pairs: list[tuple[str, int]]) -> None:
+        for i, sub in self._split(pairs).items():
+            self.children[i].save(sub)
+            self.stats["saved_blocks"] += len(sub)
+
+    def shutdown(self) -> None:
+        for ch in self.children:
+            ch.shutdown()
+
+
+_HERE = "sonar_b200.distributed.kv_transfer"
+register_connector("SharedStorageConnector", _HERE, "SharedStorageConnector")
+register_connector("ExampleConnector", _HERE, "SharedStorageConnector")
+register_connector("DecodeBenchConnector", _HERE, "DecodeBenchConnector")
+register_connector("MultiConnector", _HERE, "MultiConnector")

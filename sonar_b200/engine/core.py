@@ -41,10 +41,17 @@ class EngineCore:
             cfg.cache.kv_offload_cpu_gb * 2**30 // max(1, self.kv_cfg.num_layers * self.kv_cfg.spec.page_bytes))
         if cpu_blocks:
             self.executor.collective_rpc("init_kv_offload", cpu_blocks)
+        connector = None
+        if cfg.kv_transfer.enabled:
+            from sonar_b200.distributed.kv_transfer import create_connector
+            connector = create_connector(cfg.kv_transfer, "scheduler", world_size=cfg.parallel.tensor_parallel_size)
+            self.executor.collective_rpc("init_kv_connector")
+            logger.info("KV connector %s (%s)", cfg.kv_transfer.kv_connector, cfg.kv_transfer.kv_role)
         self.scheduler = Scheduler(cfg.scheduler, cfg.cache, self.kv_cfg.num_blocks, cfg.speculative,
                                    sliding_window=sliding, log_stats=cfg.observability.log_stats,
                                    collect_kv_events=cfg.observability.collect_kv_events,
-                                   structured_output_manager=structured, cpu_offload_blocks=cpu_blocks)
+                                   structured_output_manager=structured, cpu_offload_blocks=cpu_blocks,
+                                   kv_connector=connector)
         self.tracer = get_tracer(cfg.observability.trace_file)
         self.kv_publisher = None
         if cfg.observability.kv_events_endpoint:

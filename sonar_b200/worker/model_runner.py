@@ -177,6 +177,7 @@ class ModelRunner:
             self.model = load_model(self.cfg, self.device)
         logger.info("model %s built in %.1fs", self.model_cfg.model, time.time() - t0)
         self.eplb = None
+        self.kv_connector = None
         pc = self.cfg.parallel
         if pc.enable_eplb and pc.num_redundant_experts > 0:
             from sonar_b200.distributed.eplb import EplbConfig, EplbState
@@ -243,6 +244,19 @@ class ModelRunner:
         logger.info("KV offload: %d host blocks (%.2f GiB pinned)", num_cpu_blocks, nbytes / 2**30)
         return nbytes
 
+    def init_kv_connector(self, rank: int, world_size: int) -> None:
+        """Worker half of the configured KV connector, bound to this rank's paged caches."""
+        from sonar_b200.distributed.kv_transfer import create_connector
+        self.kv_connector = create_connector(self.cfg.kv_transfer, "worker", rank=rank, world_size=world_size)
+        self.kv_connector.bind(self.kv_caches)
+
+    def _kv_connector_save(self, so: SchedulerOutput) -> None:
+        """Blocks that this step completed go out through the connector (the copies queue behind the forward
+        pass on the compute stream)."""
+        if so.kv_ext_saves and self.kv_connector is not None:
+            self.kv_connector.save(so.kv_ext_saves)
+            self.stats["kv_connector_saves"] = self.stats.get("kv_connector_saves", 0) + len(so.kv_ext_saves)
+
     def _run_kv_transfers(self, so: SchedulerOutput) -> None:
         """Evicted blocks go to the host before their new owners overwrite them; blocks matched in the host
         tier come back before attention reads them.  Both run on the compute stream, in that order."""
@@ -258,10 +272,13 @@ class ModelRunner:
             for cache, host in zip(self.kv_caches, self.cpu_kv):
                 cache.index_copy_(0, dst, host.index_select(0, src).to(self.device, non_blocking=False))
             self.stats["kv_offload_loads"] = self.stats.get("kv_offload_loads", 0) + len(so.kv_loads)
+        if so.kv_ext_loads and self.kv_connector is not None:
+            self.kv_connector.load(so.kv_ext_loads)
+            self.stats["kv_connector_loads"] = self.stats.get("kv_connector_loads", 0) + len(so.kv_ext_loads)
 
     # --------------------------------------------------------------- states
     def _update_states(self, so: SchedulerOutput) -> None:
-        if so.kv_stores or so.kv_loads:
+        if so.kv_stores or so.kv_loads or so.kv_ext_loads:
             self._run_kv_transfers(so)
         b = self.batch
         for rid in so.finished_req_ids:
@@ -415,12 +432,14 @@ class ModelRunner:
             if self.pp is not None and not self.pp.is_last_rank:
                 self.stats["launch_s"] += time.perf_counter() - t1
                 self._send_intermediate(out)
+                self._kv_connector_save(so)
                 return None
             hidden = tp.gather_tokens(out, total)
         self.stats["launch_s"] += time.perf_counter() - t1
         t2 = time.perf_counter()
         res = self._sample(so, hidden, meta, rows, q_lens)
         self.stats["sample_s"] += time.perf_counter() - t2
+        self._kv_connector_save(so)
         if self.eplb is not None and self.eplb.step():
             self.rebalance_experts()
         if defer and not isinstance(res, _Deferred):

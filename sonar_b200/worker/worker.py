@@ -111,6 +111,14 @@ class Worker:
     def init_kv_offload(self, num_cpu_blocks: int) -> int:
         return self.runner.init_kv_offload(num_cpu_blocks)
 
+    def init_kv_connector(self) -> None:
+        from sonar_b200.parallel import state
+        self.runner.init_kv_connector(state.tp_rank(), state.tp_world_size())
+
+    def kv_connector_stats(self) -> dict:
+        c = self.runner.kv_connector
+        return dict(c.stats) if c is not None else {}
+
     # sleep / wake-up --------------------------------------------------------------
     def sleep(self, level: int = 1) -> int:
         """Level 1: weights go to pinned host memory, the KV cache is dropped.  Level 2: both are

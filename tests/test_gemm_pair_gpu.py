@@ -90,3 +90,43 @@ def test_cluster_splitk_dispatch(cu):
             _check(out, x.float() @ w.float().t(), k)
     finally:
         cu.set_gemm_cluster_splitk(False)
+
+
+@pytest.mark.parametrize("m,n,k,tp", [(256, 4096, 1024, 4), (256, 4096, 3584, 4), (128, 4096, 2048, 2), (64, 4096, 512, 8),
+                                      (200, 1536, 1024, 4)])
+def test_cluster_splitk_tp_hooks(cu, m, n, k, tp):
+    """The cluster kernel behind the tensor-parallel entry: scatter epilogue into per-owner buffers (the peers are
+    local allocations here, nothing waits on another launch) with completion flags, and the gather-flag wait with
+    flags that are already set."""
+    torch.manual_seed(m + n + k + tp)
+    shard = (m + tp - 1) // tp
+    a = (torch.randn(m, k, device=DEV) * 0.3).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) * 0.3).to(torch.bfloat16)
+    want = a.float() @ w.float().t()
+    cu.set_gemm_cluster_splitk(True)
+    try:
+        bufs = [torch.full((shard, n), float("nan"), device=DEV, dtype=torch.bfloat16) for _ in range(tp)]
+        flags = torch.zeros(tp, dtype=torch.int32, device=DEV)
+        dst = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=DEV)
+        fptr = torch.tensor([flags.data_ptr() + 4 * i for i in range(tp)], dtype=torch.int64, device=DEV)
+        done = torch.zeros(tp, dtype=torch.int32, device=DEV)
+        for seq in (1, 2):
+            cu.gemm_tp(a, w, None, tp=tp, shard_rows=shard, seq=seq, rank=0, dst_ptrs=dst, local_done=done,
+                       flag_ptrs=fptr, n_out=n, ldc=n, err=cu.error_word(a.device))
+            torch.cuda.synchronize()
+            cu.check_device_errors()
+            got = torch.cat(bufs, 0)[:m]
+            _check(got, want, k)
+            owners = (m + shard - 1) // shard
+            assert flags.tolist()[:owners] == [seq] * owners and done.tolist() == [0] * tp
+        # column-parallel side: every row block's gather flags already carry the launch's number
+        num_m = (m + 127) // 128
+        gflags = torch.full((num_m * tp,), 5, dtype=torch.int32, device=DEV)
+        out = torch.full((m, n), float("nan"), device=DEV, dtype=torch.bfloat16)
+        cu.gemm_tp(a, w, out, tp=tp, shard_rows=shard, seq=5, rank=tp - 1, gather_flags=gflags,
+                   err=cu.error_word(a.device))
+        torch.cuda.synchronize()
+        cu.check_device_errors()
+        _check(out, want, k)
+    finally:
+        cu.set_gemm_cluster_splitk(False)

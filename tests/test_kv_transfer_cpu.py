@@ -1,0 +1,126 @@
+"""KV connectors: a producer instance writes full blocks to shared storage, a consumer instance that never
+saw the prompt loads them instead of recomputing; decode-bench and multi connectors; config parsing."""
+import os
+
+import pytest
+import torch
+
+from sonar_b200 import LLM, SamplingParams
+from sonar_b200.config import EngineArgs, KVTransferConfig
+from sonar_b200.distributed.kv_transfer import (DecodeBenchConnector, MultiConnector, SharedStorageConnector,
+                                                create_connector, register_connector)
+
+KW = dict(model="tiny-llama", dtype="float32", max_model_len=128, num_gpu_blocks_override=24, device="cpu",
+          max_num_seqs=2, max_num_batched_tokens=64, seed=0)
+SP = SamplingParams(max_tokens=5, temperature=0, ignore_eos=True)
+
+
+def _kvt(path, role):
+    return {"kv_connector": "SharedStorageConnector", "kv_role": role,
+            "kv_connector_extra_config": {"shared_storage_path": str(path)}}
+
+
+def test_shared_storage_disaggregated_prefill(tmp_path):
+    prompt = {"prompt_token_ids": list(range(20, 20 + 70))}        # 4 full blocks + a tail
+    want = LLM(**KW).generate([prompt], SP)[0].outputs[0].token_ids
+    producer = LLM(**KW, kv_transfer_config=_kvt(tmp_path, "kv_producer"))
+    assert producer.generate([prompt], SamplingParams(max_tokens=1, temperature=0))[0].outputs[0].token_ids == want[:1]
+    files = [f for _, _, fs in os.walk(tmp_path) for f in fs]
+    assert len(files) == 4 and all(f.endswith(".r0of1.kv") for f in files)
+    pstats = producer.llm_engine.get_stats()["workers"][0]
+    assert pstats["kv_connector_saves"] == 4
+    # a producer never loads, even when its own files would match
+    producer.llm_engine.core.engine_core.scheduler.kv.reset_prefix_cache()
+    producer.generate([prompt], SamplingParams(max_tokens=1, temperature=0))
+    assert producer.llm_engine.core.engine_core.scheduler.kv.connector_hits == 0
+
+    consumer = LLM(**KW, kv_transfer_config=_kvt(tmp_path, "kv_consumer"))
+    out = consumer.generate([prompt], SP)[0]
+    assert out.outputs[0].token_ids == want
+    assert out.num_cached_tokens == 64                             # 4 blocks came through the connector
+    core = consumer.llm_engine.core.engine_core
+    assert core.scheduler.kv.connector_hits == 4
+    cstats = consumer.llm_engine.get_stats()["workers"][0]
+    assert cstats["kv_connector_loads"] == 4 and "kv_connector_saves" not in cstats
+    # a different prompt sharing only the first two blocks: partial hit
+    other = {"prompt_token_ids": list(range(20, 20 + 32)) + list(range(500, 530))}
+    want2 = LLM(**KW).generate([other], SP)[0].outputs[0].token_ids
+    consumer.llm_engine.core.engine_core.scheduler.kv.reset_prefix_cache()
+    out2 = consumer.generate([other], SP)[0]
+    assert out2.outputs[0].token_ids == want2 and out2.num_cached_tokens == 32
+
+
+def test_kv_both_saves_decode_blocks_and_reloads_after_reset(tmp_path):
+    llm = LLM(**KW, kv_transfer_config=_kvt(tmp_path, "kv_both"))
+    prompt = {"prompt_token_ids": list(range(40, 40 + 30))}
+    sp = SamplingParams(max_tokens=20, temperature=0, ignore_eos=True)
+    first = llm.generate([prompt], sp)[0].outputs[0].token_ids
+    n_files = sum(len(fs) for _, _, fs in os.walk(tmp_path))
+    assert n_files == (30 + 20 - 1) // 16                         # blocks filled during decode are saved too
+    kv = llm.llm_engine.core.engine_core.scheduler.kv
+    assert kv.reset_prefix_cache()
+    again = llm.generate([{"prompt_token_ids": prompt["prompt_token_ids"] + first[:10]}],
+                         SamplingParams(max_tokens=10, temperature=0, ignore_eos=True))[0]
+    assert again.outputs[0].token_ids == first[10:]
+    assert again.num_cached_tokens == 32 and kv.connector_hits == 2
+
+
+def test_decode_bench_connector_skips_prefill():
+    llm = LLM(**KW, kv_transfer_config={"kv_connector": "DecodeBenchConnector", "kv_role": "kv_consumer"})
+    out = llm.generate([{"prompt_token_ids": list(range(100, 100 + 81))}], SP)[0]
+    assert out.num_cached_tokens == 80 and len(out.outputs[0].token_ids) == 5
+    w = llm.llm_engine.get_stats()["workers"][0]
+    assert w["kv_connector_loads"] == 5
+
+
+def test_multi_connector_first_hit_wins(tmp_path):
+    a, b = tmp_path / "a", tmp_path / "b"
+    cfg = KVTransferConfig(kv_connector="MultiConnector", kv_role="kv_both", kv_connector_extra_config={
+        "connectors": [{"kv_connector": "SharedStorageConnector", "kv_connector_extra_config": {"shared_storage_path": str(a)}},
+                       {"kv_connector": "SharedStorageConnector", "kv_connector_extra_config": {"shared_storage_path": str(b)}}]})
+    sched = create_connector(cfg, "scheduler")
+    work = create_connector(cfg, "worker")
+    assert isinstance(sched, MultiConnector) and len(sched.children) == 2
+    caches = [torch.arange(4 * 2 * 8, dtype=torch.float32).reshape(4, 2, 8) + 100 * layer for layer in range(3)]
+    work.bind(caches)
+    h1, h2 = b"\x01" * 16, b"\x02" * 16
+    sched.plan_save(h1, 1)
+    saves, loads = sched.take_plan()
+    assert [k.split(":")[0] for k, _ in saves] == ["0", "1"] and not loads
+    work.save(saves)
+    assert sched.lookup(h1) and not sched.lookup(h2)
+    # only the second store has h2
+    only_b = create_connector(KVTransferConfig(**_kvt(b, "kv_producer")), "worker")
+    only_b.bind(caches)
+    only_b.save([(h2.hex(), 2)])
+    assert sched.lookup(h2)
+    sched.plan_load(h2, 3)
+    sched.lookup(h1)
+    sched.plan_load(h1, 0)
+    _, loads = sched.take_plan()
+    assert loads == [(f"1:{h2.hex()}", 3), (f"0:{h1.hex()}", 0)]
+    want3, want0 = [c[2].clone() for c in caches], [c[1].clone() for c in caches]
+    work.load(loads)
+    for c, w3, w0 in zip(caches, want3, want0):
+        assert torch.equal(c[3], w3) and torch.equal(c[0], w0)
+
+
+def test_config_and_registry(tmp_path):
+    with pytest.raises(ValueError):
+        KVTransferConfig(kv_connector="SharedStorageConnector")            # role missing
+    with pytest.raises(ValueError):
+        create_connector(KVTransferConfig(kv_connector="Nope", kv_role="kv_both"), "scheduler")
+    register_connector("AliasForTest", "sonar_b200.distributed.kv_transfer", "DecodeBenchConnector")
+    c = create_connector(KVTransferConfig(kv_connector="AliasForTest", kv_role="kv_consumer"), "scheduler")
+    assert isinstance(c, DecodeBenchConnector) and c.lookup(b"x" * 16)
+    import argparse
+    import json
+    p = EngineArgs.add_cli_args(argparse.ArgumentParser())
+    ns = p.parse_args(["--kv-transfer-config", json.dumps(_kvt(tmp_path, "kv_both"))])
+    args = EngineArgs.from_cli_args(ns)
+    assert args.kv_transfer_config["kv_connector"] == "SharedStorageConnector"
+    # module-path loading
+    cfg = KVTransferConfig(kv_connector="SharedStorageConnector", kv_role="kv_both",
+                           kv_connector_module_path="sonar_b200.distributed.kv_transfer",
+                           kv_connector_extra_config={"shared_storage_path": str(tmp_path)})
+    assert isinstance(create_connector(cfg, "worker"), SharedStorageConnector)

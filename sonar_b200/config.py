@@ -278,10 +278,25 @@ class SchedulerConfig:
 
 @dataclass
 class SpeculativeConfig:
-    method: str | None = None          # None | ngram
+    """Parity: ``aphrodite/config/speculative.py`` (``--speculative-config`` JSON: ``method``, ``model``,
+    ``num_speculative_tokens``, ``prompt_lookup_max/min``)."""
+    method: str | None = None          # None | ngram | draft_model
     num_speculative_tokens: int = 0
     prompt_lookup_max: int = 4
     prompt_lookup_min: int = 2
+    model: str | None = None           # draft model: checkpoint directory or architecture preset
+    quantization: str | None = None
+    load_format: str | None = None     # defaults to the target's
+
+    def __post_init__(self) -> None:
+        if self.method is None and self.model is not None:
+            self.method = "draft_model"
+        if self.method not in (None, "ngram", "draft_model"):
+            raise ValueError(f"unknown speculative method {self.method!r} (ngram, draft_model)")
+        if self.method == "draft_model" and not self.model:
+            raise ValueError("speculative method draft_model needs a draft model")
+        if self.method is not None and self.num_speculative_tokens <= 0:
+            raise ValueError("num_speculative_tokens must be positive when speculative decoding is on")
 
 
 @dataclass
@@ -403,6 +418,8 @@ class EngineArgs:
     # speculative
     speculative_method: str | None = None
     num_speculative_tokens: int = 0
+    speculative_model: str | None = None
+    speculative_config: dict | None = None     # fields of SpeculativeConfig (a JSON object on the command line)
     kv_offload_cpu_gb: float = 0.0
     kv_offload_cpu_blocks: int = 0
     kv_transfer_config: dict | None = None     # fields of KVTransferConfig (a JSON object on the command line)
@@ -465,8 +482,14 @@ class EngineArgs:
             max_model_len=model.max_model_len, enable_chunked_prefill=self.enable_chunked_prefill,
             long_prefill_token_threshold=self.long_prefill_token_threshold,
             policy=self.scheduling_policy, async_scheduling=self.async_scheduling)
-        spec = SpeculativeConfig(method=self.speculative_method,
-                                 num_speculative_tokens=self.num_speculative_tokens)
+        sc = self.speculative_config
+        if isinstance(sc, str):
+            sc = json.loads(sc)
+        sc = dict(sc or {})
+        sc.setdefault("method", self.speculative_method)
+        sc.setdefault("num_speculative_tokens", self.num_speculative_tokens)
+        sc.setdefault("model", self.speculative_model)
+        spec = SpeculativeConfig(**sc)
         obs = ObservabilityConfig(log_stats=not self.disable_log_stats, trace_file=self.trace_file,
                                   collect_kv_events=self.kv_events_endpoint is not None,
                                   kv_events_endpoint=self.kv_events_endpoint,
@@ -491,7 +514,7 @@ class EngineArgs:
                 continue  # positional / --model handled by the caller
             if f.type in ("bool", bool):
                 parser.add_argument(flag, action=argparse.BooleanOptionalAction, default=f.default)
-            elif f.name in ("hf_overrides", "lora_modules", "kv_transfer_config"):
+            elif f.name in ("hf_overrides", "lora_modules", "kv_transfer_config", "speculative_config"):
                 parser.add_argument(flag, type=json.loads, default=None)
             else:
                 base = str(f.type).replace(" | None", "")

@@ -1,0 +1,219 @@
+"""Speculative decoding with a draft model: a smaller language model of the same vocabulary proposes the
+next ``k`` tokens of every decoding sequence; the target model scores all of them in one step and keeps the
+prefix that its own samples agree with.
+
+Design.  The draft model is a second model in the same worker.  Its attention layers own KV caches with the
+*same block geometry* as the target's (same number of blocks, same block size), so it needs no allocator
+of its own: it reads and writes the blocks the scheduler gave the request, through the same block table.
+After every target step the proposer
+
+1. *catches up*: runs the draft model over every token the target now knows and the draft has not seen —
+   the chunk of a prompt just prefilled, or the accepted drafts plus the bonus token of a decoding sequence
+   (one variable-length batch, the draft's KV for those positions is written on the way);
+2. takes the arg-max at each sampling sequence's last position as draft 1, then runs ``k-1`` single-token
+   steps.  Positions, KV slots and context lengths of these steps are advanced *on the device* (the draft
+   tokens never visit the host in between); the positions written here lie in the look-ahead slots the
+   scheduler allocates for drafts, and are overwritten by the next catch-up with the tokens that really
+   came out.
+
+All ``k`` drafts come back in one device→host copy.  Drafts are greedy; verification (sample at every
+position, keep while equal to the draft) leaves the output distribution that of the target alone.
+
+Because the draft's caches are appended to the runner's cache list, prefix-cache hits, the CPU tier and KV
+connectors carry the draft's KV along with the target's.
+
+Parity: the draft-model proposer of ``aphrodite/v1/spec_decode/`` (``eagle.py`` ``propose()``: first pass
+over the step's tokens, then ``num_speculative_tokens - 1`` single-token passes with device-side position
+and slot updates) and ``SpeculativeConfig`` (``aphrodite/config/speculative.py``: ``model``,
+``num_speculative_tokens``, ``method="draft_model"``).
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from sonar_b200.config import ModelConfig
+from sonar_b200.layers.attention import AttentionMetadata
+from sonar_b200.logger import init_logger
+
+logger = init_logger(__name__)
+
+
+class DraftModelProposer:
+    def __init__(self, runner, spec_cfg) -> None:
+        from sonar_b200.loader.weights import load_model
+        self.runner = runner
+        self.k = int(spec_cfg.num_speculative_tokens)
+        tgt = runner.model_cfg
+        mcfg = ModelConfig(model=spec_cfg.model, dtype=tgt.dtype, seed=tgt.seed + 1, max_model_len=tgt.max_model_len,
+                           quantization=spec_cfg.quantization, load_format=spec_cfg.load_format or tgt.load_format,
+                           skip_tokenizer_init=True)
+        if mcfg.vocab_size != tgt.vocab_size:
+            raise ValueError(f"draft model vocabulary ({mcfg.vocab_size}) differs from the target's ({tgt.vocab_size})")
+        self.model_cfg = mcfg
+        with torch.inference_mode():
+            self.model = load_model(mcfg, runner.device)
+        self.layers = self.model.attention_layers()
+        a = self.layers[0]
+        self.group, self.num_kv_heads, self.head_dim = a.num_heads // a.num_kv_heads, a.num_kv_heads, a.head_dim
+        self.computed: dict[str, int] = {}          # request → tokens whose draft KV is valid
+        dev, pin = runner.device, runner.is_cuda
+        T, S = runner.max_tokens + runner.max_seqs, runner.max_seqs
+
+        def host(n, dt):
+            return torch.zeros(n, dtype=dt, pin_memory=pin)
+        self.h_ids, self.h_pos, self.h_slots = host(T, torch.int64), host(T, torch.int64), host(T, torch.int32)
+        self.h_seq, self.h_qsl, self.h_sel = host(S, torch.int32), host(S + 1, torch.int32), host(2 * S, torch.int64)
+        self.h_last = host(S, torch.int64)
+        self.d_ids = torch.zeros(T, dtype=runner.d_input_ids.dtype, device=dev)
+        self.d_pos = torch.zeros(T, dtype=runner.d_positions.dtype, device=dev)
+        self.d_slots = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.d_seq = torch.zeros(S, dtype=torch.int32, device=dev)
+        self.d_qsl = torch.zeros(S + 1, dtype=torch.int32, device=dev)
+        self.d_sel = torch.zeros(2 * S, dtype=torch.int64, device=dev)
+        self.d_last = torch.zeros(S, dtype=torch.int64, device=dev)
+        self.d_arange = torch.arange(S + 1, dtype=torch.int32, device=dev)
+        self.h_out = torch.zeros((max(self.k, 1), S), dtype=torch.int64, pin_memory=pin)
+        self._copied = torch.cuda.Event() if pin else None
+        self.stats = {"draft_steps": 0, "draft_tokens": 0}
+
+    # ---- memory ------------------------------------------------------------------------------------
+    def block_bytes(self, block_size: int, elem_bytes: int) -> int:
+        """Bytes one KV block costs across the draft model's layers."""
+        return len(self.layers) * 2 * self.num_kv_heads * block_size * self.head_dim * elem_bytes
+
+    def bind_kv_caches(self, num_blocks: int, block_size: int, dtype) -> list[torch.Tensor]:
+        caches = []
+        for layer in self.layers:
+            c = torch.zeros((num_blocks, 2, self.num_kv_heads, block_size, self.head_dim), dtype=dtype,
+                            device=self.runner.device)
+            layer.bind_kv_cache(c)
+            caches.append(c)
+        return caches
+
+    # ---- request life cycle --------------------------------------------------------------------------
+    def on_add(self, req_id: str, num_computed: int) -> None:
+        self.computed[req_id] = num_computed
+
+    def on_remove(self, req_id: str) -> None:
+        self.computed.pop(req_id, None)
+
+    # ---- one forward pass of the draft model -----------------------------------------------------------
+    def _forward(self, ids: torch.Tensor, meta: AttentionMetadata) -> torch.Tensor:
+        from sonar_b200.parallel.tp_ops import get_tp_context
+        r = self.runner
+        tp = get_tp_context()
+        total = meta.num_tokens
+        tp.begin_step(total)
+        if r.is_cuda:
+            from sonar_b200.ops import cuda as cuda_ops
+            cuda_ops.build_attention_work(meta, r, group=self.group, num_kv_heads=self.num_kv_heads)
+        out = self.model(ids, meta, None)
+        return tp.gather_tokens(out, total)
+
+    # ---- proposing -------------------------------------------------------------------------------------
+    @torch.inference_mode()
+    def propose(self, rows: np.ndarray, upto: np.ndarray, sampling: np.ndarray) -> list[list[int]]:
+        """``rows``: batch rows of this step, in step order (the runner's device block table holds their rows
+        in that order); ``upto[i]``: tokens of row i the target knows now; ``sampling[i]``: whether the row
+        produced a token this step (and so wants drafts).  Returns one draft list per row."""
+        r, b, bs = self.runner, self.runner.batch, self.runner.block_size
+        ns = len(rows)
+        out: list[list[int]] = [[] for _ in range(ns)]
+        if ns == 0:
+            return out
+        if self._copied is not None:
+            self._copied.synchronize()       # the previous call's copies out of the pinned buffers have run
+        start = np.fromiter((self.computed.get(b.req_ids[row], 0) for row in rows), dtype=np.int64, count=ns)
+        start = np.minimum(start, upto)      # after a rollback the target may know less than the draft saw
+        q_lens = (upto - start).astype(np.int64)
+        # rows with nothing new still need one query position to draft from: re-run their last token
+        redo = sampling & (q_lens == 0)
+        start[redo] -= 1
+        q_lens[redo] = 1
+        keep = np.nonzero(q_lens > 0)[0]
+        if len(keep) == 0:
+            return out
+        k_rows, k_start, k_q = rows[keep], start[keep], q_lens[keep]
+        n = len(keep)
+        total = int(k_q.sum())
+        starts = np.zeros(n + 1, dtype=np.int64)
+        np.cumsum(k_q, out=starts[1:])
+        req_of_tok = np.repeat(np.arange(n), k_q)
+        pos = k_start[req_of_tok] + (np.arange(total) - starts[:-1][req_of_tok])
+        row_of_tok = k_rows[req_of_tok]
+        self.h_ids.numpy()[:total] = b.token_ids[row_of_tok, pos]
+        self.h_pos.numpy()[:total] = pos
+        self.h_slots.numpy()[:total] = b.block_table_np[row_of_tok, pos // bs] * bs + pos % bs
+        seq_lens = k_start + k_q
+        self.h_seq.numpy()[:n] = seq_lens
+        self.h_seq.numpy()[n:] = 0
+        self.h_qsl.numpy()[:n + 1] = starts
+        self.h_qsl.numpy()[n + 1:] = total
+        self.h_sel.numpy()[:n] = keep
+        nbl = r.is_cuda
+        self.d_ids[:total].copy_(self.h_ids[:total], non_blocking=nbl)
+        self.d_pos[:total].copy_(self.h_pos[:total], non_blocking=nbl)
+        self.d_slots[:total].copy_(self.h_slots[:total], non_blocking=nbl)
+        self.d_seq.copy_(self.h_seq, non_blocking=nbl)
+        self.d_qsl.copy_(self.h_qsl, non_blocking=nbl)
+        self.d_sel[:n].copy_(self.h_sel[:n], non_blocking=nbl)
+        # the step's block-table rows, restricted to the rows taking part and in their order
+        bt = r.d_block_table[:ns].index_select(0, self.d_sel[:n])
+        meta = AttentionMetadata(
+            num_tokens=total, num_seqs=n, positions=self.d_pos[:total], slot_mapping=self.d_slots[:total],
+            block_tables=bt, seq_lens=self.d_seq, query_start_loc=self.d_qsl, max_query_len=int(k_q.max()),
+            max_seq_len=int(seq_lens.max()), query_lens_cpu=k_q, seq_lens_cpu=seq_lens)
+        hidden = self._forward(self.d_ids[:total], meta)
+        self.stats["draft_steps"] += 1
+        for i, row in zip(keep, k_rows):
+            self.computed[b.req_ids[row]] = int(upto[i])
+        # ---- drafts for the sampling rows that have room for k more positions
+        room = upto[keep] + self.k <= r.model_cfg.max_model_len
+        d_idx = np.nonzero(sampling[keep] & room)[0]           # indices into the kept rows
+        m = len(d_idx)
+        if m == 0 or self.k <= 0:
+            if self._copied is not None:
+                self._copied.record()
+            return out
+        self.h_last.numpy()[:m] = starts[1:][d_idx] - 1
+        S = r.max_seqs
+        self.h_sel.numpy()[S:S + m] = d_idx
+        self.d_last[:m].copy_(self.h_last[:m], non_blocking=nbl)
+        sel = self.d_sel[S:S + m]
+        sel.copy_(self.h_sel[S:S + m], non_blocking=nbl)
+        if self._copied is not None:
+            self._copied.record()
+        logits = self.model.compute_logits(hidden.index_select(0, self.d_last[:m]))
+        tok = logits.argmax(dim=-1)
+        drafts = [tok]
+        if self.k > 1:
+            # single-token steps over the m drafting rows; metadata advances on the device
+            bt_m = bt.index_select(0, sel)
+            pos_m = self.d_pos[:total].index_select(0, self.d_last[:m]) + 1        # position of draft 1
+            seq_m = torch.zeros_like(self.d_seq)
+            seq_m[:m] = self.d_seq.index_select(0, sel) + 1
+            qsl_m = torch.clamp(self.d_arange, max=m)
+            ones = np.ones(m, dtype=np.int64)
+            base_seq = seq_lens[d_idx]
+            for j in range(1, self.k):
+                blk = bt_m.gather(1, (pos_m // bs).to(torch.int64).unsqueeze(1)).squeeze(1)
+                slots = (blk * bs + pos_m % bs).to(torch.int32)
+                meta_j = AttentionMetadata(
+                    num_tokens=m, num_seqs=m, positions=pos_m, slot_mapping=slots, block_tables=bt_m, seq_lens=seq_m,
+                    query_start_loc=qsl_m, max_query_len=1, max_seq_len=int(base_seq.max()) + j, query_lens_cpu=ones,
+                    seq_lens_cpu=base_seq + j)
+                hidden = self._forward(tok.to(self.d_ids.dtype), meta_j)
+                tok = self.model.compute_logits(hidden[:m]).argmax(dim=-1)
+                drafts.append(tok)
+                pos_m = pos_m + 1
+                seq_m = seq_m.clone()
+                seq_m[:m] += 1
+                self.stats["draft_steps"] += 1
+        host = self.h_out[:self.k, :m]
+        host.copy_(torch.stack(drafts), non_blocking=False)
+        cols = host.numpy()
+        for c, i in enumerate(d_idx):
+            out[int(keep[i])] = [int(t) for t in cols[:, c]]
+        self.stats["draft_tokens"] += m * self.k
+        return out

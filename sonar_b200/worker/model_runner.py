@@ -178,6 +178,14 @@ class ModelRunner:
         logger.info("model %s built in %.1fs", self.model_cfg.model, time.time() - t0)
         self.eplb = None
         self.kv_connector = None
+        self.drafter = None
+        if self.spec_cfg.method == "draft_model":
+            if self.pp is not None:
+                raise ValueError("draft-model speculative decoding does not run under pipeline parallelism")
+            from sonar_b200.sample.draft_model import DraftModelProposer
+            self.drafter = DraftModelProposer(self, self.spec_cfg)
+            logger.info("draft model %s: %d layers, %d drafts per step", self.spec_cfg.model,
+                        len(self.drafter.layers), self.drafter.k)
         pc = self.cfg.parallel
         if pc.enable_eplb and pc.num_redundant_experts > 0:
             from sonar_b200.distributed.eplb import EplbConfig, EplbState
@@ -215,6 +223,16 @@ class ModelRunner:
     def num_local_layers(self) -> int:
         return len(self.model.attention_layers())
 
+    def kv_share(self) -> float:
+        """Fraction of the KV budget that goes to the target model's caches (the rest holds the draft model's
+        KV for the same blocks)."""
+        if self.drafter is None:
+            return 1.0
+        spec = self.kv_cache_spec()
+        mine = self.num_local_layers() * spec.page_bytes
+        nbytes = 1 if self.cfg.cache.cache_dtype == "fp8" else torch.empty((), dtype=self.model_cfg.dtype).element_size()
+        return mine / (mine + self.drafter.block_bytes(self.block_size, nbytes))
+
     def initialize_kv_cache(self, kv_cfg: KVCacheConfig) -> None:
         self.kv_cfg = kv_cfg
         spec = kv_cfg.spec
@@ -232,6 +250,8 @@ class ModelRunner:
             cache = torch.zeros(shape, dtype=dtype, device=self.device)
             layer.bind_kv_cache(cache)
             self.kv_caches.append(cache)
+        if self.drafter is not None:
+            self.kv_caches += self.drafter.bind_kv_caches(kv_cfg.num_blocks, spec.block_size, dtype)
         logger.info("KV cache: %d blocks × %d layers, %.2f GiB", kv_cfg.num_blocks, len(self.kv_caches),
                     kv_cfg.num_blocks * len(self.kv_caches) * spec.page_bytes / 2**30)
 
@@ -285,6 +305,11 @@ class ModelRunner:
             b.remove(rid)
         for rid in so.preempted_req_ids:
             b.remove(rid)
+        if self.drafter is not None:
+            for rid in list(so.finished_req_ids) + list(so.preempted_req_ids):
+                self.drafter.on_remove(rid)
+            for nr in so.scheduled_new_reqs:
+                self.drafter.on_add(nr.req_id, nr.num_computed_tokens)
         for nr in so.scheduled_new_reqs:
             if nr.req_id in b.index:
                 b.remove(nr.req_id)
@@ -509,6 +534,8 @@ class ModelRunner:
         self._prompt_logprobs(so, hidden, rows, q_lens, starts, req_ids, out)
         idx = np.nonzero(samples)[0]
         if len(idx) == 0:
+            if self.drafter is not None:      # prompt chunks: the draft model's KV follows the target's
+                self.drafter.propose(rows, np.minimum(computed_after, known).astype(np.int64), samples)
             return out
         # logits rows: the last position, plus one per draft token before it
         gather: list[int] = []
@@ -604,6 +631,11 @@ class ModelRunner:
                 out.logprobs[i] = res.logprobs[lo:lo + len(toks)]
             if spec_out is not None:
                 spec_out[i] = self._ngram.propose(b.token_ids[r, :nt + len(toks)])
+        if self.drafter is not None:
+            upto = np.minimum(computed_after, known).astype(np.int64)
+            upto[idx] = b.num_tokens[rows[idx]]
+            spec_out = self.drafter.propose(rows, upto, samples)
+            self.stats.update(self.drafter.stats)
         out.spec_token_ids = spec_out
         return out
 

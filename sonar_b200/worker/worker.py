@@ -93,7 +93,7 @@ class Worker:
         """Bytes this rank can give to the KV cache."""
         cfg = self.cfg
         if cfg.device != "cuda":
-            return int(os.environ.get("SONAR_CPU_KVCACHE_BYTES", 1 << 30))
+            return int(int(os.environ.get("SONAR_CPU_KVCACHE_BYTES", 1 << 30)) * self.runner.kv_share())
         torch.cuda.synchronize()
         free, total = torch.cuda.mem_get_info()
         budget = int(total * cfg.cache.gpu_memory_utilization)
@@ -102,7 +102,7 @@ class Worker:
         avail = budget - used_by_us - reserve - (total - self._baseline_free)
         logger.info("memory: total %.1f GiB, weights+state %.1f GiB, step reserve %.1f GiB → KV %.1f GiB",
                     total / 2**30, used_by_us / 2**30, reserve / 2**30, avail / 2**30)
-        return max(avail, 0)
+        return max(int(avail * self.runner.kv_share()), 0)
 
     def initialize_from_config(self, kv_cfg: KVCacheConfig) -> None:
         with self._pool("kv_cache"):

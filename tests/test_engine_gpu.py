@@ -132,3 +132,25 @@ def test_async_scheduling_on_gpu_matches_lockstep():
     assert core.run_ahead_steps > 10
     assert got == want
     llm.shutdown()
+
+
+def test_draft_model_speculation_on_gpu():
+    """A draft model (same architecture, other weights) proposes tokens; the verified greedy output is the
+    target's own.  Verification steps score several positions per sequence, so their attention runs the
+    multi-row path; allow the rare bf16 near-tie to flip."""
+    from sonar_b200 import LLM, SamplingParams
+    kw = dict(model="tiny-llama-128", max_model_len=512, num_gpu_blocks_override=256, max_num_seqs=8,
+              max_num_batched_tokens=128, seed=0)
+    prompts = [{"prompt_token_ids": [(17 * i + 3 * j) % 2000 + 3 for j in range(24 + 9 * i)]} for i in range(6)]
+    sp = SamplingParams(max_tokens=16, temperature=0, ignore_eos=True)
+    base = LLM(**kw)
+    want = [o.outputs[0].token_ids for o in base.generate(prompts, sp)]
+    base.shutdown()
+    spec = LLM(**kw, speculative_config={"model": "tiny-llama-128", "num_speculative_tokens": 3})
+    got = [o.outputs[0].token_ids for o in spec.generate(prompts, sp)]
+    st = spec.llm_engine.get_stats()
+    spec.shutdown()
+    assert all(len(g) == 16 for g in got)
+    same = sum(a == b for g, w in zip(got, want) for a, b in zip(g, w))
+    assert same >= 0.9 * 16 * len(prompts), (got, want)
+    assert st["scheduler"].spec_num_drafts > 0 and st["workers"][0]["draft_steps"] > 0

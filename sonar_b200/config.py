@@ -280,7 +280,7 @@ class SchedulerConfig:
 class SpeculativeConfig:
     """Parity: ``aphrodite/config/speculative.py`` (``--speculative-config`` JSON: ``method``, ``model``,
     ``num_speculative_tokens``, ``prompt_lookup_max/min``)."""
-    method: str | None = None          # None | ngram | draft_model
+    method: str | None = None          # None | ngram | draft_model | eagle | mtp (alias deepseek_mtp)
     num_speculative_tokens: int = 0
     prompt_lookup_max: int = 4
     prompt_lookup_min: int = 2
@@ -291,10 +291,12 @@ class SpeculativeConfig:
     def __post_init__(self) -> None:
         if self.method is None and self.model is not None:
             self.method = "draft_model"
-        if self.method not in (None, "ngram", "draft_model"):
-            raise ValueError(f"unknown speculative method {self.method!r} (ngram, draft_model)")
-        if self.method == "draft_model" and not self.model:
-            raise ValueError("speculative method draft_model needs a draft model")
+        if self.method == "deepseek_mtp":
+            self.method = "mtp"
+        if self.method not in (None, "ngram", "draft_model", "eagle", "mtp"):
+            raise ValueError(f"unknown speculative method {self.method!r} (ngram, draft_model, eagle, mtp)")
+        if self.method in ("draft_model", "eagle") and not self.model:
+            raise ValueError(f"speculative method {self.method} needs a draft model")
         if self.method is not None and self.num_speculative_tokens <= 0:
             raise ValueError("num_speculative_tokens must be positive when speculative decoding is on")
 

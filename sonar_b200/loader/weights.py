@@ -169,9 +169,10 @@ def _name_seed(name: str, seed: int) -> int:
     return (h ^ seed) & 0x7FFFFFFFFFFFFFFF
 
 
-def load_model(cfg: EngineConfig | ModelConfig, device: torch.device | str) -> nn.Module:
+def load_model(cfg: EngineConfig | ModelConfig, device: torch.device | str, cls=None) -> nn.Module:
+    """``cls``: build this class instead of the one the architecture name resolves to (draft heads)."""
     mcfg = cfg.model if isinstance(cfg, EngineConfig) else cfg
-    cls = resolve_model_cls(mcfg.architecture)
+    cls = cls or resolve_model_cls(mcfg.architecture)
     model = cls(mcfg, torch.device(device))
     model.eval()
     if mcfg.load_format == "dummy":

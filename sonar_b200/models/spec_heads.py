@@ -1,0 +1,176 @@
+"""Draft heads that continue the *target's* hidden states: EAGLE (one or a few Llama decoder layers behind a
+2H→H fusion of token embedding and previous hidden state) and DeepSeek's multi-token-prediction module
+(normalise both inputs, project 2H→H, one full DeepSeek decoder layer, own output norm, shared LM head).
+
+Both share the calling convention the proposer uses:
+
+    hidden_out = head(input_ids, meta, prev_hidden)      # [T, H], every token on every rank
+    logits     = head.compute_logits(hidden_out)
+
+``input_ids[t]`` is the token that *follows* position ``t`` and ``prev_hidden[t]`` the hidden state the
+target (or, from the second draft on, the head itself) produced at position ``t``; ``hidden_out[t]`` predicts
+the token after that.  Embedding table and LM head are the target's unless the head's checkpoint brings its
+own (``share_with(target)``).
+
+Parity: ``aphrodite/model_executor/models/llama_eagle.py`` (``fc`` over ``cat(embeds, hidden)``, layer 0
+without input norm, checkpoint names without the ``model.`` prefix) and ``deepseek_mtp.py``
+(``enorm``/``hnorm``/``eh_proj``/``shared_head``, weights stored as layer ``num_hidden_layers + i``).
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from sonar_b200 import ops
+from sonar_b200.config import ModelConfig
+from sonar_b200.layers.attention import AttentionMetadata
+from sonar_b200.layers.embedding import ParallelLMHead, VocabParallelEmbedding
+from sonar_b200.layers.linear import ReplicatedLinear
+from sonar_b200.layers.norm import RMSNorm
+from sonar_b200.parallel.tp_ops import get_tp_context
+
+
+class _HeadBase(nn.Module):
+    """Embedding / LM-head sharing and the token-replicated layout check."""
+    needs_hidden = True
+
+    def _common(self, cfg: ModelConfig, device) -> None:
+        if get_tp_context().scattered:
+            raise ValueError("hidden-state draft heads need replicated activations between blocks: "
+                             "use SONAR_TP_COMM=custom or nccl")
+        self.cfg = cfg
+        self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device,
+                                                   "model.embed_tokens")
+        self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device, "lm_head")
+        self._own_embed = self._own_head = False
+
+    def share_with(self, target: nn.Module) -> None:
+        """Use the target's embedding table / LM head for whatever the checkpoint did not provide."""
+        if not self._own_embed:
+            self.embed_tokens = target.model.embed_tokens
+        if not self._own_head:
+            self.lm_head = target.lm_head
+
+    def _embed(self, input_ids: torch.Tensor) -> torch.Tensor:
+        return get_tp_context().embed_reduce(self.embed_tokens(input_ids))
+
+
+class EagleLlamaHead(_HeadBase):
+    stacked_params = [
+        (".q_proj.", ".qkv_proj.", "q"), (".k_proj.", ".qkv_proj.", "k"), (".v_proj.", ".qkv_proj.", "v"),
+        (".gate_proj.", ".gate_up_proj.", 0), (".up_proj.", ".gate_up_proj.", 1)]
+
+    def __init__(self, cfg: ModelConfig, device=None) -> None:
+        super().__init__()
+        from sonar_b200.models.llama import LlamaDecoderLayer
+        self._common(cfg, device)
+        h = cfg.hidden_size
+        self.fc = ReplicatedLinear(2 * h, h, bias=bool(cfg.get("eagle_fc_bias", False)), dtype=cfg.dtype, device=device,
+                                   prefix="fc")
+        self.layers = nn.ModuleDict({str(i): LlamaDecoderLayer(cfg, i, device, f"layers.{i}")
+                                     for i in range(cfg.num_layers)})
+        # the first layer reads the fused input as it is
+        self.skip_first_norm = bool(cfg.get("eagle_skip_first_input_norm", True))
+        self.norm = RMSNorm(h, cfg.get("rms_norm_eps", 1e-6), cfg.dtype, device) if cfg.get("eagle_final_norm", False) \
+            else None
+
+    def forward(self, input_ids: torch.Tensor, meta: AttentionMetadata, prev_hidden: torch.Tensor) -> torch.Tensor:
+        tp = get_tp_context()
+        h = self.fc.apply(torch.cat([self._embed(input_ids), prev_hidden.to(self.cfg.dtype)], dim=-1))
+        residual = None
+        for i, layer in enumerate(self.layers.values()):
+            if i == 0 and self.skip_first_norm:
+                residual = h
+                a = layer.self_attn(h, meta)
+                x, residual = tp.add_norm(a, residual, layer.post_attention_layernorm.weight,
+                                          layer.post_attention_layernorm.eps)
+                h = layer.mlp(x)
+            else:
+                h, residual = layer(h, residual, meta)
+        if self.norm is not None:
+            x, _ = tp.add_norm(h, residual, self.norm.weight, self.norm.eps)
+            return x
+        return h + residual
+
+    def compute_logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        return self.lm_head.logits(hidden)
+
+    def attention_layers(self):
+        return [layer.self_attn.attn for layer in self.layers.values()]
+
+    def map_checkpoint_name(self, name: str):
+        if "rotary_emb.inv_freq" in name:
+            return None
+        if name.startswith("model."):
+            name = name[len("model."):]
+        if name.startswith("embed_tokens."):
+            self._own_embed = True
+        if name.startswith("lm_head."):
+            self._own_head = True
+        shard = None
+        for frag, merged, sid in self.stacked_params:
+            if frag in name:
+                name, shard = name.replace(frag, merged), sid
+                break
+        return name, shard
+
+
+class DeepseekMTPHead(_HeadBase):
+    uses_mla = True
+    stacked_params = [(".gate_proj.", ".gate_up_proj.", 0), (".up_proj.", ".gate_up_proj.", 1)]
+
+    def __init__(self, cfg: ModelConfig, device=None) -> None:
+        super().__init__()
+        from sonar_b200.models.deepseek import DeepseekDecoderLayer
+        self._common(cfg, device)
+        h, eps = cfg.hidden_size, cfg.get("rms_norm_eps", 1e-6)
+        self.layer_idx = int(cfg.get("num_hidden_layers"))          # the module's index in the checkpoint
+        self.enorm = RMSNorm(h, eps, cfg.dtype, device)
+        self.hnorm = RMSNorm(h, eps, cfg.dtype, device)
+        self.eh_proj = ReplicatedLinear(2 * h, h, bias=False, dtype=cfg.dtype, device=device, prefix="eh_proj")
+        self.block = DeepseekDecoderLayer(cfg, self.layer_idx, device, f"model.layers.{self.layer_idx}")
+        self.shared_head_norm = RMSNorm(h, eps, cfg.dtype, device)
+
+    def forward(self, input_ids: torch.Tensor, meta: AttentionMetadata, prev_hidden: torch.Tensor) -> torch.Tensor:
+        e = ops.rms_norm(self._embed(input_ids), self.enorm.weight, self.enorm.eps)
+        p = ops.rms_norm(prev_hidden.to(self.cfg.dtype), self.hnorm.weight, self.hnorm.eps)
+        h = self.eh_proj.apply(torch.cat([e, p], dim=-1))
+        h, residual = self.block(h, None, meta)
+        return h + residual
+
+    def compute_logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        return self.lm_head.logits(ops.rms_norm(hidden, self.shared_head_norm.weight, self.shared_head_norm.eps))
+
+    def attention_layers(self):
+        return [self.block.self_attn]
+
+    def kv_cache_spec(self, block_size: int, dtype_bytes: int):
+        from sonar_b200.core.kv_cache_manager import KVCacheSpec
+        a = self.block.self_attn
+        return KVCacheSpec(block_size, 1, a.row, dtype_bytes, "mla", None, a.row)
+
+    def load_special_weight(self, name: str, tensor: torch.Tensor) -> bool:
+        """Routed-expert tensors and the router's correction bias of the module's own decoder layer."""
+        from sonar_b200.models.deepseek import DeepseekForCausalLM
+        pre = f"model.layers.{self.layer_idx}."
+        if not name.startswith(pre):
+            return False
+        return DeepseekForCausalLM.load_special_weight(self, "block." + name[len(pre):], tensor)
+
+    def map_checkpoint_name(self, name: str):
+        pre = f"model.layers.{self.layer_idx}."
+        if not name.startswith(pre) or "rotary_emb.inv_freq" in name:
+            return None                                   # the target's own layers
+        rest = name[len(pre):]
+        special = {"enorm.weight": "enorm.weight", "hnorm.weight": "hnorm.weight", "eh_proj.weight": "eh_proj.weight",
+                   "shared_head.norm.weight": "shared_head_norm.weight"}
+        if rest in special:
+            return special[rest], None
+        if rest.startswith("embed_tokens."):
+            self._own_embed = True
+            return rest, None
+        if rest == "shared_head.head.weight":
+            self._own_head = True
+            return "lm_head.weight", None
+        from sonar_b200.models.deepseek import DeepseekForCausalLM
+        return DeepseekForCausalLM.map_checkpoint_name(self, "block." + rest)       # the layer's usual renames

@@ -45,17 +45,26 @@ class DraftModelProposer:
         self.runner = runner
         self.k = int(spec_cfg.num_speculative_tokens)
         tgt = runner.model_cfg
-        mcfg = ModelConfig(model=spec_cfg.model, dtype=tgt.dtype, seed=tgt.seed + 1, max_model_len=tgt.max_model_len,
-                           quantization=spec_cfg.quantization, load_format=spec_cfg.load_format or tgt.load_format,
-                           skip_tokenizer_init=True)
+        mcfg = ModelConfig(model=spec_cfg.model or tgt.model, dtype=tgt.dtype, seed=tgt.seed + 1,
+                           max_model_len=tgt.max_model_len, quantization=spec_cfg.quantization,
+                           load_format=spec_cfg.load_format or tgt.load_format, skip_tokenizer_init=True)
         if mcfg.vocab_size != tgt.vocab_size:
             raise ValueError(f"draft model vocabulary ({mcfg.vocab_size}) differs from the target's ({tgt.vocab_size})")
+        mcfg.hf_config.update({k: v for k, v in tgt.hf_config.items() if k.startswith("_")})   # parallel layout flags
         self.model_cfg = mcfg
         with torch.inference_mode():
-            self.model = load_model(mcfg, runner.device)
+            self.model = load_model(mcfg, runner.device, cls=self.model_class(spec_cfg))
+        self.needs_hidden = bool(getattr(self.model, "needs_hidden", False))
+        if self.needs_hidden:
+            self.model.share_with(runner.model)
         self.layers = self.model.attention_layers()
+        self.mla = bool(getattr(self.model, "uses_mla", False))
         a = self.layers[0]
-        self.group, self.num_kv_heads, self.head_dim = a.num_heads // a.num_kv_heads, a.num_kv_heads, a.head_dim
+        if self.mla:
+            self.group = self.num_kv_heads = self.head_dim = 0
+            self.mla_row = a.row
+        else:
+            self.group, self.num_kv_heads, self.head_dim = a.num_heads // a.num_kv_heads, a.num_kv_heads, a.head_dim
         self.computed: dict[str, int] = {}          # request → tokens whose draft KV is valid
         dev, pin = runner.device, runner.is_cuda
         T, S = runner.max_tokens + runner.max_seqs, runner.max_seqs
@@ -64,7 +73,8 @@ class DraftModelProposer:
             return torch.zeros(n, dtype=dt, pin_memory=pin)
         self.h_ids, self.h_pos, self.h_slots = host(T, torch.int64), host(T, torch.int64), host(T, torch.int32)
         self.h_seq, self.h_qsl, self.h_sel = host(S, torch.int32), host(S + 1, torch.int32), host(2 * S, torch.int64)
-        self.h_last = host(S, torch.int64)
+        self.h_last, self.h_hid = host(S, torch.int64), host(T, torch.int64)
+        self.d_hid = torch.zeros(T, dtype=torch.int64, device=dev)
         self.d_ids = torch.zeros(T, dtype=runner.d_input_ids.dtype, device=dev)
         self.d_pos = torch.zeros(T, dtype=runner.d_positions.dtype, device=dev)
         self.d_slots = torch.zeros(T, dtype=torch.int32, device=dev)
@@ -77,16 +87,24 @@ class DraftModelProposer:
         self._copied = torch.cuda.Event() if pin else None
         self.stats = {"draft_steps": 0, "draft_tokens": 0}
 
+    @staticmethod
+    def model_class(spec_cfg):
+        """None: the class the draft checkpoint's architecture names."""
+        return None
+
     # ---- memory ------------------------------------------------------------------------------------
     def block_bytes(self, block_size: int, elem_bytes: int) -> int:
         """Bytes one KV block costs across the draft model's layers."""
+        if self.mla:
+            return len(self.layers) * block_size * self.mla_row * elem_bytes
         return len(self.layers) * 2 * self.num_kv_heads * block_size * self.head_dim * elem_bytes
 
     def bind_kv_caches(self, num_blocks: int, block_size: int, dtype) -> list[torch.Tensor]:
         caches = []
         for layer in self.layers:
-            c = torch.zeros((num_blocks, 2, self.num_kv_heads, block_size, self.head_dim), dtype=dtype,
-                            device=self.runner.device)
+            shape = ((num_blocks, block_size, self.mla_row) if self.mla
+                     else (num_blocks, 2, self.num_kv_heads, block_size, self.head_dim))
+            c = torch.zeros(shape, dtype=dtype, device=self.runner.device)
             layer.bind_kv_cache(c)
             caches.append(c)
         return caches
@@ -99,15 +117,17 @@ class DraftModelProposer:
         self.computed.pop(req_id, None)
 
     # ---- one forward pass of the draft model -----------------------------------------------------------
-    def _forward(self, ids: torch.Tensor, meta: AttentionMetadata) -> torch.Tensor:
+    def _forward(self, ids: torch.Tensor, meta: AttentionMetadata, prev: torch.Tensor | None = None) -> torch.Tensor:
         from sonar_b200.parallel.tp_ops import get_tp_context
         r = self.runner
         tp = get_tp_context()
         total = meta.num_tokens
         tp.begin_step(total)
-        if r.is_cuda:
+        if r.is_cuda and not self.mla:
             from sonar_b200.ops import cuda as cuda_ops
             cuda_ops.build_attention_work(meta, r, group=self.group, num_kv_heads=self.num_kv_heads)
+        if self.needs_hidden:
+            return self.model(ids, meta, prev)
         out = self.model(ids, meta, None)
         return tp.gather_tokens(out, total)
 
@@ -131,6 +151,20 @@ class DraftModelProposer:
         redo = sampling & (q_lens == 0)
         start[redo] -= 1
         q_lens[redo] = 1
+        out = self._run(rows, start, q_lens, upto, sampling, 0, None, None)
+        for i, row in enumerate(rows):
+            if q_lens[i] > 0:
+                self.computed[b.req_ids[row]] = int(upto[i])
+        return out
+
+    def _run(self, rows, start, q_lens, upto, sampling, shift: int, target_hidden, hid_start) -> list[list[int]]:
+        """One variable-length pass over positions ``[start, start + q_lens)`` of every row, reading token
+        ``position + shift`` at each, then the draft loop for the sampling rows.  ``target_hidden`` /
+        ``hid_start[i]`` (row of ``target_hidden`` that belongs to position ``start[i]``) feed heads that
+        continue the target's hidden states."""
+        r, b, bs = self.runner, self.runner.batch, self.runner.block_size
+        ns = len(rows)
+        out: list[list[int]] = [[] for _ in range(ns)]
         keep = np.nonzero(q_lens > 0)[0]
         if len(keep) == 0:
             return out
@@ -142,7 +176,7 @@ class DraftModelProposer:
         req_of_tok = np.repeat(np.arange(n), k_q)
         pos = k_start[req_of_tok] + (np.arange(total) - starts[:-1][req_of_tok])
         row_of_tok = k_rows[req_of_tok]
-        self.h_ids.numpy()[:total] = b.token_ids[row_of_tok, pos]
+        self.h_ids.numpy()[:total] = b.token_ids[row_of_tok, pos + shift]
         self.h_pos.numpy()[:total] = pos
         self.h_slots.numpy()[:total] = b.block_table_np[row_of_tok, pos // bs] * bs + pos % bs
         seq_lens = k_start + k_q
@@ -164,10 +198,13 @@ class DraftModelProposer:
             num_tokens=total, num_seqs=n, positions=self.d_pos[:total], slot_mapping=self.d_slots[:total],
             block_tables=bt, seq_lens=self.d_seq, query_start_loc=self.d_qsl, max_query_len=int(k_q.max()),
             max_seq_len=int(seq_lens.max()), query_lens_cpu=k_q, seq_lens_cpu=seq_lens)
-        hidden = self._forward(self.d_ids[:total], meta)
+        prev = None
+        if target_hidden is not None:
+            self.h_hid.numpy()[:total] = hid_start[keep][req_of_tok] + (np.arange(total) - starts[:-1][req_of_tok])
+            self.d_hid[:total].copy_(self.h_hid[:total], non_blocking=nbl)
+            prev = target_hidden.index_select(0, self.d_hid[:total])
+        hidden = self._forward(self.d_ids[:total], meta, prev)
         self.stats["draft_steps"] += 1
-        for i, row in zip(keep, k_rows):
-            self.computed[b.req_ids[row]] = int(upto[i])
         # ---- drafts for the sampling rows that have room for k more positions
         room = upto[keep] + self.k <= r.model_cfg.max_model_len
         d_idx = np.nonzero(sampling[keep] & room)[0]           # indices into the kept rows
@@ -184,8 +221,8 @@ class DraftModelProposer:
         sel.copy_(self.h_sel[S:S + m], non_blocking=nbl)
         if self._copied is not None:
             self._copied.record()
-        logits = self.model.compute_logits(hidden.index_select(0, self.d_last[:m]))
-        tok = logits.argmax(dim=-1)
+        prev = hidden.index_select(0, self.d_last[:m])
+        tok = self.model.compute_logits(prev).argmax(dim=-1)
         drafts = [tok]
         if self.k > 1:
             # single-token steps over the m drafting rows; metadata advances on the device
@@ -203,8 +240,8 @@ class DraftModelProposer:
                     num_tokens=m, num_seqs=m, positions=pos_m, slot_mapping=slots, block_tables=bt_m, seq_lens=seq_m,
                     query_start_loc=qsl_m, max_query_len=1, max_seq_len=int(base_seq.max()) + j, query_lens_cpu=ones,
                     seq_lens_cpu=base_seq + j)
-                hidden = self._forward(tok.to(self.d_ids.dtype), meta_j)
-                tok = self.model.compute_logits(hidden[:m]).argmax(dim=-1)
+                prev = self._forward(tok.to(self.d_ids.dtype), meta_j, prev)[:m]
+                tok = self.model.compute_logits(prev).argmax(dim=-1)
                 drafts.append(tok)
                 pos_m = pos_m + 1
                 seq_m = seq_m.clone()
@@ -217,3 +254,31 @@ class DraftModelProposer:
             out[int(keep[i])] = [int(t) for t in cols[:, c]]
         self.stats["draft_tokens"] += m * self.k
         return out
+
+
+class HiddenStateProposer(DraftModelProposer):
+    """EAGLE heads and DeepSeek multi-token-prediction modules: the draft continues the target's hidden
+    states, so it needs no catching up — every step it processes exactly the positions the target just
+    computed and kept, each paired with the token that follows it (``spec_heads`` gives the convention)."""
+
+    @staticmethod
+    def model_class(spec_cfg):
+        from sonar_b200.models import spec_heads
+        return spec_heads.EagleLlamaHead if spec_cfg.method == "eagle" else spec_heads.DeepseekMTPHead
+
+    @torch.inference_mode()
+    def propose_from_hidden(self, rows: np.ndarray, computed: np.ndarray, q_lens: np.ndarray, upto: np.ndarray,
+                            sampling: np.ndarray, hidden: torch.Tensor, step_starts: np.ndarray) -> list[list[int]]:
+        """``computed[i]``, ``q_lens[i]``: the positions ``[computed, computed + q_lens)`` of row i that the target
+        processed this step, whose hidden states are rows ``step_starts[i] …`` of ``hidden``."""
+        b = self.runner.batch
+        if len(rows) == 0:
+            return []
+        if self._copied is not None:
+            self._copied.synchronize()
+        known = b.num_tokens[rows].astype(np.int64)
+        # positions whose following token is known: kept positions of sampling rows, whole chunks otherwise
+        n_pos = np.where(sampling, upto - 1 - computed, np.minimum(q_lens, known - 1 - computed))
+        n_pos = np.maximum(n_pos, 0).astype(np.int64)
+        return self._run(rows, computed.astype(np.int64), n_pos, upto - 1, sampling, 1, hidden,
+                         step_starts[:-1].astype(np.int64))

@@ -179,11 +179,12 @@ class ModelRunner:
         self.eplb = None
         self.kv_connector = None
         self.drafter = None
-        if self.spec_cfg.method == "draft_model":
+        if self.spec_cfg.method in ("draft_model", "eagle", "mtp"):
             if self.pp is not None:
                 raise ValueError("draft-model speculative decoding does not run under pipeline parallelism")
-            from sonar_b200.sample.draft_model import DraftModelProposer
-            self.drafter = DraftModelProposer(self, self.spec_cfg)
+            from sonar_b200.sample.draft_model import DraftModelProposer, HiddenStateProposer
+            cls = DraftModelProposer if self.spec_cfg.method == "draft_model" else HiddenStateProposer
+            self.drafter = cls(self, self.spec_cfg)
             logger.info("draft model %s: %d layers, %d drafts per step", self.spec_cfg.model,
                         len(self.drafter.layers), self.drafter.k)
         pc = self.cfg.parallel
@@ -535,7 +536,7 @@ class ModelRunner:
         idx = np.nonzero(samples)[0]
         if len(idx) == 0:
             if self.drafter is not None:      # prompt chunks: the draft model's KV follows the target's
-                self.drafter.propose(rows, np.minimum(computed_after, known).astype(np.int64), samples)
+                self._draft(rows, q_lens, np.minimum(computed_after, known).astype(np.int64), samples, hidden, starts)
             return out
         # logits rows: the last position, plus one per draft token before it
         gather: list[int] = []
@@ -634,10 +635,17 @@ class ModelRunner:
         if self.drafter is not None:
             upto = np.minimum(computed_after, known).astype(np.int64)
             upto[idx] = b.num_tokens[rows[idx]]
-            spec_out = self.drafter.propose(rows, upto, samples)
+            spec_out = self._draft(rows, q_lens, upto, samples, hidden, starts)
             self.stats.update(self.drafter.stats)
         out.spec_token_ids = spec_out
         return out
+
+    def _draft(self, rows, q_lens, upto, samples, hidden, starts) -> list[list[int]]:
+        d = self.drafter
+        if d.needs_hidden:
+            return d.propose_from_hidden(rows, self.batch.num_computed[rows], q_lens.astype(np.int64), upto, samples,
+                                         hidden, starts)
+        return d.propose(rows, upto, samples)
 
     def _prompt_logprobs(self, so, hidden, rows, q_lens, starts, req_ids, out: ModelRunnerOutput) -> None:
         b = self.batch

@@ -78,3 +78,76 @@ def test_speculative_config_validation():
                      speculative_config='{"method": "ngram", "num_speculative_tokens": 4, "prompt_lookup_max": 5}'
                      ).create_engine_config()
     assert cfg.speculative.method == "ngram" and cfg.speculative.prompt_lookup_max == 5
+
+
+def test_eagle_head_lossless_and_loads_hf_names(tmp_path):
+    """An EAGLE head (random weights here, so few drafts are accepted) never changes greedy output; its
+    checkpoint uses un-prefixed names and shares embedding and LM head with the target when it has none."""
+    import json
+
+    from sonar_b200.config import ARCH_PRESETS
+    from sonar_b200.loader.weights import save_checkpoint
+    tgt = make_checkpoint(str(tmp_path / "t"), "tiny-llama-128", dtype=torch.float32)
+    cfg = dict(ARCH_PRESETS["tiny-llama-128"])
+    cfg["num_hidden_layers"] = 1
+    full = make_checkpoint(str(tmp_path / "one"), "tiny-llama-128", dtype=torch.float32, seed=9)
+    from sonar_b200.loader.weights import read_safetensors
+    src = dict(read_safetensors(os.path.join(full, "model.safetensors")))
+    h = cfg["hidden_size"]
+    g = torch.Generator().manual_seed(1)
+    head = {k[len("model."):]: v for k, v in src.items() if k.startswith("model.layers.0.")}
+    head["fc.weight"] = torch.randn(h, 2 * h, generator=g) * 0.05
+    eagle_dir = str(tmp_path / "eagle")
+    cfg["architectures"] = ["LlamaForCausalLM"]
+    save_checkpoint(eagle_dir, cfg, head)
+    sp = SamplingParams(temperature=0, max_tokens=14, ignore_eos=True)
+    base = LLM(tgt, **COMMON)
+    want = [o.outputs[0].token_ids for o in base.generate(_prompts(), sp)]
+    base.shutdown()
+    spec = LLM(tgt, speculative_config={"method": "eagle", "model": eagle_dir, "num_speculative_tokens": 3}, **COMMON)
+    runner = spec.llm_engine.core.engine_core.executor.worker.runner
+    d = runner.drafter
+    assert d.needs_hidden and d.model.embed_tokens is runner.model.model.embed_tokens
+    assert d.model.lm_head is runner.model.lm_head
+    assert torch.equal(d.model.fc.weight.float(), head["fc.weight"])
+    got = [o.outputs[0].token_ids for o in spec.generate(_prompts(), sp)]
+    st = spec.llm_engine.get_stats()
+    spec.shutdown()
+    assert got == want
+    assert st["scheduler"].spec_num_drafts > 0 and st["workers"][0]["draft_steps"] > 0
+
+
+def test_deepseek_mtp_module_lossless():
+    """DeepSeek's multi-token-prediction module (MLA attention + MoE block behind enorm/hnorm/eh_proj) drafts
+    for the DeepSeek target; greedy output is unchanged and the module's latent cache shares the block tables."""
+    kw = dict(dtype="float32", max_model_len=256, num_gpu_blocks_override=96, max_num_seqs=4,
+              max_num_batched_tokens=48, device="cpu", seed=0)
+    sp = SamplingParams(temperature=0, max_tokens=10, ignore_eos=True)
+    base = LLM("tiny-deepseek", **kw)
+    want = [o.outputs[0].token_ids for o in base.generate(_prompts()[:3], sp)]
+    base.shutdown()
+    spec = LLM("tiny-deepseek", speculative_config={"method": "mtp", "num_speculative_tokens": 2}, **kw)
+    runner = spec.llm_engine.core.engine_core.executor.worker.runner
+    assert runner.drafter.mla and len(runner.kv_caches) == runner.num_local_layers() + 1
+    got = [o.outputs[0].token_ids for o in spec.generate(_prompts()[:3], sp)]
+    st = spec.llm_engine.get_stats()
+    spec.shutdown()
+    assert got == want and st["scheduler"].spec_num_drafts > 0
+
+
+def test_mtp_checkpoint_names_map_to_the_module():
+    from sonar_b200.config import ModelConfig
+    from sonar_b200.models.spec_heads import DeepseekMTPHead
+    cfg = ModelConfig(model="tiny-deepseek", dtype=torch.float32, load_format="dummy", skip_tokenizer_init=True)
+    head = DeepseekMTPHead(cfg, torch.device("cpu"))
+    L = head.layer_idx
+    m = head.map_checkpoint_name
+    assert m(f"model.layers.{L}.enorm.weight") == ("enorm.weight", None)
+    assert m(f"model.layers.{L}.eh_proj.weight") == ("eh_proj.weight", None)
+    assert m(f"model.layers.{L}.shared_head.norm.weight") == ("shared_head_norm.weight", None)
+    assert m(f"model.layers.{L}.shared_head.head.weight") == ("lm_head.weight", None) and head._own_head
+    assert m(f"model.layers.{L}.self_attn.kv_a_proj_with_mqa.weight")[0] == "block.self_attn.kv_a_proj_with_mqa.weight"
+    assert m(f"model.layers.{L}.mlp.shared_experts.up_proj.weight") == ("block.mlp.shared_experts.gate_up_proj.weight", 1)
+    assert m(f"model.layers.{L - 1}.self_attn.o_proj.weight") is None and m("model.norm.weight") is None
+    # routed experts of the module's layer go through the expert loader
+    assert head.load_special_weight("model.layers.0.mlp.experts.0.up_proj.weight", torch.zeros(1)) is False

@@ -280,21 +280,27 @@ class SchedulerConfig:
 class SpeculativeConfig:
     """Parity: ``aphrodite/config/speculative.py`` (``--speculative-config`` JSON: ``method``, ``model``,
     ``num_speculative_tokens``, ``prompt_lookup_max/min``)."""
-    method: str | None = None          # None | ngram | draft_model | eagle | mtp (alias deepseek_mtp)
+    method: str | None = None          # None | ngram | suffix | draft_model | eagle | mtp (alias deepseek_mtp) | medusa
     num_speculative_tokens: int = 0
     prompt_lookup_max: int = 4
     prompt_lookup_min: int = 2
     model: str | None = None           # draft model: checkpoint directory or architecture preset
     quantization: str | None = None
     load_format: str | None = None     # defaults to the target's
+    medusa_num_layers: int = 1         # residual blocks per Medusa head
+    suffix_decoding_max_tree_depth: int = 24
+    suffix_decoding_max_cached_requests: int = 1000
+    suffix_decoding_max_spec_factor: float = 1.0
+    suffix_decoding_min_token_prob: float = 0.1
 
     def __post_init__(self) -> None:
         if self.method is None and self.model is not None:
             self.method = "draft_model"
         if self.method == "deepseek_mtp":
             self.method = "mtp"
-        if self.method not in (None, "ngram", "draft_model", "eagle", "mtp"):
-            raise ValueError(f"unknown speculative method {self.method!r} (ngram, draft_model, eagle, mtp)")
+        if self.method not in (None, "ngram", "suffix", "draft_model", "eagle", "mtp", "medusa"):
+            raise ValueError(f"unknown speculative method {self.method!r} "
+                             "(ngram, suffix, draft_model, eagle, mtp, medusa)")
         if self.method in ("draft_model", "eagle") and not self.model:
             raise ValueError(f"speculative method {self.method} needs a draft model")
         if self.method is not None and self.num_speculative_tokens <= 0:

@@ -282,3 +282,92 @@ class HiddenStateProposer(DraftModelProposer):
         n_pos = np.maximum(n_pos, 0).astype(np.int64)
         return self._run(rows, computed.astype(np.int64), n_pos, upto - 1, sampling, 1, hidden,
                          step_starts[:-1].astype(np.int64))
+
+
+class MedusaProposer:
+    """Medusa: ``k`` small heads on the target's last hidden state, head ``i`` predicting the token ``i + 1``
+    places after the one the target just sampled.  Each head is ``num_layers`` residual blocks
+    (``x + SiLU(W x + b)``) and its own vocabulary projection.  No attention and no KV cache: the drafts of a
+    step are one batched pass over the hidden states of the rows that sampled.
+
+    Checkpoint names: ``blocks.{i}.layers.{j}.weight|bias`` and ``lm_heads.{i}.weight`` (the layout the
+    reference loads).  Parity: ``aphrodite/model_executor/models/medusa.py`` and
+    ``aphrodite/v1/spec_decode/medusa.py``.
+    """
+    needs_hidden = True
+    mla = False
+
+    def __init__(self, runner, spec_cfg) -> None:
+        from sonar_b200.loader.weights import _iter_checkpoint
+        self.runner = runner
+        self.k = int(spec_cfg.num_speculative_tokens)
+        cfg = runner.model_cfg
+        h, v, dev, dt = cfg.hidden_size, cfg.vocab_size, runner.device, cfg.dtype
+        self.num_layers = int(spec_cfg.medusa_num_layers)
+        gen = torch.Generator().manual_seed(cfg.seed + 7)
+
+        def rnd(*shape):
+            return (torch.randn(*shape, generator=gen) * 0.02).to(dt).to(dev)
+        self.w = [[rnd(h, h) for _ in range(self.num_layers)] for _ in range(self.k)]
+        self.b = [[torch.zeros(h, dtype=dt, device=dev) for _ in range(self.num_layers)] for _ in range(self.k)]
+        self.heads = [rnd(v, h) for _ in range(self.k)]
+        load_format = spec_cfg.load_format or cfg.load_format
+        if load_format != "dummy":
+            if not spec_cfg.model:
+                raise ValueError("speculative method medusa needs a checkpoint of heads")
+            seen = 0
+            for name, t in _iter_checkpoint(spec_cfg.model):
+                parts = name.split(".")
+                if parts[0] == "blocks" and int(parts[1]) < self.k and int(parts[3]) < self.num_layers:
+                    (self.w if parts[4] == "weight" else self.b)[int(parts[1])][int(parts[3])].copy_(t)
+                    seen += 1
+                elif parts[0] == "lm_heads" and int(parts[1]) < self.k:
+                    self.heads[int(parts[1])].copy_(t)
+                    seen += 1
+            if seen == 0:
+                raise RuntimeError(f"no Medusa tensor found in {spec_cfg.model}")
+        S = runner.max_seqs
+        self.h_idx = torch.zeros(S, dtype=torch.int64, pin_memory=runner.is_cuda)
+        self.d_idx = torch.zeros(S, dtype=torch.int64, device=dev)
+        self.h_out = torch.zeros((max(self.k, 1), S), dtype=torch.int64, pin_memory=runner.is_cuda)
+        self.layers: list = []
+        self.stats = {"draft_steps": 0, "draft_tokens": 0}
+
+    def block_bytes(self, block_size: int, elem_bytes: int) -> int:
+        return 0
+
+    def bind_kv_caches(self, num_blocks: int, block_size: int, dtype) -> list[torch.Tensor]:
+        return []
+
+    def on_add(self, req_id: str, num_computed: int) -> None:
+        pass
+
+    def on_remove(self, req_id: str) -> None:
+        pass
+
+    @torch.inference_mode()
+    def propose_from_hidden(self, rows, computed, q_lens, upto, sampling, hidden, step_starts) -> list[list[int]]:
+        out: list[list[int]] = [[] for _ in range(len(rows))]
+        idx = np.nonzero(sampling & (upto + self.k <= self.runner.model_cfg.max_model_len))[0]
+        m = len(idx)
+        if m == 0:
+            return out
+        # hidden state at the last position the target kept for each sampling row: the one whose logits gave
+        # the newest token
+        self.h_idx.numpy()[:m] = step_starts[:-1][idx] + (upto[idx] - 2 - computed[idx])
+        self.d_idx[:m].copy_(self.h_idx[:m], non_blocking=False)
+        x0 = hidden.index_select(0, self.d_idx[:m])
+        toks = []
+        for i in range(self.k):
+            x = x0
+            for w, b in zip(self.w[i], self.b[i]):
+                x = x + torch.nn.functional.silu(torch.nn.functional.linear(x, w, b))
+            toks.append(torch.nn.functional.linear(x, self.heads[i]).argmax(dim=-1))
+        host = self.h_out[:self.k, :m]
+        host.copy_(torch.stack(toks), non_blocking=False)
+        cols = host.numpy()
+        for c, i in enumerate(idx):
+            out[int(i)] = [int(t) for t in cols[:, c]]
+        self.stats["draft_steps"] += 1
+        self.stats["draft_tokens"] += m * self.k
+        return out

@@ -169,6 +169,10 @@ class ModelRunner:
         if self.spec_cfg.method == "ngram":
             from sonar_b200.sample.spec_decode import NgramProposer
             self._ngram = NgramProposer(self.spec_cfg)
+        self._suffix = None
+        if self.spec_cfg.method == "suffix":
+            from sonar_b200.sample.spec_decode import SuffixProposer
+            self._ngram = self._suffix = SuffixProposer(self.spec_cfg)
 
     # --------------------------------------------------------------- set-up
     def load_model(self) -> None:
@@ -179,11 +183,12 @@ class ModelRunner:
         self.eplb = None
         self.kv_connector = None
         self.drafter = None
-        if self.spec_cfg.method in ("draft_model", "eagle", "mtp"):
+        if self.spec_cfg.method in ("draft_model", "eagle", "mtp", "medusa"):
             if self.pp is not None:
                 raise ValueError("draft-model speculative decoding does not run under pipeline parallelism")
-            from sonar_b200.sample.draft_model import DraftModelProposer, HiddenStateProposer
-            cls = DraftModelProposer if self.spec_cfg.method == "draft_model" else HiddenStateProposer
+            from sonar_b200.sample.draft_model import DraftModelProposer, HiddenStateProposer, MedusaProposer
+            cls = {"draft_model": DraftModelProposer, "medusa": MedusaProposer}.get(self.spec_cfg.method,
+                                                                                   HiddenStateProposer)
             self.drafter = cls(self, self.spec_cfg)
             logger.info("draft model %s: %d layers, %d drafts per step", self.spec_cfg.model,
                         len(self.drafter.layers), self.drafter.k)
@@ -302,6 +307,13 @@ class ModelRunner:
         if so.kv_stores or so.kv_loads or so.kv_ext_loads:
             self._run_kv_transfers(so)
         b = self.batch
+        if self._suffix is not None:
+            for rid in so.finished_req_ids:
+                row = b.index.get(rid)
+                if row is not None:
+                    self._suffix.finish(rid, b.token_ids[row, :int(b.num_tokens[row])], int(b.num_prompt[row]))
+            for rid in so.preempted_req_ids:
+                self._suffix.local.pop(rid, None)
         for rid in so.finished_req_ids:
             b.remove(rid)
         for rid in so.preempted_req_ids:
@@ -631,7 +643,9 @@ class ModelRunner:
             if want_lp:
                 out.logprobs[i] = res.logprobs[lo:lo + len(toks)]
             if spec_out is not None:
-                spec_out[i] = self._ngram.propose(b.token_ids[r, :nt + len(toks)])
+                ctx = b.token_ids[r, :nt + len(toks)]
+                spec_out[i] = (self._suffix.propose(ctx, req_ids[i]) if self._suffix is not None
+                               else self._ngram.propose(ctx))
         if self.drafter is not None:
             upto = np.minimum(computed_after, known).astype(np.int64)
             upto[idx] = b.num_tokens[rows[idx]]

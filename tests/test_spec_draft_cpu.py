@@ -71,7 +71,7 @@ def test_speculative_config_validation():
     with pytest.raises(ValueError):
         SpeculativeConfig(method="draft_model", num_speculative_tokens=2)
     with pytest.raises(ValueError):
-        SpeculativeConfig(method="medusa", num_speculative_tokens=2)
+        SpeculativeConfig(method="lookahead", num_speculative_tokens=2)
     with pytest.raises(ValueError):
         SpeculativeConfig(method="ngram")
     cfg = EngineArgs(model="tiny-llama", device="cpu", dtype="float32",
@@ -151,3 +151,63 @@ def test_mtp_checkpoint_names_map_to_the_module():
     assert m(f"model.layers.{L - 1}.self_attn.o_proj.weight") is None and m("model.norm.weight") is None
     # routed experts of the module's layer go through the expert loader
     assert head.load_special_weight("model.layers.0.mlp.experts.0.up_proj.weight", torch.zeros(1)) is False
+
+
+def test_suffix_decoding_proposer_and_engine():
+    import numpy as np
+
+    from sonar_b200.sample.spec_decode import SuffixProposer
+    cfg = SpeculativeConfig(method="suffix", num_speculative_tokens=6, suffix_decoding_max_tree_depth=8)
+    p = SuffixProposer(cfg)
+    ctx = np.array([5, 6, 7, 8, 9, 1, 2, 5, 6, 7])
+    assert p.propose(ctx, "a") == [8, 9, 1, 2]                    # a match of 3 tokens allows 1.0 × 3 + 1 drafts
+    assert p.propose(np.array([40, 41]), "b") == []
+    # a finished request's output serves other requests
+    p.finish("a", np.array([1, 2, 3, 50, 51, 52, 53, 54]), 3)
+    assert "a" not in p.local
+    assert p.propose(np.array([9, 9, 50, 51]), "c") == [52, 53, 54]
+    # an ambiguous continuation stops the draft where its probability drops
+    q = SuffixProposer(SpeculativeConfig(method="suffix", num_speculative_tokens=4, suffix_decoding_min_token_prob=0.6))
+    q.finish("x", np.array([0, 1, 2, 3, 1, 2, 4]), 1)
+    assert q.propose(np.array([7, 1]), "y") == [2]               # after "1 2" comes 3 or 4 with p = 0.5 each
+    common = dict(dtype="float32", max_model_len=512, num_gpu_blocks_override=128, max_num_seqs=4,
+                  max_num_batched_tokens=64, device="cpu")
+    sp = SamplingParams(temperature=0, max_tokens=24, ignore_eos=True)
+    prompts = [{"prompt_token_ids": [7, 8, 9, 10] * 6}, {"prompt_token_ids": [3, 1, 4, 1, 5, 9, 2, 6, 5, 3, 5]}]
+    base = LLM("tiny-llama", **common)
+    want = [o.outputs[0].token_ids for o in base.generate(prompts, sp)]
+    base.shutdown()
+    spec = LLM("tiny-llama", speculative_config={"method": "suffix", "num_speculative_tokens": 4}, **common)
+    got = [o.outputs[0].token_ids for o in spec.generate(prompts, sp)]
+    again = [o.outputs[0].token_ids for o in spec.generate(prompts, sp)]     # now the shared trie knows the answers
+    st = spec.llm_engine.get_stats()["scheduler"]
+    spec.shutdown()
+    assert got == want and again == want
+    assert st.spec_num_drafts > 0 and st.spec_num_accepted > 0
+
+
+def test_medusa_heads_lossless_and_loaded(tmp_path):
+    from sonar_b200.config import ARCH_PRESETS
+    from sonar_b200.loader.weights import save_checkpoint
+    tgt = make_checkpoint(str(tmp_path / "t"), "tiny-llama-128", dtype=torch.float32)
+    cfg = dict(ARCH_PRESETS["tiny-llama-128"])
+    h, v = cfg["hidden_size"], cfg["vocab_size"]
+    g = torch.Generator().manual_seed(2)
+    heads = {}
+    for i in range(2):
+        heads[f"blocks.{i}.layers.0.weight"] = torch.randn(h, h, generator=g) * 0.05
+        heads[f"blocks.{i}.layers.0.bias"] = torch.randn(h, generator=g) * 0.05
+        heads[f"lm_heads.{i}.weight"] = torch.randn(v, h, generator=g) * 0.05
+    mdir = str(tmp_path / "medusa")
+    save_checkpoint(mdir, {"hidden_size": h, "vocab_size": v, "num_heads": 2, "num_hidden_layers": 1}, heads)
+    sp = SamplingParams(temperature=0, max_tokens=12, ignore_eos=True)
+    base = LLM(tgt, **COMMON)
+    want = [o.outputs[0].token_ids for o in base.generate(_prompts(), sp)]
+    base.shutdown()
+    spec = LLM(tgt, speculative_config={"method": "medusa", "model": mdir, "num_speculative_tokens": 2}, **COMMON)
+    d = spec.llm_engine.core.engine_core.executor.worker.runner.drafter
+    assert torch.equal(d.heads[1].float(), heads["lm_heads.1.weight"]) and torch.equal(d.b[0][0].float(), heads["blocks.0.layers.0.bias"])
+    got = [o.outputs[0].token_ids for o in spec.generate(_prompts(), sp)]
+    st = spec.llm_engine.get_stats()
+    spec.shutdown()
+    assert got == want and st["scheduler"].spec_num_drafts > 0 and st["workers"][0]["draft_tokens"] > 0

@@ -50,6 +50,8 @@ class DraftModelProposer:
                            load_format=spec_cfg.load_format or tgt.load_format, skip_tokenizer_init=True)
         if mcfg.vocab_size != tgt.vocab_size:
             raise ValueError(f"draft model vocabulary ({mcfg.vocab_size}) differs from the target's ({tgt.vocab_size})")
+        if not spec_cfg.model:
+            mcfg.hf_config.update(tgt.hf_config)          # a module of the target's own checkpoint: same overrides
         mcfg.hf_config.update({k: v for k, v in tgt.hf_config.items() if k.startswith("_")})   # parallel layout flags
         self.model_cfg = mcfg
         with torch.inference_mode():

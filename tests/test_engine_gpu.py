@@ -154,3 +154,34 @@ def test_draft_model_speculation_on_gpu():
     same = sum(a == b for g, w in zip(got, want) for a, b in zip(g, w))
     assert same >= 0.9 * 16 * len(prompts), (got, want)
     assert st["scheduler"].spec_num_drafts > 0 and st["workers"][0]["draft_steps"] > 0
+
+
+@pytest.mark.parametrize("model,spec", [
+    ("tiny-llama-128", {"method": "eagle", "model": "tiny-llama-128", "num_speculative_tokens": 3}),
+    ("tiny-llama-128", {"method": "medusa", "num_speculative_tokens": 2}),
+    ("tiny-deepseek", {"method": "mtp", "num_speculative_tokens": 2}),
+    ("tiny-llama-128", {"method": "suffix", "num_speculative_tokens": 4}),
+])
+def test_hidden_state_proposers_on_gpu(model, spec):
+    """EAGLE head, Medusa heads, the DeepSeek multi-token-prediction module and suffix decoding drive the CUDA
+    kernels (varlen draft pass, device-advanced single-token passes, MLA latent cache for the MTP block); the
+    verified greedy output stays the target's, up to rare bf16 near-ties in the multi-position steps."""
+    from sonar_b200 import LLM, SamplingParams
+    kw = dict(model=model, max_model_len=512, num_gpu_blocks_override=256, max_num_seqs=8,
+              max_num_batched_tokens=128, seed=0)
+    if model == "tiny-deepseek":
+        kw["hf_overrides"] = {"index_n_heads": 8}      # the GEMM kernels want output widths in multiples of 8
+    prompts = [{"prompt_token_ids": [(11 * i + 5 * j) % 500 + 3 for j in range(20 + 11 * i)]} for i in range(5)]
+    sp = SamplingParams(max_tokens=12, temperature=0, ignore_eos=True)
+    base = LLM(**kw)
+    want = [o.outputs[0].token_ids for o in base.generate(prompts, sp)]
+    base.shutdown()
+    llm = LLM(**kw, speculative_config=spec)
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    st = llm.llm_engine.get_stats()
+    llm.shutdown()
+    assert all(len(g) == 12 for g in got)
+    same = sum(a == b for g, w in zip(got, want) for a, b in zip(g, w))
+    assert same >= 0.85 * 12 * len(prompts), (got, want)
+    if spec["method"] != "suffix":
+        assert st["scheduler"].spec_num_drafts > 0

@@ -180,6 +180,15 @@ class AsyncLLM:
     async def is_sleeping(self) -> bool:
         return await self.core.call_utility_async("is_sleeping")
 
+    async def init_weight_transfer_engine(self, backend: str, init_info: dict | None = None) -> bool:
+        return await self.core.call_utility_async("init_weight_transfer_engine", backend, init_info)
+
+    async def update_weights(self, update_info: dict) -> int:
+        return await self.core.call_utility_async("update_weights", update_info)
+
+    async def get_world_size(self) -> int:
+        return await self.core.call_utility_async("get_world_size")
+
     async def start_profile(self, trace_dir: str | None = None) -> bool:
         return await self.core.call_utility_async("start_profile", trace_dir)
 

@@ -168,6 +168,21 @@ class EngineCore:
     def is_sleeping(self) -> bool:
         return self.sleeping
 
+    def init_weight_transfer_engine(self, backend: str, init_info: dict | None = None) -> bool:
+        return all(self.executor.collective_rpc("init_weight_transfer_engine", backend, init_info))
+
+    def update_weights(self, update_info: dict) -> int:
+        """New weights for every worker, in place; cached KV of the old weights is dropped.  Refused while
+        requests are running: their KV would mix two policies."""
+        if self.scheduler.has_unfinished_requests():
+            raise ValueError("cannot update weights with unfinished requests (pause and drain, or abort them)")
+        n = min(self.executor.collective_rpc("update_weights", update_info))
+        self.scheduler.reset_prefix_cache()
+        return n
+
+    def get_world_size(self) -> int:
+        return self.cfg.parallel.world_size
+
     def start_profile(self, trace_dir: str | None = None) -> bool:
         return all(self.executor.collective_rpc("start_profile", trace_dir))
 

@@ -163,6 +163,12 @@ class LLMEngine:
     def is_sleeping(self) -> bool:
         return self.core.call_utility("is_sleeping")
 
+    def init_weight_transfer_engine(self, backend: str, init_info: dict | None = None) -> bool:
+        return self.core.call_utility("init_weight_transfer_engine", backend, init_info)
+
+    def update_weights(self, update_info: dict) -> int:
+        return self.core.call_utility("update_weights", update_info)
+
     def start_profile(self, trace_dir: str | None = None) -> bool:
         return self.core.call_utility("start_profile", trace_dir)
 

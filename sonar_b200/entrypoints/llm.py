@@ -138,5 +138,14 @@ class LLM:
     def reset_prefix_cache(self) -> bool:
         return self.llm_engine.reset_prefix_cache()
 
+    def init_weight_transfer_engine(self, backend: str = "checkpoint", init_info: dict | None = None) -> bool:
+        """Set up how new weights reach the workers (``checkpoint`` | ``store`` | ``nccl``)."""
+        return self.llm_engine.init_weight_transfer_engine(backend, init_info)
+
+    def update_weights(self, update_info: dict) -> int:
+        """Replace the model's weights in place (``{"path": dir}`` for the checkpoint backend, the trainer's
+        ``update_info`` otherwise) and drop the prefix cache.  Returns the number of tensors applied."""
+        return self.llm_engine.update_weights(update_info)
+
     def shutdown(self) -> None:
         self.llm_engine.shutdown()

@@ -20,7 +20,7 @@ import uuid
 from typing import Any
 
 import torch
-from fastapi import FastAPI
+from fastapi import FastAPI, Request
 from fastapi.responses import JSONResponse
 
 from sonar_b200.sampling_params import PoolingParams, SamplingParams
@@ -78,6 +78,29 @@ def register(app: FastAPI, state) -> None:
         except Exception as e:  # noqa: BLE001
             return _error(str(e))
         return {"sleeping": await state.engine.is_sleeping(), "mapped_bytes": n}
+
+    # ------------------------------------------------------------------ RLHF weight updates
+    @app.post("/init_weight_transfer_engine")
+    async def init_weight_transfer_engine(raw: Request):
+        body = await raw.json()
+        try:
+            ok = await state.engine.init_weight_transfer_engine(body.get("backend", "checkpoint"), body.get("init_info"))
+        except Exception as e:  # noqa: BLE001
+            return JSONResponse({"error": {"message": str(e), "type": "BadRequestError"}}, status_code=400)
+        return {"ok": bool(ok)}
+
+    @app.post("/update_weights")
+    async def update_weights(raw: Request):
+        body = await raw.json()
+        try:
+            n = await state.engine.update_weights(body.get("update_info") or body)
+        except Exception as e:  # noqa: BLE001
+            return JSONResponse({"error": {"message": str(e), "type": "BadRequestError"}}, status_code=400)
+        return {"updated_tensors": n}
+
+    @app.get("/get_world_size")
+    async def get_world_size():
+        return {"world_size": await state.engine.get_world_size()}
 
     @app.get("/is_sleeping")
     async def is_sleeping():

@@ -182,10 +182,15 @@ def load_model(cfg: EngineConfig | ModelConfig, device: torch.device | str, cls=
         logger.info("loaded %d tensors from %s", len(loaded), mcfg.checkpoint_dir)
         if not loaded:
             raise RuntimeError(f"no tensor of {mcfg.checkpoint_dir} matched the model")
+    finish_loading(model)
+    return model
+
+
+def finish_loading(model: nn.Module) -> None:
+    """Post-load processing of every layer (weight repacking, fp8 scales); also run after an in-place update."""
     for mod in model.modules():
         if isinstance(mod, LinearBase):
             mod.method.process_after_load(mod)
         post = getattr(mod, "process_after_load", None)
         if post is not None and not isinstance(mod, LinearBase):
             post()
-    return model

@@ -204,6 +204,42 @@ class Worker:
     def list_loras(self) -> list[str]:
         return self._lora().list_adapters()
 
+    # in-place weight updates (RLHF) -------------------------------------------------
+    def init_weight_transfer_engine(self, backend: str, init_info: dict | None = None) -> bool:
+        from sonar_b200.distributed.weight_transfer import create_engine
+        from sonar_b200.parallel import state
+        old = getattr(self, "weight_transfer", None)
+        if old is not None:
+            old.shutdown()
+        self.weight_transfer = create_engine(backend, self.device, state.tp_rank() if state.model_parallel_is_initialized() else 0,
+                                             state.tp_world_size())
+        self.weight_transfer.init_transfer_engine(init_info or {})
+        return True
+
+    @torch.inference_mode()
+    def update_weights(self, update_info: dict) -> int:
+        """Receive new weights through the transfer engine and load them over the current ones (same name
+        mapping and shard slicing as checkpoint loading).  Parameters keep their addresses unless a layer's
+        post-load step rebuilds them, in which case the captured decode graphs are rebuilt too.  Returns the
+        number of checkpoint tensors applied."""
+        from sonar_b200.loader.weights import finish_loading, load_weights_from
+        if getattr(self, "weight_transfer", None) is None:
+            self.init_weight_transfer_engine("checkpoint")
+        model = self.runner.model
+        before = {n: p.data_ptr() for n, p in model.named_parameters()}
+        loaded = load_weights_from(model, self.weight_transfer.receive(update_info))
+        if not loaded:
+            raise RuntimeError("weight update matched no parameter of the model")
+        finish_loading(model)
+        moved = [n for n, p in model.named_parameters() if before.get(n) != p.data_ptr()]
+        if moved and self.runner.graphs:
+            logger.info("weight update moved %d parameters: recapturing decode graphs", len(moved))
+            self.runner.graphs.clear()
+            self.compile_or_warm_up_model()
+        if self.cfg.device == "cuda":
+            torch.cuda.synchronize()
+        return len(loaded)
+
     def check_health(self) -> bool:
         return True
 

@@ -186,6 +186,12 @@ class AsyncLLM:
     async def update_weights(self, update_info: dict) -> int:
         return await self.core.call_utility_async("update_weights", update_info)
 
+    async def fault_status(self) -> dict:
+        return await self.core.call_utility_async("fault_status")
+
+    async def handle_fault(self, instruction: str, params: dict | None = None) -> dict:
+        return await self.core.call_utility_async("handle_fault", instruction, params)
+
     async def get_world_size(self) -> int:
         return await self.core.call_utility_async("get_world_size")
 

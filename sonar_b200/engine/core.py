@@ -9,6 +9,8 @@ Parity: ``aphrodite/v1/engine/core.py:102`` (``_initialize_kv_caches`` :232,
 """
 from __future__ import annotations
 
+import os
+
 import time
 from typing import Any
 
@@ -182,6 +184,18 @@ class EngineCore:
 
     def get_world_size(self) -> int:
         return self.cfg.parallel.world_size
+
+    def fault_status(self) -> dict:
+        """One engine core: healthy while its executor has not reported a lost worker."""
+        bad = bool(getattr(self.executor, "is_failed", False))
+        return {"healthy": not bad, "serving": not bad, "restarts": 0,
+                "replicas": [{"index": self.cfg.parallel.data_parallel_rank or 0, "state": "dead" if bad else "alive",
+                              "reason": "a worker process died" if bad else None,
+                              "in_flight": self.scheduler.get_num_unfinished_requests(), "pid": os.getpid()}]}
+
+    def handle_fault(self, instruction: str, params: dict | None = None) -> dict:
+        return {"success": False, "reason": "a single engine core cannot restart itself; run with "
+                                            "data_parallel_size > 1 or restart the server"}
 
     def start_profile(self, trace_dir: str | None = None) -> bool:
         return all(self.executor.collective_rpc("start_profile", trace_dir))

@@ -215,8 +215,17 @@ class AsyncMPClient(_MPBase):
         self.outputs.put_nowait(outs)
 
     def _on_death(self) -> None:
-        if self.loop is not None:
-            self.loop.call_soon_threadsafe(self.outputs.put_nowait, EngineDeadError("engine core died"))
+        if self.loop is None:
+            return
+
+        def fail() -> None:
+            err = EngineDeadError("engine core died")
+            self.outputs.put_nowait(err)
+            for fut in self._futures.values():          # utility calls in flight would wait forever
+                if not fut.done():
+                    fut.set_exception(err)
+            self._futures.clear()
+        self.loop.call_soon_threadsafe(fail)
 
     async def add_request_async(self, req: EngineCoreRequest) -> None:
         self._ensure_loop()
@@ -255,30 +264,42 @@ class DPLBAsyncClient(EngineCoreClient):
     """
 
     def __init__(self, cfg: EngineConfig, executor_class=None) -> None:
-        import copy
         self.cfg = cfg
-        self.clients: list[AsyncMPClient] = []
-        for r in range(cfg.parallel.data_parallel_size):
-            c = copy.deepcopy(cfg)
-            c.parallel.data_parallel_rank = r
-            self.clients.append(AsyncMPClient(c, executor_class))
+        self.executor_class = executor_class
+        self.clients: list[AsyncMPClient] = [self._spawn(r) for r in range(cfg.parallel.data_parallel_size)]
         self.in_flight = [0] * len(self.clients)
+        self.failed: dict[int, str] = {}          # replica → why it is out of service
+        self.restarts = 0
         self.owner: dict[str, int] = {}
         self.merged: asyncio.Queue | None = None
-        self._pumps: list[asyncio.Task] = []
+        self._pumps: dict[int, asyncio.Task] = {}
+
+    def _spawn(self, rank: int) -> AsyncMPClient:
+        import copy
+        c = copy.deepcopy(self.cfg)
+        c.parallel.data_parallel_rank = rank
+        return AsyncMPClient(c, self.executor_class)
 
     @property
     def dead(self) -> bool:
-        return any(c.dead for c in self.clients)
+        """Only when no replica is left: a single replica's death takes its own requests with it and
+        nothing else (``fault_status`` / ``handle_fault`` show and repair it)."""
+        return all(c.dead or i in self.failed for i, c in enumerate(self.clients))
+
+    def _alive(self) -> list[int]:
+        return [i for i, c in enumerate(self.clients) if not c.dead and i not in self.failed]
 
     def _ensure(self) -> None:
         if self.merged is None:
             self.merged = asyncio.Queue()
-            loop = asyncio.get_running_loop()
             for i, c in enumerate(self.clients):
-                self._pumps.append(loop.create_task(self._pump(i, c)))
+                self._start_pump(i, c)
+
+    def _start_pump(self, idx: int, client: AsyncMPClient) -> None:
+        self._pumps[idx] = asyncio.get_running_loop().create_task(self._pump(idx, client))
 
     async def _pump(self, idx: int, client: AsyncMPClient) -> None:
+        from sonar_b200.request import EngineCoreOutput, FinishReason
         try:
             while True:
                 outs = await client.get_output_async()
@@ -289,14 +310,31 @@ class DPLBAsyncClient(EngineCoreClient):
                 await self.merged.put(outs)
         except asyncio.CancelledError:
             raise
-        except Exception as e:  # noqa: BLE001
-            await self.merged.put(e)
+        except Exception as e:  # noqa: BLE001 - the replica is gone: its requests end with an error, the rest go on
+            self.failed[idx] = str(e) or type(e).__name__
+            lost = [rid for rid, i in self.owner.items() if i == idx]
+            for rid in lost:
+                del self.owner[rid]
+            self.in_flight[idx] = 0
+            logger.error("engine replica %d failed (%s): %d requests lost, %d replicas left", idx, e, len(lost),
+                         len(self._alive()))
+            if lost:
+                await self.merged.put(EngineCoreOutputs(
+                    outputs=[EngineCoreOutput(rid, [], finish_reason=FinishReason.ERROR) for rid in lost],
+                    engine_index=idx))
+            if not self._alive():
+                await self.merged.put(EngineDeadError("every engine replica is dead"))
 
     async def add_request_async(self, req: EngineCoreRequest) -> None:
         self._ensure()
+        alive = self._alive()
+        if not alive:
+            raise EngineDeadError("every engine replica is dead")
         idx = req.data_parallel_rank
         if idx is None:
-            idx = min(range(len(self.clients)), key=lambda i: (self.in_flight[i], i))
+            idx = min(alive, key=lambda i: (self.in_flight[i], i))
+        elif idx not in alive:
+            raise EngineDeadError(f"engine replica {idx} is dead")
         self.owner[req.request_id] = idx
         self.in_flight[idx] += 1
         await self.clients[idx].add_request_async(req)
@@ -320,13 +358,66 @@ class DPLBAsyncClient(EngineCoreClient):
         return item
 
     async def call_utility_async(self, method: str, *args, **kwargs) -> Any:
-        res = await asyncio.gather(*(c.call_utility_async(method, *args, **kwargs) for c in self.clients))
-        if method in ("reset_prefix_cache",):
+        if method == "fault_status":
+            return self.fault_status()
+        if method == "handle_fault":
+            return await self.handle_fault(*args, **kwargs)
+        alive = self._alive()
+        if not alive:
+            raise EngineDeadError("every engine replica is dead")
+        res = await asyncio.gather(*(self.clients[i].call_utility_async(method, *args, **kwargs) for i in alive))
+        if method in ("reset_prefix_cache", "init_weight_transfer_engine"):
             return all(res)
-        return res if len(res) > 1 else res[0]
+        if method == "update_weights":
+            return min(res)
+        return res if len(self.clients) > 1 else res[0]
+
+    # fault tolerance -----------------------------------------------------------------
+    def fault_status(self) -> dict:
+        reps = []
+        for i, c in enumerate(self.clients):
+            bad = c.dead or i in self.failed
+            reps.append({"index": i, "state": "dead" if bad else "alive", "reason": self.failed.get(i),
+                         "in_flight": self.in_flight[i], "pid": c.proc.pid})
+        return {"healthy": all(r["state"] == "alive" for r in reps), "serving": bool(self._alive()),
+                "replicas": reps, "restarts": self.restarts}
+
+    async def handle_fault(self, instruction: str, params: dict | None = None) -> dict:
+        """``retry``: start a fresh engine core for every dead replica (or only ``params["replica"]``) and put it
+        back into rotation.  Requests that were running on the dead replica have already ended with an
+        error; nothing of its KV cache survives."""
+        if instruction != "retry":
+            return {"success": False, "reason": f"unknown instruction {instruction!r}"}
+        self._ensure()
+        want = (params or {}).get("replica")
+        targets = [i for i, c in enumerate(self.clients)
+                   if (c.dead or i in self.failed) and (want is None or i == int(want))]
+        loop = asyncio.get_running_loop()
+        restarted = []
+        for i in targets:
+            old = self.clients[i]
+            pump = self._pumps.pop(i, None)
+            if pump is not None:
+                pump.cancel()
+            try:
+                old.shutdown()
+            except Exception:  # noqa: BLE001 - the process is gone already
+                pass
+            try:
+                new = await loop.run_in_executor(None, self._spawn, i)
+            except Exception as e:  # noqa: BLE001
+                self.failed[i] = f"restart failed: {e}"
+                return {"success": False, "reason": self.failed[i], "restarted": restarted}
+            self.clients[i] = new
+            self.failed.pop(i, None)
+            self.in_flight[i] = 0
+            self._start_pump(i, new)
+            self.restarts += 1
+            restarted.append(i)
+        return {"success": True, "restarted": restarted}
 
     def shutdown(self) -> None:
-        for t in self._pumps:
+        for t in self._pumps.values():
             t.cancel()
         for c in self.clients:
             c.shutdown()

@@ -98,6 +98,38 @@ def register(app: FastAPI, state) -> None:
             return JSONResponse({"error": {"message": str(e), "type": "BadRequestError"}}, status_code=400)
         return {"updated_tensors": n}
 
+    # ------------------------------------------------------------------ fault tolerance
+    ft_state: dict[str, Any] = {"last": None}
+
+    @app.post("/fault_tolerance/apply")
+    async def fault_tolerance_apply(raw: Request):
+        import asyncio
+        body = await raw.json()
+        instruction = body.get("instruction") if isinstance(body, dict) else None
+        if instruction not in ("retry",):
+            return _error(f"invalid instruction {instruction!r} (known: retry)")
+        params = body.get("params") or {}
+        if not isinstance(params, dict):
+            return _error("'params' must be an object")
+        rid = uuid.uuid4().hex
+
+        async def run() -> None:
+            try:
+                ft_state["last"] = {"request_id": rid, **(await state.engine.handle_fault(instruction, params))}
+            except Exception as e:  # noqa: BLE001
+                ft_state["last"] = {"request_id": rid, "success": False, "reason": str(e)}
+        ft_state["task"] = asyncio.get_running_loop().create_task(run())      # recovery outlives this request
+        return JSONResponse({"message": "accepted; poll /fault_tolerance/status", "request_id": rid}, status_code=202)
+
+    @app.get("/fault_tolerance/status")
+    async def fault_tolerance_status():
+        try:
+            st = await state.engine.fault_status()
+        except Exception as e:  # noqa: BLE001
+            st = {"healthy": False, "serving": False, "replicas": [], "reason": str(e)}
+        st["last_recovery"] = ft_state["last"]
+        return st
+
     @app.get("/get_world_size")
     async def get_world_size():
         return {"world_size": await state.engine.get_world_size()}

@@ -81,8 +81,9 @@ def test_tokenize_metrics_and_dev_routes(client):
 
 
 def test_data_parallel_load_balancing_and_engine_death():
-    """Two engine replicas behind one frontend: requests spread over both; killing one replica surfaces as
-    EngineDeadError instead of a hang."""
+    """Two engine replicas behind one frontend: requests spread over both.  Killing one replica ends only its
+    own requests (with an error), the other keeps serving; ``handle_fault("retry")`` starts a fresh replica;
+    with every replica gone the engine reports EngineDeadError instead of hanging."""
     import asyncio
     import os
     import signal
@@ -107,10 +108,28 @@ def test_data_parallel_load_balancing_and_engine_death():
         stats = await engine.get_stats()
         steps = [s["workers"][0]["steps"] for s in stats]
         assert len(steps) == 2 and all(x > 0 for x in steps)          # both replicas did work
+        st = await engine.fault_status()
+        assert st["healthy"] and [r["state"] for r in st["replicas"]] == ["alive", "alive"]
         os.kill(engine.core.clients[1].proc.pid, signal.SIGKILL)
         await asyncio.sleep(1.0)
+        st = await engine.fault_status()
+        assert not st["healthy"] and st["serving"] and [r["state"] for r in st["replicas"]] == ["alive", "dead"]
+        outs = await asyncio.gather(*(one(10 + i, 8) for i in range(4)))         # the survivor serves them all
+        assert all(len(o.outputs[0].token_ids) == 8 for o in outs)
+        res = await engine.handle_fault("retry")
+        assert res == {"success": True, "restarted": [1]}
+        st = await engine.fault_status()
+        assert st["healthy"] and st["restarts"] == 1
+        outs = await asyncio.gather(*(one(20 + i, 5) for i in range(6)))
+        assert all(len(o.outputs[0].token_ids) == 5 for o in outs)
+        stats = await engine.get_stats()
+        assert stats[1]["workers"][0]["steps"] > 0                    # the new replica takes work
+        assert (await engine.handle_fault("reboot"))["success"] is False
+        for c in engine.core.clients:
+            os.kill(c.proc.pid, signal.SIGKILL)
+        await asyncio.sleep(1.0)
         with pytest.raises(EngineDeadError):
-            await asyncio.gather(*(one(10 + i, 50) for i in range(4)))
+            await asyncio.gather(*(one(40 + i, 50) for i in range(4)))
     try:
         asyncio.run(main())
     finally:
@@ -161,5 +180,49 @@ def test_management_pooling_and_parser_routes(tmp_path):
             assert traces and traces[0].endswith(".json")
             # LoRA routes without LoRA enabled answer 400
             assert c.post("/v1/load_lora_adapter", json={"lora_name": "a", "lora_path": "/nonexistent"}).status_code == 400
+    finally:
+        engine.shutdown()
+
+
+def test_fault_tolerance_and_weight_update_routes(tmp_path):
+    import os
+    import sys
+    import time
+
+    import torch
+    from fastapi.testclient import TestClient
+
+    from sonar_b200.engine.async_llm import AsyncLLM
+    from sonar_b200.entrypoints.openai.api_server import ServingState, build_app
+    sys.path.insert(0, os.path.dirname(__file__))
+    from tp_common import make_checkpoint
+    a = make_checkpoint(str(tmp_path / "a"), "tiny-llama-128", dtype=torch.float32, seed=0)
+    b = make_checkpoint(str(tmp_path / "b"), "tiny-llama-128", dtype=torch.float32, seed=1)
+    args = EngineArgs(model=a, dtype="float32", max_model_len=128, num_gpu_blocks_override=64, max_num_seqs=4,
+                      max_num_batched_tokens=64, device="cpu", skip_tokenizer_init=False)
+    engine = AsyncLLM.from_engine_args(args)
+    app = build_app(ServingState(engine, "tiny", None))
+    body = {"prompt": [11, 12, 13, 14, 15], "max_tokens": 6, "temperature": 0, "ignore_eos": True, "logprobs": 1}
+    try:
+        with TestClient(app) as c:
+            st = c.get("/fault_tolerance/status").json()
+            assert st["healthy"] and st["replicas"][0]["state"] == "alive" and st["last_recovery"] is None
+            assert c.post("/fault_tolerance/apply", json={"instruction": "explode"}).status_code == 400
+            r = c.post("/fault_tolerance/apply", json={"instruction": "retry"})
+            assert r.status_code == 202 and r.json()["request_id"]
+            for _ in range(50):
+                last = c.get("/fault_tolerance/status").json()["last_recovery"]
+                if last is not None:
+                    break
+                time.sleep(0.05)
+            assert last["success"] is False and "single engine" in last["reason"]
+            assert c.get("/get_world_size").json() == {"world_size": 1}
+            before = c.post("/v1/completions", json=body).json()["choices"][0]["logprobs"]["token_logprobs"]
+            assert c.post("/init_weight_transfer_engine", json={"backend": "checkpoint"}).json() == {"ok": True}
+            r = c.post("/update_weights", json={"update_info": {"path": b}})
+            assert r.status_code == 200 and r.json()["updated_tensors"] > 10
+            after = c.post("/v1/completions", json=body).json()["choices"][0]["logprobs"]["token_logprobs"]
+            assert len(after) == 6 and after != before
+            assert c.post("/update_weights", json={"update_info": {"path": str(tmp_path / "nope")}}).status_code == 400
     finally:
         engine.shutdown()

@@ -222,6 +222,7 @@ class ParallelConfig:
     data_parallel_size: int = 1
     enable_expert_parallel: bool = False
     decode_context_parallel_size: int = 1
+    enable_elastic_ep: bool = False            # replica-managing client even at data_parallel_size 1: scalable later
     prefill_context_parallel_size: int = 1
     expert_placement: str = "linear"            # linear | round_robin
     all2all_backend: str = "fused_nvlink"       # fused_nvlink | allgather_reducescatter
@@ -410,6 +411,7 @@ class EngineArgs:
     prefill_context_parallel_size: int = 1
     expert_placement: str = "linear"
     all2all_backend: str = "fused_nvlink"
+    enable_elastic_ep: bool = False
     enable_eplb: bool = False
     num_redundant_experts: int = 0
     eplb_window: int = 1000
@@ -478,6 +480,7 @@ class EngineArgs:
             decode_context_parallel_size=self.decode_context_parallel_size,
             prefill_context_parallel_size=self.prefill_context_parallel_size,
             expert_placement=self.expert_placement, all2all_backend=self.all2all_backend,
+            enable_elastic_ep=self.enable_elastic_ep,
             enable_eplb=self.enable_eplb, num_redundant_experts=self.num_redundant_experts,
             eplb_window=self.eplb_window, eplb_interval=self.eplb_interval,
             distributed_executor_backend=self.distributed_executor_backend,

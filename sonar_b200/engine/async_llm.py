@@ -192,6 +192,16 @@ class AsyncLLM:
     async def handle_fault(self, instruction: str, params: dict | None = None) -> dict:
         return await self.core.call_utility_async("handle_fault", instruction, params)
 
+    async def scale_elastic_ep(self, new_data_parallel_size: int, drain_timeout: float = 120.0) -> int:
+        """Change the number of engine replicas at run time (needs ``data_parallel_size > 1`` or
+        ``enable_elastic_ep`` at start-up, so that the replica-managing client is in place)."""
+        if not hasattr(self.core, "scale"):
+            raise ValueError("elastic scaling needs the engine to start with enable_elastic_ep or data parallelism")
+        return await self.core.scale(new_data_parallel_size, drain_timeout)
+
+    async def is_scaling_elastic_ep(self) -> bool:
+        return bool(getattr(self.core, "scaling", False))
+
     async def get_world_size(self) -> int:
         return await self.core.call_utility_async("get_world_size")
 

@@ -34,7 +34,7 @@ class EngineCoreClient:
     @staticmethod
     def make_client(cfg: EngineConfig, multiprocess: bool, asyncio_mode: bool, executor_class=None):
         if asyncio_mode:
-            if cfg.parallel.data_parallel_size > 1:
+            if cfg.parallel.data_parallel_size > 1 or cfg.parallel.enable_elastic_ep:
                 return DPLBAsyncClient(cfg, executor_class)
             return AsyncMPClient(cfg, executor_class)
         if multiprocess:
@@ -269,6 +269,8 @@ class DPLBAsyncClient(EngineCoreClient):
         self.clients: list[AsyncMPClient] = [self._spawn(r) for r in range(cfg.parallel.data_parallel_size)]
         self.in_flight = [0] * len(self.clients)
         self.failed: dict[int, str] = {}          # replica → why it is out of service
+        self.draining: set[int] = set()           # replicas being scaled away: no new requests
+        self.scaling = False
         self.restarts = 0
         self.owner: dict[str, int] = {}
         self.merged: asyncio.Queue | None = None
@@ -287,7 +289,8 @@ class DPLBAsyncClient(EngineCoreClient):
         return all(c.dead or i in self.failed for i, c in enumerate(self.clients))
 
     def _alive(self) -> list[int]:
-        return [i for i, c in enumerate(self.clients) if not c.dead and i not in self.failed]
+        return [i for i, c in enumerate(self.clients)
+                if not c.dead and i not in self.failed and i not in self.draining]
 
     def _ensure(self) -> None:
         if self.merged is None:
@@ -362,6 +365,10 @@ class DPLBAsyncClient(EngineCoreClient):
             return self.fault_status()
         if method == "handle_fault":
             return await self.handle_fault(*args, **kwargs)
+        if method == "scale_elastic_ep":
+            return await self.scale(*args, **kwargs)
+        if method == "is_scaling_elastic_ep":
+            return self.scaling
         alive = self._alive()
         if not alive:
             raise EngineDeadError("every engine replica is dead")
@@ -415,6 +422,52 @@ class DPLBAsyncClient(EngineCoreClient):
             self.restarts += 1
             restarted.append(i)
         return {"success": True, "restarted": restarted}
+
+    # elastic scaling ------------------------------------------------------------------
+    async def scale(self, new_size: int, drain_timeout: float = 120.0) -> int:
+        """Grow or shrink the set of engine replicas while serving.  Growing starts fresh engine cores (each
+        on the next slice of GPUs) and adds them to the rotation.  Shrinking stops routing to the highest
+        replicas, waits up to ``drain_timeout`` seconds for their requests to finish (``TimeoutError`` and no
+        change otherwise), then shuts them down."""
+        if new_size <= 0:
+            raise ValueError("new_data_parallel_size must be positive")
+        if self.scaling:
+            raise RuntimeError("a scaling operation is already running")
+        self._ensure()
+        self.scaling = True
+        loop = asyncio.get_running_loop()
+        try:
+            cur = len(self.clients)
+            if new_size > cur:
+                new = await asyncio.gather(*(loop.run_in_executor(None, self._spawn, r) for r in range(cur, new_size)))
+                for r, c in zip(range(cur, new_size), new):
+                    self.clients.append(c)
+                    self.in_flight.append(0)
+                    self._start_pump(r, c)
+            elif new_size < cur:
+                going = set(range(new_size, cur))
+                self.draining |= going
+                deadline = loop.time() + drain_timeout
+                while any(self.in_flight[i] > 0 and i not in self.failed and not self.clients[i].dead for i in going):
+                    if loop.time() > deadline:
+                        self.draining -= going
+                        raise TimeoutError(f"replicas {sorted(going)} still had requests after {drain_timeout}s")
+                    await asyncio.sleep(0.05)
+                for i in sorted(going, reverse=True):
+                    pump = self._pumps.pop(i, None)
+                    if pump is not None:
+                        pump.cancel()
+                    try:
+                        self.clients[i].shutdown()
+                    except Exception:  # noqa: BLE001
+                        pass
+                    del self.clients[i], self.in_flight[i]
+                    self.failed.pop(i, None)
+                self.draining -= going
+            self.cfg.parallel.data_parallel_size = len(self.clients)
+            return len(self.clients)
+        finally:
+            self.scaling = False
 
     def shutdown(self) -> None:
         for t in self._pumps.values():

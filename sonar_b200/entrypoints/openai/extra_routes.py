@@ -130,6 +130,30 @@ def register(app: FastAPI, state) -> None:
         st["last_recovery"] = ft_state["last"]
         return st
 
+    # ------------------------------------------------------------------ elastic scaling
+    @app.post("/scale_elastic_ep")
+    async def scale_elastic_ep(raw: Request):
+        body = await raw.json()
+        new = body.get("new_data_parallel_size")
+        drain = body.get("drain_timeout", 120)
+        if not isinstance(new, int) or new <= 0:
+            return _error("new_data_parallel_size must be a positive integer")
+        if not isinstance(drain, (int, float)) or drain <= 0:
+            return _error("drain_timeout must be positive")
+        try:
+            n = await state.engine.scale_elastic_ep(new, drain)
+        except TimeoutError as e:
+            return _error(f"scale failed: {e}", 408, "TimeoutError")
+        except ValueError as e:
+            return _error(str(e))
+        except Exception as e:  # noqa: BLE001
+            return _error(f"scale failed: {e}", 500, "InternalServerError")
+        return {"message": f"Scaled to {n} data parallel engines", "data_parallel_size": n}
+
+    @app.post("/is_scaling_elastic_ep")
+    async def is_scaling_elastic_ep():
+        return {"is_scaling_elastic_ep": await state.engine.is_scaling_elastic_ep()}
+
     @app.get("/get_world_size")
     async def get_world_size():
         return {"world_size": await state.engine.get_world_size()}

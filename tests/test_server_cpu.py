@@ -226,3 +226,52 @@ def test_fault_tolerance_and_weight_update_routes(tmp_path):
             assert c.post("/update_weights", json={"update_info": {"path": str(tmp_path / "nope")}}).status_code == 400
     finally:
         engine.shutdown()
+
+
+def test_elastic_scaling_of_engine_replicas():
+    """Start with one replica behind the replica-managing client, scale to two while serving, then back to one
+    (draining first); the routes validate their input."""
+    import asyncio
+
+    from fastapi.testclient import TestClient
+
+    from sonar_b200 import SamplingParams
+    from sonar_b200.engine.async_llm import AsyncLLM
+    from sonar_b200.entrypoints.openai.api_server import ServingState, build_app
+    args = EngineArgs(model="tiny-llama", dtype="float32", max_model_len=128, num_gpu_blocks_override=64,
+                      max_num_seqs=4, max_num_batched_tokens=64, device="cpu", enable_elastic_ep=True)
+    engine = AsyncLLM.from_engine_args(args)
+
+    async def one(i, n=6):
+        last = None
+        async for out in engine.generate({"prompt_token_ids": [5 + i, 6, 7, 8]},
+                                         SamplingParams(max_tokens=n, ignore_eos=True, temperature=0), f"e{i}"):
+            last = out
+        return last
+
+    async def main():
+        assert len(engine.core.clients) == 1
+        first = await one(0)
+        assert await engine.scale_elastic_ep(2) == 2
+        outs = await asyncio.gather(*(one(i) for i in range(1, 7)))
+        assert all(len(o.outputs[0].token_ids) == 6 for o in outs)
+        stats = await engine.get_stats()
+        assert len(stats) == 2 and all(s["workers"][0]["steps"] > 0 for s in stats)
+        # shrink while requests run: they finish on the draining replica first
+        running = [asyncio.ensure_future(one(10 + i, 20)) for i in range(4)]
+        await asyncio.sleep(0.05)
+        assert await engine.scale_elastic_ep(1, drain_timeout=60) == 1
+        outs = await asyncio.gather(*running)
+        assert all(len(o.outputs[0].token_ids) == 20 for o in outs)
+        assert len(engine.core.clients) == 1 and not await engine.is_scaling_elastic_ep()
+        again = await one(0)
+        assert again.outputs[0].token_ids == first.outputs[0].token_ids
+    try:
+        asyncio.run(main())
+        app = build_app(ServingState(engine, "tiny", None))
+        with TestClient(app) as c:
+            assert c.post("/scale_elastic_ep", json={"new_data_parallel_size": 0}).status_code == 400
+            assert c.post("/scale_elastic_ep", json={"new_data_parallel_size": 1, "drain_timeout": -1}).status_code == 400
+            assert c.post("/is_scaling_elastic_ep").json() == {"is_scaling_elastic_ep": False}
+    finally:
+        engine.shutdown()

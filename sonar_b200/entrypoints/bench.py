@@ -1,10 +1,14 @@
-"""``sonar bench {throughput,latency,serve}``.
+"""``sonar bench {throughput,latency,serve,startup,sweep}``.
 
 * throughput — offline: N requests of fixed input/output length through ``LLM.generate``.
 * latency    — offline: one batch, repeated; mean/percentile end-to-end latency.
 * serve      — online: Poisson arrivals against a running server; TTFT / TPOT / output tok/s.
+* startup    — cold start: seconds from ``LLM(...)`` to the first generated token, split into engine
+  construction (weights, KV cache, graph capture) and the first request.
+* sweep      — ``serve`` repeated over ``--request-rates``; one JSON line per rate and a summary table.
 
-Parity: ``aphrodite/benchmarks/throughput.py:50,1063``, ``latency.py``, ``serve.py:526,714``.
+Parity: ``aphrodite/benchmarks/throughput.py:50,1063``, ``latency.py``, ``serve.py:526,714``, ``startup.py``,
+``sweep/``.
 """
 from __future__ import annotations
 
@@ -18,7 +22,9 @@ import time
 
 def add_args(p: argparse.ArgumentParser) -> None:
     from sonar_b200.config import EngineArgs
-    p.add_argument("mode", choices=["throughput", "latency", "serve"])
+    p.add_argument("mode", choices=["throughput", "latency", "serve", "startup", "sweep"])
+    p.add_argument("--request-rates", type=float, nargs="+", default=[1.0, 4.0, 16.0, float("inf")],
+                   help="sweep: the request rates to run, in order")
     p.add_argument("--model", default=None)
     p.add_argument("--num-prompts", type=int, default=200)
     p.add_argument("--input-len", type=int, default=1024)
@@ -29,7 +35,6 @@ def add_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--request-rate", type=float, default=float("inf"), help="serve: Poisson arrivals per second")
     p.add_argument("--url", default="http://127.0.0.1:2242")
     p.add_argument("--vocab-size", type=int, default=32000, help="serve: range of random token ids")
-    p.add_argument("--seed", type=int, default=0)
     EngineArgs.add_cli_args(p)
 
 
@@ -38,6 +43,25 @@ def _percentile(xs: list[float], q: float) -> float:
         return 0.0
     xs = sorted(xs)
     return xs[min(len(xs) - 1, int(q * len(xs)))]
+
+
+def _startup(ns: argparse.Namespace) -> dict:
+    from sonar_b200 import LLM, SamplingParams
+    from sonar_b200.config import EngineArgs
+    ns.model = ns.model or "tiny-llama"
+    args = EngineArgs.from_cli_args(ns)
+    args.skip_tokenizer_init = True
+    runs = []
+    for _ in range(max(1, ns.num_iters)):
+        t0 = time.perf_counter()
+        llm = LLM(args.model, **{k: v for k, v in vars(args).items() if k != "model"})
+        t1 = time.perf_counter()
+        llm.generate([{"prompt_token_ids": [1, 2, 3, 4]}], SamplingParams(max_tokens=1, detokenize=False))
+        t2 = time.perf_counter()
+        llm.shutdown()
+        runs.append((t1 - t0, t2 - t1))
+    return {"engine_init_s": statistics.mean(r[0] for r in runs), "first_token_s": statistics.mean(r[1] for r in runs),
+            "cold_start_s": statistics.mean(sum(r) for r in runs), "iterations": len(runs)}
 
 
 def _offline(ns: argparse.Namespace) -> None:
@@ -123,8 +147,26 @@ async def _serve(ns: argparse.Namespace) -> dict:
             "tpot_p50_ms": _percentile(tpot, 0.5) * 1e3, "tpot_p99_ms": _percentile(tpot, 0.99) * 1e3}
 
 
+def _sweep(ns: argparse.Namespace) -> list[dict]:
+    rows = []
+    for rate in ns.request_rates:
+        ns.request_rate = rate
+        row = asyncio.run(_serve(ns))
+        print(json.dumps(row), flush=True)
+        rows.append(row)
+    print(f"{'rate':>8} {'out tok/s':>10} {'ttft p50':>9} {'ttft p99':>9} {'tpot p50':>9} {'tpot p99':>9}")
+    for r in rows:
+        print(f"{r['request_rate']:>8} {r['output_tokens_per_s']:>10.1f} {r['ttft_p50_ms']:>9.1f} {r['ttft_p99_ms']:>9.1f} "
+              f"{r['tpot_p50_ms']:>9.2f} {r['tpot_p99_ms']:>9.2f}")
+    return rows
+
+
 def main(ns: argparse.Namespace) -> None:
-    if ns.mode == "serve":
+    if ns.mode == "startup":
+        print(json.dumps(_startup(ns)))
+    elif ns.mode == "sweep":
+        _sweep(ns)
+    elif ns.mode == "serve":
         print(json.dumps(asyncio.run(_serve(ns))))
     else:
         _offline(ns)

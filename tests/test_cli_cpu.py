@@ -1,0 +1,51 @@
+"""Command line entry points run in-process on the CPU path."""
+import json
+
+from sonar_b200.entrypoints import cli
+
+ENGINE = ["--device", "cpu", "--dtype", "float32", "--max-model-len", "128", "--num-gpu-blocks-override", "32",
+          "--max-num-seqs", "4", "--max-num-batched-tokens", "64"]
+
+
+def _last_json(capsys):
+    lines = [l for l in capsys.readouterr().out.splitlines() if l.startswith("{")]
+    return json.loads(lines[-1])
+
+
+def test_parser_knows_every_subcommand():
+    p = cli.build_parser()
+    for argv in (["serve", "tiny-llama"], ["run", "--prompt", "hi"], ["bench", "throughput"], ["collect-env"],
+                 ["chat", "--quick", "hi"], ["complete", "--quick", "hi"], ["run-batch", "-i", "a", "-o", "b"]):
+        assert p.parse_args(argv).cmd == argv[0]
+
+
+def test_bench_modes(capsys):
+    cli.main(["bench", "throughput", "--model", "tiny-llama", "--num-prompts", "4", "--input-len", "16",
+              "--output-len", "4", *ENGINE])
+    r = _last_json(capsys)
+    assert r["output_tokens_per_s"] > 0 and r["requests_per_s"] > 0
+    cli.main(["bench", "latency", "--model", "tiny-llama", "--batch-size", "2", "--num-iters", "2", "--input-len", "8",
+              "--output-len", "3", *ENGINE])
+    r = _last_json(capsys)
+    assert r["avg_latency_s"] > 0 and r["batch_size"] == 2
+    cli.main(["bench", "startup", "--model", "tiny-llama", "--num-iters", "1", *ENGINE])
+    r = _last_json(capsys)
+    assert r["cold_start_s"] >= r["engine_init_s"] > 0
+
+
+def test_run_batch_and_collect_env(tmp_path, capsys):
+    src, dst = tmp_path / "in.jsonl", tmp_path / "out.jsonl"
+    src.write_text("\n".join(json.dumps(x) for x in [
+        {"custom_id": "a", "method": "POST", "url": "/v1/completions", "body": {"prompt": "hello", "max_tokens": 3}},
+        {"custom_id": "b", "method": "POST", "url": "/v1/chat/completions",
+         "body": {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 2}}]))
+    cli.main(["run-batch", "-i", str(src), "-o", str(dst), "--model", "tiny-llama", *ENGINE])
+    rows = [json.loads(l) for l in dst.read_text().splitlines()]
+    assert [r["custom_id"] for r in rows] == ["a", "b"]
+    assert rows[0]["response"]["body"]["usage"]["completion_tokens"] == 3
+    assert "message" in rows[1]["response"]["body"]["choices"][0]
+    capsys.readouterr()
+    cli.main(["collect-env"])
+    out = capsys.readouterr().out
+    info = json.loads(out[out.find("{"):])
+    assert "torch" in info and "kernel_library" in info

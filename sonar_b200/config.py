@@ -100,10 +100,25 @@ def _resolve_hf_config(model: str) -> tuple[dict[str, Any], str | None]:
     cfg_path = os.path.join(model, "config.json")
     if os.path.isdir(model) and os.path.isfile(cfg_path):
         with open(cfg_path) as f:
-            return json.load(f), model
+            return _normalise_hf_config(json.load(f)), model
     raise ValueError(
         f"model {model!r} is neither a built-in architecture preset ({', '.join(sorted(ARCH_PRESETS))}) "
         "nor a local directory with config.json (no hub access in this build)")
+
+
+def _normalise_hf_config(cfg: dict[str, Any]) -> dict[str, Any]:
+    """Config files written by newer ``transformers`` keep the rotary settings in one ``rope_parameters``
+    object (``rope_theta`` inside, ``rope_type: default`` when unscaled) and nest the language model of
+    a multimodal checkpoint under ``text_config``; the model code reads the classic flat keys."""
+    rp = cfg.get("rope_parameters")
+    if isinstance(rp, dict):
+        if "rope_theta" in rp:
+            cfg.setdefault("rope_theta", rp["rope_theta"])
+        if rp.get("rope_type", rp.get("type", "default")) != "default" and not cfg.get("rope_scaling"):
+            cfg["rope_scaling"] = {k: v for k, v in rp.items() if k != "rope_theta"}
+    if cfg.get("dtype") and not cfg.get("torch_dtype"):
+        cfg["torch_dtype"] = cfg["dtype"]
+    return cfg
 
 
 @dataclass

@@ -170,12 +170,15 @@ class DeepseekMoE(nn.Module):
         super().__init__()
         g = cfg.get
         n_exp, inter = int(g("n_routed_experts")), int(g("moe_intermediate_size"))
+        # V3-family configs written by newer tools may omit the routing keys: sigmoid scores with the
+        # bias-corrected group selection are that family's definition, softmax + greedy groups is V2's
+        v3 = g("model_type", "") in ("deepseek_v3", "deepseek_v32", "kimi_k2")
         self.gate = ReplicatedLinear(cfg.hidden_size, n_exp, False, cfg.dtype, device, None, f"{prefix}.gate")
         self.experts = FusedMoE(
             n_exp, int(g("num_experts_per_tok")), cfg.hidden_size, inter, cfg.dtype, device,
-            renormalize=bool(g("norm_topk_prob", True)), scoring=g("scoring_func", "softmax"),
+            renormalize=bool(g("norm_topk_prob", True)), scoring=g("scoring_func", "sigmoid" if v3 else "softmax"),
             n_group=int(g("n_group", 1) or 1), topk_group=int(g("topk_group", 1) or 1),
-            routed_scaling=float(g("routed_scaling_factor", 1.0)), use_bias=g("topk_method", "noaux_tc") == "noaux_tc",
+            routed_scaling=float(g("routed_scaling_factor", 1.0)), use_bias=g("topk_method", "noaux_tc" if v3 else "greedy") == "noaux_tc",
             expert_parallel=bool(g("_expert_parallel", False)), placement=g("_expert_placement", "linear"),
             prefix=f"{prefix}.experts", num_redundant=int(g("_num_redundant_experts", 0) or 0),
             quantization=cfg.quantization)

@@ -1,0 +1,106 @@
+"""Model numerics against the Hugging Face implementations: a tiny randomly initialised HF model is saved with
+``save_pretrained`` and loaded here; greedy tokens and their log-probabilities must agree in fp32 on CPU."""
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+from sonar_b200 import LLM, SamplingParams  # noqa: E402
+
+PROMPTS = [[3, 17, 99, 45, 200, 7, 7, 81, 150, 23, 64], [250, 11, 5, 90, 33, 180, 2, 2, 19]]
+N_NEW = 8
+
+
+def _hf_greedy(model, prompt):
+    ids = torch.tensor([prompt])
+    toks, lps = [], []
+    with torch.no_grad():
+        for _ in range(N_NEW):
+            logits = model(ids).logits[0, -1].float()
+            lp = torch.log_softmax(logits, dim=-1)
+            t = int(lp.argmax())
+            toks.append(t)
+            lps.append(float(lp[t]))
+            ids = torch.cat([ids, torch.tensor([[t]])], dim=1)
+    return toks, lps
+
+
+def _check(tmp_path, hf_cfg, hf_cls, atol=2e-3, init_std=None, **llm_kw):
+    torch.manual_seed(0)
+    model = hf_cls(hf_cfg).float().eval()
+    if init_std is not None:
+        with torch.no_grad():
+            for p in model.parameters():
+                if p.dim() >= 2:
+                    p.normal_(0.0, init_std)
+    path = str(tmp_path / "hf")
+    model.save_pretrained(path, safe_serialization=True)
+    llm = LLM(path, dtype="float32", device="cpu", max_model_len=128, num_gpu_blocks_override=32, max_num_seqs=4,
+              max_num_batched_tokens=64, skip_tokenizer_init=True, **llm_kw)
+    sp = SamplingParams(temperature=0, max_tokens=N_NEW, logprobs=1, ignore_eos=True, detokenize=False)
+    outs = llm.generate([{"prompt_token_ids": p} for p in PROMPTS], sp)
+    llm.shutdown()
+    for p, o in zip(PROMPTS, outs):
+        want_t, want_lp = _hf_greedy(model, p)
+        c = o.outputs[0]
+        got_lp = [d[t] if isinstance(d[t], float) else d[t].logprob for t, d in zip(c.token_ids, c.logprobs)]
+        assert list(c.token_ids) == want_t, (c.token_ids, want_t)
+        assert torch.allclose(torch.tensor(got_lp), torch.tensor(want_lp), atol=atol), (got_lp, want_lp)
+
+
+COMMON = dict(vocab_size=256, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, max_position_embeddings=256, rms_norm_eps=1e-5, rope_theta=10000.0,
+              tie_word_embeddings=False)
+
+
+def test_llama(tmp_path):
+    from transformers import LlamaConfig, LlamaForCausalLM
+    _check(tmp_path, LlamaConfig(**COMMON, head_dim=16), LlamaForCausalLM, init_std=0.08)
+
+
+def test_llama3_rope_scaling_and_tied_embeddings(tmp_path):
+    from transformers import LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig(**{**COMMON, "tie_word_embeddings": True}, head_dim=16,
+                      rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                    "high_freq_factor": 4.0, "original_max_position_embeddings": 64})
+    _check(tmp_path, cfg, LlamaForCausalLM, init_std=0.08)
+
+
+def test_qwen2_bias(tmp_path):
+    from transformers import Qwen2Config, Qwen2ForCausalLM
+    _check(tmp_path, Qwen2Config(**COMMON), Qwen2ForCausalLM, init_std=0.08)
+
+
+def test_qwen3_qk_norm(tmp_path):
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+    _check(tmp_path, Qwen3Config(**COMMON, head_dim=16), Qwen3ForCausalLM, init_std=0.08)
+
+
+def test_mistral_sliding_window(tmp_path):
+    from transformers import MistralConfig, MistralForCausalLM
+    _check(tmp_path, MistralConfig(**COMMON, head_dim=16, sliding_window=8), MistralForCausalLM, init_std=0.08)
+
+
+def test_qwen3_moe(tmp_path):
+    from transformers import Qwen3MoeConfig, Qwen3MoeForCausalLM
+    cfg = Qwen3MoeConfig(**COMMON, head_dim=16, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=32,
+                         norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[])
+    _check(tmp_path, cfg, Qwen3MoeForCausalLM, init_std=0.08)
+
+
+def test_mixtral(tmp_path):
+    from transformers import MixtralConfig, MixtralForCausalLM
+    cfg = MixtralConfig(**COMMON, head_dim=16, num_local_experts=4, num_experts_per_tok=2, sliding_window=None)
+    _check(tmp_path, cfg, MixtralForCausalLM, init_std=0.08)
+
+
+def test_deepseek_v3(tmp_path):
+    from transformers import DeepseekV3Config, DeepseekV3ForCausalLM
+    cfg = DeepseekV3Config(vocab_size=256, hidden_size=64, intermediate_size=128, moe_intermediate_size=32,
+                           num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4, n_shared_experts=1,
+                           n_routed_experts=8, routed_scaling_factor=2.5, kv_lora_rank=32, q_lora_rank=48,
+                           qk_rope_head_dim=16, v_head_dim=32, qk_nope_head_dim=32, n_group=4, topk_group=2,
+                           num_experts_per_tok=2, first_k_dense_replace=1, norm_topk_prob=True,
+                           max_position_embeddings=256, rms_norm_eps=1e-6, rope_theta=10000.0,
+                           tie_word_embeddings=False)
+    _check(tmp_path, cfg, DeepseekV3ForCausalLM, init_std=0.08)

@@ -67,14 +67,15 @@ class LlamaAttention(nn.Module):
         super().__init__()
         hidden, hd = cfg.hidden_size, cfg.head_dim
         quant = cfg.quantization
-        bias = bool(cfg.get("attention_bias", False)) or cfg.get("model_type") == "qwen2"
+        bias = bool(cfg.get("attention_bias", False)) or cfg.get("model_type") in ("qwen2", "qwen2_moe")
         self.qkv_proj = QKVParallelLinear(hidden, hd, cfg.num_attention_heads, cfg.num_kv_heads, bias,
                                           cfg.dtype, device, quant, f"{prefix}.qkv_proj")
         self.o_proj = RowParallelLinear(cfg.num_attention_heads * hd, hidden, False, cfg.dtype, device, quant,
                                         f"{prefix}.o_proj")
-        qk_eps = cfg.get("rms_norm_eps", 1e-6) if cfg.get("model_type") in ("qwen3", "qwen3_moe") else None
+        qk_eps = cfg.get("rms_norm_eps", 1e-6) if cfg.get("model_type") in ("qwen3", "qwen3_moe", "dots1") else None
         sw = cfg.get("sliding_window") if cfg.get("use_sliding_window", cfg.get("model_type") == "mistral") else None
-        self.attn = Attention(self.qkv_proj.num_heads, self.qkv_proj.num_kv_heads, hd, hd ** -0.5, layer_idx,
+        scale = float(cfg.get("attention_multiplier") or hd ** -0.5)      # Granite scales scores by a config value
+        self.attn = Attention(self.qkv_proj.num_heads, self.qkv_proj.num_kv_heads, hd, scale, layer_idx,
                               float(cfg.get("rope_theta", 1e4)), cfg.max_model_len, cfg.get("rope_scaling"),
                               sw, device, qk_eps, cfg.dtype)
 

@@ -1,0 +1,128 @@
+"""Llama-shaped families that differ in checkpoint layout or in a few scalars.
+
+* Phi-3 / Phi-4 (``Phi3ForCausalLM``): ``qkv_proj`` and ``gate_up_proj`` are stored fused; they are cut into
+  the q / k / v and gate / up pieces the sharded loaders expect.
+* Granite (``GraniteForCausalLM``): four multipliers — embeddings × ``embedding_multiplier``, attention
+  scores × ``attention_multiplier`` (instead of 1/√d), every block output × ``residual_multiplier`` before it
+  joins the residual stream, logits ÷ ``logits_scaling``.  The residual and embedding multipliers are folded
+  into the weights once after loading, so the fused add+norm kernels and the GEMM epilogues stay as they are.
+* Qwen2-MoE (``Qwen2MoeForCausalLM``): Qwen2 attention (q/k/v bias) with a routed mixture plus one shared
+  expert whose output is gated by ``sigmoid(shared_expert_gate(x))``.
+
+Parity: ``aphrodite/model_executor/models/phi3.py``, ``granite.py``, ``qwen2_moe.py``.
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from sonar_b200 import ops
+from sonar_b200.config import ModelConfig
+from sonar_b200.layers.linear import ReplicatedLinear
+from sonar_b200.models.llama import LlamaDecoderLayer, LlamaForCausalLM, LlamaMLP, LlamaModel
+from sonar_b200.models.qwen3_moe import Qwen3MoeForCausalLM, SparseMoeBlock
+from sonar_b200.parallel.tp_ops import get_tp_context
+
+
+class Phi3ForCausalLM(LlamaForCausalLM):
+    def load_special_weight(self, name: str, tensor: torch.Tensor) -> bool:
+        from sonar_b200.loader.weights import _assign
+        if ".self_attn.qkv_proj." in name:
+            hd, hq, hk = self.cfg.head_dim, self.cfg.num_attention_heads, self.cfg.num_kv_heads
+            q, k, v = tensor.split([hq * hd, hk * hd, hk * hd], dim=0)
+            return all([_assign(self, name, part, shard) for part, shard in ((q, "q"), (k, "k"), (v, "v"))])
+        if ".mlp.gate_up_proj." in name:
+            gate, up = tensor.chunk(2, dim=0)
+            return all([_assign(self, name, gate, 0), _assign(self, name, up, 1)])
+        return False
+
+
+class GraniteForCausalLM(LlamaForCausalLM):
+    def __init__(self, cfg: ModelConfig, device=None) -> None:
+        super().__init__(cfg, device)
+        self.embed_mult = float(cfg.get("embedding_multiplier", 1.0))
+        self.resid_mult = float(cfg.get("residual_multiplier", 1.0))
+        div = float(cfg.get("logits_scaling", 1.0))
+        # a tied LM head shares the (scaled) embedding table: take the scale out of the logits again
+        self.logit_mult = 1.0 / (div * (self.embed_mult if self.tied else 1.0))
+
+    @torch.no_grad()
+    def process_after_load(self) -> None:
+        """Fold the residual multiplier into the two projections that write to the residual stream and the
+        embedding multiplier into the embedding table (unquantised weights only)."""
+        def scale(p: torch.Tensor, m: float) -> None:
+            if m != 1.0:
+                if p.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+                    raise ValueError("Granite multipliers are folded into 16/32-bit weights; quantised "
+                                     "Granite checkpoints are not supported")
+                p.mul_(m)
+        for layer in self.model.layers.values():
+            scale(layer.self_attn.o_proj.weight.data, self.resid_mult)
+            scale(layer.mlp.down_proj.weight.data, self.resid_mult)
+        if hasattr(self.model, "embed_tokens"):
+            scale(self.model.embed_tokens.weight.data, self.embed_mult)
+
+    def compute_logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        return self.lm_head.logits(hidden * self.logit_mult if self.logit_mult != 1.0 else hidden)
+
+
+class Qwen2MoeBlock(SparseMoeBlock):
+    def __init__(self, cfg: ModelConfig, device, prefix: str, expert_parallel: bool, placement: str) -> None:
+        super().__init__(cfg, device, prefix, expert_parallel, placement)
+        inter = int(cfg.get("shared_expert_intermediate_size", 0) or 0)
+        self.shared_expert = (LlamaMLP(cfg.hidden_size, inter, cfg.dtype, device, cfg.quantization,
+                                       f"{prefix}.shared_expert") if inter else None)
+        self.shared_expert_gate = (ReplicatedLinear(cfg.hidden_size, 1, False, cfg.dtype, device, None,
+                                                    f"{prefix}.shared_expert_gate") if inter else None)
+
+    def forward(self, x):
+        tp = get_tp_context()
+        xf = tp.materialize(x)
+        y = self.experts(xf, self.gate(xf), None)
+        if self.shared_expert is not None:
+            se = self.shared_expert
+            s = se.down_proj(ops.silu_and_mul(se.gate_up_proj(xf)))
+            g = torch.sigmoid(torch.nn.functional.linear(xf, self.shared_expert_gate.weight))   # [T, 1]: below GEMM size
+            y = y + g * s
+        return tp.finish_partial(y, None)
+
+
+class Qwen2MoeDecoderLayer(LlamaDecoderLayer):
+    def _make_mlp(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> nn.Module:
+        only = cfg.get("mlp_only_layers", []) or []
+        step = int(cfg.get("decoder_sparse_step", 1))
+        if layer_idx in only or (layer_idx + 1) % step != 0:
+            return LlamaMLP(cfg.hidden_size, int(cfg.get("intermediate_size")), cfg.dtype, device, cfg.quantization, prefix)
+        return Qwen2MoeBlock(cfg, device, prefix, bool(cfg.get("_expert_parallel", False)),
+                             cfg.get("_expert_placement", "linear"))
+
+
+class Qwen2MoeModel(LlamaModel):
+    layer_cls = Qwen2MoeDecoderLayer
+
+
+class Qwen2MoeForCausalLM(Qwen3MoeForCausalLM):
+    model_cls = Qwen2MoeModel
+
+
+class Dots1DecoderLayer(LlamaDecoderLayer):
+    """dots.llm1: Qwen3-style attention (per-head q/k norm) with DeepSeek-V3's mixture (sigmoid scores, bias-corrected
+    group-limited top-k, shared experts, the first layers dense)."""
+
+    def _make_mlp(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> nn.Module:
+        from sonar_b200.models.deepseek import DeepseekMoE
+        if layer_idx < int(cfg.get("first_k_dense_replace", 0)) or not cfg.get("n_routed_experts"):
+            return LlamaMLP(cfg.hidden_size, int(cfg.get("intermediate_size")), cfg.dtype, device, cfg.quantization, prefix)
+        return DeepseekMoE(cfg, device, prefix)
+
+
+class Dots1Model(LlamaModel):
+    layer_cls = Dots1DecoderLayer
+
+
+class Dots1ForCausalLM(LlamaForCausalLM):
+    model_cls = Dots1Model
+
+    def load_special_weight(self, name: str, tensor: torch.Tensor) -> bool:
+        from sonar_b200.models.deepseek import DeepseekForCausalLM
+        return DeepseekForCausalLM.load_special_weight(self, name, tensor)

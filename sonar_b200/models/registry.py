@@ -7,10 +7,15 @@ import importlib
 _MODELS: dict[str, tuple[str, str]] = {
     "LlamaForCausalLM": ("sonar_b200.models.llama", "LlamaForCausalLM"),
     "MistralForCausalLM": ("sonar_b200.models.llama", "LlamaForCausalLM"),
+    "SeedOssForCausalLM": ("sonar_b200.models.llama", "LlamaForCausalLM"),
     "Qwen2ForCausalLM": ("sonar_b200.models.llama", "LlamaForCausalLM"),
     "Qwen3ForCausalLM": ("sonar_b200.models.llama", "LlamaForCausalLM"),
     "Qwen3MoeForCausalLM": ("sonar_b200.models.qwen3_moe", "Qwen3MoeForCausalLM"),
     "MixtralForCausalLM": ("sonar_b200.models.qwen3_moe", "MixtralForCausalLM"),
+    "Phi3ForCausalLM": ("sonar_b200.models.llama_variants", "Phi3ForCausalLM"),
+    "GraniteForCausalLM": ("sonar_b200.models.llama_variants", "GraniteForCausalLM"),
+    "Qwen2MoeForCausalLM": ("sonar_b200.models.llama_variants", "Qwen2MoeForCausalLM"),
+    "Dots1ForCausalLM": ("sonar_b200.models.llama_variants", "Dots1ForCausalLM"),
     "DeepseekV2ForCausalLM": ("sonar_b200.models.deepseek", "DeepseekForCausalLM"),
     "DeepseekV3ForCausalLM": ("sonar_b200.models.deepseek", "DeepseekForCausalLM"),
     "DeepseekV32ForCausalLM": ("sonar_b200.models.deepseek", "DeepseekForCausalLM"),

@@ -104,3 +104,52 @@ def test_deepseek_v3(tmp_path):
                            max_position_embeddings=256, rms_norm_eps=1e-6, rope_theta=10000.0,
                            tie_word_embeddings=False)
     _check(tmp_path, cfg, DeepseekV3ForCausalLM, init_std=0.08)
+
+
+def test_phi3_fused_projections(tmp_path):
+    from transformers import Phi3Config, Phi3ForCausalLM
+    cfg = Phi3Config(**{**COMMON, "num_key_value_heads": 2}, pad_token_id=0, original_max_position_embeddings=256)
+    _check(tmp_path, cfg, Phi3ForCausalLM, init_std=0.08)
+
+
+def test_granite_multipliers(tmp_path):
+    from transformers import GraniteConfig, GraniteForCausalLM
+    for tied in (True, False):
+        cfg = GraniteConfig(**{**COMMON, "tie_word_embeddings": tied}, embedding_multiplier=6.0, attention_multiplier=0.2,
+                            residual_multiplier=0.35, logits_scaling=3.0)
+        _check(tmp_path / f"tied{int(tied)}", cfg, GraniteForCausalLM, init_std=0.08)
+
+
+def test_qwen2_moe_shared_expert(tmp_path):
+    from transformers import Qwen2MoeConfig, Qwen2MoeForCausalLM
+    cfg = Qwen2MoeConfig(**COMMON, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=32,
+                         shared_expert_intermediate_size=48, norm_topk_prob=False, decoder_sparse_step=1,
+                         mlp_only_layers=[])
+    _check(tmp_path, cfg, Qwen2MoeForCausalLM, init_std=0.08)
+
+
+def test_seed_oss_attention_bias(tmp_path):
+    from transformers import SeedOssConfig, SeedOssForCausalLM
+    cfg = SeedOssConfig(**COMMON, head_dim=16, attention_bias=True, attention_out_bias=False, mlp_bias=False)
+    _check(tmp_path, cfg, SeedOssForCausalLM, init_std=0.08)
+
+
+def test_deepseek_v2_softmax_routing(tmp_path):
+    from transformers import DeepseekV2Config, DeepseekV2ForCausalLM
+    cfg = DeepseekV2Config(vocab_size=256, hidden_size=64, intermediate_size=128, moe_intermediate_size=32,
+                           num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4, n_shared_experts=1,
+                           n_routed_experts=8, routed_scaling_factor=1.0, kv_lora_rank=32, q_lora_rank=None,
+                           qk_rope_head_dim=16, v_head_dim=32, qk_nope_head_dim=32, n_group=1, topk_group=1,
+                           num_experts_per_tok=2, first_k_dense_replace=1, norm_topk_prob=False,
+                           topk_method="greedy", max_position_embeddings=256, rms_norm_eps=1e-6,
+                           rope_theta=10000.0, tie_word_embeddings=False)
+    _check(tmp_path, cfg, DeepseekV2ForCausalLM, init_std=0.08)
+
+
+
+def test_dots1(tmp_path):
+    from transformers import Dots1Config, Dots1ForCausalLM
+    cfg = Dots1Config(**COMMON, head_dim=16, moe_intermediate_size=32, n_routed_experts=8, n_shared_experts=1,
+                      num_experts_per_tok=2, n_group=2, topk_group=1, first_k_dense_replace=1, norm_topk_prob=True,
+                      routed_scaling_factor=1.5, sliding_window=None, layer_types=["full_attention"] * 2)
+    _check(tmp_path, cfg, Dots1ForCausalLM, init_std=0.08)

@@ -126,3 +126,20 @@ class Dots1ForCausalLM(LlamaForCausalLM):
     def load_special_weight(self, name: str, tensor: torch.Tensor) -> bool:
         from sonar_b200.models.deepseek import DeepseekForCausalLM
         return DeepseekForCausalLM.load_special_weight(self, name, tensor)
+
+
+class InterleavedRopeLlama(LlamaForCausalLM):
+    """Families whose rotary embedding pairs neighbouring channels (2i, 2i+1) instead of the two halves of a
+    head (Helium, ERNIE 4.5).  Attention scores only see q·k, which any permutation of a head's channels
+    applied to both q and k leaves unchanged, so the rows of ``q_proj`` / ``k_proj`` are reordered once at load
+    (even channels first, then odd ones) and the half-split rotary kernel is used as it is."""
+
+    def load_special_weight(self, name: str, tensor: torch.Tensor) -> bool:
+        from sonar_b200.loader.weights import _assign
+        if ".self_attn.q_proj." not in name and ".self_attn.k_proj." not in name:
+            return False
+        hd = self.cfg.head_dim
+        t = tensor.reshape(-1, hd // 2, 2, *tensor.shape[1:])            # [heads, pairs, 2, …]
+        t = torch.cat([t[:, :, 0], t[:, :, 1]], dim=1).reshape(tensor.shape)
+        mapped = self.map_checkpoint_name(name)
+        return mapped is not None and _assign(self, mapped[0], t, mapped[1])

@@ -15,6 +15,8 @@ _MODELS: dict[str, tuple[str, str]] = {
     "Phi3ForCausalLM": ("sonar_b200.models.llama_variants", "Phi3ForCausalLM"),
     "GraniteForCausalLM": ("sonar_b200.models.llama_variants", "GraniteForCausalLM"),
     "Qwen2MoeForCausalLM": ("sonar_b200.models.llama_variants", "Qwen2MoeForCausalLM"),
+    "HeliumForCausalLM": ("sonar_b200.models.llama_variants", "InterleavedRopeLlama"),
+    "Ernie4_5ForCausalLM": ("sonar_b200.models.llama_variants", "InterleavedRopeLlama"),
     "Dots1ForCausalLM": ("sonar_b200.models.llama_variants", "Dots1ForCausalLM"),
     "DeepseekV2ForCausalLM": ("sonar_b200.models.deepseek", "DeepseekForCausalLM"),
     "DeepseekV3ForCausalLM": ("sonar_b200.models.deepseek", "DeepseekForCausalLM"),

@@ -153,3 +153,14 @@ def test_dots1(tmp_path):
                       num_experts_per_tok=2, n_group=2, topk_group=1, first_k_dense_replace=1, norm_topk_prob=True,
                       routed_scaling_factor=1.5, sliding_window=None, layer_types=["full_attention"] * 2)
     _check(tmp_path, cfg, Dots1ForCausalLM, init_std=0.08)
+
+
+def test_helium_interleaved_rotary(tmp_path):
+    from transformers import HeliumConfig, HeliumForCausalLM
+    _check(tmp_path, HeliumConfig(**COMMON, head_dim=16), HeliumForCausalLM, init_std=0.08)
+
+
+def test_ernie45_interleaved_rotary(tmp_path):
+    from transformers import Ernie4_5Config, Ernie4_5ForCausalLM
+    _check(tmp_path, Ernie4_5Config(**{**COMMON, "tie_word_embeddings": True}, head_dim=16, use_bias=False),
+           Ernie4_5ForCausalLM, init_std=0.08)

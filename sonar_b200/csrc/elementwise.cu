@@ -98,7 +98,8 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ x, 
 // ------------------------------------------------------------------ RoPE + cache write
 // One warp per (token, head) over packed qkv rows [q heads | k heads | v heads], head_dim 128
 // or 64 (HD/8 lanes active... we use all 32 lanes with HD/32 elements each, NeoX pairing:
-// element i pairs with i + HD/2).  q heads: optional RMSNorm, rotate, write back in place.
+// element i pairs with i + HD/2).  With rot_dim < HD only pairs i < rot_dim/2 rotate (checkpoints whose
+// rotary channels are the first rot_dim of a head are reordered into this layout when they are loaded).  q heads: optional RMSNorm, rotate, write back in place.
 // k heads: optional RMSNorm, rotate, write to cache (and back in place).  v heads: copy to cache.
 // Cache layout [blocks, 2, kv_heads, block_size, HD]; CT is the cache element type.
 template <typename T, typename CT, int HD>
@@ -143,7 +144,7 @@ __global__ void __launch_bounds__(256) rope_cache_kernel(
 #pragma unroll
     for (int i = 0; i < PPL; ++i) {
       int j = lane * PPL + i;          // pair index inside the head
-      if (rot_dim == HD) {
+      if (j < rh) {                    // partial rotary: channels rh … HD/2 of either half pass through
         float c = cs[j], s = cs[rh + j];
         float a = lo[i], b = hi[i];
         lo[i] = a * c - b * s;
@@ -208,7 +209,7 @@ SONAR_API int sonar_rope_and_cache(void* qkv, long row_stride, const long* posit
                                    int head_dim, int block_size, const void* qw, const void* kw, float eps,
                                    float k_scale, float v_scale, int dtype, int cache_dtype, cudaStream_t s) {
   if (n_tokens == 0) return SONAR_OK;
-  if (rot_dim != head_dim) return SONAR_BAD_ARG;  // partial rotary is not built yet
+  if (rot_dim > head_dim || rot_dim <= 0 || (rot_dim & 1)) return SONAR_BAD_ARG;
   long warps = (long)n_tokens * (hq + 2 * hk);
   int blocks = (int)((warps + 7) / 8);
 #define LAUNCH(T, CT, HD)                                                                               \

@@ -172,7 +172,7 @@ class DeepseekMoE(nn.Module):
         n_exp, inter = int(g("n_routed_experts")), int(g("moe_intermediate_size"))
         # V3-family configs written by newer tools may omit the routing keys: sigmoid scores with the
         # bias-corrected group selection are that family's definition, softmax + greedy groups is V2's
-        v3 = g("model_type", "") in ("deepseek_v3", "deepseek_v32", "kimi_k2", "dots1")
+        v3 = g("model_type", "") in ("deepseek_v3", "deepseek_v32", "kimi_k2", "dots1", "glm4_moe")
         self.gate = ReplicatedLinear(cfg.hidden_size, n_exp, False, cfg.dtype, device, None, f"{prefix}.gate")
         self.experts = FusedMoE(
             n_exp, int(g("num_experts_per_tok")), cfg.hidden_size, inter, cfg.dtype, device,

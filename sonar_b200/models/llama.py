@@ -72,12 +72,14 @@ class LlamaAttention(nn.Module):
                                           cfg.dtype, device, quant, f"{prefix}.qkv_proj")
         self.o_proj = RowParallelLinear(cfg.num_attention_heads * hd, hidden, False, cfg.dtype, device, quant,
                                         f"{prefix}.o_proj")
-        qk_eps = cfg.get("rms_norm_eps", 1e-6) if cfg.get("model_type") in ("qwen3", "qwen3_moe", "dots1") else None
+        has_qk_norm = cfg.get("model_type") in ("qwen3", "qwen3_moe", "dots1") or bool(cfg.get("use_qk_norm", False))
+        qk_eps = cfg.get("rms_norm_eps", 1e-6) if has_qk_norm else None
         sw = cfg.get("sliding_window") if cfg.get("use_sliding_window", cfg.get("model_type") == "mistral") else None
         scale = float(cfg.get("attention_multiplier") or hd ** -0.5)      # Granite scales scores by a config value
         self.attn = Attention(self.qkv_proj.num_heads, self.qkv_proj.num_kv_heads, hd, scale, layer_idx,
                               float(cfg.get("rope_theta", 1e4)), cfg.max_model_len, cfg.get("rope_scaling"),
-                              sw, device, qk_eps, cfg.dtype)
+                              sw, device, qk_eps, cfg.dtype,
+                              rot_dim=int(hd * float(cfg.get("partial_rotary_factor", 1.0) or 1.0)))
 
     def forward(self, x: torch.Tensor, meta: AttentionMetadata) -> torch.Tensor:
         tp = get_tp_context()

@@ -143,3 +143,25 @@ class InterleavedRopeLlama(LlamaForCausalLM):
         t = torch.cat([t[:, :, 0], t[:, :, 1]], dim=1).reshape(tensor.shape)
         mapped = self.map_checkpoint_name(name)
         return mapped is not None and _assign(self, mapped[0], t, mapped[1])
+
+
+class Glm4MoeForCausalLM(Dots1ForCausalLM):
+    """GLM-4.5 / 4.6: rotary on the first half of every head only, q/k/v bias, optional per-head q/k norm, and
+    the DeepSeek-V3 style mixture.  The checkpoint keeps a head's rotary channels in front; the rows of
+    ``q_proj`` / ``k_proj`` (weights, biases, and the q/k norm gains) are reordered at load into the layout the
+    rotary kernel turns (``ops.torch_ref.partial_rotary_perm``), which leaves q·k unchanged."""
+
+    def load_special_weight(self, name: str, tensor: torch.Tensor) -> bool:
+        from sonar_b200.loader.weights import _assign
+        from sonar_b200.ops.torch_ref import partial_rotary_perm
+        qk = any(f in name for f in (".self_attn.q_proj.", ".self_attn.k_proj.", ".self_attn.q_norm.", ".self_attn.k_norm."))
+        if not qk:
+            return super().load_special_weight(name, tensor)
+        hd = self.cfg.head_dim
+        rot = int(hd * float(self.cfg.get("partial_rotary_factor", 1.0) or 1.0))
+        if rot != hd:
+            perm = partial_rotary_perm(hd, rot)
+            t = tensor.reshape(-1, hd, *tensor.shape[1:])
+            tensor = t[:, perm].reshape(tensor.shape)
+        mapped = self.map_checkpoint_name(name)
+        return mapped is not None and _assign(self, mapped[0], tensor, mapped[1])

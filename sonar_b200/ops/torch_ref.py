@@ -92,7 +92,10 @@ def _rotate(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, neox: bool) -
 
 def rope(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor,
          head_dim: int, neox: bool = True) -> tuple[torch.Tensor, torch.Tensor]:
-    """q: [T, Hq*D], k: [T, Hk*D]; rotates the first ``rot_dim`` lanes of each head."""
+    """q: [T, Hq*D], k: [T, Hk*D].  Full rotary: channel i pairs with i + D/2.  Partial rotary
+    (``rot_dim < D``) keeps that pairing and rotates only the pairs i < rot_dim/2: channels
+    ``[0, rot/2)`` and ``[D/2, D/2 + rot/2)`` of a head turn, the rest pass through (``partial_rotary_perm``
+    brings a checkpoint's "first rot_dim channels" layout into this one)."""
     rot = cos_sin.shape[-1]
     cs = cos_sin[positions.long()]
     cos, sin = cs[:, None, : rot // 2], cs[:, None, rot // 2:]
@@ -100,9 +103,30 @@ def rope(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, cos_sin: tor
     def one(x: torch.Tensor) -> torch.Tensor:
         t = x.shape[0]
         xv = x.reshape(t, -1, head_dim).float()
-        xr = _rotate(xv[..., :rot], cos, sin, neox)
-        return torch.cat([xr, xv[..., rot:]], dim=-1).reshape(t, -1).to(x.dtype)
+        if rot == head_dim or not neox:
+            xr = _rotate(xv[..., :rot], cos, sin, neox)
+            return torch.cat([xr, xv[..., rot:]], dim=-1).reshape(t, -1).to(x.dtype)
+        rh, half = rot // 2, head_dim // 2
+        a, b = xv[..., :rh], xv[..., half:half + rh]
+        out = xv.clone()
+        out[..., :rh] = a * cos - b * sin
+        out[..., half:half + rh] = b * cos + a * sin
+        return out.reshape(t, -1).to(x.dtype)
     return one(q), one(k)
+
+
+def partial_rotary_perm(head_dim: int, rot_dim: int, interleaved: bool = False) -> torch.Tensor:
+    """Row order (new → old, within one head) that takes q/k projection rows from the checkpoint layout —
+    rotary channels first (``[first halves | second halves]``, or neighbouring pairs when ``interleaved``),
+    then the pass-through channels — to the layout ``rope`` rotates: pair partners D/2 apart."""
+    rh, half = rot_dim // 2, head_dim // 2
+    pa = half - rh
+    if interleaved:
+        first, second = torch.arange(0, rot_dim, 2), torch.arange(1, rot_dim, 2)
+    else:
+        first, second = torch.arange(0, rh), torch.arange(rh, rot_dim)
+    rest = torch.arange(rot_dim, head_dim)
+    return torch.cat([first, rest[:pa], second, rest[pa:]])
 
 
 def qk_norm_rope(q: torch.Tensor, k: torch.Tensor, q_w: torch.Tensor, k_w: torch.Tensor, eps: float,

@@ -33,6 +33,8 @@ def _check(tmp_path, hf_cfg, hf_cls, atol=2e-3, init_std=None, **llm_kw):
             for p in model.parameters():
                 if p.dim() >= 2:
                     p.normal_(0.0, init_std)
+                else:                       # norm gains, biases, router corrections: away from their 1 / 0 defaults
+                    p.add_(torch.randn_like(p) * 0.05)
     path = str(tmp_path / "hf")
     model.save_pretrained(path, safe_serialization=True)
     llm = LLM(path, dtype="float32", device="cpu", max_model_len=128, num_gpu_blocks_override=32, max_num_seqs=4,
@@ -164,3 +166,13 @@ def test_ernie45_interleaved_rotary(tmp_path):
     from transformers import Ernie4_5Config, Ernie4_5ForCausalLM
     _check(tmp_path, Ernie4_5Config(**{**COMMON, "tie_word_embeddings": True}, head_dim=16, use_bias=False),
            Ernie4_5ForCausalLM, init_std=0.08)
+
+
+@pytest.mark.parametrize("qk_norm", [False, True])
+def test_glm4_moe_partial_rotary(tmp_path, qk_norm):
+    from transformers import Glm4MoeConfig, Glm4MoeForCausalLM
+    cfg = Glm4MoeConfig(**COMMON, head_dim=16, partial_rotary_factor=0.5, attention_bias=True, use_qk_norm=qk_norm,
+                        moe_intermediate_size=32, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2,
+                        n_group=1, topk_group=1, first_k_dense_replace=1, norm_topk_prob=True,
+                        routed_scaling_factor=1.5)
+    _check(tmp_path, cfg, Glm4MoeForCausalLM, init_std=0.08)

@@ -85,6 +85,38 @@ def test_rope_and_cache(cu, qk_norm, head_dim):
     _close(cache, cache_ref, 4e-2, 2e-2)
 
 
+@pytest.mark.parametrize("head_dim,rot", [(128, 64), (64, 32), (128, 32)])
+@pytest.mark.parametrize("qk_norm", [False, True])
+def test_rope_partial_rotary(cu, head_dim, rot, qk_norm):
+    """Only the pairs below rot/2 turn; the other channels of both halves pass through (and are still normed
+    and written to the cache)."""
+    torch.manual_seed(4)
+    t, hq, hk, bs, nblocks = 37, 4, 2, 16, 8
+    qkv = torch.randn(t, (hq + 2 * hk) * head_dim, device=DEV, dtype=torch.bfloat16)
+    pos = torch.randint(0, 300, (t,), device=DEV, dtype=torch.int64)
+    cs = ref.build_cos_sin_cache(rot, 512, 1e4, None, DEV)
+    slots = torch.randperm(nblocks * bs, device=DEV)[:t].int()
+    qw = (torch.rand(head_dim, device=DEV) + 0.5).to(torch.bfloat16) if qk_norm else None
+    kw = (torch.rand(head_dim, device=DEV) + 0.5).to(torch.bfloat16) if qk_norm else None
+    cache_ref = torch.zeros(nblocks, 2, hk, bs, head_dim, device=DEV, dtype=torch.bfloat16)
+    cache = cache_ref.clone()
+    q, k, v = qkv.float().split([hq * head_dim, hk * head_dim, hk * head_dim], dim=-1)
+    if qk_norm:
+        q_ref, k_ref = ref.qk_norm_rope(q, k, qw.float(), kw.float(), 1e-6, pos, cs, head_dim)
+    else:
+        q_ref, k_ref = ref.rope(q, k, pos, cs, head_dim)
+    ref.reshape_and_cache(k_ref.reshape(t, hk, head_dim), v.reshape(t, hk, head_dim), cache_ref, slots)
+    work = qkv.clone()
+    cu.rope_and_cache(work, pos, cs, cache, slots, hq, hk, head_dim, qw, kw, 1e-6, 1.0, 1.0)
+    _close(work[:, : hq * head_dim], q_ref, 4e-2, 2e-2)
+    _close(cache, cache_ref, 4e-2, 2e-2)
+    if not qk_norm:      # pass-through channels are bit-identical
+        half, rh = head_dim // 2, rot // 2
+        got = work[:, : hq * head_dim].reshape(t, hq, head_dim)
+        src = qkv[:, : hq * head_dim].reshape(t, hq, head_dim)
+        assert torch.equal(got[..., rh:half], src[..., rh:half]) and torch.equal(got[..., half + rh:], src[..., half + rh:])
+
+
 def _make_attn_case(q_lens, ctx_lens, hq, hk, d, seed=0, nblocks=None):
     torch.manual_seed(seed)
     bs = 16

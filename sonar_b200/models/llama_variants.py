@@ -165,3 +165,52 @@ class Glm4MoeForCausalLM(Dots1ForCausalLM):
             tensor = t[:, perm].reshape(tensor.shape)
         mapped = self.map_checkpoint_name(name)
         return mapped is not None and _assign(self, mapped[0], tensor, mapped[1])
+
+
+class Glm4DecoderLayer(LlamaDecoderLayer):
+    """Sandwich norms: the attention and MLP outputs are normalised once more before they join the residual
+    stream.  The extra norms need complete rows, so this family runs with replicated activations between
+    blocks (``NEEDS_REPLICATED_ACTIVATIONS``)."""
+
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> None:
+        from sonar_b200.layers.norm import RMSNorm
+        super().__init__(cfg, layer_idx, device, prefix)
+        eps = cfg.get("rms_norm_eps", 1e-6)
+        self.post_self_attn_layernorm = RMSNorm(cfg.hidden_size, eps, cfg.dtype, device)
+        self.post_mlp_layernorm = RMSNorm(cfg.hidden_size, eps, cfg.dtype, device)
+
+    def forward(self, h, residual, meta):
+        tp = get_tp_context()
+        x, residual = tp.add_norm(h, residual, self.input_layernorm.weight, self.input_layernorm.eps)
+        a = self.post_self_attn_layernorm(self.self_attn(x, meta))
+        x, residual = tp.add_norm(a, residual, self.post_attention_layernorm.weight, self.post_attention_layernorm.eps)
+        return self.post_mlp_layernorm(self.mlp(x)), residual
+
+
+class Glm4Model(LlamaModel):
+    layer_cls = Glm4DecoderLayer
+
+
+class Glm4ForCausalLM(LlamaForCausalLM):
+    """GLM-4 dense (0414): fused ``gate_up_proj`` in the checkpoint, rotary over neighbouring channel pairs of the
+    first half of each head, q/k/v bias, sandwich norms."""
+    model_cls = Glm4Model
+
+    def load_special_weight(self, name: str, tensor: torch.Tensor) -> bool:
+        from sonar_b200.loader.weights import _assign
+        from sonar_b200.ops.torch_ref import partial_rotary_perm
+        if ".mlp.gate_up_proj." in name:
+            gate, up = tensor.chunk(2, dim=0)
+            return all([_assign(self, name, gate, 0), _assign(self, name, up, 1)])
+        if ".self_attn.q_proj." in name or ".self_attn.k_proj." in name:
+            hd = self.cfg.head_dim
+            rot = int(hd * float(self.cfg.get("partial_rotary_factor", 0.5) or 1.0))
+            perm = partial_rotary_perm(hd, rot, interleaved=True)
+            t = tensor.reshape(-1, hd, *tensor.shape[1:])
+            mapped = self.map_checkpoint_name(name)
+            return mapped is not None and _assign(self, mapped[0], t[:, perm].reshape(tensor.shape), mapped[1])
+        return False
+
+
+#: architectures whose blocks need every token's full row between the two halves of a layer
+NEEDS_REPLICATED_ACTIVATIONS = {"Glm4ForCausalLM"}

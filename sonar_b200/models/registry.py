@@ -17,6 +17,7 @@ _MODELS: dict[str, tuple[str, str]] = {
     "Qwen2MoeForCausalLM": ("sonar_b200.models.llama_variants", "Qwen2MoeForCausalLM"),
     "HeliumForCausalLM": ("sonar_b200.models.llama_variants", "InterleavedRopeLlama"),
     "Ernie4_5ForCausalLM": ("sonar_b200.models.llama_variants", "InterleavedRopeLlama"),
+    "Glm4ForCausalLM": ("sonar_b200.models.llama_variants", "Glm4ForCausalLM"),
     "Glm4MoeForCausalLM": ("sonar_b200.models.llama_variants", "Glm4MoeForCausalLM"),
     "Dots1ForCausalLM": ("sonar_b200.models.llama_variants", "Dots1ForCausalLM"),
     "DeepseekV2ForCausalLM": ("sonar_b200.models.deepseek", "DeepseekForCausalLM"),

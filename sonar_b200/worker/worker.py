@@ -65,6 +65,10 @@ class Worker:
         if mode == "auto":
             plain = (self.cfg.model.quantization is None and self.cfg.model.dtype == torch.bfloat16
                      and not self.cfg.lora.enable_lora and self.cfg.parallel.pipeline_parallel_size == 1)
+            from sonar_b200.models.llama_variants import NEEDS_REPLICATED_ACTIVATIONS
+            if self.cfg.model.architecture in NEEDS_REPLICATED_ACTIVATIONS or self.cfg.speculative.method in (
+                    "eagle", "mtp"):
+                plain = False
             mode = "fused" if plain else "custom"
         ctx = None
         if (self.cfg.device == "cuda" and state.tp_world_size() > 1 and mode in ("fused", "custom")

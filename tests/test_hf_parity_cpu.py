@@ -176,3 +176,9 @@ def test_glm4_moe_partial_rotary(tmp_path, qk_norm):
                         n_group=1, topk_group=1, first_k_dense_replace=1, norm_topk_prob=True,
                         routed_scaling_factor=1.5)
     _check(tmp_path, cfg, Glm4MoeForCausalLM, init_std=0.08)
+
+
+def test_glm4_dense_sandwich_norms(tmp_path):
+    from transformers import Glm4Config, Glm4ForCausalLM
+    cfg = Glm4Config(**COMMON, head_dim=16, partial_rotary_factor=0.5, attention_bias=True, pad_token_id=0)
+    _check(tmp_path, cfg, Glm4ForCausalLM, init_std=0.08)

@@ -135,6 +135,7 @@ class ModelConfig:
     skip_tokenizer_init: bool = False
     served_model_name: str | None = None
     generation_config: dict[str, Any] = field(default_factory=dict)
+    int4_config: dict[str, Any] | None = None   # set for AWQ / GPTQ checkpoints (loader/int4.py)
 
     def __post_init__(self) -> None:
         if not self.hf_config:
@@ -152,6 +153,9 @@ class ModelConfig:
                 self.quantization = "fp8" if qc.get("weight_block_size") else "fp8_tensor"
             elif method in ("compressed-tensors", "modelopt") and "fp8" in str(qc).lower().replace("float8", "fp8"):
                 self.quantization = "fp8_tensor"     # per-tensor or per-channel weight scales, per-token activations
+        if isinstance(qc, dict) and qc.get("quant_method") in ("awq", "gptq"):
+            # weight-only int4: widened to 16 bit while loading
+            self.int4_config = dict(qc)
         if self.quantization not in (None, "fp8", "fp8_tensor"):
             raise ValueError(f"unsupported quantization {self.quantization!r}; supported: fp8, fp8_tensor")
         derived = int(self.hf_config.get("max_position_embeddings", 8192))

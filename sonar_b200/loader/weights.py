@@ -178,7 +178,11 @@ def load_model(cfg: EngineConfig | ModelConfig, device: torch.device | str, cls=
     if mcfg.load_format == "dummy":
         initialize_dummy_weights(model, mcfg.seed)
     else:
-        loaded = load_weights_from(model, _iter_checkpoint(mcfg.checkpoint_dir))
+        weights = _iter_checkpoint(mcfg.checkpoint_dir)
+        if mcfg.int4_config:
+            from sonar_b200.loader.int4 import widen_int4_checkpoint
+            weights = widen_int4_checkpoint(weights, mcfg.int4_config)
+        loaded = load_weights_from(model, weights)
         logger.info("loaded %d tensors from %s", len(loaded), mcfg.checkpoint_dir)
         if not loaded:
             raise RuntimeError(f"no tensor of {mcfg.checkpoint_dir} matched the model")

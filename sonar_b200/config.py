@@ -385,6 +385,7 @@ class EngineConfig:
     observability: ObservabilityConfig = field(default_factory=ObservabilityConfig)
     lora: LoRAConfig = field(default_factory=LoRAConfig)
     kv_transfer: KVTransferConfig = field(default_factory=KVTransferConfig)
+    logits_processors: list = field(default_factory=list)      # classes or qualified names (sample/logits_processor.py)
     enable_sleep_mode: bool = False
     enforce_eager: bool = False
     device: str = "auto"               # auto | cuda | cpu
@@ -452,6 +453,7 @@ class EngineArgs:
     kv_offload_cpu_gb: float = 0.0
     kv_offload_cpu_blocks: int = 0
     kv_transfer_config: dict | None = None     # fields of KVTransferConfig (a JSON object on the command line)
+    logits_processors: list | None = None      # qualified class names (a JSON list on the command line) or classes
     # LoRA
     enable_lora: bool = False
     max_loras: int = 4
@@ -532,6 +534,7 @@ class EngineArgs:
         kv_transfer = kvt if isinstance(kvt, KVTransferConfig) else KVTransferConfig(**(kvt or {}))
         return EngineConfig(model=model, cache=cache, parallel=parallel, scheduler=sched,
                             speculative=spec, observability=obs, lora=lora, kv_transfer=kv_transfer,
+                            logits_processors=list(self.logits_processors or []),
                             enable_sleep_mode=self.enable_sleep_mode,
                             enforce_eager=self.enforce_eager, device=device)
 
@@ -544,7 +547,7 @@ class EngineArgs:
                 continue  # positional / --model handled by the caller
             if f.type in ("bool", bool):
                 parser.add_argument(flag, action=argparse.BooleanOptionalAction, default=f.default)
-            elif f.name in ("hf_overrides", "lora_modules", "kv_transfer_config", "speculative_config"):
+            elif f.name in ("hf_overrides", "lora_modules", "kv_transfer_config", "speculative_config", "logits_processors"):
                 parser.add_argument(flag, type=json.loads, default=None)
             else:
                 base = str(f.type).replace(" | None", "")

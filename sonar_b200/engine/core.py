@@ -24,6 +24,11 @@ from sonar_b200.utils.tracing import get_tracer
 logger = init_logger(__name__)
 
 
+def _custom_logits_processors(cfg) -> bool:
+    from sonar_b200.sample.logits_processor import any_configured
+    return any_configured(cfg)
+
+
 class EngineCore:
     def __init__(self, cfg: EngineConfig, executor_class: type[Executor] | None = None) -> None:
         from sonar_b200.plugins import load_general_plugins
@@ -65,7 +70,8 @@ class EngineCore:
         self.sleeping = False
         self.run_ahead_steps = 0
         self.pending = None              # (scheduler output, deferred runner output) of the step in flight
-        self.run_ahead_ok = cfg.scheduler.async_scheduling and getattr(self.executor, "supports_defer", False)
+        self.run_ahead_ok = (cfg.scheduler.async_scheduling and getattr(self.executor, "supports_defer", False)
+                             and not _custom_logits_processors(cfg))  # they see complete token histories
         self.steps = 0
         self.host_time = {"schedule": 0.0, "execute": 0.0, "update": 0.0}
         logger.info("engine core ready in %.1fs (%d KV blocks of %d tokens)", time.time() - t0,

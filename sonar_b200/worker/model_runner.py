@@ -169,6 +169,9 @@ class ModelRunner:
         if self.spec_cfg.method == "ngram":
             from sonar_b200.sample.spec_decode import NgramProposer
             self._ngram = NgramProposer(self.spec_cfg)
+        from sonar_b200.sample.logits_processor import load_logits_processors
+        self.logits_processors = load_logits_processors(cfg.logits_processors, cfg, device)
+        self._lp_history = any(p.needs_history for p in self.logits_processors)
         self._suffix = None
         if self.spec_cfg.method == "suffix":
             from sonar_b200.sample.spec_decode import SuffixProposer
@@ -573,7 +576,8 @@ class ModelRunner:
             p = b.params[r]
             lo, cnt = row_span[j]
             npmt, ntok = int(b.num_prompt[r]), int(b.num_tokens[r])
-            need_hist = p.needs_penalties or p.needs_extended or p.min_tokens > 0 or bool(p._bad_words_token_ids)
+            need_hist = (p.needs_penalties or p.needs_extended or p.min_tokens > 0 or bool(p._bad_words_token_ids)
+                         or self._lp_history)
             for c in range(cnt):
                 params.append(p)
                 sample_rids.append(req_ids[i])
@@ -598,6 +602,10 @@ class ModelRunner:
                     ridx = ridx.to(logits.device)
                 logits = logits.float() if logits.dtype != torch.float32 else logits
                 ops.apply_token_bitmask(logits, bm, ridx)
+        if self.logits_processors:
+            from sonar_b200.sample.logits_processor import RowView, run_logits_processors
+            views = [RowView(rid, p, pr, ou) for rid, p, pr, ou in zip(sample_rids, params, prompts, outs_hist)]
+            logits = run_logits_processors(self.logits_processors, logits, views)
         mu = {k: b.mirostat_mu[rid] for k, rid in enumerate(sample_rids) if rid in b.mirostat_mu}
         md = make_sampling_metadata(params, prompts, outs_hist, logits.device, gens, mu, sample_rids)
         res = self.sampler(logits, md)

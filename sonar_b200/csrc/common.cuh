@@ -1,5 +1,6 @@
 // Shared device/host helpers for the sonar_b200 kernel library (sm_100a only).
 #pragma once
+#include <type_traits>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
@@ -68,10 +69,26 @@ template <> __device__ __forceinline__ float from_f<float>(float v) { return v; 
 
 // 16-byte vector of 8 half-precision values <-> 8 floats
 template <typename T>
-__device__ __forceinline__ void unpack8(const uint4& raw, float* f) {
-  const T* p = reinterpret_cast<const T*>(&raw);
+__device__ __forceinline__ void unpack8(uint4 raw, float* f) {
+  // `raw` comes BY VALUE: the caller's `ptr[v]` is then one 128-bit load.  Taking a reference to global
+  // memory and reading eight 16-bit elements through it compiled to eight narrow loads per vector, which
+  // saturated the LSU pipe (l1tex__data_pipe_lsu_wavefronts ≈ 90 %) long before DRAM.
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-  for (int i = 0; i < 8; ++i) f[i] = to_f<T>(p[i]);
+  for (int i = 0; i < 4; ++i) {
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    } else if constexpr (std::is_same<T, __half>::value) {
+      const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      f[2 * i] = v.x;
+      f[2 * i + 1] = v.y;
+    } else {
+      const T* p = reinterpret_cast<const T*>(&w[i]);
+      f[2 * i] = to_f<T>(p[0]);
+      f[2 * i + 1] = to_f<T>(p[1]);
+    }
+  }
 }
 template <typename T>
 __device__ __forceinline__ uint4 pack8(const float* f) {

@@ -79,19 +79,35 @@ int launch_rms_norm(const T* x, T* residual, const T* w, T* out, int rows, int h
 template <typename T>
 __global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int d,
                                                        long x_stride, long total_vec) {
-  // grid-stride over (row, vec) pairs; x row = [gate(d) | up(d)]
+  // grid-stride over (row, vec) pairs, two per trip so that four 16-byte loads are in flight per thread
+  // before the first use; x row = [gate(d) | up(d)]
   const int vec_per_row = d >> 3;
-  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total_vec; i += (long)gridDim.x * blockDim.x) {
-    long row = i / vec_per_row;
-    int v = (int)(i - row * vec_per_row);
-    const uint4* g = reinterpret_cast<const uint4*>(x + row * x_stride) + v;
-    const uint4* u = reinterpret_cast<const uint4*>(x + row * x_stride + d) + v;
+  const long stride = (long)gridDim.x * blockDim.x;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total_vec; i += 2 * stride) {
+    const long i2 = i + stride;
+    const bool two = i2 < total_vec;
+    const long row = i / vec_per_row, row2 = two ? i2 / vec_per_row : row;
+    const int v = (int)(i - row * vec_per_row), v2 = two ? (int)(i2 - row2 * vec_per_row) : v;
+    const uint4 g = reinterpret_cast<const uint4*>(x + row * x_stride)[v];
+    const uint4 u = reinterpret_cast<const uint4*>(x + row * x_stride + d)[v];
+    uint4 g2 = g, u2 = u;
+    if (two) {
+      g2 = reinterpret_cast<const uint4*>(x + row2 * x_stride)[v2];
+      u2 = reinterpret_cast<const uint4*>(x + row2 * x_stride + d)[v2];
+    }
     float a[8], b[8];
-    unpack8<T>(*g, a);
-    unpack8<T>(*u, b);
+    unpack8<T>(g, a);
+    unpack8<T>(u, b);
 #pragma unroll
     for (int j = 0; j < 8; ++j) a[j] = (a[j] / (1.f + __expf(-a[j]))) * b[j];
     reinterpret_cast<uint4*>(out + row * (long)d)[v] = pack8<T>(a);
+    if (two) {
+      unpack8<T>(g2, a);
+      unpack8<T>(u2, b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] = (a[j] / (1.f + __expf(-a[j]))) * b[j];
+      reinterpret_cast<uint4*>(out + row2 * (long)d)[v2] = pack8<T>(a);
+    }
   }
 }
 

@@ -153,7 +153,8 @@ class ModelConfig:
                 self.quantization = "fp8" if qc.get("weight_block_size") else "fp8_tensor"
             elif method in ("compressed-tensors", "modelopt") and "fp8" in str(qc).lower().replace("float8", "fp8"):
                 self.quantization = "fp8_tensor"     # per-tensor or per-channel weight scales, per-token activations
-        if isinstance(qc, dict) and qc.get("quant_method") in ("awq", "gptq"):
+        if isinstance(qc, dict) and (qc.get("quant_method") in ("awq", "gptq") or (
+                qc.get("quant_method") == "compressed-tensors" and qc.get("format") == "pack-quantized")):
             # weight-only int4: widened to 16 bit while loading
             self.int4_config = dict(qc)
         if self.quantization not in (None, "fp8", "fp8_tensor"):

@@ -14,7 +14,11 @@ Layouts (as written by the AutoAWQ and AutoGPTQ / GPTQModel exporters):
   packs along the output dimension in natural order and, in the classic ``gptq`` checkpoint format, stores
   ``z - 1``; ``scales [in/g, out]``; optional ``g_idx [in]`` maps input channels to groups (act-order).
 
-Parity: ``aphrodite/model_executor/layers/quantization/{awq,gptq}.py`` (tensor layouts and the dequantisation
+* compressed-tensors ``pack-quantized`` (llm-compressor W4A16): ``weight_packed [out, in/8]`` packs along the
+  INPUT dimension in natural order, values stored offset by 8 when symmetric; ``weight_scale [out, in/g]``;
+  optional ``weight_zero_point [out/8, in/g]`` packed along the output dimension; ``weight_shape``.
+
+Parity: ``aphrodite/model_executor/layers/quantization/{awq,gptq}.py``, ``compressed_tensors/`` (tensor layouts and the dequantisation
 formula; the reference keeps the weights packed and runs Marlin / exllama kernels).
 """
 from __future__ import annotations
@@ -64,10 +68,55 @@ def dequantize_gptq(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.T
     return w.t().contiguous()
 
 
+def dequantize_compressed_tensors(packed: torch.Tensor, scale: torch.Tensor, zero_point: torch.Tensor | None,
+                                  group_size: int, shape: tuple[int, int] | None = None) -> torch.Tensor:
+    """→ ``[out, in]``.  Symmetric checkpoints (no zero point) store ``q + 8``."""
+    q = _unpack_cols(packed)                                   # [out, in]
+    n_out, n_in = (int(shape[0]), int(shape[1])) if shape is not None else tuple(q.shape)
+    q = q[:n_out, :n_in]
+    g = n_in if group_size in (-1, 0, None) else group_size
+    grp = torch.arange(n_in) // g
+    if zero_point is None:
+        z = torch.full((n_out, scale.shape[1]), 8, dtype=torch.int32)
+    else:
+        z = _unpack_rows(zero_point)[:n_out] if zero_point.dtype == torch.int32 else zero_point.to(torch.int32)
+    return ((q - z[:, grp]).to(scale.dtype) * scale[:, grp]).contiguous()
+
+
+def widen_compressed_tensors(weights: Iterator[tuple[str, torch.Tensor]], qcfg: dict) -> Iterator[tuple[str, torch.Tensor]]:
+    """``weight_packed`` / ``weight_scale`` / ``weight_shape`` (/ ``weight_zero_point``) → ``weight``."""
+    group, sym = 128, True
+    for grp_cfg in (qcfg.get("config_groups") or {}).values():
+        w = grp_cfg.get("weights") or {}
+        if w.get("num_bits", 4) != 4:
+            raise ValueError("compressed-tensors pack-quantized checkpoints are supported for 4-bit weights only")
+        group = w.get("group_size") or -1
+        sym = bool(w.get("symmetric", True))
+    need = {"weight_packed", "weight_scale", "weight_shape"} | (set() if sym else {"weight_zero_point"})
+    pending: dict[str, dict[str, torch.Tensor]] = {}
+    for name, t in weights:
+        prefix, _, leaf = name.rpartition(".")
+        if leaf not in ("weight_packed", "weight_scale", "weight_shape", "weight_zero_point", "weight_g_idx"):
+            yield name, t
+            continue
+        parts = pending.setdefault(prefix, {})
+        parts[leaf] = t
+        if need <= parts.keys():
+            yield prefix + ".weight", dequantize_compressed_tensors(
+                parts["weight_packed"], parts["weight_scale"], parts.get("weight_zero_point"), group,
+                tuple(parts["weight_shape"].tolist()))
+            del pending[prefix]
+    if pending:
+        raise ValueError(f"incomplete pack-quantized tensors for {sorted(pending)[:3]}")
+
+
 def widen_int4_checkpoint(weights: Iterator[tuple[str, torch.Tensor]], qcfg: dict) -> Iterator[tuple[str, torch.Tensor]]:
     """Wrap a checkpoint iterator: ``qweight`` / ``qzeros`` / ``scales`` (/ ``g_idx``) triples come out as one
     ``weight`` tensor; everything else passes through."""
     method = qcfg.get("quant_method")
+    if method == "compressed-tensors":
+        yield from widen_compressed_tensors(weights, qcfg)
+        return
     bits = int(qcfg.get("bits", qcfg.get("w_bit", 4)))
     if bits != 4:
         raise ValueError(f"{method} checkpoints with {bits}-bit weights are not supported (4-bit only)")

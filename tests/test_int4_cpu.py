@@ -90,3 +90,23 @@ def test_engine_loads_int4_checkpoint(tmp_path, method):
     assert list(got.token_ids) == list(want.token_ids)
     plain = LLM(base, **kw).generate(prompt, sp)[0].outputs[0]
     assert len(plain.token_ids) == 8                                # the unquantised model runs too (sanity)
+
+
+@pytest.mark.parametrize("sym", [True, False])
+def test_compressed_tensors_pack_quantized(tmp_path, sym):
+    torch.manual_seed(2)
+    w = torch.randn(40, 64) * 0.1
+    q, z, s = _quantize(w, 32, sym)                                # q [in, out], z/s [in/g, out]
+    want = ((q - z.repeat_interleave(32, 0)).float() * s.float().repeat_interleave(32, 0)).t()
+    packed = int4.pack_cols(q.t().contiguous())                   # [out, in/8]
+    zp = None if sym else int4.pack_rows(z.t().contiguous())      # [out/8, in/g]
+    got = int4.dequantize_compressed_tensors(packed, s.t().contiguous(), zp, 32, (40, 64))
+    assert torch.allclose(got.float(), want, atol=1e-3)
+    qcfg = {"quant_method": "compressed-tensors", "format": "pack-quantized",
+            "config_groups": {"group_0": {"weights": {"num_bits": 4, "group_size": 32, "symmetric": sym}}}}
+    stream = [("a.norm.weight", torch.ones(4)), ("a.proj.weight_packed", packed), ("a.proj.weight_scale", s.t().contiguous()),
+              ("a.proj.weight_shape", torch.tensor([40, 64]))]
+    if not sym:
+        stream.append(("a.proj.weight_zero_point", zp))
+    out = dict(int4.widen_int4_checkpoint(iter(stream), qcfg))
+    assert set(out) == {"a.norm.weight", "a.proj.weight"} and torch.allclose(out["a.proj.weight"].float(), want, atol=1e-3)

@@ -40,6 +40,8 @@ class NewRequestData:
     num_computed_tokens: int
     pooling: bool = False
     lora_name: str | None = None
+    embeds: list | None = None
+    mm_inputs: list | None = None
 
 
 @dataclass
@@ -335,7 +337,8 @@ class Scheduler:
                     sampling_params=req.sampling_params,
                     block_ids=list(self.kv.get_block_ids(req.request_id)),
                     num_computed_tokens=req.num_computed_tokens,
-                    pooling=req.pooling_params is not None, lora_name=req.lora_name))
+                    pooling=req.pooling_params is not None, lora_name=req.lora_name,
+                    embeds=req.embeds, mm_inputs=req.mm_inputs))
                 self._known_to_runner.add(req.request_id)
 
         total = cfg.max_num_batched_tokens - budget

@@ -11,6 +11,8 @@ Parity: ``aphrodite/v1/engine/llm_engine.py:48`` (``add_request`` :207, ``step``
 from __future__ import annotations
 
 import time
+
+import torch
 from typing import Any
 
 from sonar_b200.config import EngineArgs, EngineConfig
@@ -41,6 +43,24 @@ class InputProcessor:
                 arrival_time: float | None = None, priority: int = 0, lora_name: str | None = None,
                 cache_salt: str | None = None) -> tuple[str | None, EngineCoreRequest]:
         text: str | None = None
+        embeds = mm_inputs = emb_salt = None
+        if isinstance(prompt, dict) and prompt.get("prompt_embeds") is not None:
+            # the prompt as embeddings [n, hidden]: placeholder ids keep positions and KV bookkeeping as usual
+            e = torch.as_tensor(prompt["prompt_embeds"])
+            if e.dim() != 2 or e.shape[1] != self.cfg.model.hidden_size:
+                raise ValueError(f"prompt_embeds must be [num_tokens, {self.cfg.model.hidden_size}], got {tuple(e.shape)}")
+            embeds = [(0, e.detach().cpu().contiguous())]
+            prompt = {**prompt, "prompt_token_ids": [0] * e.shape[0]}
+        if isinstance(prompt, dict) and prompt.get("multi_modal_data"):
+            from sonar_b200.multimodal import expand_placeholders
+            prompt, mm_inputs = expand_placeholders(self.cfg.model, self.tokenizer, prompt)
+        if embeds is not None or mm_inputs is not None:
+            import hashlib
+            h = hashlib.sha1()
+            for item in (embeds or []) + (mm_inputs or []):
+                t = item[-1]
+                h.update(t.detach().cpu().contiguous().view(torch.uint8).numpy().tobytes())
+            emb_salt = "|emb:" + h.hexdigest()          # same placeholder tokens, other content: no shared prefix
         if isinstance(prompt, str):
             text = prompt
         elif isinstance(prompt, dict):
@@ -89,10 +109,12 @@ class InputProcessor:
             sp, pp = params, None
         else:
             sp, pp = None, params
+        if emb_salt:
+            cache_salt = (cache_salt or "") + emb_salt
         req = EngineCoreRequest(request_id=request_id, prompt_token_ids=ids, sampling_params=sp,
                                 pooling_params=pp, eos_token_id=eos_id,
                                 arrival_time=arrival_time or time.time(), priority=priority,
-                                cache_salt=cache_salt, lora_name=lora_name)
+                                cache_salt=cache_salt, lora_name=lora_name, embeds=embeds, mm_inputs=mm_inputs)
         return text, req
 
 

@@ -136,13 +136,17 @@ class LlamaModel(nn.Module):
             self.norm = RMSNorm(cfg.hidden_size, cfg.get("rms_norm_eps", 1e-6), cfg.dtype, device)
 
     def forward(self, input_ids: torch.Tensor | None, meta: AttentionMetadata,
-                intermediate: tuple[torch.Tensor, torch.Tensor | None] | None = None):
+                intermediate: tuple[torch.Tensor, torch.Tensor | None] | None = None, embed_patch=None):
+        """``embed_patch = (token indices, rows)``: these tokens enter the first layer with the given embedding
+        instead of their id's (prompt embeddings, multimodal encoder outputs)."""
         tp = get_tp_context()
         if self.is_first:
             if tp.scattered:
                 h = self.embed_tokens(tp.shard_token_ids(input_ids))
             else:
                 h = tp.embed_reduce(self.embed_tokens(input_ids))
+            if embed_patch is not None:
+                h = h.index_copy(0, embed_patch[0], embed_patch[1].to(h.dtype))
             residual = None
         else:
             h, residual = intermediate
@@ -174,8 +178,10 @@ class LlamaForCausalLM(nn.Module):
             else:
                 self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, cfg.dtype, device, "lm_head")
 
-    def forward(self, input_ids, meta, intermediate=None):
-        return self.model(input_ids, meta, intermediate)
+    supports_embed_patch = True
+
+    def forward(self, input_ids, meta, intermediate=None, embed_patch=None):
+        return self.model(input_ids, meta, intermediate, embed_patch)
 
     def compute_logits(self, hidden: torch.Tensor) -> torch.Tensor:
         return self.lm_head.logits(hidden)

@@ -66,6 +66,11 @@ class EngineCoreRequest:
     lora_name: str | None = None
     data_parallel_rank: int | None = None
     client_index: int = 0
+    # input embeddings that replace the embedded token ids at prompt positions: [(start, tensor [k, H])]
+    # (a whole-prompt ``prompt_embeds``, or the output of a multimodal encoder at its placeholder tokens)
+    embeds: list | None = None
+    # multimodal encoder inputs the worker turns into such embeddings: [(start, num_tokens, kind, tensor)]
+    mm_inputs: list | None = None
 
 
 @dataclass
@@ -116,7 +121,7 @@ class Request:
         "arrival_time", "priority", "cache_salt", "lora_name", "client_index", "status", "stop_reason",
         "output_token_ids", "all_token_ids", "num_prompt_tokens", "num_computed_tokens",
         "num_cached_tokens", "spec_token_ids", "max_tokens", "block_hashes", "num_preemptions",
-        "events", "num_output_placeholders", "_hasher", "grammar")
+        "events", "num_output_placeholders", "_hasher", "grammar", "embeds", "mm_inputs")
 
     def __init__(self, core_req: EngineCoreRequest, block_hasher=None) -> None:
         self.request_id = core_req.request_id
@@ -128,6 +133,8 @@ class Request:
         self.priority = core_req.priority
         self.cache_salt = core_req.cache_salt
         self.lora_name = core_req.lora_name
+        self.embeds = core_req.embeds
+        self.mm_inputs = core_req.mm_inputs
         self.client_index = core_req.client_index
         self.status = RequestStatus.WAITING
         self.stop_reason: int | str | None = None

@@ -186,6 +186,10 @@ class ModelRunner:
         self.eplb = None
         self.kv_connector = None
         self.drafter = None
+        self.req_embeds: dict[str, list[tuple[int, torch.Tensor]]] = {}    # request → [(start, rows on device)]
+        self.mm_encoder = None
+        if getattr(self.model, "encode_multimodal", None) is not None:
+            self.mm_encoder = self.model.encode_multimodal
         if self.spec_cfg.method in ("draft_model", "eagle", "mtp", "medusa"):
             if self.pp is not None:
                 raise ValueError("draft-model speculative decoding does not run under pipeline parallelism")
@@ -326,6 +330,10 @@ class ModelRunner:
                 self.drafter.on_remove(rid)
             for nr in so.scheduled_new_reqs:
                 self.drafter.on_add(nr.req_id, nr.num_computed_tokens)
+        for rid in list(so.finished_req_ids) + list(so.preempted_req_ids):
+            self.req_embeds.pop(rid, None)
+        for nr in so.scheduled_new_reqs:
+            self._register_embeds(nr)
         for nr in so.scheduled_new_reqs:
             if nr.req_id in b.index:
                 b.remove(nr.req_id)
@@ -343,6 +351,51 @@ class ModelRunner:
                 n = int(b.num_tokens[row])
                 b.token_ids[row, n:n + len(toks)] = toks
                 b.num_tokens[row] = n + len(toks)
+
+    # --------------------------------------------------------------- input embeddings
+    def _register_embeds(self, nr) -> None:
+        """Embeddings that stand in for token ids at prompt positions: given with the request, or computed
+        here by the model's multimodal encoder (once per request; kept until the request ends)."""
+        patches = []
+        for start, rows in (nr.embeds or []):
+            patches.append((int(start), rows.to(self.device, self.model_cfg.dtype)))
+        if nr.mm_inputs:
+            if self.mm_encoder is None:
+                raise ValueError(f"model {self.model_cfg.architecture} takes no multimodal inputs")
+            with torch.inference_mode():
+                for start, n_tok, kind, data in nr.mm_inputs:
+                    rows = self.mm_encoder(kind, data.to(self.device))
+                    if rows.shape[0] != n_tok:
+                        raise ValueError(f"{kind} encoder produced {rows.shape[0]} embeddings for {n_tok} placeholders")
+                    patches.append((int(start), rows.to(self.model_cfg.dtype)))
+        if patches:
+            if get_tp_context().scattered:
+                raise ValueError("input embeddings need replicated activations: use SONAR_TP_COMM=custom or nccl")
+            if not getattr(self.model, "supports_embed_patch", False):
+                raise ValueError(f"model {self.model_cfg.architecture} does not take input embeddings")
+            self.req_embeds[nr.req_id] = patches
+
+    def _embed_patch(self, rows: np.ndarray, q_lens: np.ndarray):
+        """(token indices of this step, embedding rows) for the scheduled prompt positions that have one."""
+        if not self.req_embeds:
+            return None
+        b = self.batch
+        idx: list[torch.Tensor] = []
+        vals: list[torch.Tensor] = []
+        off = 0
+        for r, q in zip(rows, q_lens):
+            patches = self.req_embeds.get(b.req_ids[r])
+            c = int(b.num_computed[r])
+            if patches:
+                for start, e in patches:
+                    lo, hi = max(start, c), min(start + e.shape[0], c + int(q))
+                    if lo < hi:
+                        idx.append(torch.arange(off + lo - c, off + hi - c))
+                        vals.append(e[lo - start:hi - start])
+            off += int(q)
+        if not idx:
+            return None
+        return torch.cat(idx).to(self.device), torch.cat(vals)
 
     # --------------------------------------------------------------- inputs
     def _prepare_inputs(self, so: SchedulerOutput) -> tuple[AttentionMetadata, np.ndarray, np.ndarray]:
@@ -469,7 +522,9 @@ class ModelRunner:
             ids = self.d_input_ids[:total]
             if self.pp is not None and not self.pp.is_first_rank:
                 intermediate = self._recv_intermediate(tp.local_tokens(total))
-            out = self.model(ids, meta, intermediate)
+            patch = self._embed_patch(rows, q_lens)
+            out = (self.model(ids, meta, intermediate, embed_patch=patch) if patch is not None
+                   else self.model(ids, meta, intermediate))
             if self.pp is not None and not self.pp.is_last_rank:
                 self.stats["launch_s"] += time.perf_counter() - t1
                 self._send_intermediate(out)

@@ -69,6 +69,14 @@ ARCH_PRESETS: dict[str, dict[str, Any]] = {
         num_attention_heads=4, num_key_value_heads=2, head_dim=128, intermediate_size=1024,
         vocab_size=2048, rope_theta=5e5, rms_norm_eps=1e-5, tie_word_embeddings=False,
         max_position_embeddings=4096),
+    "tiny-llava": dict(
+        architectures=["LlavaForConditionalGeneration"], model_type="llava", num_hidden_layers=2, hidden_size=512,
+        num_attention_heads=4, num_key_value_heads=2, head_dim=128, intermediate_size=1024,
+        vocab_size=2048, rope_theta=5e5, rms_norm_eps=1e-5, tie_word_embeddings=False,
+        max_position_embeddings=4096, image_token_index=2000, vision_feature_layer=-2,
+        vision_feature_select_strategy="default", projector_hidden_act="gelu",
+        vision_config=dict(model_type="clip_vision_model", hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                           num_attention_heads=4, image_size=56, patch_size=14, hidden_act="quick_gelu")),
     "tiny-qwen3": dict(
         architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=256,
         num_attention_heads=4, num_key_value_heads=2, head_dim=128, intermediate_size=512,
@@ -110,6 +118,12 @@ def _normalise_hf_config(cfg: dict[str, Any]) -> dict[str, Any]:
     """Config files written by newer ``transformers`` keep the rotary settings in one ``rope_parameters``
     object (``rope_theta`` inside, ``rope_type: default`` when unscaled) and nest the language model of
     a multimodal checkpoint under ``text_config``; the model code reads the classic flat keys."""
+    tc = cfg.get("text_config")
+    if isinstance(tc, dict):
+        for k, v in tc.items():                      # the language model's keys, flat; the wrapper's own keys win
+            if k not in ("architectures", "model_type") and k not in cfg:
+                cfg[k] = v
+        cfg.setdefault("text_model_type", tc.get("model_type"))
     rp = cfg.get("rope_parameters")
     if isinstance(rp, dict):
         if "rope_theta" in rp:

@@ -12,6 +12,7 @@ _MODELS: dict[str, tuple[str, str]] = {
     "Qwen3ForCausalLM": ("sonar_b200.models.llama", "LlamaForCausalLM"),
     "Qwen3MoeForCausalLM": ("sonar_b200.models.qwen3_moe", "Qwen3MoeForCausalLM"),
     "MixtralForCausalLM": ("sonar_b200.models.qwen3_moe", "MixtralForCausalLM"),
+    "LlavaForConditionalGeneration": ("sonar_b200.models.llava", "LlavaForConditionalGeneration"),
     "Phi3ForCausalLM": ("sonar_b200.models.llama_variants", "Phi3ForCausalLM"),
     "GraniteForCausalLM": ("sonar_b200.models.llama_variants", "GraniteForCausalLM"),
     "Qwen2MoeForCausalLM": ("sonar_b200.models.llama_variants", "Qwen2MoeForCausalLM"),

@@ -185,3 +185,27 @@ def test_hidden_state_proposers_on_gpu(model, spec):
     assert same >= 0.85 * 12 * len(prompts), (got, want)
     if spec["method"] != "suffix":
         assert st["scheduler"].spec_num_drafts > 0
+
+
+def test_llava_image_request_on_gpu():
+    """An image request on the CUDA path: the CLIP tower runs in the worker, its projected features are patched
+    over the 16 placeholder positions; a text-only request of the same model is unaffected by the patching, and a
+    different image gives different log-probabilities."""
+    from sonar_b200 import LLM, SamplingParams
+    llm = LLM("tiny-llava", max_model_len=512, num_gpu_blocks_override=128, max_num_seqs=8, max_num_batched_tokens=64,
+              seed=0, skip_tokenizer_init=True)
+    sp = SamplingParams(max_tokens=8, temperature=0, ignore_eos=True, logprobs=1, detokenize=False)
+    g = torch.Generator().manual_seed(0)
+    img_a, img_b = torch.randn(3, 56, 56, generator=g), torch.randn(3, 56, 56, generator=g)
+    text = {"prompt_token_ids": [7, 8, 9, 10, 11, 12]}
+    base = llm.generate([text], sp)[0].outputs[0]
+    outs = llm.generate([{"prompt_token_ids": [7, 8, 2000, 9, 10], "multi_modal_data": {"image": img_a}}, text,
+                         {"prompt_token_ids": [7, 8, 2000, 9, 10], "multi_modal_data": {"image": img_b}}], sp)
+    assert len(outs[0].prompt_token_ids) == 4 + 16 and len(outs[0].outputs[0].token_ids) == 8
+    assert outs[1].outputs[0].token_ids == base.token_ids
+
+    def lps(o):
+        c = o.outputs[0]
+        return [d[t] if isinstance(d[t], float) else d[t].logprob for t, d in zip(c.token_ids, c.logprobs)]
+    assert lps(outs[0]) != lps(outs[2])
+    llm.shutdown()

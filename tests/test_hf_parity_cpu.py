@@ -182,3 +182,51 @@ def test_glm4_dense_sandwich_norms(tmp_path):
     from transformers import Glm4Config, Glm4ForCausalLM
     cfg = Glm4Config(**COMMON, head_dim=16, partial_rotary_factor=0.5, attention_bias=True, pad_token_id=0)
     _check(tmp_path, cfg, Glm4ForCausalLM, init_std=0.08)
+
+
+def test_llava_clip_tower_projector_and_placeholders(tmp_path):
+    """Image + text against Hugging Face LLaVA: the CLIP tower's second-to-last hidden state, projected, fills the
+    expanded image-token positions; greedy tokens and log-probabilities agree."""
+    from transformers import CLIPVisionConfig, LlamaConfig, LlavaConfig, LlavaForConditionalGeneration
+    vc = CLIPVisionConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4,
+                          image_size=28, patch_size=14, projection_dim=16)
+    tc = LlamaConfig(**COMMON, head_dim=16)
+    cfg = LlavaConfig(vision_config=vc, text_config=tc, image_token_index=250, vision_feature_layer=-2,
+                      vision_feature_select_strategy="default", image_seq_length=4)
+    torch.manual_seed(0)
+    model = LlavaForConditionalGeneration(cfg).float().eval()
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() >= 2:
+                p.normal_(0.0, 0.08)
+            else:
+                p.add_(torch.randn_like(p) * 0.05)
+    path = str(tmp_path / "hf")
+    model.save_pretrained(path, safe_serialization=True)
+    pixels = torch.randn(3, 28, 28)
+    prompt = [5, 17, 250, 99, 45, 200, 7]                          # one image token → 4 placeholders
+    expanded = [5, 17, 250, 250, 250, 250, 99, 45, 200, 7]
+    ids = torch.tensor([expanded])
+    want_t, want_lp = [], []
+    with torch.no_grad():
+        for _ in range(N_NEW):
+            lp = torch.log_softmax(model(input_ids=ids, pixel_values=pixels[None]).logits[0, -1].float(), -1)
+            t = int(lp.argmax())
+            want_t.append(t)
+            want_lp.append(float(lp[t]))
+            ids = torch.cat([ids, torch.tensor([[t]])], dim=1)
+    llm = LLM(path, dtype="float32", device="cpu", max_model_len=128, num_gpu_blocks_override=32, max_num_seqs=4,
+              max_num_batched_tokens=8, skip_tokenizer_init=True)          # 8-token budget: the image spans two chunks
+    sp = SamplingParams(temperature=0, max_tokens=N_NEW, logprobs=1, ignore_eos=True, detokenize=False)
+    out = llm.generate([{"prompt_token_ids": prompt, "multi_modal_data": {"image": pixels}}], sp)[0]
+    assert out.prompt_token_ids == expanded
+    c = out.outputs[0]
+    got_lp = [d[t] if isinstance(d[t], float) else d[t].logprob for t, d in zip(c.token_ids, c.logprobs)]
+    assert list(c.token_ids) == want_t
+    assert torch.allclose(torch.tensor(got_lp), torch.tensor(want_lp), atol=2e-3)
+    # a different image: different continuation or at least different log-probabilities, and no cache sharing
+    out2 = llm.generate([{"prompt_token_ids": prompt, "multi_modal_data": {"image": pixels.flip(2)}}], sp)[0]
+    assert out2.num_cached_tokens == 0
+    with pytest.raises(ValueError):
+        llm.generate([{"prompt_token_ids": [5, 6, 7], "multi_modal_data": {"image": pixels}}], sp)
+    llm.shutdown()

@@ -284,9 +284,22 @@ def build_app(state: ServingState) -> FastAPI:
             return _error("chat needs a tokenizer")
         try:
             msgs = [m.model_dump(exclude_none=True) for m in req.messages]
+            images = []
+            mcfg = getattr(getattr(state.engine, "cfg", None), "model", None)
+            if mcfg is not None and any(isinstance(m.get("content"), list) and any(
+                    isinstance(p, dict) and p.get("type") in ("image_url", "input_image") for p in m["content"])
+                    for m in msgs):
+                from sonar_b200.multimodal.image import extract_chat_images
+                if mcfg.get("image_token_index") is None:
+                    return _error("this model takes no image inputs")
+                msgs, images = extract_chat_images(msgs, mcfg)
             prompt = apply_chat_template(tok, msgs, req.add_generation_prompt, req.chat_template, req.tools)
             n_lp = (req.top_logprobs or 1) if req.logprobs else None
             default_max = req.max_completion_tokens or (state.max_model_len - len(tok.encode(prompt)) - 1)
+            if images:
+                from sonar_b200.multimodal.image import encode_with_placeholders
+                prompt = {"prompt_token_ids": encode_with_placeholders(tok, prompt, int(mcfg.get("image_token_index"))),
+                          "multi_modal_data": {"image": images}}
             sp = req.to_sampling_params(max(default_max, 1), n_lp, req.stream)
         except (ValueError, TypeError) as e:
             return _error(str(e))

@@ -275,3 +275,55 @@ def test_elastic_scaling_of_engine_replicas():
             assert c.post("/is_scaling_elastic_ep").json() == {"is_scaling_elastic_ep": False}
     finally:
         engine.shutdown()
+
+
+def test_chat_with_image_content_parts():
+    """OpenAI-style image parts: the data URL is decoded and preprocessed, the placeholder becomes one image token
+    that the engine expands; another image changes the answer's log-probabilities; a text-only model refuses."""
+    import base64
+    import io
+
+    import numpy as np
+    from fastapi.testclient import TestClient
+    from PIL import Image
+
+    from sonar_b200.engine.async_llm import AsyncLLM
+    from sonar_b200.entrypoints.openai.api_server import ServingState, build_app
+    from sonar_b200.multimodal.image import encode_with_placeholders, preprocess_clip
+    from sonar_b200.utils.tokenizer import get_tokenizer
+
+    def data_url(seed):
+        arr = np.random.default_rng(seed).integers(0, 255, (40, 70, 3), dtype=np.uint8)
+        buf = io.BytesIO()
+        Image.fromarray(arr).save(buf, format="PNG")
+        return "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+
+    x = preprocess_clip(Image.fromarray(np.zeros((40, 70, 3), dtype=np.uint8)), 56)
+    assert tuple(x.shape) == (3, 56, 56) and abs(float(x[0, 0, 0]) + 0.48145466 / 0.26862954) < 1e-5
+    tok = get_tokenizer(None, 2048)
+    ids = encode_with_placeholders(tok, "ab<image>c", 2000)
+    assert ids.count(2000) == 1 and len(ids) == 1 + 2 + 1 + 1
+
+    args = EngineArgs(model="tiny-llava", dtype="float32", max_model_len=512, num_gpu_blocks_override=64,
+                      max_num_seqs=4, max_num_batched_tokens=64, device="cpu")
+    engine = AsyncLLM.from_engine_args(args)
+    app = build_app(ServingState(engine, "tiny-llava", None))
+
+    def ask(c, seed):
+        body = {"messages": [{"role": "user", "content": [{"type": "text", "text": "what is this? "},
+                                                           {"type": "image_url", "image_url": {"url": data_url(seed)}}]}],
+                "max_tokens": 4, "temperature": 0, "logprobs": True, "top_logprobs": 1}
+        r = c.post("/v1/chat/completions", json=body)
+        assert r.status_code == 200, r.text
+        j = r.json()
+        return j["usage"]["prompt_tokens"], [e["logprob"] for e in j["choices"][0]["logprobs"]["content"]]
+    try:
+        with TestClient(app) as c:
+            n1, lp1 = ask(c, 1)
+            n2, lp2 = ask(c, 2)
+            assert n1 == n2 and n1 > 16 and lp1 != lp2              # 16 image positions are part of the prompt
+            bad = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": [
+                {"type": "image_url", "image_url": {"url": "http://example.com/x.png"}}]}], "max_tokens": 2})
+            assert bad.status_code == 400
+    finally:
+        engine.shutdown()

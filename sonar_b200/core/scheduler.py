@@ -19,7 +19,7 @@ import heapq
 import time
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Iterable
+from typing import Any, Iterable
 
 from sonar_b200.config import CacheConfig, SchedulerConfig, SpeculativeConfig
 from sonar_b200.core.block_pool import make_block_hasher
@@ -38,7 +38,7 @@ class NewRequestData:
     sampling_params: SamplingParams | None
     block_ids: list[int]
     num_computed_tokens: int
-    pooling: bool = False
+    pooling: Any = False               # the request's PoolingParams, or False for a generation request
     lora_name: str | None = None
     embeds: list | None = None
     mm_inputs: list | None = None
@@ -337,7 +337,7 @@ class Scheduler:
                     sampling_params=req.sampling_params,
                     block_ids=list(self.kv.get_block_ids(req.request_id)),
                     num_computed_tokens=req.num_computed_tokens,
-                    pooling=req.pooling_params is not None, lora_name=req.lora_name,
+                    pooling=req.pooling_params or False, lora_name=req.lora_name,
                     embeds=req.embeds, mm_inputs=req.mm_inputs))
                 self._known_to_runner.add(req.request_id)
 

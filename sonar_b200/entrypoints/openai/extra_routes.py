@@ -240,6 +240,22 @@ def register(app: FastAPI, state) -> None:
         a generative model used as a zero-shot classifier."""
         inputs, labels = body.get("input"), body.get("labels")
         tok = state.tokenizer
+        mcfg = state.engine.cfg.model
+        if inputs is not None and mcfg.architecture.endswith("ForSequenceClassification"):
+            # a checkpoint with a classification head: class probabilities from the head itself
+            if isinstance(inputs, str) or (inputs and isinstance(inputs[0], int)):
+                inputs = [inputs]
+            names = mcfg.get("id2label") or {}
+            data = []
+            for i, item in enumerate(inputs):
+                final = await state.engine.encode(item if isinstance(item, str) else {"prompt_token_ids": list(item)},
+                                                  PoolingParams(task="classify"), f"cls-{uuid.uuid4().hex}")
+                probs = [float(x) for x in final.outputs.data.tolist()]
+                best = max(range(len(probs)), key=lambda k: probs[k])
+                data.append({"index": i, "label": names.get(str(best), names.get(best, str(best))), "probs": probs,
+                             "num_classes": len(probs)})
+            return {"id": f"classify-{uuid.uuid4().hex}", "object": "list", "model": body.get("model", state.name),
+                    "data": data}
         if inputs is None or not labels or tok is None:
             return _error("input and labels are required (and a tokenizer)")
         if isinstance(inputs, str):

@@ -1,0 +1,38 @@
+"""Sequence-classification heads on the Llama-family decoders (``*ForSequenceClassification``): the hidden state
+of the last prompt token goes through a ``score`` projection to ``num_labels`` logits.  Pooling requests with
+``task="classify"`` get the softmax over labels (sigmoid for a single label), ``task="score"`` / ``"reward"``
+the raw logits, ``task="embed"`` the hidden state itself.
+
+Parity: ``aphrodite/model_executor/models/adapters.py`` (``as_seq_cls_model``: last-token pooling + ``score``
+head, softmax / sigmoid by label count).
+"""
+from __future__ import annotations
+
+import torch
+
+from sonar_b200.config import ModelConfig
+from sonar_b200.layers.linear import ReplicatedLinear
+from sonar_b200.models.llama import LlamaForCausalLM
+
+
+class LlamaForSequenceClassification(LlamaForCausalLM):
+    def __init__(self, cfg: ModelConfig, device=None) -> None:
+        super().__init__(cfg, device)
+        self.num_labels = int(cfg.get("num_labels", len(cfg.get("id2label") or {}) or 2))
+        self.score = ReplicatedLinear(cfg.hidden_size, self.num_labels, bias=bool(cfg.get("classifier_bias", False)),
+                                      dtype=cfg.dtype, device=device, prefix="score")
+
+    def pool(self, hidden: torch.Tensor, task: str) -> torch.Tensor:
+        """``hidden [H]`` of the last prompt token → what the task asks for (fp32, on the CPU side later)."""
+        if task == "embed":
+            return hidden.float()
+        logits = torch.nn.functional.linear(hidden.to(self.score.weight.dtype), self.score.weight,
+                                            getattr(self.score, "bias", None)).float()
+        if task == "classify":
+            return torch.sigmoid(logits) if self.num_labels == 1 else torch.softmax(logits, dim=-1)
+        return logits
+
+    def map_checkpoint_name(self, name: str):
+        if name.startswith("lm_head."):
+            return None                       # classification checkpoints carry no LM head
+        return super().map_checkpoint_name(name)

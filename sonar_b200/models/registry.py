@@ -13,6 +13,10 @@ _MODELS: dict[str, tuple[str, str]] = {
     "Qwen3MoeForCausalLM": ("sonar_b200.models.qwen3_moe", "Qwen3MoeForCausalLM"),
     "MixtralForCausalLM": ("sonar_b200.models.qwen3_moe", "MixtralForCausalLM"),
     "LlavaForConditionalGeneration": ("sonar_b200.models.llava", "LlavaForConditionalGeneration"),
+    "LlamaForSequenceClassification": ("sonar_b200.models.pooling", "LlamaForSequenceClassification"),
+    "MistralForSequenceClassification": ("sonar_b200.models.pooling", "LlamaForSequenceClassification"),
+    "Qwen2ForSequenceClassification": ("sonar_b200.models.pooling", "LlamaForSequenceClassification"),
+    "Qwen3ForSequenceClassification": ("sonar_b200.models.pooling", "LlamaForSequenceClassification"),
     "Phi3ForCausalLM": ("sonar_b200.models.llama_variants", "Phi3ForCausalLM"),
     "GraniteForCausalLM": ("sonar_b200.models.llama_variants", "GraniteForCausalLM"),
     "Qwen2MoeForCausalLM": ("sonar_b200.models.llama_variants", "Qwen2MoeForCausalLM"),

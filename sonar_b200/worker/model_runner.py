@@ -599,8 +599,21 @@ class ModelRunner:
         pool_rows = [i for i in range(ns) if b.pooling[rows[i]]]
         for i in pool_rows:
             if samples[i]:
-                vec = hidden[starts[i + 1] - 1].float()
-                out.pooled[req_ids[i]] = torch.nn.functional.normalize(vec, dim=0).cpu()
+                pp = b.pooling[rows[i]]
+                task = getattr(pp, "task", "embed")
+                vec = hidden[starts[i + 1] - 1]
+                pooler = getattr(self.model, "pool", None)
+                if pooler is not None:
+                    vec = pooler(vec, task)
+                elif task != "embed":
+                    raise ValueError(f"pooling task {task!r} needs a model with a classification head")
+                vec = vec.float()
+                if task == "embed":
+                    if getattr(pp, "dimensions", None):
+                        vec = vec[: pp.dimensions]                  # matryoshka truncation before normalising
+                    if getattr(pp, "normalize", True):
+                        vec = torch.nn.functional.normalize(vec, dim=0)
+                out.pooled[req_ids[i]] = vec.cpu()
             samples[i] = False
         self._prompt_logprobs(so, hidden, rows, q_lens, starts, req_ids, out)
         idx = np.nonzero(samples)[0]

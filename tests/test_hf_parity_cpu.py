@@ -230,3 +230,33 @@ def test_llava_clip_tower_projector_and_placeholders(tmp_path):
     with pytest.raises(ValueError):
         llm.generate([{"prompt_token_ids": [5, 6, 7], "multi_modal_data": {"image": pixels}}], sp)
     llm.shutdown()
+
+
+def test_sequence_classification_head(tmp_path):
+    """``LlamaForSequenceClassification``: class probabilities, raw scores and embeddings of the last prompt token
+    against Hugging Face (which pools at the last non-pad token)."""
+    from transformers import LlamaConfig, LlamaForSequenceClassification
+
+    from sonar_b200.sampling_params import PoolingParams
+    cfg = LlamaConfig(**COMMON, head_dim=16, num_labels=3, pad_token_id=0)
+    torch.manual_seed(0)
+    model = LlamaForSequenceClassification(cfg).float().eval()
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() >= 2:
+                p.normal_(0.0, 0.08)
+    path = str(tmp_path / "hf")
+    model.save_pretrained(path, safe_serialization=True)
+    llm = LLM(path, dtype="float32", device="cpu", max_model_len=128, num_gpu_blocks_override=32, max_num_seqs=4,
+              max_num_batched_tokens=8, skip_tokenizer_init=True)
+    prompts = [{"prompt_token_ids": p} for p in PROMPTS]
+    probs = llm.encode(prompts, PoolingParams(task="classify"))
+    raw = llm.encode(prompts, PoolingParams(task="score"))
+    emb = llm.encode(prompts, PoolingParams(task="embed", normalize=False))
+    for p, pr, rw, em in zip(PROMPTS, probs, raw, emb):
+        with torch.no_grad():
+            out = model(torch.tensor([p]), output_hidden_states=True)
+        assert torch.allclose(rw.outputs.data, out.logits[0], atol=2e-4)
+        assert torch.allclose(pr.outputs.data, torch.softmax(out.logits[0], -1), atol=2e-4)
+        assert torch.allclose(em.outputs.data, out.hidden_states[-1][0, -1], atol=2e-4)
+    llm.shutdown()

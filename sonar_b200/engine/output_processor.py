@@ -92,8 +92,16 @@ class OutputProcessor:
         out = []
         for rid in request_ids:
             if rid in self.states:
-                del self.states[rid]
+                st = self.states.pop(rid)
                 out.append(rid)
+                if st.queue is not None and rid not in self.parents:
+                    # whoever still reads this request's stream (an abort can come from elsewhere) gets an end
+                    try:
+                        final = self._make_output(st, FinishReason.ABORT, None)
+                    except Exception:  # noqa: BLE001 - a half-built state must not block the abort
+                        final = None
+                    if final is not None:
+                        st.queue.put_nowait(final)
             parent = self.parents.pop(rid, None)
             if parent is not None:
                 for i in range(parent.n):

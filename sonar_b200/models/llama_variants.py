@@ -214,3 +214,51 @@ class Glm4ForCausalLM(LlamaForCausalLM):
 
 #: architectures whose blocks need every token's full row between the two halves of a layer
 NEEDS_REPLICATED_ACTIVATIONS = {"Glm4ForCausalLM"}
+
+
+class GraniteMoeDecoderLayer(LlamaDecoderLayer):
+    def _make_mlp(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> nn.Module:
+        return SparseMoeBlock(cfg, device, prefix, bool(cfg.get("_expert_parallel", False)),
+                              cfg.get("_expert_placement", "linear"))
+
+
+class GraniteMoeModel(LlamaModel):
+    layer_cls = GraniteMoeDecoderLayer
+
+
+class GraniteMoeForCausalLM(GraniteForCausalLM):
+    """Granite 3.x MoE: Granite's multipliers around a top-k softmax mixture whose experts are stored fused per
+    layer (``block_sparse_moe.input_linear [E, 2I, H]``: gate rows then up rows; ``output_linear [E, H, I]``;
+    ``router.layer [E, H]``)."""
+    model_cls = GraniteMoeModel
+
+    def load_special_weight(self, name: str, tensor: torch.Tensor) -> bool:
+        if ".block_sparse_moe." not in name:
+            return False
+        prefix, _, leaf = name.partition(".block_sparse_moe.")
+        try:
+            block = self.get_submodule(prefix + ".mlp")
+        except AttributeError:
+            return True
+        if leaf == "router.layer.weight":
+            block.gate.weight.data.copy_(tensor)
+            return True
+        if leaf in ("input_linear.weight", "output_linear.weight"):
+            half = tensor.shape[1] // 2
+            for e in range(tensor.shape[0]):
+                if leaf == "input_linear.weight":
+                    block.experts.load_expert_weight(e, "gate", tensor[e, :half])
+                    block.experts.load_expert_weight(e, "up", tensor[e, half:])
+                else:
+                    block.experts.load_expert_weight(e, "down", tensor[e])
+            return True
+        return False
+
+    @torch.no_grad()
+    def process_after_load(self) -> None:
+        for layer in self.model.layers.values():
+            if self.resid_mult != 1.0:
+                layer.self_attn.o_proj.weight.data.mul_(self.resid_mult)
+                layer.mlp.experts.w2.data.mul_(self.resid_mult)
+        if hasattr(self.model, "embed_tokens") and self.embed_mult != 1.0:
+            self.model.embed_tokens.weight.data.mul_(self.embed_mult)

@@ -19,6 +19,7 @@ _MODELS: dict[str, tuple[str, str]] = {
     "Qwen3ForSequenceClassification": ("sonar_b200.models.pooling", "LlamaForSequenceClassification"),
     "Phi3ForCausalLM": ("sonar_b200.models.llama_variants", "Phi3ForCausalLM"),
     "GraniteForCausalLM": ("sonar_b200.models.llama_variants", "GraniteForCausalLM"),
+    "GraniteMoeForCausalLM": ("sonar_b200.models.llama_variants", "GraniteMoeForCausalLM"),
     "Qwen2MoeForCausalLM": ("sonar_b200.models.llama_variants", "Qwen2MoeForCausalLM"),
     "HeliumForCausalLM": ("sonar_b200.models.llama_variants", "InterleavedRopeLlama"),
     "Ernie4_5ForCausalLM": ("sonar_b200.models.llama_variants", "InterleavedRopeLlama"),

@@ -260,3 +260,11 @@ def test_sequence_classification_head(tmp_path):
         assert torch.allclose(pr.outputs.data, torch.softmax(out.logits[0], -1), atol=2e-4)
         assert torch.allclose(em.outputs.data, out.hidden_states[-1][0, -1], atol=2e-4)
     llm.shutdown()
+
+
+def test_granite_moe_fused_expert_tensors(tmp_path):
+    from transformers import GraniteMoeConfig, GraniteMoeForCausalLM
+    cfg = GraniteMoeConfig(**{**COMMON, "tie_word_embeddings": True}, num_local_experts=4, num_experts_per_tok=2,
+                           embedding_multiplier=4.0, attention_multiplier=0.25, residual_multiplier=0.4,
+                           logits_scaling=2.0)
+    _check(tmp_path, cfg, GraniteMoeForCausalLM, init_std=0.08)

@@ -103,10 +103,9 @@ def reference_arm(args) -> None:
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
     why = None
     if not os.path.isdir(os.path.join(ref_dir, "aphrodite")):
-        why = ("reference not installed: `pip install --no-index --no-build-isolation --find-links /opt/wheelhouse "
-               "--target baseline/_ref /root/reference` fails in metadata generation (setup.py imports "
-               "setuptools_scm, absent from the image and the wheelhouse); its CUDA build also fetches CUTLASS "
-               "and FlashAttention sources from the network")
+        why = ("reference not installed: the offline pip install of the reference into baseline/_ref fails in "
+               "metadata generation (its setup.py imports setuptools_scm, absent from the image and from the offline "
+               "wheelhouse); its CUDA build also fetches CUTLASS and FlashAttention sources from the network")
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps({"impl": "reference", "unavailable": why or "reference import failed"}))
 

@@ -61,7 +61,7 @@ def read_safetensors(path: str) -> Iterator[tuple[str, torch.Tensor]]:
 def write_safetensors(path: str, tensors: dict[str, torch.Tensor]) -> None:
     header, off, blobs = {}, 0, []
     for name, t in tensors.items():
-        raw = t.detach().cpu().contiguous().view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.detach().cpu().contiguous().reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
         header[name] = {"dtype": _ST_NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
         off += len(raw)
         blobs.append(raw)
@@ -105,10 +105,45 @@ def _assign(model: nn.Module, name: str, tensor: torch.Tensor, shard) -> bool:
     return True
 
 
+_KV_SCALE_LEAVES = (".self_attn.k_scale", ".self_attn.v_scale", ".self_attn.kv_scale", ".self_attn.k_proj.k_scale",
+                    ".self_attn.v_proj.v_scale", ".self_attn.attn.k_scale", ".self_attn.attn.v_scale")
+
+
+def _load_kv_scale(model: nn.Module, name: str, tensor: torch.Tensor) -> bool:
+    """Per-layer scales of an fp8 KV cache (``k_scale`` / ``v_scale``, or one legacy ``kv_scale`` for both), under
+    the names the common exporters use.  They are plain floats on the attention layer: the cache-write kernel
+    divides by them, the attention kernels multiply."""
+    leaf = next((lf for lf in _KV_SCALE_LEAVES if name.endswith(lf)), None)
+    if leaf is None:
+        return False
+    mapped = model.map_checkpoint_name(name[: -len(leaf)] + ".self_attn.o_proj.weight")
+    if mapped is None:
+        return True                                    # a layer this rank / stage does not hold
+    try:
+        attn = model.get_submodule(mapped[0][: -len(".o_proj.weight")])
+    except AttributeError:
+        return True
+    target = getattr(attn, "attn", attn)
+    if not hasattr(target, "k_scale"):
+        return False
+    val = float(tensor.float().reshape(-1)[0])
+    if val <= 0:
+        raise ValueError(f"{name}: KV-cache scales must be positive, got {val}")
+    which = leaf.rsplit(".", 1)[1]
+    if which in ("k_scale", "kv_scale"):
+        target.k_scale = val
+    if which in ("v_scale", "kv_scale"):
+        target.v_scale = val
+    return True
+
+
 def load_weights_from(model: nn.Module, weights: Iterator[tuple[str, torch.Tensor]]) -> set[str]:
     loaded: set[str] = set()
     custom = getattr(model, "load_special_weight", None)
     for name, tensor in weights:
+        if name.endswith("_scale") and _load_kv_scale(model, name, tensor):
+            loaded.add(name)
+            continue
         if custom is not None and custom(name, tensor):
             loaded.add(name)
             continue

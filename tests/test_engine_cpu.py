@@ -282,3 +282,33 @@ def test_fp8_per_tensor_checkpoint_loads_and_matches_dequantised(tmp_path):
     la = [a.prompt_logprobs[i][prompt["prompt_token_ids"][i]].logprob for i in range(1, 8)]
     lb = [b.prompt_logprobs[i][prompt["prompt_token_ids"][i]].logprob for i in range(1, 8)]
     assert max(abs(x - y) for x, y in zip(la, lb)) < 0.25, (la, lb)
+
+
+def test_kv_cache_scales_load_from_checkpoint(tmp_path):
+    """fp8-KV checkpoints carry per-layer ``k_scale`` / ``v_scale``; they end up on the attention layers and the
+    fp8 cache then reproduces the unquantised model's greedy tokens on a short run."""
+    import json
+    import os
+    import sys
+
+    import torch
+    from sonar_b200.loader.weights import read_safetensors, save_checkpoint
+    sys.path.insert(0, os.path.dirname(__file__))
+    from tp_common import make_checkpoint
+    base = make_checkpoint(str(tmp_path / "base"), "tiny-llama-128", dtype=torch.float32)
+    cfg = json.load(open(os.path.join(base, "config.json")))
+    tensors = {k: v.clone() for k, v in read_safetensors(os.path.join(base, "model.safetensors"))}
+    for i in range(cfg["num_hidden_layers"]):
+        tensors[f"model.layers.{i}.self_attn.k_scale"] = torch.tensor(0.02 + 0.01 * i)
+        tensors[f"model.layers.{i}.self_attn.v_scale"] = torch.tensor([0.03])
+    save_checkpoint(str(tmp_path / "kv"), cfg, tensors)
+    kw = dict(dtype="float32", device="cpu", max_model_len=128, num_gpu_blocks_override=32, max_num_seqs=2,
+              max_num_batched_tokens=64, skip_tokenizer_init=True)
+    sp = SamplingParams(temperature=0, max_tokens=6, ignore_eos=True, detokenize=False)
+    prompt = [{"prompt_token_ids": list(range(40, 60))}]
+    want = LLM(base, **kw).generate(prompt, sp)[0].outputs[0].token_ids
+    llm = LLM(str(tmp_path / "kv"), kv_cache_dtype="fp8", **kw)
+    layers = llm.llm_engine.core.engine_core.executor.worker.runner.model.attention_layers()
+    assert [round(a.k_scale, 4) for a in layers] == [0.02, 0.03] and all(abs(a.v_scale - 0.03) < 1e-6 for a in layers)
+    got = llm.generate(prompt, sp)[0].outputs[0].token_ids
+    assert len(got) == 6 and sum(a == b for a, b in zip(got, want)) >= 4

@@ -262,3 +262,50 @@ class GraniteMoeForCausalLM(GraniteForCausalLM):
                 layer.mlp.experts.w2.data.mul_(self.resid_mult)
         if hasattr(self.model, "embed_tokens") and self.embed_mult != 1.0:
             self.model.embed_tokens.weight.data.mul_(self.embed_mult)
+
+
+class Ernie45MoeDecoderLayer(LlamaDecoderLayer):
+    def _make_mlp(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> nn.Module:
+        from sonar_b200.models.deepseek import DeepseekMoE
+        n_layers = int(cfg.get("num_hidden_layers"))
+        start = int(cfg.get("moe_layer_start_index", 0) or 0)
+        end = cfg.get("moe_layer_end_index", -1)
+        end = n_layers - 1 if end in (None, -1) else int(end)
+        sparse = ((layer_idx + 1) % int(cfg.get("moe_layer_interval", 1) or 1) == 0) and start <= layer_idx <= end
+        if not sparse:
+            return LlamaMLP(cfg.hidden_size, int(cfg.get("intermediate_size")), cfg.dtype, device, cfg.quantization, prefix)
+        return DeepseekMoE(cfg, device, prefix)
+
+
+class Ernie45MoeModel(LlamaModel):
+    layer_cls = Ernie45MoeDecoderLayer
+
+
+class Ernie45MoeForCausalLM(InterleavedRopeLlama):
+    """ERNIE-4.5 MoE (21B-A3B, 300B-A47B): pair-interleaved rotary, and a mixture with softmax scores, a
+    bias-corrected top-k choice (``moe_statics.e_score_correction_bias``), weights renormalised over the chosen
+    experts, plus always-on shared experts.  The mixture block is the DeepSeek one under translated config keys."""
+    model_cls = Ernie45MoeModel
+
+    def __init__(self, cfg: ModelConfig, device=None) -> None:
+        hf = cfg.hf_config
+        hf.setdefault("n_routed_experts", hf.get("moe_num_experts"))
+        hf.setdefault("num_experts_per_tok", hf.get("moe_k"))
+        hf.setdefault("n_shared_experts", hf.get("moe_num_shared_experts", 0))
+        for k, v in (("scoring_func", "softmax"), ("topk_method", "noaux_tc"), ("norm_topk_prob", True),
+                     ("n_group", 1), ("topk_group", 1), ("routed_scaling_factor", 1.0)):
+            hf.setdefault(k, v)
+        super().__init__(cfg, device)
+
+    def load_special_weight(self, name: str, tensor: torch.Tensor) -> bool:
+        from sonar_b200.models.deepseek import DeepseekForCausalLM
+        if name.endswith(".mlp.moe_statics.e_score_correction_bias"):
+            try:
+                block = self.get_submodule(name[: -len(".moe_statics.e_score_correction_bias")])
+            except AttributeError:
+                return True
+            block.experts.e_bias.data.copy_(tensor.float().reshape(-1))
+            return True
+        if super().load_special_weight(name, tensor):          # q/k row reordering
+            return True
+        return DeepseekForCausalLM.load_special_weight(self, name, tensor)

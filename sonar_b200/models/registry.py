@@ -25,6 +25,7 @@ _MODELS: dict[str, tuple[str, str]] = {
     "Ernie4_5ForCausalLM": ("sonar_b200.models.llama_variants", "InterleavedRopeLlama"),
     "Glm4ForCausalLM": ("sonar_b200.models.llama_variants", "Glm4ForCausalLM"),
     "Glm4MoeForCausalLM": ("sonar_b200.models.llama_variants", "Glm4MoeForCausalLM"),
+    "Ernie4_5_MoeForCausalLM": ("sonar_b200.models.llama_variants", "Ernie45MoeForCausalLM"),
     "Dots1ForCausalLM": ("sonar_b200.models.llama_variants", "Dots1ForCausalLM"),
     "DeepseekV2ForCausalLM": ("sonar_b200.models.deepseek", "DeepseekForCausalLM"),
     "DeepseekV3ForCausalLM": ("sonar_b200.models.deepseek", "DeepseekForCausalLM"),

@@ -268,3 +268,17 @@ def test_granite_moe_fused_expert_tensors(tmp_path):
                            embedding_multiplier=4.0, attention_multiplier=0.25, residual_multiplier=0.4,
                            logits_scaling=2.0)
     _check(tmp_path, cfg, GraniteMoeForCausalLM, init_std=0.08)
+
+
+def test_ernie45_moe(tmp_path):
+    from transformers import Ernie4_5_MoeConfig, Ernie4_5_MoeForCausalLM
+    cfg = Ernie4_5_MoeConfig(**{**COMMON, "num_hidden_layers": 3}, head_dim=16, use_bias=False, moe_num_experts=8, moe_k=2,
+                             moe_intermediate_size=32, moe_num_shared_experts=1, moe_layer_start_index=1,
+                             moe_layer_end_index=-1, moe_layer_interval=1, moe_norm_min=1e-12)
+    torch.manual_seed(0)
+    model = Ernie4_5_MoeForCausalLM(cfg).float().eval()
+    with torch.no_grad():
+        for n, b in model.named_buffers():
+            if "e_score_correction_bias" in n:
+                b.copy_(torch.randn_like(b) * 0.05)        # a correction that changes which experts win
+    _check(tmp_path, cfg, lambda c: model, init_std=0.08)

@@ -57,12 +57,20 @@ class Attention(nn.Module):
     def __init__(self, num_heads: int, num_kv_heads: int, head_dim: int, scale: float, layer_idx: int,
                  rope_theta: float, max_position: int, rope_scaling: dict | None = None,
                  sliding_window: int | None = None, device=None, qk_norm_eps: float | None = None,
-                 dtype=torch.bfloat16, rot_dim: int | None = None) -> None:
+                 dtype=torch.bfloat16, rot_dim: int | None = None, use_rope: bool = True) -> None:
         super().__init__()
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
         self.scale, self.layer_idx, self.sliding_window = scale, layer_idx, sliding_window
         self.rot_dim = rot_dim or head_dim         # partial rotary: only rot_dim channels of a head turn
         self.cos_sin = get_cos_sin_cache(self.rot_dim, max_position, rope_theta, rope_scaling, device)
+        if not use_rope:
+            # a layer without positional rotation (NoPE): the same kernel with the identity rotation
+            key = ("nope", self.rot_dim, max_position, str(device))
+            if key not in _ROPE_CACHE:
+                ident = torch.zeros_like(self.cos_sin)
+                ident[:, : self.rot_dim // 2] = 1.0
+                _ROPE_CACHE[key] = ident
+            self.cos_sin = _ROPE_CACHE[key]
         self.kv_cache: torch.Tensor | None = None
         self.k_scale = self.v_scale = 1.0
         self.qk_norm_eps = qk_norm_eps

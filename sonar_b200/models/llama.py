@@ -62,6 +62,12 @@ class LlamaMLP(nn.Module):
         return tp.row_linear(act, self.down_proj)
 
 
+def _layer_uses_rope(cfg: ModelConfig, layer_idx: int) -> bool:
+    """SmolLM3-style ``no_rope_layers``: a 0 entry switches the rotation off for that layer."""
+    flags = cfg.get("no_rope_layers")
+    return True if not flags or layer_idx >= len(flags) else bool(flags[layer_idx])
+
+
 class LlamaAttention(nn.Module):
     def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> None:
         super().__init__()
@@ -79,7 +85,8 @@ class LlamaAttention(nn.Module):
         self.attn = Attention(self.qkv_proj.num_heads, self.qkv_proj.num_kv_heads, hd, scale, layer_idx,
                               float(cfg.get("rope_theta", 1e4)), cfg.max_model_len, cfg.get("rope_scaling"),
                               sw, device, qk_eps, cfg.dtype,
-                              rot_dim=int(hd * float(cfg.get("partial_rotary_factor", 1.0) or 1.0)))
+                              rot_dim=int(hd * float(cfg.get("partial_rotary_factor", 1.0) or 1.0)),
+                              use_rope=_layer_uses_rope(cfg, layer_idx))
 
     def forward(self, x: torch.Tensor, meta: AttentionMetadata) -> torch.Tensor:
         tp = get_tp_context()

@@ -309,3 +309,9 @@ class Ernie45MoeForCausalLM(InterleavedRopeLlama):
         if super().load_special_weight(name, tensor):          # q/k row reordering
             return True
         return DeepseekForCausalLM.load_special_weight(self, name, tensor)
+
+
+class GlmForCausalLM(Glm4ForCausalLM):
+    """GLM-4-9B (HF layout): the GLM-4 checkpoint conventions (fused ``gate_up_proj``, interleaved rotary on half of
+    each head, q/k/v bias) on plain pre-norm blocks."""
+    model_cls = LlamaModel

@@ -23,6 +23,8 @@ _MODELS: dict[str, tuple[str, str]] = {
     "Qwen2MoeForCausalLM": ("sonar_b200.models.llama_variants", "Qwen2MoeForCausalLM"),
     "HeliumForCausalLM": ("sonar_b200.models.llama_variants", "InterleavedRopeLlama"),
     "Ernie4_5ForCausalLM": ("sonar_b200.models.llama_variants", "InterleavedRopeLlama"),
+    "GlmForCausalLM": ("sonar_b200.models.llama_variants", "GlmForCausalLM"),
+    "SmolLM3ForCausalLM": ("sonar_b200.models.llama", "LlamaForCausalLM"),
     "Glm4ForCausalLM": ("sonar_b200.models.llama_variants", "Glm4ForCausalLM"),
     "Glm4MoeForCausalLM": ("sonar_b200.models.llama_variants", "Glm4MoeForCausalLM"),
     "Ernie4_5_MoeForCausalLM": ("sonar_b200.models.llama_variants", "Ernie45MoeForCausalLM"),

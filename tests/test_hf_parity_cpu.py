@@ -282,3 +282,12 @@ def test_ernie45_moe(tmp_path):
             if "e_score_correction_bias" in n:
                 b.copy_(torch.randn_like(b) * 0.05)        # a correction that changes which experts win
     _check(tmp_path, cfg, lambda c: model, init_std=0.08)
+
+
+def test_glm_and_smollm3(tmp_path):
+    from transformers import GlmConfig, GlmForCausalLM, SmolLM3Config, SmolLM3ForCausalLM
+    _check(tmp_path / "glm", GlmConfig(**COMMON, head_dim=16, partial_rotary_factor=0.5, attention_bias=True, pad_token_id=0),
+           GlmForCausalLM, init_std=0.08)
+    cfg = SmolLM3Config(**{**COMMON, "num_hidden_layers": 4}, no_rope_layers=[1, 1, 1, 0], no_rope_layer_interval=4,
+                        use_sliding_window=False, pad_token_id=0)
+    _check(tmp_path / "smol", cfg, SmolLM3ForCausalLM, init_std=0.08)

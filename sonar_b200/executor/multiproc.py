@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import multiprocessing as mp
 import os
+from collections import deque
 import signal
 import socket
 import threading
@@ -57,6 +58,20 @@ def _worker_main(cfg: EngineConfig, rank: int, world: int, init_method: str, rpc
     except Exception:
         resp_q.put(("error", traceback.format_exc()))
         raise
+    # Steps launched with defer=True whose sampled tokens have not been read back yet, oldest first.  The
+    # engine runs at most one step ahead: the reply to step N goes out once step N+1 has been launched (or
+    # when the engine asks with "__resolve__", or before any other call is served, so replies keep call order).
+    pending: deque = deque()
+
+    def finish(item) -> None:
+        deferred, reply_ranks = item
+        try:
+            out, status = deferred.result(), "ok"
+        except Exception:
+            out, status = traceback.format_exc(), "error"
+        if reply_ranks is None or rank in reply_ranks or status == "error":
+            resp_q.put((status, out))
+
     while True:
         try:
             msg = rpc_q.get(timeout_s=2.0)
@@ -68,6 +83,21 @@ def _worker_main(cfg: EngineConfig, rank: int, world: int, init_method: str, rpc
         if method == "__shutdown__":
             worker.shutdown()
             return
+        if method == "execute_model" and kwargs.get("defer"):
+            try:
+                pending.append((worker.execute_model(*args, defer=True), reply_ranks))
+            except Exception:
+                while pending:
+                    finish(pending.popleft())
+                resp_q.put(("error", traceback.format_exc()))
+                continue
+            while len(pending) > 1:
+                finish(pending.popleft())
+            continue
+        while pending:
+            finish(pending.popleft())
+        if method == "__resolve__":
+            continue
         try:
             out = getattr(worker, method)(*args, **kwargs)
             status = "ok"
@@ -77,9 +107,69 @@ def _worker_main(cfg: EngineConfig, rank: int, world: int, init_method: str, rpc
             resp_q.put((status, out))
 
 
+class _MPDeferred:
+    """The reply to a step launched ahead; ``result()`` reads it (and the ones before it) off the reply queue."""
+
+    def __init__(self, executor: "MultiprocExecutor") -> None:
+        self.executor, self.done, self.value = executor, False, None
+
+    def result(self):
+        return self.executor._resolve(self)
+
+
 class MultiprocExecutor(Executor):
+    @property
+    def supports_defer(self) -> bool:          # run-ahead needs the sampled tokens on the rank that launches
+        return self.cfg.parallel.pipeline_parallel_size == 1
+
+    def execute_model(self, so, defer: bool = False):
+        if not defer or not self.supports_defer:
+            return self.collective_rpc("execute_model", so, output_rank_only=True)[0]
+        if self.is_failed:
+            raise WorkerDeadError("a worker process has died")
+        with self._lock:
+            self.rpc_q.put(("execute_model", (so,), {"defer": True}, [self.output_rank]),
+                           timeout_s=envs.SONAR_RPC_TIMEOUT_S)
+            d = _MPDeferred(self)
+            self._deferred.append(d)
+        return d
+
+    def _read_reply(self, rank: int, what: str, timeout_s: float):
+        deadline = time.time() + timeout_s
+        while True:
+            if self.is_failed:
+                raise WorkerDeadError("a worker process has died")
+            try:
+                status, val = self.resp_qs[rank].get(timeout_s=0.5)
+                break
+            except QueueTimeout:
+                if time.time() > deadline:
+                    raise TimeoutError(f"worker {rank} did not answer {what} within {timeout_s}s") from None
+        if status != "ok":
+            raise RuntimeError(f"worker {rank} failed in {what}:\n{val}")
+        return val
+
+    def _resolve(self, d: _MPDeferred):
+        with self._lock:
+            return self._resolve_locked(d)
+
+    def _resolve_locked(self, d: _MPDeferred | None):
+        """Read deferred replies in launch order up to ``d`` (all of them for ``None``).  The workers answer
+        step N by themselves once step N+1 is launched; the newest step needs the explicit flush."""
+        while self._deferred and (d is None or not d.done):
+            if len(self._deferred) == 1:
+                self.rpc_q.put(("__resolve__", (), {}, None), timeout_s=envs.SONAR_RPC_TIMEOUT_S)
+            oldest = self._deferred[0]
+            try:
+                oldest.value = self._read_reply(self.output_rank, "execute_model", envs.SONAR_RPC_TIMEOUT_S)
+            finally:
+                oldest.done = True
+                self._deferred.pop(0)
+        return d.value if d is not None else None
+
     def _init_executor(self) -> None:
         cfg = self.cfg
+        self._deferred: list[_MPDeferred] = []
         self.world = cfg.parallel.world_size
         ctx = mp.get_context("spawn")
         self.rpc_q = MessageQueue.create(self.world, slot_bytes=1 << 20, n_slots=8)
@@ -132,6 +222,7 @@ class MultiprocExecutor(Executor):
         timeout_s = timeout_s or envs.SONAR_RPC_TIMEOUT_S
         ranks = [self.output_rank] if output_rank_only else list(range(self.world))
         with self._lock:
+            self._resolve_locked(None)          # replies of steps still in flight come first
             self.rpc_q.put((method, args, kwargs, ranks if output_rank_only else None), timeout_s=timeout_s)
             out = []
             deadline = time.time() + timeout_s

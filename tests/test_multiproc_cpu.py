@@ -94,3 +94,33 @@ def test_worker_death_is_detected(tmp_path):
     with pytest.raises(WorkerDeadError):
         ex.collective_rpc("check_health")
     ex.shutdown()
+
+
+def test_multiproc_executor_runs_one_step_ahead(tmp_path):
+    """Run-ahead scheduling through the worker processes: step N+1 is launched before step N's tokens are read
+    back, replies keep their order, other calls wait for the step in flight, and the tokens equal lock-step's."""
+    from sonar_b200 import LLM, SamplingParams
+    ckpt = make_checkpoint(str(tmp_path / "ckpt"), "tiny-llama", dtype=torch.float32)
+    prompts = [{"prompt_token_ids": [(5 * i + j) % 900 + 4 for j in range(12 + 9 * i)]} for i in range(5)]
+    sps = [SamplingParams(temperature=0, max_tokens=6 + 3 * i, ignore_eos=True, detokenize=False) for i in range(5)]
+    common = dict(dtype="float32", max_model_len=256, num_gpu_blocks_override=128, max_num_seqs=4,
+                  max_num_batched_tokens=32, device="cpu", skip_tokenizer_init=True)
+    one = LLM(ckpt, **common)
+    want = [o.outputs[0].token_ids for o in one.generate(prompts, sps)]
+    one.shutdown()
+    llm = LLM(ckpt, tensor_parallel_size=2, distributed_executor_backend="mp", async_scheduling=True, **common)
+    core = llm.llm_engine.core.engine_core
+    assert core.run_ahead_ok
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, sps)]
+    assert got == want
+    assert core.run_ahead_steps > 5 and not core.executor._deferred
+    stats = llm.collective_rpc("get_stats")                       # an ordinary call after deferred ones
+    assert len(stats) == 2 and stats[0]["steps"] == stats[1]["steps"] > 0
+    # a second batch mixing a lock-step request (penalties) with run-ahead ones
+    sps2 = [SamplingParams(temperature=0, max_tokens=5, ignore_eos=True, detokenize=False,
+                           repetition_penalty=1.2 if i == 1 else 1.0) for i in range(5)]
+    ref = LLM(ckpt, **common)
+    want2 = [o.outputs[0].token_ids for o in ref.generate(prompts, sps2)]
+    ref.shutdown()
+    assert [o.outputs[0].token_ids for o in llm.generate(prompts, sps2)] == want2
+    llm.shutdown()

@@ -209,3 +209,22 @@ def test_llava_image_request_on_gpu():
         return [d[t] if isinstance(d[t], float) else d[t].logprob for t, d in zip(c.token_ids, c.logprobs)]
     assert lps(outs[0]) != lps(outs[2])
     llm.shutdown()
+
+
+def test_multiproc_executor_run_ahead_on_gpu():
+    """The worker process launches step N+1 (a CUDA-graph replay) before step N's sampled ids are read back; the
+    deferred replies cross the shared-memory ring in order."""
+    from sonar_b200 import LLM, SamplingParams
+    kw = dict(model="tiny-llama-128", max_model_len=512, num_gpu_blocks_override=256, max_num_seqs=16,
+              max_num_batched_tokens=128, seed=0, skip_tokenizer_init=True)
+    prompts = [{"prompt_token_ids": [(13 * i + j) % 2000 + 3 for j in range(20 + 7 * i)]} for i in range(8)]
+    sps = [SamplingParams(max_tokens=6 + 2 * i, temperature=0, ignore_eos=True, detokenize=False) for i in range(8)]
+    sync = LLM(**kw)
+    want = [o.outputs[0].token_ids for o in sync.generate(prompts, sps)]
+    sync.shutdown()
+    llm = LLM(**kw, distributed_executor_backend="mp", async_scheduling=True)
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, sps)]
+    core = llm.llm_engine.core.engine_core
+    assert core.run_ahead_steps > 5
+    assert got == want
+    llm.shutdown()

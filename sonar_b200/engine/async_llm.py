@@ -39,7 +39,12 @@ class AsyncLLM:
         self.output_processor = OutputProcessor(self.tokenizer, cfg.observability.log_stats)
         self.core = EngineCoreClient.make_client(cfg, multiprocess=True, asyncio_mode=True,
                                                  executor_class=executor_class)
-        self.metrics = EngineMetrics(cfg.model.served_model_name or cfg.model.model)
+        from sonar_b200.utils.perf_model import ModelCost
+        try:
+            cost = ModelCost.from_config(cfg.model)
+        except Exception:  # noqa: BLE001 - an architecture the cost model does not describe: no MFU gauge
+            cost = None
+        self.metrics = EngineMetrics(cfg.model.served_model_name or cfg.model.model, cost)
         self._handler: asyncio.Task | None = None
         self._dead: Exception | None = None
         self._paused = False

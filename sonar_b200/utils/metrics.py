@@ -56,14 +56,19 @@ class Histogram:
 
 
 class EngineMetrics:
-    def __init__(self, model_name: str) -> None:
+    def __init__(self, model_name: str, cost=None) -> None:
+        """``cost``: a ``perf_model.ModelCost`` — with it the linear-layer FLOPs of every step are accumulated
+        and a model-FLOPs-utilisation gauge is kept over a sliding window."""
         self.labels = f'model_name="{model_name}"'
         self.lock = threading.Lock()
-        self.gauges = {"num_requests_running": 0.0, "num_requests_waiting": 0.0, "kv_cache_usage_perc": 0.0}
+        self.cost = cost
+        self._window: list[tuple[float, float]] = []          # (time, flops) of recent steps
+        self.gauges = {"num_requests_running": 0.0, "num_requests_waiting": 0.0, "kv_cache_usage_perc": 0.0,
+                       "model_flops_utilization": 0.0}
         self.counters = {"prompt_tokens_total": 0.0, "generation_tokens_total": 0.0, "num_preemptions_total": 0.0,
                          "prefix_cache_queries_total": 0.0, "prefix_cache_hits_total": 0.0,
                          "spec_decode_num_draft_tokens_total": 0.0, "spec_decode_num_accepted_tokens_total": 0.0,
-                         "request_arrivals_total": 0.0}
+                         "request_arrivals_total": 0.0, "model_flops_total": 0.0}
         self.finished: dict[str, int] = {}
         self.ttft = Histogram(_TTFT_BUCKETS)
         self.e2e = Histogram(_E2E_BUCKETS)
@@ -82,6 +87,19 @@ class EngineMetrics:
             c["prefix_cache_hits_total"] = s.prefix_cache_hits
             c["spec_decode_num_draft_tokens_total"] = s.spec_num_drafts
             c["spec_decode_num_accepted_tokens_total"] = s.spec_num_accepted
+            if self.cost is not None:
+                new = s.step_prompt_tokens + s.step_generation_tokens
+                if new:
+                    from sonar_b200.utils.perf_model import peaks
+                    flops, _ = self.cost.step(new, s.num_running or 1)
+                    c["model_flops_total"] += flops
+                    now = time.time()
+                    self._window.append((now, flops))
+                    while self._window and now - self._window[0][0] > 10.0:
+                        self._window.pop(0)
+                    span = max(now - self._window[0][0], 1e-3) if len(self._window) > 1 else None
+                    if span:
+                        g["model_flops_utilization"] = sum(f for _, f in self._window[1:]) / span / peaks()[0]
 
     def request_arrived(self, n_prompt: int) -> None:
         with self.lock:

@@ -108,8 +108,16 @@ def silu_and_mul(x, out=None):
 
 # ---- GEMM ----------------------------------------------------------------------
 def gemm(x, w, bias=None, out=None):
-    """y[T, N] = x[T, K] @ w[N, K]^T."""
+    """y[T, N] = x[T, K] @ w[N, K]^T.  The tcgen05 kernels need 16-byte row pitches (N and K multiples of 8 for
+    16-bit types); the few layers that are not (a router over 60 experts, a 3-label classification head) are
+    far too small to matter and go to the library GEMM."""
     if _use_cuda(x):
+        if w.shape[0] % 8 or w.shape[1] % 8:
+            y = torch.nn.functional.linear(x, w, bias)
+            if out is not None:
+                out.copy_(y)
+                return out
+            return y
         return cuda_ops().gemm(x, w, bias, out)
     y = ref.gemm(x, w, bias)
     if out is not None:

@@ -222,9 +222,14 @@ TOOL_PARSERS: dict[str, type[ToolParser]] = {
 }
 
 
+def _more() -> None:
+    from sonar_b200.entrypoints import parsers_more  # noqa: F401 - registers further formats
+
+
 def get_reasoning_parser(name: str | None) -> ReasoningParser | None:
     if not name:
         return None
+    _more()
     if name not in REASONING_PARSERS:
         raise ValueError(f"unknown reasoning parser {name!r}; known: {sorted(REASONING_PARSERS)}")
     return REASONING_PARSERS[name]()
@@ -233,6 +238,7 @@ def get_reasoning_parser(name: str | None) -> ReasoningParser | None:
 def get_tool_parser(name: str | None) -> ToolParser | None:
     if not name:
         return None
+    _more()
     if name not in TOOL_PARSERS:
         raise ValueError(f"unknown tool-call parser {name!r}; known: {sorted(TOOL_PARSERS)}")
     return TOOL_PARSERS[name]()

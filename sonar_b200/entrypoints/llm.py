@@ -75,7 +75,20 @@ class LLM:
              add_generation_prompt: bool = True, tools: list[dict] | None = None) -> list[RequestOutput]:
         convs = messages if messages and isinstance(messages[0], list) else [messages]
         tok = self.get_tokenizer()
-        prompts = [apply_chat_template(tok, c, add_generation_prompt, chat_template, tools) for c in convs]
+        mcfg = self.llm_engine.cfg.model
+        prompts = []
+        for c in convs:
+            images = []
+            if mcfg.get("image_token_index") is not None:
+                # image_url parts (data URLs) become image placeholders and preprocessed pixel values
+                from sonar_b200.multimodal.image import encode_with_placeholders, extract_chat_images
+                c, images = extract_chat_images(c, mcfg)
+            text = apply_chat_template(tok, c, add_generation_prompt, chat_template, tools)
+            if images:
+                prompts.append({"prompt_token_ids": encode_with_placeholders(tok, text, int(mcfg.get("image_token_index"))),
+                                "multi_modal_data": {"image": images}})
+            else:
+                prompts.append(text)
         return self.generate(prompts, sampling_params)
 
     def embed(self, prompts, pooling_params: PoolingParams | None = None) -> list[PoolingRequestOutput]:

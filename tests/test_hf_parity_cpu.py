@@ -232,19 +232,27 @@ def test_llava_clip_tower_projector_and_placeholders(tmp_path):
     llm.shutdown()
 
 
-def test_sequence_classification_head(tmp_path):
-    """``LlamaForSequenceClassification``: class probabilities, raw scores and embeddings of the last prompt token
+@pytest.mark.parametrize("family", ["llama", "qwen2"])
+def test_sequence_classification_head(tmp_path, family):
+    """``*ForSequenceClassification``: class probabilities, raw scores and embeddings of the last prompt token
     against Hugging Face (which pools at the last non-pad token)."""
-    from transformers import LlamaConfig, LlamaForSequenceClassification
+    import transformers
 
     from sonar_b200.sampling_params import PoolingParams
-    cfg = LlamaConfig(**COMMON, head_dim=16, num_labels=3, pad_token_id=0)
+    if family == "llama":
+        cfg = transformers.LlamaConfig(**COMMON, head_dim=16, num_labels=3, pad_token_id=0)
+        hf_cls = transformers.LlamaForSequenceClassification
+    else:
+        cfg = transformers.Qwen2Config(**COMMON, num_labels=2, pad_token_id=0)
+        hf_cls = transformers.Qwen2ForSequenceClassification
     torch.manual_seed(0)
-    model = LlamaForSequenceClassification(cfg).float().eval()
+    model = hf_cls(cfg).float().eval()
     with torch.no_grad():
         for p in model.parameters():
             if p.dim() >= 2:
                 p.normal_(0.0, 0.08)
+            else:
+                p.add_(torch.randn_like(p) * 0.05)
     path = str(tmp_path / "hf")
     model.save_pretrained(path, safe_serialization=True)
     llm = LLM(path, dtype="float32", device="cpu", max_model_len=128, num_gpu_blocks_override=32, max_num_seqs=4,

@@ -62,6 +62,24 @@ class LlamaMLP(nn.Module):
         return tp.row_linear(act, self.down_proj)
 
 
+def _layer_window(cfg: ModelConfig, layer_idx: int) -> int | None:
+    """Sliding-window width of a layer.  Newer configs list ``layer_types`` per layer ("sliding_attention" /
+    "full_attention"); older ones switch the window on for the whole model (Mistral) or for the layers from
+    ``max_window_layers`` on (Qwen2 with ``use_sliding_window``)."""
+    window = cfg.get("sliding_window")
+    if not window:
+        return None
+    types = cfg.get("layer_types")
+    if types and layer_idx < len(types):
+        return int(window) if types[layer_idx] == "sliding_attention" else None
+    if not cfg.get("use_sliding_window", cfg.get("model_type") == "mistral"):
+        return None
+    first = cfg.get("max_window_layers")
+    if first is not None and cfg.get("model_type") in ("qwen2", "qwen2_moe", "qwen3", "qwen3_moe") and layer_idx < int(first):
+        return None
+    return int(window)
+
+
 def _layer_uses_rope(cfg: ModelConfig, layer_idx: int) -> bool:
     """SmolLM3-style ``no_rope_layers``: a 0 entry switches the rotation off for that layer."""
     flags = cfg.get("no_rope_layers")
@@ -80,7 +98,7 @@ class LlamaAttention(nn.Module):
                                         f"{prefix}.o_proj")
         has_qk_norm = cfg.get("model_type") in ("qwen3", "qwen3_moe", "dots1") or bool(cfg.get("use_qk_norm", False))
         qk_eps = cfg.get("rms_norm_eps", 1e-6) if has_qk_norm else None
-        sw = cfg.get("sliding_window") if cfg.get("use_sliding_window", cfg.get("model_type") == "mistral") else None
+        sw = _layer_window(cfg, layer_idx)
         scale = float(cfg.get("attention_multiplier") or hd ** -0.5)      # Granite scales scores by a config value
         self.attn = Attention(self.qkv_proj.num_heads, self.qkv_proj.num_kv_heads, hd, scale, layer_idx,
                               float(cfg.get("rope_theta", 1e4)), cfg.max_model_len, cfg.get("rope_scaling"),

@@ -229,9 +229,12 @@ class ModelRunner:
         spec_fn = getattr(self.model, "kv_cache_spec", None)
         if spec_fn is not None:
             return spec_fn(self.block_size, nbytes)
-        attn = self.model.attention_layers()[0]
-        return KVCacheSpec(self.block_size, attn.num_kv_heads, attn.head_dim, nbytes, "full",
-                           attn.sliding_window)
+        layers = self.model.attention_layers()
+        attn = layers[0]
+        # blocks that slid out of the window can be given back only if no layer still reads them
+        windows = {a.sliding_window for a in layers}
+        window = attn.sliding_window if len(windows) == 1 else None
+        return KVCacheSpec(self.block_size, attn.num_kv_heads, attn.head_dim, nbytes, "full", window)
 
     def num_local_layers(self) -> int:
         return len(self.model.attention_layers())

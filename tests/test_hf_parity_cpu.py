@@ -299,3 +299,15 @@ def test_glm_and_smollm3(tmp_path):
     cfg = SmolLM3Config(**{**COMMON, "num_hidden_layers": 4}, no_rope_layers=[1, 1, 1, 0], no_rope_layer_interval=4,
                         use_sliding_window=False, pad_token_id=0)
     _check(tmp_path / "smol", cfg, SmolLM3ForCausalLM, init_std=0.08)
+
+
+def test_per_layer_sliding_window(tmp_path):
+    """``layer_types`` mixes windowed and full-attention layers; prompts longer than the window exercise the mask,
+    and blocks outside the window must stay allocated for the full-attention layer."""
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+    cfg = Qwen3Config(**COMMON, head_dim=16, sliding_window=6, use_sliding_window=True, max_window_layers=0,
+                      layer_types=["sliding_attention", "full_attention"])
+    _check(tmp_path / "mixed", cfg, Qwen3ForCausalLM, init_std=0.08)
+    cfg = Qwen3Config(**COMMON, head_dim=16, sliding_window=6, use_sliding_window=True, max_window_layers=0,
+                      layer_types=["sliding_attention", "sliding_attention"])
+    _check(tmp_path / "all", cfg, Qwen3ForCausalLM, init_std=0.08)

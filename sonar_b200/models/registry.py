@@ -7,6 +7,7 @@ import importlib
 _MODELS: dict[str, tuple[str, str]] = {
     "LlamaForCausalLM": ("sonar_b200.models.llama", "LlamaForCausalLM"),
     "MistralForCausalLM": ("sonar_b200.models.llama", "LlamaForCausalLM"),
+    "MinistralForCausalLM": ("sonar_b200.models.llama", "LlamaForCausalLM"),
     "SeedOssForCausalLM": ("sonar_b200.models.llama", "LlamaForCausalLM"),
     "Qwen2ForCausalLM": ("sonar_b200.models.llama", "LlamaForCausalLM"),
     "Qwen3ForCausalLM": ("sonar_b200.models.llama", "LlamaForCausalLM"),

@@ -311,3 +311,9 @@ def test_per_layer_sliding_window(tmp_path):
     cfg = Qwen3Config(**COMMON, head_dim=16, sliding_window=6, use_sliding_window=True, max_window_layers=0,
                       layer_types=["sliding_attention", "sliding_attention"])
     _check(tmp_path / "all", cfg, Qwen3ForCausalLM, init_std=0.08)
+
+
+def test_ministral_alternating_windows(tmp_path):
+    from transformers import MinistralConfig, MinistralForCausalLM
+    cfg = MinistralConfig(**COMMON, head_dim=16, sliding_window=6, layer_types=["sliding_attention", "full_attention"])
+    _check(tmp_path, cfg, MinistralForCausalLM, init_std=0.08)

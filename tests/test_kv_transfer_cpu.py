@@ -124,3 +124,33 @@ def test_config_and_registry(tmp_path):
                            kv_connector_module_path="sonar_b200.distributed.kv_transfer",
                            kv_connector_extra_config={"shared_storage_path": str(tmp_path)})
     assert isinstance(create_connector(cfg, "worker"), SharedStorageConnector)
+
+
+def test_shared_storage_with_tensor_parallel_ranks(tmp_path):
+    """Every tensor-parallel rank saves and loads its own shard of a block; a block counts as present only when
+    all ranks' files exist."""
+    import sys
+    sys.path.insert(0, os.path.dirname(__file__))
+    from tp_common import make_checkpoint
+    ckpt = make_checkpoint(str(tmp_path / "ckpt"), "tiny-llama", dtype=torch.float32)
+    store = tmp_path / "kv"
+    kw = dict(dtype="float32", max_model_len=128, num_gpu_blocks_override=24, device="cpu", max_num_seqs=2,
+              max_num_batched_tokens=64, skip_tokenizer_init=True, tensor_parallel_size=2,
+              distributed_executor_backend="mp")
+    sp = SamplingParams(max_tokens=5, temperature=0, ignore_eos=True, detokenize=False)
+    prompt = {"prompt_token_ids": list(range(20, 20 + 40))}        # 2 full blocks
+    producer = LLM(ckpt, **kw, kv_transfer_config=_kvt(store, "kv_producer"))
+    want = producer.generate([prompt], sp)[0].outputs[0].token_ids
+    producer.shutdown()
+    files = sorted(f for _, _, fs in os.walk(store) for f in fs)
+    assert len(files) == 4 and sum(f.endswith(".r0of2.kv") for f in files) == 2     # 2 full blocks × 2 ranks
+    consumer = LLM(ckpt, **kw, kv_transfer_config=_kvt(store, "kv_consumer"))
+    out = consumer.generate([prompt], sp)[0]
+    assert out.outputs[0].token_ids == want and out.num_cached_tokens == 32
+    # with one rank's file missing the block is not offered
+    victim = next(os.path.join(d, f) for d, _, fs in os.walk(store) for f in fs if f.endswith(".r1of2.kv"))
+    os.remove(victim)
+    consumer.llm_engine.reset_prefix_cache()
+    out = consumer.generate([prompt], sp)[0]
+    assert out.outputs[0].token_ids == want and out.num_cached_tokens < 32
+    consumer.shutdown()

@@ -315,3 +315,34 @@ class GlmForCausalLM(Glm4ForCausalLM):
     """GLM-4-9B (HF layout): the GLM-4 checkpoint conventions (fused ``gate_up_proj``, interleaved rotary on half of
     each head, q/k/v bias) on plain pre-norm blocks."""
     model_cls = LlamaModel
+
+
+class PlainMLP(nn.Module):
+    """Non-gated feed-forward block ``down(act(up(x)))`` (Arcee: ReLU²)."""
+
+    def __init__(self, hidden: int, inter: int, act: str, dtype, device, quant, prefix: str) -> None:
+        from sonar_b200.layers.linear import ColumnParallelLinear, RowParallelLinear
+        super().__init__()
+        self.act = act
+        self.up_proj = ColumnParallelLinear(hidden, [inter], False, dtype, device, quant, f"{prefix}.up_proj")
+        self.down_proj = RowParallelLinear(inter, hidden, False, dtype, device, quant, f"{prefix}.down_proj")
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        tp = get_tp_context()
+        return tp.row_linear(ops.activation(tp.col_linear(x, self.up_proj), self.act), self.down_proj)
+
+
+class ArceeDecoderLayer(LlamaDecoderLayer):
+    def _make_mlp(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> nn.Module:
+        return PlainMLP(cfg.hidden_size, int(cfg.get("intermediate_size")), cfg.get("hidden_act", "relu2"), cfg.dtype,
+                        device, cfg.quantization, prefix)
+
+
+class ArceeModel(LlamaModel):
+    layer_cls = ArceeDecoderLayer
+
+
+class ArceeForCausalLM(LlamaForCausalLM):
+    """Arcee AFM: the Llama block with a non-gated ReLU² feed-forward."""
+    model_cls = ArceeModel
+    stacked_params = [(".q_proj.", ".qkv_proj.", "q"), (".k_proj.", ".qkv_proj.", "k"), (".v_proj.", ".qkv_proj.", "v")]

@@ -27,6 +27,7 @@ _MODELS: dict[str, tuple[str, str]] = {
     "GlmForCausalLM": ("sonar_b200.models.llama_variants", "GlmForCausalLM"),
     "SmolLM3ForCausalLM": ("sonar_b200.models.llama", "LlamaForCausalLM"),
     "Glm4ForCausalLM": ("sonar_b200.models.llama_variants", "Glm4ForCausalLM"),
+    "ArceeForCausalLM": ("sonar_b200.models.llama_variants", "ArceeForCausalLM"),
     "Glm4MoeForCausalLM": ("sonar_b200.models.llama_variants", "Glm4MoeForCausalLM"),
     "Ernie4_5_MoeForCausalLM": ("sonar_b200.models.llama_variants", "Ernie45MoeForCausalLM"),
     "Dots1ForCausalLM": ("sonar_b200.models.llama_variants", "Dots1ForCausalLM"),

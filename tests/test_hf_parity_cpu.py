@@ -317,3 +317,8 @@ def test_ministral_alternating_windows(tmp_path):
     from transformers import MinistralConfig, MinistralForCausalLM
     cfg = MinistralConfig(**COMMON, head_dim=16, sliding_window=6, layer_types=["sliding_attention", "full_attention"])
     _check(tmp_path, cfg, MinistralForCausalLM, init_std=0.08)
+
+
+def test_arcee_relu2_mlp(tmp_path):
+    from transformers import ArceeConfig, ArceeForCausalLM
+    _check(tmp_path, ArceeConfig(**COMMON, head_dim=16, hidden_act="relu2"), ArceeForCausalLM, init_std=0.08)

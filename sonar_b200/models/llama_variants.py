@@ -346,3 +346,76 @@ class ArceeForCausalLM(LlamaForCausalLM):
     """Arcee AFM: the Llama block with a non-gated ReLU² feed-forward."""
     model_cls = ArceeModel
     stacked_params = [(".q_proj.", ".qkv_proj.", "q"), (".k_proj.", ".qkv_proj.", "k"), (".v_proj.", ".qkv_proj.", "v")]
+
+
+class Olmo2Attention(nn.Module):
+    """q and k are RMS-normalised over the WHOLE projection (all heads together) before the rotation."""
+
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> None:
+        from sonar_b200.layers.attention import Attention
+        from sonar_b200.layers.linear import QKVParallelLinear, RowParallelLinear
+        from sonar_b200.layers.norm import RMSNorm
+        from sonar_b200.models.llama import _layer_window
+        from sonar_b200.parallel import state
+        super().__init__()
+        if state.tp_world_size() > 1:
+            raise ValueError("OLMo-2's whole-projection q/k norm is not sharded: run it with tensor_parallel_size=1")
+        h, hd = cfg.hidden_size, cfg.head_dim
+        self.qkv_proj = QKVParallelLinear(h, hd, cfg.num_attention_heads, cfg.num_kv_heads, bool(cfg.get("attention_bias", False)),
+                                          cfg.dtype, device, cfg.quantization, f"{prefix}.qkv_proj")
+        self.o_proj = RowParallelLinear(cfg.num_attention_heads * hd, h, False, cfg.dtype, device, cfg.quantization,
+                                        f"{prefix}.o_proj")
+        eps = cfg.get("rms_norm_eps", 1e-6)
+        self.q_norm = RMSNorm(cfg.num_attention_heads * hd, eps, cfg.dtype, device)
+        self.k_norm = RMSNorm(cfg.num_kv_heads * hd, eps, cfg.dtype, device)
+        self.qd, self.kd = cfg.num_attention_heads * hd, cfg.num_kv_heads * hd
+        self.attn = Attention(cfg.num_attention_heads, cfg.num_kv_heads, hd, hd ** -0.5, layer_idx,
+                              float(cfg.get("rope_theta", 1e4)), cfg.max_model_len, cfg.get("rope_scaling"),
+                              _layer_window(cfg, layer_idx), device, None, cfg.dtype)
+
+    def forward(self, x: torch.Tensor, meta) -> torch.Tensor:
+        qkv = self.qkv_proj.apply(x)
+        q = ops.rms_norm(qkv[:, : self.qd].contiguous(), self.q_norm.weight, self.q_norm.eps)
+        k = ops.rms_norm(qkv[:, self.qd: self.qd + self.kd].contiguous(), self.k_norm.weight, self.k_norm.eps)
+        qkv = torch.cat([q, k, qkv[:, self.qd + self.kd:]], dim=-1)
+        return self.o_proj.apply(self.attn(qkv, meta))
+
+
+class Olmo2DecoderLayer(nn.Module):
+    """Post-norm block: ``x += norm(attn(x)); x += norm(mlp(x))`` — the norms sit on the branch outputs."""
+
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> None:
+        from sonar_b200.layers.norm import RMSNorm
+        super().__init__()
+        eps = cfg.get("rms_norm_eps", 1e-6)
+        self.self_attn = Olmo2Attention(cfg, layer_idx, device, f"{prefix}.self_attn")
+        self.mlp = LlamaMLP(cfg.hidden_size, int(cfg.get("intermediate_size")), cfg.dtype, device, cfg.quantization,
+                            f"{prefix}.mlp")
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, eps, cfg.dtype, device)
+        self.post_feedforward_layernorm = RMSNorm(cfg.hidden_size, eps, cfg.dtype, device)
+
+    def forward(self, h, residual, meta):
+        x = h if residual is None else h + residual
+        x = x + self.post_attention_layernorm(self.self_attn(x, meta))
+        x = x + self.post_feedforward_layernorm(self.mlp(x))
+        return x, None
+
+
+class Olmo2Model(LlamaModel):
+    layer_cls = Olmo2DecoderLayer
+
+
+class Olmo2ForCausalLM(LlamaForCausalLM):
+    """OLMo-2 / OLMo-3: post-norm blocks and a q/k norm over all heads at once (tensor-parallel size 1 only)."""
+    model_cls = Olmo2Model
+
+    def attention_layers(self):
+        return [layer.self_attn.attn for layer in self.model.layers.values()]
+
+    def map_checkpoint_name(self, name: str):
+        if ".self_attn.q_norm." in name or ".self_attn.k_norm." in name:
+            return name, None                      # whole-projection norms are ordinary modules here
+        return super().map_checkpoint_name(name)
+
+
+NEEDS_REPLICATED_ACTIVATIONS |= {"Olmo2ForCausalLM", "Olmo3ForCausalLM"}

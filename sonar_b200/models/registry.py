@@ -27,6 +27,8 @@ _MODELS: dict[str, tuple[str, str]] = {
     "GlmForCausalLM": ("sonar_b200.models.llama_variants", "GlmForCausalLM"),
     "SmolLM3ForCausalLM": ("sonar_b200.models.llama", "LlamaForCausalLM"),
     "Glm4ForCausalLM": ("sonar_b200.models.llama_variants", "Glm4ForCausalLM"),
+    "Olmo2ForCausalLM": ("sonar_b200.models.llama_variants", "Olmo2ForCausalLM"),
+    "Olmo3ForCausalLM": ("sonar_b200.models.llama_variants", "Olmo2ForCausalLM"),
     "ArceeForCausalLM": ("sonar_b200.models.llama_variants", "ArceeForCausalLM"),
     "Glm4MoeForCausalLM": ("sonar_b200.models.llama_variants", "Glm4MoeForCausalLM"),
     "Ernie4_5_MoeForCausalLM": ("sonar_b200.models.llama_variants", "Ernie45MoeForCausalLM"),

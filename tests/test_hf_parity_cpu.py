@@ -322,3 +322,17 @@ def test_ministral_alternating_windows(tmp_path):
 def test_arcee_relu2_mlp(tmp_path):
     from transformers import ArceeConfig, ArceeForCausalLM
     _check(tmp_path, ArceeConfig(**COMMON, head_dim=16, hidden_act="relu2"), ArceeForCausalLM, init_std=0.08)
+
+
+def test_olmo2_post_norm_and_whole_projection_qk_norm(tmp_path):
+    from transformers import Olmo2Config, Olmo2ForCausalLM
+    _check(tmp_path, Olmo2Config(**COMMON, pad_token_id=0), Olmo2ForCausalLM, init_std=0.08)
+
+
+def test_olmo3_sliding_layers(tmp_path):
+    transformers_mod = pytest.importorskip("transformers")
+    if not hasattr(transformers_mod, "Olmo3ForCausalLM"):
+        pytest.skip("this transformers build has no OLMo-3")
+    from transformers import Olmo3Config, Olmo3ForCausalLM
+    cfg = Olmo3Config(**COMMON, pad_token_id=0, sliding_window=6, layer_types=["sliding_attention", "full_attention"])
+    _check(tmp_path, cfg, Olmo3ForCausalLM, init_std=0.08)

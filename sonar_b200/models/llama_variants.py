@@ -419,3 +419,31 @@ class Olmo2ForCausalLM(LlamaForCausalLM):
 
 
 NEEDS_REPLICATED_ACTIVATIONS |= {"Olmo2ForCausalLM", "Olmo3ForCausalLM"}
+
+
+class OlmoeDecoderLayer(LlamaDecoderLayer):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> None:
+        super().__init__(cfg, layer_idx, device, prefix)
+        self.self_attn = Olmo2Attention(cfg, layer_idx, device, f"{prefix}.self_attn")
+
+    def _make_mlp(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> nn.Module:
+        return SparseMoeBlock(cfg, device, prefix, bool(cfg.get("_expert_parallel", False)),
+                              cfg.get("_expert_placement", "linear"))
+
+
+class OlmoeModel(LlamaModel):
+    layer_cls = OlmoeDecoderLayer
+
+
+class OlmoeForCausalLM(Qwen3MoeForCausalLM):
+    """OLMoE: pre-norm blocks, OLMo's whole-projection q/k norm, a softmax top-k mixture (weights not renormalised
+    unless the config says so); tensor-parallel size 1 only."""
+    model_cls = OlmoeModel
+
+    def map_checkpoint_name(self, name: str):
+        if ".self_attn.q_norm." in name or ".self_attn.k_norm." in name:
+            return name, None
+        return super().map_checkpoint_name(name)
+
+
+NEEDS_REPLICATED_ACTIVATIONS |= {"OlmoeForCausalLM"}

@@ -336,3 +336,9 @@ def test_olmo3_sliding_layers(tmp_path):
     from transformers import Olmo3Config, Olmo3ForCausalLM
     cfg = Olmo3Config(**COMMON, pad_token_id=0, sliding_window=6, layer_types=["sliding_attention", "full_attention"])
     _check(tmp_path, cfg, Olmo3ForCausalLM, init_std=0.08)
+
+
+def test_olmoe(tmp_path):
+    from transformers import OlmoeConfig, OlmoeForCausalLM
+    cfg = OlmoeConfig(**COMMON, pad_token_id=0, num_experts=8, num_experts_per_tok=2, norm_topk_prob=False)
+    _check(tmp_path, cfg, OlmoeForCausalLM, init_std=0.08)

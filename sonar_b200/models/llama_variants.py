@@ -447,3 +447,52 @@ class OlmoeForCausalLM(Qwen3MoeForCausalLM):
 
 
 NEEDS_REPLICATED_ACTIVATIONS |= {"OlmoeForCausalLM"}
+
+
+class Exaone4Attention(nn.Module):
+    """Per-head q/k norm (in the rope kernel); sliding-window layers rotate, global layers of a hybrid model do not."""
+
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> None:
+        from sonar_b200.layers.attention import Attention
+        from sonar_b200.layers.linear import QKVParallelLinear, RowParallelLinear
+        from sonar_b200.models.llama import _layer_window
+        super().__init__()
+        h, hd = cfg.hidden_size, cfg.head_dim
+        self.qkv_proj = QKVParallelLinear(h, hd, cfg.num_attention_heads, cfg.num_kv_heads, False, cfg.dtype, device,
+                                          cfg.quantization, f"{prefix}.qkv_proj")
+        self.o_proj = RowParallelLinear(cfg.num_attention_heads * hd, h, False, cfg.dtype, device, cfg.quantization,
+                                        f"{prefix}.o_proj")
+        window = _layer_window(cfg, layer_idx)
+        hybrid = bool(cfg.get("sliding_window"))
+        self.attn = Attention(self.qkv_proj.num_heads, self.qkv_proj.num_kv_heads, hd, hd ** -0.5, layer_idx,
+                              float(cfg.get("rope_theta", 1e4)), cfg.max_model_len, cfg.get("rope_scaling"), window,
+                              device, cfg.get("rms_norm_eps", 1e-6), cfg.dtype,
+                              use_rope=(not hybrid) or window is not None)
+
+    def forward(self, x: torch.Tensor, meta) -> torch.Tensor:
+        tp = get_tp_context()
+        return tp.row_linear(self.attn(tp.col_linear(x, self.qkv_proj), meta), self.o_proj)
+
+
+class Exaone4DecoderLayer(Olmo2DecoderLayer):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> None:
+        nn.Module.__init__(self)
+        from sonar_b200.layers.norm import RMSNorm
+        eps = cfg.get("rms_norm_eps", 1e-6)
+        self.self_attn = Exaone4Attention(cfg, layer_idx, device, f"{prefix}.self_attn")
+        self.mlp = LlamaMLP(cfg.hidden_size, int(cfg.get("intermediate_size")), cfg.dtype, device, cfg.quantization,
+                            f"{prefix}.mlp")
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, eps, cfg.dtype, device)
+        self.post_feedforward_layernorm = RMSNorm(cfg.hidden_size, eps, cfg.dtype, device)
+
+
+class Exaone4Model(LlamaModel):
+    layer_cls = Exaone4DecoderLayer
+
+
+class Exaone4ForCausalLM(LlamaForCausalLM):
+    """EXAONE-4: post-norm blocks, per-head q/k norm, local (rotated, windowed) and global (unrotated) layers."""
+    model_cls = Exaone4Model
+
+
+NEEDS_REPLICATED_ACTIVATIONS |= {"Exaone4ForCausalLM"}

@@ -342,3 +342,12 @@ def test_olmoe(tmp_path):
     from transformers import OlmoeConfig, OlmoeForCausalLM
     cfg = OlmoeConfig(**COMMON, pad_token_id=0, num_experts=8, num_experts_per_tok=2, norm_topk_prob=False)
     _check(tmp_path, cfg, OlmoeForCausalLM, init_std=0.08)
+
+
+def test_exaone4_hybrid_and_plain(tmp_path):
+    from transformers import Exaone4Config, Exaone4ForCausalLM
+    hybrid = Exaone4Config(**{**COMMON, "num_hidden_layers": 4}, head_dim=16, sliding_window=6, sliding_window_pattern=4,
+                           layer_types=["sliding_attention"] * 3 + ["full_attention"])
+    _check(tmp_path / "hybrid", hybrid, Exaone4ForCausalLM, init_std=0.08)
+    plain = Exaone4Config(**COMMON, head_dim=16, sliding_window=None, layer_types=["full_attention"] * 2)
+    _check(tmp_path / "plain", plain, Exaone4ForCausalLM, init_std=0.08)

@@ -1,0 +1,106 @@
+"""Decoders built on LayerNorm (with bias) and a plain GELU feed-forward: StarCoder2.
+
+The attention, KV cache, rotary embedding and every GEMM are this package's kernels; the LayerNorm itself is
+the framework's ``layer_norm`` (no kernel of its own here — these families are outside the benchmark set), so
+the blocks keep the residual stream explicit instead of using the fused add+RMSNorm path, and run with
+replicated activations under tensor parallelism.
+
+Parity: ``aphrodite/model_executor/models/starcoder2.py``.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from sonar_b200 import ops
+from sonar_b200.config import ModelConfig
+from sonar_b200.layers.linear import ColumnParallelLinear, RowParallelLinear
+from sonar_b200.models.llama import LlamaAttention, LlamaForCausalLM, LlamaModel
+from sonar_b200.parallel.tp_ops import get_tp_context
+
+
+class LayerNorm(nn.Module):
+    def __init__(self, size: int, eps: float, dtype, device) -> None:
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(size, dtype=dtype, device=device), requires_grad=False)
+        self.bias = nn.Parameter(torch.zeros(size, dtype=dtype, device=device), requires_grad=False)
+        self.eps = eps
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return F.layer_norm(x, (x.shape[-1],), self.weight, self.bias, self.eps)
+
+
+class BiasedMLP(nn.Module):
+    """``c_proj(act(c_fc(x)))`` with biases."""
+
+    def __init__(self, cfg: ModelConfig, device, prefix: str) -> None:
+        super().__init__()
+        h, inter, bias = cfg.hidden_size, int(cfg.get("intermediate_size")), bool(cfg.get("use_bias", True))
+        self.act = {"gelu_pytorch_tanh": "gelu_tanh", "gelu_new": "gelu_new", "gelu": "gelu"}.get(
+            cfg.get("hidden_act", "gelu_pytorch_tanh"), cfg.get("hidden_act"))
+        self.c_fc = ColumnParallelLinear(h, [inter], bias, cfg.dtype, device, cfg.quantization, f"{prefix}.c_fc")
+        self.c_proj = RowParallelLinear(inter, h, bias, cfg.dtype, device, cfg.quantization, f"{prefix}.c_proj")
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        tp = get_tp_context()
+        return tp.row_linear(ops.activation(tp.col_linear(x, self.c_fc), self.act), self.c_proj)
+
+
+class Starcoder2Attention(LlamaAttention):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> None:
+        super().__init__(cfg, layer_idx, device, prefix)
+        if cfg.get("use_bias", True):       # q/k/v bias comes with attention_bias; the output projection has one too
+            self.o_proj = RowParallelLinear(cfg.num_attention_heads * cfg.head_dim, cfg.hidden_size, True, cfg.dtype,
+                                            device, cfg.quantization, f"{prefix}.o_proj")
+
+
+class Starcoder2DecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> None:
+        super().__init__()
+        eps = float(cfg.get("norm_epsilon", cfg.get("layer_norm_eps", 1e-5)))
+        self.self_attn = Starcoder2Attention(cfg, layer_idx, device, f"{prefix}.self_attn")
+        self.mlp = BiasedMLP(cfg, device, f"{prefix}.mlp")
+        self.input_layernorm = LayerNorm(cfg.hidden_size, eps, cfg.dtype, device)
+        self.post_attention_layernorm = LayerNorm(cfg.hidden_size, eps, cfg.dtype, device)
+
+    def forward(self, h, residual, meta):
+        x = h if residual is None else h + residual
+        x = x + self.self_attn(self.input_layernorm(x), meta)
+        x = x + self.mlp(self.post_attention_layernorm(x))
+        return x, None
+
+
+class Starcoder2Model(LlamaModel):
+    layer_cls = Starcoder2DecoderLayer
+
+    def __init__(self, cfg: ModelConfig, device) -> None:
+        super().__init__(cfg, device)
+        if self.is_last:
+            self.norm = LayerNorm(cfg.hidden_size, float(cfg.get("norm_epsilon", 1e-5)), cfg.dtype, device)
+
+    def forward(self, input_ids, meta, intermediate=None, embed_patch=None):
+        tp = get_tp_context()
+        if self.is_first:
+            h = tp.embed_reduce(self.embed_tokens(input_ids))
+            if embed_patch is not None:
+                h = h.index_copy(0, embed_patch[0], embed_patch[1].to(h.dtype))
+            residual = None
+        else:
+            h, residual = intermediate
+        for layer in self.layers.values():
+            h, residual = layer(h, residual, meta)
+        if not self.is_last:
+            return h, residual
+        return self.norm(h if residual is None else h + residual)
+
+
+class Starcoder2ForCausalLM(LlamaForCausalLM):
+    model_cls = Starcoder2Model
+    stacked_params = [(".q_proj.", ".qkv_proj.", "q"), (".k_proj.", ".qkv_proj.", "k"), (".v_proj.", ".qkv_proj.", "v")]
+
+    def __init__(self, cfg: ModelConfig, device=None) -> None:
+        cfg.hf_config.setdefault("attention_bias", bool(cfg.get("use_bias", True)))
+        if cfg.get("sliding_window") and "use_sliding_window" not in cfg.hf_config:
+            cfg.hf_config["use_sliding_window"] = True
+        super().__init__(cfg, device)

@@ -496,3 +496,5 @@ class Exaone4ForCausalLM(LlamaForCausalLM):
 
 
 NEEDS_REPLICATED_ACTIVATIONS |= {"Exaone4ForCausalLM"}
+
+NEEDS_REPLICATED_ACTIVATIONS |= {"Starcoder2ForCausalLM"}

@@ -31,6 +31,7 @@ _MODELS: dict[str, tuple[str, str]] = {
     "Olmo3ForCausalLM": ("sonar_b200.models.llama_variants", "Olmo2ForCausalLM"),
     "OlmoeForCausalLM": ("sonar_b200.models.llama_variants", "OlmoeForCausalLM"),
     "Exaone4ForCausalLM": ("sonar_b200.models.llama_variants", "Exaone4ForCausalLM"),
+    "Starcoder2ForCausalLM": ("sonar_b200.models.layernorm_family", "Starcoder2ForCausalLM"),
     "ArceeForCausalLM": ("sonar_b200.models.llama_variants", "ArceeForCausalLM"),
     "Glm4MoeForCausalLM": ("sonar_b200.models.llama_variants", "Glm4MoeForCausalLM"),
     "Ernie4_5_MoeForCausalLM": ("sonar_b200.models.llama_variants", "Ernie45MoeForCausalLM"),

@@ -351,3 +351,12 @@ def test_exaone4_hybrid_and_plain(tmp_path):
     _check(tmp_path / "hybrid", hybrid, Exaone4ForCausalLM, init_std=0.08)
     plain = Exaone4Config(**COMMON, head_dim=16, sliding_window=None, layer_types=["full_attention"] * 2)
     _check(tmp_path / "plain", plain, Exaone4ForCausalLM, init_std=0.08)
+
+
+def test_starcoder2_layernorm_family(tmp_path):
+    from transformers import Starcoder2Config, Starcoder2ForCausalLM
+    kw = {k: v for k, v in COMMON.items() if k not in ("rms_norm_eps",)}
+    cfg = Starcoder2Config(**kw, use_bias=True, sliding_window=None, norm_epsilon=1e-5, hidden_act="gelu_pytorch_tanh")
+    _check(tmp_path / "full", cfg, Starcoder2ForCausalLM, init_std=0.08)
+    cfg = Starcoder2Config(**kw, use_bias=True, sliding_window=6, norm_epsilon=1e-5, hidden_act="gelu_pytorch_tanh")
+    _check(tmp_path / "window", cfg, Starcoder2ForCausalLM, init_std=0.08)

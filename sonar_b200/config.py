@@ -124,6 +124,13 @@ def _normalise_hf_config(cfg: dict[str, Any]) -> dict[str, Any]:
             if k not in ("architectures", "model_type") and k not in cfg:
                 cfg[k] = v
         cfg.setdefault("text_model_type", tc.get("model_type"))
+    # GPT-2 style key names
+    for old, new in (("n_embd", "hidden_size"), ("n_layer", "num_hidden_layers"), ("n_head", "num_attention_heads"),
+                     ("n_positions", "max_position_embeddings")):
+        if old in cfg and new not in cfg:
+            cfg[new] = cfg[old]
+    if "n_embd" in cfg and not cfg.get("intermediate_size"):
+        cfg["intermediate_size"] = cfg.get("n_inner") or 4 * cfg["n_embd"]
     rp = cfg.get("rope_parameters")
     if isinstance(rp, dict):
         if "rope_theta" in rp:

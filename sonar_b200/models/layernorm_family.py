@@ -104,3 +104,56 @@ class Starcoder2ForCausalLM(LlamaForCausalLM):
         if cfg.get("sliding_window") and "use_sliding_window" not in cfg.hf_config:
             cfg.hf_config["use_sliding_window"] = True
         super().__init__(cfg, device)
+
+
+class GPT2Model(Starcoder2Model):
+    """Learned absolute positions (``wpe``) added to the token embeddings; attention layers do not rotate."""
+
+    def __init__(self, cfg: ModelConfig, device) -> None:
+        super().__init__(cfg, device)
+        self.wpe = nn.Embedding(int(cfg.get("max_position_embeddings", 1024)), cfg.hidden_size, dtype=cfg.dtype, device=device)
+
+    def forward(self, input_ids, meta, intermediate=None, embed_patch=None):
+        tp = get_tp_context()
+        h = tp.embed_reduce(self.embed_tokens(input_ids)) + self.wpe(meta.positions[: input_ids.shape[0]].long())
+        if embed_patch is not None:
+            h = h.index_copy(0, embed_patch[0], embed_patch[1].to(h.dtype))
+        residual = None
+        for layer in self.layers.values():
+            h, residual = layer(h, residual, meta)
+        return self.norm(h if residual is None else h + residual)
+
+
+class GPT2LMHeadModel(Starcoder2ForCausalLM):
+    """GPT-2: checkpoint tensors are ``Conv1D`` weights (``[in, out]``) with a fused ``c_attn``; they are transposed
+    and cut into q / k / v when loaded."""
+    model_cls = GPT2Model
+
+    def __init__(self, cfg: ModelConfig, device=None) -> None:
+        hf = cfg.hf_config
+        hf.setdefault("no_rope_layers", [0] * int(hf["num_hidden_layers"]))
+        hf.setdefault("tie_word_embeddings", True)
+        hf.setdefault("use_bias", True)
+        hf.setdefault("norm_epsilon", hf.get("layer_norm_epsilon", 1e-5))
+        hf.setdefault("hidden_act", hf.get("activation_function", "gelu_new"))
+        super().__init__(cfg, device)
+
+    _RENAME = (("transformer.wte.", "model.embed_tokens."), ("transformer.wpe.", "model.wpe."), ("transformer.ln_f.", "model.norm."),
+               ("transformer.h.", "model.layers."), (".ln_1.", ".input_layernorm."), (".ln_2.", ".post_attention_layernorm."),
+               (".attn.c_proj.", ".self_attn.o_proj."), (".attn.c_attn.", ".self_attn.qkv_proj."))
+
+    def load_special_weight(self, name: str, tensor: torch.Tensor) -> bool:
+        from sonar_b200.loader.weights import _assign
+        if name.endswith((".attn.bias", ".attn.masked_bias")):
+            return True                                   # causal-mask buffers of old checkpoints
+        for old, new in self._RENAME:
+            name = name.replace(old, new)
+        conv = any(s in name for s in (".qkv_proj.weight", ".o_proj.weight", ".c_fc.weight", ".mlp.c_proj.weight"))
+        if conv:
+            tensor = tensor.t()
+        if ".self_attn.qkv_proj." in name:
+            q, k, v = tensor.chunk(3, dim=0)
+            return all([_assign(self, name, part.contiguous(), sid) for part, sid in ((q, "q"), (k, "k"), (v, "v"))])
+        if name.startswith("lm_head."):
+            return True
+        return _assign(self, name, tensor.contiguous() if conv else tensor, None)

@@ -498,3 +498,4 @@ class Exaone4ForCausalLM(LlamaForCausalLM):
 NEEDS_REPLICATED_ACTIVATIONS |= {"Exaone4ForCausalLM"}
 
 NEEDS_REPLICATED_ACTIVATIONS |= {"Starcoder2ForCausalLM"}
+NEEDS_REPLICATED_ACTIVATIONS |= {"GPT2LMHeadModel"}

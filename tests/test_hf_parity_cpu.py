@@ -360,3 +360,9 @@ def test_starcoder2_layernorm_family(tmp_path):
     _check(tmp_path / "full", cfg, Starcoder2ForCausalLM, init_std=0.08)
     cfg = Starcoder2Config(**kw, use_bias=True, sliding_window=6, norm_epsilon=1e-5, hidden_act="gelu_pytorch_tanh")
     _check(tmp_path / "window", cfg, Starcoder2ForCausalLM, init_std=0.08)
+
+
+def test_gpt2(tmp_path):
+    from transformers import GPT2Config, GPT2LMHeadModel
+    cfg = GPT2Config(vocab_size=256, n_embd=64, n_layer=2, n_head=4, n_positions=256)
+    _check(tmp_path, cfg, GPT2LMHeadModel, init_std=0.08)

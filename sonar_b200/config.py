@@ -135,6 +135,8 @@ def _normalise_hf_config(cfg: dict[str, Any]) -> dict[str, Any]:
     if isinstance(rp, dict):
         if "rope_theta" in rp:
             cfg.setdefault("rope_theta", rp["rope_theta"])
+        if "partial_rotary_factor" in rp:
+            cfg.setdefault("partial_rotary_factor", rp["partial_rotary_factor"])
         if rp.get("rope_type", rp.get("type", "default")) != "default" and not cfg.get("rope_scaling"):
             cfg["rope_scaling"] = {k: v for k, v in rp.items() if k != "rope_theta"}
     if cfg.get("dtype") and not cfg.get("torch_dtype"):

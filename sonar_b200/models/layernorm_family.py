@@ -157,3 +157,57 @@ class GPT2LMHeadModel(Starcoder2ForCausalLM):
         if name.startswith("lm_head."):
             return True
         return _assign(self, name, tensor.contiguous() if conv else tensor, None)
+
+
+class NeoXDecoderLayer(Starcoder2DecoderLayer):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, device, prefix: str) -> None:
+        super().__init__(cfg, layer_idx, device, prefix)
+        self.parallel = bool(cfg.get("use_parallel_residual", True))
+
+    def forward(self, h, residual, meta):
+        x = h if residual is None else h + residual
+        a = self.self_attn(self.input_layernorm(x), meta)
+        if self.parallel:        # both branches read the same input
+            return x + a + self.mlp(self.post_attention_layernorm(x)), None
+        x = x + a
+        return x + self.mlp(self.post_attention_layernorm(x)), None
+
+
+class NeoXModel(Starcoder2Model):
+    layer_cls = NeoXDecoderLayer
+
+
+class GPTNeoXForCausalLM(Starcoder2ForCausalLM):
+    """GPT-NeoX / Pythia: parallel residual blocks, rotary on the first ``rotary_pct`` of each head, and a fused
+    ``query_key_value`` whose rows are grouped per head as (q, k, v)."""
+    model_cls = NeoXModel
+
+    def __init__(self, cfg: ModelConfig, device=None) -> None:
+        hf = cfg.hf_config
+        hf.setdefault("partial_rotary_factor", hf.get("rotary_pct", 0.25))
+        hf.setdefault("use_bias", bool(hf.get("attention_bias", True)))
+        hf.setdefault("norm_epsilon", hf.get("layer_norm_eps", 1e-5))
+        hf.setdefault("hidden_act", "gelu")
+        super().__init__(cfg, device)
+
+    _RENAME = (("gpt_neox.embed_in.", "model.embed_tokens."), ("gpt_neox.final_layer_norm.", "model.norm."),
+               ("gpt_neox.layers.", "model.layers."), (".attention.dense.", ".self_attn.o_proj."),
+               (".attention.query_key_value.", ".self_attn.qkv_proj."), (".mlp.dense_h_to_4h.", ".mlp.c_fc."),
+               (".mlp.dense_4h_to_h.", ".mlp.c_proj."), ("embed_out.", "lm_head."))
+
+    def load_special_weight(self, name: str, tensor: torch.Tensor) -> bool:
+        from sonar_b200.loader.weights import _assign
+        from sonar_b200.ops.torch_ref import partial_rotary_perm
+        if "rotary_emb" in name or name.endswith((".attention.bias", ".attention.masked_bias")):
+            return True
+        for old, new in self._RENAME:
+            name = name.replace(old, new)
+        if ".self_attn.qkv_proj." not in name:
+            return _assign(self, name, tensor, None)
+        hd, heads = self.cfg.head_dim, self.cfg.num_attention_heads
+        rot = int(hd * float(self.cfg.get("partial_rotary_factor", 1.0)))
+        t = tensor.reshape(heads, 3, hd, *tensor.shape[1:])
+        perm = partial_rotary_perm(hd, rot) if rot != hd else torch.arange(hd)
+        parts = {"q": t[:, 0][:, perm], "k": t[:, 1][:, perm], "v": t[:, 2]}
+        return all([_assign(self, name, p.reshape(heads * hd, *tensor.shape[1:]).contiguous(), sid)
+                    for sid, p in parts.items()])

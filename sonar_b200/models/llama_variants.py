@@ -499,3 +499,4 @@ NEEDS_REPLICATED_ACTIVATIONS |= {"Exaone4ForCausalLM"}
 
 NEEDS_REPLICATED_ACTIVATIONS |= {"Starcoder2ForCausalLM"}
 NEEDS_REPLICATED_ACTIVATIONS |= {"GPT2LMHeadModel"}
+NEEDS_REPLICATED_ACTIVATIONS |= {"GPTNeoXForCausalLM"}

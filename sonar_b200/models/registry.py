@@ -32,6 +32,7 @@ _MODELS: dict[str, tuple[str, str]] = {
     "OlmoeForCausalLM": ("sonar_b200.models.llama_variants", "OlmoeForCausalLM"),
     "Exaone4ForCausalLM": ("sonar_b200.models.llama_variants", "Exaone4ForCausalLM"),
     "Starcoder2ForCausalLM": ("sonar_b200.models.layernorm_family", "Starcoder2ForCausalLM"),
+    "GPTNeoXForCausalLM": ("sonar_b200.models.layernorm_family", "GPTNeoXForCausalLM"),
     "GPT2LMHeadModel": ("sonar_b200.models.layernorm_family", "GPT2LMHeadModel"),
     "ArceeForCausalLM": ("sonar_b200.models.llama_variants", "ArceeForCausalLM"),
     "Glm4MoeForCausalLM": ("sonar_b200.models.llama_variants", "Glm4MoeForCausalLM"),

@@ -366,3 +366,12 @@ def test_gpt2(tmp_path):
     from transformers import GPT2Config, GPT2LMHeadModel
     cfg = GPT2Config(vocab_size=256, n_embd=64, n_layer=2, n_head=4, n_positions=256)
     _check(tmp_path, cfg, GPT2LMHeadModel, init_std=0.08)
+
+
+@pytest.mark.parametrize("parallel", [True, False])
+def test_gpt_neox(tmp_path, parallel):
+    from transformers import GPTNeoXConfig, GPTNeoXForCausalLM
+    cfg = GPTNeoXConfig(vocab_size=256, hidden_size=64, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                        max_position_embeddings=256, rotary_pct=0.25, use_parallel_residual=parallel,
+                        tie_word_embeddings=False)
+    _check(tmp_path, cfg, GPTNeoXForCausalLM, init_std=0.08)
